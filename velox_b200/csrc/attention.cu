@@ -1,0 +1,687 @@
+// Attention over the paged KV cache, for prefill portions and decode tokens alike.
+//
+// Compiled once per head size: -DVX_HEAD_DIM=<D>, D a multiple of 16 up to 256.
+//
+// What is computed follows the reference's two Triton kernels (paths inside that project):
+//   src/attention_prefill.py:62-139 and src/decode_attention.py:64-131: scores (q.k) * scale in
+//   float32, -inf where the key is after the query, online softmax over key tiles, p rounded to
+//   the cache dtype before the PV product, o = acc / l;
+//   src/decode_attention.py:132-153,188-211: a split of the key range writes o and
+//   lse = m + log l, and the merge weights the splits by exp(lse - max lse).
+// How the work is cut differs.  The host lays out *work items*; every item is one tile of rows
+// of one sequence against a range of keys.  A row is a (query token, query head of the group)
+// pair: row = token_in_portion * group + head_in_group, so the query heads that share a KV head
+// share every K/V tile they read, in prefill and in decode.  A decode token is a portion of
+// length 1.  When a key range is split, every split writes normalised partial rows and their
+// log-sum-exp to scratch and a merge kernel combines them.
+//
+// Item layout, int32[8]: {seq, row_begin, row_count, kv_begin, kv_end, partial_base, -, -}.
+//   seq < 0: the item is padding and does nothing.
+//   partial_base < 0: the item covers every key its rows may see and writes the output itself.
+//   otherwise partial rows go to partial_base + kv_head * row_count + r.
+// Visibility of key n to a row whose token is at absolute position pos:
+//   kv_begin <= n < kv_end, n <= pos, and n > pos - window when window > 0.
+// Key tiles start at multiples of the tile width from position 0, whatever kv_begin is, so the
+// float32 result of an unsplit row does not depend on how the prompt was cut into portions.
+#include "common.cuh"
+
+#include <math_constants.h>
+
+#ifndef VX_HEAD_DIM
+#error "compile with -DVX_HEAD_DIM=<head size>"
+#endif
+#if (VX_HEAD_DIM % 16) != 0 || VX_HEAD_DIM < 16 || VX_HEAD_DIM > 256
+#error "head size must be a multiple of 16 between 16 and 256"
+#endif
+
+namespace vx {
+
+constexpr int D = VX_HEAD_DIM;
+
+struct AttnArgs {
+  const void* q;            // [tokens, q_stride]; head h at h * D
+  void* out;                // [tokens, out_stride]; head h at h * D
+  const void* k_cache;      // [pages, page_size, G, D]
+  const void* v_cache;
+  const int* block_tables;  // [S, table_stride]
+  const int* q_start;       // [S] first batch row of the sequence's portion
+  const int* q_len;         // [S] tokens of the portion
+  const int* kv_len;        // [S] keys in the cache once this step's tokens are written
+  const int* items;         // [n, 8]
+  float* partial_o;         // [rows, D]
+  float* partial_lse;       // [rows], log2 units
+  int q_stride, out_stride, table_stride;
+  int num_kv_heads, group, page_size, window;
+  float scale_log2;  // softmax scale * log2(e)
+};
+
+__device__ __forceinline__ bool key_visible(int n, int pos, int kv_begin, int kv_end, int window) {
+  return n >= kv_begin && n < kv_end && n <= pos && (window <= 0 || n > pos - window);
+}
+
+// =============================================================================================
+// float32 family: FP32 pipes only.  4 warps x 4 rows, 32 keys per tile, one key per lane.
+// =============================================================================================
+constexpr int F_ROWS = 16, F_RPW = 4, F_BN = 32;
+constexpr int F_DV = (D + 31) / 32;  // output dims per lane
+
+__global__ void __launch_bounds__(128) attn_f32_kernel(AttnArgs a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float(*q_s)[D] = reinterpret_cast<float(*)[D]>(smem_raw);
+  float(*k_s)[D + 1] = reinterpret_cast<float(*)[D + 1]>(smem_raw + sizeof(float) * F_ROWS * D);
+  float(*v_s)[D + 1] = k_s + F_BN;
+  __shared__ const float* krow_ptr[F_BN];
+  __shared__ const float* vrow_ptr[F_BN];
+
+  const int* item = a.items + (size_t)blockIdx.x * 8;
+  const int seq = item[0];
+  if (seq < 0) return;
+  const int row_begin = item[1], row_count = item[2];
+  const int kv_begin = item[3], kv_end = item[4], partial_base = item[5];
+  const int kvh = blockIdx.y;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  const int q_start = a.q_start[seq], q_len = a.q_len[seq], kv_len = a.kv_len[seq];
+  const int ctx = kv_len - q_len;
+  const int* table = a.block_tables + (size_t)seq * a.table_stride;
+  const float* qbase = (const float*)a.q;
+  const float* kc = (const float*)a.k_cache;
+  const float* vc = (const float*)a.v_cache;
+
+  for (int idx = tid; idx < F_ROWS * D; idx += 128) {
+    const int r = idx / D, d = idx - r * D;
+    float v = 0.f;
+    if (r < row_count) {
+      const int row = row_begin + r;
+      const int tok = row / a.group, hg = row - tok * a.group;
+      v = qbase[(size_t)(q_start + tok) * a.q_stride + (size_t)(kvh * a.group + hg) * D + d];
+    }
+    q_s[r][d] = v;
+  }
+
+  float m[F_RPW], l[F_RPW], acc[F_RPW][F_DV];
+  int pos[F_RPW];
+#pragma unroll
+  for (int i = 0; i < F_RPW; ++i) {
+    m[i] = -CUDART_INF_F;
+    l[i] = 0.f;
+#pragma unroll
+    for (int j = 0; j < F_DV; ++j) acc[i][j] = 0.f;
+    const int r = warp * F_RPW + i;
+    pos[i] = r < row_count ? ctx + (row_begin + r) / a.group : -1;
+  }
+
+  for (int n0 = (kv_begin / F_BN) * F_BN; n0 < kv_end; n0 += F_BN) {
+    __syncthreads();
+    if (tid < F_BN) {
+      const int n = n0 + tid;
+      const float* kp = nullptr;
+      const float* vp = nullptr;
+      if (n < kv_end) {
+        const int page = table[n / a.page_size];
+        const size_t slot = (size_t)page * a.page_size + (n % a.page_size);
+        kp = kc + (slot * a.num_kv_heads + kvh) * D;
+        vp = vc + (slot * a.num_kv_heads + kvh) * D;
+      }
+      krow_ptr[tid] = kp;
+      vrow_ptr[tid] = vp;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < F_BN * D; idx += 128) {
+      const int j = idx / D, d = idx - j * D;
+      k_s[j][d] = krow_ptr[j] ? krow_ptr[j][d] : 0.f;
+      v_s[j][d] = vrow_ptr[j] ? vrow_ptr[j][d] : 0.f;
+    }
+    __syncthreads();
+
+#pragma unroll
+    for (int i = 0; i < F_RPW; ++i) {
+      const int r = warp * F_RPW + i;
+      if (pos[i] < 0) continue;
+      float s = 0.f;
+      for (int d = 0; d < D; ++d) s = fmaf(q_s[r][d], k_s[lane][d], s);
+      s *= a.scale_log2;
+      const int n = n0 + lane;
+      if (!key_visible(n, pos[i], kv_begin, kv_end, a.window)) s = -CUDART_INF_F;
+      const float m_new = fmaxf(m[i], warp_max(s));
+      const float m_safe = m_new == -CUDART_INF_F ? 0.f : m_new;
+      const float p = exp2f(s - m_safe);
+      const float alpha = exp2f(m[i] - m_safe);
+      l[i] = l[i] * alpha + warp_sum(p);
+#pragma unroll
+      for (int j = 0; j < F_DV; ++j) acc[i][j] *= alpha;
+      for (int kk = 0; kk < F_BN; ++kk) {
+        const float pk = __shfl_sync(0xffffffffu, p, kk);
+#pragma unroll
+        for (int j = 0; j < F_DV; ++j) {
+          const int d = lane + 32 * j;
+          if (d < D) acc[i][j] = fmaf(pk, v_s[kk][d], acc[i][j]);
+        }
+      }
+      m[i] = m_new;
+    }
+  }
+
+#pragma unroll
+  for (int i = 0; i < F_RPW; ++i) {
+    const int r = warp * F_RPW + i;
+    if (r >= row_count) continue;
+    const float inv = l[i] > 0.f ? 1.0f / l[i] : 0.f;
+    if (partial_base < 0) {
+      const int row = row_begin + r;
+      const int tok = row / a.group, hg = row - tok * a.group;
+      float* o = (float*)a.out + (size_t)(q_start + tok) * a.out_stride +
+                 (size_t)(kvh * a.group + hg) * D;
+#pragma unroll
+      for (int j = 0; j < F_DV; ++j) {
+        const int d = lane + 32 * j;
+        if (d < D) o[d] = acc[i][j] * inv;
+      }
+    } else {
+      const size_t prow = (size_t)partial_base + (size_t)kvh * row_count + r;
+#pragma unroll
+      for (int j = 0; j < F_DV; ++j) {
+        const int d = lane + 32 * j;
+        if (d < D) a.partial_o[prow * D + d] = acc[i][j] * inv;
+      }
+      if (lane == 0) a.partial_lse[prow] = l[i] > 0.f ? m[i] + log2f(l[i]) : -CUDART_INF_F;
+    }
+  }
+}
+
+// =============================================================================================
+// bfloat16 family: mma.sync m16n8k16 tensor-core tiles, float32 softmax and accumulators.
+//   WIDE  : 64 rows per item; each of 4 warps owns 16 rows and sees all 64 keys of a tile.
+//   NARROW: 16 rows per item; each of 4 warps owns 16 keys of every 64-key tile and the warps
+//           merge at the end (decode tokens and short portions; this is what gets split).
+// =============================================================================================
+constexpr int B_BN = 64;
+constexpr int B_LD = D + 8;  // row pitch in elements: 16-byte aligned, conflict-free ldmatrix
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(addr), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
+}
+
+template <int ROWS>
+__device__ __forceinline__ void load_q_tile(const AttnArgs& a, __nv_bfloat16* q_s, int q_start,
+                                            int row_begin, int row_count, int kvh) {
+  constexpr int CH = D / 8;
+  const __nv_bfloat16* qbase = (const __nv_bfloat16*)a.q;
+  for (int idx = threadIdx.x; idx < ROWS * CH; idx += blockDim.x) {
+    const int r = idx / CH, c = idx - r * CH;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (r < row_count) {
+      const int row = row_begin + r;
+      const int tok = row / a.group, hg = row - tok * a.group;
+      v = *reinterpret_cast<const uint4*>(qbase + (size_t)(q_start + tok) * a.q_stride +
+                                          (size_t)(kvh * a.group + hg) * D + c * 8);
+    }
+    *reinterpret_cast<uint4*>(q_s + r * B_LD + c * 8) = v;
+  }
+}
+
+// Loads keys [n0, n0 + 64) of one KV head into k_s / v_s; rows at or past kv_end are zeroed.
+__device__ __forceinline__ void load_kv_tile(const AttnArgs& a, __nv_bfloat16* k_s,
+                                             __nv_bfloat16* v_s, const int* table, int n0,
+                                             int kv_end, int kvh) {
+  constexpr int CH = D / 8;
+  const __nv_bfloat16* kc = (const __nv_bfloat16*)a.k_cache;
+  const __nv_bfloat16* vc = (const __nv_bfloat16*)a.v_cache;
+  for (int idx = threadIdx.x; idx < B_BN * CH; idx += blockDim.x) {
+    const int j = idx / CH, c = idx - j * CH;
+    const int n = n0 + j;
+    __nv_bfloat16* kd = k_s + j * B_LD + c * 8;
+    __nv_bfloat16* vd = v_s + j * B_LD + c * 8;
+    if (n < kv_end) {
+      const int page = table[n / a.page_size];
+      const size_t off =
+          (((size_t)page * a.page_size + (n % a.page_size)) * a.num_kv_heads + kvh) * D + c * 8;
+      cp_async16(kd, kc + off);
+      cp_async16(vd, vc + off);
+    } else {
+      *reinterpret_cast<uint4*>(kd) = make_uint4(0u, 0u, 0u, 0u);
+      *reinterpret_cast<uint4*>(vd) = make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+}
+
+// One warp: S[16 rows x NT*8 keys] = Q[16 x D] * K^T, keys key0.. of the tile in smem.
+template <int NT>
+__device__ __forceinline__ void warp_qk(float (&s)[NT][4], const __nv_bfloat16* q_rows,
+                                        const __nv_bfloat16* k_s, int key0, int lane) {
+#pragma unroll
+  for (int j = 0; j < NT; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+    uint32_t qa[4];
+    ldmatrix_x4(qa, q_rows + (lane & 15) * B_LD + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+    for (int j = 0; j < NT; j += 2) {
+      uint32_t kb[4];
+      const int jm = lane >> 3;
+      ldmatrix_x4(kb, k_s + (key0 + j * 8 + (jm >> 1) * 8 + (lane & 7)) * B_LD + kk * 16 +
+                          (jm & 1) * 8);
+      mma_bf16(s[j], qa, kb[0], kb[1]);
+      mma_bf16(s[j + 1], qa, kb[2], kb[3]);
+    }
+  }
+}
+
+// One warp: O[16 x D] += P[16 x NT*8] * V[NT*8 x D]; P comes from the score registers.
+template <int NT>
+__device__ __forceinline__ void warp_pv(float (&o)[D / 8][4], const float (&p)[NT][4],
+                                        const __nv_bfloat16* v_s, int key0, int lane) {
+#pragma unroll
+  for (int ks = 0; ks < NT / 2; ++ks) {
+    uint32_t pa[4];
+    pa[0] = pack_bf16(p[2 * ks][0], p[2 * ks][1]);
+    pa[1] = pack_bf16(p[2 * ks][2], p[2 * ks][3]);
+    pa[2] = pack_bf16(p[2 * ks + 1][0], p[2 * ks + 1][1]);
+    pa[3] = pack_bf16(p[2 * ks + 1][2], p[2 * ks + 1][3]);
+#pragma unroll
+    for (int jd = 0; jd < D / 8; jd += 2) {
+      uint32_t vb[4];
+      const int jm = lane >> 3;
+      ldmatrix_x4_trans(vb, v_s + (key0 + ks * 16 + (jm & 1) * 8 + (lane & 7)) * B_LD + jd * 8 +
+                                (jm >> 1) * 8);
+      mma_bf16(o[jd], pa, vb[0], vb[1]);
+      mma_bf16(o[jd + 1], pa, vb[2], vb[3]);
+    }
+  }
+}
+
+// Masks, online softmax and rescale for the two rows (g, g + 8) a thread holds.
+template <int NT>
+__device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&o)[D / 8][4],
+                                             float (&m)[2], float (&l)[2], const int (&pos)[2],
+                                             int nbase, int kv_begin, int kv_end, int window,
+                                             float scale_log2, int lane) {
+  float mx[2] = {-CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+  for (int j = 0; j < NT; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int n = nbase + j * 8 + 2 * (lane & 3) + (e & 1);
+      const int h = e >> 1;
+      float v = s[j][e] * scale_log2;
+      if (pos[h] < 0 || !key_visible(n, pos[h], kv_begin, kv_end, window)) v = -CUDART_INF_F;
+      s[j][e] = v;
+      mx[h] = fmaxf(mx[h], v);
+    }
+  float alpha[2], m_safe[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+    mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+    const float m_new = fmaxf(m[h], mx[h]);
+    m_safe[h] = m_new == -CUDART_INF_F ? 0.f : m_new;
+    alpha[h] = exp2f(m[h] - m_safe[h]);
+    m[h] = m_new;
+  }
+  float sum[2] = {0.f, 0.f};
+#pragma unroll
+  for (int j = 0; j < NT; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int h = e >> 1;
+      const float p = exp2f(s[j][e] - m_safe[h]);
+      s[j][e] = p;
+      sum[h] += p;
+    }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    sum[h] += __shfl_xor_sync(0xffffffffu, sum[h], 1);
+    sum[h] += __shfl_xor_sync(0xffffffffu, sum[h], 2);
+    l[h] = l[h] * alpha[h] + sum[h];
+  }
+#pragma unroll
+  for (int jd = 0; jd < D / 8; ++jd) {
+    o[jd][0] *= alpha[0];
+    o[jd][1] *= alpha[0];
+    o[jd][2] *= alpha[1];
+    o[jd][3] *= alpha[1];
+  }
+}
+
+// Writes the two rows a thread holds, to the output (bf16) or to the partial scratch (f32).
+__device__ __forceinline__ void store_rows(const AttnArgs& a, const float (&o)[D / 8][4],
+                                           const float (&m)[2], const float (&l)[2], int r0,
+                                           int row_begin, int row_count, int q_start, int kvh,
+                                           int partial_base, int lane) {
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = r0 + (lane >> 2) + 8 * h;
+    if (r >= row_count) continue;
+    const float inv = l[h] > 0.f ? 1.0f / l[h] : 0.f;
+    if (partial_base < 0) {
+      const int row = row_begin + r;
+      const int tok = row / a.group, hg = row - tok * a.group;
+      __nv_bfloat16* dst = (__nv_bfloat16*)a.out + (size_t)(q_start + tok) * a.out_stride +
+                           (size_t)(kvh * a.group + hg) * D;
+#pragma unroll
+      for (int jd = 0; jd < D / 8; ++jd)
+        *reinterpret_cast<__nv_bfloat162*>(dst + jd * 8 + 2 * (lane & 3)) =
+            __floats2bfloat162_rn(o[jd][2 * h] * inv, o[jd][2 * h + 1] * inv);
+    } else {
+      const size_t prow = (size_t)partial_base + (size_t)kvh * row_count + r;
+      float* dst = a.partial_o + prow * D;
+#pragma unroll
+      for (int jd = 0; jd < D / 8; ++jd)
+        *reinterpret_cast<float2*>(dst + jd * 8 + 2 * (lane & 3)) =
+            make_float2(o[jd][2 * h] * inv, o[jd][2 * h + 1] * inv);
+      if ((lane & 3) == 0)
+        a.partial_lse[prow] = l[h] > 0.f ? m[h] + log2f(l[h]) : -CUDART_INF_F;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(128) attn_bf16_wide_kernel(AttnArgs a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+  __nv_bfloat16* k_s = q_s + 64 * B_LD;
+  __nv_bfloat16* v_s = k_s + B_BN * B_LD;
+
+  const int* item = a.items + (size_t)blockIdx.x * 8;
+  const int seq = item[0];
+  if (seq < 0) return;
+  const int row_begin = item[1], row_count = item[2];
+  const int kv_begin = item[3], kv_end = item[4], partial_base = item[5];
+  const int kvh = blockIdx.y;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int q_start = a.q_start[seq], q_len = a.q_len[seq], kv_len = a.kv_len[seq];
+  const int ctx = kv_len - q_len;
+  const int* table = a.block_tables + (size_t)seq * a.table_stride;
+
+  load_q_tile<64>(a, q_s, q_start, row_begin, row_count, kvh);
+
+  float o[D / 8][4];
+#pragma unroll
+  for (int jd = 0; jd < D / 8; ++jd)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[jd][e] = 0.f;
+  float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
+  int pos[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = warp * 16 + (lane >> 2) + 8 * h;
+    pos[h] = r < row_count ? ctx + (row_begin + r) / a.group : -1;
+  }
+  // Keys past the last row's position are hidden from every row of the item.
+  const int last_pos = ctx + (row_begin + row_count - 1) / a.group;
+  const int tile_end = min(kv_end, last_pos + 1);
+
+  for (int n0 = (kv_begin / B_BN) * B_BN; n0 < tile_end; n0 += B_BN) {
+    __syncthreads();
+    load_kv_tile(a, k_s, v_s, table, n0, kv_end, kvh);
+    cp_async_wait_all();
+    __syncthreads();
+    float s[8][4];
+    warp_qk<8>(s, q_s + warp * 16 * B_LD, k_s, 0, lane);
+    softmax_step<8>(s, o, m, l, pos, n0, kv_begin, kv_end, a.window, a.scale_log2, lane);
+    warp_pv<8>(o, s, v_s, 0, lane);
+  }
+  store_rows(a, o, m, l, warp * 16, row_begin, row_count, q_start, kvh, partial_base, lane);
+}
+
+__global__ void __launch_bounds__(128) attn_bf16_narrow_kernel(AttnArgs a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+  __nv_bfloat16* k_s = q_s + 16 * B_LD;
+  __nv_bfloat16* v_s = k_s + B_BN * B_LD;
+
+  const int* item = a.items + (size_t)blockIdx.x * 8;
+  const int seq = item[0];
+  if (seq < 0) return;
+  const int row_begin = item[1], row_count = item[2];
+  const int kv_begin = item[3], kv_end = item[4], partial_base = item[5];
+  const int kvh = blockIdx.y;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int q_start = a.q_start[seq], q_len = a.q_len[seq], kv_len = a.kv_len[seq];
+  const int ctx = kv_len - q_len;
+  const int* table = a.block_tables + (size_t)seq * a.table_stride;
+
+  load_q_tile<16>(a, q_s, q_start, row_begin, row_count, kvh);
+
+  float o[D / 8][4];
+#pragma unroll
+  for (int jd = 0; jd < D / 8; ++jd)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[jd][e] = 0.f;
+  float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
+  int pos[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = (lane >> 2) + 8 * h;
+    pos[h] = r < row_count ? ctx + (row_begin + r) / a.group : -1;
+  }
+  const int last_pos = ctx + (row_begin + row_count - 1) / a.group;
+  const int tile_end = min(kv_end, last_pos + 1);
+
+  for (int n0 = (kv_begin / B_BN) * B_BN; n0 < tile_end; n0 += B_BN) {
+    __syncthreads();
+    load_kv_tile(a, k_s, v_s, table, n0, kv_end, kvh);
+    cp_async_wait_all();
+    __syncthreads();
+    float s[2][4];
+    warp_qk<2>(s, q_s, k_s, warp * 16, lane);
+    softmax_step<2>(s, o, m, l, pos, n0 + warp * 16, kv_begin, kv_end, a.window, a.scale_log2,
+                    lane);
+    warp_pv<2>(o, s, v_s, warp * 16, lane);
+  }
+
+  // Merge the four warps (each saw a quarter of every tile) through shared memory.
+  __syncthreads();
+  float* mo = reinterpret_cast<float*>(smem_raw);  // [4][16][D]
+  float* mm = mo + 4 * 16 * D;                      // [4][16]
+  float* ml = mm + 4 * 16;                          // [4][16]
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = (lane >> 2) + 8 * h;
+    float* dst = mo + ((size_t)warp * 16 + r) * D;
+#pragma unroll
+    for (int jd = 0; jd < D / 8; ++jd) {
+      dst[jd * 8 + 2 * (lane & 3)] = o[jd][2 * h];
+      dst[jd * 8 + 2 * (lane & 3) + 1] = o[jd][2 * h + 1];
+    }
+    if ((lane & 3) == 0) {
+      mm[warp * 16 + r] = m[h];
+      ml[warp * 16 + r] = l[h];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < 16 * D; idx += blockDim.x) {
+    const int r = idx / D, d = idx - r * D;
+    if (r >= row_count) continue;
+    float mt = -CUDART_INF_F;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mt = fmaxf(mt, mm[w * 16 + r]);
+    const float m_safe = mt == -CUDART_INF_F ? 0.f : mt;
+    float lt = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float wgt = exp2f(mm[w * 16 + r] - m_safe);
+      lt += ml[w * 16 + r] * wgt;
+      acc += mo[((size_t)w * 16 + r) * D + d] * wgt;
+    }
+    const float val = lt > 0.f ? acc / lt : 0.f;
+    if (partial_base < 0) {
+      const int row = row_begin + r;
+      const int tok = row / a.group, hg = row - tok * a.group;
+      ((__nv_bfloat16*)a.out)[(size_t)(q_start + tok) * a.out_stride +
+                              (size_t)(kvh * a.group + hg) * D + d] = __float2bfloat16_rn(val);
+    } else {
+      const size_t prow = (size_t)partial_base + (size_t)kvh * row_count + r;
+      a.partial_o[prow * D + d] = val;
+      if (d == 0) a.partial_lse[prow] = lt > 0.f ? mt + log2f(lt) : -CUDART_INF_F;
+    }
+  }
+}
+
+// =============================================================================================
+// Merge of split key ranges.  Merge item, int32[8]:
+//   {seq, row_begin, row_count, first_partial_base, num_splits, split_stride, -, -}
+// split s of the item wrote its rows at first_partial_base + s * split_stride.
+// =============================================================================================
+template <typename T>
+__global__ void attn_merge_kernel(AttnArgs a, const int* __restrict__ merge_items) {
+  const int* item = merge_items + (size_t)blockIdx.x * 8;
+  const int seq = item[0];
+  if (seq < 0) return;
+  const int row_begin = item[1], row_count = item[2], first = item[3], splits = item[4],
+            stride = item[5];
+  const int kvh = blockIdx.y;
+  const int q_start = a.q_start[seq];
+  for (int idx = threadIdx.x; idx < row_count * D; idx += blockDim.x) {
+    const int r = idx / D, d = idx - r * D;
+    float mt = -CUDART_INF_F;
+    for (int s = 0; s < splits; ++s)
+      mt = fmaxf(mt, a.partial_lse[(size_t)first + (size_t)s * stride + kvh * row_count + r]);
+    const float m_safe = mt == -CUDART_INF_F ? 0.f : mt;
+    float den = 0.f, acc = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const size_t prow = (size_t)first + (size_t)s * stride + kvh * row_count + r;
+      const float lse = a.partial_lse[prow];
+      const float w = lse == -CUDART_INF_F ? 0.f : exp2f(lse - m_safe);
+      den += w;
+      acc += w * a.partial_o[prow * D + d];
+    }
+    const float val = den > 0.f ? acc / den : 0.f;
+    const int row = row_begin + r;
+    const int tok = row / a.group, hg = row - tok * a.group;
+    ((T*)a.out)[(size_t)(q_start + tok) * a.out_stride + (size_t)(kvh * a.group + hg) * D + d] =
+        from_float<T>(val);
+  }
+}
+
+}  // namespace vx
+
+using namespace vx;
+
+static AttnArgs make_args(const void* q, void* out, const void* k_cache, const void* v_cache,
+                          const int* block_tables, const int* q_start, const int* q_len,
+                          const int* kv_len, const int* items, float* partial_o,
+                          float* partial_lse, int q_stride, int out_stride, int table_stride,
+                          int num_kv_heads, int group, int page_size, int window,
+                          float softmax_scale) {
+  AttnArgs a;
+  a.q = q;
+  a.out = out;
+  a.k_cache = k_cache;
+  a.v_cache = v_cache;
+  a.block_tables = block_tables;
+  a.q_start = q_start;
+  a.q_len = q_len;
+  a.kv_len = kv_len;
+  a.items = items;
+  a.partial_o = partial_o;
+  a.partial_lse = partial_lse;
+  a.q_stride = q_stride;
+  a.out_stride = out_stride;
+  a.table_stride = table_stride;
+  a.num_kv_heads = num_kv_heads;
+  a.group = group;
+  a.page_size = page_size;
+  a.window = window;
+  a.scale_log2 = softmax_scale * 1.4426950408889634f;
+  return a;
+}
+
+VX_API int vx_attn_head_dim() { return D; }
+
+// Rows per item that each family expects: kind 0 = float32, 1 = bf16 wide, 2 = bf16 narrow.
+VX_API int vx_attn_tile_rows(int kind) { return kind == 1 ? 64 : 16; }
+
+// kind: 0 = float32, 1 = bf16 wide (64 rows), 2 = bf16 narrow (16 rows).
+VX_API int vx_attention(int kind, const void* q, void* out, const void* k_cache,
+                        const void* v_cache, const int* block_tables, const int* q_start,
+                        const int* q_len, const int* kv_len, const int* items, int num_items,
+                        float* partial_o, float* partial_lse, int q_stride, int out_stride,
+                        int table_stride, int num_kv_heads, int group, int page_size, int window,
+                        float softmax_scale, cudaStream_t stream) {
+  if (num_items <= 0) return 0;
+  const AttnArgs a = make_args(q, out, k_cache, v_cache, block_tables, q_start, q_len, kv_len,
+                               items, partial_o, partial_lse, q_stride, out_stride, table_stride,
+                               num_kv_heads, group, page_size, window, softmax_scale);
+  const dim3 grid(num_items, num_kv_heads);
+  if (kind == 0) {
+    const size_t smem = sizeof(float) * (size_t)(F_ROWS * D + 2 * F_BN * (D + 1));
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(attn_f32_kernel,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+      configured = true;
+    }
+    attn_f32_kernel<<<grid, 128, smem, stream>>>(a);
+  } else if (kind == 1) {
+    const size_t smem = (size_t)(64 + 2 * B_BN) * B_LD * sizeof(__nv_bfloat16);
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(attn_bf16_wide_kernel,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+      configured = true;
+    }
+    attn_bf16_wide_kernel<<<grid, 128, smem, stream>>>(a);
+  } else if (kind == 2) {
+    size_t smem = (size_t)(16 + 2 * B_BN) * B_LD * sizeof(__nv_bfloat16);
+    const size_t merge = (size_t)(4 * 16 * D + 2 * 4 * 16) * sizeof(float);
+    if (merge > smem) smem = merge;
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(attn_bf16_narrow_kernel,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+      configured = true;
+    }
+    attn_bf16_narrow_kernel<<<grid, 128, smem, stream>>>(a);
+  } else {
+    return (int)cudaErrorInvalidValue;
+  }
+  return (int)cudaGetLastError();
+}
+
+VX_API int vx_attention_merge(int dtype, void* out, const int* q_start, const int* merge_items,
+                              int num_items, const float* partial_o, const float* partial_lse,
+                              int out_stride, int num_kv_heads, int group, cudaStream_t stream) {
+  if (num_items <= 0) return 0;
+  AttnArgs a = make_args(nullptr, out, nullptr, nullptr, nullptr, q_start, nullptr, nullptr,
+                         nullptr, const_cast<float*>(partial_o), const_cast<float*>(partial_lse),
+                         0, out_stride, 0, num_kv_heads, group, 1, 0, 1.0f);
+  const dim3 grid(num_items, num_kv_heads);
+  if (dtype == VX_DTYPE_F32)
+    attn_merge_kernel<float><<<grid, 128, 0, stream>>>(a, merge_items);
+  else
+    attn_merge_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(a, merge_items);
+  return (int)cudaGetLastError();
+}

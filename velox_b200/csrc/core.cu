@@ -1,0 +1,293 @@
+// Row-wise kernels of the model step: embedding, fused residual-add + RMSNorm, rotate-half RoPE
+// fused with the K/V write into the paged cache, SwiGLU, and a float32 SIMT GEMM for the true
+// 32-bit path.  All arithmetic that the engine promises in 32-bit (norm statistics, rotation,
+// the residual sum, SiLU) is float32 here whatever the storage type.
+//
+// Formulas follow the reference engine (paths inside that project):
+//   RMSNorm            src/rmsnorm.py:20-28      x * rsqrt(mean(x^2) + eps) * w
+//   RoPE               src/rope_inplace.py:25-47 lo' = lo*cos - hi*sin ; hi' = lo*sin + hi*cos
+//   cache write        src/paged_kv_cache.py:122-123  flat[slot] = k / v of the token
+//   SwiGLU             src/mlp.py:13-15          silu(gate) * up on the halves of [T, 2I]
+// The residual stream is kept in float32 (the reference adds in the model dtype,
+// src/decoder_layer.py:49,54).
+#include "common.cuh"
+
+namespace vx {
+
+// ---------------------------------------------------------------------------------------------
+// Embedding: resid[t, :] = float(table[ids[t], :])
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                             float* __restrict__ resid, int hidden, int vocab, int* status) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  const bool bad = id < 0 || id >= vocab;
+  if (bad) {
+    if (threadIdx.x == 0) atomicOr(status, VX_STATUS_BAD_TOKEN_ID);
+    id = 0;
+  }
+  const T* row = table + (size_t)id * hidden;
+  float* dst = resid + (size_t)t * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = bad ? 0.f : to_float(row[i]);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Fused residual add + RMSNorm.
+//   v = resid[r] + delta[r]   (delta may be null)
+//   if write_resid: resid[r] = v
+//   out[o] = v * (1 / sqrt(mean(v^2) + eps)) * weight
+// `rows` (may be null) selects the rows to normalise: out row o comes from input row rows[o].
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+                                   const float* __restrict__ weight, float eps,
+                                   T* __restrict__ out, const int* __restrict__ rows, int hidden,
+                                   int write_resid) {
+  __shared__ float scratch[32];
+  const int o = blockIdx.x;
+  const int r = rows ? rows[o] : o;
+  float* x = resid + (size_t)r * hidden;
+  const T* d = delta ? delta + (size_t)r * hidden : nullptr;
+
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = d ? x[i] + to_float(d[i]) : x[i];
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+  T* y = out + (size_t)o * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = d ? x[i] + to_float(d[i]) : x[i];
+    if (write_resid) x[i] = v;
+    y[i] = from_float<T>(v * inv * weight[i]);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// RoPE on q (in place) and on k, fused with the write of k and v into the paged cache.
+//   qkv row layout: [H*D q | G*D k | G*D v]; the first `rot` dims of every head rotate as two
+//   halves (rot = 0: no rotation), cos/sin are float32 tables [max_pos, rot/2].
+//   slots[t] is the flat cache index (page * page_size + offset); a negative slot skips the
+//   write (padding rows).  write_cache = 0 rotates q only (a layer that reads another's cache).
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_cache_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+                                        const float* __restrict__ cos_t,
+                                        const float* __restrict__ sin_t,
+                                        const int* __restrict__ slots, T* __restrict__ k_cache,
+                                        T* __restrict__ v_cache, int H, int G, int D, int rot,
+                                        int max_pos, long long num_slots, int write_cache,
+                                        int* status) {
+  const int t = blockIdx.x;
+  const int half = rot >> 1;
+  int pos = positions[t];
+  if (rot > 0 && (pos < 0 || pos >= max_pos)) {
+    if (threadIdx.x == 0) atomicOr(status, VX_STATUS_BAD_POSITION);
+    pos = 0;
+  }
+  const float* c = cos_t + (size_t)pos * half;
+  const float* s = sin_t + (size_t)pos * half;
+  T* row = qkv + (size_t)t * (size_t)(H + 2 * G) * D;
+
+  for (int idx = threadIdx.x; idx < H * half; idx += blockDim.x) {
+    const int h = idx / half, i = idx - h * half;
+    T* p = row + h * D + i;
+    const float lo = to_float(p[0]), hi = to_float(p[half]);
+    p[0] = from_float<T>(lo * c[i] - hi * s[i]);
+    p[half] = from_float<T>(lo * s[i] + hi * c[i]);
+  }
+  if (!write_cache) return;
+  const int slot = slots[t];
+  if (slot < 0) return;
+  if ((long long)slot >= num_slots) {
+    if (threadIdx.x == 0) atomicOr(status, VX_STATUS_BAD_SLOT);
+    return;
+  }
+  const T* krow = row + (size_t)H * D;
+  const T* vrow = krow + (size_t)G * D;
+  T* kdst = k_cache + (size_t)slot * G * D;
+  T* vdst = v_cache + (size_t)slot * G * D;
+  for (int idx = threadIdx.x; idx < G * half; idx += blockDim.x) {
+    const int g = idx / half, i = idx - g * half;
+    const float lo = to_float(krow[g * D + i]), hi = to_float(krow[g * D + i + half]);
+    kdst[g * D + i] = from_float<T>(lo * c[i] - hi * s[i]);
+    kdst[g * D + i + half] = from_float<T>(lo * s[i] + hi * c[i]);
+  }
+  const int tail = D - rot;
+  for (int idx = threadIdx.x; idx < G * tail; idx += blockDim.x) {
+    const int g = idx / tail, i = idx - g * tail;
+    kdst[g * D + rot + i] = krow[g * D + rot + i];
+  }
+  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) vdst[idx] = vrow[idx];
+}
+
+// ---------------------------------------------------------------------------------------------
+// SwiGLU: out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i], float32 inside, one rounding.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long total,
+                              int inter) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += stride) {
+    const long long t = idx / inter;
+    const int i = (int)(idx - t * inter);
+    const float g = to_float(gate_up[t * 2 * inter + i]);
+    const float u = to_float(gate_up[t * 2 * inter + inter + i]);
+    const float silu = g / (1.0f + expf(-g));
+    out[idx] = from_float<T>(silu * u);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// float32 GEMM on the FP32 pipes (no tensor cores, no TF32): C[M,N] = A[M,K] * W[N,K]^T + bias.
+// Every output element is summed over k = 0..K-1 in order by one thread, so a row's result does
+// not depend on M or on where the row sits in the batch.
+// ---------------------------------------------------------------------------------------------
+constexpr int GF_BM = 64, GF_BN = 64, GF_BK = 16;
+
+__global__ void __launch_bounds__(256)
+gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ W,
+                const float* __restrict__ bias, float* __restrict__ C, int M, int N, int K) {
+  __shared__ float As[GF_BK][GF_BM + 4];
+  __shared__ float Ws[GF_BK][GF_BN + 4];
+  const int tid = threadIdx.x;
+  const int m0 = blockIdx.y * GF_BM, n0 = blockIdx.x * GF_BN;
+  const int ty = tid >> 4, tx = tid & 15;
+  const int load_row = tid >> 2, load_k = (tid & 3) * 4;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+
+  for (int k0 = 0; k0 < K; k0 += GF_BK) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int k = k0 + load_k + j;
+      const int am = m0 + load_row, wn = n0 + load_row;
+      As[load_k + j][load_row] = (am < M && k < K) ? A[(size_t)am * K + k] : 0.f;
+      Ws[load_k + j][load_row] = (wn < N && k < K) ? W[(size_t)wn * K + k] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < GF_BK; ++k) {
+      float a[4], w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[k][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) w[j] = Ws[k][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + ty * 4 + i;
+    if (m >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < N) C[(size_t)m * N + n] = acc[i][j] + (bias ? bias[n] : 0.f);
+    }
+  }
+}
+
+// bf16 -> float32 copy of selected rows (logits of the bfloat16 path are returned as float32).
+__global__ void cast_bf16_to_f32_kernel(const __nv_bfloat16* __restrict__ in,
+                                        float* __restrict__ out, long long total) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += stride)
+    out[idx] = __bfloat162float(in[idx]);
+}
+
+}  // namespace vx
+
+// =============================================================================================
+// Launchers
+// =============================================================================================
+using namespace vx;
+
+VX_API int vx_embed(const void* table, int dtype, const int* ids, float* resid, int num_tokens,
+                    int hidden, int vocab, int* status, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  const int threads = hidden >= 1024 ? 256 : 128;
+  if (dtype == VX_DTYPE_F32)
+    embed_kernel<float><<<num_tokens, threads, 0, stream>>>((const float*)table, ids, resid,
+                                                            hidden, vocab, status);
+  else
+    embed_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>(
+        (const __nv_bfloat16*)table, ids, resid, hidden, vocab, status);
+  return (int)cudaGetLastError();
+}
+
+VX_API int vx_add_rmsnorm(float* resid, const void* delta, const float* weight, float eps,
+                          void* out, int dtype, const int* rows, int num_out_rows, int hidden,
+                          int write_resid, cudaStream_t stream) {
+  if (num_out_rows <= 0) return 0;
+  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  if (dtype == VX_DTYPE_F32)
+    add_rmsnorm_kernel<float><<<num_out_rows, threads, 0, stream>>>(
+        resid, (const float*)delta, weight, eps, (float*)out, rows, hidden, write_resid);
+  else
+    add_rmsnorm_kernel<__nv_bfloat16><<<num_out_rows, threads, 0, stream>>>(
+        resid, (const __nv_bfloat16*)delta, weight, eps, (__nv_bfloat16*)out, rows, hidden,
+        write_resid);
+  return (int)cudaGetLastError();
+}
+
+VX_API int vx_rope_cache_write(void* qkv, int dtype, const int* positions, const float* cos_t,
+                               const float* sin_t, const int* slots, void* k_cache,
+                               void* v_cache, int num_tokens, int H, int G, int D, int rot,
+                               int max_pos, long long num_slots, int write_cache, int* status,
+                               cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  const int threads = 128;
+  if (dtype == VX_DTYPE_F32)
+    rope_cache_write_kernel<float><<<num_tokens, threads, 0, stream>>>(
+        (float*)qkv, positions, cos_t, sin_t, slots, (float*)k_cache, (float*)v_cache, H, G, D,
+        rot, max_pos, num_slots, write_cache, status);
+  else
+    rope_cache_write_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>(
+        (__nv_bfloat16*)qkv, positions, cos_t, sin_t, slots, (__nv_bfloat16*)k_cache,
+        (__nv_bfloat16*)v_cache, H, G, D, rot, max_pos, num_slots, write_cache, status);
+  return (int)cudaGetLastError();
+}
+
+VX_API int vx_swiglu(const void* gate_up, void* out, int dtype, int num_tokens, int inter,
+                     cudaStream_t stream) {
+  const long long total = (long long)num_tokens * inter;
+  if (total <= 0) return 0;
+  const int threads = 256;
+  long long blocks = (total + threads - 1) / threads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (dtype == VX_DTYPE_F32)
+    swiglu_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out,
+                                                              total, inter);
+  else
+    swiglu_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, stream>>>(
+        (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, total, inter);
+  return (int)cudaGetLastError();
+}
+
+VX_API int vx_gemm_f32(const float* A, const float* W, const float* bias, float* C, int M, int N,
+                       int K, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  dim3 grid((N + GF_BN - 1) / GF_BN, (M + GF_BM - 1) / GF_BM);
+  gemm_f32_kernel<<<grid, 256, 0, stream>>>(A, W, bias, C, M, N, K);
+  return (int)cudaGetLastError();
+}
+
+VX_API int vx_cast_bf16_to_f32(const void* in, float* out, long long total, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  cast_bf16_to_f32_kernel<<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)in, out, total);
+  return (int)cudaGetLastError();
+}

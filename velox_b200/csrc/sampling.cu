@@ -1,0 +1,305 @@
+// On-device sampling over float32 logits [R, V]: greedy, temperature, top-k, top-p, and the
+// repetition / presence / frequency penalties.
+//
+// What is sampled follows the reference's sampler (engine/sampler.py:131-258 in that project):
+//   penalties   logit[v] -= frequency * count(v); then logit[v] = logit[v] > 0 ? logit[v] / rep
+//               : logit[v] * rep; then logit[v] -= presence, for every token v in the request's
+//               prompt and output so far (sampler.py:169-189);
+//   greedy      argmax, first index on ties (sampler.py:155-156);
+//   otherwise   scaled = logit / max(temperature, 1e-5); candidates are the k most probable
+//               tokens and the smallest most-probable set whose mass reaches top_p
+//               (sampler.py:216-228); the draw is the exponential race
+//               argmax(p / noise), noise ~ Exp(1) clamped at 1e-10 (sampler.py:230-258).
+// How it is done differs: the race runs over the whole vocabulary as argmax(scaled - log noise)
+// (the same draw, since log is monotone and the normaliser is a constant), the candidate set is
+// found as a value threshold by bisection instead of a sort, and the noise comes from a
+// counter-based generator (Philox4x32-10) keyed by the request's seed and counted by
+// (index of the output token, vocabulary index), so a request's draws do not depend on what
+// else is in the batch.  Bit-equality with torch's generator stream is not a goal.
+#include "common.cuh"
+
+#include <math_constants.h>
+
+namespace vx {
+
+// ---------------------------------------------------------------------------------------------
+// Philox4x32-10 (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3", SC'11).
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint4 philox4x32_10(uint4 ctr, uint2 key) {
+  const uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
+#pragma unroll
+  for (int round = 0; round < 10; ++round) {
+    const uint32_t hi0 = __umulhi(M0, ctr.x), lo0 = M0 * ctr.x;
+    const uint32_t hi1 = __umulhi(M1, ctr.z), lo1 = M1 * ctr.z;
+    ctr = make_uint4(hi1 ^ ctr.y ^ key.x, lo1, hi0 ^ ctr.w ^ key.y, lo0);
+    key.x += W0;
+    key.y += W1;
+  }
+  return ctr;
+}
+
+// Uniform in (0, 1) from 32 random bits.
+__device__ __forceinline__ float uniform_open(uint32_t bits) {
+  return ((float)(bits >> 8) + 0.5f) * (1.0f / 16777216.0f);
+}
+
+// Order-preserving map float -> uint32 (larger float, larger key).
+__device__ __forceinline__ uint32_t float_key(float v) {
+  const uint32_t b = __float_as_uint(v);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float key_float(uint32_t k) {
+  const uint32_t b = (k & 0x80000000u) ? (k & 0x7fffffffu) : ~k;
+  return __uint_as_float(b);
+}
+
+struct Best {
+  float score;
+  int index;
+};
+
+__device__ __forceinline__ Best better(Best a, Best b) {
+  // Larger score wins; on equal scores the lower index (torch.argmax returns the first maximum).
+  if (b.index < 0) return a;
+  if (a.index < 0) return b;
+  if (b.score > a.score || (b.score == a.score && b.index < a.index)) return b;
+  return a;
+}
+
+__device__ __forceinline__ Best block_best(Best v, Best* scratch /* 32 */) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int num_warps = (blockDim.x + 31) >> 5;
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) {
+    Best o;
+    o.score = __shfl_xor_sync(0xffffffffu, v.score, offset);
+    o.index = __shfl_xor_sync(0xffffffffu, v.index, offset);
+    v = better(v, o);
+  }
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    Best w;
+    w.score = 0.f;
+    w.index = -1;
+    if (lane < num_warps) w = scratch[lane];
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+      Best o;
+      o.score = __shfl_xor_sync(0xffffffffu, w.score, offset);
+      o.index = __shfl_xor_sync(0xffffffffu, w.index, offset);
+      w = better(w, o);
+    }
+    if (lane == 0) scratch[0] = w;
+  }
+  __syncthreads();
+  const Best out = scratch[0];
+  __syncthreads();
+  return out;
+}
+
+// ---------------------------------------------------------------------------------------------
+// One token per row.  temperature[r] == 0: argmax.  Otherwise the exponential race over the
+// entries with logit / T >= threshold[r] (threshold may be null: no filter).
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024)
+sample_kernel(const float* __restrict__ logits, int vocab, long long row_stride,
+              const float* __restrict__ temperature, const unsigned long long* __restrict__ seeds,
+              const int* __restrict__ draw_index, const float* __restrict__ threshold,
+              int* __restrict__ out, int* __restrict__ history, long long history_stride,
+              const int* __restrict__ history_slots, const int* __restrict__ history_lengths) {
+  __shared__ Best scratch[32];
+  const int r = blockIdx.x;
+  const float* row = logits + (size_t)r * row_stride;
+  const float temp = temperature ? temperature[r] : 0.f;
+  Best best;
+  best.score = 0.f;
+  best.index = -1;
+
+  if (temp == 0.f) {
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+      Best c;
+      c.score = row[i];
+      c.index = i;
+      if (c.score == c.score) best = better(best, c);
+    }
+  } else {
+    const float inv_t = 1.0f / fmaxf(temp, 1e-5f);
+    const float cut = threshold ? threshold[r] : -CUDART_INF_F;
+    const unsigned long long seed = seeds[r];
+    const uint2 key = make_uint2((uint32_t)seed, (uint32_t)(seed >> 32));
+    const uint32_t draw = (uint32_t)draw_index[r];
+    for (int base = threadIdx.x * 4; base < vocab; base += blockDim.x * 4) {
+      const uint4 bits = philox4x32_10(make_uint4((uint32_t)(base >> 2), draw, 0u, 0u), key);
+      const uint32_t b[4] = {bits.x, bits.y, bits.z, bits.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int i = base + j;
+        if (i >= vocab) break;
+        const float scaled = row[i] * inv_t;
+        if (!(scaled >= cut)) continue;
+        const float noise = fmaxf(-logf(uniform_open(b[j])), 1e-10f);
+        Best c;
+        c.score = scaled - logf(noise);
+        c.index = i;
+        best = better(best, c);
+      }
+    }
+  }
+  best = block_best(best, scratch);
+  if (threadIdx.x == 0) {
+    const int token = best.index < 0 ? 0 : best.index;
+    out[r] = token;
+    // Append to the request's token history (kept for the penalties) when there is one.
+    if (history != nullptr) {
+      const int n = history_lengths[r];
+      if (n >= 0 && n < history_stride) history[(size_t)history_slots[r] * history_stride + n] = token;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Candidate threshold for top-k / top-p.  For a value x let count(x) be the number of entries
+// with scaled > x and mass(x) their softmax probability.  An entry is a candidate iff
+// count(scaled_i) < k (when k > 0) and mass(scaled_i) < top_p: it is among the k largest, and
+// the entries before it do not already reach top_p.  Both are monotone in x, so the candidates
+// are the entries >= a threshold, found by bisection over the ordered bit patterns of float.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024)
+filter_threshold_kernel(const float* __restrict__ logits, int vocab, long long row_stride,
+                        const float* __restrict__ temperature, const int* __restrict__ top_k,
+                        const float* __restrict__ top_p, float* __restrict__ threshold) {
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  const float temp = temperature[r];
+  const int k = top_k[r];
+  const float p = top_p[r];
+  const bool use_k = k > 0 && k < vocab;
+  const bool use_p = p < 1.0f;
+  if (temp == 0.f || (!use_k && !use_p)) {
+    if (threadIdx.x == 0) threshold[r] = -CUDART_INF_F;
+    return;
+  }
+  const float* row = logits + (size_t)r * row_stride;
+  const float inv_t = 1.0f / fmaxf(temp, 1e-5f);
+
+  float m = -CUDART_INF_F;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) m = fmaxf(m, row[i] * inv_t);
+  m = warp_max(m);
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float w = threadIdx.x < ((blockDim.x + 31) >> 5) ? scratch[threadIdx.x] : -CUDART_INF_F;
+    w = warp_max(w);
+    if (threadIdx.x == 0) scratch[0] = w;
+  }
+  __syncthreads();
+  m = scratch[0];
+  __syncthreads();
+
+  float z = 0.f;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) z += expf(row[i] * inv_t - m);
+  z = block_sum(z, scratch);
+  const float mass_limit = p * z;
+
+  // Smallest key whose value x satisfies count(x) < k and mass(x) < top_p.
+  uint32_t lo = 0u, hi = float_key(m);
+  while (lo < hi) {
+    const uint32_t mid = lo + ((hi - lo) >> 1);
+    const float x = key_float(mid);
+    float cnt = 0.f, mass = 0.f;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+      const float s = row[i] * inv_t;
+      if (s > x) {
+        cnt += 1.f;
+        mass += expf(s - m);
+      }
+    }
+    cnt = block_sum(cnt, scratch);
+    mass = block_sum(mass, scratch);
+    const bool keep = (!use_k || cnt < (float)k) && (!use_p || mass < mass_limit);
+    if (keep)
+      hi = mid;
+    else
+      lo = mid + 1u;
+  }
+  if (threadIdx.x == 0) threshold[r] = key_float(lo);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Penalties.  `history` holds each request's prompt and output tokens, one row per state slot.
+// counts is scratch [R, V] int32, zeroed by the first kernel.
+// ---------------------------------------------------------------------------------------------
+__global__ void penalty_count_kernel(const int* __restrict__ history, long long history_stride,
+                                     const int* __restrict__ slots,
+                                     const int* __restrict__ lengths, int* __restrict__ counts,
+                                     int vocab) {
+  const int r = blockIdx.x;
+  int* c = counts + (size_t)r * vocab;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) c[i] = 0;
+  __syncthreads();
+  const int* h = history + (size_t)slots[r] * history_stride;
+  const int n = lengths[r];
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int v = h[i];
+    if (v >= 0 && v < vocab) atomicAdd(&c[v], 1);
+  }
+}
+
+__global__ void penalty_apply_kernel(float* __restrict__ logits, long long row_stride,
+                                     const int* __restrict__ counts, int vocab,
+                                     const float* __restrict__ repetition,
+                                     const float* __restrict__ presence,
+                                     const float* __restrict__ frequency) {
+  const int r = blockIdx.x;
+  float* row = logits + (size_t)r * row_stride;
+  const int* c = counts + (size_t)r * vocab;
+  const float rep = repetition[r], pres = presence[r], freq = frequency[r];
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    const int n = c[i];
+    if (n == 0) continue;
+    float x = row[i] - freq * (float)n;
+    x = x > 0.f ? x / rep : x * rep;
+    row[i] = x - pres;
+  }
+}
+
+}  // namespace vx
+
+using namespace vx;
+
+VX_API int vx_sample(const float* logits, int num_rows, int vocab, long long row_stride,
+                     const float* temperature, const unsigned long long* seeds,
+                     const int* draw_index, const float* threshold, int* out, int* history,
+                     long long history_stride, const int* history_slots,
+                     const int* history_lengths, cudaStream_t stream) {
+  if (num_rows <= 0) return 0;
+  const int threads = vocab >= 4096 ? 1024 : 256;
+  sample_kernel<<<num_rows, threads, 0, stream>>>(logits, vocab, row_stride, temperature, seeds,
+                                                  draw_index, threshold, out, history,
+                                                  history_stride, history_slots, history_lengths);
+  return (int)cudaGetLastError();
+}
+
+VX_API int vx_filter_threshold(const float* logits, int num_rows, int vocab, long long row_stride,
+                               const float* temperature, const int* top_k, const float* top_p,
+                               float* threshold, cudaStream_t stream) {
+  if (num_rows <= 0) return 0;
+  const int threads = vocab >= 4096 ? 1024 : 256;
+  filter_threshold_kernel<<<num_rows, threads, 0, stream>>>(logits, vocab, row_stride,
+                                                            temperature, top_k, top_p, threshold);
+  return (int)cudaGetLastError();
+}
+
+VX_API int vx_apply_penalties(float* logits, int num_rows, int vocab, long long row_stride,
+                              const int* history, long long history_stride, const int* slots,
+                              const int* lengths, int* counts, const float* repetition,
+                              const float* presence, const float* frequency,
+                              cudaStream_t stream) {
+  if (num_rows <= 0) return 0;
+  penalty_count_kernel<<<num_rows, 256, 0, stream>>>(history, history_stride, slots, lengths,
+                                                     counts, vocab);
+  penalty_apply_kernel<<<num_rows, 256, 0, stream>>>(logits, row_stride, counts, vocab,
+                                                     repetition, presence, frequency);
+  return (int)cudaGetLastError();
+}

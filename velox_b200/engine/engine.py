@@ -1,0 +1,304 @@
+"""The engine: scheduler, step function and sampler in one loop, and the Python entry point.
+
+The public surface follows the reference (engine/engine.py:105-417; README "offline" snippet):
+
+    engine = Engine.from_pretrained(EngineConfig(model="<folder>"))
+    request = Request("r0", prompt_token_ids=[...], sampling_params=SamplingParams(max_tokens=64))
+    engine.generate([request])
+    request.output_token_ids
+
+plus ``add_request`` / ``step`` / ``has_work`` / ``abort_request`` / ``snapshot`` for callers
+that drive the loop themselves, and ``LLM`` as a thin wrapper that takes and returns token id
+lists.  One step is: schedule -> one mixed forward -> sample the rows that completed -> one
+read-back of the sampled tokens (the only host wait of the step) -> bookkeeping.
+"""
+from __future__ import annotations
+
+import json
+import logging
+import os
+import time
+from typing import Dict, FrozenSet, Iterable, List, Optional, Sequence
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..cache.storage import compute_num_pages
+from ..config.engine_config import EngineConfig, SchedulerConfig
+from ..config.registry import architecture_of, load_model_config
+from ..config.model_config import read_config_json
+from ..ops import kernels
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import Sampler
+from ..weights.loader import Checkpoint, WeightStore
+from .model import CausalLM
+from .request import FinishReason, Request
+from .runner import ModelRunner, StepChunk
+from .scheduler import Scheduler
+
+logger = logging.getLogger(__name__)
+
+# What the reference falls back to when a model folder names no end-of-sequence ids
+# (engine/engine.py:23).
+DEFAULT_EOS_TOKEN_IDS = frozenset({151643, 151645})
+
+
+def load_model(model_dir: str, dtype: torch.dtype, device: torch.device, max_position: Optional[int] = None):
+    """Model folder -> (typed config, spec, model).  The class is chosen by config.json."""
+    raw = read_config_json(model_dir)
+    arch = architecture_of(raw)
+    config = arch.parse_config(raw)
+    spec = arch.build_spec(config)
+    store = WeightStore(Checkpoint(model_dir), spec, dtype, device)
+    model = CausalLM(spec, store, dtype, device, max_position=max_position)
+    return config, spec, model
+
+
+def _eos_token_ids(model_dir: str, spec_ids: Sequence[int]) -> FrozenSet[int]:
+    path = os.path.join(model_dir, "generation_config.json")
+    if os.path.isfile(path):
+        try:
+            with open(path, "r", encoding="utf-8") as handle:
+                eos = json.load(handle).get("eos_token_id")
+            if isinstance(eos, int):
+                return frozenset({eos})
+            if eos:
+                return frozenset(int(t) for t in eos)
+        except (OSError, ValueError):
+            pass
+    if spec_ids:
+        return frozenset(spec_ids)
+    return DEFAULT_EOS_TOKEN_IDS
+
+
+class Engine:
+    def __init__(
+        self,
+        model: CausalLM,
+        config: EngineConfig,
+        num_pages: int,
+        eos_token_ids: Optional[Iterable[int]] = None,
+    ) -> None:
+        config.validate()
+        self.config = config
+        self.model = model
+        self.device = model.device
+        self.eos_token_ids: FrozenSet[int] = frozenset(
+            DEFAULT_EOS_TOKEN_IDS if eos_token_ids is None else eos_token_ids
+        )
+        self.cache = CacheManager(
+            model.cache_groups,
+            num_pages=num_pages,
+            page_size=config.block_size,
+            max_model_len=config.max_model_len,
+            max_num_seqs=config.max_num_seqs,
+        )
+        self.scheduler = Scheduler(
+            self.cache,
+            SchedulerConfig(
+                max_num_seqs=config.max_num_seqs,
+                max_num_batched_tokens=config.max_num_batched_tokens,
+                max_prefill_chunk_size=config.max_prefill_chunk_size,
+                max_model_len=config.max_model_len,
+            ),
+        )
+        self.max_model_len = self.scheduler.config.max_model_len
+        self.runner = ModelRunner(
+            model,
+            self.cache,
+            max_num_seqs=config.max_num_seqs,
+            max_num_batched_tokens=config.max_num_batched_tokens,
+        )
+        self.sampler = Sampler(
+            self.device, model.vocab_size, config.max_num_seqs, self.max_model_len, seed=config.seed
+        )
+        runner_hook = self.cache.on_slot_acquired
+
+        def on_slot(seq):
+            if runner_hook is not None:
+                runner_hook(seq)
+            request = self.scheduler.requests.get(seq.seq_id)
+            if request is not None:
+                self.sampler.start_sequence(seq.slot, request.all_token_ids, request.sampling_params)
+
+        self.cache.on_slot_acquired = on_slot
+
+        self.stats: Dict[str, List[float]] = {
+            "scheduler_ms": [],
+            "prepare_ms": [],
+            "gpu_ms": [],
+            "cpu_sync_wait_ms": [],
+            "sampling_ms": [],
+            "step_ms": [],
+        }
+        self.num_steps = 0
+        self._timing = True
+
+    # ------------------------------------------------------------------ construction
+    @classmethod
+    def from_pretrained(cls, config: Optional[EngineConfig] = None, **overrides) -> "Engine":
+        config = config or EngineConfig(**overrides)
+        config.validate()
+        kernels._require_cuda()
+        device = torch.device(config.device)
+        dtype = config.torch_dtype()
+        model_config = load_model_config(config.model)
+        config.max_model_len = min(config.max_model_len, model_config.max_position_embeddings)
+        _, spec, model = load_model(config.model, dtype, device, max_position=config.max_model_len)
+        num_pages = config.num_gpu_blocks or compute_num_pages(
+            model.entry_needs,
+            config.block_size,
+            dtype,
+            device,
+            gpu_memory_utilization=config.gpu_memory_utilization,
+            reserve_bytes=config.kv_cache_reserve_mb * 1024 * 1024,
+        )
+        # No request can use more than max_model_len tokens per sequence slot.
+        most = config.max_num_seqs * (-(-config.max_model_len // config.block_size)) + 1
+        if config.num_gpu_blocks is None:
+            num_pages = min(num_pages, most)
+        engine = cls(model, config, num_pages, _eos_token_ids(config.model, spec.eos_token_ids))
+        engine.warmup()
+        return engine
+
+    def warmup(self) -> None:
+        """One short request through the whole loop, so that library handles and kernel images
+        exist before the first real step (engine/engine.py:174-211 does the same)."""
+        limit = self.max_model_len - 2
+        if limit < 1:
+            return
+        request = Request(
+            "__warmup__", [0] * min(8, limit), SamplingParams(temperature=0.0, max_tokens=2, ignore_eos=True)
+        )
+        self.add_request(request)
+        guard = 0
+        while self.has_work() and guard < 16:
+            self.step()
+            guard += 1
+        self.scheduler.abort_request(request.request_id)
+        torch.cuda.synchronize(self.device)
+        for values in self.stats.values():
+            values.clear()
+        self.num_steps = 0
+        self.scheduler.num_finished = 0
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, request: Request) -> None:
+        self.scheduler.add_request(request)
+
+    def abort_request(self, request_id: str) -> bool:
+        return self.scheduler.abort_request(request_id)
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    # ------------------------------------------------------------------ one step
+    @torch.no_grad()
+    def step(self) -> None:
+        step_start = time.perf_counter()
+        scheduled = self.scheduler.schedule()
+        t_sched = time.perf_counter()
+        self.stats["scheduler_ms"].append((t_sched - step_start) * 1000)
+        if scheduled.is_empty():
+            return
+
+        chunks: List[StepChunk] = []
+        sampled: List[Request] = []
+        for request in scheduled.scheduled:
+            n = request.current_chunk_size
+            completes = request.num_computed_tokens + n >= len(request.all_token_ids)
+            chunks.append(
+                StepChunk(request.cache, request.tokens_for_chunk(n), want=(n - 1,) if completes else ())
+            )
+            if completes:
+                sampled.append(request)
+
+        if self._timing:
+            start_event = torch.cuda.Event(enable_timing=True)
+            end_event = torch.cuda.Event(enable_timing=True)
+            start_event.record()
+        logits = self.runner.step(chunks)
+        t_prepare = time.perf_counter()
+        self.stats["prepare_ms"].append((t_prepare - t_sched) * 1000)
+
+        tokens: List[int] = []
+        if sampled:
+            tokens_gpu = self.sampler.sample(
+                logits,
+                [r.sampling_params for r in sampled],
+                [r.request_id for r in sampled],
+                [r.num_output_tokens for r in sampled],
+                slots=[r.seq_index for r in sampled],
+                history_lengths=[r.num_tokens for r in sampled],
+            )
+            if self._timing:
+                end_event.record()
+            sync_start = time.perf_counter()
+            # The one place per step where the host waits for the device.
+            tokens = tokens_gpu.tolist()
+            now = time.perf_counter()
+            self.stats["cpu_sync_wait_ms"].append((now - sync_start) * 1000)
+            self.stats["sampling_ms"].append((now - t_prepare) * 1000)
+            if self._timing:
+                self.stats["gpu_ms"].append(start_event.elapsed_time(end_event))
+
+        for request in scheduled.scheduled:
+            self.cache.advance(request.cache, request.current_chunk_size)
+            request.refresh_status()
+        for request, token in zip(sampled, tokens):
+            request.append_token(int(token))
+            request.refresh_status()
+            reason = request.should_stop(int(token), self.eos_token_ids)
+            if reason is not None:
+                request.finish(reason)
+
+        self.num_steps += 1
+        self.stats["step_ms"].append((time.perf_counter() - step_start) * 1000)
+
+    @torch.no_grad()
+    def generate(self, requests: Sequence[Request], max_steps: Optional[int] = None) -> List[Request]:
+        for request in requests:
+            self.add_request(request)
+        steps = 0
+        while self.has_work():
+            self.step()
+            steps += 1
+            if max_steps is not None and steps >= max_steps:
+                break
+        return list(requests)
+
+    def snapshot(self) -> Dict[str, float]:
+        stats = self.scheduler.stats()
+        stats["num_steps"] = float(self.num_steps)
+        stats["kv_cache_bytes"] = float(self.runner.kv_cache_bytes())
+        return stats
+
+
+class LLM:
+    """Token ids in, token ids out: the shortest way to generate with a model folder.
+
+        llm = LLM("<folder>", dtype="bfloat16", max_num_seqs=8)
+        outputs = llm.generate([[1, 2, 3], [4, 5]], SamplingParams(temperature=0.0, max_tokens=16))
+    """
+
+    def __init__(self, model: str, **engine_options) -> None:
+        self.engine = Engine.from_pretrained(EngineConfig(model=model, **engine_options))
+        self._counter = 0
+
+    def generate(
+        self,
+        prompt_token_ids: Sequence[Sequence[int]],
+        sampling_params: Optional[SamplingParams | Sequence[SamplingParams]] = None,
+    ) -> List[List[int]]:
+        if sampling_params is None or isinstance(sampling_params, SamplingParams):
+            params = [sampling_params or SamplingParams()] * len(prompt_token_ids)
+        else:
+            params = list(sampling_params)
+            if len(params) != len(prompt_token_ids):
+                raise ValueError("one SamplingParams per prompt, or one for all")
+        requests = []
+        for prompt, p in zip(prompt_token_ids, params):
+            requests.append(Request(f"llm-{self._counter}", list(prompt), p))
+            self._counter += 1
+        self.engine.generate(requests)
+        return [r.output_token_ids for r in requests]

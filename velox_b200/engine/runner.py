@@ -1,0 +1,361 @@
+"""The step function: one batch of (request, its next tokens) through the model, from the cache.
+
+``ModelRunner.step`` takes portions of prompts beside single decoded tokens, cut anywhere, runs
+only the tokens it is given as one flat batch, and returns float32 logits at the wanted places.
+It is the only way tokens reach the model: generation (``engine.Engine``) and trace replay
+(``bin/trace_run``) both call it, with the cache manager deciding where the keys and values
+go.  The reference runs two homogeneous forwards per step, a prefill batch and a decode batch
+on two streams (engine/engine.py:303-329, engine/model_runner.py:171-270); here a decoded
+token is a portion of length one and the whole step is one forward.
+
+Per step the host builds, as int32 arrays (engine/model_runner.py:175-210 of the reference
+builds the same quantities): token ids, absolute positions, per cache group the flat cache
+slot of every token and the block table of every sequence, per sequence the first row, the
+portion length and the cache length after the step, the rows whose logits are wanted, and the
+attention work items.  Everything goes to the device in one copy from pinned memory.
+
+The caller grows the block tables before the step (``CacheManager.append_slots``) and records
+progress after it (``CacheManager.advance``).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager, SequenceCache
+from ..cache.storage import LayerCache, allocate_layer_cache
+from ..ops import attention_plan as ap
+from ..ops import kernels
+from .model import CausalLM
+
+
+@dataclass
+class StepChunk:
+    """A request's next tokens in this step and the places among them whose logits are wanted."""
+
+    seq: SequenceCache
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+@dataclass
+class GroupContext:
+    block_tables: torch.Tensor  # int32 [S, width]
+    slot_mapping: torch.Tensor  # int32 [T]; -1 = do not write
+
+
+@dataclass
+class DevicePlan:
+    launches: List[Tuple[int, torch.Tensor, int]] = field(default_factory=list)
+    merge_items: Optional[torch.Tensor] = None
+    num_merges: int = 0
+    partial_o: Optional[torch.Tensor] = None
+    partial_lse: Optional[torch.Tensor] = None
+
+
+class Workspace:
+    """Named device buffers that live across steps; parts ask for them by name and size."""
+
+    def __init__(self, max_tokens: int, max_logit_rows: int, device: torch.device) -> None:
+        self.max_tokens = max_tokens
+        self.max_logit_rows = max_logit_rows
+        self.device = device
+        self._buffers: Dict[str, torch.Tensor] = {}
+
+    def get(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        buf = self._buffers.get(name)
+        if buf is None or buf.dtype != dtype or tuple(buf.shape) != tuple(shape):
+            buf = torch.empty(shape, dtype=dtype, device=self.device)
+            self._buffers[name] = buf
+        return buf
+
+    def num_bytes(self) -> int:
+        return sum(b.numel() * b.element_size() for b in self._buffers.values())
+
+
+@dataclass
+class StepContext:
+    num_tokens: int
+    num_seqs: int
+    positions: torch.Tensor
+    q_start: torch.Tensor
+    q_len: torch.Tensor
+    kv_len: torch.Tensor
+    seq_slots: torch.Tensor
+    groups: List[GroupContext]
+    status: torch.Tensor
+    workspace: Workspace
+    plans: Dict[Tuple[Optional[int], Tuple], DevicePlan]
+    # Host copies, for parts that lay out work of their own.
+    q_lens_host: List[int] = field(default_factory=list)
+    kv_lens_host: List[int] = field(default_factory=list)
+
+    def attention_plan(self, group: Optional[int], signature: Tuple) -> DevicePlan:
+        return self.plans[(group, signature)]
+
+
+class _Packer:
+    """Lays int32 arrays end to end (16-byte aligned) so one copy moves them all."""
+
+    def __init__(self) -> None:
+        self.pieces: List[Tuple[int, np.ndarray]] = []
+        self.size = 0
+
+    def add(self, array: np.ndarray) -> Tuple[int, Tuple[int, ...]]:
+        flat = np.ascontiguousarray(array, dtype=np.int32).reshape(-1)
+        offset = self.size
+        self.pieces.append((offset, flat))
+        self.size += (flat.size + 3) // 4 * 4
+        return offset, tuple(array.shape)
+
+
+_STATUS_NAMES = {
+    1: "a token id outside the vocabulary",
+    2: "a position outside the position table",
+    4: "a cache slot outside the pool",
+    8: "a page id outside the pool",
+    16: "a bounded wait ran out",
+}
+
+
+class ModelRunner:
+    def __init__(
+        self,
+        model: CausalLM,
+        cache: CacheManager,
+        max_num_seqs: int,
+        max_num_batched_tokens: int,
+        max_logit_rows: Optional[int] = None,
+        plan_overrides: Optional[dict] = None,
+    ) -> None:
+        kernels._require_cuda()
+        self.model = model
+        self.cache = cache
+        self.device = model.device
+        self.dtype = model.dtype
+        self.page_size = cache.page_size
+        self.max_num_seqs = max_num_seqs
+        self.max_tokens = max(max_num_batched_tokens, max_num_seqs)
+        self.plan_overrides = dict(plan_overrides or {})
+        if [g.window for g in cache.groups] != [g.window for g in model.cache_groups]:
+            raise ValueError("the cache manager's groups are not the model's cache groups")
+
+        self.workspace = Workspace(self.max_tokens, max_logit_rows or max_num_seqs, self.device)
+        self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+
+        # One cache per schedule entry that owns one; entries that read another's share it.
+        self.layer_caches: List[LayerCache] = []
+        for index, entry in enumerate(model.spec.schedule):
+            if entry.cache_of is not None:
+                owner = self.layer_caches[entry.cache_of]
+                self.layer_caches.append(
+                    LayerCache(group=owner.group, k=owner.k, v=owner.v, state=owner.state, read_only=True)
+                )
+            else:
+                self.layer_caches.append(
+                    allocate_layer_cache(
+                        model.entry_needs[index], model.entry_group[index], cache.num_pages,
+                        cache.page_size, max_num_seqs, self.dtype, self.device,
+                    )
+                )
+        self._signatures = model.attention_signatures()
+
+        self._host: List[Optional[torch.Tensor]] = [None, None]
+        self._copied: List[Optional[torch.cuda.Event]] = [None, None]
+        self._device_meta: Optional[torch.Tensor] = None
+        self._flip = 0
+        self.num_steps = 0
+
+        cache.on_slot_acquired = self._zero_state
+
+    # ------------------------------------------------------------------ state slots
+    def _zero_state(self, seq: SequenceCache) -> None:
+        """A request that takes a state slot starts from zero state."""
+        for layer_cache in self.layer_caches:
+            if layer_cache.state is not None and not layer_cache.read_only:
+                layer_cache.state[seq.slot].zero_()
+
+    def kv_cache_bytes(self) -> int:
+        return sum(c.num_bytes() for c in self.layer_caches if not c.read_only)
+
+    # ------------------------------------------------------------------ staging
+    def _staging(self, size: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        index = self._flip
+        self._flip ^= 1
+        if self._copied[index] is not None:
+            self._copied[index].synchronize()
+        host = self._host[index]
+        if host is None or host.numel() < size:
+            capacity = max(size, 1 << 14)
+            capacity = 1 << (capacity - 1).bit_length()
+            host = torch.empty(capacity, dtype=torch.int32, pin_memory=True)
+            self._host[index] = host
+        if self._device_meta is None or self._device_meta.numel() < size:
+            capacity = 1 << (max(size, 1 << 14) - 1).bit_length()
+            self._device_meta = torch.empty(capacity, dtype=torch.int32, device=self.device)
+        if self._copied[index] is None:
+            self._copied[index] = torch.cuda.Event()
+        return host, self._device_meta
+
+    # ------------------------------------------------------------------ the step
+    @torch.no_grad()
+    def step(self, chunks: Sequence[StepChunk]) -> Optional[torch.Tensor]:
+        """Run one batch.  Returns float32 logits [number of wanted places, vocab] in the order
+        of the chunks and of their ``want`` lists, or None if nothing is wanted."""
+        if not chunks:
+            return None
+        P = self.page_size
+        num_seqs = len(chunks)
+        q_lens = [len(chunk.tokens) for chunk in chunks]
+        num_tokens = sum(q_lens)
+        if min(q_lens) < 1:
+            raise ValueError("every chunk of a step needs at least one token")
+        if num_tokens > self.max_tokens:
+            raise ValueError(f"step of {num_tokens} tokens exceeds the runner's {self.max_tokens}")
+        if num_seqs > self.max_num_seqs:
+            raise ValueError(f"step of {num_seqs} requests exceeds the runner's {self.max_num_seqs}")
+
+        ids = np.empty(num_tokens, np.int32)
+        positions = np.empty(num_tokens, np.int32)
+        q_start = np.empty(num_seqs, np.int32)
+        kv_lens: List[int] = []
+        seq_slots = np.empty(num_seqs, np.int32)
+        logit_rows: List[int] = []
+        num_groups = len(self.cache.groups)
+        slot_maps = [np.empty(num_tokens, np.int32) for _ in range(num_groups)]
+        width = 1
+        row = 0
+        for s, chunk in enumerate(chunks):
+            seq, n = chunk.seq, q_lens[s]
+            start = seq.num_computed
+            if (start + n + P - 1) // P > seq.num_logical_blocks:
+                raise ValueError(
+                    f"{seq.seq_id}: block tables hold {seq.num_logical_blocks} pages, "
+                    f"{start + n} tokens need more (append_slots was not called)"
+                )
+            ids[row : row + n] = chunk.tokens
+            pos = np.arange(start, start + n, dtype=np.int32)
+            positions[row : row + n] = pos
+            q_start[s] = row
+            kv_lens.append(start + n)
+            seq_slots[s] = self.max_num_seqs if seq.slot is None else seq.slot
+            for g in range(num_groups):
+                table = np.asarray(seq.tables[g], dtype=np.int32)
+                slot_maps[g][row : row + n] = table[pos // P] * P + pos % P
+            width = max(width, seq.num_logical_blocks)
+            for w in chunk.want:
+                if not 0 <= w < n:
+                    raise ValueError(f"{seq.seq_id}: wanted place {w} is outside its {n} tokens")
+                logit_rows.append(row + w)
+            row += n
+        width = (width + 7) // 8 * 8
+        tables = [np.zeros((num_seqs, width), np.int32) for _ in range(num_groups)]
+        for s, chunk in enumerate(chunks):
+            for g in range(num_groups):
+                t = chunk.seq.tables[g]
+                tables[g][s, : len(t)] = t
+        num_logit_rows = len(logit_rows)
+        if num_logit_rows > self.workspace.max_logit_rows:
+            self.workspace.max_logit_rows = num_logit_rows
+
+        # Attention work, one layout per distinct (cache group, head grouping, window).
+        host_plans = {}
+        for group, signature in self._signatures:
+            num_kv_heads, heads_per_kv, window = signature
+            options = dict(
+                num_kv_heads=num_kv_heads, group=heads_per_kv, window=window,
+                use_f32=self.dtype == torch.float32, target_ctas=2 * self.num_sms,
+            )
+            options.update(self.plan_overrides)
+            host_plans[(group, signature)] = ap.plan_attention(q_lens, kv_lens, ap.PlanOptions(**options))
+
+        packer = _Packer()
+        where = {
+            "ids": packer.add(ids),
+            "positions": packer.add(positions),
+            "q_start": packer.add(q_start),
+            "q_len": packer.add(np.asarray(q_lens, np.int32)),
+            "kv_len": packer.add(np.asarray(kv_lens, np.int32)),
+            "seq_slots": packer.add(seq_slots),
+            "logit_rows": packer.add(np.asarray(logit_rows, np.int32)),
+        }
+        for g in range(num_groups):
+            where[f"slots{g}"] = packer.add(slot_maps[g])
+            where[f"tables{g}"] = packer.add(tables[g])
+        plan_where = {}
+        for key, plan in host_plans.items():
+            entry = {kind: packer.add(items) for kind, items in plan.items.items()}
+            merge = packer.add(plan.merge_items) if len(plan.merge_items) else None
+            plan_where[key] = (entry, merge)
+
+        host, dev = self._staging(packer.size)
+        host_np = host.numpy()
+        for offset, flat in packer.pieces:
+            host_np[offset : offset + flat.size] = flat
+        dev[: packer.size].copy_(host[: packer.size], non_blocking=True)
+        self._copied[self._flip ^ 1].record()
+
+        def view(name: str) -> torch.Tensor:
+            offset, shape = where[name]
+            count = int(np.prod(shape)) if shape else 1
+            return dev[offset : offset + count].view(shape)
+
+        plans: Dict[Tuple[Optional[int], Tuple], DevicePlan] = {}
+        for key, plan in host_plans.items():
+            entry, merge = plan_where[key]
+            device_plan = DevicePlan()
+            for kind, (offset, shape) in entry.items():
+                count = shape[0]
+                device_plan.launches.append((kind, dev[offset : offset + count * 8].view(count, 8), count))
+            if merge is not None:
+                offset, shape = merge
+                device_plan.merge_items = dev[offset : offset + shape[0] * 8].view(shape[0], 8)
+                device_plan.num_merges = shape[0]
+            if plan.partial_rows:
+                head_dim = max(self.model.head_dims())
+                device_plan.partial_o = self._scratch("attention.partial_o", plan.partial_rows * head_dim)
+                device_plan.partial_lse = self._scratch("attention.partial_lse", plan.partial_rows)
+            plans[key] = device_plan
+
+        ctx = StepContext(
+            num_tokens=num_tokens,
+            num_seqs=num_seqs,
+            positions=view("positions"),
+            q_start=view("q_start"),
+            q_len=view("q_len"),
+            kv_len=view("kv_len"),
+            seq_slots=view("seq_slots"),
+            groups=[
+                GroupContext(block_tables=view(f"tables{g}"), slot_mapping=view(f"slots{g}"))
+                for g in range(num_groups)
+            ],
+            status=self.status,
+            workspace=self.workspace,
+            plans=plans,
+            q_lens_host=q_lens,
+            kv_lens_host=kv_lens,
+        )
+        logits = self.model.forward(ctx, self.layer_caches, view("ids"), view("logit_rows"), num_logit_rows)
+        self.num_steps += 1
+        return logits
+
+    def _scratch(self, name: str, count: int) -> torch.Tensor:
+        ws = self.workspace
+        current = ws._buffers.get(name)
+        if current is not None and current.numel() >= count:
+            return current
+        capacity = 1 << (max(count, 1 << 16) - 1).bit_length()
+        return ws.get(name, (capacity,), torch.float32)
+
+    # ------------------------------------------------------------------ checks
+    def check_status(self) -> None:
+        """Read the device status word (this synchronises) and raise if a kernel flagged a fault."""
+        word = int(self.status[0].item())
+        if word:
+            self.status.zero_()
+            what = [text for bit, text in _STATUS_NAMES.items() if word & bit]
+            raise RuntimeError("a kernel of the step refused an access: " + "; ".join(what))

@@ -1,0 +1,124 @@
+"""Host-side layout of attention work for one step: which tile of rows meets which keys.
+
+The attention kernels (csrc/attention.cu) run *work items*; this module makes them from the
+batch's (portion length, cache length) pairs.  A row is a (query token, query head of a KV
+group) pair, ``row = token_in_portion * group + head_in_group``.  Rows of one sequence are cut
+into tiles of the kernel family's height; a tile's key range is what its first and last token
+may see (causal bound above, window bound below); a long key range of a short tile is split
+so that the step fills the GPU, and the splits are merged afterwards.
+
+The reference sizes its split count from ``batch * kv_heads`` against the SM count with a cap
+of 8 (src/decode_attention.py:237-252); the rule here is the same idea without the cap, in
+units of 64-key tiles.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+
+KIND_F32, KIND_BF16_WIDE, KIND_BF16_NARROW = 0, 1, 2
+TILE_ROWS = {KIND_F32: 16, KIND_BF16_WIDE: 64, KIND_BF16_NARROW: 16}
+KEY_TILE = 64
+ITEM_WIDTH = 8
+
+
+@dataclass
+class AttentionPlan:
+    # kind -> int32 [n, 8] work items {seq, row_begin, row_count, kv_begin, kv_end, partial_base, 0, 0}
+    items: Dict[int, np.ndarray] = field(default_factory=dict)
+    # int32 [m, 8] {seq, row_begin, row_count, first_partial_base, num_splits, split_stride, 0, 0}
+    merge_items: np.ndarray = field(default_factory=lambda: np.zeros((0, ITEM_WIDTH), np.int32))
+    # Rows of float32 scratch ([rows, D] and [rows]) the splits write.
+    partial_rows: int = 0
+
+
+@dataclass(frozen=True)
+class PlanOptions:
+    num_kv_heads: int
+    group: int
+    window: Optional[int]
+    use_f32: bool
+    # CTAs the step should reach before key ranges stop being split.
+    target_ctas: int = 148 * 2
+    # A split never gets fewer keys than this.
+    min_split_keys: int = 256
+    max_splits: int = 64
+    # Portions with at most this many rows use the narrow (16-row) bf16 family.
+    narrow_max_rows: int = 64
+
+
+def _key_range(q_len: int, kv_len: int, group: int, window: Optional[int], row_begin: int,
+               row_count: int) -> Tuple[int, int]:
+    ctx = kv_len - q_len
+    first_tok = row_begin // group
+    last_tok = (row_begin + row_count - 1) // group
+    hi = ctx + last_tok + 1
+    lo = max(0, ctx + first_tok - window + 1) if window else 0
+    return lo, hi
+
+
+def plan_attention(
+    q_lens: Sequence[int],
+    kv_lens: Sequence[int],
+    opt: PlanOptions,
+    fixed_splits: Optional[int] = None,
+) -> AttentionPlan:
+    """Lay out one step.  ``fixed_splits`` forces that many splits for every tile (some may be
+    empty), which gives a layout whose shape depends on the batch size only."""
+    tiles: List[Tuple[int, int, int, int, int, int]] = []  # kind, seq, row_begin, row_count, lo, hi
+    for seq, (q_len, kv_len) in enumerate(zip(q_lens, kv_lens)):
+        rows = q_len * opt.group
+        if rows <= 0:
+            continue
+        if opt.use_f32:
+            kind = KIND_F32
+        else:
+            kind = KIND_BF16_NARROW if rows <= opt.narrow_max_rows else KIND_BF16_WIDE
+        height = TILE_ROWS[kind]
+        for row_begin in range(0, rows, height):
+            row_count = min(height, rows - row_begin)
+            lo, hi = _key_range(q_len, kv_len, opt.group, opt.window, row_begin, row_count)
+            tiles.append((kind, seq, row_begin, row_count, lo, hi))
+
+    base_ctas = len(tiles) * opt.num_kv_heads
+    per_kind: Dict[int, List[List[int]]] = {}
+    merges: List[List[int]] = []
+    partial_rows = 0
+    for kind, seq, row_begin, row_count, lo, hi in tiles:
+        span = hi - lo
+        if fixed_splits is not None:
+            splits = fixed_splits
+        elif base_ctas >= opt.target_ctas:
+            splits = 1
+        else:
+            wanted = -(-opt.target_ctas // max(base_ctas, 1))
+            splits = max(1, min(wanted, span // max(opt.min_split_keys, 1), opt.max_splits))
+        out = per_kind.setdefault(kind, [])
+        if splits <= 1:
+            out.append([seq, row_begin, row_count, lo, hi, -1, 0, 0])
+            continue
+        first_tile = lo // KEY_TILE
+        num_key_tiles = -(-hi // KEY_TILE) - first_tile
+        tiles_per_split = -(-num_key_tiles // splits)
+        stride = opt.num_kv_heads * row_count
+        merges.append([seq, row_begin, row_count, partial_rows, splits, stride, 0, 0])
+        for s in range(splits):
+            begin = max(lo, (first_tile + s * tiles_per_split) * KEY_TILE)
+            end = min(hi, (first_tile + (s + 1) * tiles_per_split) * KEY_TILE)
+            end = max(end, begin)
+            out.append([seq, row_begin, row_count, begin, end, partial_rows, 0, 0])
+            partial_rows += stride
+
+    plan = AttentionPlan(partial_rows=partial_rows)
+    for kind, rows_ in per_kind.items():
+        arr = np.asarray(rows_, dtype=np.int32).reshape(-1, ITEM_WIDTH)
+        if fixed_splits is None and len(arr) > 1:
+            # Longest key ranges first: the tail of the grid is then made of short items.
+            order = np.argsort(-(arr[:, 4] - arr[:, 3]), kind="stable")
+            arr = arr[order]
+        plan.items[kind] = arr
+    if merges:
+        plan.merge_items = np.asarray(merges, dtype=np.int32).reshape(-1, ITEM_WIDTH)
+    return plan

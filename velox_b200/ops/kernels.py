@@ -1,0 +1,399 @@
+"""Python entry points of the hand-written CUDA kernels (ctypes over the C launchers).
+
+Every function here takes torch tensors that already live on the GPU, checks what a wrong
+call could silently get wrong (dtype, contiguity, sizes), and launches on the current torch
+stream.  There is no fallback: without a CUDA device or without a working nvcc build these
+functions raise.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from ..csrc import build
+
+_c_int = ctypes.c_int
+_c_ll = ctypes.c_longlong
+_c_f = ctypes.c_float
+_ptr = ctypes.c_void_p
+
+DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+
+_core = None
+_attention = {}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _require_cuda() -> None:
+    if not torch.cuda.is_available():
+        raise KernelError(
+            "velox_b200 runs on a CUDA device only (sm_100a); no CUDA device is available "
+            "and there is no CPU path"
+        )
+
+
+def core():
+    global _core
+    if _core is None:
+        lib = build.load_core()
+        lib.vx_embed.argtypes = [_ptr, _c_int, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr, _ptr]
+        lib.vx_add_rmsnorm.argtypes = [
+            _ptr, _ptr, _ptr, _c_f, _ptr, _c_int, _ptr, _c_int, _c_int, _c_int, _ptr,
+        ]
+        lib.vx_rope_cache_write.argtypes = [
+            _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
+            _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _ptr, _ptr,
+        ]
+        lib.vx_swiglu.argtypes = [_ptr, _ptr, _c_int, _c_int, _c_int, _ptr]
+        lib.vx_gemm_f32.argtypes = [_ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr]
+        lib.vx_cast_bf16_to_f32.argtypes = [_ptr, _ptr, _c_ll, _ptr]
+        lib.vx_sample.argtypes = [
+            _ptr, _c_int, _c_int, _c_ll, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_ll, _ptr, _ptr, _ptr,
+        ]
+        lib.vx_filter_threshold.argtypes = [
+            _ptr, _c_int, _c_int, _c_ll, _ptr, _ptr, _ptr, _ptr, _ptr,
+        ]
+        lib.vx_apply_penalties.argtypes = [
+            _ptr, _c_int, _c_int, _c_ll, _ptr, _c_ll, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
+        ]
+        _core = lib
+    return _core
+
+
+def attention_lib(head_dim: int):
+    lib = _attention.get(head_dim)
+    if lib is None:
+        lib = build.load_attention(head_dim)
+        lib.vx_attention.argtypes = [
+            _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _ptr, _ptr,
+            _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_f, _ptr,
+        ]
+        lib.vx_attention_merge.argtypes = [
+            _c_int, _ptr, _ptr, _ptr, _c_int, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr,
+        ]
+        lib.vx_attn_head_dim.restype = _c_int
+        if lib.vx_attn_head_dim() != head_dim:
+            raise KernelError(f"attention library for head size {head_dim} reports another size")
+        _attention[head_dim] = lib
+    return lib
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise KernelError(f"{what}: CUDA error {code} at launch")
+
+
+def _p(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _need(t: torch.Tensor, dtype: torch.dtype, name: str) -> None:
+    if t.dtype != dtype:
+        raise TypeError(f"{name} must be {dtype}, got {t.dtype}")
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+
+
+def _code(dtype: torch.dtype) -> int:
+    try:
+        return DTYPE_CODE[dtype]
+    except KeyError:
+        raise TypeError(f"compute dtype must be float32 or bfloat16, got {dtype}") from None
+
+
+# ------------------------------------------------------------------------------------------
+def embed(table: torch.Tensor, ids: torch.Tensor, resid: torch.Tensor, status: torch.Tensor) -> None:
+    """resid[t, :] = float32(table[ids[t], :]); ids outside the table set a status bit."""
+    _need(ids, torch.int32, "ids")
+    _need(resid, torch.float32, "resid")
+    _need(table, table.dtype, "table")
+    vocab, hidden = table.shape
+    n = ids.numel()
+    if resid.shape[0] < n or resid.shape[1] != hidden:
+        raise ValueError(f"resid {tuple(resid.shape)} cannot hold {n} rows of width {hidden}")
+    _check(
+        core().vx_embed(_p(table), _code(table.dtype), _p(ids), _p(resid), n, hidden, vocab,
+                        _p(status), _stream()),
+        "embed",
+    )
+
+
+def add_rmsnorm(
+    resid: torch.Tensor,
+    delta: Optional[torch.Tensor],
+    weight: torch.Tensor,
+    eps: float,
+    out: torch.Tensor,
+    num_rows: int,
+    rows: Optional[torch.Tensor] = None,
+    write_resid: bool = True,
+) -> None:
+    """v = resid + delta; resid = v (if write_resid); out = rmsnorm(v) * weight, float32 inside.
+
+    With ``rows`` (int32 indices), output row o is computed from input row rows[o].
+    """
+    _need(resid, torch.float32, "resid")
+    _need(weight, torch.float32, "weight")
+    _need(out, out.dtype, "out")
+    hidden = resid.shape[1]
+    if weight.numel() != hidden or out.shape[1] != hidden:
+        raise ValueError("norm weight / output width does not match the residual width")
+    if delta is not None:
+        _need(delta, out.dtype, "delta")
+        if delta.shape[1] != hidden:
+            raise ValueError("delta width does not match the residual width")
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+    _check(
+        core().vx_add_rmsnorm(_p(resid), _p(delta), _p(weight), float(eps), _p(out),
+                              _code(out.dtype), _p(rows), num_rows, hidden,
+                              1 if write_resid else 0, _stream()),
+        "add_rmsnorm",
+    )
+
+
+def rope_cache_write(
+    qkv: torch.Tensor,
+    positions: torch.Tensor,
+    cos: torch.Tensor,
+    sin: torch.Tensor,
+    slots: torch.Tensor,
+    k_cache: Optional[torch.Tensor],
+    v_cache: Optional[torch.Tensor],
+    num_tokens: int,
+    num_heads: int,
+    num_kv_heads: int,
+    head_dim: int,
+    rotary_dim: int,
+    status: torch.Tensor,
+) -> None:
+    """Rotate q in place; rotate k and write k, v to the paged cache at ``slots``.
+
+    ``k_cache``/``v_cache`` None: rotate q only (a layer that reads another layer's cache).
+    """
+    _need(qkv, qkv.dtype, "qkv")
+    _need(positions, torch.int32, "positions")
+    _need(slots, torch.int32, "slots")
+    if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
+        raise ValueError("qkv width does not match the head counts")
+    write = k_cache is not None
+    if write:
+        _need(k_cache, qkv.dtype, "k_cache")
+        _need(v_cache, qkv.dtype, "v_cache")
+        num_slots = k_cache.shape[0] * k_cache.shape[1]
+    else:
+        num_slots = 0
+    if rotary_dim > 0:
+        _need(cos, torch.float32, "cos")
+        _need(sin, torch.float32, "sin")
+        max_pos = cos.shape[0]
+        if cos.shape[1] != rotary_dim // 2:
+            raise ValueError("cos/sin tables do not match the rotary width")
+    else:
+        max_pos = 0
+    _check(
+        core().vx_rope_cache_write(_p(qkv), _code(qkv.dtype), _p(positions), _p(cos), _p(sin),
+                                   _p(slots), _p(k_cache), _p(v_cache), num_tokens, num_heads,
+                                   num_kv_heads, head_dim, rotary_dim, max_pos, num_slots,
+                                   1 if write else 0, _p(status), _stream()),
+        "rope_cache_write",
+    )
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, num_tokens: int) -> None:
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+    _need(gate_up, gate_up.dtype, "gate_up")
+    _need(out, gate_up.dtype, "out")
+    inter = out.shape[1]
+    if gate_up.shape[1] != 2 * inter:
+        raise ValueError("gate_up must be twice as wide as the output")
+    _check(
+        core().vx_swiglu(_p(gate_up), _p(out), _code(out.dtype), num_tokens, inter, _stream()),
+        "swiglu",
+    )
+
+
+def gemm_f32(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+             num_rows: int) -> None:
+    """out[:M] = a[:M] @ w.T + bias on the FP32 pipes (true 32-bit, no tensor cores)."""
+    _need(a, torch.float32, "a")
+    _need(w, torch.float32, "w")
+    _need(out, torch.float32, "out")
+    n, k = w.shape
+    if a.shape[1] != k or out.shape[1] != n:
+        raise ValueError(f"gemm shapes do not agree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+        if bias.numel() != n:
+            raise ValueError("bias length does not match the output width")
+    _check(core().vx_gemm_f32(_p(a), _p(w), _p(bias), _p(out), num_rows, n, k, _stream()), "gemm_f32")
+
+
+def cast_bf16_to_f32(src: torch.Tensor, out: torch.Tensor, count: int) -> None:
+    _need(src, torch.bfloat16, "src")
+    _need(out, torch.float32, "out")
+    _check(core().vx_cast_bf16_to_f32(_p(src), _p(out), count, _stream()), "cast")
+
+
+# ------------------------------------------------------------------------------------------
+ATTN_F32, ATTN_BF16_WIDE, ATTN_BF16_NARROW = 0, 1, 2
+
+
+def tile_rows(kind: int) -> int:
+    return 64 if kind == ATTN_BF16_WIDE else 16
+
+
+def attention(
+    kind: int,
+    q: torch.Tensor,
+    out: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    block_tables: torch.Tensor,
+    q_start: torch.Tensor,
+    q_len: torch.Tensor,
+    kv_len: torch.Tensor,
+    items: torch.Tensor,
+    num_items: int,
+    partial_o: Optional[torch.Tensor],
+    partial_lse: Optional[torch.Tensor],
+    num_heads: int,
+    num_kv_heads: int,
+    head_dim: int,
+    window: Optional[int],
+    softmax_scale: float,
+) -> None:
+    """Run ``num_items`` work items (see attention.cu for their layout) of one kernel family."""
+    want = torch.float32 if kind == ATTN_F32 else torch.bfloat16
+    _need(q, want, "q")
+    _need(out, want, "out")
+    _need(k_cache, want, "k_cache")
+    _need(v_cache, want, "v_cache")
+    for name, t in (("block_tables", block_tables), ("q_start", q_start), ("q_len", q_len),
+                    ("kv_len", kv_len), ("items", items)):
+        _need(t, torch.int32, name)
+    if k_cache.shape[2] != num_kv_heads or k_cache.shape[3] != head_dim:
+        raise ValueError(f"cache shape {tuple(k_cache.shape)} does not match {num_kv_heads} x {head_dim}")
+    if num_heads % num_kv_heads != 0:
+        raise ValueError("num_heads must be a multiple of num_kv_heads")
+    if partial_o is not None:
+        _need(partial_o, torch.float32, "partial_o")
+        _need(partial_lse, torch.float32, "partial_lse")
+    lib = attention_lib(head_dim)
+    _check(
+        lib.vx_attention(kind, _p(q), _p(out), _p(k_cache), _p(v_cache), _p(block_tables),
+                         _p(q_start), _p(q_len), _p(kv_len), _p(items), num_items,
+                         _p(partial_o), _p(partial_lse), q.shape[1], out.shape[1],
+                         block_tables.shape[1], num_kv_heads, num_heads // num_kv_heads,
+                         k_cache.shape[1], int(window or 0), float(softmax_scale), _stream()),
+        "attention",
+    )
+
+
+def attention_merge(
+    out: torch.Tensor,
+    q_start: torch.Tensor,
+    merge_items: torch.Tensor,
+    num_items: int,
+    partial_o: torch.Tensor,
+    partial_lse: torch.Tensor,
+    num_heads: int,
+    num_kv_heads: int,
+    head_dim: int,
+) -> None:
+    _need(merge_items, torch.int32, "merge_items")
+    lib = attention_lib(head_dim)
+    _check(
+        lib.vx_attention_merge(_code(out.dtype), _p(out), _p(q_start), _p(merge_items), num_items,
+                               _p(partial_o), _p(partial_lse), out.shape[1], num_kv_heads,
+                               num_heads // num_kv_heads, _stream()),
+        "attention_merge",
+    )
+
+
+# ------------------------------------------------------------------------------------------
+def sample(
+    logits: torch.Tensor,
+    num_rows: int,
+    temperature: Optional[torch.Tensor],
+    seeds: Optional[torch.Tensor],
+    draw_index: Optional[torch.Tensor],
+    threshold: Optional[torch.Tensor],
+    out: torch.Tensor,
+    history: Optional[torch.Tensor] = None,
+    history_slots: Optional[torch.Tensor] = None,
+    history_lengths: Optional[torch.Tensor] = None,
+) -> None:
+    """One token per row: argmax where temperature is 0 (or None), else the exponential race.
+
+    With ``history`` (int32 [slots, width]) the token of row r is also stored at
+    ``history[history_slots[r], history_lengths[r]]``."""
+    _need(logits, torch.float32, "logits")
+    _need(out, torch.int32, "out")
+    if temperature is not None:
+        _need(temperature, torch.float32, "temperature")
+        _need(seeds, torch.int64, "seeds")
+        _need(draw_index, torch.int32, "draw_index")
+    _check(
+        core().vx_sample(_p(logits), num_rows, logits.shape[1], logits.stride(0), _p(temperature),
+                         _p(seeds), _p(draw_index), _p(threshold), _p(out), _p(history),
+                         0 if history is None else history.stride(0), _p(history_slots),
+                         _p(history_lengths), _stream()),
+        "sample",
+    )
+
+
+def filter_threshold(
+    logits: torch.Tensor,
+    num_rows: int,
+    temperature: torch.Tensor,
+    top_k: torch.Tensor,
+    top_p: torch.Tensor,
+    threshold: torch.Tensor,
+) -> None:
+    _need(logits, torch.float32, "logits")
+    _need(temperature, torch.float32, "temperature")
+    _need(top_k, torch.int32, "top_k")
+    _need(top_p, torch.float32, "top_p")
+    _need(threshold, torch.float32, "threshold")
+    _check(
+        core().vx_filter_threshold(_p(logits), num_rows, logits.shape[1], logits.stride(0),
+                                   _p(temperature), _p(top_k), _p(top_p), _p(threshold), _stream()),
+        "filter_threshold",
+    )
+
+
+def apply_penalties(
+    logits: torch.Tensor,
+    num_rows: int,
+    history: torch.Tensor,
+    slots: torch.Tensor,
+    lengths: torch.Tensor,
+    counts: torch.Tensor,
+    repetition: torch.Tensor,
+    presence: torch.Tensor,
+    frequency: torch.Tensor,
+) -> None:
+    _need(logits, torch.float32, "logits")
+    _need(history, torch.int32, "history")
+    _need(slots, torch.int32, "slots")
+    _need(lengths, torch.int32, "lengths")
+    _need(counts, torch.int32, "counts")
+    _check(
+        core().vx_apply_penalties(_p(logits), num_rows, logits.shape[1], logits.stride(0),
+                                  _p(history), history.stride(0), _p(slots), _p(lengths),
+                                  _p(counts), _p(repetition), _p(presence), _p(frequency),
+                                  _stream()),
+        "apply_penalties",
+    )

@@ -1,0 +1,92 @@
+"""Attention mixer over the paged KV cache.
+
+One forward is: fused q/k/v projection (+bias) -> position encoding on q and k, k and v written
+to the cache -> attention of the step's rows over the cache -> output projection
+(src/self_attention.py:48-90 of the reference).  A step's tokens attend to themselves through
+the cache: the write comes first.  Whether a row belongs to a prompt portion or is a single
+decoded token makes no difference here; the step's work layout decides which kernel family
+runs which rows.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..ops import kernels
+from ..ops.linear import linear
+from .base import CacheNeeds, Mixer, PagedCacheSpec
+from .registry import register_part
+
+
+@register_part("mixer", "attention")
+class Attention(Mixer):
+    def __init__(self, params, weights, dtype, device, position=None) -> None:
+        super().__init__(params, weights, dtype, device)
+        self.hidden_size = int(params["hidden_size"])
+        self.num_heads = int(params["num_heads"])
+        self.num_kv_heads = int(params["num_kv_heads"])
+        self.head_dim = int(params["head_dim"])
+        self.window: Optional[int] = params.get("window")
+        self.softmax_scale = float(params["softmax_scale"])
+        if self.num_heads % self.num_kv_heads != 0:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        if self.head_dim % 16 != 0 or not 16 <= self.head_dim <= 256:
+            raise ValueError(
+                f"head_dim={self.head_dim} is not supported by the attention kernels "
+                "(a multiple of 16 between 16 and 256)"
+            )
+        if position is None:
+            raise ValueError("the attention mixer needs a position encoding part ('none' for none)")
+        self.position = position
+        self.q_size = self.num_heads * self.head_dim
+        self.kv_size = self.num_kv_heads * self.head_dim
+        self.qkv_width = self.q_size + 2 * self.kv_size
+        self.w_qkv = self.expect("qkv.weight", (self.qkv_width, self.hidden_size))
+        self.b_qkv = None
+        self.b_qkv_lowp = None
+        if params.get("qkv_bias", False):
+            self.b_qkv = self.expect("qkv.bias", (self.qkv_width,))
+            if dtype != torch.float32:
+                self.b_qkv_lowp = self.b_qkv.to(dtype)
+        self.w_out = self.expect("out.weight", (self.hidden_size, self.q_size))
+        # Compile (or find) the kernels for this head size now, not in the first step.
+        kernels.attention_lib(self.head_dim)
+
+    def cache_needs(self) -> CacheNeeds:
+        return CacheNeeds(paged=PagedCacheSpec(self.num_kv_heads, self.head_dim, self.window))
+
+    def attention_signature(self):
+        return (self.num_kv_heads, self.num_heads // self.num_kv_heads, self.window)
+
+    def forward(self, x, ctx, cache):
+        T = ctx.num_tokens
+        ws = ctx.workspace
+        qkv = ws.get("attention.qkv", (ws.max_tokens, self.qkv_width), self.dtype)
+        linear(x, self.w_qkv, self.b_qkv, qkv, T, self.b_qkv_lowp)
+
+        group = ctx.groups[cache.group]
+        if cache.read_only:
+            self.position.rotate_and_store(qkv, ctx, group.slot_mapping, None, None,
+                                           self.num_heads, self.num_kv_heads)
+        else:
+            self.position.rotate_and_store(qkv, ctx, group.slot_mapping, cache.k, cache.v,
+                                           self.num_heads, self.num_kv_heads)
+
+        attn = ws.get("attention.out", (ws.max_tokens, self.q_size), self.dtype)
+        plan = ctx.attention_plan(cache.group, self.attention_signature())
+        for kind, items, count in plan.launches:
+            kernels.attention(
+                kind, qkv, attn, cache.k, cache.v, group.block_tables, ctx.q_start, ctx.q_len,
+                ctx.kv_len, items, count, plan.partial_o, plan.partial_lse, self.num_heads,
+                self.num_kv_heads, self.head_dim, self.window, self.softmax_scale,
+            )
+        if plan.num_merges:
+            kernels.attention_merge(
+                attn, ctx.q_start, plan.merge_items, plan.num_merges, plan.partial_o,
+                plan.partial_lse, self.num_heads, self.num_kv_heads, self.head_dim,
+            )
+
+        out = ws.get("mixer.out", (ws.max_tokens, self.hidden_size), self.dtype)
+        linear(attn, self.w_out, None, out, T)
+        return out

@@ -1,0 +1,31 @@
+"""Dense feed-forward parts.  ``swiglu`` is the reference's MLP: ``down(silu(gate(x)) * up(x))``
+with gate and up fused into one matrix whose first half is gate, and no biases
+(src/mlp.py:9-15).  SiLU and the product are computed in float32 and rounded once (the reference
+rounds to the model dtype between the two)."""
+from __future__ import annotations
+
+from ..ops import kernels
+from ..ops.linear import linear
+from .base import FeedForward
+from .registry import register_part
+
+
+@register_part("feed_forward", "swiglu")
+class SwiGLU(FeedForward):
+    def __init__(self, params, weights, dtype, device) -> None:
+        super().__init__(params, weights, dtype, device)
+        self.hidden_size = int(params["hidden_size"])
+        self.intermediate_size = int(params["intermediate_size"])
+        self.w_gate_up = self.expect("gate_up.weight", (2 * self.intermediate_size, self.hidden_size))
+        self.w_down = self.expect("down.weight", (self.hidden_size, self.intermediate_size))
+
+    def forward(self, x, ctx):
+        T = ctx.num_tokens
+        ws = ctx.workspace
+        gate_up = ws.get("swiglu.gate_up", (ws.max_tokens, 2 * self.intermediate_size), self.dtype)
+        linear(x, self.w_gate_up, None, gate_up, T)
+        act = ws.get("swiglu.act", (ws.max_tokens, self.intermediate_size), self.dtype)
+        kernels.swiglu(gate_up, act, T)
+        out = ws.get("feed_forward.out", (ws.max_tokens, self.hidden_size), self.dtype)
+        linear(act, self.w_down, None, out, T)
+        return out
