@@ -1,0 +1,189 @@
+"""Generation through the Python entry point: greedy tokens against the plain implementation,
+batched against one at a time, preemption under page pressure, seeded sampling, limits."""
+import numpy as np
+import pytest
+import torch
+
+import plain_model
+import tiny_configs
+from helpers import random_prompts, read_tensors, write_model
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    out = {}
+    for name, cfg in (("tiny_a", tiny_configs.TINY_A), ("tiny_b", tiny_configs.TINY_B), ("tiny_w", tiny_configs.TINY_W)):
+        folder = str(tmp_path_factory.mktemp(name))
+        write_model(folder, cfg, seed=31, dtype="bfloat16")
+        out[name] = (folder, cfg, read_tensors(folder))
+    return out
+
+
+def build_engine(folder, dtype="float32", **kw):
+    from velox_b200.config import EngineConfig
+    from velox_b200.engine.engine import Engine
+
+    options = dict(model=folder, dtype=dtype, max_model_len=128, max_num_seqs=4, max_num_batched_tokens=64,
+                   max_prefill_chunk_size=16, block_size=4, num_gpu_blocks=200, seed=0)
+    options.update(kw)
+    return Engine.from_pretrained(EngineConfig(**options))
+
+
+def make_requests(prompts, **params):
+    from velox_b200.engine.request import Request
+    from velox_b200.sampling.params import SamplingParams
+
+    return [Request(f"r{i}", p, SamplingParams(ignore_eos=True, **params)) for i, p in enumerate(prompts)]
+
+
+def teacher_forced_argmax(tensors, cfg, request):
+    """What greedy decoding must have produced, given what it did produce before each token."""
+    full = request.all_token_ids
+    logits = plain_model.forward_logits(tensors, cfg, full[:-1], dtype=torch.float64)
+    return logits[request.num_prompt_tokens - 1 :].argmax(-1).tolist()
+
+
+@pytest.mark.parametrize("case,page,chunk", [("tiny_a", 4, 32), ("tiny_a", 4, 3), ("tiny_b", 8, 16), ("tiny_w", 16, 7)])
+def test_greedy_generation_matches_plain(folders, case, page, chunk):
+    folder, cfg, tensors = folders[case]
+    engine = build_engine(folder, "float32", block_size=page, max_prefill_chunk_size=chunk)
+    prompts = random_prompts(cfg["vocab_size"], (5, 11, 17, 40), seed=1)
+    requests = make_requests(prompts, temperature=0.0, max_tokens=8)
+    engine.generate(requests)
+    for request in requests:
+        assert request.finish_reason.value == "length"
+        assert len(request.output_token_ids) == 8
+        assert request.output_token_ids == teacher_forced_argmax(tensors, cfg, request)
+    engine.scheduler.schedule()  # reaps the finished requests
+    engine.cache.assert_consistent()
+    assert engine.cache.num_free_pages() == engine.cache.num_total_pages
+    assert engine.cache.num_free_slots == engine.config.max_num_seqs
+
+
+def test_greedy_generation_bfloat16_tracks_plain(folders):
+    folder, cfg, tensors = folders["tiny_b"]
+    engine = build_engine(folder, "bfloat16", block_size=8)
+    prompts = random_prompts(cfg["vocab_size"], (9, 33, 70), seed=2)
+    requests = make_requests(prompts, temperature=0.0, max_tokens=12)
+    engine.generate(requests)
+    for request in requests:
+        full = request.all_token_ids
+        logits = plain_model.forward_logits(tensors, cfg, full[:-1], dtype=torch.float64)
+        rows = logits[request.num_prompt_tokens - 1 :]
+        for row, token in zip(rows, request.output_token_ids):
+            # the chosen token is the plain argmax, or within bfloat16 noise of it
+            assert row[token] >= row.max() - 3e-2 * row.abs().max()
+
+
+def test_batched_equals_one_at_a_time(folders):
+    folder, cfg, _ = folders["tiny_a"]
+    prompts = random_prompts(cfg["vocab_size"], (3, 20, 9, 31, 14), seed=3)
+    engine = build_engine(folder, "float32")
+    together = make_requests(prompts, temperature=0.0, max_tokens=20)
+    engine.generate(together)
+    for index, prompt in enumerate(prompts):
+        alone = make_requests([prompt], temperature=0.0, max_tokens=20)
+        engine.generate(alone)
+        assert alone[0].output_token_ids == together[index].output_token_ids
+
+
+def test_preemption_recomputes_and_gives_same_tokens(folders):
+    folder, cfg, tensors = folders["tiny_a"]
+    prompts = random_prompts(cfg["vocab_size"], (30, 28, 26, 33), seed=4)
+    roomy = build_engine(folder, "float32", num_gpu_blocks=200)
+    want = make_requests(prompts, temperature=0.0, max_tokens=40)
+    roomy.generate(want)
+    assert roomy.scheduler.num_preemptions == 0
+    # 4-token pages: every request ends with 70 tokens = 18 pages; 40 usable pages cannot hold four.
+    tight = build_engine(folder, "float32", num_gpu_blocks=41)
+    got = make_requests(prompts, temperature=0.0, max_tokens=40)
+    tight.generate(got)
+    assert tight.scheduler.num_preemptions > 0
+    for a, b in zip(got, want):
+        assert len(a.output_token_ids) == 40
+        assert a.output_token_ids == b.output_token_ids
+    tight.scheduler.schedule()
+    tight.cache.assert_consistent()
+    assert tight.cache.num_free_pages() == tight.cache.num_total_pages
+
+
+def test_seeded_temperature_is_reproducible_and_independent_of_the_batch(folders):
+    folder, cfg, _ = folders["tiny_b"]
+    prompts = random_prompts(cfg["vocab_size"], (1, 9, 33, 70), seed=5)
+    from velox_b200.engine.request import Request
+    from velox_b200.sampling.params import SamplingParams
+
+    def run(engine, subset):
+        requests = [
+            Request(f"s{i}", prompts[i], SamplingParams(temperature=0.8, seed=7 + i, max_tokens=12, ignore_eos=True))
+            for i in subset
+        ]
+        engine.generate(requests)
+        return {i: r.output_token_ids for i, r in zip(subset, requests)}
+
+    engine = build_engine(folder, "float32", block_size=8, max_model_len=192)
+    all_together = run(engine, [0, 1, 2, 3])
+    assert run(engine, [0, 1, 2, 3]) == all_together
+    for i in range(4):
+        assert run(engine, [i])[i] == all_together[i]
+    assert len({tuple(v) for v in all_together.values()}) == 4
+    # temperature changes what is drawn
+    greedy = make_requests([prompts[2]], temperature=0.0, max_tokens=12)
+    engine.generate(greedy)
+    assert greedy[0].output_token_ids != all_together[2]
+
+
+def test_greedy_row_is_not_disturbed_by_sampled_neighbours(folders):
+    folder, cfg, _ = folders["tiny_a"]
+    prompts = random_prompts(cfg["vocab_size"], (12, 12, 12), seed=6)
+    from velox_b200.engine.request import Request
+    from velox_b200.sampling.params import SamplingParams
+
+    engine = build_engine(folder, "float32")
+    alone = make_requests([prompts[0]], temperature=0.0, max_tokens=10)
+    engine.generate(alone)
+    mixed = [
+        Request("g", prompts[0], SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True)),
+        Request("h1", prompts[1], SamplingParams(temperature=1.5, max_tokens=10, ignore_eos=True, top_k=20)),
+        Request("h2", prompts[2], SamplingParams(temperature=1.5, max_tokens=10, ignore_eos=True, top_p=0.7,
+                                                 repetition_penalty=1.2, presence_penalty=0.1, frequency_penalty=0.1)),
+    ]
+    engine.generate(mixed)
+    assert mixed[0].output_token_ids == alone[0].output_token_ids
+    assert all(len(r.output_token_ids) == 10 for r in mixed)
+
+
+def test_stop_tokens_max_tokens_and_limits(folders):
+    folder, cfg, tensors = folders["tiny_a"]
+    from velox_b200.engine.request import Request
+    from velox_b200.sampling.params import SamplingParams
+
+    engine = build_engine(folder, "float32")
+    prompt = random_prompts(cfg["vocab_size"], (10,), seed=8)[0]
+    free_run = make_requests([prompt], temperature=0.0, max_tokens=6)
+    engine.generate(free_run)
+    tokens = free_run[0].output_token_ids
+    stopper = Request("stop", prompt, SamplingParams(temperature=0.0, max_tokens=6, stop_token_ids=[tokens[2]]))
+    engine.generate([stopper])
+    first = tokens.index(tokens[2])
+    assert stopper.output_token_ids == tokens[: first + 1]
+    assert stopper.finish_reason.value == "stop"
+    with pytest.raises(ValueError):
+        engine.add_request(Request("long", [1] * 128, SamplingParams(max_tokens=1)))
+    with pytest.raises(ValueError):
+        engine.add_request(Request("long2", [1] * 100, SamplingParams(max_tokens=40)))
+
+
+def test_llm_entry_point(folders):
+    folder, cfg, tensors = folders["tiny_a"]
+    from velox_b200.engine.engine import LLM
+    from velox_b200.sampling.params import SamplingParams
+
+    llm = LLM(folder, dtype="float32", max_model_len=128, max_num_seqs=4, max_num_batched_tokens=64,
+              max_prefill_chunk_size=16, block_size=4, num_gpu_blocks=100)
+    prompts = random_prompts(cfg["vocab_size"], (6, 13), seed=9)
+    outputs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True))
+    for prompt, output in zip(prompts, outputs):
+        assert output == plain_model.greedy_generate(tensors, cfg, prompt, 5, dtype=torch.float64)

@@ -1,0 +1,313 @@
+"""Each part of a layer alone against the plain implementation, and the generality of the
+composition: a toy architecture, defined here, with a mixer that keeps per-request state of its
+own, a layer that runs twice and a layer that reads another layer's cache, is registered, built
+from a model folder and stepped through the engine's step function without any change to the
+package's files."""
+import math
+from dataclasses import dataclass
+from typing import Any, Dict, Mapping
+
+import numpy as np
+import pytest
+import torch
+
+import plain_model
+import tiny_configs
+from helpers import random_prompts, read_tensors, write_model
+
+pytestmark = pytest.mark.gpu
+
+
+# ----------------------------------------------------------------------------------------------
+# Parts alone
+# ----------------------------------------------------------------------------------------------
+def one_layer_runner(folder, dtype, page):
+    from velox_b200.cache.manager import CacheManager
+    from velox_b200.engine.engine import load_model
+    from velox_b200.engine.runner import ModelRunner
+
+    _, spec, model = load_model(folder, dtype, torch.device("cuda:0"), max_position=256)
+    cache = CacheManager(model.cache_groups, num_pages=40, page_size=page, max_model_len=256, max_num_seqs=4)
+    return spec, model, cache, ModelRunner(model, cache, max_num_seqs=4, max_num_batched_tokens=256)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("case,page", [("tiny_a", 4), ("tiny_c", 16)])
+def test_parts_of_one_layer(tmp_path, dtype, case, page):
+    from velox_b200.engine.runner import StepChunk
+    from velox_b200.parts.base import HiddenState
+
+    cfg = tiny_configs.ALL[case]
+    write_model(str(tmp_path), cfg, seed=3, dtype="bfloat16")
+    tensors = {k: v.double() for k, v in read_tensors(str(tmp_path)).items()}
+    spec, model, cache, runner = one_layer_runner(str(tmp_path), dtype, page)
+    tol = 2e-5 if dtype == torch.float32 else 3e-2
+
+    T = 37
+    tokens = random_prompts(cfg["vocab_size"], (T,), seed=1)[0]
+    seq = cache.new_sequence("s")
+    assert cache.acquire_slot(seq) and cache.append_slots(seq, T)
+    ctx, ids, rows, _ = runner.prepare([StepChunk(seq, tokens, ())])
+    block = model.blocks[0]
+    E = cfg["hidden_size"]
+    heads, kv_heads = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    D = cfg.get("head_dim") or E // heads
+    eps = cfg["rms_norm_eps"]
+    p = "model.layers.0."
+
+    def close(got, want, what):
+        got, want = got.double().cpu(), want.double()
+        err = (got - want).abs().max().item()
+        assert err <= tol * max(want.abs().max().item(), 1e-3), f"{what}: {err:.3e}"
+
+    # embedding
+    resid = torch.zeros(256, E, device="cuda")
+    model.embedding.forward(ids, resid, ctx)
+    h0 = tensors["model.embed_tokens.weight"][torch.tensor(tokens)]
+    close(resid[:T], h0, "embedding")
+
+    # norm (no pending delta)
+    normed = torch.zeros(256, E, dtype=dtype, device="cuda")
+    block.norm_mixer.forward(resid, None, normed, T)
+    x0 = plain_model.rms_norm(h0, tensors[p + "input_layernorm.weight"], eps)
+    close(normed[:T], x0, "norm")
+
+    # mixer: attention over the cache, whole prompt
+    angles = plain_model.rope_angles(D, cfg["rope_theta"], 1.0, torch.arange(T))
+    want_attn = plain_model.attention_block(x0, tensors, p + "self_attn.", heads, kv_heads, D,
+                                            angles.cos().double(), angles.sin().double(), None)
+    exact_in = x0.to(dtype).cuda()
+    padded = torch.zeros(256, E, dtype=dtype, device="cuda")
+    padded[:T] = exact_in
+    mixed = block.mixer.forward(padded, ctx, runner.layer_caches[0])
+    close(mixed[:T], want_attn, "attention mixer")
+
+    # feed-forward
+    y = torch.randn(T, E, generator=torch.Generator().manual_seed(2)).double()
+    padded[:T] = y.to(dtype).cuda()
+    ff = block.feed_forward.forward(padded, ctx)
+    want_ff = plain_model.swiglu_mlp(y.to(dtype).double(), tensors[p + "mlp.gate_proj.weight"],
+                                     tensors[p + "mlp.up_proj.weight"], tensors[p + "mlp.down_proj.weight"])
+    close(ff[:T], want_ff, "feed-forward")
+
+    # block: norm + mixer + norm + feed-forward around the residual stream
+    seq2 = cache.new_sequence("s2")
+    assert cache.acquire_slot(seq2) and cache.append_slots(seq2, T)
+    ctx2, ids2, _, _ = runner.prepare([StepChunk(seq2, tokens, ())])
+    resid2 = torch.zeros(256, E, device="cuda")
+    model.embedding.forward(ids2, resid2, ctx2)
+    hidden = HiddenState(resid=resid2, delta=None)
+    block.forward(hidden, ctx2, runner.layer_caches[0])
+    torch.cuda.synchronize()
+    want_h = plain_model.decoder_layer(h0, tensors, 0, cfg, angles.cos().double(), angles.sin().double(), None)
+    close(hidden.resid[:T] + hidden.delta[:T].float(), want_h, "block")
+
+    # lm head on selected rows
+    final = torch.zeros(8, E, dtype=dtype, device="cuda")
+    z = torch.randn(3, E, generator=torch.Generator().manual_seed(4))
+    final[:3] = z.to(dtype).cuda()
+    logits = model.lm_head.forward(final, 3, ctx2)
+    head = tensors["model.embed_tokens.weight"] if cfg["tie_word_embeddings"] else tensors["lm_head.weight"]
+    close(logits, z.to(dtype).double() @ head.T, "lm head")
+    runner.check_status()
+
+
+# ----------------------------------------------------------------------------------------------
+# A toy architecture defined in this file
+# ----------------------------------------------------------------------------------------------
+TOY_ARCH = "ToyStateForCausalLM"
+
+
+def register_toy():
+    from velox_b200.config import ModelConfig, register_architecture
+    from velox_b200.parts import Mixer, StateSpec, register_part
+    from velox_b200.parts.base import CacheNeeds
+    from velox_b200.parts.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, TensorSource, WeightSpec
+
+    @register_part("mixer", "toy_running_mean")
+    class RunningMean(Mixer):
+        """out[t] = W @ mean(x[0..t]): the mean is carried in per-request state (sum and count),
+        so a portion continues where the previous one stopped.  Written with torch ops: it is a
+        test double, not a product kernel."""
+
+        def __init__(self, params, weights, dtype, device):
+            super().__init__(params, weights, dtype, device)
+            self.size = int(params["hidden_size"])
+            self.w = self.expect("proj.weight", (self.size, self.size))
+
+        def cache_needs(self):
+            return CacheNeeds(state=StateSpec(shape=(self.size + 1,), dtype=torch.float32))
+
+        def forward(self, x, ctx, cache):
+            out = ctx.workspace.get("toy.out", (ctx.workspace.max_tokens, self.size), self.dtype)
+            slots = ctx.seq_slots.tolist()
+            starts = ctx.q_start.tolist()
+            for s, (n, slot) in enumerate(zip(ctx.q_lens_host, slots)):
+                rows = x[starts[s] : starts[s] + n].float()
+                state = cache.state[slot]
+                sums = state[: self.size] + rows.cumsum(0)
+                counts = state[self.size] + torch.arange(1, n + 1, device=x.device, dtype=torch.float32)
+                mean = sums / counts.unsqueeze(1)
+                out[starts[s] : starts[s] + n] = (mean @ self.w.float().T).to(self.dtype)
+                state[: self.size] = sums[-1]
+                state[self.size] = counts[-1]
+            return out
+
+    @dataclass(frozen=True)
+    class ToyConfig(ModelConfig):
+        num_attention_heads: int = 2
+        head_dim: int = 16
+        intermediate_size: int = 64
+
+        def to_json_dict(self):
+            return {
+                "architectures": [self.architecture], "vocab_size": self.vocab_size, "hidden_size": self.hidden_size,
+                "num_hidden_layers": self.num_hidden_layers, "max_position_embeddings": self.max_position_embeddings,
+                "tie_word_embeddings": self.tie_word_embeddings, "num_attention_heads": self.num_attention_heads,
+                "head_dim": self.head_dim, "intermediate_size": self.intermediate_size,
+            }
+
+    def parse(cfg: Mapping[str, Any]) -> ToyConfig:
+        return ToyConfig(
+            architecture=TOY_ARCH, vocab_size=cfg["vocab_size"], hidden_size=cfg["hidden_size"],
+            num_hidden_layers=cfg["num_hidden_layers"], max_position_embeddings=cfg["max_position_embeddings"],
+            tie_word_embeddings=cfg["tie_word_embeddings"], num_attention_heads=cfg["num_attention_heads"],
+            head_dim=cfg["head_dim"], intermediate_size=cfg["intermediate_size"],
+        )
+
+    def build(c: ToyConfig) -> ModelSpec:
+        E, H, D, I, V = c.hidden_size, c.num_attention_heads, c.head_dim, c.intermediate_size, c.vocab_size
+        mat = lambda *src: WeightSpec(tuple(src), "matrix")
+        vec = lambda *src: WeightSpec(tuple(src), "vector")
+        rms = lambda name: PartSpec("rms", {"size": E, "eps": 1e-5},
+                                    {"weight": vec(TensorSource(name, (E,), "one_plus_normal"))})
+        position = PartSpec("rotary_half", {"head_dim": D, "rotary_dim": D // 2, "theta": 500.0,
+                                            "scaling_factor": 1.0, "max_position": c.max_position_embeddings})
+
+        def ffn(p):
+            return PartSpec("swiglu", {"hidden_size": E, "intermediate_size": I}, {
+                "gate_up.weight": mat(TensorSource(p + "gate.weight", (I, E)), TensorSource(p + "up.weight", (I, E))),
+                "down.weight": mat(TensorSource(p + "down.weight", (E, I)))})
+
+        def attn(p):
+            return PartSpec("attention", {"hidden_size": E, "num_heads": H, "num_kv_heads": H, "head_dim": D,
+                                          "qkv_bias": False, "window": None, "softmax_scale": 1 / math.sqrt(D)}, {
+                "qkv.weight": mat(TensorSource(p + "q.weight", (H * D, E)), TensorSource(p + "k.weight", (H * D, E)),
+                                  TensorSource(p + "v.weight", (H * D, E))),
+                "out.weight": mat(TensorSource(p + "o.weight", (E, H * D)))})
+
+        layers = [
+            LayerSpec("pre_norm", attn("l0.attn."), ffn("l0.ffn."),
+                      {"mixer": rms("l0.n1"), "feed_forward": rms("l0.n2")}, position),
+            LayerSpec("pre_norm", PartSpec("toy_running_mean", {"hidden_size": E},
+                                           {"proj.weight": mat(TensorSource("l1.mix.weight", (E, E)))}),
+                      ffn("l1.ffn."), {"mixer": rms("l1.n1"), "feed_forward": rms("l1.n2")}, None),
+            LayerSpec("pre_norm", attn("l2.attn."), ffn("l2.ffn."),
+                      {"mixer": rms("l2.n1"), "feed_forward": rms("l2.n2")}, position),
+        ]
+        embed = TensorSource("embed.weight", (V, E))
+        return ModelSpec(
+            architecture=TOY_ARCH, hidden_size=E, vocab_size=V, max_position=c.max_position_embeddings,
+            embedding=PartSpec("token_embedding", {"vocab_size": V, "hidden_size": E}, {"weight": mat(embed)}),
+            layers=tuple(layers),
+            # layer 0, the stateful layer, layer 0 again (its own cache), layer 2 reading the
+            # cache of the first entry, the stateful layer again (its own state)
+            schedule=(ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0), ScheduleEntry(2, cache_of=0), ScheduleEntry(1)),
+            final_norm=rms("final.weight"),
+            lm_head=PartSpec("linear_head", {"hidden_size": E, "vocab_size": V}, {"weight": mat(embed)}),
+        )
+
+    register_architecture(TOY_ARCH, parse, build)
+
+
+def toy_plain_logits(tensors, cfg, tokens):
+    """Plain float64 forward of the toy model, whole sequence."""
+    t = {k: v.double() for k, v in tensors.items()}
+    E, H, D = cfg["hidden_size"], cfg["num_attention_heads"], cfg["head_dim"]
+    T = len(tokens)
+    h = t["embed.weight"][torch.tensor(tokens)]
+    rot = D // 2
+    ang = plain_model.rope_angles(rot, 500.0, 1.0, torch.arange(T)).double()
+
+    def rope(x):
+        return torch.cat([plain_model.rotate_half(x[..., :rot], ang.cos(), ang.sin()), x[..., rot:]], -1)
+
+    def attn(x, p, shared_kv=None):
+        q = rope((x @ t[p + "q.weight"].T).view(T, H, D))
+        if shared_kv is None:
+            k = rope((x @ t[p + "k.weight"].T).view(T, H, D))
+            v = (x @ t[p + "v.weight"].T).view(T, H, D)
+        else:
+            k, v = shared_kv
+        o = plain_model.causal_attention(q, k, v, 1 / math.sqrt(D))
+        return o.reshape(T, H * D) @ t[p + "o.weight"].T, (k, v)
+
+    def ffn(x, p):
+        return plain_model.swiglu_mlp(x, t[p + "gate.weight"], t[p + "up.weight"], t[p + "down.weight"])
+
+    def running_mean(x):
+        mean = x.cumsum(0) / torch.arange(1, T + 1, dtype=torch.float64).unsqueeze(1)
+        return mean @ t["l1.mix.weight"].T
+
+    norm = lambda x, name: plain_model.rms_norm(x, t[name], 1e-5)
+    kv_first = None
+    for entry, (layer, shared) in enumerate([(0, False), (1, False), (0, False), (2, True), (1, False)]):
+        p = f"l{layer}."
+        x = norm(h, p + "n1")
+        if layer == 1:
+            mixed = running_mean(x)
+        else:
+            mixed, kv = attn(x, p + "attn.", kv_first if shared else None)
+            if entry == 0:
+                kv_first = kv
+        h = h + mixed
+        h = h + ffn(norm(h, p + "n2"), p + "ffn.")
+    return norm(h, "final.weight") @ t["embed.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_with_stateful_mixer(tmp_path, dtype):
+    from velox_b200.config import unregister_architecture
+    from velox_b200.engine.replay import TraceReplayer
+    from velox_b200.parts import unregister_part
+    from velox_b200.weights import write_random_model
+
+    register_toy()
+    try:
+        cfg = {"architectures": [TOY_ARCH], "vocab_size": 97, "hidden_size": 48, "num_hidden_layers": 3,
+               "max_position_embeddings": 128, "tie_word_embeddings": True, "num_attention_heads": 2,
+               "head_dim": 16, "intermediate_size": 72}
+        folder = str(tmp_path)
+        write_random_model(folder, cfg, seed=5, dtype="bfloat16", std=0.08)
+        tensors = read_tensors(folder)
+        prompts = random_prompts(97, (50, 23), seed=3)
+        want = [toy_plain_logits(tensors, cfg, p) for p in prompts]
+        replayer = TraceReplayer(folder, dtype, max_tokens=128, block_size=8)
+        a, b = prompts
+        # a: 20 tokens, then 2, then one by one beside b's portions; b ends, its slot is reused by c = a again
+        got_a = np.zeros((50, 97), np.float32)
+        got_b = np.zeros((23, 97), np.float32)
+        plan = [
+            [("a", 0, 20)], [("a", 20, 2), ("b", 0, 9)], [("a", 22, 1), ("b", 9, 13)], [("b", 22, 1), ("a", 23, 1)],
+            [("a", 24, 26)],
+        ]
+        for step, entries in enumerate(plan):
+            rec = {"step": step, "end": [],
+                   "entries": [{"id": n, "tokens": (a if n == "a" else b)[s : s + c], "want": list(range(c))} for n, s, c in entries]}
+            if step == 3:
+                rec["end"] = ["b"]
+            out = replayer.run_step(rec)
+            row = 0
+            for n, s, c in entries:
+                (got_a if n == "a" else got_b)[s : s + c] = out[row : row + c]
+                row += c
+        # a new request in b's old slot must start from zero state
+        out_c = replayer.run_step({"step": 9, "entries": [{"id": "c", "tokens": b, "want": list(range(23))}], "end": ["c", "a"]})
+        tol = 2e-5 if dtype == "float32" else 3e-2
+        for got, ref, what in ((got_a, want[0], "a"), (got_b, want[1], "b"), (out_c, want[1], "c")):
+            err = (torch.from_numpy(got).double() - ref).abs().max().item()
+            assert err <= tol * ref.abs().max().item(), (what, err, ref.abs().max().item())
+        assert replayer.cache.num_free_pages() == replayer.cache.num_total_pages
+    finally:
+        unregister_architecture(TOY_ARCH)
+        unregister_part("mixer", "toy_running_mean")

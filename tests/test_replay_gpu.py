@@ -1,0 +1,255 @@
+"""Trace replay against the plain implementation: the same requests whole, with the last 32
+tokens decoded one by one, in portions of changing size down to two tokens, and mixed with
+other requests in a pool so small that pages are used again; in float32 and in bfloat16, on
+tiny configurations that differ in every size and option."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_model
+import tiny_configs
+from helpers import random_prompts, read_tensors, write_model
+
+pytestmark = pytest.mark.gpu
+
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+# name -> (config, page size, request lengths)
+CASES = {
+    "tiny_a": (tiny_configs.TINY_A, 4, (5, 11, 17, 60, 100)),
+    "tiny_b": (tiny_configs.TINY_B, 8, (1, 9, 33, 70, 150)),
+    "tiny_w": (tiny_configs.TINY_W, 16, (40, 3, 90, 130, 64)),
+    "tiny_c": (tiny_configs.TINY_C, 16, (77, 2, 35, 200, 129)),
+}
+
+
+def tolerance(dtype: str, scale: float) -> float:
+    """float32: both sides round differently in sums of a few hundred terms.  bfloat16:
+    activations are rounded to 8 bits of mantissa about six times per layer; over a few layers
+    that is about 1e-2 of the activations' scale (3 sigma: 3e-2)."""
+    return (2e-5 if dtype == "float32" else 3e-2) * max(scale, 1e-3)
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    """Model folders (bfloat16 storage, so both dtypes see the same weights) and plain logits."""
+    out = {}
+    for name, (cfg, page, lengths) in CASES.items():
+        folder = str(tmp_path_factory.mktemp(name))
+        write_model(folder, cfg, seed=21 + len(name), dtype="bfloat16")
+        tensors = read_tensors(folder)
+        prompts = random_prompts(cfg["vocab_size"], lengths, seed=77)
+        want = [plain_model.forward_logits(tensors, cfg, p, dtype=torch.float64) for p in prompts]
+        out[name] = (folder, cfg, page, prompts, want)
+    return out
+
+
+def make_replayer(folder, dtype, max_tokens, page, **kw):
+    from velox_b200.engine.replay import TraceReplayer
+
+    return TraceReplayer(folder, dtype, max_tokens, block_size=page, **kw)
+
+
+def check(got_rows, want_rows, dtype, what):
+    got = torch.from_numpy(np.asarray(got_rows)).double()
+    want = want_rows.double()
+    assert got.shape == want.shape, (what, got.shape, want.shape)
+    scale = want.abs().max().item()
+    err = (got - want).abs().max().item()
+    assert err <= tolerance(dtype, scale), f"{what}: max abs error {err:.3e}, logit scale {scale:.3e}"
+    if dtype == "float32":
+        assert torch.equal(got.argmax(-1), want.argmax(-1)), what
+
+
+def replay_one(replayer, name, tokens, cuts):
+    """Feed ``tokens`` of one request in portions ``cuts``; logits at every position."""
+    rows, start = [], 0
+    for step, n in enumerate(cuts):
+        rec = {"step": step, "entries": [{"id": name, "tokens": tokens[start : start + n], "want": list(range(n))}],
+               "end": [name] if start + n == len(tokens) else []}
+        rows.append(replayer.run_step(rec))
+        start += n
+    assert start == len(tokens)
+    return np.concatenate(rows, axis=0)
+
+
+def changing_cuts(total):
+    sizes = [7, 2, 16, 3, 2, 5, 33, 2, 9, 64, 4, 2, 21]
+    cuts, left, i = [], total, 0
+    while left > 0:
+        n = min(sizes[i % len(sizes)], left)
+        if left - n == 1:  # never leave a single token as a "portion": it is covered elsewhere
+            n = left
+        cuts.append(n)
+        left -= n
+        i += 1
+    return cuts
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("case", list(CASES))
+def test_whole_then_decode_then_portions(models, case, dtype):
+    folder, cfg, page, prompts, want = models[case]
+    replayer = make_replayer(folder, dtype, max_tokens=256, page=page)
+    for index, (tokens, ref) in enumerate(zip(prompts, want)):
+        L = len(tokens)
+        whole = replay_one(replayer, f"w{index}", tokens, [L])
+        check(whole, ref, dtype, f"{case} request {index} whole")
+        tail = min(32, L - 1)
+        if tail > 0:
+            decoded = replay_one(replayer, f"d{index}", tokens, [L - tail] + [1] * tail)
+            check(decoded, ref, dtype, f"{case} request {index} last {tail} one by one")
+            if dtype == "float32":
+                # same kernels, same order of sums: no split below 512 keys
+                assert np.array_equal(decoded, whole), "decode differs from the whole prompt in float32"
+        if L > 2:
+            portions = replay_one(replayer, f"p{index}", tokens, changing_cuts(L))
+            check(portions, ref, dtype, f"{case} request {index} in portions")
+            if dtype == "float32":
+                assert np.array_equal(portions, whole), "portions differ from the whole prompt in float32"
+    replayer.cache.assert_consistent()
+    assert replayer.cache.num_free_pages() == replayer.cache.num_total_pages
+
+
+def mixed_trace(prompts, rng, max_live=4):
+    """Up to ``max_live`` live requests; each step feeds a portion of some and single tokens of
+    others.  Returns (steps, for each request the (step, row range) of every position)."""
+    progress = [0] * len(prompts)
+    waiting = list(range(len(prompts)))
+    live, steps = [], []
+    step = 0
+    while waiting or live:
+        while waiting and len(live) < max_live:
+            live.append(waiting.pop(0))
+        entries, ends = [], []
+        for r in list(live):
+            left = len(prompts[r]) - progress[r]
+            if rng.random() < 0.2 and len(live) > 1:
+                continue  # this request sits the step out
+            decoding = left <= 12 or rng.random() < 0.3
+            n = 1 if decoding else min(left, int(rng.choice([2, 3, 5, 8, 13, 30])))
+            if left - n == 0:
+                ends.append(r)
+            entries.append((r, progress[r], n))
+            progress[r] += n
+        if not entries:
+            continue
+        steps.append((step, entries, ends))
+        for r in ends:
+            live.remove(r)
+        step += 1
+    return steps
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("case", list(CASES))
+def test_mixed_batches_with_page_reuse(models, case, dtype):
+    folder, cfg, page, prompts, want = models[case]
+    # Twice over the requests, so that later ones run in pages earlier ones gave back.
+    order = list(range(len(prompts))) * 2
+    seqs = [prompts[i] for i in order]
+    rng = np.random.default_rng(5)
+    steps = mixed_trace(seqs, rng)
+    # The four longest requests rounded up to 64 must fit; nothing more is given.
+    need = sum(sorted((-(-len(p) // 64) * 64 for p in prompts), reverse=True)[:4])
+    replayer = make_replayer(folder, dtype, max_tokens=need, page=page)
+    used_pages = set()
+    got = [np.zeros((len(p), cfg["vocab_size"]), np.float32) for p in seqs]
+    for step, entries, ends in steps:
+        rec = {"step": step, "end": [f"r{r}" for r in ends],
+               "entries": [{"id": f"r{r}", "tokens": seqs[r][s : s + n], "want": list(range(n))} for r, s, n in entries]}
+        before = {name: list(seq.tables[0]) for name, seq in replayer.live.items()}
+        out = replayer.run_step(rec)
+        row = 0
+        for r, s, n in entries:
+            got[r][s : s + n] = out[row : row + n]
+            row += n
+        for table in before.values():
+            used_pages.update(table)
+        replayer.cache.assert_consistent()
+    for r, ref_index in enumerate(order):
+        check(got[r], want[ref_index], dtype, f"{case} mixed request {r}")
+    if dtype == "float32":
+        # the second pass of a request ran in other pages beside other neighbours
+        for r in range(len(prompts)):
+            assert np.array_equal(got[r], got[r + len(prompts)]), f"request {r}: pages or neighbours changed its logits"
+    assert replayer.cache.num_free_pages() == replayer.cache.num_total_pages
+    assert len(used_pages) <= replayer.cache.num_total_pages + 1
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decode_with_split_key_ranges(models, dtype):
+    """Decode far past the point where key ranges are split and merged."""
+    folder, cfg, page, _, _ = models["tiny_c"]
+    tensors = read_tensors(folder)
+    tokens = random_prompts(cfg["vocab_size"], [600], seed=4)[0]
+    ref = plain_model.forward_logits(tensors, cfg, tokens, dtype=torch.float64)
+    replayer = make_replayer(folder, dtype, max_tokens=640, page=page,
+                             plan_overrides={"min_split_keys": 64, "target_ctas": 4096})
+    rows = replay_one(replayer, "long", tokens, [40] + [1] * 560)
+    check(rows, ref, dtype, "long decode")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens(models, dtype):
+    """A request's very first tokens: position 0 alone, then 1, then two at once."""
+    folder, cfg, page, prompts, want = models["tiny_b"]
+    replayer = make_replayer(folder, dtype, max_tokens=64, page=page)
+    tokens, ref = prompts[3][:6], want[3][:6]
+    rows = replay_one(replayer, "f", tokens, [1, 1, 2, 2])
+    check(rows, ref, dtype, "first tokens")
+
+
+def test_want_subset_and_skipped_steps(models):
+    folder, cfg, page, prompts, want = models["tiny_a"]
+    replayer = make_replayer(folder, "float32", max_tokens=256, page=page)
+    a, b = prompts[3], prompts[2]
+    out0 = replayer.run_step({"step": 0, "entries": [{"id": "a", "tokens": a[:30], "want": [0, 29]},
+                                                     {"id": "b", "tokens": b[:5], "want": []}], "end": []})
+    assert out0.shape == (2, cfg["vocab_size"])
+    out1 = replayer.run_step({"step": 1, "entries": [{"id": "b", "tokens": b[5:], "want": [len(b) - 6]}], "end": ["b"]})
+    out2 = replayer.run_step({"step": 2, "entries": [{"id": "a", "tokens": a[30:], "want": []}], "end": []})
+    assert out2 is None
+    check(out0, want[3][[0, 29]], "float32", "subset")
+    check(out1, want[2][[len(b) - 1]], "float32", "after a skipped step")
+
+
+def test_out_of_pages_is_an_error(models):
+    folder, cfg, page, prompts, _ = models["tiny_a"]
+    replayer = make_replayer(folder, "float32", max_tokens=64, page=page)
+    replayer.run_step({"step": 0, "entries": [{"id": "a", "tokens": prompts[3][:60], "want": []}], "end": []})
+    with pytest.raises(RuntimeError, match="no pages left"):
+        replayer.run_step({"step": 1, "entries": [{"id": "b", "tokens": prompts[2], "want": []}], "end": []})
+
+
+def test_trace_run_program(models, tmp_path):
+    """The program itself, as a user runs it: JSON lines in, .f32 files and 'done' lines out."""
+    folder, cfg, page, prompts, want = models["tiny_b"]
+    a, b = prompts[2], prompts[1]
+    lines = [
+        {"step": 0, "entries": [{"id": "a", "tokens": a[:20], "want": [19]}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": a[20:], "want": list(range(len(a) - 20))},
+                                {"id": "b", "tokens": b, "want": [0, len(b) - 1]}], "end": ["a", "b"]},
+        {"step": 2, "entries": [{"id": "c", "tokens": b[:2], "want": []}], "end": ["c"]},
+    ]
+    for dtype in ("float32", "bfloat16"):
+        out_dir = tmp_path / dtype
+        proc = subprocess.run(
+            [os.path.join(REPO, "bin", "trace_run"), "--model", folder, "--dtype", dtype, "--out", str(out_dir),
+             "--max-tokens", "128"],
+            input="\n".join(json.dumps(line) for line in lines) + "\n", capture_output=True, text=True, timeout=600,
+        )
+        assert proc.returncode == 0, proc.stderr[-2000:]
+        assert [line for line in proc.stdout.splitlines() if line.startswith("done")] == ["done 0", "done 1", "done 2"]
+        V = cfg["vocab_size"]
+        s0 = np.fromfile(out_dir / "0.f32", dtype="<f4").reshape(-1, V)
+        s1 = np.fromfile(out_dir / "1.f32", dtype="<f4").reshape(-1, V)
+        assert not (out_dir / "2.f32").exists()
+        check(s0, want[2][[19]], dtype, "trace_run step 0")
+        expect1 = torch.cat([want[2][20:], want[1][[0, len(b) - 1]]])
+        check(s1, expect1, dtype, "trace_run step 1")

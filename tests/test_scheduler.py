@@ -1,0 +1,252 @@
+"""The scheduler's decisions, with a fake step: budgets, portions, order, and what happens when
+pages run out."""
+import pytest
+
+from velox_b200.cache import CacheGroup, CacheManager
+from velox_b200.config import SchedulerConfig
+from velox_b200.engine.request import FinishReason, Request, RequestStatus
+from velox_b200.engine.scheduler import Scheduler
+from velox_b200.sampling.params import SamplingParams
+
+
+def make(num_pages=64, page_size=4, max_num_seqs=4, budget=32, chunk=16, max_model_len=256, groups=None):
+    cache = CacheManager(groups or [CacheGroup("all")], num_pages=num_pages, page_size=page_size,
+                         max_model_len=max_model_len, max_num_seqs=max_num_seqs)
+    config = SchedulerConfig(max_num_seqs=max_num_seqs, max_num_batched_tokens=budget,
+                             max_prefill_chunk_size=chunk, max_model_len=max_model_len)
+    return Scheduler(cache, config), cache
+
+
+def request(name, prompt_len, max_tokens=8):
+    return Request(name, list(range(1, prompt_len + 1)), SamplingParams(temperature=0.0, max_tokens=max_tokens, ignore_eos=True))
+
+
+def fake_step(scheduler, cache, output, token=7):
+    """What the engine does after a forward, without a model."""
+    for r in output.scheduled:
+        completes = r.num_computed_tokens + r.current_chunk_size >= len(r.all_token_ids)
+        cache.advance(r.cache, r.current_chunk_size)
+        r.refresh_status()
+        if completes:
+            r.append_token(token)
+            r.refresh_status()
+            reason = r.should_stop(token, frozenset())
+            if reason is not None:
+                r.finish(reason)
+
+
+def run_all(scheduler, cache, limit=500):
+    history = []
+    while scheduler.has_work() and len(history) < limit:
+        out = scheduler.schedule()
+        history.append(out)
+        fake_step(scheduler, cache, out)
+        cache.assert_consistent()
+    return history
+
+
+def test_prompts_are_cut_into_portions_under_the_budget():
+    scheduler, cache = make(budget=20, chunk=16)
+    a, b = request("a", 40), request("b", 10)
+    scheduler.add_request(a)
+    scheduler.add_request(b)
+    out = scheduler.schedule()
+    assert [(r.request_id, r.current_chunk_size) for r in out.prefill_batch] == [("a", 16), ("b", 4)]
+    assert out.num_batched_tokens == 20 and not out.decode_batch
+    fake_step(scheduler, cache, out)
+    out = scheduler.schedule()
+    assert [(r.request_id, r.current_chunk_size) for r in out.prefill_batch] == [("a", 16), ("b", 4)]
+    fake_step(scheduler, cache, out)
+    out = scheduler.schedule()
+    # a has 8 left, b 2: both finish their prompts and will sample
+    assert [(r.request_id, r.current_chunk_size) for r in out.prefill_batch] == [("a", 8), ("b", 2)]
+    fake_step(scheduler, cache, out)
+    assert a.status is RequestStatus.RUNNING_DECODE and len(a.output_token_ids) == 1
+
+
+def test_decodes_go_first_and_cost_one_token_each():
+    scheduler, cache = make(budget=10, chunk=8)
+    a = request("a", 3)
+    scheduler.add_request(a)
+    fake_step(scheduler, cache, scheduler.schedule())
+    b = request("b", 30)
+    scheduler.add_request(b)
+    out = scheduler.schedule()
+    assert out.decode_batch == [a] and a.current_chunk_size == 1
+    assert out.prefill_batch == [b] and b.current_chunk_size == 8
+    assert out.scheduled == [b, a]
+    fake_step(scheduler, cache, out)
+    out = scheduler.schedule()
+    assert out.decode_batch == [a] and b.current_chunk_size == 8  # 10 - 1 = 9, capped by the chunk size
+
+
+def test_admission_is_in_order_and_limited_by_slots():
+    scheduler, cache = make(max_num_seqs=2, budget=64)
+    reqs = [request(f"r{i}", 5, max_tokens=2) for i in range(4)]
+    for r in reqs:
+        scheduler.add_request(r)
+    out = scheduler.schedule()
+    assert out.prefill_batch == reqs[:2] and scheduler.num_waiting == 2
+    assert [r.seq_index for r in reqs[:2]] == [0, 1] and reqs[2].seq_index is None
+    history = run_all(scheduler, cache)
+    assert all(r.finished and r.finish_reason is FinishReason.LENGTH for r in reqs)
+    assert scheduler.num_finished == 4
+    assert cache.num_free_pages() == cache.num_total_pages and cache.num_free_slots == 2
+    # finished requests are reaped at the start of the next schedule(), not in their last step
+    first_finish = next(i for i, h in enumerate(history) if any(r.finished for r in h.scheduled))
+    assert reqs[2] not in history[first_finish].scheduled
+
+
+def test_head_of_line_is_never_skipped():
+    # 9 usable pages of 4 tokens; watermark 1 page.  The head needs 8 pages and gets them;
+    # then a 40-token request waits at the head and the short one behind it waits too.
+    scheduler, cache = make(num_pages=10, budget=64, chunk=64, max_model_len=40)
+    big, big2, small = request("big", 30, 2), request("big2", 30, 2), request("small", 3, 2)
+    for r in (big, big2, small):
+        scheduler.add_request(r)
+    out = scheduler.schedule()
+    assert out.prefill_batch == [big]
+    assert list(scheduler.waiting) == [big2, small]
+
+
+def test_watermark_keeps_pages_free_at_admission():
+    scheduler, cache = make(num_pages=11, budget=64, chunk=64, max_model_len=44)  # 10 usable, watermark 1
+    a = request("a", 39, 1)
+    scheduler.add_request(a)
+    out = scheduler.schedule()
+    # 9 pages = 36 tokens may be taken at admission; the rest follows as a running prefill
+    assert a.current_chunk_size == 36
+    fake_step(scheduler, cache, out)
+    out = scheduler.schedule()
+    assert out.prefill_batch == [a] and a.current_chunk_size == 3
+
+
+def test_portion_shrinks_to_the_free_pages():
+    scheduler, cache = make(num_pages=13, budget=64, chunk=32, max_model_len=48)  # 12 usable
+    a, b = request("a", 30, 1), request("b", 30, 1)
+    scheduler.add_request(a)
+    scheduler.add_request(b)
+    out = scheduler.schedule()
+    # a takes 30 tokens = 8 pages; 4 are free, minus the watermark: b gets 3 pages = 12 tokens
+    assert [(r.request_id, r.current_chunk_size) for r in out.prefill_batch] == [("a", 30), ("b", 12)]
+
+
+def test_decode_preempts_the_newest_and_it_requeues_at_the_front():
+    scheduler, cache = make(num_pages=7, page_size=4, budget=64, chunk=64, max_model_len=24)  # 6 usable pages
+    a, b = request("a", 8, 10), request("b", 7, 10)
+    scheduler.add_request(a)
+    scheduler.add_request(b)
+    c = request("c", 2, 2)
+    out = scheduler.schedule()
+    assert out.prefill_batch == [a, b]  # a: 2 pages, b: 2 pages (8th slot free in its second page)
+    fake_step(scheduler, cache, out)
+    scheduler.add_request(c)
+    preempted_seen = []
+    for _ in range(60):
+        if not scheduler.has_work():
+            break
+        out = scheduler.schedule()
+        preempted_seen.extend(r.request_id for r in out.preempted)
+        if out.preempted:
+            victim = out.preempted[0]
+            # recompute: nothing cached, generated tokens kept, back at the head of the queue
+            # (it may be admitted again in the same schedule() when the pages allow it)
+            assert victim.num_computed_tokens == 0
+            if victim in out.prefill_batch:
+                assert victim.status is RequestStatus.RUNNING_PREFILL
+            else:
+                assert victim.status is RequestStatus.PREEMPTED and victim.block_table == []
+                assert scheduler.waiting[0] is victim
+        fake_step(scheduler, cache, out)
+        cache.assert_consistent()
+    assert preempted_seen and preempted_seen[0] in ("b", "c")
+    assert "a" not in preempted_seen[:1]
+    assert all(r.finished for r in (a, b, c))
+    assert len(a.output_token_ids) == 10 and len(b.output_token_ids) == 10
+    assert scheduler.num_preemptions == len(preempted_seen)
+    assert cache.num_free_pages() == cache.num_total_pages
+
+
+def test_preempted_request_is_prefilled_again_with_its_generated_tokens():
+    scheduler, cache = make(num_pages=6, page_size=4, budget=64, chunk=64, max_model_len=20)  # 5 usable
+    a, b = request("a", 6, 8), request("b", 6, 8)
+    scheduler.add_request(a)
+    scheduler.add_request(b)
+    seen_b_prefill_lengths = []
+    for _ in range(80):
+        if not scheduler.has_work():
+            break
+        out = scheduler.schedule()
+        for r in out.prefill_batch:
+            if r is b:
+                seen_b_prefill_lengths.append((r.num_computed_tokens, r.current_chunk_size, len(r.all_token_ids)))
+        fake_step(scheduler, cache, out)
+    assert a.finished and b.finished and b.num_preemptions >= 1
+    # after a preemption b starts again from token 0 and covers prompt + generated tokens
+    restarts = [entry for entry in seen_b_prefill_lengths if entry[0] == 0]
+    assert len(restarts) >= 2 and restarts[-1][2] > 6
+    assert len(b.output_token_ids) == 8
+
+
+def test_a_lone_request_that_cannot_grow_preempts_itself_and_retries():
+    scheduler, cache = make(num_pages=4, page_size=4, budget=64, chunk=64, max_model_len=12)  # 3 usable = 12 tokens
+    a = request("a", 6, 6)
+    scheduler.add_request(a)
+    history = run_all(scheduler, cache, limit=100)
+    assert a.finished and len(a.output_token_ids) == 6
+    assert len(history) < 100
+
+
+def test_oldest_running_prefill_may_preempt_younger_ones():
+    scheduler, cache = make(num_pages=9, page_size=4, budget=16, chunk=8, max_model_len=32)  # 8 usable
+    a, b = request("a", 30, 1), request("b", 20, 1)
+    scheduler.add_request(a)
+    scheduler.add_request(b)
+    preemptions = []
+    for _ in range(100):
+        if not scheduler.has_work():
+            break
+        out = scheduler.schedule()
+        preemptions.extend(r.request_id for r in out.preempted)
+        fake_step(scheduler, cache, out)
+        cache.assert_consistent()
+    assert a.finished and b.finished
+    assert preemptions and set(preemptions) == {"b"}
+
+
+def test_limits_and_abort():
+    scheduler, cache = make(max_model_len=32, num_pages=64)
+    with pytest.raises(ValueError, match="does not fit"):
+        scheduler.add_request(request("long", 32, 1))
+    with pytest.raises(ValueError, match="exceeds"):
+        scheduler.add_request(request("long2", 20, 13))
+    with pytest.raises(ValueError):
+        Request("empty", [], SamplingParams())
+    a, b = request("a", 5, 4), request("b", 5, 4)
+    scheduler.add_request(a)
+    scheduler.add_request(b)
+    with pytest.raises(ValueError, match="already"):
+        scheduler.add_request(request("a", 3, 1))
+    fake_step(scheduler, cache, scheduler.schedule())
+    assert scheduler.abort_request("a") and a.finish_reason is FinishReason.ABORT
+    assert not scheduler.abort_request("a") and not scheduler.abort_request("zzz")
+    run_all(scheduler, cache)
+    assert b.finished and cache.num_free_pages() == cache.num_total_pages and cache.num_free_slots == 4
+
+
+def test_pages_are_counted_in_every_group():
+    groups = [CacheGroup("all"), CacheGroup("w", window=8)]
+    scheduler, cache = make(num_pages=12, page_size=4, budget=64, chunk=64, max_model_len=44, groups=groups)
+    reqs = [request(f"r{i}", 14, 6) for i in range(3)]
+    for r in reqs:
+        scheduler.add_request(r)
+    run_all(scheduler, cache)
+    assert all(r.finished and len(r.output_token_ids) == 6 for r in reqs)
+    assert all(alloc.num_used == 0 for alloc in cache.allocators)
+
+
+def test_stats():
+    scheduler, cache = make()
+    scheduler.add_request(request("a", 5, 2))
+    stats = scheduler.stats()
+    assert stats["num_waiting"] == 1 and stats["num_running"] == 0 and stats["free_blocks"] == 63

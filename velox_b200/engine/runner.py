@@ -208,6 +208,13 @@ class ModelRunner:
         of the chunks and of their ``want`` lists, or None if nothing is wanted."""
         if not chunks:
             return None
+        ctx, ids, logit_rows, num_logit_rows = self.prepare(chunks)
+        logits = self.model.forward(ctx, self.layer_caches, ids, logit_rows, num_logit_rows)
+        self.num_steps += 1
+        return logits
+
+    def prepare(self, chunks: Sequence[StepChunk]):
+        """Build the step's device-side description: (context, token ids, logit rows, their count)."""
         P = self.page_size
         num_seqs = len(chunks)
         q_lens = [len(chunk.tokens) for chunk in chunks]
@@ -339,9 +346,7 @@ class ModelRunner:
             q_lens_host=q_lens,
             kv_lens_host=kv_lens,
         )
-        logits = self.model.forward(ctx, self.layer_caches, view("ids"), view("logit_rows"), num_logit_rows)
-        self.num_steps += 1
-        return logits
+        return ctx, view("ids"), view("logit_rows"), num_logit_rows
 
     def _scratch(self, name: str, count: int) -> torch.Tensor:
         ws = self.workspace
