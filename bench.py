@@ -1,0 +1,357 @@
+"""Benchmark: decode tokens/s (batch 8 by default; batch 1 and 64 as extra points) and prefill
+tokens/s at 2,048 tokens, at Qwen2.5-1.5B layer sizes with random weights, on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference]
+
+Prints ONE JSON line.  ``value`` is decoded tokens per second of the step function (device time
+of K decode steps, CUDA events); ``e2e`` is the same through the Python entry point
+(``Engine.step``: host token ids in through pinned memory, sampled tokens read back, every
+step).  ``prefill`` is one 2,048-token prompt in one step; ``roofline`` is the decode step's
+bytes (every weight once, the live requests' cache) over its time against the measured copy
+bandwidth.  With --gpus N > 1 it says that the engine is single-GPU and exits with 2.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# Qwen2.5-1.5B layer sizes (the benchmark's third configuration).
+MODEL_1P5B = {
+    "architectures": ["Qwen2ForCausalLM"],
+    "model_type": "qwen2",
+    "num_hidden_layers": 28,
+    "hidden_size": 1536,
+    "num_attention_heads": 12,
+    "num_key_value_heads": 2,
+    "intermediate_size": 8960,
+    "vocab_size": 151936,
+    "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6,
+    "tie_word_embeddings": True,
+    "use_sliding_window": False,
+    "max_position_embeddings": 32768,
+    "hidden_act": "silu",
+}
+FULL_LAYERS = 28
+CONTEXT = 4096
+PREFILL_TOKENS = 2048
+BLOCK_SIZE = 16
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        with open(path) as handle:
+            peaks = json.load(handle)
+        peaks["source"] = "measured"
+        return peaks
+    return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples = []
+        self._proc = None
+        self._thread = None
+
+    def start(self):
+        try:
+            self._proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+            )
+        except OSError:
+            return
+        self._thread = threading.Thread(target=self._read, daemon=True)
+        self._thread.start()
+
+    def _read(self):
+        for line in self._proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self._proc is not None:
+            self._proc.terminate()
+            try:
+                self._proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self._proc.kill()
+        sm, reasons, sm_max = [], set(), None
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for parts in self.samples:
+            try:
+                sm.append(float(parts[0]))
+                sm_max = float(parts[1])
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[2:6]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {
+            "sm_mhz": sm[len(sm) // 2] if sm else None,
+            "sm_max_mhz": sm_max,
+            "reasons": sorted(reasons),
+            "samples": len(sm),
+        }
+
+
+def model_bytes(cfg, layers):
+    E, H, G, I, V = (cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"],
+                     cfg["intermediate_size"], cfg["vocab_size"])
+    D = E // H
+    per_layer = ((H + 2 * G) * D * E + E * H * D + 3 * I * E) * 2 + ((H + 2 * G) * D + 2 * E) * 4
+    head = V * E * 2
+    return layers * per_layer + head + E * 4, 2 * G * D * 2 * layers  # weight bytes, KV bytes per token
+
+
+def model_flops_per_token(cfg, layers, context):
+    """Multiply-add flops of one token at a given number of visible keys."""
+    E, H, G, I, V = (cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"],
+                     cfg["intermediate_size"], cfg["vocab_size"])
+    D = E // H
+    gemm = 2 * ((H + 2 * G) * D * E + E * H * D + 3 * I * E)
+    attn = 4 * H * D * context
+    return layers * (gemm + attn)
+
+
+def run_own(args):
+    import numpy as np
+    import torch
+
+    from velox_b200.config import EngineConfig
+    from velox_b200.engine.engine import Engine
+    from velox_b200.engine.request import Request
+    from velox_b200.engine.runner import StepChunk
+    from velox_b200.ops import kernels
+    from velox_b200.sampling.params import SamplingParams
+    from velox_b200.weights import write_random_model
+
+    peaks = load_peaks()
+    layers = args.layers
+    cfg = dict(MODEL_1P5B, num_hidden_layers=layers)
+    folder = tempfile.mkdtemp(prefix="velox_bench_")
+    t0 = time.time()
+    write_random_model(folder, cfg, seed=0, dtype="bfloat16")
+    print(f"[bench] wrote random {layers}-layer model in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
+
+    max_batch = max(args.batch, 64 if args.points else args.batch)
+    pages_per_seq = CONTEXT // BLOCK_SIZE + 1
+    engine = Engine.from_pretrained(EngineConfig(
+        model=folder, dtype="bfloat16", max_model_len=CONTEXT + 16, max_num_seqs=max_batch,
+        max_num_batched_tokens=max(PREFILL_TOKENS, max_batch), max_prefill_chunk_size=PREFILL_TOKENS,
+        block_size=BLOCK_SIZE, num_gpu_blocks=max_batch * pages_per_seq + 8, seed=0,
+    ))
+    import shutil
+
+    shutil.rmtree(folder, ignore_errors=True)
+    runner, cache, sampler = engine.runner, engine.cache, engine.sampler
+    vocab = cfg["vocab_size"]
+    rng = np.random.default_rng(0)
+    weight_bytes, kv_bytes_per_token = model_bytes(cfg, layers)
+
+    def fill(batch, context):
+        """``batch`` sequences with ``context`` tokens in the cache, through the step function."""
+        seqs = []
+        for b in range(batch):
+            seq = cache.new_sequence(f"bench{b}")
+            assert cache.acquire_slot(seq)
+            seqs.append(seq)
+            done = 0
+            while done < context:
+                n = min(PREFILL_TOKENS, context - done)
+                assert cache.append_slots(seq, n)
+                runner.step([StepChunk(seq, rng.integers(0, vocab, n).tolist(), ())])
+                cache.advance(seq, n)
+                done += n
+        torch.cuda.synchronize()
+        return seqs
+
+    def release(seqs):
+        for seq in seqs:
+            cache.free(seq)
+            cache.release_slot(seq)
+
+    def decode_steps(seqs, steps, warmup):
+        """Device time (ms) of each of ``steps`` decode steps after ``warmup`` untimed ones."""
+        batch = len(seqs)
+        tokens = rng.integers(0, vocab, batch).tolist()
+        params = [SamplingParams(temperature=0.0, max_tokens=1)] * batch
+        names = [s.seq_id for s in seqs]
+        times = []
+        launches_before = None
+        for step in range(warmup + steps):
+            if step == warmup:
+                launches_before = kernels.launch_count
+            chunks = []
+            for seq, token in zip(seqs, tokens):
+                assert cache.append_slots(seq, 1)
+                chunks.append(StepChunk(seq, [token], (0,)))
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            start.record()
+            logits = runner.step(chunks)
+            out = sampler.sample(logits, params, names, [0] * batch)
+            end.record()
+            torch.cuda.synchronize()
+            tokens = out.tolist()
+            for seq in seqs:
+                cache.advance(seq, 1)
+            if step >= warmup:
+                times.append(start.elapsed_time(end))
+        return times, kernels.launch_count - launches_before
+
+    def decode_point(batch, steps, warmup):
+        context = CONTEXT - steps - warmup - 1
+        seqs = fill(batch, context)
+        times, launches = decode_steps(seqs, steps, warmup)
+        release(seqs)
+        ms = sum(times) / len(times)
+        return batch * 1000.0 / ms, ms, launches, context + warmup + steps // 2
+
+    clocks = ClockSampler()
+    clocks.start()
+    value, ms_per_step, launches, mean_context = decode_point(args.batch, args.steps, args.warmup)
+    clock_summary = clocks.stop()
+
+    step_bytes = weight_bytes + args.batch * mean_context * kv_bytes_per_token
+    achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": round(achieved / peaks["hbm_gbs"], 4), "peak_source": peaks["source"]}
+
+    # Prefill: one 2,048-token prompt in one step.
+    prefill_times = []
+    for i in range(3 + 3):
+        seq = cache.new_sequence(f"prefill{i}")
+        assert cache.acquire_slot(seq) and cache.append_slots(seq, PREFILL_TOKENS)
+        ids = rng.integers(0, vocab, PREFILL_TOKENS).tolist()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        runner.step([StepChunk(seq, ids, (PREFILL_TOKENS - 1,))])
+        end.record()
+        torch.cuda.synchronize()
+        cache.advance(seq, PREFILL_TOKENS)
+        release([seq])
+        if i >= 3:
+            prefill_times.append(start.elapsed_time(end))
+    prefill_ms = sum(prefill_times) / len(prefill_times)
+    prefill_flops = sum(model_flops_per_token(cfg, layers, t + 1) for t in range(PREFILL_TOKENS))
+    prefill_flops += 2 * cfg["vocab_size"] * cfg["hidden_size"]  # one row of logits
+    prefill = {"value": round(PREFILL_TOKENS * 1000.0 / prefill_ms, 1), "tokens": PREFILL_TOKENS,
+               "ms": round(prefill_ms, 3),
+               "frac": round(prefill_flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
+
+    points = {}
+    if args.points:
+        for batch in (1, 64):
+            tok_s, _, _, _ = decode_point(batch, max(8, args.steps // 2), 3)
+            points[f"decode_b{batch}"] = round(tok_s, 1)
+
+    # End to end through the entry point: Engine.step with host tokens in and out.
+    prompts = [rng.integers(0, vocab, CONTEXT - args.steps - args.warmup - 8).tolist() for _ in range(args.batch)]
+    requests = [Request(f"e2e{i}", p, SamplingParams(temperature=0.0, max_tokens=args.steps + args.warmup + 4,
+                                                     ignore_eos=True)) for i, p in enumerate(prompts)]
+    for request in requests:
+        engine.add_request(request)
+    while any(not r.is_decoding or r.num_output_tokens < 1 for r in requests):
+        engine.step()
+    for _ in range(args.warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    produced_before = sum(r.num_output_tokens for r in requests)
+    t_start = time.perf_counter()
+    for _ in range(args.steps):
+        engine.step()
+    torch.cuda.synchronize()
+    e2e_seconds = time.perf_counter() - t_start
+    produced = sum(r.num_output_tokens for r in requests) - produced_before
+    for request in requests:
+        engine.abort_request(request.request_id)
+    meta_bytes = 4 * (args.batch * (6 + 2 * (CONTEXT // BLOCK_SIZE + 8)))
+    e2e = {"value": round(produced / e2e_seconds, 1), "unit": "tokens/s",
+           "h2d_bytes_per_step": meta_bytes, "d2h_bytes_per_step": 4 * args.batch}
+
+    line = {
+        "metric": "decode tok/s at batch 1/8/64; prefill tok/s at 2,048 tokens (Qwen2.5-1.5B)",
+        "value": round(value, 1),
+        "unit": "tokens/s",
+        "n_gpus": 1,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": round(ms_per_step, 4),
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic: seeded random weights, uniform-random token ids",
+        "config": {
+            "model": "Qwen2.5-1.5B layer sizes", "layers": layers, "layers_full_model": FULL_LAYERS,
+            "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+            "head_dim": cfg["hidden_size"] // cfg["num_attention_heads"], "intermediate": cfg["intermediate_size"],
+            "vocab": cfg["vocab_size"], "global_batch": args.batch, "seq_len": CONTEXT, "prefill_tokens": PREFILL_TOKENS,
+            "kv_block_size": BLOCK_SIZE, "tied_embeddings": True, "parallelism": "single GPU",
+            "l2": "inputs larger than L2 (weights streamed every step)", "gemm": "cuBLAS bf16 (library), as the reference",
+        },
+        "clocks": clock_summary,
+        "e2e": e2e,
+        "gpu_launches": launches,
+        "prefill": prefill,
+        "roofline": roofline,
+        "points": points,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def run_reference(args):
+    print(json.dumps({
+        "impl": "reference",
+        "unavailable": "the reference has neither setup.py nor pyproject.toml: pip install of its tree fails "
+                       "('Directory is not installable'), so there is no baseline/_ref to run",
+    }))
+    return 0
+
+
+def main():
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers of the same sizes (reported)")
+    parser.add_argument("--impl", default="own", choices=["own", "reference"])
+    parser.add_argument("--no-points", dest="points", action="store_false", help="skip the batch 1 / 64 points")
+    args = parser.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.gpus > 1 or world > 1:
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(f"bench.py: this engine runs on one GPU; --gpus {max(args.gpus, world)} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        return run_reference(args)
+    return run_own(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,192 @@
+"""End-to-end benchmark command line, in the manner of the reference's ``benchmark.py``.
+
+    python -m velox_b200.cli.benchmark --model DIR [--workload mixed] [--num-requests 16] ...
+
+Option names and meanings are the reference's where it has them (benchmark.py:349-388 of that
+project): ``--model``, ``--workload {short,long,mixed}``, ``--num-requests``, ``--max-tokens``,
+``--temperature``, ``--top-p``, ``--max-model-len``, ``--max-num-seqs``,
+``--max-num-batched-tokens``, ``--max-prefill-chunk-size``, ``--block-size``,
+``--num-gpu-blocks``, ``--gpu-memory-utilization``, ``--sweep-batch-size``, ``--show-outputs``,
+``--output-json``, ``--seed``.  The reference builds its prompts from English text through a
+tokenizer; there is no tokenizer here, so prompts are seeded uniform-random token ids whose
+lengths follow the workload (short: 16-64, long: 512-1536, mixed: both).  Added: ``--dtype``,
+``--random-weights CONFIG_JSON`` with ``--weights-seed`` (writes the model folder first), and
+``--top-k``.  It prints what the reference prints: wall time, steps, prompt and generated
+tokens, decode tokens/s (generated / wall), time to first token and inter-token latency
+percentiles, the per-stage time of a step, and the sweep table.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import sys
+import tempfile
+import time
+from typing import Dict, List, Optional
+
+WORKLOADS = {"short": [(16, 64)], "long": [(512, 1536)], "mixed": [(16, 64), (512, 1536), (128, 384)]}
+
+
+def parse_args(argv: Optional[List[str]] = None) -> argparse.Namespace:
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--model", default=None, help="model folder (config.json + model.safetensors)")
+    parser.add_argument("--random-weights", default=None, metavar="CONFIG_JSON",
+                        help="write a random-weights model folder from this config.json first")
+    parser.add_argument("--weights-seed", type=int, default=0)
+    parser.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    parser.add_argument("--workload", default="mixed", choices=sorted(WORKLOADS))
+    parser.add_argument("--num-requests", type=int, default=16)
+    parser.add_argument("--max-tokens", type=int, default=128)
+    parser.add_argument("--temperature", type=float, default=0.0)
+    parser.add_argument("--top-p", type=float, default=1.0)
+    parser.add_argument("--top-k", type=int, default=0)
+    parser.add_argument("--max-model-len", type=int, default=2048)
+    parser.add_argument("--max-num-seqs", type=int, default=32)
+    parser.add_argument("--max-num-batched-tokens", type=int, default=2048)
+    parser.add_argument("--max-prefill-chunk-size", type=int, default=512)
+    parser.add_argument("--block-size", type=int, default=16)
+    parser.add_argument("--num-gpu-blocks", type=int, default=None)
+    parser.add_argument("--gpu-memory-utilization", type=float, default=0.85)
+    parser.add_argument("--no-cuda-graphs", action="store_true")
+    parser.add_argument("--sweep-batch-size", default=None, help="comma-separated max_num_seqs values to sweep")
+    parser.add_argument("--show-outputs", action="store_true")
+    parser.add_argument("--output-json", default=None)
+    parser.add_argument("--seed", type=int, default=0)
+    args = parser.parse_args(argv)
+    if (args.model is None) == (args.random_weights is None):
+        parser.error("give exactly one of --model and --random-weights")
+    return args
+
+
+def build_prompts(workload: str, count: int, vocab: int, limit: int, seed: int) -> List[List[int]]:
+    import numpy as np
+
+    rng = np.random.default_rng(seed)
+    ranges = WORKLOADS[workload]
+    prompts = []
+    for index in range(count):
+        low, high = ranges[index % len(ranges)]
+        length = int(min(rng.integers(low, high + 1), limit))
+        prompts.append(rng.integers(0, vocab, length).tolist())
+    return prompts
+
+
+def percentile(values: List[float], q: float) -> float:
+    if not values:
+        return float("nan")
+    ordered = sorted(values)
+    return ordered[min(len(ordered) - 1, int(q * len(ordered)))]
+
+
+def run_workload(engine, prompts, args) -> Dict[str, object]:
+    from ..engine.request import Request
+    from ..sampling.params import SamplingParams
+
+    token_times: Dict[str, List[float]] = {}
+    requests = []
+    for index, prompt in enumerate(prompts):
+        params = SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k,
+                                max_tokens=args.max_tokens, ignore_eos=True, seed=args.seed + index)
+        request = Request(f"bench-{index}", prompt, params)
+        token_times[request.request_id] = []
+        request.add_listener(
+            lambda r, kind, token: token_times[r.request_id].append(time.perf_counter()) if kind == "token" else None
+        )
+        requests.append(request)
+    start = time.perf_counter()
+    for request in requests:
+        request.arrival_time = time.time()
+        engine.add_request(request)
+    steps = 0
+    while engine.has_work():
+        engine.step()
+        steps += 1
+    wall = time.perf_counter() - start
+    generated = sum(r.num_output_tokens for r in requests)
+    ttft = [times[0] - start for times in token_times.values() if times]
+    itl = [b - a for times in token_times.values() for a, b in zip(times, times[1:])]
+    return {
+        "wall_s": wall,
+        "steps": steps,
+        "prompt_tokens": sum(len(p) for p in prompts),
+        "generated_tokens": generated,
+        "decode_tok_s": generated / wall if wall > 0 else 0.0,
+        "ttft_mean_s": statistics.mean(ttft) if ttft else float("nan"),
+        "ttft_p50_s": percentile(ttft, 0.5),
+        "ttft_p99_s": percentile(ttft, 0.99),
+        "itl_p50_ms": 1000 * percentile(itl, 0.5),
+        "itl_p95_ms": 1000 * percentile(itl, 0.95),
+        "preemptions": engine.scheduler.num_preemptions,
+        "stages_ms": {name: (statistics.mean(v) if v else 0.0) for name, v in engine.stats.items()},
+        "blocks_used_peak": None,
+        "requests": requests,
+    }
+
+
+def report(result: Dict[str, object], label: str) -> None:
+    print(f"== {label}")
+    print(f"wall time          {result['wall_s']:.3f} s   steps {result['steps']}")
+    print(f"prompt tokens      {result['prompt_tokens']}   generated tokens {result['generated_tokens']}")
+    print(f"decode throughput  {result['decode_tok_s']:.1f} tok/s")
+    print(f"TTFT mean / p50 / p99   {result['ttft_mean_s']:.4f} / {result['ttft_p50_s']:.4f} / {result['ttft_p99_s']:.4f} s")
+    print(f"ITL p50 / p95      {result['itl_p50_ms']:.3f} / {result['itl_p95_ms']:.3f} ms")
+    print(f"preemptions        {result['preemptions']}")
+    stages = result["stages_ms"]
+    print("per-step stage (mean ms): " + "  ".join(f"{k}={v:.3f}" for k, v in stages.items()))
+    if stages.get("step_ms"):
+        print(f"GPU-busy fraction  {stages.get('gpu_ms', 0.0) / stages['step_ms']:.2f}")
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    args = parse_args(argv)
+    from ..config import EngineConfig
+    from ..engine.engine import Engine
+
+    model_dir = args.model
+    holder = None
+    if args.random_weights is not None:
+        from ..weights import write_random_model
+
+        with open(args.random_weights, "r", encoding="utf-8") as handle:
+            config_json = json.load(handle)
+        holder = tempfile.TemporaryDirectory(prefix="velox_model_")
+        model_dir = holder.name
+        write_random_model(model_dir, config_json, seed=args.weights_seed, dtype="bfloat16")
+
+    sweep = [int(v) for v in args.sweep_batch_size.split(",")] if args.sweep_batch_size else [args.max_num_seqs]
+    table = []
+    for max_num_seqs in sweep:
+        engine = Engine.from_pretrained(EngineConfig(
+            model=model_dir, dtype=args.dtype, max_model_len=args.max_model_len, max_num_seqs=max_num_seqs,
+            max_num_batched_tokens=max(args.max_num_batched_tokens, max_num_seqs),
+            max_prefill_chunk_size=args.max_prefill_chunk_size, block_size=args.block_size,
+            num_gpu_blocks=args.num_gpu_blocks, gpu_memory_utilization=args.gpu_memory_utilization,
+            enable_cuda_graphs=not args.no_cuda_graphs, seed=args.seed,
+        ))
+        limit = engine.max_model_len - args.max_tokens - 1
+        prompts = build_prompts(args.workload, args.num_requests, engine.model.vocab_size, limit, args.seed)
+        result = run_workload(engine, prompts, args)
+        report(result, f"max_num_seqs={max_num_seqs} workload={args.workload} dtype={args.dtype}")
+        if args.show_outputs:
+            for request in result["requests"]:
+                print(request.request_id, request.output_token_ids)
+        stats = engine.snapshot()
+        table.append({"max_num_seqs": max_num_seqs, **{k: v for k, v in result.items() if k != "requests"},
+                      "total_blocks": stats["total_blocks"]})
+        del engine
+    if len(table) > 1:
+        print("== sweep")
+        print("max_num_seqs  decode tok/s  TTFT p50 s  preemptions")
+        for row in table:
+            print(f"{row['max_num_seqs']:>12}  {row['decode_tok_s']:>12.1f}  {row['ttft_p50_s']:>10.4f}  {row['preemptions']:>11}")
+    if args.output_json:
+        with open(args.output_json, "w", encoding="utf-8") as handle:
+            json.dump(table, handle, indent=1)
+    if holder is not None:
+        holder.cleanup()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -87,7 +87,13 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+# Launcher calls made so far (each is at least one kernel of this package).
+launch_count = 0
+
+
 def _check(code: int, what: str) -> None:
+    global launch_count
+    launch_count += 1
     if code != 0:
         raise KernelError(f"{what}: CUDA error {code} at launch")
 
