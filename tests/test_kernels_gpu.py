@@ -500,3 +500,76 @@ def test_penalties(k):
         x = torch.where(x > 0, x / rep[r].double(), x * rep[r].double()) - pres[r].double()
         want = torch.where(count > 0, x, want)
         assert (logits[r].cpu().double() - want).abs().max().item() < 1e-5
+
+
+# ----------------------------------------------------------------------------------------------
+# bf16 GEMM on tcgen05 tensor cores
+# ----------------------------------------------------------------------------------------------
+GEMM_SHAPES = [
+    # T, N, K
+    (1, 128, 64), (8, 256, 128), (16, 2048, 1536), (5, 331, 240), (33, 704, 256), (64, 1536, 8960),
+    (100, 136, 480), (300, 640, 200), (2, 97, 48), (7, 1000, 72),
+]
+
+
+@pytest.mark.parametrize("T,N,K", GEMM_SHAPES)
+def test_gemm_bf16_plain_and_bias(k, status, T, N, K):
+    gen = torch.Generator().manual_seed(T * N + K)
+    x = torch.randn(T + 5, K, generator=gen).to(torch.bfloat16).cuda()
+    w = (torch.randn(N, K, generator=gen) / math.sqrt(K)).to(torch.bfloat16).cuda()
+    bias = torch.randn(N, generator=gen).cuda()
+    want = x[:T].double() @ w.double().T
+    out = torch.full((T + 5, N), 9.0, dtype=torch.bfloat16, device="cuda")
+    k.gemm_bf16(x, w, None, out, k.GEMM_OUT_BF16, T, status)
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0
+    scale = want.abs().max().item()
+    assert (out[:T].double().cpu() - want.cpu()).abs().max().item() <= 1e-2 * scale
+    assert torch.all(out[T:] == 9.0)
+    outf = torch.full((T + 5, N), 9.0, dtype=torch.float32, device="cuda")
+    k.gemm_bf16(x, w, bias, outf, k.GEMM_OUT_F32, T, status)
+    want_b = want + bias.double()
+    # float32 accumulation of bf16 products: error ~ sqrt(K) * 2^-24 relative to the terms
+    assert (outf[:T].double().cpu() - want_b.cpu()).abs().max().item() <= 2e-5 * max(scale, 1.0)
+    assert torch.all(outf[T:] == 9.0)
+    assert int(status[0]) == 0
+
+
+@pytest.mark.parametrize("T,N,K,splits", [(8, 1536, 8960, 12), (3, 256, 704, 4), (64, 2048, 1536, 8), (17, 136, 480, 100)])
+def test_gemm_bf16_split_products(k, status, T, N, K, splits):
+    gen = torch.Generator().manual_seed(K)
+    x = torch.randn(T, K, generator=gen).to(torch.bfloat16).cuda()
+    w = (torch.randn(N, K, generator=gen) / math.sqrt(K)).to(torch.bfloat16).cuda()
+    out = torch.zeros(splits, T, N, dtype=torch.float32, device="cuda")
+    used = k.gemm_bf16(x, w, None, out, k.GEMM_OUT_F32, T, status, splits=splits)
+    assert 1 <= used <= splits
+    want = x.double() @ w.double().T
+    got = out[:used].double().sum(0)
+    assert (got.cpu() - want.cpu()).abs().max().item() <= 2e-5 * max(want.abs().max().item(), 1.0)
+    assert torch.all(out[used:] == 0)
+    assert int(status[0]) == 0
+
+
+@pytest.mark.parametrize("T,N,K", [(4, 1536, 1536), (70, 240, 200), (256, 1536, 8960)])
+def test_gemm_bf16_adds_into_residual(k, status, T, N, K):
+    gen = torch.Generator().manual_seed(N)
+    x = torch.randn(T, K, generator=gen).to(torch.bfloat16).cuda()
+    w = (torch.randn(N, K, generator=gen) / math.sqrt(K)).to(torch.bfloat16).cuda()
+    resid = torch.randn(T, N, generator=gen).cuda()
+    want = resid.double() + x.double() @ w.double().T
+    k.gemm_bf16(x, w, None, resid, k.GEMM_ADD_F32, T, status)
+    assert (resid.double().cpu() - want.cpu()).abs().max().item() <= 2e-5 * want.abs().max().item()
+    assert int(status[0]) == 0
+
+
+@pytest.mark.parametrize("T,I,K", [(8, 8960, 1536), (40, 704, 256), (3, 200, 240), (130, 312, 136)])
+def test_gemm_bf16_swiglu(k, status, T, I, K):
+    gen = torch.Generator().manual_seed(I)
+    x = torch.randn(T, K, generator=gen).to(torch.bfloat16).cuda()
+    w = (torch.randn(2 * I, K, generator=gen) * 2 / math.sqrt(K)).to(torch.bfloat16).cuda()
+    out = torch.zeros(T, I, dtype=torch.bfloat16, device="cuda")
+    k.gemm_bf16(x, w, None, out, k.GEMM_SWIGLU, T, status)
+    gu = x.double() @ w.double().T
+    want = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
+    assert (out.double().cpu() - want.cpu()).abs().max().item() <= 1e-2 * want.abs().max().item()
+    assert int(status[0]) == 0

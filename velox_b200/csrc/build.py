@@ -30,7 +30,7 @@ _SRC_DIR = os.path.dirname(os.path.abspath(__file__))
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo"]
 
-CORE_SOURCES = ("core.cu", "sampling.cu")
+CORE_SOURCES = ("core.cu", "sampling.cu", "gemm_bf16.cu")
 ATTENTION_SOURCES = ("attention.cu",)
 HEADERS = ("common.cuh",)
 

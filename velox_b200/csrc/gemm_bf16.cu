@@ -1,0 +1,490 @@
+// bfloat16 projections on the 5th-generation tensor cores: Y[T, N] = X[T, K] * W[N, K]^T.
+//
+// The weight is the M operand of the MMA: a CTA owns 128 rows of W (128 output features) and
+// BN tokens, D^T[128, BN] = W_tile[128, K] * X_tile[BN, K]^T, accumulated in tensor memory.
+// With few tokens (decode) the tensor-core tile is still full, because its 128-row side is made
+// of weight rows; the kernel then streams W once at memory speed, and the key range can be split
+// over several CTAs (split-K) so that a projection with few output tiles still fills the GPU.
+//
+//   warp 0, one lane : TMA producer.  cp.async.bulk.tensor 2-D tiles of W [128 x 64] and
+//                      X [BN x 64] into a ring of 128-byte-swizzled shared-memory stages.
+//   warp 1, one lane : tcgen05.mma issuer (kind::f16, bf16 x bf16 -> f32 in TMEM), four
+//                      K=16 instructions per stage; tcgen05.commit frees the stage and, after
+//                      the last stage, signals the epilogue.  The warp owns the TMEM allocation.
+//   warps 2..5       : epilogue.  tcgen05.ld 32 lanes x 32 columns; a thread holds one output
+//                      feature for 32 tokens, so for a fixed token a warp writes 32 consecutive
+//                      features (one coalesced segment).
+//
+// Epilogue modes:
+//   0  out bf16  [T, ldy] = acc + bias
+//   1  out f32   [T, ldy] = acc + bias          (logits; split-K partials with a split offset)
+//   2  out f32   [T, ldy] += acc                (projection added straight into the float32
+//                                                residual stream; one CTA owns each element)
+//   3  out bf16  [T, ldy] = silu(gate) * up     W rows are [64 gate | 64 up] per CTA (the host
+//                                                passes two tensor maps of the same matrix)
+//
+// Every wait on an mbarrier is bounded: when the bound is hit the thread sets a status bit,
+// stops issuing work, and the CTA still frees its tensor memory and returns.
+// The reference engine leaves these products to cuBLAS (nn.Linear; src/self_attention.py:32-33,
+// src/mlp.py:9-15, src/transformer.py:60 of that project).
+#include <cuda.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "common.cuh"
+
+namespace vx {
+
+constexpr int GB_BM = 128;
+constexpr int GB_BK = 64;
+constexpr int GB_THREADS = 192;
+constexpr uint32_t GB_A_BYTES = GB_BM * GB_BK * 2;
+constexpr unsigned long long GB_WAIT_CYCLES = 4000000000ull;  // about two seconds
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait.  Returns false (and records it) if the barrier did not flip in time.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long start = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - start > GB_WAIT_CYCLES) {
+      atomicOr(status, VX_STATUS_WAIT_TIMEOUT);
+      return false;
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows at a 128-byte pitch,
+// groups of eight rows 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr) {
+  uint64_t desc = 0;
+  desc |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);  // start address, bits 0-13
+  desc |= (uint64_t)0 << 16;                         // leading byte offset (unused here)
+  desc |= (uint64_t)(1024u >> 4) << 32;              // stride byte offset, bits 32-45
+  desc |= (uint64_t)1 << 46;                         // descriptor version of sm_100
+  desc |= (uint64_t)2 << 61;                         // 128-byte swizzle
+  return desc;
+}
+
+// Instruction descriptor of kind::f16: D f32, A and B bf16, both K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t umma_instr_desc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(GB_BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+               ::"r"(bar)
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_load_32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+        "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+        "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ void tmem_load_16(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+struct GemmArgs {
+  const float* bias;  // [N] or null
+  void* out;
+  int* status;
+  long long ldy;         // row pitch of out, in elements
+  long long split_pitch; // elements between the outputs of consecutive splits (mode 1)
+  int T, N, K;
+  int mode;
+  int kb_per_split;      // 64-wide K blocks per split
+};
+
+template <int BN>
+struct GemmShape {
+  static constexpr uint32_t B_BYTES = BN * GB_BK * 2;
+  static constexpr uint32_t STAGE_BYTES = GB_A_BYTES + B_BYTES;
+  static constexpr int STAGES_FIT = (200 * 1024) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
+  static constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+  static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(GB_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
+                 const __grid_constant__ CUtensorMap map_x, GemmArgs g) {
+  using S = GemmShape<BN>;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[S::STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[S::STAGES];
+  __shared__ __align__(8) uint64_t acc_bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int epilogue_failed;
+  __shared__ float swap_buf[64 * 33];
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * (g.mode == 3 ? 64 : GB_BM);
+  const int t0 = blockIdx.y * BN;
+  const int split = blockIdx.z;
+  const int num_kb_total = (g.K + GB_BK - 1) / GB_BK;
+  const int kb_begin = split * g.kb_per_split;
+  const int kb_end = min(num_kb_total, kb_begin + g.kb_per_split);
+  const int num_kb = max(0, kb_end - kb_begin);
+
+  if (threadIdx.x == 0) {
+    epilogue_failed = 0;
+    for (int s = 0; s < S::STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    mbar_init(smem_u32(&acc_bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_slot)), "r"(S::TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_acc = tmem_slot;
+
+  if (warp == 0 && lane == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    for (int i = 0; i < num_kb; ++i) {
+      const int stage = i % S::STAGES;
+      const uint32_t phase = (uint32_t)(i / S::STAGES) & 1u;
+      if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, g.status)) break;
+      const uint32_t full = smem_u32(&full_bar[stage]);
+      const uint32_t a_dst = smem_base + stage * S::STAGE_BYTES;
+      const uint32_t b_dst = a_dst + GB_A_BYTES;
+      mbar_expect_tx(full, S::STAGE_BYTES);
+      const int kx = (kb_begin + i) * GB_BK;
+      if (g.mode == 3) {
+        // 64 gate rows then 64 up rows: two boxes of 64 rows each.
+        tma_load_2d(a_dst, &map_w, kx, n0, full);
+        tma_load_2d(a_dst + GB_A_BYTES / 2, &map_w2, kx, n0, full);
+      } else {
+        tma_load_2d(a_dst, &map_w, kx, n0, full);
+      }
+      tma_load_2d(b_dst, &map_x, kx, t0, full);
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---------------------------------------------------------------- MMA issuer
+    constexpr uint32_t idesc = umma_instr_desc(BN);
+    bool ok = true;
+    for (int i = 0; i < num_kb && ok; ++i) {
+      const int stage = i % S::STAGES;
+      const uint32_t phase = (uint32_t)(i / S::STAGES) & 1u;
+      ok = mbar_wait(smem_u32(&full_bar[stage]), phase, g.status);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t a_addr = smem_base + stage * S::STAGE_BYTES;
+      const uint32_t b_addr = a_addr + GB_A_BYTES;
+#pragma unroll
+      for (int k = 0; k < GB_BK / 16; ++k) {
+        umma_bf16(tmem_acc, umma_smem_desc(a_addr + k * 32), umma_smem_desc(b_addr + k * 32),
+                  idesc, (i > 0 || k > 0) ? 1u : 0u);
+      }
+      umma_commit(smem_u32(&empty_bar[stage]));
+    }
+    // Arrives when every MMA above has finished (or at once if there were none).
+    umma_commit(smem_u32(&acc_bar));
+  } else if (warp >= 2) {
+    // ---------------------------------------------------------------- epilogue
+    const int quarter = warp & 3;  // TMEM lanes 32 * quarter .. + 31 belong to this warp
+    if (!mbar_wait(smem_u32(&acc_bar), 0u, g.status)) epilogue_failed = 1;
+    // All four epilogue warps take the same path below (mode 3 has barriers among them).
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    const bool ready = epilogue_failed == 0;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const int row = quarter * 32 + lane;  // row of the CTA's W tile
+    if (ready && num_kb > 0) {
+      if (g.mode == 3) {
+        // rows 0..63 gate, 64..127 up of the same 64 output features
+        const int n = n0 + (row & 63);
+        __nv_bfloat16* out = (__nv_bfloat16*)g.out;
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          float v[32];
+          if (BN >= 32)
+            tmem_load_32(tmem_acc + ((uint32_t)(quarter * 32) << 16) + c0, v);
+          else
+            tmem_load_16(tmem_acc + ((uint32_t)(quarter * 32) << 16) + c0, v);
+          const int cols = BN >= 32 ? 32 : 16;
+          // up rows hand their values to the gate rows through shared memory
+          if (row >= 64) {
+            for (int j = 0; j < cols; ++j) swap_buf[(row - 64) * 33 + j] = v[j];
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (row < 64 && n < g.N) {
+            for (int j = 0; j < cols; ++j) {
+              const int t = t0 + c0 + j;
+              if (t < g.T) {
+                const float gate = v[j], up = swap_buf[row * 33 + j];
+                out[(size_t)t * g.ldy + n] = __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * up);
+              }
+            }
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+      } else {
+        const int n = n0 + row;
+        const float b = (g.bias != nullptr && n < g.N) ? g.bias[n] : 0.f;
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          float v[32];
+          if (BN >= 32)
+            tmem_load_32(tmem_acc + ((uint32_t)(quarter * 32) << 16) + c0, v);
+          else
+            tmem_load_16(tmem_acc + ((uint32_t)(quarter * 32) << 16) + c0, v);
+          const int cols = BN >= 32 ? 32 : 16;
+          if (n < g.N) {
+            if (g.mode == 0) {
+              __nv_bfloat16* out = (__nv_bfloat16*)g.out;
+              for (int j = 0; j < cols; ++j) {
+                const int t = t0 + c0 + j;
+                if (t < g.T) out[(size_t)t * g.ldy + n] = __float2bfloat16_rn(v[j] + b);
+              }
+            } else if (g.mode == 1) {
+              float* out = (float*)g.out + (size_t)split * g.split_pitch;
+              for (int j = 0; j < cols; ++j) {
+                const int t = t0 + c0 + j;
+                if (t < g.T) out[(size_t)t * g.ldy + n] = v[j] + b;
+              }
+            } else {
+              float* out = (float*)g.out;
+              for (int j = 0; j < cols; ++j) {
+                const int t = t0 + c0 + j;
+                if (t < g.T) out[(size_t)t * g.ldy + n] += v[j] + b;
+              }
+            }
+          }
+        }
+      }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  }
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc),
+                 "r"(S::TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side: tensor maps (cached) and the launcher.
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) ==
+            cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// A [rows, K] row-major bf16 matrix cut into boxes of [box_rows, 64], 128-byte swizzled.
+static bool tensor_map_2d(CUtensorMap* map, const void* base, long long rows, long long K,
+                          int box_rows) {
+  static std::map<std::tuple<const void*, long long, long long, int>, CUtensorMap> cache;
+  static std::mutex lock;
+  const auto key = std::make_tuple(base, rows, K, box_rows);
+  std::lock_guard<std::mutex> guard(lock);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *map = it->second;
+    return true;
+  }
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (encode == nullptr) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)GB_BK, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base),
+                            dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  if (cache.size() > 4096) cache.clear();
+  cache[key] = *map;
+  return true;
+}
+
+template <int BN>
+static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx,
+                       const GemmArgs& g, dim3 grid, cudaStream_t stream) {
+  using S = GemmShape<BN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)S::SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  gemm_bf16_kernel<BN><<<grid, GB_THREADS, S::SMEM_BYTES, stream>>>(mw, mw2, mx, g);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace vx
+
+using namespace vx;
+
+// Token-tile widths the kernel is built for.
+VX_API int vx_gemm_bf16_token_tile(int num_tokens) {
+  if (num_tokens <= 16) return 16;
+  if (num_tokens <= 32) return 32;
+  if (num_tokens <= 64) return 64;
+  if (num_tokens <= 128) return 128;
+  return 256;
+}
+
+// x [T, K] bf16, w [N, K] bf16 (mode 3: w [2 * N, K], gate rows then up rows).
+// Returns 0 on launch, a cudaError_t on failure, or -1 if the sizes are refused
+// (K not a multiple of 8, unaligned pointers, no driver entry point).
+// x_rows is the number of rows the x buffer really has (>= T); rows T.. are read but their
+// results are never written.
+VX_API int vx_gemm_bf16(const void* x, const void* w, const float* bias, void* out, int mode,
+                        int T, int x_rows, int N, int K, long long ldy, int splits,
+                        long long split_pitch, int* status, cudaStream_t stream) {
+  if (T <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K % 8) != 0) return -1;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return -1;
+  if (mode < 0 || mode > 3) return -1;
+  const int bn = vx_gemm_bf16_token_tile(T);
+  const int num_kb = (K + GB_BK - 1) / GB_BK;
+  if (splits < 1) splits = 1;
+  if (splits > num_kb) splits = num_kb;
+  if (mode != 1) splits = 1;
+  GemmArgs g;
+  g.bias = bias;
+  g.out = out;
+  g.status = status;
+  g.ldy = ldy;
+  g.split_pitch = split_pitch;
+  g.T = T;
+  g.N = N;
+  g.K = K;
+  g.mode = mode;
+  g.kb_per_split = (num_kb + splits - 1) / splits;
+  splits = (num_kb + g.kb_per_split - 1) / g.kb_per_split;
+
+  CUtensorMap mw, mw2, mx;
+  if (mode == 3) {
+    if (!tensor_map_2d(&mw, w, N, K, 64)) return -1;
+    if (!tensor_map_2d(&mw2, (const __nv_bfloat16*)w + (size_t)N * K, N, K, 64)) return -1;
+  } else {
+    if (!tensor_map_2d(&mw, w, N, K, GB_BM)) return -1;
+    mw2 = mw;
+  }
+  if (x_rows < T) return -1;
+  if (!tensor_map_2d(&mx, x, x_rows, K, bn)) return -1;
+  const int n_tile = mode == 3 ? 64 : GB_BM;
+  const dim3 grid((N + n_tile - 1) / n_tile, (T + bn - 1) / bn, splits);
+  switch (bn) {
+    case 16: return launch_gemm<16>(mw, mw2, mx, g, grid, stream);
+    case 32: return launch_gemm<32>(mw, mw2, mx, g, grid, stream);
+    case 64: return launch_gemm<64>(mw, mw2, mx, g, grid, stream);
+    case 128: return launch_gemm<128>(mw, mw2, mx, g, grid, stream);
+    default: return launch_gemm<256>(mw, mw2, mx, g, grid, stream);
+  }
+}
+
+// Number of splits the launcher will really use for (K, splits asked).
+VX_API int vx_gemm_bf16_effective_splits(int K, int splits) {
+  const int num_kb = (K + GB_BK - 1) / GB_BK;
+  if (splits < 1) splits = 1;
+  if (splits > num_kb) splits = num_kb;
+  const int per = (num_kb + splits - 1) / splits;
+  return (num_kb + per - 1) / per;
+}

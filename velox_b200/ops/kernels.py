@@ -61,6 +61,10 @@ def core():
         lib.vx_apply_penalties.argtypes = [
             _ptr, _c_int, _c_int, _c_ll, _ptr, _c_ll, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
         ]
+        lib.vx_gemm_bf16.argtypes = [
+            _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _c_ll,
+            _ptr, _ptr,
+        ]
         _core = lib
     return _core
 
@@ -244,6 +248,64 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out
         if bias.numel() != n:
             raise ValueError("bias length does not match the output width")
     _check(core().vx_gemm_f32(_p(a), _p(w), _p(bias), _p(out), num_rows, n, k, _stream()), "gemm_f32")
+
+
+GEMM_OUT_BF16, GEMM_OUT_F32, GEMM_ADD_F32, GEMM_SWIGLU = 0, 1, 2, 3
+
+
+def gemm_bf16_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """The tensor-core kernel moves tiles with TMA: rows must be 16-byte multiples."""
+    return w.shape[1] % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+
+
+def gemm_bf16(
+    x: torch.Tensor,
+    w: torch.Tensor,
+    bias: Optional[torch.Tensor],
+    out: torch.Tensor,
+    mode: int,
+    num_rows: int,
+    status: torch.Tensor,
+    splits: int = 1,
+) -> int:
+    """out = x[:num_rows] @ w.T on tcgen05 tensor cores (see gemm_bf16.cu for the modes).
+
+    Mode GEMM_OUT_F32 with ``splits`` > 1 writes one partial product per split to
+    ``out[split]`` (out is [splits, rows, N]); the caller sums them.  Returns the splits used.
+    """
+    _need(x, torch.bfloat16, "x")
+    _need(w, torch.bfloat16, "w")
+    n, k = w.shape
+    if mode == GEMM_SWIGLU:
+        if n % 2:
+            raise ValueError("a gate/up matrix needs an even number of rows")
+        n //= 2
+    if x.shape[1] != k:
+        raise ValueError(f"gemm shapes do not agree: x {tuple(x.shape)}, w {tuple(w.shape)}")
+    want = torch.bfloat16 if mode in (GEMM_OUT_BF16, GEMM_SWIGLU) else torch.float32
+    _need(out, want, "out")
+    if out.shape[-1] != n:
+        raise ValueError(f"output width {out.shape[-1]} does not match {n}")
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+    split_pitch = 0
+    if mode == GEMM_OUT_F32 and splits > 1:
+        if out.dim() != 3 or out.shape[0] < splits:
+            raise ValueError("split products need an output of [splits, rows, N]")
+        split_pitch = out.stride(0)
+    else:
+        splits = 1
+    code = core().vx_gemm_bf16(_p(x), _p(w), _p(bias), _p(out), mode, num_rows, x.shape[0], n, k,
+                               out.stride(-2), splits, split_pitch, _p(status), _stream())
+    if code == -1:
+        raise KernelError(
+            f"gemm_bf16 refuses x {tuple(x.shape)} w {tuple(w.shape)}: the inner size must be a "
+            "multiple of 8 and both operands 16-byte aligned"
+        )
+    _check(code, "gemm_bf16")
+    kb = -(-k // 64)
+    per = -(-kb // max(1, min(splits, kb)))
+    return -(-kb // per)
 
 
 def cast_bf16_to_f32(src: torch.Tensor, out: torch.Tensor, count: int) -> None:
