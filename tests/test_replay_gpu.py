@@ -253,3 +253,50 @@ def test_trace_run_program(models, tmp_path):
         check(s0, want[2][[19]], dtype, "trace_run step 0")
         expect1 = torch.cat([want[2][20:], want[1][[0, len(b) - 1]]])
         check(s1, expect1, dtype, "trace_run step 1")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_prompt_whole_and_in_large_portions(models, dtype):
+    """600 tokens at once and as 300 + 300: steps above the small-step limit of the projections
+    (library GEMM in bfloat16) and attention tiles far from the start of the sequence."""
+    folder, cfg, page, _, _ = models["tiny_c"]
+    tensors = read_tensors(folder)
+    tokens = random_prompts(cfg["vocab_size"], [600], seed=14)[0]
+    ref = plain_model.forward_logits(tensors, cfg, tokens, dtype=torch.float64)
+    replayer = make_replayer(folder, dtype, max_tokens=640, page=page)
+    check(replay_one(replayer, "whole", tokens, [600]), ref, dtype, "600 tokens whole")
+    check(replay_one(replayer, "halves", tokens, [300, 300]), ref, dtype, "600 tokens as 300 + 300")
+
+
+def test_decode_as_cuda_graph_matches_eager(models):
+    """Single-token steps replayed as a captured graph against the same steps run eagerly:
+    batches of 1 to 3 requests of different lengths, requests leaving and joining."""
+    folder, cfg, page, prompts, want = models["tiny_b"]
+    outs = {}
+    for graphs in (True, False):
+        replayer = make_replayer(folder, "bfloat16", max_tokens=512, page=page, enable_graphs=graphs)
+        seqs = {"a": prompts[4], "b": prompts[3], "c": prompts[2]}
+        rows = {name: [] for name in seqs}
+        done = {name: 0 for name in seqs}
+        heads = {"a": 100, "b": 40, "c": 20}
+        replayer.run_step({"step": 0, "end": [], "entries": [
+            {"id": n, "tokens": seqs[n][: heads[n]], "want": []} for n in seqs]})
+        for n in seqs:
+            done[n] = heads[n]
+        step = 1
+        while any(done[n] < len(seqs[n]) for n in seqs):
+            live = [n for n in seqs if done[n] < len(seqs[n])]
+            rec = {"step": step, "end": [n for n in live if done[n] + 1 == len(seqs[n])],
+                   "entries": [{"id": n, "tokens": [seqs[n][done[n]]], "want": [0]} for n in live]}
+            out = replayer.run_step(rec)
+            for i, n in enumerate(live):
+                rows[n].append(out[i])
+                done[n] += 1
+            step += 1
+        outs[graphs] = {n: np.stack(r) for n, r in rows.items()}
+        if graphs:
+            assert replayer.runner._graphs and not replayer.runner._graphs_broken
+    for n, ref_index in (("a", 4), ("b", 3), ("c", 2)):
+        head = {"a": 100, "b": 40, "c": 20}[n]
+        check(outs[True][n], want[ref_index][head:], "bfloat16", f"graph decode {n}")
+        check(outs[False][n], want[ref_index][head:], "bfloat16", f"eager decode {n}")

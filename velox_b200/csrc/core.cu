@@ -34,32 +34,47 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
 
 // ---------------------------------------------------------------------------------------------
 // Fused residual add + RMSNorm.
-//   v = resid[r] + delta[r]   (delta may be null)
+//   v = resid[r] + delta[r] + sum_s partials[s][r]   (delta and partials may be null; the
+//       partials are the float32 split products of a projection, [num_partials, T, hidden])
 //   if write_resid: resid[r] = v
 //   out[o] = v * (1 / sqrt(mean(v^2) + eps)) * weight
 // `rows` (may be null) selects the rows to normalise: out row o comes from input row rows[o].
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restrict__ delta,
-                                   const float* __restrict__ weight, float eps,
-                                   T* __restrict__ out, const int* __restrict__ rows, int hidden,
-                                   int write_resid) {
+                                   const float* __restrict__ partials, int num_partials,
+                                   long long partial_pitch, const float* __restrict__ weight,
+                                   float eps, T* __restrict__ out, const int* __restrict__ rows,
+                                   int hidden, int write_resid) {
   __shared__ float scratch[32];
   const int o = blockIdx.x;
   const int r = rows ? rows[o] : o;
   float* x = resid + (size_t)r * hidden;
   const T* d = delta ? delta + (size_t)r * hidden : nullptr;
+  const float* p = partials ? partials + (size_t)r * hidden : nullptr;
+
+  // The sum of a row: residual, then the pending delta, then the split products in order.
+  auto value = [&](int i) {
+    float v = x[i];
+    if (d) v += to_float(d[i]);
+    if (p) {
+      float acc = p[i];
+      for (int s = 1; s < num_partials; ++s) acc += p[(size_t)s * partial_pitch + i];
+      v += acc;
+    }
+    return v;
+  };
 
   float ss = 0.f;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    const float v = d ? x[i] + to_float(d[i]) : x[i];
+    const float v = value(i);
     ss += v * v;
   }
   ss = block_sum(ss, scratch);
   const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
   T* y = out + (size_t)o * hidden;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    const float v = d ? x[i] + to_float(d[i]) : x[i];
+    const float v = value(i);
     if (write_resid) x[i] = v;
     y[i] = from_float<T>(v * inv * weight[i]);
   }
@@ -69,11 +84,17 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restric
 // RoPE on q (in place) and on k, fused with the write of k and v into the paged cache.
 //   qkv row layout: [H*D q | G*D k | G*D v]; the first `rot` dims of every head rotate as two
 //   halves (rot = 0: no rotation), cos/sin are float32 tables [max_pos, rot/2].
+//   The row comes from the qkv buffer itself or, when `partials` is given, from the float32
+//   split products of the projection ([num_partials, T, width]) plus `bias`; the rotated q is
+//   written to the qkv buffer either way.
 //   slots[t] is the flat cache index (page * page_size + offset); a negative slot skips the
 //   write (padding rows).  write_cache = 0 rotates q only (a layer that reads another's cache).
 // ---------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void rope_cache_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+__global__ void rope_cache_write_kernel(T* __restrict__ qkv, const float* __restrict__ partials,
+                                        int num_partials, long long partial_pitch,
+                                        const float* __restrict__ bias,
+                                        const int* __restrict__ positions,
                                         const float* __restrict__ cos_t,
                                         const float* __restrict__ sin_t,
                                         const int* __restrict__ slots, T* __restrict__ k_cache,
@@ -89,14 +110,31 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, const int* __restri
   }
   const float* c = cos_t + (size_t)pos * half;
   const float* s = sin_t + (size_t)pos * half;
-  T* row = qkv + (size_t)t * (size_t)(H + 2 * G) * D;
+  const size_t width = (size_t)(H + 2 * G) * D;
+  T* row = qkv + (size_t)t * width;
+  const float* prow = partials ? partials + (size_t)t * width : nullptr;
+  // Element e of the token's q|k|v row: from the buffer, or bias plus the split products.
+  auto load = [&](int e) {
+    if (!prow) return to_float(row[e]);
+    float acc = prow[e];
+    for (int sp = 1; sp < num_partials; ++sp) acc += prow[(size_t)sp * partial_pitch + e];
+    return bias ? acc + bias[e] : acc;
+  };
 
   for (int idx = threadIdx.x; idx < H * half; idx += blockDim.x) {
     const int h = idx / half, i = idx - h * half;
-    T* p = row + h * D + i;
-    const float lo = to_float(p[0]), hi = to_float(p[half]);
-    p[0] = from_float<T>(lo * c[i] - hi * s[i]);
-    p[half] = from_float<T>(lo * s[i] + hi * c[i]);
+    const int e = h * D + i;
+    const float lo = load(e), hi = load(e + half);
+    row[e] = from_float<T>(lo * c[i] - hi * s[i]);
+    row[e + half] = from_float<T>(lo * s[i] + hi * c[i]);
+  }
+  if (prow) {
+    // q dims that do not rotate still have to reach the buffer the attention kernel reads.
+    const int tail_q = D - rot;
+    for (int idx = threadIdx.x; idx < H * tail_q; idx += blockDim.x) {
+      const int h = idx / tail_q, i = idx - h * tail_q;
+      row[h * D + rot + i] = from_float<T>(load(h * D + rot + i));
+    }
   }
   if (!write_cache) return;
   const int slot = slots[t];
@@ -105,22 +143,22 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, const int* __restri
     if (threadIdx.x == 0) atomicOr(status, VX_STATUS_BAD_SLOT);
     return;
   }
-  const T* krow = row + (size_t)H * D;
-  const T* vrow = krow + (size_t)G * D;
+  const int k0 = H * D, v0 = (H + G) * D;
   T* kdst = k_cache + (size_t)slot * G * D;
   T* vdst = v_cache + (size_t)slot * G * D;
   for (int idx = threadIdx.x; idx < G * half; idx += blockDim.x) {
     const int g = idx / half, i = idx - g * half;
-    const float lo = to_float(krow[g * D + i]), hi = to_float(krow[g * D + i + half]);
+    const float lo = load(k0 + g * D + i), hi = load(k0 + g * D + i + half);
     kdst[g * D + i] = from_float<T>(lo * c[i] - hi * s[i]);
     kdst[g * D + i + half] = from_float<T>(lo * s[i] + hi * c[i]);
   }
   const int tail = D - rot;
   for (int idx = threadIdx.x; idx < G * tail; idx += blockDim.x) {
     const int g = idx / tail, i = idx - g * tail;
-    kdst[g * D + rot + i] = krow[g * D + rot + i];
+    kdst[g * D + rot + i] = from_float<T>(load(k0 + g * D + rot + i));
   }
-  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) vdst[idx] = vrow[idx];
+  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x)
+    vdst[idx] = from_float<T>(load(v0 + idx));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -227,22 +265,26 @@ VX_API int vx_embed(const void* table, int dtype, const int* ids, float* resid, 
   return (int)cudaGetLastError();
 }
 
-VX_API int vx_add_rmsnorm(float* resid, const void* delta, const float* weight, float eps,
-                          void* out, int dtype, const int* rows, int num_out_rows, int hidden,
-                          int write_resid, cudaStream_t stream) {
+VX_API int vx_add_rmsnorm(float* resid, const void* delta, const float* partials,
+                          int num_partials, long long partial_pitch, const float* weight,
+                          float eps, void* out, int dtype, const int* rows, int num_out_rows,
+                          int hidden, int write_resid, cudaStream_t stream) {
   if (num_out_rows <= 0) return 0;
   const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
   if (dtype == VX_DTYPE_F32)
     add_rmsnorm_kernel<float><<<num_out_rows, threads, 0, stream>>>(
-        resid, (const float*)delta, weight, eps, (float*)out, rows, hidden, write_resid);
+        resid, (const float*)delta, partials, num_partials, partial_pitch, weight, eps,
+        (float*)out, rows, hidden, write_resid);
   else
     add_rmsnorm_kernel<__nv_bfloat16><<<num_out_rows, threads, 0, stream>>>(
-        resid, (const __nv_bfloat16*)delta, weight, eps, (__nv_bfloat16*)out, rows, hidden,
-        write_resid);
+        resid, (const __nv_bfloat16*)delta, partials, num_partials, partial_pitch, weight, eps,
+        (__nv_bfloat16*)out, rows, hidden, write_resid);
   return (int)cudaGetLastError();
 }
 
-VX_API int vx_rope_cache_write(void* qkv, int dtype, const int* positions, const float* cos_t,
+VX_API int vx_rope_cache_write(void* qkv, int dtype, const float* partials, int num_partials,
+                               long long partial_pitch, const float* bias, const int* positions,
+                               const float* cos_t,
                                const float* sin_t, const int* slots, void* k_cache,
                                void* v_cache, int num_tokens, int H, int G, int D, int rot,
                                int max_pos, long long num_slots, int write_cache, int* status,
@@ -251,12 +293,13 @@ VX_API int vx_rope_cache_write(void* qkv, int dtype, const int* positions, const
   const int threads = 128;
   if (dtype == VX_DTYPE_F32)
     rope_cache_write_kernel<float><<<num_tokens, threads, 0, stream>>>(
-        (float*)qkv, positions, cos_t, sin_t, slots, (float*)k_cache, (float*)v_cache, H, G, D,
-        rot, max_pos, num_slots, write_cache, status);
+        (float*)qkv, partials, num_partials, partial_pitch, bias, positions, cos_t, sin_t, slots,
+        (float*)k_cache, (float*)v_cache, H, G, D, rot, max_pos, num_slots, write_cache, status);
   else
     rope_cache_write_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>(
-        (__nv_bfloat16*)qkv, positions, cos_t, sin_t, slots, (__nv_bfloat16*)k_cache,
-        (__nv_bfloat16*)v_cache, H, G, D, rot, max_pos, num_slots, write_cache, status);
+        (__nv_bfloat16*)qkv, partials, num_partials, partial_pitch, bias, positions, cos_t, sin_t,
+        slots, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, H, G, D, rot, max_pos, num_slots,
+        write_cache, status);
   return (int)cudaGetLastError();
 }
 

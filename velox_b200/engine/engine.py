@@ -108,6 +108,7 @@ class Engine:
             self.cache,
             max_num_seqs=config.max_num_seqs,
             max_num_batched_tokens=config.max_num_batched_tokens,
+            enable_graphs=config.enable_cuda_graphs,
         )
         self.sampler = Sampler(
             self.device, model.vocab_size, config.max_num_seqs, self.max_model_len, seed=config.seed

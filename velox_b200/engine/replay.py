@@ -30,6 +30,7 @@ class TraceReplayer:
         max_live: int = 8,
         device: str = "cuda:0",
         plan_overrides: Optional[dict] = None,
+        enable_graphs: bool = True,
     ) -> None:
         if block_size < 1 or 64 % block_size != 0:
             raise ValueError("block_size must divide 64")
@@ -46,7 +47,7 @@ class TraceReplayer:
         )
         self.runner = ModelRunner(
             self.model, self.cache, max_num_seqs=max_live, max_num_batched_tokens=capacity,
-            plan_overrides=plan_overrides,
+            plan_overrides=plan_overrides, enable_graphs=enable_graphs,
         )
         self.max_live = max_live
         self.max_tokens = max_tokens

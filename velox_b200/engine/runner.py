@@ -64,12 +64,15 @@ class Workspace:
         self.max_logit_rows = max_logit_rows
         self.device = device
         self._buffers: Dict[str, torch.Tensor] = {}
+        # Counts allocations: a captured graph is valid while this stands still.
+        self.generation = 0
 
     def get(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
         buf = self._buffers.get(name)
         if buf is None or buf.dtype != dtype or tuple(buf.shape) != tuple(shape):
-            buf = torch.empty(shape, dtype=dtype, device=self.device)
+            buf = torch.zeros(shape, dtype=dtype, device=self.device)
             self._buffers[name] = buf
+            self.generation += 1
         return buf
 
     def num_bytes(self) -> int:
@@ -130,6 +133,7 @@ class ModelRunner:
         max_num_batched_tokens: int,
         max_logit_rows: Optional[int] = None,
         plan_overrides: Optional[dict] = None,
+        enable_graphs: bool = True,
     ) -> None:
         kernels._require_cuda()
         self.model = model
@@ -169,6 +173,13 @@ class ModelRunner:
         self._device_meta: Optional[torch.Tensor] = None
         self._flip = 0
         self.num_steps = 0
+        self.last_meta_bytes = 0
+        # The float32 path stays eager: it is the checking path, and without the fixed key-range
+        # splits of a captured step its results do not depend on how the work was cut.
+        self.enable_graphs = enable_graphs and self.dtype != torch.float32
+        self._graphs: Dict[int, tuple] = {}
+        self._graphs_broken = False
+        self._meta_generation = 0
 
         cache.on_slot_acquired = self._zero_state
 
@@ -197,6 +208,7 @@ class ModelRunner:
         if self._device_meta is None or self._device_meta.numel() < size:
             capacity = 1 << (max(size, 1 << 14) - 1).bit_length()
             self._device_meta = torch.empty(capacity, dtype=torch.int32, device=self.device)
+            self._meta_generation += 1
         if self._copied[index] is None:
             self._copied[index] = torch.cuda.Event()
         return host, self._device_meta
@@ -208,32 +220,50 @@ class ModelRunner:
         of the chunks and of their ``want`` lists, or None if nothing is wanted."""
         if not chunks:
             return None
+        if self._graph_eligible(chunks):
+            logits = self._graph_step(chunks)
+            if logits is not None:
+                self.num_steps += 1
+                return logits
         ctx, ids, logit_rows, num_logit_rows = self.prepare(chunks)
         logits = self.model.forward(ctx, self.layer_caches, ids, logit_rows, num_logit_rows)
         self.num_steps += 1
         return logits
 
-    def prepare(self, chunks: Sequence[StepChunk]):
-        """Build the step's device-side description: (context, token ids, logit rows, their count)."""
+    def prepare(self, chunks: Sequence[StepChunk], pad_to: Optional[int] = None):
+        """Build the step's device-side description: (context, token ids, logit rows, their count).
+
+        ``pad_to`` (single-token steps only) pads the batch to that many sequences with rows
+        that do nothing: they write to no cache slot, attend through no work item, and their
+        logits are never looked at.  A padded step has the same shape whatever the real batch
+        is, every array lands at the same place of the device buffer, and the logits of all
+        ``pad_to`` rows are computed.
+        """
         P = self.page_size
-        num_seqs = len(chunks)
+        real_seqs = len(chunks)
         q_lens = [len(chunk.tokens) for chunk in chunks]
-        num_tokens = sum(q_lens)
-        if min(q_lens) < 1:
+        if q_lens and min(q_lens) < 1:
             raise ValueError("every chunk of a step needs at least one token")
+        padded = pad_to is not None
+        if padded and (any(n != 1 for n in q_lens) or real_seqs > pad_to):
+            raise ValueError("only steps of single tokens can be padded")
+        num_seqs = pad_to if padded else real_seqs
+        num_tokens = num_seqs if padded else sum(q_lens)
         if num_tokens > self.max_tokens:
             raise ValueError(f"step of {num_tokens} tokens exceeds the runner's {self.max_tokens}")
         if num_seqs > self.max_num_seqs:
             raise ValueError(f"step of {num_seqs} requests exceeds the runner's {self.max_num_seqs}")
 
-        ids = np.empty(num_tokens, np.int32)
-        positions = np.empty(num_tokens, np.int32)
-        q_start = np.empty(num_seqs, np.int32)
+        ids = np.zeros(num_tokens, np.int32)
+        positions = np.zeros(num_tokens, np.int32)
+        q_start = np.arange(num_seqs, dtype=np.int32) if padded else np.empty(num_seqs, np.int32)
+        q_len_arr = np.ones(num_seqs, np.int32)
+        kv_len_arr = np.ones(num_seqs, np.int32)
         kv_lens: List[int] = []
-        seq_slots = np.empty(num_seqs, np.int32)
+        seq_slots = np.full(num_seqs, self.max_num_seqs, np.int32)
         logit_rows: List[int] = []
         num_groups = len(self.cache.groups)
-        slot_maps = [np.empty(num_tokens, np.int32) for _ in range(num_groups)]
+        slot_maps = [np.full(num_tokens, -1, np.int32) for _ in range(num_groups)]
         width = 1
         row = 0
         for s, chunk in enumerate(chunks):
@@ -248,17 +278,24 @@ class ModelRunner:
             pos = np.arange(start, start + n, dtype=np.int32)
             positions[row : row + n] = pos
             q_start[s] = row
+            q_len_arr[s] = n
+            kv_len_arr[s] = start + n
             kv_lens.append(start + n)
-            seq_slots[s] = self.max_num_seqs if seq.slot is None else seq.slot
+            if seq.slot is not None:
+                seq_slots[s] = seq.slot
             for g in range(num_groups):
                 table = np.asarray(seq.tables[g], dtype=np.int32)
                 slot_maps[g][row : row + n] = table[pos // P] * P + pos % P
             width = max(width, seq.num_logical_blocks)
-            for w in chunk.want:
-                if not 0 <= w < n:
-                    raise ValueError(f"{seq.seq_id}: wanted place {w} is outside its {n} tokens")
-                logit_rows.append(row + w)
+            if not padded:
+                for w in chunk.want:
+                    if not 0 <= w < n:
+                        raise ValueError(f"{seq.seq_id}: wanted place {w} is outside its {n} tokens")
+                    logit_rows.append(row + w)
             row += n
+        if padded:
+            width = self.cache.max_blocks_per_seq
+            logit_rows = list(range(num_seqs))
         width = (width + 7) // 8 * 8
         tables = [np.zeros((num_seqs, width), np.int32) for _ in range(num_groups)]
         for s, chunk in enumerate(chunks):
@@ -278,15 +315,22 @@ class ModelRunner:
                 use_f32=self.dtype == torch.float32, target_ctas=2 * self.num_sms,
             )
             options.update(self.plan_overrides)
-            host_plans[(group, signature)] = ap.plan_attention(q_lens, kv_lens, ap.PlanOptions(**options))
+            opt = ap.PlanOptions(**options)
+            if padded:
+                splits = self._padded_splits(num_seqs, opt)
+                plan = ap.plan_attention(q_lens, kv_lens, opt, fixed_splits=splits)
+                plan = ap.pad_plan(plan, num_seqs, splits, opt)
+            else:
+                plan = ap.plan_attention(q_lens, kv_lens, opt)
+            host_plans[(group, signature)] = plan
 
         packer = _Packer()
         where = {
             "ids": packer.add(ids),
             "positions": packer.add(positions),
             "q_start": packer.add(q_start),
-            "q_len": packer.add(np.asarray(q_lens, np.int32)),
-            "kv_len": packer.add(np.asarray(kv_lens, np.int32)),
+            "q_len": packer.add(q_len_arr),
+            "kv_len": packer.add(kv_len_arr),
             "seq_slots": packer.add(seq_slots),
             "logit_rows": packer.add(np.asarray(logit_rows, np.int32)),
         }
@@ -295,7 +339,7 @@ class ModelRunner:
             where[f"tables{g}"] = packer.add(tables[g])
         plan_where = {}
         for key, plan in host_plans.items():
-            entry = {kind: packer.add(items) for kind, items in plan.items.items()}
+            entry = {kind: packer.add(items) for kind, items in sorted(plan.items.items())}
             merge = packer.add(plan.merge_items) if len(plan.merge_items) else None
             plan_where[key] = (entry, merge)
 
@@ -305,6 +349,7 @@ class ModelRunner:
             host_np[offset : offset + flat.size] = flat
         dev[: packer.size].copy_(host[: packer.size], non_blocking=True)
         self._copied[self._flip ^ 1].record()
+        self.last_meta_bytes = packer.size * 4
 
         def view(name: str) -> torch.Tensor:
             offset, shape = where[name]
@@ -343,10 +388,74 @@ class ModelRunner:
             status=self.status,
             workspace=self.workspace,
             plans=plans,
-            q_lens_host=q_lens,
-            kv_lens_host=kv_lens,
+            q_lens_host=[int(n) for n in q_len_arr],
+            kv_lens_host=[int(n) for n in kv_len_arr],
         )
         return ctx, view("ids"), view("logit_rows"), num_logit_rows
+
+    # ------------------------------------------------------------------ decode steps as CUDA graphs
+    def _padded_splits(self, num_seqs: int, opt: "ap.PlanOptions") -> int:
+        """Key-range splits of a padded single-token step: enough work items to fill the GPU
+        at this batch size, the same number for every sequence whatever its length."""
+        tiles = -(-opt.group // 16)
+        per_split = max(1, num_seqs * opt.num_kv_heads * tiles)
+        return max(1, min(32, -(-opt.target_ctas // per_split)))
+
+    def _graph_eligible(self, chunks: Sequence[StepChunk]) -> bool:
+        if not self.enable_graphs or self._graphs_broken:
+            return False
+        if len(chunks) > self.max_num_seqs:
+            return False
+        return all(len(c.tokens) == 1 and tuple(c.want) == (0,) for c in chunks)
+
+    def _bucket(self, num_seqs: int) -> int:
+        size = 1
+        while size < num_seqs:
+            size *= 2
+        return min(size, self.max_num_seqs)
+
+    def _graph_step(self, chunks: Sequence[StepChunk]) -> Optional[torch.Tensor]:
+        """A step of single tokens, padded to a bucket size and replayed as one CUDA graph
+        (the reference captures its decode forward per bucket too, engine/model_runner.py:330-393)."""
+        bucket = self._bucket(len(chunks))
+        entry = self._graphs.get(bucket)
+        if entry is not None and entry[2] != (self.workspace.generation, self._meta_generation):
+            entry = None
+        if entry is None:
+            try:
+                entry = self._capture(bucket)
+            except Exception as exc:  # a part that cannot be captured: run eagerly from now on
+                import logging
+
+                logging.getLogger(__name__).warning("CUDA graph capture failed (%s); running eagerly", exc)
+                self._graphs_broken = True
+                torch.cuda.synchronize(self.device)
+                return None
+            self._graphs[bucket] = entry
+        self.prepare(chunks, pad_to=bucket)
+        if entry[2] != (self.workspace.generation, self._meta_generation):
+            # A buffer grew while the step was laid out: the graph points at old memory.
+            self._graphs.pop(bucket, None)
+            return None
+        graph, logits, _ = entry
+        graph.replay()
+        return logits[: len(chunks)]
+
+    def _capture(self, bucket: int):
+        # Twice eagerly on an all-padding batch: buffers get their final size and addresses.
+        for _ in range(2):
+            ctx, ids, rows, count = self.prepare([], pad_to=bucket)
+            self.model.forward(ctx, self.layer_caches, ids, rows, count)
+        torch.cuda.synchronize(self.device)
+        generation = (self.workspace.generation, self._meta_generation)
+        ctx, ids, rows, count = self.prepare([], pad_to=bucket)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            logits = self.model.forward(ctx, self.layer_caches, ids, rows, count)
+        torch.cuda.synchronize(self.device)
+        if generation != (self.workspace.generation, self._meta_generation):
+            raise RuntimeError("buffers moved during capture")
+        return graph, logits, generation
 
     def _scratch(self, name: str, count: int) -> torch.Tensor:
         ws = self.workspace

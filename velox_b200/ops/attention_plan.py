@@ -122,3 +122,31 @@ def plan_attention(
     if merges:
         plan.merge_items = np.asarray(merges, dtype=np.int32).reshape(-1, ITEM_WIDTH)
     return plan
+
+
+def pad_plan(plan: AttentionPlan, num_seqs: int, splits: int, opt: PlanOptions) -> AttentionPlan:
+    """Give a plan of single-token sequences (made with ``fixed_splits=splits``) the shape it
+    would have with ``num_seqs`` sequences: missing work items are padding (seq = -1).  The
+    result has the same array sizes for every real batch size up to ``num_seqs``."""
+    rows = opt.group
+    if opt.use_f32:
+        kind = KIND_F32
+    else:
+        kind = KIND_BF16_NARROW if rows <= opt.narrow_max_rows else KIND_BF16_WIDE
+    height = TILE_ROWS[kind]
+    tiles = -(-rows // height)
+    want_items = num_seqs * tiles * max(splits, 1)
+    items = plan.items.get(kind, np.zeros((0, ITEM_WIDTH), np.int32))
+    if set(plan.items) - {kind} or len(items) > want_items:
+        raise ValueError("pad_plan: the plan is not one of single-token sequences")
+    padding = np.zeros((want_items - len(items), ITEM_WIDTH), np.int32)
+    padding[:, 0] = -1
+    padding[:, 5] = -1
+    out = AttentionPlan(items={kind: np.concatenate([items, padding], axis=0)})
+    if splits > 1:
+        want_merges = num_seqs * tiles
+        merge_padding = np.zeros((want_merges - len(plan.merge_items), ITEM_WIDTH), np.int32)
+        merge_padding[:, 0] = -1
+        out.merge_items = np.concatenate([plan.merge_items, merge_padding], axis=0)
+        out.partial_rows = want_items * opt.num_kv_heads * height
+    return out

@@ -43,10 +43,11 @@ def core():
         lib = build.load_core()
         lib.vx_embed.argtypes = [_ptr, _c_int, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr, _ptr]
         lib.vx_add_rmsnorm.argtypes = [
-            _ptr, _ptr, _ptr, _c_f, _ptr, _c_int, _ptr, _c_int, _c_int, _c_int, _ptr,
+            _ptr, _ptr, _ptr, _c_int, _c_ll, _ptr, _c_f, _ptr, _c_int, _ptr, _c_int, _c_int, _c_int,
+            _ptr,
         ]
         lib.vx_rope_cache_write.argtypes = [
-            _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
+            _ptr, _c_int, _ptr, _c_int, _c_ll, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
             _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _ptr, _ptr,
         ]
         lib.vx_swiglu.argtypes = [_ptr, _ptr, _c_int, _c_int, _c_int, _ptr]
@@ -148,9 +149,13 @@ def add_rmsnorm(
     num_rows: int,
     rows: Optional[torch.Tensor] = None,
     write_resid: bool = True,
+    partials: Optional[torch.Tensor] = None,
+    num_partials: int = 0,
 ) -> None:
-    """v = resid + delta; resid = v (if write_resid); out = rmsnorm(v) * weight, float32 inside.
+    """v = resid + delta + sum(partials); resid = v (if write_resid); out = rmsnorm(v) * weight.
 
+    ``delta`` is a pending product in the compute dtype, ``partials`` float32
+    [>= num_partials, rows, hidden] the split products of a projection; either may be None.
     With ``rows`` (int32 indices), output row o is computed from input row rows[o].
     """
     _need(resid, torch.float32, "resid")
@@ -165,8 +170,15 @@ def add_rmsnorm(
             raise ValueError("delta width does not match the residual width")
     if rows is not None:
         _need(rows, torch.int32, "rows")
+    pitch = 0
+    if partials is not None:
+        _need(partials, torch.float32, "partials")
+        if partials.dim() != 3 or partials.shape[2] != hidden or partials.shape[0] < num_partials:
+            raise ValueError("partials must be [splits, rows, hidden]")
+        pitch = partials.stride(0)
     _check(
-        core().vx_add_rmsnorm(_p(resid), _p(delta), _p(weight), float(eps), _p(out),
+        core().vx_add_rmsnorm(_p(resid), _p(delta), _p(partials), num_partials, pitch,
+                              _p(weight), float(eps), _p(out),
                               _code(out.dtype), _p(rows), num_rows, hidden,
                               1 if write_resid else 0, _stream()),
         "add_rmsnorm",
@@ -187,10 +199,15 @@ def rope_cache_write(
     head_dim: int,
     rotary_dim: int,
     status: torch.Tensor,
+    partials: Optional[torch.Tensor] = None,
+    num_partials: int = 0,
+    bias: Optional[torch.Tensor] = None,
 ) -> None:
     """Rotate q in place; rotate k and write k, v to the paged cache at ``slots``.
 
     ``k_cache``/``v_cache`` None: rotate q only (a layer that reads another layer's cache).
+    With ``partials`` (float32 [splits, rows, width]) the q|k|v row is the sum of the split
+    products plus ``bias`` instead of the contents of ``qkv``; q still lands in ``qkv``.
     """
     _need(qkv, qkv.dtype, "qkv")
     _need(positions, torch.int32, "positions")
@@ -212,8 +229,17 @@ def rope_cache_write(
             raise ValueError("cos/sin tables do not match the rotary width")
     else:
         max_pos = 0
+    pitch = 0
+    if partials is not None:
+        _need(partials, torch.float32, "partials")
+        if partials.dim() != 3 or partials.shape[2] != qkv.shape[1] or partials.shape[0] < num_partials:
+            raise ValueError("partials must be [splits, rows, qkv width]")
+        pitch = partials.stride(0)
+        if bias is not None:
+            _need(bias, torch.float32, "bias")
     _check(
-        core().vx_rope_cache_write(_p(qkv), _code(qkv.dtype), _p(positions), _p(cos), _p(sin),
+        core().vx_rope_cache_write(_p(qkv), _code(qkv.dtype), _p(partials), num_partials, pitch,
+                                   _p(bias), _p(positions), _p(cos), _p(sin),
                                    _p(slots), _p(k_cache), _p(v_cache), num_tokens, num_heads,
                                    num_kv_heads, head_dim, rotary_dim, max_pos, num_slots,
                                    1 if write else 0, _p(status), _stream()),

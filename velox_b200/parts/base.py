@@ -12,14 +12,17 @@ Interfaces (T = tokens of the step, E = model width, dt = compute dtype):
     normalised rows to ``out`` (dt).  Fusing the add into the norm is why the interface has
     both.
 
-``Mixer.forward(x, ctx, cache) -> dt [T, E]``
+A part's product that is waiting to be added to the residual stream ("delta") is either a
+tensor dt [T, E] or ``ops.linear.Partials`` (float32 split products whose sum is the value).
+
+``Mixer.forward(x, ctx, cache) -> delta``
     x dt [T, E] is the normalised input.  ``cache`` is the mixer's own ``LayerCache`` (its
     pages of the cache group it declared and/or its slot-indexed state) or, for a layer that
     reads another layer's cache, that layer's cache with ``cache.read_only`` set.
     ``Mixer.cache_spec()`` declares what it needs: a ``PagedCacheSpec`` (keys and values in
     pages; a window or all keys), a ``StateSpec`` (fixed size per request), both or neither.
 
-``FeedForward.forward(x, ctx) -> dt [T, E]``
+``FeedForward.forward(x, ctx) -> delta``
 
 ``PositionEncoding``: owned by the mixer that applies it; the rotary kinds offer
     ``rotate_and_store`` (rotate q in place, rotate k and write k, v to the cache in one kernel).

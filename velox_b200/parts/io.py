@@ -5,7 +5,7 @@ from __future__ import annotations
 import torch
 
 from ..ops import kernels
-from ..ops.linear import linear
+from ..ops.linear import linear, use_tensor_core_kernel
 from .base import Part
 from .registry import register_part
 
@@ -39,6 +39,9 @@ class LinearHead(Part):
         logits = ws.get("lm_head.logits", (ws.max_logit_rows, self.vocab_size), torch.float32)
         if self.dtype == torch.float32:
             linear(x, self.weight, None, logits, num_rows)
+        elif use_tensor_core_kernel(x, self.weight, num_rows):
+            # float32 logits straight from the accumulators
+            linear(x, self.weight, None, logits, num_rows, status=ctx.status)
         else:
             low = ws.get("lm_head.logits_lowp", (ws.max_logit_rows, self.vocab_size), self.dtype)
             linear(x, self.weight, None, low, num_rows)

@@ -5,7 +5,7 @@ rounds to the model dtype between the two)."""
 from __future__ import annotations
 
 from ..ops import kernels
-from ..ops.linear import linear
+from ..ops.linear import linear, linear_split, split_scratch, swiglu_linear, use_tensor_core_kernel
 from .base import FeedForward
 from .registry import register_part
 
@@ -22,9 +22,14 @@ class SwiGLU(FeedForward):
     def forward(self, x, ctx):
         T = ctx.num_tokens
         ws = ctx.workspace
+        act = ws.get("swiglu.act", (ws.max_tokens, self.intermediate_size), self.dtype)
+        if use_tensor_core_kernel(x, self.w_gate_up, T) and use_tensor_core_kernel(act, self.w_down, T):
+            # Few tokens: SiLU(gate) * up in the projection's epilogue, then the down projection
+            # as split products that the next norm sums into the residual stream.
+            swiglu_linear(x, self.w_gate_up, act, T, ctx.status)
+            return linear_split(act, self.w_down, split_scratch(ws, self.hidden_size), T, ctx.status)
         gate_up = ws.get("swiglu.gate_up", (ws.max_tokens, 2 * self.intermediate_size), self.dtype)
         linear(x, self.w_gate_up, None, gate_up, T)
-        act = ws.get("swiglu.act", (ws.max_tokens, self.intermediate_size), self.dtype)
         kernels.swiglu(gate_up, act, T)
         out = ws.get("feed_forward.out", (ws.max_tokens, self.hidden_size), self.dtype)
         linear(act, self.w_down, None, out, T)
