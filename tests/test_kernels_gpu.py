@@ -252,7 +252,7 @@ def run_attention_case(k, dtype, H, G, D, P, seqs, window=None, seed=0, min_spli
         k.attention(kind, *args, dev(items), len(items), partial_o, partial_lse, H, G, D, window, 1 / math.sqrt(D))
     if len(plan.merge_items):
         k.attention_merge(out, dev(q_start), dev(plan.merge_items), len(plan.merge_items), partial_o,
-                          partial_lse, H, G, D)
+                          partial_lse, H, G, D, max_rows=64)
     torch.cuda.synchronize()
     return out.view(T, H, D).double().cpu(), want, plan
 

@@ -37,6 +37,9 @@
 namespace vx {
 
 constexpr int D = VX_HEAD_DIM;
+// A key range is cut into at most this many splits (the merge kernel keeps their weights in
+// shared memory).
+constexpr int ATTN_MAX_SPLITS = 64;
 
 struct AttnArgs {
   const void* q;            // [tokens, q_stride]; head h at h * D
@@ -228,6 +231,13 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
 }
 __device__ __forceinline__ void cp_async_wait_all() {
   asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
+}
+__device__ __forceinline__ void cp_async_commit() {
+  asm volatile("cp.async.commit_group;\n" ::: "memory");
+}
+// Wait until at most one committed group (the newest) is still in flight.
+__device__ __forceinline__ void cp_async_wait_but_one() {
+  asm volatile("cp.async.wait_group 1;\n" ::: "memory");
 }
 
 template <int ROWS>
@@ -455,9 +465,10 @@ __global__ void __launch_bounds__(128) attn_bf16_wide_kernel(AttnArgs a) {
 
 __global__ void __launch_bounds__(128) attn_bf16_narrow_kernel(AttnArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  // Two K/V stages: the next tile is in flight while this one is multiplied.
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-  __nv_bfloat16* k_s = q_s + 16 * B_LD;
-  __nv_bfloat16* v_s = k_s + B_BN * B_LD;
+  __nv_bfloat16* kv_s = q_s + 16 * B_LD;  // stage st: K at kv_s + st * 2 * tile, V after it
+  constexpr int TILE = B_BN * B_LD;
 
   const int* item = a.items + (size_t)blockIdx.x * 8;
   const int seq = item[0];
@@ -486,17 +497,27 @@ __global__ void __launch_bounds__(128) attn_bf16_narrow_kernel(AttnArgs a) {
   }
   const int last_pos = ctx + (row_begin + row_count - 1) / a.group;
   const int tile_end = min(kv_end, last_pos + 1);
+  const int n_first = (kv_begin / B_BN) * B_BN;
 
-  for (int n0 = (kv_begin / B_BN) * B_BN; n0 < tile_end; n0 += B_BN) {
+  if (n_first < tile_end) load_kv_tile(a, kv_s, kv_s + TILE, table, n_first, kv_end, kvh);
+  cp_async_commit();
+  int stage = 0;
+  for (int n0 = n_first; n0 < tile_end; n0 += B_BN) {
+    const int next = n0 + B_BN;
+    __nv_bfloat16* k_next = kv_s + (stage ^ 1) * 2 * TILE;
+    if (next < tile_end) load_kv_tile(a, k_next, k_next + TILE, table, next, kv_end, kvh);
+    cp_async_commit();
+    cp_async_wait_but_one();
     __syncthreads();
-    load_kv_tile(a, k_s, v_s, table, n0, kv_end, kvh);
-    cp_async_wait_all();
-    __syncthreads();
+    const __nv_bfloat16* k_s = kv_s + stage * 2 * TILE;
+    const __nv_bfloat16* v_s = k_s + TILE;
     float s[2][4];
     warp_qk<2>(s, q_s, k_s, warp * 16, lane);
     softmax_step<2>(s, o, m, l, pos, n0 + warp * 16, kv_begin, kv_end, a.window, a.scale_log2,
                     lane);
     warp_pv<2>(o, s, v_s, warp * 16, lane);
+    __syncthreads();  // everyone is done with this stage before it is refilled
+    stage ^= 1;
   }
 
   // Merge the four warps (each saw a quarter of every tile) through shared memory.
@@ -554,32 +575,56 @@ __global__ void __launch_bounds__(128) attn_bf16_narrow_kernel(AttnArgs a) {
 // =============================================================================================
 template <typename T>
 __global__ void attn_merge_kernel(AttnArgs a, const int* __restrict__ merge_items) {
+  __shared__ float weight_s[ATTN_MAX_SPLITS];
+  __shared__ float denom_s;
   const int* item = merge_items + (size_t)blockIdx.x * 8;
   const int seq = item[0];
   if (seq < 0) return;
   const int row_begin = item[1], row_count = item[2], first = item[3], splits = item[4],
             stride = item[5];
   const int kvh = blockIdx.y;
-  const int q_start = a.q_start[seq];
-  for (int idx = threadIdx.x; idx < row_count * D; idx += blockDim.x) {
-    const int r = idx / D, d = idx - r * D;
+  const int r = blockIdx.z;  // one block per row of the tile
+  if (r >= row_count) return;
+  const size_t base = (size_t)first + (size_t)kvh * row_count + r;
+
+  // Weights of the splits from their log-sum-exps (warp 0), then every thread sums its dims.
+  if (threadIdx.x < 32) {
     float mt = -CUDART_INF_F;
-    for (int s = 0; s < splits; ++s)
-      mt = fmaxf(mt, a.partial_lse[(size_t)first + (size_t)s * stride + kvh * row_count + r]);
+    for (int s = threadIdx.x; s < splits; s += 32)
+      mt = fmaxf(mt, a.partial_lse[base + (size_t)s * stride]);
+    mt = warp_max(mt);
     const float m_safe = mt == -CUDART_INF_F ? 0.f : mt;
-    float den = 0.f, acc = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const size_t prow = (size_t)first + (size_t)s * stride + kvh * row_count + r;
-      const float lse = a.partial_lse[prow];
+    float den = 0.f;
+    for (int s = threadIdx.x; s < splits; s += 32) {
+      const float lse = a.partial_lse[base + (size_t)s * stride];
       const float w = lse == -CUDART_INF_F ? 0.f : exp2f(lse - m_safe);
+      weight_s[s] = w;
       den += w;
-      acc += w * a.partial_o[prow * D + d];
     }
-    const float val = den > 0.f ? acc / den : 0.f;
-    const int row = row_begin + r;
-    const int tok = row / a.group, hg = row - tok * a.group;
-    ((T*)a.out)[(size_t)(q_start + tok) * a.out_stride + (size_t)(kvh * a.group + hg) * D + d] =
-        from_float<T>(val);
+    den = warp_sum(den);
+    if (threadIdx.x == 0) denom_s = den;
+  }
+  __syncthreads();
+  const float den = denom_s;
+  const int row = row_begin + r;
+  const int tok = row / a.group, hg = row - tok * a.group;
+  T* dst = (T*)a.out + (size_t)(a.q_start[seq] + tok) * a.out_stride +
+           (size_t)(kvh * a.group + hg) * D;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float acc = 0.f;
+    int s = 0;
+    for (; s + 4 <= splits; s += 4) {
+      const float o0 = a.partial_o[(base + (size_t)s * stride) * D + d];
+      const float o1 = a.partial_o[(base + (size_t)(s + 1) * stride) * D + d];
+      const float o2 = a.partial_o[(base + (size_t)(s + 2) * stride) * D + d];
+      const float o3 = a.partial_o[(base + (size_t)(s + 3) * stride) * D + d];
+      acc += weight_s[s] * o0;
+      acc += weight_s[s + 1] * o1;
+      acc += weight_s[s + 2] * o2;
+      acc += weight_s[s + 3] * o3;
+    }
+    for (; s < splits; ++s) acc += weight_s[s] * a.partial_o[(base + (size_t)s * stride) * D + d];
+    dst[d] = from_float<T>(den > 0.f ? acc / den : 0.f);
   }
 }
 
@@ -654,7 +699,7 @@ VX_API int vx_attention(int kind, const void* q, void* out, const void* k_cache,
     }
     attn_bf16_wide_kernel<<<grid, 128, smem, stream>>>(a);
   } else if (kind == 2) {
-    size_t smem = (size_t)(16 + 2 * B_BN) * B_LD * sizeof(__nv_bfloat16);
+    size_t smem = (size_t)(16 + 4 * B_BN) * B_LD * sizeof(__nv_bfloat16);
     const size_t merge = (size_t)(4 * 16 * D + 2 * 4 * 16) * sizeof(float);
     if (merge > smem) smem = merge;
     static bool configured = false;
@@ -671,17 +716,20 @@ VX_API int vx_attention(int kind, const void* q, void* out, const void* k_cache,
   return (int)cudaGetLastError();
 }
 
+// max_rows: the most rows a merge item has (the height of the tiles that were split).
 VX_API int vx_attention_merge(int dtype, void* out, const int* q_start, const int* merge_items,
-                              int num_items, const float* partial_o, const float* partial_lse,
-                              int out_stride, int num_kv_heads, int group, cudaStream_t stream) {
-  if (num_items <= 0) return 0;
+                              int num_items, int max_rows, const float* partial_o,
+                              const float* partial_lse, int out_stride, int num_kv_heads,
+                              int group, cudaStream_t stream) {
+  if (num_items <= 0 || max_rows <= 0) return 0;
   AttnArgs a = make_args(nullptr, out, nullptr, nullptr, nullptr, q_start, nullptr, nullptr,
                          nullptr, const_cast<float*>(partial_o), const_cast<float*>(partial_lse),
                          0, out_stride, 0, num_kv_heads, group, 1, 0, 1.0f);
-  const dim3 grid(num_items, num_kv_heads);
+  const dim3 grid(num_items, num_kv_heads, max_rows);
+  const int threads = D >= 128 ? 128 : (D >= 64 ? 64 : 32);
   if (dtype == VX_DTYPE_F32)
-    attn_merge_kernel<float><<<grid, 128, 0, stream>>>(a, merge_items);
+    attn_merge_kernel<float><<<grid, threads, 0, stream>>>(a, merge_items);
   else
-    attn_merge_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(a, merge_items);
+    attn_merge_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(a, merge_items);
   return (int)cudaGetLastError();
 }

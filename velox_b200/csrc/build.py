@@ -159,6 +159,14 @@ def build_library(name: str, sources: Sequence[str], defines: Sequence[str] = ()
         if proc.returncode != 0:
             raise BuildError(f"link failed:\n{' '.join(link)}\n{proc.stdout}\n{proc.stderr}")
         os.replace(partial, target)
+        # Older builds of the same library (other source hashes) are of no use any more.
+        prefix = f"libvelox_{name}_"
+        for stale in os.listdir(out_dir):
+            if stale.startswith(prefix) and stale.endswith(".so") and stale != os.path.basename(target):
+                try:
+                    os.remove(os.path.join(out_dir, stale))
+                except OSError:
+                    pass
     finally:
         shutil.rmtree(work, ignore_errors=True)
     _say(f"built {os.path.basename(target)} in {time.time() - started:.1f} s")

@@ -40,6 +40,25 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
 //   out[o] = v * (1 / sqrt(mean(v^2) + eps)) * weight
 // `rows` (may be null) selects the rows to normalise: out row o comes from input row rows[o].
 // ---------------------------------------------------------------------------------------------
+// Sum of the split products of one element, four loads in flight at a time.
+__device__ __forceinline__ float sum_partials(const float* __restrict__ p, int num_partials,
+                                              long long pitch) {
+  float acc = 0.f;
+  int s = 0;
+  for (; s + 4 <= num_partials; s += 4) {
+    const float a0 = p[(size_t)s * pitch], a1 = p[(size_t)(s + 1) * pitch];
+    const float a2 = p[(size_t)(s + 2) * pitch], a3 = p[(size_t)(s + 3) * pitch];
+    acc += a0;
+    acc += a1;
+    acc += a2;
+    acc += a3;
+  }
+  for (; s < num_partials; ++s) acc += p[(size_t)s * pitch];
+  return acc;
+}
+
+constexpr int NORM_MAX_PER_THREAD = 8;
+
 template <typename T>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restrict__ delta,
                                    const float* __restrict__ partials, int num_partials,
@@ -57,26 +76,45 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restric
   auto value = [&](int i) {
     float v = x[i];
     if (d) v += to_float(d[i]);
-    if (p) {
-      float acc = p[i];
-      for (int s = 1; s < num_partials; ++s) acc += p[(size_t)s * partial_pitch + i];
-      v += acc;
-    }
+    if (p) v += sum_partials(p + i, num_partials, partial_pitch);
     return v;
   };
 
+  // A row of up to 8 elements per thread is read once and kept in registers.
+  const bool cached = hidden <= NORM_MAX_PER_THREAD * (int)blockDim.x;
+  float vals[NORM_MAX_PER_THREAD];
   float ss = 0.f;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    const float v = value(i);
-    ss += v * v;
+  if (cached) {
+#pragma unroll
+    for (int j = 0; j < NORM_MAX_PER_THREAD; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      vals[j] = i < hidden ? value(i) : 0.f;
+      ss += vals[j] * vals[j];
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      const float v = value(i);
+      ss += v * v;
+    }
   }
   ss = block_sum(ss, scratch);
   const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
   T* y = out + (size_t)o * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    const float v = value(i);
-    if (write_resid) x[i] = v;
-    y[i] = from_float<T>(v * inv * weight[i]);
+  if (cached) {
+#pragma unroll
+    for (int j = 0; j < NORM_MAX_PER_THREAD; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      if (i < hidden) {
+        if (write_resid) x[i] = vals[j];
+        y[i] = from_float<T>(vals[j] * inv * weight[i]);
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      const float v = value(i);
+      if (write_resid) x[i] = v;
+      y[i] = from_float<T>(v * inv * weight[i]);
+    }
   }
 }
 
@@ -89,6 +127,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restric
 //   written to the qkv buffer either way.
 //   slots[t] is the flat cache index (page * page_size + offset); a negative slot skips the
 //   write (padding rows).  write_cache = 0 rotates q only (a layer that reads another's cache).
+//   One block per (token, head of q|k|v).
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void rope_cache_write_kernel(T* __restrict__ qkv, const float* __restrict__ partials,
@@ -102,63 +141,52 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, const float* __rest
                                         int max_pos, long long num_slots, int write_cache,
                                         int* status) {
   const int t = blockIdx.x;
+  const int head = blockIdx.y;  // 0..H-1 q, H..H+G-1 k, H+G.. v
   const int half = rot >> 1;
+  const bool is_q = head < H, is_k = !is_q && head < H + G;
+  if (!is_q && !write_cache) return;
   int pos = positions[t];
   if (rot > 0 && (pos < 0 || pos >= max_pos)) {
-    if (threadIdx.x == 0) atomicOr(status, VX_STATUS_BAD_POSITION);
+    if (threadIdx.x == 0 && head == 0) atomicOr(status, VX_STATUS_BAD_POSITION);
     pos = 0;
   }
   const float* c = cos_t + (size_t)pos * half;
   const float* s = sin_t + (size_t)pos * half;
   const size_t width = (size_t)(H + 2 * G) * D;
-  T* row = qkv + (size_t)t * width;
-  const float* prow = partials ? partials + (size_t)t * width : nullptr;
-  // Element e of the token's q|k|v row: from the buffer, or bias plus the split products.
+  T* row = qkv + (size_t)t * width + (size_t)head * D;
+  const float* prow = partials ? partials + (size_t)t * width + (size_t)head * D : nullptr;
+  const float* brow = bias ? bias + (size_t)head * D : nullptr;
+  // Element e of this head: from the buffer, or bias plus the split products.
   auto load = [&](int e) {
     if (!prow) return to_float(row[e]);
-    float acc = prow[e];
-    for (int sp = 1; sp < num_partials; ++sp) acc += prow[(size_t)sp * partial_pitch + e];
-    return bias ? acc + bias[e] : acc;
+    const float acc = sum_partials(prow + e, num_partials, partial_pitch);
+    return brow ? acc + brow[e] : acc;
   };
 
-  for (int idx = threadIdx.x; idx < H * half; idx += blockDim.x) {
-    const int h = idx / half, i = idx - h * half;
-    const int e = h * D + i;
-    const float lo = load(e), hi = load(e + half);
-    row[e] = from_float<T>(lo * c[i] - hi * s[i]);
-    row[e + half] = from_float<T>(lo * s[i] + hi * c[i]);
-  }
-  if (prow) {
-    // q dims that do not rotate still have to reach the buffer the attention kernel reads.
-    const int tail_q = D - rot;
-    for (int idx = threadIdx.x; idx < H * tail_q; idx += blockDim.x) {
-      const int h = idx / tail_q, i = idx - h * tail_q;
-      row[h * D + rot + i] = from_float<T>(load(h * D + rot + i));
+  T* dst = row;  // q is rotated in place
+  if (!is_q) {
+    const int slot = slots[t];
+    if (slot < 0) return;
+    if ((long long)slot >= num_slots) {
+      if (threadIdx.x == 0) atomicOr(status, VX_STATUS_BAD_SLOT);
+      return;
     }
+    const int g = is_k ? head - H : head - H - G;
+    dst = (is_k ? k_cache : v_cache) + ((size_t)slot * G + g) * D;
   }
-  if (!write_cache) return;
-  const int slot = slots[t];
-  if (slot < 0) return;
-  if ((long long)slot >= num_slots) {
-    if (threadIdx.x == 0) atomicOr(status, VX_STATUS_BAD_SLOT);
-    return;
+  if (is_q || is_k) {
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+      const float lo = load(i), hi = load(i + half);
+      dst[i] = from_float<T>(lo * c[i] - hi * s[i]);
+      dst[i + half] = from_float<T>(lo * s[i] + hi * c[i]);
+    }
+    // Dims that do not rotate: copied for k, and for q when it comes from split products.
+    if (is_k || prow) {
+      for (int i = rot + threadIdx.x; i < D; i += blockDim.x) dst[i] = from_float<T>(load(i));
+    }
+  } else {
+    for (int i = threadIdx.x; i < D; i += blockDim.x) dst[i] = from_float<T>(load(i));
   }
-  const int k0 = H * D, v0 = (H + G) * D;
-  T* kdst = k_cache + (size_t)slot * G * D;
-  T* vdst = v_cache + (size_t)slot * G * D;
-  for (int idx = threadIdx.x; idx < G * half; idx += blockDim.x) {
-    const int g = idx / half, i = idx - g * half;
-    const float lo = load(k0 + g * D + i), hi = load(k0 + g * D + i + half);
-    kdst[g * D + i] = from_float<T>(lo * c[i] - hi * s[i]);
-    kdst[g * D + i + half] = from_float<T>(lo * s[i] + hi * c[i]);
-  }
-  const int tail = D - rot;
-  for (int idx = threadIdx.x; idx < G * tail; idx += blockDim.x) {
-    const int g = idx / tail, i = idx - g * tail;
-    kdst[g * D + rot + i] = from_float<T>(load(k0 + g * D + rot + i));
-  }
-  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x)
-    vdst[idx] = from_float<T>(load(v0 + idx));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -270,7 +298,9 @@ VX_API int vx_add_rmsnorm(float* resid, const void* delta, const float* partials
                           float eps, void* out, int dtype, const int* rows, int num_out_rows,
                           int hidden, int write_resid, cudaStream_t stream) {
   if (num_out_rows <= 0) return 0;
-  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  // About four elements per thread: enough loads in flight per row without starving the sum.
+  int threads = ((hidden + 3) / 4 + 31) / 32 * 32;
+  threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
   if (dtype == VX_DTYPE_F32)
     add_rmsnorm_kernel<float><<<num_out_rows, threads, 0, stream>>>(
         resid, (const float*)delta, partials, num_partials, partial_pitch, weight, eps,
@@ -290,13 +320,14 @@ VX_API int vx_rope_cache_write(void* qkv, int dtype, const float* partials, int 
                                int max_pos, long long num_slots, int write_cache, int* status,
                                cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
-  const int threads = 128;
+  const int threads = D >= 128 ? 64 : 32;
+  const dim3 grid(num_tokens, H + 2 * G);
   if (dtype == VX_DTYPE_F32)
-    rope_cache_write_kernel<float><<<num_tokens, threads, 0, stream>>>(
+    rope_cache_write_kernel<float><<<grid, threads, 0, stream>>>(
         (float*)qkv, partials, num_partials, partial_pitch, bias, positions, cos_t, sin_t, slots,
         (float*)k_cache, (float*)v_cache, H, G, D, rot, max_pos, num_slots, write_cache, status);
   else
-    rope_cache_write_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>(
+    rope_cache_write_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
         (__nv_bfloat16*)qkv, partials, num_partials, partial_pitch, bias, positions, cos_t, sin_t,
         slots, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, H, G, D, rot, max_pos, num_slots,
         write_cache, status);

@@ -52,6 +52,7 @@ class DevicePlan:
     launches: List[Tuple[int, torch.Tensor, int]] = field(default_factory=list)
     merge_items: Optional[torch.Tensor] = None
     num_merges: int = 0
+    merge_rows: int = 16  # the most rows a merge item can have (height of the split tiles)
     partial_o: Optional[torch.Tensor] = None
     partial_lse: Optional[torch.Tensor] = None
 
@@ -367,6 +368,7 @@ class ModelRunner:
                 offset, shape = merge
                 device_plan.merge_items = dev[offset : offset + shape[0] * 8].view(shape[0], 8)
                 device_plan.num_merges = shape[0]
+                device_plan.merge_rows = max(ap.TILE_ROWS[kind] for kind in entry)
             if plan.partial_rows:
                 head_dim = max(self.model.head_dims())
                 device_plan.partial_o = self._scratch("attention.partial_o", plan.partial_rows * head_dim)

@@ -79,7 +79,7 @@ def attention_lib(head_dim: int):
             _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_f, _ptr,
         ]
         lib.vx_attention_merge.argtypes = [
-            _c_int, _ptr, _ptr, _ptr, _c_int, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr,
+            _c_int, _ptr, _ptr, _ptr, _c_int, _c_int, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr,
         ]
         lib.vx_attn_head_dim.restype = _c_int
         if lib.vx_attn_head_dim() != head_dim:
@@ -405,12 +405,14 @@ def attention_merge(
     num_heads: int,
     num_kv_heads: int,
     head_dim: int,
+    max_rows: int = 64,
 ) -> None:
+    """Combine the splits of the merge items; ``max_rows`` bounds the rows of any item."""
     _need(merge_items, torch.int32, "merge_items")
     lib = attention_lib(head_dim)
     _check(
         lib.vx_attention_merge(_code(out.dtype), _p(out), _p(q_start), _p(merge_items), num_items,
-                               _p(partial_o), _p(partial_lse), out.shape[1], num_kv_heads,
+                               max_rows, _p(partial_o), _p(partial_lse), out.shape[1], num_kv_heads,
                                num_heads // num_kv_heads, _stream()),
         "attention_merge",
     )

@@ -90,6 +90,7 @@ class Attention(Mixer):
             kernels.attention_merge(
                 attn, ctx.q_start, plan.merge_items, plan.num_merges, plan.partial_o,
                 plan.partial_lse, self.num_heads, self.num_kv_heads, self.head_dim,
+                max_rows=plan.merge_rows,
             )
 
         if use_tensor_core_kernel(attn, self.w_out, T):
