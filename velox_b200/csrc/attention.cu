@@ -76,6 +76,8 @@ __global__ void __launch_bounds__(128) attn_f32_kernel(AttnArgs a) {
   __shared__ const float* krow_ptr[F_BN];
   __shared__ const float* vrow_ptr[F_BN];
 
+  allow_dependents();
+  grid_dependency_wait();
   const int* item = a.items + (size_t)blockIdx.x * 8;
   const int seq = item[0];
   if (seq < 0) return;
@@ -259,26 +261,32 @@ __device__ __forceinline__ void load_q_tile(const AttnArgs& a, __nv_bfloat16* q_
 }
 
 // Loads keys [n0, n0 + 64) of one KV head into k_s / v_s; rows at or past kv_end are zeroed.
+// Two threads share a key row (128 threads, 64 rows): one block-table lookup per thread.
 __device__ __forceinline__ void load_kv_tile(const AttnArgs& a, __nv_bfloat16* k_s,
                                              __nv_bfloat16* v_s, const int* table, int n0,
                                              int kv_end, int kvh) {
-  constexpr int CH = D / 8;
-  const __nv_bfloat16* kc = (const __nv_bfloat16*)a.k_cache;
-  const __nv_bfloat16* vc = (const __nv_bfloat16*)a.v_cache;
-  for (int idx = threadIdx.x; idx < B_BN * CH; idx += blockDim.x) {
-    const int j = idx / CH, c = idx - j * CH;
-    const int n = n0 + j;
-    __nv_bfloat16* kd = k_s + j * B_LD + c * 8;
-    __nv_bfloat16* vd = v_s + j * B_LD + c * 8;
-    if (n < kv_end) {
-      const int page = table[n / a.page_size];
-      const size_t off =
-          (((size_t)page * a.page_size + (n % a.page_size)) * a.num_kv_heads + kvh) * D + c * 8;
-      cp_async16(kd, kc + off);
-      cp_async16(vd, vc + off);
-    } else {
-      *reinterpret_cast<uint4*>(kd) = make_uint4(0u, 0u, 0u, 0u);
-      *reinterpret_cast<uint4*>(vd) = make_uint4(0u, 0u, 0u, 0u);
+  constexpr int CH = D / 8;       // 16-byte chunks per row
+  constexpr int HALF_CH = CH / 2;  // chunks per thread
+  const int j = threadIdx.x >> 1, side = threadIdx.x & 1;
+  const int n = n0 + j;
+  __nv_bfloat16* kd = k_s + j * B_LD + side * HALF_CH * 8;
+  __nv_bfloat16* vd = v_s + j * B_LD + side * HALF_CH * 8;
+  if (n < kv_end) {
+    const int page = table[n / a.page_size];
+    const size_t off = (((size_t)page * a.page_size + (n % a.page_size)) * a.num_kv_heads + kvh) * D +
+                       side * HALF_CH * 8;
+    const __nv_bfloat16* ksrc = (const __nv_bfloat16*)a.k_cache + off;
+    const __nv_bfloat16* vsrc = (const __nv_bfloat16*)a.v_cache + off;
+#pragma unroll
+    for (int c = 0; c < HALF_CH; ++c) {
+      cp_async16(kd + c * 8, ksrc + c * 8);
+      cp_async16(vd + c * 8, vsrc + c * 8);
+    }
+  } else {
+#pragma unroll
+    for (int c = 0; c < HALF_CH; ++c) {
+      *reinterpret_cast<uint4*>(kd + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+      *reinterpret_cast<uint4*>(vd + c * 8) = make_uint4(0u, 0u, 0u, 0u);
     }
   }
 }
@@ -421,6 +429,8 @@ __global__ void __launch_bounds__(128) attn_bf16_wide_kernel(AttnArgs a) {
   __nv_bfloat16* k_s = q_s + 64 * B_LD;
   __nv_bfloat16* v_s = k_s + B_BN * B_LD;
 
+  allow_dependents();
+  grid_dependency_wait();
   const int* item = a.items + (size_t)blockIdx.x * 8;
   const int seq = item[0];
   if (seq < 0) return;
@@ -470,6 +480,8 @@ __global__ void __launch_bounds__(128) attn_bf16_narrow_kernel(AttnArgs a) {
   __nv_bfloat16* kv_s = q_s + 16 * B_LD;  // stage st: K at kv_s + st * 2 * tile, V after it
   constexpr int TILE = B_BN * B_LD;
 
+  allow_dependents();
+  grid_dependency_wait();
   const int* item = a.items + (size_t)blockIdx.x * 8;
   const int seq = item[0];
   if (seq < 0) return;
@@ -577,6 +589,8 @@ template <typename T>
 __global__ void attn_merge_kernel(AttnArgs a, const int* __restrict__ merge_items) {
   __shared__ float weight_s[ATTN_MAX_SPLITS];
   __shared__ float denom_s;
+  allow_dependents();
+  grid_dependency_wait();
   const int* item = merge_items + (size_t)blockIdx.x * 8;
   const int seq = item[0];
   if (seq < 0) return;
@@ -687,7 +701,7 @@ VX_API int vx_attention(int kind, const void* q, void* out, const void* k_cache,
       if (e != cudaSuccess) return (int)e;
       configured = true;
     }
-    attn_f32_kernel<<<grid, 128, smem, stream>>>(a);
+    launch_pdl(attn_f32_kernel, dim3(grid), dim3(128), smem, stream, a);
   } else if (kind == 1) {
     const size_t smem = (size_t)(64 + 2 * B_BN) * B_LD * sizeof(__nv_bfloat16);
     static bool configured = false;
@@ -697,7 +711,7 @@ VX_API int vx_attention(int kind, const void* q, void* out, const void* k_cache,
       if (e != cudaSuccess) return (int)e;
       configured = true;
     }
-    attn_bf16_wide_kernel<<<grid, 128, smem, stream>>>(a);
+    launch_pdl(attn_bf16_wide_kernel, dim3(grid), dim3(128), smem, stream, a);
   } else if (kind == 2) {
     size_t smem = (size_t)(16 + 4 * B_BN) * B_LD * sizeof(__nv_bfloat16);
     const size_t merge = (size_t)(4 * 16 * D + 2 * 4 * 16) * sizeof(float);
@@ -709,7 +723,7 @@ VX_API int vx_attention(int kind, const void* q, void* out, const void* k_cache,
       if (e != cudaSuccess) return (int)e;
       configured = true;
     }
-    attn_bf16_narrow_kernel<<<grid, 128, smem, stream>>>(a);
+    launch_pdl(attn_bf16_narrow_kernel, dim3(grid), dim3(128), smem, stream, a);
   } else {
     return (int)cudaErrorInvalidValue;
   }
@@ -728,8 +742,8 @@ VX_API int vx_attention_merge(int dtype, void* out, const int* q_start, const in
   const dim3 grid(num_items, num_kv_heads, max_rows);
   const int threads = D >= 128 ? 128 : (D >= 64 ? 64 : 32);
   if (dtype == VX_DTYPE_F32)
-    attn_merge_kernel<float><<<grid, threads, 0, stream>>>(a, merge_items);
+    launch_pdl(attn_merge_kernel<float>, dim3(grid), dim3(threads), 0, stream, a, merge_items);
   else
-    attn_merge_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(a, merge_items);
+    launch_pdl(attn_merge_kernel<__nv_bfloat16>, dim3(grid), dim3(threads), 0, stream, a, merge_items);
   return (int)cudaGetLastError();
 }

@@ -72,4 +72,36 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 32 floa
   return total;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Programmatic dependent launch.  Every kernel of a step is launched with the attribute that
+// lets it start while its predecessor in the stream is still running; it may then do work that
+// does not depend on the predecessor (set up barriers, prefetch weights) and must call
+// grid_dependency_wait() before it reads or writes anything another kernel of the stream
+// touches.  The wait returns once the predecessor has completed and its writes are visible.
+// allow_dependents() tells the scheduler that the successor may be started.
+// Launched without the attribute, both calls do nothing.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void allow_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
+}
+
 }  // namespace vx

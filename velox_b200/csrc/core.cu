@@ -20,6 +20,8 @@ namespace vx {
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                              float* __restrict__ resid, int hidden, int vocab, int* status) {
+  allow_dependents();
+  grid_dependency_wait();
   const int t = blockIdx.x;
   int id = ids[t];
   const bool bad = id < 0 || id >= vocab;
@@ -66,6 +68,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restric
                                    float eps, T* __restrict__ out, const int* __restrict__ rows,
                                    int hidden, int write_resid) {
   __shared__ float scratch[32];
+  allow_dependents();
+  grid_dependency_wait();
   const int o = blockIdx.x;
   const int r = rows ? rows[o] : o;
   float* x = resid + (size_t)r * hidden;
@@ -140,6 +144,8 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, const float* __rest
                                         T* __restrict__ v_cache, int H, int G, int D, int rot,
                                         int max_pos, long long num_slots, int write_cache,
                                         int* status) {
+  allow_dependents();
+  grid_dependency_wait();
   const int t = blockIdx.x;
   const int head = blockIdx.y;  // 0..H-1 q, H..H+G-1 k, H+G.. v
   const int half = rot >> 1;
@@ -195,6 +201,8 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, const float* __rest
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long total,
                               int inter) {
+  allow_dependents();
+  grid_dependency_wait();
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += stride) {
@@ -217,6 +225,8 @@ constexpr int GF_BM = 64, GF_BN = 64, GF_BK = 16;
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ W,
                 const float* __restrict__ bias, float* __restrict__ C, int M, int N, int K) {
+  allow_dependents();
+  grid_dependency_wait();
   __shared__ float As[GF_BK][GF_BM + 4];
   __shared__ float Ws[GF_BK][GF_BN + 4];
   const int tid = threadIdx.x;
@@ -267,6 +277,8 @@ gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ W,
 // bf16 -> float32 copy of selected rows (logits of the bfloat16 path are returned as float32).
 __global__ void cast_bf16_to_f32_kernel(const __nv_bfloat16* __restrict__ in,
                                         float* __restrict__ out, long long total) {
+  allow_dependents();
+  grid_dependency_wait();
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += stride)
@@ -285,10 +297,10 @@ VX_API int vx_embed(const void* table, int dtype, const int* ids, float* resid, 
   if (num_tokens <= 0) return 0;
   const int threads = hidden >= 1024 ? 256 : 128;
   if (dtype == VX_DTYPE_F32)
-    embed_kernel<float><<<num_tokens, threads, 0, stream>>>((const float*)table, ids, resid,
+    launch_pdl(embed_kernel<float>, dim3(num_tokens), dim3(threads), 0, stream, (const float*)table, ids, resid,
                                                             hidden, vocab, status);
   else
-    embed_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>(
+    launch_pdl(embed_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(threads), 0, stream, 
         (const __nv_bfloat16*)table, ids, resid, hidden, vocab, status);
   return (int)cudaGetLastError();
 }
@@ -302,11 +314,11 @@ VX_API int vx_add_rmsnorm(float* resid, const void* delta, const float* partials
   int threads = ((hidden + 3) / 4 + 31) / 32 * 32;
   threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
   if (dtype == VX_DTYPE_F32)
-    add_rmsnorm_kernel<float><<<num_out_rows, threads, 0, stream>>>(
+    launch_pdl(add_rmsnorm_kernel<float>, dim3(num_out_rows), dim3(threads), 0, stream, 
         resid, (const float*)delta, partials, num_partials, partial_pitch, weight, eps,
         (float*)out, rows, hidden, write_resid);
   else
-    add_rmsnorm_kernel<__nv_bfloat16><<<num_out_rows, threads, 0, stream>>>(
+    launch_pdl(add_rmsnorm_kernel<__nv_bfloat16>, dim3(num_out_rows), dim3(threads), 0, stream, 
         resid, (const __nv_bfloat16*)delta, partials, num_partials, partial_pitch, weight, eps,
         (__nv_bfloat16*)out, rows, hidden, write_resid);
   return (int)cudaGetLastError();
@@ -323,11 +335,11 @@ VX_API int vx_rope_cache_write(void* qkv, int dtype, const float* partials, int 
   const int threads = D >= 128 ? 64 : 32;
   const dim3 grid(num_tokens, H + 2 * G);
   if (dtype == VX_DTYPE_F32)
-    rope_cache_write_kernel<float><<<grid, threads, 0, stream>>>(
+    launch_pdl(rope_cache_write_kernel<float>, dim3(grid), dim3(threads), 0, stream, 
         (float*)qkv, partials, num_partials, partial_pitch, bias, positions, cos_t, sin_t, slots,
         (float*)k_cache, (float*)v_cache, H, G, D, rot, max_pos, num_slots, write_cache, status);
   else
-    rope_cache_write_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
+    launch_pdl(rope_cache_write_kernel<__nv_bfloat16>, dim3(grid), dim3(threads), 0, stream, 
         (__nv_bfloat16*)qkv, partials, num_partials, partial_pitch, bias, positions, cos_t, sin_t,
         slots, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, H, G, D, rot, max_pos, num_slots,
         write_cache, status);
@@ -342,10 +354,10 @@ VX_API int vx_swiglu(const void* gate_up, void* out, int dtype, int num_tokens, 
   long long blocks = (total + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (dtype == VX_DTYPE_F32)
-    swiglu_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out,
+    launch_pdl(swiglu_kernel<float>, dim3((int)blocks), dim3(threads), 0, stream, (const float*)gate_up, (float*)out,
                                                               total, inter);
   else
-    swiglu_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, stream>>>(
+    launch_pdl(swiglu_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(threads), 0, stream, 
         (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, total, inter);
   return (int)cudaGetLastError();
 }
@@ -354,7 +366,7 @@ VX_API int vx_gemm_f32(const float* A, const float* W, const float* bias, float*
                        int K, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   dim3 grid((N + GF_BN - 1) / GF_BN, (M + GF_BM - 1) / GF_BM);
-  gemm_f32_kernel<<<grid, 256, 0, stream>>>(A, W, bias, C, M, N, K);
+  launch_pdl(gemm_f32_kernel, dim3(grid), dim3(256), 0, stream, A, W, bias, C, M, N, K);
   return (int)cudaGetLastError();
 }
 
@@ -362,6 +374,6 @@ VX_API int vx_cast_bf16_to_f32(const void* in, float* out, long long total, cuda
   if (total <= 0) return 0;
   long long blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  cast_bf16_to_f32_kernel<<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)in, out, total);
+  launch_pdl(cast_bf16_to_f32_kernel, dim3((int)blocks), dim3(256), 0, stream, (const __nv_bfloat16*)in, out, total);
   return (int)cudaGetLastError();
 }

@@ -195,6 +195,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   __shared__ int epilogue_failed;
   __shared__ float swap_buf[64 * 33];
 
+  allow_dependents();
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * (g.mode == 3 ? 64 : GB_BM);
@@ -228,15 +229,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
 
   if (warp == 0 && lane == 0) {
     // ---------------------------------------------------------------- TMA producer
-    for (int i = 0; i < num_kb; ++i) {
+    // The weight does not depend on the kernel before this one: its tiles for the first
+    // round of stages are requested at once, the activations after the dependency wait.
+    const int first_round = min(num_kb, S::STAGES);
+    auto load_w = [&](int i) {
       const int stage = i % S::STAGES;
-      const uint32_t phase = (uint32_t)(i / S::STAGES) & 1u;
-      if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, g.status)) break;
       const uint32_t full = smem_u32(&full_bar[stage]);
       const uint32_t a_dst = smem_base + stage * S::STAGE_BYTES;
-      const uint32_t b_dst = a_dst + GB_A_BYTES;
-      mbar_expect_tx(full, S::STAGE_BYTES);
       const int kx = (kb_begin + i) * GB_BK;
+      mbar_expect_tx(full, S::STAGE_BYTES);
       if (g.mode == 3) {
         // 64 gate rows then 64 up rows: two boxes of 64 rows each.
         tma_load_2d(a_dst, &map_w, kx, n0, full);
@@ -244,7 +245,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       } else {
         tma_load_2d(a_dst, &map_w, kx, n0, full);
       }
-      tma_load_2d(b_dst, &map_x, kx, t0, full);
+    };
+    auto load_x = [&](int i) {
+      const int stage = i % S::STAGES;
+      const uint32_t b_dst = smem_base + stage * S::STAGE_BYTES + GB_A_BYTES;
+      tma_load_2d(b_dst, &map_x, (kb_begin + i) * GB_BK, t0, smem_u32(&full_bar[stage]));
+    };
+    for (int i = 0; i < first_round; ++i) load_w(i);
+    grid_dependency_wait();
+    for (int i = 0; i < first_round; ++i) load_x(i);
+    for (int i = first_round; i < num_kb; ++i) {
+      const int stage = i % S::STAGES;
+      const uint32_t phase = (uint32_t)(i / S::STAGES) & 1u;
+      if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, g.status)) break;
+      load_w(i);
+      load_x(i);
     }
   } else if (warp == 1 && lane == 0) {
     // ---------------------------------------------------------------- MMA issuer
@@ -269,6 +284,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     umma_commit(smem_u32(&acc_bar));
   } else if (warp >= 2) {
     // ---------------------------------------------------------------- epilogue
+    grid_dependency_wait();
     const int quarter = warp & 3;  // TMEM lanes 32 * quarter .. + 31 belong to this warp
     if (!mbar_wait(smem_u32(&acc_bar), 0u, g.status)) epilogue_failed = 1;
     // All four epilogue warps take the same path below (mode 3 has barriers among them).
@@ -412,7 +428,7 @@ static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mw2, const CUte
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  gemm_bf16_kernel<BN><<<grid, GB_THREADS, S::SMEM_BYTES, stream>>>(mw, mw2, mx, g);
+  launch_pdl(gemm_bf16_kernel<BN>, dim3(grid), dim3(GB_THREADS), S::SMEM_BYTES, stream, mw, mw2, mx, g);
   return (int)cudaGetLastError();
 }
 

@@ -109,6 +109,8 @@ sample_kernel(const float* __restrict__ logits, int vocab, long long row_stride,
               int* __restrict__ out, int* __restrict__ history, long long history_stride,
               const int* __restrict__ history_slots, const int* __restrict__ history_lengths) {
   __shared__ Best scratch[32];
+  allow_dependents();
+  grid_dependency_wait();
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * row_stride;
   const float temp = temperature ? temperature[r] : 0.f;
@@ -170,6 +172,8 @@ filter_threshold_kernel(const float* __restrict__ logits, int vocab, long long r
                         const float* __restrict__ temperature, const int* __restrict__ top_k,
                         const float* __restrict__ top_p, float* __restrict__ threshold) {
   __shared__ float scratch[32];
+  allow_dependents();
+  grid_dependency_wait();
   const int r = blockIdx.x;
   const float temp = temperature[r];
   const int k = top_k[r];
@@ -234,6 +238,8 @@ __global__ void penalty_count_kernel(const int* __restrict__ history, long long 
                                      const int* __restrict__ slots,
                                      const int* __restrict__ lengths, int* __restrict__ counts,
                                      int vocab) {
+  allow_dependents();
+  grid_dependency_wait();
   const int r = blockIdx.x;
   int* c = counts + (size_t)r * vocab;
   for (int i = threadIdx.x; i < vocab; i += blockDim.x) c[i] = 0;
@@ -251,6 +257,8 @@ __global__ void penalty_apply_kernel(float* __restrict__ logits, long long row_s
                                      const float* __restrict__ repetition,
                                      const float* __restrict__ presence,
                                      const float* __restrict__ frequency) {
+  allow_dependents();
+  grid_dependency_wait();
   const int r = blockIdx.x;
   float* row = logits + (size_t)r * row_stride;
   const int* c = counts + (size_t)r * vocab;
@@ -275,7 +283,7 @@ VX_API int vx_sample(const float* logits, int num_rows, int vocab, long long row
                      const int* history_lengths, cudaStream_t stream) {
   if (num_rows <= 0) return 0;
   const int threads = vocab >= 4096 ? 1024 : 256;
-  sample_kernel<<<num_rows, threads, 0, stream>>>(logits, vocab, row_stride, temperature, seeds,
+  launch_pdl(sample_kernel, dim3(num_rows), dim3(threads), 0, stream, logits, vocab, row_stride, temperature, seeds,
                                                   draw_index, threshold, out, history,
                                                   history_stride, history_slots, history_lengths);
   return (int)cudaGetLastError();
@@ -286,7 +294,7 @@ VX_API int vx_filter_threshold(const float* logits, int num_rows, int vocab, lon
                                float* threshold, cudaStream_t stream) {
   if (num_rows <= 0) return 0;
   const int threads = vocab >= 4096 ? 1024 : 256;
-  filter_threshold_kernel<<<num_rows, threads, 0, stream>>>(logits, vocab, row_stride,
+  launch_pdl(filter_threshold_kernel, dim3(num_rows), dim3(threads), 0, stream, logits, vocab, row_stride,
                                                             temperature, top_k, top_p, threshold);
   return (int)cudaGetLastError();
 }
@@ -297,9 +305,9 @@ VX_API int vx_apply_penalties(float* logits, int num_rows, int vocab, long long 
                               const float* presence, const float* frequency,
                               cudaStream_t stream) {
   if (num_rows <= 0) return 0;
-  penalty_count_kernel<<<num_rows, 256, 0, stream>>>(history, history_stride, slots, lengths,
+  launch_pdl(penalty_count_kernel, dim3(num_rows), dim3(256), 0, stream, history, history_stride, slots, lengths,
                                                      counts, vocab);
-  penalty_apply_kernel<<<num_rows, 256, 0, stream>>>(logits, row_stride, counts, vocab,
+  launch_pdl(penalty_apply_kernel, dim3(num_rows), dim3(256), 0, stream, logits, row_stride, counts, vocab,
                                                      repetition, presence, frequency);
   return (int)cudaGetLastError();
 }
