@@ -199,6 +199,8 @@ __global__ void __launch_bounds__(128) attn_f32_kernel(AttnArgs a) {
 //   WIDE  : 64 rows per item; each of 4 warps owns 16 rows and sees all 64 keys of a tile.
 //   NARROW: 16 rows per item; each of 4 warps owns 16 keys of every 64-key tile and the warps
 //           merge at the end (decode tokens and short portions; this is what gets split).
+// K/V tiles arrive by cp.async into a ring of shared-memory stages, gathered row by row
+// through the block table.
 // =============================================================================================
 constexpr int B_BN = 64;
 constexpr int B_LD = D + 8;  // row pitch in elements: 16-byte aligned, conflict-free ldmatrix
@@ -260,10 +262,15 @@ __device__ __forceinline__ void load_q_tile(const AttnArgs& a, __nv_bfloat16* q_
   }
 }
 
+// Block-table entries of an item's key range are copied to shared memory once, so that the
+// loads of a tile do not wait for a table lookup first.
+constexpr int TABLE_CAP = 1024;
+
 // Loads keys [n0, n0 + 64) of one KV head into k_s / v_s; rows at or past kv_end are zeroed.
-// Two threads share a key row (128 threads, 64 rows): one block-table lookup per thread.
+// Two threads share a key row (128 threads, 64 rows).
 __device__ __forceinline__ void load_kv_tile(const AttnArgs& a, __nv_bfloat16* k_s,
-                                             __nv_bfloat16* v_s, const int* table, int n0,
+                                             __nv_bfloat16* v_s, const int* table,
+                                             const int* table_s, int first_block, int n0,
                                              int kv_end, int kvh) {
   constexpr int CH = D / 8;       // 16-byte chunks per row
   constexpr int HALF_CH = CH / 2;  // chunks per thread
@@ -272,8 +279,10 @@ __device__ __forceinline__ void load_kv_tile(const AttnArgs& a, __nv_bfloat16* k
   __nv_bfloat16* kd = k_s + j * B_LD + side * HALF_CH * 8;
   __nv_bfloat16* vd = v_s + j * B_LD + side * HALF_CH * 8;
   if (n < kv_end) {
-    const int page = table[n / a.page_size];
-    const size_t off = (((size_t)page * a.page_size + (n % a.page_size)) * a.num_kv_heads + kvh) * D +
+    const int block = n / a.page_size;
+    const int local = block - first_block;
+    const int page = local < TABLE_CAP ? table_s[local] : table[block];
+    const size_t off = (((size_t)page * a.page_size + (n - block * a.page_size)) * a.num_kv_heads + kvh) * D +
                        side * HALF_CH * 8;
     const __nv_bfloat16* ksrc = (const __nv_bfloat16*)a.k_cache + off;
     const __nv_bfloat16* vsrc = (const __nv_bfloat16*)a.v_cache + off;
@@ -423,11 +432,23 @@ __device__ __forceinline__ void store_rows(const AttnArgs& a, const float (&o)[D
   }
 }
 
-__global__ void __launch_bounds__(128) attn_bf16_wide_kernel(AttnArgs a) {
+template <int N>
+__device__ __forceinline__ void cp_async_wait_group() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+// NARROW = false: 64 rows, every warp owns 16 rows and all 64 keys of a tile.
+// NARROW = true : 16 rows, every warp owns 16 keys of each tile; the warps merge at the end.
+// STAGES K/V tiles are in shared memory at a time: STAGES - 1 in flight while one is multiplied.
+template <bool NARROW, int STAGES>
+__global__ void __launch_bounds__(128) attn_bf16_kernel(AttnArgs a) {
+  constexpr int ROWS = NARROW ? 16 : 64;
+  constexpr int NT = NARROW ? 2 : 8;
+  constexpr int TILE = B_BN * B_LD;
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ int table_s[TABLE_CAP];
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-  __nv_bfloat16* k_s = q_s + 64 * B_LD;
-  __nv_bfloat16* v_s = k_s + B_BN * B_LD;
+  __nv_bfloat16* kv_s = q_s + ROWS * B_LD;  // stage st: K at kv_s + st * 2 * TILE, V after it
 
   allow_dependents();
   grid_dependency_wait();
@@ -442,58 +463,17 @@ __global__ void __launch_bounds__(128) attn_bf16_wide_kernel(AttnArgs a) {
   const int ctx = kv_len - q_len;
   const int* table = a.block_tables + (size_t)seq * a.table_stride;
 
-  load_q_tile<64>(a, q_s, q_start, row_begin, row_count, kvh);
-
-  float o[D / 8][4];
-#pragma unroll
-  for (int jd = 0; jd < D / 8; ++jd)
-#pragma unroll
-    for (int e = 0; e < 4; ++e) o[jd][e] = 0.f;
-  float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
-  int pos[2];
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const int r = warp * 16 + (lane >> 2) + 8 * h;
-    pos[h] = r < row_count ? ctx + (row_begin + r) / a.group : -1;
-  }
   // Keys past the last row's position are hidden from every row of the item.
   const int last_pos = ctx + (row_begin + row_count - 1) / a.group;
   const int tile_end = min(kv_end, last_pos + 1);
-
-  for (int n0 = (kv_begin / B_BN) * B_BN; n0 < tile_end; n0 += B_BN) {
-    __syncthreads();
-    load_kv_tile(a, k_s, v_s, table, n0, kv_end, kvh);
-    cp_async_wait_all();
-    __syncthreads();
-    float s[8][4];
-    warp_qk<8>(s, q_s + warp * 16 * B_LD, k_s, 0, lane);
-    softmax_step<8>(s, o, m, l, pos, n0, kv_begin, kv_end, a.window, a.scale_log2, lane);
-    warp_pv<8>(o, s, v_s, 0, lane);
+  const int n_first = (kv_begin / B_BN) * B_BN;
+  const int first_block = n_first / a.page_size;
+  if (n_first < tile_end) {
+    const int blocks = min(TABLE_CAP, (tile_end - 1) / a.page_size - first_block + 1);
+    for (int i = threadIdx.x; i < blocks; i += blockDim.x) table_s[i] = table[first_block + i];
   }
-  store_rows(a, o, m, l, warp * 16, row_begin, row_count, q_start, kvh, partial_base, lane);
-}
-
-__global__ void __launch_bounds__(128) attn_bf16_narrow_kernel(AttnArgs a) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  // Two K/V stages: the next tile is in flight while this one is multiplied.
-  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-  __nv_bfloat16* kv_s = q_s + 16 * B_LD;  // stage st: K at kv_s + st * 2 * tile, V after it
-  constexpr int TILE = B_BN * B_LD;
-
-  allow_dependents();
-  grid_dependency_wait();
-  const int* item = a.items + (size_t)blockIdx.x * 8;
-  const int seq = item[0];
-  if (seq < 0) return;
-  const int row_begin = item[1], row_count = item[2];
-  const int kv_begin = item[3], kv_end = item[4], partial_base = item[5];
-  const int kvh = blockIdx.y;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int q_start = a.q_start[seq], q_len = a.q_len[seq], kv_len = a.kv_len[seq];
-  const int ctx = kv_len - q_len;
-  const int* table = a.block_tables + (size_t)seq * a.table_stride;
-
-  load_q_tile<16>(a, q_s, q_start, row_begin, row_count, kvh);
+  load_q_tile<ROWS>(a, q_s, q_start, row_begin, row_count, kvh);
+  __syncthreads();
 
   float o[D / 8][4];
 #pragma unroll
@@ -501,38 +481,50 @@ __global__ void __launch_bounds__(128) attn_bf16_narrow_kernel(AttnArgs a) {
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[jd][e] = 0.f;
   float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
+  const int row0 = NARROW ? 0 : warp * 16;   // first row this warp works on
+  const int key0 = NARROW ? warp * 16 : 0;   // first key of a tile this warp works on
   int pos[2];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
-    const int r = (lane >> 2) + 8 * h;
+    const int r = row0 + (lane >> 2) + 8 * h;
     pos[h] = r < row_count ? ctx + (row_begin + r) / a.group : -1;
   }
-  const int last_pos = ctx + (row_begin + row_count - 1) / a.group;
-  const int tile_end = min(kv_end, last_pos + 1);
-  const int n_first = (kv_begin / B_BN) * B_BN;
 
-  if (n_first < tile_end) load_kv_tile(a, kv_s, kv_s + TILE, table, n_first, kv_end, kvh);
-  cp_async_commit();
-  int stage = 0;
-  for (int n0 = n_first; n0 < tile_end; n0 += B_BN) {
-    const int next = n0 + B_BN;
-    __nv_bfloat16* k_next = kv_s + (stage ^ 1) * 2 * TILE;
-    if (next < tile_end) load_kv_tile(a, k_next, k_next + TILE, table, next, kv_end, kvh);
+#pragma unroll
+  for (int st = 0; st < STAGES - 1; ++st) {
+    const int n = n_first + st * B_BN;
+    if (n < tile_end)
+      load_kv_tile(a, kv_s + st * 2 * TILE, kv_s + st * 2 * TILE + TILE, table, table_s,
+                   first_block, n, kv_end, kvh);
     cp_async_commit();
-    cp_async_wait_but_one();
+  }
+  int stage = 0, fill = STAGES - 1;
+  for (int n0 = n_first; n0 < tile_end; n0 += B_BN) {
+    const int ahead = n0 + (STAGES - 1) * B_BN;
+    if (ahead < tile_end)
+      load_kv_tile(a, kv_s + fill * 2 * TILE, kv_s + fill * 2 * TILE + TILE, table, table_s,
+                   first_block, ahead, kv_end, kvh);
+    cp_async_commit();
+    cp_async_wait_group<STAGES - 1>();  // the tile of this iteration has landed
     __syncthreads();
     const __nv_bfloat16* k_s = kv_s + stage * 2 * TILE;
     const __nv_bfloat16* v_s = k_s + TILE;
-    float s[2][4];
-    warp_qk<2>(s, q_s, k_s, warp * 16, lane);
-    softmax_step<2>(s, o, m, l, pos, n0 + warp * 16, kv_begin, kv_end, a.window, a.scale_log2,
-                    lane);
-    warp_pv<2>(o, s, v_s, warp * 16, lane);
+    float s[NT][4];
+    warp_qk<NT>(s, q_s + row0 * B_LD, k_s, key0, lane);
+    softmax_step<NT>(s, o, m, l, pos, n0 + key0, kv_begin, kv_end, a.window, a.scale_log2, lane);
+    warp_pv<NT>(o, s, v_s, key0, lane);
     __syncthreads();  // everyone is done with this stage before it is refilled
-    stage ^= 1;
+    stage = stage + 1 == STAGES ? 0 : stage + 1;
+    fill = fill + 1 == STAGES ? 0 : fill + 1;
+  }
+
+  if (!NARROW) {
+    store_rows(a, o, m, l, row0, row_begin, row_count, q_start, kvh, partial_base, lane);
+    return;
   }
 
   // Merge the four warps (each saw a quarter of every tile) through shared memory.
+  cp_async_wait_group<0>();
   __syncthreads();
   float* mo = reinterpret_cast<float*>(smem_raw);  // [4][16][D]
   float* mm = mo + 4 * 16 * D;                      // [4][16]
@@ -579,6 +571,9 @@ __global__ void __launch_bounds__(128) attn_bf16_narrow_kernel(AttnArgs a) {
     }
   }
 }
+
+constexpr int WIDE_STAGES = 2;
+constexpr int NARROW_STAGES = 3;
 
 // =============================================================================================
 // Merge of split key ranges.  Merge item, int32[8]:
@@ -703,27 +698,27 @@ VX_API int vx_attention(int kind, const void* q, void* out, const void* k_cache,
     }
     launch_pdl(attn_f32_kernel, dim3(grid), dim3(128), smem, stream, a);
   } else if (kind == 1) {
-    const size_t smem = (size_t)(64 + 2 * B_BN) * B_LD * sizeof(__nv_bfloat16);
+    const size_t smem = (size_t)(64 + 2 * WIDE_STAGES * B_BN) * B_LD * sizeof(__nv_bfloat16);
     static bool configured = false;
     if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(attn_bf16_wide_kernel,
+      cudaError_t e = cudaFuncSetAttribute(attn_bf16_kernel<false, WIDE_STAGES>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return (int)e;
       configured = true;
     }
-    launch_pdl(attn_bf16_wide_kernel, dim3(grid), dim3(128), smem, stream, a);
+    launch_pdl(attn_bf16_kernel<false, WIDE_STAGES>, dim3(grid), dim3(128), smem, stream, a);
   } else if (kind == 2) {
-    size_t smem = (size_t)(16 + 4 * B_BN) * B_LD * sizeof(__nv_bfloat16);
+    size_t smem = (size_t)(16 + 2 * NARROW_STAGES * B_BN) * B_LD * sizeof(__nv_bfloat16);
     const size_t merge = (size_t)(4 * 16 * D + 2 * 4 * 16) * sizeof(float);
     if (merge > smem) smem = merge;
     static bool configured = false;
     if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(attn_bf16_narrow_kernel,
+      cudaError_t e = cudaFuncSetAttribute(attn_bf16_kernel<true, NARROW_STAGES>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return (int)e;
       configured = true;
     }
-    launch_pdl(attn_bf16_narrow_kernel, dim3(grid), dim3(128), smem, stream, a);
+    launch_pdl(attn_bf16_kernel<true, NARROW_STAGES>, dim3(grid), dim3(128), smem, stream, a);
   } else {
     return (int)cudaErrorInvalidValue;
   }

@@ -11,6 +11,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define VX_DTYPE_F32 0
 #define VX_DTYPE_BF16 1
@@ -96,11 +97,16 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   config.blockDim = block;
   config.dynamicSmemBytes = smem;
   config.stream = stream;
+  // VELOX_B200_NO_PDL=1 launches every kernel fully serialised (for bisecting a fault).
+  static const bool serialised = [] {
+    const char* value = getenv("VELOX_B200_NO_PDL");
+    return value != nullptr && value[0] == '1';
+  }();
   cudaLaunchAttribute attribute[1];
   attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attribute[0].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attribute;
-  config.numAttrs = 1;
+  config.numAttrs = serialised ? 0 : 1;
   return cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
 }
 

@@ -89,12 +89,32 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restric
   float vals[NORM_MAX_PER_THREAD];
   float ss = 0.f;
   if (cached) {
+    // All loads of the row are independent of each other: element by element for the residual
+    // and the delta, then split by split for the products, eight elements at a time.
 #pragma unroll
     for (int j = 0; j < NORM_MAX_PER_THREAD; ++j) {
       const int i = threadIdx.x + j * blockDim.x;
-      vals[j] = i < hidden ? value(i) : 0.f;
-      ss += vals[j] * vals[j];
+      vals[j] = 0.f;
+      if (i < hidden) vals[j] = d ? x[i] + to_float(d[i]) : x[i];
     }
+    if (p) {
+      float sums[NORM_MAX_PER_THREAD];
+#pragma unroll
+      for (int j = 0; j < NORM_MAX_PER_THREAD; ++j) sums[j] = 0.f;
+#pragma unroll 2
+      for (int s = 0; s < num_partials; ++s) {
+        const float* ps = p + (size_t)s * partial_pitch;
+#pragma unroll
+        for (int j = 0; j < NORM_MAX_PER_THREAD; ++j) {
+          const int i = threadIdx.x + j * blockDim.x;
+          if (i < hidden) sums[j] += ps[i];
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < NORM_MAX_PER_THREAD; ++j) vals[j] += sums[j];
+    }
+#pragma unroll
+    for (int j = 0; j < NORM_MAX_PER_THREAD; ++j) ss += vals[j] * vals[j];
   } else {
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
       const float v = value(i);
