@@ -536,19 +536,38 @@ def test_gemm_bf16_plain_and_bias(k, status, T, N, K):
     assert int(status[0]) == 0
 
 
-@pytest.mark.parametrize("T,N,K,splits", [(8, 1536, 8960, 12), (3, 256, 704, 4), (64, 2048, 1536, 8), (17, 136, 480, 100)])
-def test_gemm_bf16_split_products(k, status, T, N, K, splits):
-    gen = torch.Generator().manual_seed(K)
+@pytest.mark.parametrize("T,N,K,splits", [(8, 1536, 8960, 8), (3, 256, 704, 4), (64, 2048, 1536, 8),
+                                          (17, 136, 480, 100), (1, 1536, 1536, 2), (40, 331, 240, 3)])
+@pytest.mark.parametrize("mode", ["bf16", "f32", "add"])
+def test_gemm_bf16_split_over_a_cluster(k, status, T, N, K, splits, mode):
+    """K split over a thread-block cluster, reduced through distributed shared memory."""
+    gen = torch.Generator().manual_seed(K + splits)
     x = torch.randn(T, K, generator=gen).to(torch.bfloat16).cuda()
     w = (torch.randn(N, K, generator=gen) / math.sqrt(K)).to(torch.bfloat16).cuda()
-    out = torch.zeros(splits, T, N, dtype=torch.float32, device="cuda")
-    used = k.gemm_bf16(x, w, None, out, k.GEMM_OUT_F32, T, status, splits=splits)
-    assert 1 <= used <= splits
-    want = x.double() @ w.double().T
-    got = out[:used].double().sum(0)
-    assert (got.cpu() - want.cpu()).abs().max().item() <= 2e-5 * max(want.abs().max().item(), 1.0)
-    assert torch.all(out[used:] == 0)
+    bias = torch.randn(N, generator=gen).cuda()
+    want = x.double() @ w.double().T + bias.double()
+    scale = max(want.abs().max().item(), 1.0)
+    if mode == "bf16":
+        out = torch.zeros(T, N, dtype=torch.bfloat16, device="cuda")
+        k.gemm_bf16(x, w, bias, out, k.GEMM_OUT_BF16, T, status, splits=splits)
+        tol = 1e-2
+    elif mode == "f32":
+        out = torch.zeros(T, N, dtype=torch.float32, device="cuda")
+        k.gemm_bf16(x, w, bias, out, k.GEMM_OUT_F32, T, status, splits=splits)
+        tol = 2e-5
+    else:
+        start = torch.randn(T, N, generator=gen).cuda()
+        out = start.clone()
+        k.gemm_bf16(x, w, bias, out, k.GEMM_ADD_F32, T, status, splits=splits)
+        want = want + start.double()
+        tol = 2e-5
+    assert (out.double().cpu() - want.cpu()).abs().max().item() <= tol * scale
     assert int(status[0]) == 0
+    # the same call twice gives the same bits: the order of the sums is fixed
+    if mode == "f32":
+        again = torch.zeros_like(out)
+        k.gemm_bf16(x, w, bias, again, k.GEMM_OUT_F32, T, status, splits=splits)
+        assert torch.equal(out, again)
 
 
 @pytest.mark.parametrize("T,N,K", [(4, 1536, 1536), (70, 240, 200), (256, 1536, 8960)])

@@ -55,14 +55,6 @@ def test_parts_of_one_layer(tmp_path, dtype, case, page):
     eps = cfg["rms_norm_eps"]
     p = "model.layers.0."
 
-    def value(delta):
-        """A pending product as a tensor, whether it is one or a sum of split products."""
-        from velox_b200.ops.linear import Partials
-
-        if isinstance(delta, Partials):
-            return delta.data[: delta.count].sum(0)
-        return delta
-
     def close(got, want, what):
         got, want = got.double().cpu(), want.double()
         err = (got - want).abs().max().item()
@@ -87,13 +79,13 @@ def test_parts_of_one_layer(tmp_path, dtype, case, page):
     exact_in = x0.to(dtype).cuda()
     padded = torch.zeros(256, E, dtype=dtype, device="cuda")
     padded[:T] = exact_in
-    mixed = value(block.mixer.forward(padded, ctx, runner.layer_caches[0]))
+    mixed = block.mixer.forward(padded, ctx, runner.layer_caches[0])
     close(mixed[:T], want_attn, "attention mixer")
 
     # feed-forward
     y = torch.randn(T, E, generator=torch.Generator().manual_seed(2)).double()
     padded[:T] = y.to(dtype).cuda()
-    ff = value(block.feed_forward.forward(padded, ctx))
+    ff = block.feed_forward.forward(padded, ctx)
     want_ff = plain_model.swiglu_mlp(y.to(dtype).double(), tensors[p + "mlp.gate_proj.weight"],
                                      tensors[p + "mlp.up_proj.weight"], tensors[p + "mlp.down_proj.weight"])
     close(ff[:T], want_ff, "feed-forward")
@@ -108,7 +100,8 @@ def test_parts_of_one_layer(tmp_path, dtype, case, page):
     block.forward(hidden, ctx2, runner.layer_caches[0])
     torch.cuda.synchronize()
     want_h = plain_model.decoder_layer(h0, tensors, 0, cfg, angles.cos().double(), angles.sin().double(), None)
-    close(hidden.resid[:T] + value(hidden.delta)[:T].float(), want_h, "block")
+    pending = 0 if hidden.delta is None else hidden.delta[:T].float()
+    close(hidden.resid[:T] + pending, want_h, "block")
 
     # lm head on selected rows
     final = torch.zeros(8, E, dtype=dtype, device="cuda")

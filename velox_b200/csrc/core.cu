@@ -36,37 +36,18 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
 
 // ---------------------------------------------------------------------------------------------
 // Fused residual add + RMSNorm.
-//   v = resid[r] + delta[r] + sum_s partials[s][r]   (delta and partials may be null; the
-//       partials are the float32 split products of a projection, [num_partials, T, hidden])
+//   v = resid[r] + delta[r]   (delta may be null)
 //   if write_resid: resid[r] = v
 //   out[o] = v * (1 / sqrt(mean(v^2) + eps)) * weight
 // `rows` (may be null) selects the rows to normalise: out row o comes from input row rows[o].
 // ---------------------------------------------------------------------------------------------
-// Sum of the split products of one element, four loads in flight at a time.
-__device__ __forceinline__ float sum_partials(const float* __restrict__ p, int num_partials,
-                                              long long pitch) {
-  float acc = 0.f;
-  int s = 0;
-  for (; s + 4 <= num_partials; s += 4) {
-    const float a0 = p[(size_t)s * pitch], a1 = p[(size_t)(s + 1) * pitch];
-    const float a2 = p[(size_t)(s + 2) * pitch], a3 = p[(size_t)(s + 3) * pitch];
-    acc += a0;
-    acc += a1;
-    acc += a2;
-    acc += a3;
-  }
-  for (; s < num_partials; ++s) acc += p[(size_t)s * pitch];
-  return acc;
-}
-
 constexpr int NORM_MAX_PER_THREAD = 8;
 
 template <typename T>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restrict__ delta,
-                                   const float* __restrict__ partials, int num_partials,
-                                   long long partial_pitch, const float* __restrict__ weight,
-                                   float eps, T* __restrict__ out, const int* __restrict__ rows,
-                                   int hidden, int write_resid) {
+                                   const float* __restrict__ weight, float eps,
+                                   T* __restrict__ out, const int* __restrict__ rows, int hidden,
+                                   int write_resid) {
   __shared__ float scratch[32];
   allow_dependents();
   grid_dependency_wait();
@@ -74,44 +55,17 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restric
   const int r = rows ? rows[o] : o;
   float* x = resid + (size_t)r * hidden;
   const T* d = delta ? delta + (size_t)r * hidden : nullptr;
-  const float* p = partials ? partials + (size_t)r * hidden : nullptr;
-
-  // The sum of a row: residual, then the pending delta, then the split products in order.
-  auto value = [&](int i) {
-    float v = x[i];
-    if (d) v += to_float(d[i]);
-    if (p) v += sum_partials(p + i, num_partials, partial_pitch);
-    return v;
-  };
+  auto value = [&](int i) { return d ? x[i] + to_float(d[i]) : x[i]; };
 
   // A row of up to 8 elements per thread is read once and kept in registers.
   const bool cached = hidden <= NORM_MAX_PER_THREAD * (int)blockDim.x;
   float vals[NORM_MAX_PER_THREAD];
   float ss = 0.f;
   if (cached) {
-    // All loads of the row are independent of each other: element by element for the residual
-    // and the delta, then split by split for the products, eight elements at a time.
 #pragma unroll
     for (int j = 0; j < NORM_MAX_PER_THREAD; ++j) {
       const int i = threadIdx.x + j * blockDim.x;
-      vals[j] = 0.f;
-      if (i < hidden) vals[j] = d ? x[i] + to_float(d[i]) : x[i];
-    }
-    if (p) {
-      float sums[NORM_MAX_PER_THREAD];
-#pragma unroll
-      for (int j = 0; j < NORM_MAX_PER_THREAD; ++j) sums[j] = 0.f;
-#pragma unroll 2
-      for (int s = 0; s < num_partials; ++s) {
-        const float* ps = p + (size_t)s * partial_pitch;
-#pragma unroll
-        for (int j = 0; j < NORM_MAX_PER_THREAD; ++j) {
-          const int i = threadIdx.x + j * blockDim.x;
-          if (i < hidden) sums[j] += ps[i];
-        }
-      }
-#pragma unroll
-      for (int j = 0; j < NORM_MAX_PER_THREAD; ++j) vals[j] += sums[j];
+      vals[j] = i < hidden ? value(i) : 0.f;
     }
 #pragma unroll
     for (int j = 0; j < NORM_MAX_PER_THREAD; ++j) ss += vals[j] * vals[j];
@@ -146,18 +100,12 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restric
 // RoPE on q (in place) and on k, fused with the write of k and v into the paged cache.
 //   qkv row layout: [H*D q | G*D k | G*D v]; the first `rot` dims of every head rotate as two
 //   halves (rot = 0: no rotation), cos/sin are float32 tables [max_pos, rot/2].
-//   The row comes from the qkv buffer itself or, when `partials` is given, from the float32
-//   split products of the projection ([num_partials, T, width]) plus `bias`; the rotated q is
-//   written to the qkv buffer either way.
 //   slots[t] is the flat cache index (page * page_size + offset); a negative slot skips the
 //   write (padding rows).  write_cache = 0 rotates q only (a layer that reads another's cache).
 //   One block per (token, head of q|k|v).
 // ---------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void rope_cache_write_kernel(T* __restrict__ qkv, const float* __restrict__ partials,
-                                        int num_partials, long long partial_pitch,
-                                        const float* __restrict__ bias,
-                                        const int* __restrict__ positions,
+__global__ void rope_cache_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
                                         const float* __restrict__ cos_t,
                                         const float* __restrict__ sin_t,
                                         const int* __restrict__ slots, T* __restrict__ k_cache,
@@ -180,14 +128,7 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, const float* __rest
   const float* s = sin_t + (size_t)pos * half;
   const size_t width = (size_t)(H + 2 * G) * D;
   T* row = qkv + (size_t)t * width + (size_t)head * D;
-  const float* prow = partials ? partials + (size_t)t * width + (size_t)head * D : nullptr;
-  const float* brow = bias ? bias + (size_t)head * D : nullptr;
-  // Element e of this head: from the buffer, or bias plus the split products.
-  auto load = [&](int e) {
-    if (!prow) return to_float(row[e]);
-    const float acc = sum_partials(prow + e, num_partials, partial_pitch);
-    return brow ? acc + brow[e] : acc;
-  };
+  auto load = [&](int e) { return to_float(row[e]); };
 
   T* dst = row;  // q is rotated in place
   if (!is_q) {
@@ -206,8 +147,8 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, const float* __rest
       dst[i] = from_float<T>(lo * c[i] - hi * s[i]);
       dst[i + half] = from_float<T>(lo * s[i] + hi * c[i]);
     }
-    // Dims that do not rotate: copied for k, and for q when it comes from split products.
-    if (is_k || prow) {
+    // Dims that do not rotate stay where they are for q and are copied for k.
+    if (is_k) {
       for (int i = rot + threadIdx.x; i < D; i += blockDim.x) dst[i] = from_float<T>(load(i));
     }
   } else {
@@ -325,28 +266,24 @@ VX_API int vx_embed(const void* table, int dtype, const int* ids, float* resid, 
   return (int)cudaGetLastError();
 }
 
-VX_API int vx_add_rmsnorm(float* resid, const void* delta, const float* partials,
-                          int num_partials, long long partial_pitch, const float* weight,
-                          float eps, void* out, int dtype, const int* rows, int num_out_rows,
-                          int hidden, int write_resid, cudaStream_t stream) {
+VX_API int vx_add_rmsnorm(float* resid, const void* delta, const float* weight, float eps,
+                          void* out, int dtype, const int* rows, int num_out_rows, int hidden,
+                          int write_resid, cudaStream_t stream) {
   if (num_out_rows <= 0) return 0;
   // About four elements per thread: enough loads in flight per row without starving the sum.
   int threads = ((hidden + 3) / 4 + 31) / 32 * 32;
   threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
   if (dtype == VX_DTYPE_F32)
     launch_pdl(add_rmsnorm_kernel<float>, dim3(num_out_rows), dim3(threads), 0, stream, 
-        resid, (const float*)delta, partials, num_partials, partial_pitch, weight, eps,
-        (float*)out, rows, hidden, write_resid);
+        resid, (const float*)delta, weight, eps, (float*)out, rows, hidden, write_resid);
   else
     launch_pdl(add_rmsnorm_kernel<__nv_bfloat16>, dim3(num_out_rows), dim3(threads), 0, stream, 
-        resid, (const __nv_bfloat16*)delta, partials, num_partials, partial_pitch, weight, eps,
-        (__nv_bfloat16*)out, rows, hidden, write_resid);
+        resid, (const __nv_bfloat16*)delta, weight, eps, (__nv_bfloat16*)out, rows, hidden,
+        write_resid);
   return (int)cudaGetLastError();
 }
 
-VX_API int vx_rope_cache_write(void* qkv, int dtype, const float* partials, int num_partials,
-                               long long partial_pitch, const float* bias, const int* positions,
-                               const float* cos_t,
+VX_API int vx_rope_cache_write(void* qkv, int dtype, const int* positions, const float* cos_t,
                                const float* sin_t, const int* slots, void* k_cache,
                                void* v_cache, int num_tokens, int H, int G, int D, int rot,
                                int max_pos, long long num_slots, int write_cache, int* status,
@@ -356,13 +293,12 @@ VX_API int vx_rope_cache_write(void* qkv, int dtype, const float* partials, int 
   const dim3 grid(num_tokens, H + 2 * G);
   if (dtype == VX_DTYPE_F32)
     launch_pdl(rope_cache_write_kernel<float>, dim3(grid), dim3(threads), 0, stream, 
-        (float*)qkv, partials, num_partials, partial_pitch, bias, positions, cos_t, sin_t, slots,
-        (float*)k_cache, (float*)v_cache, H, G, D, rot, max_pos, num_slots, write_cache, status);
+        (float*)qkv, positions, cos_t, sin_t, slots, (float*)k_cache, (float*)v_cache, H, G, D,
+        rot, max_pos, num_slots, write_cache, status);
   else
     launch_pdl(rope_cache_write_kernel<__nv_bfloat16>, dim3(grid), dim3(threads), 0, stream, 
-        (__nv_bfloat16*)qkv, partials, num_partials, partial_pitch, bias, positions, cos_t, sin_t,
-        slots, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, H, G, D, rot, max_pos, num_slots,
-        write_cache, status);
+        (__nv_bfloat16*)qkv, positions, cos_t, sin_t, slots, (__nv_bfloat16*)k_cache,
+        (__nv_bfloat16*)v_cache, H, G, D, rot, max_pos, num_slots, write_cache, status);
   return (int)cudaGetLastError();
 }
 

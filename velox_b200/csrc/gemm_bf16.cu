@@ -3,8 +3,12 @@
 // The weight is the M operand of the MMA: a CTA owns 128 rows of W (128 output features) and
 // BN tokens, D^T[128, BN] = W_tile[128, K] * X_tile[BN, K]^T, accumulated in tensor memory.
 // With few tokens (decode) the tensor-core tile is still full, because its 128-row side is made
-// of weight rows; the kernel then streams W once at memory speed, and the key range can be split
-// over several CTAs (split-K) so that a projection with few output tiles still fills the GPU.
+// of weight rows; the kernel then streams W once at memory speed.  A projection with few output
+// tiles is split along K over a thread-block cluster (2, 4 or 8 CTAs): every CTA accumulates its
+// share of K in its own tensor memory, parks the partial tile in its shared memory, and after a
+// cluster barrier each CTA sums one slice of the tile over all peers through distributed shared
+// memory, in rank order, and writes it out.  No partial product touches global memory and the
+// order of the sums is fixed.
 //
 //   warp 0, one lane : TMA producer.  cp.async.bulk.tensor 2-D tiles of W [128 x 64] and
 //                      X [BN x 64] into a ring of 128-byte-swizzled shared-memory stages.
@@ -17,7 +21,7 @@
 //
 // Epilogue modes:
 //   0  out bf16  [T, ldy] = acc + bias
-//   1  out f32   [T, ldy] = acc + bias          (logits; split-K partials with a split offset)
+//   1  out f32   [T, ldy] = acc + bias          (logits)
 //   2  out f32   [T, ldy] += acc                (projection added straight into the float32
 //                                                residual stream; one CTA owns each element)
 //   3  out bf16  [T, ldy] = silu(gate) * up     W rows are [64 gate | 64 up] per CTA (the host
@@ -166,18 +170,49 @@ struct GemmArgs {
   void* out;
   int* status;
   long long ldy;         // row pitch of out, in elements
-  long long split_pitch; // elements between the outputs of consecutive splits (mode 1)
   int T, N, K;
   int mode;
   int kb_per_split;      // 64-wide K blocks per split
+  int splits;            // CTAs of the cluster that share one output tile (1: no cluster)
 };
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  return rank;
+}
+
+// A float of a peer CTA's shared memory, at the same offset as `local_addr` here.
+__device__ __forceinline__ float load_peer_shared(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
+// One element of the output in the epilogue mode of the launch (modes 0, 1, 2).
+__device__ __forceinline__ void store_output(const GemmArgs& g, size_t index, float value) {
+  if (g.mode == 0)
+    ((__nv_bfloat16*)g.out)[index] = __float2bfloat16_rn(value);
+  else if (g.mode == 1)
+    ((float*)g.out)[index] = value;
+  else
+    ((float*)g.out)[index] += value;
+}
 
 template <int BN>
 struct GemmShape {
   static constexpr uint32_t B_BYTES = BN * GB_BK * 2;
   static constexpr uint32_t STAGE_BYTES = GB_A_BYTES + B_BYTES;
-  static constexpr int STAGES_FIT = (200 * 1024) / STAGE_BYTES;
-  static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
+  // Four stages: 64 KB of weight tiles in flight per CTA, and with few tokens two CTAs fit on
+  // an SM, so the next projection's CTAs can move in and prefetch while this one drains.
+  static constexpr int STAGES = 4;
   static constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
   static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024;
 };
@@ -205,6 +240,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   const int kb_begin = split * g.kb_per_split;
   const int kb_end = min(num_kb_total, kb_begin + g.kb_per_split);
   const int num_kb = max(0, kb_end - kb_begin);
+  const bool clustered = g.splits > 1;
 
   if (threadIdx.x == 0) {
     epilogue_failed = 0;
@@ -289,21 +325,31 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     if (!mbar_wait(smem_u32(&acc_bar), 0u, g.status)) epilogue_failed = 1;
     // All four epilogue warps take the same path below (mode 3 has barriers among them).
     asm volatile("bar.sync 1, 128;" ::: "memory");
-    const bool ready = epilogue_failed == 0;
+    const bool ready = epilogue_failed == 0 && num_kb > 0;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const int row = quarter * 32 + lane;  // row of the CTA's W tile
-    if (ready && num_kb > 0) {
+    constexpr int cols = BN >= 32 ? 32 : 16;
+    const uint32_t lane_base = tmem_acc + ((uint32_t)(quarter * 32) << 16);
+    if (clustered) {
+      // Park the partial tile in shared memory (the stages are free once the MMAs are done):
+      // partial[row][token] at a pitch of BN + 1 floats.
+      float* partial = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw)));
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        float v[32];
+        if (ready) {
+          if (BN >= 32) tmem_load_32(lane_base + c0, v); else tmem_load_16(lane_base + c0, v);
+        }
+#pragma unroll
+        for (int j = 0; j < cols; ++j) partial[row * (BN + 1) + c0 + j] = ready ? v[j] : 0.f;
+      }
+    } else if (ready) {
       if (g.mode == 3) {
         // rows 0..63 gate, 64..127 up of the same 64 output features
         const int n = n0 + (row & 63);
         __nv_bfloat16* out = (__nv_bfloat16*)g.out;
         for (int c0 = 0; c0 < BN; c0 += 32) {
           float v[32];
-          if (BN >= 32)
-            tmem_load_32(tmem_acc + ((uint32_t)(quarter * 32) << 16) + c0, v);
-          else
-            tmem_load_16(tmem_acc + ((uint32_t)(quarter * 32) << 16) + c0, v);
-          const int cols = BN >= 32 ? 32 : 16;
+          if (BN >= 32) tmem_load_32(lane_base + c0, v); else tmem_load_16(lane_base + c0, v);
           // up rows hand their values to the gate rows through shared memory
           if (row >= 64) {
             for (int j = 0; j < cols; ++j) swap_buf[(row - 64) * 33 + j] = v[j];
@@ -325,30 +371,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         const float b = (g.bias != nullptr && n < g.N) ? g.bias[n] : 0.f;
         for (int c0 = 0; c0 < BN; c0 += 32) {
           float v[32];
-          if (BN >= 32)
-            tmem_load_32(tmem_acc + ((uint32_t)(quarter * 32) << 16) + c0, v);
-          else
-            tmem_load_16(tmem_acc + ((uint32_t)(quarter * 32) << 16) + c0, v);
-          const int cols = BN >= 32 ? 32 : 16;
+          if (BN >= 32) tmem_load_32(lane_base + c0, v); else tmem_load_16(lane_base + c0, v);
           if (n < g.N) {
-            if (g.mode == 0) {
-              __nv_bfloat16* out = (__nv_bfloat16*)g.out;
-              for (int j = 0; j < cols; ++j) {
-                const int t = t0 + c0 + j;
-                if (t < g.T) out[(size_t)t * g.ldy + n] = __float2bfloat16_rn(v[j] + b);
-              }
-            } else if (g.mode == 1) {
-              float* out = (float*)g.out + (size_t)split * g.split_pitch;
-              for (int j = 0; j < cols; ++j) {
-                const int t = t0 + c0 + j;
-                if (t < g.T) out[(size_t)t * g.ldy + n] = v[j] + b;
-              }
-            } else {
-              float* out = (float*)g.out;
-              for (int j = 0; j < cols; ++j) {
-                const int t = t0 + c0 + j;
-                if (t < g.T) out[(size_t)t * g.ldy + n] += v[j] + b;
-              }
+            for (int j = 0; j < cols; ++j) {
+              const int t = t0 + c0 + j;
+              if (t < g.T) store_output(g, (size_t)t * g.ldy + n, v[j] + b);
             }
           }
         }
@@ -357,6 +384,30 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   }
   __syncthreads();
+  if (clustered) {
+    // Every CTA of the cluster has parked its partial tile.
+    cluster_sync_all();
+    if (warp >= 2) {
+      // This CTA sums the tokens [rank * BN / splits, (rank + 1) * BN / splits) of the tile over
+      // all peers, in rank order, and writes them: a thread per output feature.
+      const int row = (warp & 3) * 32 + lane;
+      const int n = n0 + row;
+      const int per_cta = BN / g.splits;
+      const uint32_t rank = cluster_rank();
+      const uint32_t local = smem_base + (uint32_t)(row * (BN + 1)) * 4u;
+      const float b = (g.bias != nullptr && n < g.N) ? g.bias[n] : 0.f;
+      for (int j = (int)rank * per_cta; j < ((int)rank + 1) * per_cta; ++j) {
+        const int t = t0 + j;
+        if (t >= g.T || n >= g.N) continue;
+        float acc = 0.f;
+        for (int peer = 0; peer < g.splits; ++peer)
+          acc += load_peer_shared(local + (uint32_t)j * 4u, (uint32_t)peer);
+        store_output(g, (size_t)t * g.ldy + n, acc + b);
+      }
+    }
+    // No CTA may leave while a peer still reads its shared memory.
+    cluster_sync_all();
+  }
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc),
@@ -428,8 +479,29 @@ static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mw2, const CUte
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  launch_pdl(gemm_bf16_kernel<BN>, dim3(grid), dim3(GB_THREADS), S::SMEM_BYTES, stream, mw, mw2, mx, g);
-  return (int)cudaGetLastError();
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = dim3(GB_THREADS);
+  config.dynamicSmemBytes = S::SMEM_BYTES;
+  config.stream = stream;
+  cudaLaunchAttribute attributes[2];
+  int count = 0;
+  const char* serialised = getenv("VELOX_B200_NO_PDL");
+  if (serialised == nullptr || serialised[0] != '1') {
+    attributes[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[count].val.programmaticStreamSerializationAllowed = 1;
+    ++count;
+  }
+  if (g.splits > 1) {
+    attributes[count].id = cudaLaunchAttributeClusterDimension;
+    attributes[count].val.clusterDim.x = 1;
+    attributes[count].val.clusterDim.y = 1;
+    attributes[count].val.clusterDim.z = (unsigned)g.splits;
+    ++count;
+  }
+  config.attrs = attributes;
+  config.numAttrs = count;
+  return (int)cudaLaunchKernelEx(&config, gemm_bf16_kernel<BN>, mw, mw2, mx, g);
 }
 
 }  // namespace vx
@@ -445,35 +517,42 @@ VX_API int vx_gemm_bf16_token_tile(int num_tokens) {
   return 256;
 }
 
+// Largest power of two <= value, at most 8 (a portable cluster).
+static int floor_pow2_8(int value) {
+  int p = 1;
+  while (p * 2 <= value && p < 8) p *= 2;
+  return p;
+}
+
 // x [T, K] bf16, w [N, K] bf16 (mode 3: w [2 * N, K], gate rows then up rows).
+// x_rows is the number of rows the x buffer really has (>= T); rows T.. are read but their
+// results are never written.  `splits` (rounded down to 1, 2, 4 or 8 and to what K and the
+// token tile allow) CTAs share each output tile as a cluster.
 // Returns 0 on launch, a cudaError_t on failure, or -1 if the sizes are refused
 // (K not a multiple of 8, unaligned pointers, no driver entry point).
-// x_rows is the number of rows the x buffer really has (>= T); rows T.. are read but their
-// results are never written.
 VX_API int vx_gemm_bf16(const void* x, const void* w, const float* bias, void* out, int mode,
                         int T, int x_rows, int N, int K, long long ldy, int splits,
-                        long long split_pitch, int* status, cudaStream_t stream) {
+                        int* status, cudaStream_t stream) {
   if (T <= 0 || N <= 0) return 0;
   if (K <= 0 || (K % 8) != 0) return -1;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return -1;
   if (mode < 0 || mode > 3) return -1;
   const int bn = vx_gemm_bf16_token_tile(T);
   const int num_kb = (K + GB_BK - 1) / GB_BK;
-  if (splits < 1) splits = 1;
-  if (splits > num_kb) splits = num_kb;
-  if (mode != 1) splits = 1;
+  if (splits < 1 || mode == 3 || bn > 64) splits = 1;
+  splits = floor_pow2_8(splits < num_kb ? splits : num_kb);
+  if (splits > bn) splits = bn;
   GemmArgs g;
   g.bias = bias;
   g.out = out;
   g.status = status;
   g.ldy = ldy;
-  g.split_pitch = split_pitch;
   g.T = T;
   g.N = N;
   g.K = K;
   g.mode = mode;
   g.kb_per_split = (num_kb + splits - 1) / splits;
-  splits = (num_kb + g.kb_per_split - 1) / g.kb_per_split;
+  g.splits = splits;
 
   CUtensorMap mw, mw2, mx;
   if (mode == 3) {
@@ -494,13 +573,4 @@ VX_API int vx_gemm_bf16(const void* x, const void* w, const float* bias, void* o
     case 128: return launch_gemm<128>(mw, mw2, mx, g, grid, stream);
     default: return launch_gemm<256>(mw, mw2, mx, g, grid, stream);
   }
-}
-
-// Number of splits the launcher will really use for (K, splits asked).
-VX_API int vx_gemm_bf16_effective_splits(int K, int splits) {
-  const int num_kb = (K + GB_BK - 1) / GB_BK;
-  if (splits < 1) splits = 1;
-  if (splits > num_kb) splits = num_kb;
-  const int per = (num_kb + splits - 1) / splits;
-  return (num_kb + per - 1) / per;
 }

@@ -93,6 +93,8 @@ class StepContext:
     status: torch.Tensor
     workspace: Workspace
     plans: Dict[Tuple[Optional[int], Tuple], DevicePlan]
+    # The float32 residual stream while a block runs its parts (they may add into it), else None.
+    residual: Optional[torch.Tensor] = None
     # Host copies, for parts that lay out work of their own.
     q_lens_host: List[int] = field(default_factory=list)
     kv_lens_host: List[int] = field(default_factory=list)

@@ -43,11 +43,10 @@ def core():
         lib = build.load_core()
         lib.vx_embed.argtypes = [_ptr, _c_int, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr, _ptr]
         lib.vx_add_rmsnorm.argtypes = [
-            _ptr, _ptr, _ptr, _c_int, _c_ll, _ptr, _c_f, _ptr, _c_int, _ptr, _c_int, _c_int, _c_int,
-            _ptr,
+            _ptr, _ptr, _ptr, _c_f, _ptr, _c_int, _ptr, _c_int, _c_int, _c_int, _ptr,
         ]
         lib.vx_rope_cache_write.argtypes = [
-            _ptr, _c_int, _ptr, _c_int, _c_ll, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
+            _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
             _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _ptr, _ptr,
         ]
         lib.vx_swiglu.argtypes = [_ptr, _ptr, _c_int, _c_int, _c_int, _ptr]
@@ -63,8 +62,7 @@ def core():
             _ptr, _c_int, _c_int, _c_ll, _ptr, _c_ll, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
         ]
         lib.vx_gemm_bf16.argtypes = [
-            _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _c_ll,
-            _ptr, _ptr,
+            _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _ptr, _ptr,
         ]
         _core = lib
     return _core
@@ -149,14 +147,11 @@ def add_rmsnorm(
     num_rows: int,
     rows: Optional[torch.Tensor] = None,
     write_resid: bool = True,
-    partials: Optional[torch.Tensor] = None,
-    num_partials: int = 0,
 ) -> None:
-    """v = resid + delta + sum(partials); resid = v (if write_resid); out = rmsnorm(v) * weight.
+    """v = resid + delta; resid = v (if write_resid); out = rmsnorm(v) * weight, float32 inside.
 
-    ``delta`` is a pending product in the compute dtype, ``partials`` float32
-    [>= num_partials, rows, hidden] the split products of a projection; either may be None.
-    With ``rows`` (int32 indices), output row o is computed from input row rows[o].
+    ``delta`` is a pending product in the compute dtype, or None.  With ``rows`` (int32
+    indices), output row o is computed from input row rows[o].
     """
     _need(resid, torch.float32, "resid")
     _need(weight, torch.float32, "weight")
@@ -170,15 +165,8 @@ def add_rmsnorm(
             raise ValueError("delta width does not match the residual width")
     if rows is not None:
         _need(rows, torch.int32, "rows")
-    pitch = 0
-    if partials is not None:
-        _need(partials, torch.float32, "partials")
-        if partials.dim() != 3 or partials.shape[2] != hidden or partials.shape[0] < num_partials:
-            raise ValueError("partials must be [splits, rows, hidden]")
-        pitch = partials.stride(0)
     _check(
-        core().vx_add_rmsnorm(_p(resid), _p(delta), _p(partials), num_partials, pitch,
-                              _p(weight), float(eps), _p(out),
+        core().vx_add_rmsnorm(_p(resid), _p(delta), _p(weight), float(eps), _p(out),
                               _code(out.dtype), _p(rows), num_rows, hidden,
                               1 if write_resid else 0, _stream()),
         "add_rmsnorm",
@@ -199,15 +187,10 @@ def rope_cache_write(
     head_dim: int,
     rotary_dim: int,
     status: torch.Tensor,
-    partials: Optional[torch.Tensor] = None,
-    num_partials: int = 0,
-    bias: Optional[torch.Tensor] = None,
 ) -> None:
     """Rotate q in place; rotate k and write k, v to the paged cache at ``slots``.
 
     ``k_cache``/``v_cache`` None: rotate q only (a layer that reads another layer's cache).
-    With ``partials`` (float32 [splits, rows, width]) the q|k|v row is the sum of the split
-    products plus ``bias`` instead of the contents of ``qkv``; q still lands in ``qkv``.
     """
     _need(qkv, qkv.dtype, "qkv")
     _need(positions, torch.int32, "positions")
@@ -229,17 +212,8 @@ def rope_cache_write(
             raise ValueError("cos/sin tables do not match the rotary width")
     else:
         max_pos = 0
-    pitch = 0
-    if partials is not None:
-        _need(partials, torch.float32, "partials")
-        if partials.dim() != 3 or partials.shape[2] != qkv.shape[1] or partials.shape[0] < num_partials:
-            raise ValueError("partials must be [splits, rows, qkv width]")
-        pitch = partials.stride(0)
-        if bias is not None:
-            _need(bias, torch.float32, "bias")
     _check(
-        core().vx_rope_cache_write(_p(qkv), _code(qkv.dtype), _p(partials), num_partials, pitch,
-                                   _p(bias), _p(positions), _p(cos), _p(sin),
+        core().vx_rope_cache_write(_p(qkv), _code(qkv.dtype), _p(positions), _p(cos), _p(sin),
                                    _p(slots), _p(k_cache), _p(v_cache), num_tokens, num_heads,
                                    num_kv_heads, head_dim, rotary_dim, max_pos, num_slots,
                                    1 if write else 0, _p(status), _stream()),
@@ -293,11 +267,11 @@ def gemm_bf16(
     num_rows: int,
     status: torch.Tensor,
     splits: int = 1,
-) -> int:
+) -> None:
     """out = x[:num_rows] @ w.T on tcgen05 tensor cores (see gemm_bf16.cu for the modes).
 
-    Mode GEMM_OUT_F32 with ``splits`` > 1 writes one partial product per split to
-    ``out[split]`` (out is [splits, rows, N]); the caller sums them.  Returns the splits used.
+    ``splits`` CTAs (1, 2, 4 or 8; rounded down) share each output tile as a thread-block
+    cluster and reduce through distributed shared memory; the output is final either way.
     """
     _need(x, torch.bfloat16, "x")
     _need(w, torch.bfloat16, "w")
@@ -310,28 +284,18 @@ def gemm_bf16(
         raise ValueError(f"gemm shapes do not agree: x {tuple(x.shape)}, w {tuple(w.shape)}")
     want = torch.bfloat16 if mode in (GEMM_OUT_BF16, GEMM_SWIGLU) else torch.float32
     _need(out, want, "out")
-    if out.shape[-1] != n:
-        raise ValueError(f"output width {out.shape[-1]} does not match {n}")
+    if out.dim() != 2 or out.shape[1] != n:
+        raise ValueError(f"output {tuple(out.shape)} does not match width {n}")
     if bias is not None:
         _need(bias, torch.float32, "bias")
-    split_pitch = 0
-    if mode == GEMM_OUT_F32 and splits > 1:
-        if out.dim() != 3 or out.shape[0] < splits:
-            raise ValueError("split products need an output of [splits, rows, N]")
-        split_pitch = out.stride(0)
-    else:
-        splits = 1
     code = core().vx_gemm_bf16(_p(x), _p(w), _p(bias), _p(out), mode, num_rows, x.shape[0], n, k,
-                               out.stride(-2), splits, split_pitch, _p(status), _stream())
+                               out.stride(0), splits, _p(status), _stream())
     if code == -1:
         raise KernelError(
             f"gemm_bf16 refuses x {tuple(x.shape)} w {tuple(w.shape)}: the inner size must be a "
             "multiple of 8 and both operands 16-byte aligned"
         )
     _check(code, "gemm_bf16")
-    kb = -(-k // 64)
-    per = -(-kb // max(1, min(splits, kb)))
-    return -(-kb // per)
 
 
 def cast_bf16_to_f32(src: torch.Tensor, out: torch.Tensor, count: int) -> None:

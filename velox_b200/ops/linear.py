@@ -5,15 +5,14 @@ true 32-bit path and sums every output element in a fixed order.
 
 bfloat16: the tcgen05/TMA kernel of ``csrc/gemm_bf16.cu`` when the step has few tokens (decode
 and short portions: the weight fills the 128-row side of the tensor-core tile and is streamed
-once; key ranges are split over CTAs to fill the GPU), a library GEMM (cuBLAS through torch)
-for long portions and for inner sizes the TMA tiles cannot take.  The reference engine uses a
-library GEMM for every projection (``nn.Linear``, src/self_attention.py:32-33,
-src/mlp.py:9-10, src/transformer.py:60 of that project).
+once; projections with few output tiles are split along K over a thread-block cluster), a
+library GEMM (cuBLAS through torch) for long portions and for inner sizes the TMA tiles cannot
+take.  The reference engine uses a library GEMM for every projection (``nn.Linear``,
+src/self_attention.py:32-33, src/mlp.py:9-10, src/transformer.py:60 of that project).
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
-from typing import Optional, Union
+from typing import Optional
 
 import torch
 
@@ -31,14 +30,6 @@ def _num_sms() -> int:
     return _NUM_SMS
 
 
-@dataclass
-class Partials:
-    """A product that exists as float32 split sums: the value is ``data[:count].sum(0)``."""
-
-    data: torch.Tensor  # float32 [splits, rows, N]
-    count: int
-
-
 def use_tensor_core_kernel(x: torch.Tensor, weight: torch.Tensor, num_rows: int) -> bool:
     return (
         weight.dtype == torch.bfloat16
@@ -47,22 +38,12 @@ def use_tensor_core_kernel(x: torch.Tensor, weight: torch.Tensor, num_rows: int)
     )
 
 
-MAX_SPLITS = 16
-
-
-def choose_splits(out_features: int, in_features: int, num_rows: int, tile: int = 128) -> int:
-    """Splits of the inner dimension so that tiles x splits is about the number of SMs, with at
-    least two 64-wide blocks per split and at most about 4 MB of split products."""
+def choose_splits(out_features: int, in_features: int, tile: int = 128) -> int:
+    """CTAs per output tile so that tiles x splits is about the number of SMs, with at least two
+    64-wide blocks of the inner dimension each (the launcher rounds down to 1, 2, 4 or 8)."""
     tiles = -(-out_features // tile)
     blocks = -(-in_features // 64)
-    by_traffic = max(1, (4 << 20) // max(1, num_rows * out_features * 4))
-    return max(1, min(_num_sms() // max(tiles, 1), blocks // 2, by_traffic, MAX_SPLITS))
-
-
-def split_scratch(workspace, out_features: int) -> torch.Tensor:
-    """The float32 buffer [MAX_SPLITS, rows, N] that split products of width N are written to."""
-    rows = min(workspace.max_tokens, SMALL_STEP_TOKENS)
-    return workspace.get(f"linear.partials.{out_features}", (MAX_SPLITS, rows, out_features), torch.float32)
+    return max(1, min(_num_sms() // max(tiles, 1), blocks // 2, 8))
 
 
 def linear(
@@ -73,19 +54,32 @@ def linear(
     num_rows: int,
     bias_lowp: Optional[torch.Tensor] = None,
     status: Optional[torch.Tensor] = None,
+    accumulate: bool = False,
 ) -> torch.Tensor:
-    """out[:num_rows] = x[:num_rows] @ weight.T (+ bias), in the dtype of ``out``."""
+    """out[:num_rows] = x[:num_rows] @ weight.T (+ bias), in the dtype of ``out``.
+
+    ``accumulate`` (tensor-core kernel only, float32 ``out``): add to ``out`` instead, which is
+    how a projection goes straight into the float32 residual stream.
+    """
     if num_rows == 0:
         return out
     if weight.dtype == torch.float32:
+        if accumulate:
+            raise ValueError("the float32 GEMM does not accumulate")
         kernels.gemm_f32(x, weight, bias_f32, out, num_rows)
         return out
     if weight.dtype != torch.bfloat16:
         raise TypeError(f"linear: weights must be float32 or bfloat16, got {weight.dtype}")
     if status is not None and use_tensor_core_kernel(x, weight, num_rows):
-        mode = kernels.GEMM_OUT_F32 if out.dtype == torch.float32 else kernels.GEMM_OUT_BF16
-        kernels.gemm_bf16(x, weight, bias_f32, out, mode, num_rows, status)
+        if accumulate:
+            mode = kernels.GEMM_ADD_F32
+        else:
+            mode = kernels.GEMM_OUT_F32 if out.dtype == torch.float32 else kernels.GEMM_OUT_BF16
+        kernels.gemm_bf16(x, weight, bias_f32, out, mode, num_rows, status,
+                          splits=choose_splits(weight.shape[0], weight.shape[1]))
         return out
+    if accumulate:
+        raise ValueError("only the tensor-core kernel accumulates into its output")
     if out.dtype != torch.bfloat16:
         raise TypeError("the library GEMM path writes bfloat16")
     xs, os_ = x[:num_rows], out[:num_rows]
@@ -98,19 +92,6 @@ def linear(
     return out
 
 
-def linear_split(
-    x: torch.Tensor,
-    weight: torch.Tensor,
-    scratch: torch.Tensor,
-    num_rows: int,
-    status: torch.Tensor,
-) -> Partials:
-    """x @ weight.T as float32 split products in ``scratch`` [max_splits, rows, N] (no bias)."""
-    splits = min(choose_splits(weight.shape[0], weight.shape[1], num_rows), scratch.shape[0])
-    used = kernels.gemm_bf16(x, weight, None, scratch, kernels.GEMM_OUT_F32, num_rows, status, splits=splits)
-    return Partials(scratch, used)
-
-
 def swiglu_linear(
     x: torch.Tensor,
     gate_up_weight: torch.Tensor,
@@ -121,6 +102,3 @@ def swiglu_linear(
     """out = silu(x @ Wg.T) * (x @ Wu.T) in one kernel (gate and up rows of one matrix)."""
     kernels.gemm_bf16(x, gate_up_weight, None, out, kernels.GEMM_SWIGLU, num_rows, status)
     return out
-
-
-Pending = Union[torch.Tensor, Partials, None]

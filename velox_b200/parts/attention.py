@@ -14,7 +14,7 @@ from typing import Optional
 import torch
 
 from ..ops import kernels
-from ..ops.linear import linear, linear_split, split_scratch, use_tensor_core_kernel
+from ..ops.linear import linear, use_tensor_core_kernel
 from .base import CacheNeeds, Mixer, PagedCacheSpec
 from .registry import register_part
 
@@ -63,20 +63,11 @@ class Attention(Mixer):
         T = ctx.num_tokens
         ws = ctx.workspace
         qkv = ws.get("attention.qkv", (ws.max_tokens, self.qkv_width), self.dtype)
-        # Few tokens: the projections run as split products on the tensor-core kernel and the
-        # kernel that consumes them (rotation here, the next norm for the output) sums them.
-        small = use_tensor_core_kernel(x, self.w_qkv, T)
+        linear(x, self.w_qkv, self.b_qkv, qkv, T, self.b_qkv_lowp, status=ctx.status)
         group = ctx.groups[cache.group]
         k_cache, v_cache = (None, None) if cache.read_only else (cache.k, cache.v)
-        if small:
-            parts = linear_split(x, self.w_qkv, split_scratch(ws, self.qkv_width), T, ctx.status)
-            self.position.rotate_and_store(qkv, ctx, group.slot_mapping, k_cache, v_cache,
-                                           self.num_heads, self.num_kv_heads,
-                                           partials=parts, bias=self.b_qkv)
-        else:
-            linear(x, self.w_qkv, self.b_qkv, qkv, T, self.b_qkv_lowp)
-            self.position.rotate_and_store(qkv, ctx, group.slot_mapping, k_cache, v_cache,
-                                           self.num_heads, self.num_kv_heads)
+        self.position.rotate_and_store(qkv, ctx, group.slot_mapping, k_cache, v_cache,
+                                       self.num_heads, self.num_kv_heads)
 
         attn = ws.get("attention.out", (ws.max_tokens, self.q_size), self.dtype)
         plan = ctx.attention_plan(cache.group, self.attention_signature())
@@ -93,8 +84,10 @@ class Attention(Mixer):
                 max_rows=plan.merge_rows,
             )
 
-        if use_tensor_core_kernel(attn, self.w_out, T):
-            return linear_split(attn, self.w_out, split_scratch(ws, self.hidden_size), T, ctx.status)
+        if ctx.residual is not None and use_tensor_core_kernel(attn, self.w_out, T):
+            # Few tokens: the projection is added straight into the float32 residual stream.
+            linear(attn, self.w_out, None, ctx.residual, T, status=ctx.status, accumulate=True)
+            return None
         out = ws.get("mixer.out", (ws.max_tokens, self.hidden_size), self.dtype)
-        linear(attn, self.w_out, None, out, T)
+        linear(attn, self.w_out, None, out, T, status=ctx.status)
         return out

@@ -12,8 +12,9 @@ Interfaces (T = tokens of the step, E = model width, dt = compute dtype):
     normalised rows to ``out`` (dt).  Fusing the add into the norm is why the interface has
     both.
 
-A part's product that is waiting to be added to the residual stream ("delta") is either a
-tensor dt [T, E] or ``ops.linear.Partials`` (float32 split products whose sum is the value).
+A part's product that is waiting to be added to the residual stream ("delta") is a tensor
+dt [T, E], or None when the part has added it into ``ctx.residual`` (the float32 residual
+stream, set by the block around the calls) itself.
 
 ``Mixer.forward(x, ctx, cache) -> delta``
     x dt [T, E] is the normalised input.  ``cache`` is the mixer's own ``LayerCache`` (its

@@ -23,6 +23,9 @@ class PreNormBlock:
         ws = ctx.workspace
         normed = ws.get("block.normed", (ws.max_tokens, hidden.resid.shape[1]), self.mixer.dtype)
         self.norm_mixer.forward(hidden.resid, hidden.delta, normed, T)
+        # A part may add its product into the residual stream itself and return None.
+        ctx.residual = hidden.resid
         mixed = self.mixer.forward(normed, ctx, cache)
         self.norm_feed_forward.forward(hidden.resid, mixed, normed, T)
         hidden.delta = self.feed_forward.forward(normed, ctx)
+        ctx.residual = None

@@ -5,7 +5,7 @@ rounds to the model dtype between the two)."""
 from __future__ import annotations
 
 from ..ops import kernels
-from ..ops.linear import linear, linear_split, split_scratch, swiglu_linear, use_tensor_core_kernel
+from ..ops.linear import linear, swiglu_linear, use_tensor_core_kernel
 from .base import FeedForward
 from .registry import register_part
 
@@ -25,9 +25,14 @@ class SwiGLU(FeedForward):
         act = ws.get("swiglu.act", (ws.max_tokens, self.intermediate_size), self.dtype)
         if use_tensor_core_kernel(x, self.w_gate_up, T) and use_tensor_core_kernel(act, self.w_down, T):
             # Few tokens: SiLU(gate) * up in the projection's epilogue, then the down projection
-            # as split products that the next norm sums into the residual stream.
+            # added straight into the float32 residual stream.
             swiglu_linear(x, self.w_gate_up, act, T, ctx.status)
-            return linear_split(act, self.w_down, split_scratch(ws, self.hidden_size), T, ctx.status)
+            if ctx.residual is not None:
+                linear(act, self.w_down, None, ctx.residual, T, status=ctx.status, accumulate=True)
+                return None
+            out = ws.get("feed_forward.out", (ws.max_tokens, self.hidden_size), self.dtype)
+            linear(act, self.w_down, None, out, T, status=ctx.status)
+            return out
         gate_up = ws.get("swiglu.gate_up", (ws.max_tokens, 2 * self.intermediate_size), self.dtype)
         linear(x, self.w_gate_up, None, gate_up, T)
         kernels.swiglu(gate_up, act, T)

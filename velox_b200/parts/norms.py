@@ -3,7 +3,6 @@ src/decoder_layer.py:49,54)."""
 from __future__ import annotations
 
 from ..ops import kernels
-from ..ops.linear import Partials
 from .base import Norm
 from .registry import register_part
 
@@ -19,9 +18,5 @@ class RMSNorm(Norm):
         self.weight = self.expect("weight", (self.size,))
 
     def forward(self, resid, delta, out, num_rows, rows=None, write_resid=True):
-        if isinstance(delta, Partials):
-            kernels.add_rmsnorm(resid, None, self.weight, self.eps, out, num_rows, rows, write_resid,
-                                partials=delta.data, num_partials=delta.count)
-        else:
-            kernels.add_rmsnorm(resid, delta, self.weight, self.eps, out, num_rows, rows, write_resid)
+        kernels.add_rmsnorm(resid, delta, self.weight, self.eps, out, num_rows, rows, write_resid)
         return out

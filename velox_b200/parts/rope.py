@@ -4,8 +4,7 @@
 theta^(-2i/R)`` (src/rope.py:45-56) and the rotate-half form ``lo' = lo*cos - hi*sin``,
 ``hi' = lo*sin + hi*cos`` on the two halves of the first R dims of every head
 (src/rope_inplace.py:25-47).  ``none`` rotates nothing.  Both write k and v into the paged
-cache in the same kernel that rotates, and both can take the q|k|v row as the float32 split
-products of the projection plus its bias instead of a finished buffer.
+cache in the same kernel that rotates.
 """
 from __future__ import annotations
 
@@ -38,13 +37,10 @@ class RotaryHalf(PositionEncoding):
         self.cos = angles.cos().to(device).contiguous()
         self.sin = angles.sin().to(device).contiguous()
 
-    def rotate_and_store(self, qkv, ctx, slots, k_cache, v_cache, num_heads, num_kv_heads,
-                         partials=None, bias=None):
+    def rotate_and_store(self, qkv, ctx, slots, k_cache, v_cache, num_heads, num_kv_heads):
         kernels.rope_cache_write(
             qkv, ctx.positions, self.cos, self.sin, slots, k_cache, v_cache, ctx.num_tokens,
             num_heads, num_kv_heads, self.head_dim, self.rotary_dim, ctx.status,
-            partials=None if partials is None else partials.data,
-            num_partials=0 if partials is None else partials.count, bias=bias,
         )
 
 
@@ -54,11 +50,8 @@ class NoPosition(PositionEncoding):
         super().__init__(params, weights, dtype, device)
         self.head_dim = int(params["head_dim"])
 
-    def rotate_and_store(self, qkv, ctx, slots, k_cache, v_cache, num_heads, num_kv_heads,
-                         partials=None, bias=None):
+    def rotate_and_store(self, qkv, ctx, slots, k_cache, v_cache, num_heads, num_kv_heads):
         kernels.rope_cache_write(
             qkv, ctx.positions, None, None, slots, k_cache, v_cache, ctx.num_tokens,
             num_heads, num_kv_heads, self.head_dim, 0, ctx.status,
-            partials=None if partials is None else partials.data,
-            num_partials=0 if partials is None else partials.count, bias=bias,
         )
