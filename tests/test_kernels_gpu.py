@@ -197,7 +197,7 @@ def plain_paged_attention(q, k_all, v_all, ctx, scale, window):
 
 
 def run_attention_case(k, dtype, H, G, D, P, seqs, window=None, seed=0, min_split_keys=256,
-                       target_ctas=296, spike=None):
+                       target_ctas=296, spike=None, fused_merge=True):
     """seqs: list of (q_len, ctx_len).  Returns (got, want) as float64 [T, H, D]."""
     from velox_b200.ops import attention_plan as ap
 
@@ -248,9 +248,16 @@ def run_attention_case(k, dtype, H, G, D, P, seqs, window=None, seed=0, min_spli
     partial_o = torch.zeros(max(plan.partial_rows, 1) * D, device="cuda")
     partial_lse = torch.zeros(max(plan.partial_rows, 1), device="cuda")
     args = (qkv.cuda(), out, k_cache.cuda(), v_cache.cuda(), tables.cuda(), dev(q_start), dev(q_lens), dev(kv_lens))
+    fused = fused_merge and dtype != torch.float32 and len(plan.merge_items) > 0
+    counters = torch.zeros(max(1, len(plan.merge_items) * G), dtype=torch.int32, device="cuda") if fused else None
+    merge_dev = dev(plan.merge_items) if fused else None
     for kind, items in plan.items.items():
-        k.attention(kind, *args, dev(items), len(items), partial_o, partial_lse, H, G, D, window, 1 / math.sqrt(D))
-    if len(plan.merge_items):
+        k.attention(kind, *args, dev(items), len(items), partial_o, partial_lse, H, G, D, window, 1 / math.sqrt(D),
+                    merge_items=merge_dev, split_counters=counters)
+    if fused:
+        torch.cuda.synchronize()
+        assert int(counters.abs().sum()) == 0  # the last split of every item put its counter back
+    elif len(plan.merge_items):
         k.attention_merge(out, dev(q_start), dev(plan.merge_items), len(plan.merge_items), partial_o,
                           partial_lse, H, G, D, max_rows=64)
     torch.cuda.synchronize()
@@ -296,11 +303,13 @@ def test_attention_window(k, dtype, H, G, D, P, window):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,G,D,P", [(4, 2, 16, 4), (12, 2, 128, 16), (6, 2, 80, 16)])
-def test_attention_split_key_ranges(k, dtype, H, G, D, P):
-    # Long contexts with few rows: the key range is cut into many splits and merged.
-    seqs = [(1, 1500), (1, 700), (2, 1023), (3, 64)]
+@pytest.mark.parametrize("fused_merge", [True, False])
+def test_attention_split_key_ranges(k, dtype, H, G, D, P, fused_merge):
+    # Long contexts with few rows: the key range is cut into many splits and merged, by the
+    # last split to finish (bfloat16) or by the merge kernel.
+    seqs = [(1, 1500), (1, 700), (2, 1023), (3, 64), (70, 900)]
     got, want, plan = run_attention_case(k, dtype, H, G, D, P, seqs, seed=5, min_split_keys=64,
-                                         target_ctas=10_000)
+                                         target_ctas=10_000, fused_merge=fused_merge)
     assert len(plan.merge_items) > 0 and plan.partial_rows > 0
     err = (got - want).abs().max().item()
     assert err <= _attn_tol(dtype) * want.abs().max().item(), err

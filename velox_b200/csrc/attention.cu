@@ -15,10 +15,12 @@
 // length 1.  When a key range is split, every split writes normalised partial rows and their
 // log-sum-exp to scratch and a merge kernel combines them.
 //
-// Item layout, int32[8]: {seq, row_begin, row_count, kv_begin, kv_end, partial_base, -, -}.
+// Item layout, int32[8]:
+//   {seq, row_begin, row_count, kv_begin, kv_end, partial_base, merge_index, num_splits}.
 //   seq < 0: the item is padding and does nothing.
 //   partial_base < 0: the item covers every key its rows may see and writes the output itself.
-//   otherwise partial rows go to partial_base + kv_head * row_count + r.
+//   otherwise partial rows go to partial_base + kv_head * row_count + r, and merge_index names
+//   the merge item that lists all splits of the same rows.
 // Visibility of key n to a row whose token is at absolute position pos:
 //   kv_begin <= n < kv_end, n <= pos, and n > pos - window when window > 0.
 // Key tiles start at multiples of the tile width from position 0, whatever kv_begin is, so the
@@ -53,6 +55,10 @@ struct AttnArgs {
   const int* items;         // [n, 8]
   float* partial_o;         // [rows, D]
   float* partial_lse;       // [rows], log2 units
+  // Fused merge (bf16 families): when a split item is done it bumps the counter of its
+  // (merge item, KV head); the CTA that brings it to the number of splits merges them all.
+  const int* merge_items;   // [m, 8] or null
+  int* split_counters;      // [m * G], zero between steps; null: a separate kernel merges
   int q_stride, out_stride, table_stride;
   int num_kv_heads, group, page_size, window;
   float scale_log2;  // softmax scale * log2(e)
@@ -267,35 +273,32 @@ __device__ __forceinline__ void load_q_tile(const AttnArgs& a, __nv_bfloat16* q_
 constexpr int TABLE_CAP = 1024;
 
 // Loads keys [n0, n0 + 64) of one KV head into k_s / v_s; rows at or past kv_end are zeroed.
-// Two threads share a key row (128 threads, 64 rows).
+// Consecutive threads copy consecutive 16-byte chunks of a key row, so a warp's request covers
+// whole rows (a row of one KV head is D * 2 contiguous bytes).
 __device__ __forceinline__ void load_kv_tile(const AttnArgs& a, __nv_bfloat16* k_s,
                                              __nv_bfloat16* v_s, const int* table,
                                              const int* table_s, int first_block, int n0,
                                              int kv_end, int kvh) {
-  constexpr int CH = D / 8;       // 16-byte chunks per row
-  constexpr int HALF_CH = CH / 2;  // chunks per thread
-  const int j = threadIdx.x >> 1, side = threadIdx.x & 1;
-  const int n = n0 + j;
-  __nv_bfloat16* kd = k_s + j * B_LD + side * HALF_CH * 8;
-  __nv_bfloat16* vd = v_s + j * B_LD + side * HALF_CH * 8;
-  if (n < kv_end) {
-    const int block = n / a.page_size;
-    const int local = block - first_block;
-    const int page = local < TABLE_CAP ? table_s[local] : table[block];
-    const size_t off = (((size_t)page * a.page_size + (n - block * a.page_size)) * a.num_kv_heads + kvh) * D +
-                       side * HALF_CH * 8;
-    const __nv_bfloat16* ksrc = (const __nv_bfloat16*)a.k_cache + off;
-    const __nv_bfloat16* vsrc = (const __nv_bfloat16*)a.v_cache + off;
-#pragma unroll
-    for (int c = 0; c < HALF_CH; ++c) {
-      cp_async16(kd + c * 8, ksrc + c * 8);
-      cp_async16(vd + c * 8, vsrc + c * 8);
-    }
-  } else {
-#pragma unroll
-    for (int c = 0; c < HALF_CH; ++c) {
-      *reinterpret_cast<uint4*>(kd + c * 8) = make_uint4(0u, 0u, 0u, 0u);
-      *reinterpret_cast<uint4*>(vd + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+  constexpr int CH = D / 8;  // 16-byte chunks per row
+  const __nv_bfloat16* kc = (const __nv_bfloat16*)a.k_cache;
+  const __nv_bfloat16* vc = (const __nv_bfloat16*)a.v_cache;
+#pragma unroll 4
+  for (int idx = threadIdx.x; idx < B_BN * CH; idx += 128) {
+    const int j = idx / CH, c = idx - j * CH;
+    const int n = n0 + j;
+    __nv_bfloat16* kd = k_s + j * B_LD + c * 8;
+    __nv_bfloat16* vd = v_s + j * B_LD + c * 8;
+    if (n < kv_end) {
+      const int block = n / a.page_size;
+      const int local = block - first_block;
+      const int page = local < TABLE_CAP ? table_s[local] : table[block];
+      const size_t off =
+          (((size_t)page * a.page_size + (n - block * a.page_size)) * a.num_kv_heads + kvh) * D + c * 8;
+      cp_async16(kd, kc + off);
+      cp_async16(vd, vc + off);
+    } else {
+      *reinterpret_cast<uint4*>(kd) = make_uint4(0u, 0u, 0u, 0u);
+      *reinterpret_cast<uint4*>(vd) = make_uint4(0u, 0u, 0u, 0u);
     }
   }
 }
@@ -432,6 +435,97 @@ __device__ __forceinline__ void store_rows(const AttnArgs& a, const float (&o)[D
   }
 }
 
+// =============================================================================================
+// Merge of split key ranges.  Merge item, int32[8]:
+//   {seq, row_begin, row_count, first_partial_base, num_splits, split_stride, -, -}
+// split s of the item wrote its rows at first_partial_base + s * split_stride.
+// merge_row is called by all threads of a block for one row r of an item.
+// =============================================================================================
+template <typename T>
+__device__ __forceinline__ void merge_row(const AttnArgs& a, const int* item, int kvh, int r,
+                                          float* weight_s, float* denom_s) {
+  const int seq = item[0], row_begin = item[1], row_count = item[2], first = item[3],
+            splits = item[4], stride = item[5];
+  const size_t base = (size_t)first + (size_t)kvh * row_count + r;
+  // Weights of the splits from their log-sum-exps (warp 0), then every thread sums its dims.
+  if (threadIdx.x < 32) {
+    float mt = -CUDART_INF_F;
+    for (int s = threadIdx.x; s < splits; s += 32)
+      mt = fmaxf(mt, __ldcg(&a.partial_lse[base + (size_t)s * stride]));
+    mt = warp_max(mt);
+    const float m_safe = mt == -CUDART_INF_F ? 0.f : mt;
+    float den = 0.f;
+    for (int s = threadIdx.x; s < splits; s += 32) {
+      const float lse = __ldcg(&a.partial_lse[base + (size_t)s * stride]);
+      const float w = lse == -CUDART_INF_F ? 0.f : exp2f(lse - m_safe);
+      weight_s[s] = w;
+      den += w;
+    }
+    den = warp_sum(den);
+    if (threadIdx.x == 0) *denom_s = den;
+  }
+  __syncthreads();
+  const float den = *denom_s;
+  const int row = row_begin + r;
+  const int tok = row / a.group, hg = row - tok * a.group;
+  T* dst = (T*)a.out + (size_t)(a.q_start[seq] + tok) * a.out_stride +
+           (size_t)(kvh * a.group + hg) * D;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float acc = 0.f;
+    int s = 0;
+    for (; s + 4 <= splits; s += 4) {
+      const float o0 = __ldcg(&a.partial_o[(base + (size_t)s * stride) * D + d]);
+      const float o1 = __ldcg(&a.partial_o[(base + (size_t)(s + 1) * stride) * D + d]);
+      const float o2 = __ldcg(&a.partial_o[(base + (size_t)(s + 2) * stride) * D + d]);
+      const float o3 = __ldcg(&a.partial_o[(base + (size_t)(s + 3) * stride) * D + d]);
+      acc += weight_s[s] * o0;
+      acc += weight_s[s + 1] * o1;
+      acc += weight_s[s + 2] * o2;
+      acc += weight_s[s + 3] * o3;
+    }
+    for (; s < splits; ++s)
+      acc += weight_s[s] * __ldcg(&a.partial_o[(base + (size_t)s * stride) * D + d]);
+    dst[d] = from_float<T>(den > 0.f ? acc / den : 0.f);
+  }
+  __syncthreads();  // weight_s is reused for the next row
+}
+
+template <typename T>
+__global__ void attn_merge_kernel(AttnArgs a, const int* __restrict__ merge_items) {
+  __shared__ float weight_s[ATTN_MAX_SPLITS];
+  __shared__ float denom_s;
+  VX_TRACE_SCOPE(22);
+  allow_dependents();
+  grid_dependency_wait();
+  const int* item = merge_items + (size_t)blockIdx.x * 8;
+  if (item[0] < 0) return;
+  const int r = blockIdx.z;  // one block per row of the tile
+  if (r >= item[2]) return;
+  merge_row<T>(a, item, blockIdx.y, r, weight_s, &denom_s);
+}
+
+// Called by every thread of a CTA after it has written the partial rows of a split item.
+// Returns after the merge if this CTA was the last of its splits to finish.
+__device__ __forceinline__ void finish_split(const AttnArgs& a, int merge_index, int num_splits,
+                                             int kvh) {
+  __shared__ float weight_s[ATTN_MAX_SPLITS];
+  __shared__ float denom_s;
+  __shared__ int last_s;
+  __threadfence();  // this thread's partial rows are visible before the counter moves
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* counter = a.split_counters + (size_t)merge_index * a.num_kv_heads + kvh;
+    const int seen = atomicAdd(counter, 1);
+    last_s = seen == num_splits - 1;
+    if (last_s) *counter = 0;  // ready for the next step
+  }
+  __syncthreads();
+  if (!last_s) return;
+  __threadfence();
+  const int* item = a.merge_items + (size_t)merge_index * 8;
+  for (int r = 0; r < item[2]; ++r) merge_row<__nv_bfloat16>(a, item, kvh, r, weight_s, &denom_s);
+}
+
 template <int N>
 __device__ __forceinline__ void cp_async_wait_group() {
   asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
@@ -450,13 +544,17 @@ __global__ void __launch_bounds__(128) attn_bf16_kernel(AttnArgs a) {
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   __nv_bfloat16* kv_s = q_s + ROWS * B_LD;  // stage st: K at kv_s + st * 2 * TILE, V after it
 
+  VX_TRACE_SCOPE(NARROW ? 21 : 20);
   allow_dependents();
   grid_dependency_wait();
+  VX_TRACE_MARK(0);
   const int* item = a.items + (size_t)blockIdx.x * 8;
   const int seq = item[0];
   if (seq < 0) return;
   const int row_begin = item[1], row_count = item[2];
   const int kv_begin = item[3], kv_end = item[4], partial_base = item[5];
+  const int merge_index = item[6], num_splits = item[7];
+  const bool fused_merge = partial_base >= 0 && a.split_counters != nullptr;
   const int kvh = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int q_start = a.q_start[seq], q_len = a.q_len[seq], kv_len = a.kv_len[seq];
@@ -474,6 +572,7 @@ __global__ void __launch_bounds__(128) attn_bf16_kernel(AttnArgs a) {
   }
   load_q_tile<ROWS>(a, q_s, q_start, row_begin, row_count, kvh);
   __syncthreads();
+  VX_TRACE_MARK(1);
 
   float o[D / 8][4];
 #pragma unroll
@@ -507,6 +606,7 @@ __global__ void __launch_bounds__(128) attn_bf16_kernel(AttnArgs a) {
     cp_async_commit();
     cp_async_wait_group<STAGES - 1>();  // the tile of this iteration has landed
     __syncthreads();
+    if (n0 == n_first) VX_TRACE_MARK(2);
     const __nv_bfloat16* k_s = kv_s + stage * 2 * TILE;
     const __nv_bfloat16* v_s = k_s + TILE;
     float s[NT][4];
@@ -518,8 +618,10 @@ __global__ void __launch_bounds__(128) attn_bf16_kernel(AttnArgs a) {
     fill = fill + 1 == STAGES ? 0 : fill + 1;
   }
 
+  VX_TRACE_MARK(3);
   if (!NARROW) {
     store_rows(a, o, m, l, row0, row_begin, row_count, q_start, kvh, partial_base, lane);
+    if (fused_merge) finish_split(a, merge_index, num_splits, kvh);
     return;
   }
 
@@ -570,81 +672,23 @@ __global__ void __launch_bounds__(128) attn_bf16_kernel(AttnArgs a) {
       if (d == 0) a.partial_lse[prow] = lt > 0.f ? mt + log2f(lt) : -CUDART_INF_F;
     }
   }
+  if (fused_merge) finish_split(a, merge_index, num_splits, kvh);
 }
 
 constexpr int WIDE_STAGES = 2;
 constexpr int NARROW_STAGES = 3;
 
-// =============================================================================================
-// Merge of split key ranges.  Merge item, int32[8]:
-//   {seq, row_begin, row_count, first_partial_base, num_splits, split_stride, -, -}
-// split s of the item wrote its rows at first_partial_base + s * split_stride.
-// =============================================================================================
-template <typename T>
-__global__ void attn_merge_kernel(AttnArgs a, const int* __restrict__ merge_items) {
-  __shared__ float weight_s[ATTN_MAX_SPLITS];
-  __shared__ float denom_s;
-  allow_dependents();
-  grid_dependency_wait();
-  const int* item = merge_items + (size_t)blockIdx.x * 8;
-  const int seq = item[0];
-  if (seq < 0) return;
-  const int row_begin = item[1], row_count = item[2], first = item[3], splits = item[4],
-            stride = item[5];
-  const int kvh = blockIdx.y;
-  const int r = blockIdx.z;  // one block per row of the tile
-  if (r >= row_count) return;
-  const size_t base = (size_t)first + (size_t)kvh * row_count + r;
-
-  // Weights of the splits from their log-sum-exps (warp 0), then every thread sums its dims.
-  if (threadIdx.x < 32) {
-    float mt = -CUDART_INF_F;
-    for (int s = threadIdx.x; s < splits; s += 32)
-      mt = fmaxf(mt, a.partial_lse[base + (size_t)s * stride]);
-    mt = warp_max(mt);
-    const float m_safe = mt == -CUDART_INF_F ? 0.f : mt;
-    float den = 0.f;
-    for (int s = threadIdx.x; s < splits; s += 32) {
-      const float lse = a.partial_lse[base + (size_t)s * stride];
-      const float w = lse == -CUDART_INF_F ? 0.f : exp2f(lse - m_safe);
-      weight_s[s] = w;
-      den += w;
-    }
-    den = warp_sum(den);
-    if (threadIdx.x == 0) denom_s = den;
-  }
-  __syncthreads();
-  const float den = denom_s;
-  const int row = row_begin + r;
-  const int tok = row / a.group, hg = row - tok * a.group;
-  T* dst = (T*)a.out + (size_t)(a.q_start[seq] + tok) * a.out_stride +
-           (size_t)(kvh * a.group + hg) * D;
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float acc = 0.f;
-    int s = 0;
-    for (; s + 4 <= splits; s += 4) {
-      const float o0 = a.partial_o[(base + (size_t)s * stride) * D + d];
-      const float o1 = a.partial_o[(base + (size_t)(s + 1) * stride) * D + d];
-      const float o2 = a.partial_o[(base + (size_t)(s + 2) * stride) * D + d];
-      const float o3 = a.partial_o[(base + (size_t)(s + 3) * stride) * D + d];
-      acc += weight_s[s] * o0;
-      acc += weight_s[s + 1] * o1;
-      acc += weight_s[s + 2] * o2;
-      acc += weight_s[s + 3] * o3;
-    }
-    for (; s < splits; ++s) acc += weight_s[s] * a.partial_o[(base + (size_t)s * stride) * D + d];
-    dst[d] = from_float<T>(den > 0.f ? acc / den : 0.f);
-  }
-}
-
 }  // namespace vx
 
 using namespace vx;
 
+VX_TRACE_API(vx_attn)
+
 static AttnArgs make_args(const void* q, void* out, const void* k_cache, const void* v_cache,
                           const int* block_tables, const int* q_start, const int* q_len,
                           const int* kv_len, const int* items, float* partial_o,
-                          float* partial_lse, int q_stride, int out_stride, int table_stride,
+                          float* partial_lse, const int* merge_items, int* split_counters,
+                          int q_stride, int out_stride, int table_stride,
                           int num_kv_heads, int group, int page_size, int window,
                           float softmax_scale) {
   AttnArgs a;
@@ -659,6 +703,8 @@ static AttnArgs make_args(const void* q, void* out, const void* k_cache, const v
   a.items = items;
   a.partial_o = partial_o;
   a.partial_lse = partial_lse;
+  a.merge_items = merge_items;
+  a.split_counters = split_counters;
   a.q_stride = q_stride;
   a.out_stride = out_stride;
   a.table_stride = table_stride;
@@ -679,12 +725,16 @@ VX_API int vx_attn_tile_rows(int kind) { return kind == 1 ? 64 : 16; }
 VX_API int vx_attention(int kind, const void* q, void* out, const void* k_cache,
                         const void* v_cache, const int* block_tables, const int* q_start,
                         const int* q_len, const int* kv_len, const int* items, int num_items,
-                        float* partial_o, float* partial_lse, int q_stride, int out_stride,
-                        int table_stride, int num_kv_heads, int group, int page_size, int window,
+                        float* partial_o, float* partial_lse, const int* merge_items,
+                        int* split_counters, int q_stride, int out_stride, int table_stride,
+                        int num_kv_heads, int group, int page_size, int window,
                         float softmax_scale, cudaStream_t stream) {
   if (num_items <= 0) return 0;
+  // The float32 family leaves merging to the merge kernel.
+  if (kind == 0) split_counters = nullptr;
   const AttnArgs a = make_args(q, out, k_cache, v_cache, block_tables, q_start, q_len, kv_len,
-                               items, partial_o, partial_lse, q_stride, out_stride, table_stride,
+                               items, partial_o, partial_lse, merge_items, split_counters,
+                               q_stride, out_stride, table_stride,
                                num_kv_heads, group, page_size, window, softmax_scale);
   const dim3 grid(num_items, num_kv_heads);
   if (kind == 0) {
@@ -733,7 +783,7 @@ VX_API int vx_attention_merge(int dtype, void* out, const int* q_start, const in
   if (num_items <= 0 || max_rows <= 0) return 0;
   AttnArgs a = make_args(nullptr, out, nullptr, nullptr, nullptr, q_start, nullptr, nullptr,
                          nullptr, const_cast<float*>(partial_o), const_cast<float*>(partial_lse),
-                         0, out_stride, 0, num_kv_heads, group, 1, 0, 1.0f);
+                         merge_items, nullptr, 0, out_stride, 0, num_kv_heads, group, 1, 0, 1.0f);
   const dim3 grid(num_items, num_kv_heads, max_rows);
   const int threads = D >= 128 ? 128 : (D >= 64 ? 64 : 32);
   if (dtype == VX_DTYPE_F32)

@@ -16,6 +16,7 @@ from __future__ import annotations
 import ctypes
 import hashlib
 import os
+import re
 import shutil
 import subprocess
 import sys
@@ -29,6 +30,9 @@ _SRC_DIR = os.path.dirname(os.path.abspath(__file__))
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo"]
+# VELOX_B200_TRACE=1 builds (and loads) libraries whose kernels record a timeline.
+if os.environ.get("VELOX_B200_TRACE") == "1":
+    COMMON_FLAGS = COMMON_FLAGS + ["-DVX_TRACE"]
 
 CORE_SOURCES = ("core.cu", "sampling.cu", "gemm_bf16.cu")
 ATTENTION_SOURCES = ("attention.cu",)
@@ -129,6 +133,8 @@ def build_library(name: str, sources: Sequence[str], defines: Sequence[str] = ()
     """Build (or find) the shared library and return its path."""
     nvcc = find_nvcc()
     version = _nvcc_version(nvcc)
+    if "-DVX_TRACE" in COMMON_FLAGS:
+        name = name + "_trace"
     key = _build_key(sources, defines, version)
     out_dir = build_dir()
     target = os.path.join(out_dir, f"libvelox_{name}_{key}.so")
@@ -160,9 +166,9 @@ def build_library(name: str, sources: Sequence[str], defines: Sequence[str] = ()
             raise BuildError(f"link failed:\n{' '.join(link)}\n{proc.stdout}\n{proc.stderr}")
         os.replace(partial, target)
         # Older builds of the same library (other source hashes) are of no use any more.
-        prefix = f"libvelox_{name}_"
+        pattern = re.compile(re.escape(f"libvelox_{name}_") + r"[0-9a-f]{16}\.so")
         for stale in os.listdir(out_dir):
-            if stale.startswith(prefix) and stale.endswith(".so") and stale != os.path.basename(target):
+            if pattern.fullmatch(stale) and stale != os.path.basename(target):
                 try:
                     os.remove(os.path.join(out_dir, stale))
                 except OSError:

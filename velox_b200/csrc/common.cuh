@@ -110,4 +110,79 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   return cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Timeline tracing, compiled in with -DVX_TRACE only (VELOX_B200_TRACE=1 at build time).  Every
+// CTA appends (kernel id, grid size, block, SM, start ns, end ns) to a buffer the host set up;
+// the host groups the events by launch.  A build without the flag contains none of this.
+// ---------------------------------------------------------------------------------------------
+#ifdef VX_TRACE
+struct TraceEvent {
+  unsigned long long t0, t1;
+  int kernel, grid, block, sm;
+  unsigned long long marks[4];  // optional points inside the kernel, 0 if never reached
+};
+// One buffer per translation unit (each .cu file is its own device module).
+static __device__ TraceEvent* g_trace_events = nullptr;
+static __device__ unsigned int g_trace_capacity = 0;
+static __device__ unsigned int g_trace_cursor = 0;
+
+__device__ __forceinline__ unsigned long long trace_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+struct TraceScope {
+  unsigned long long t0;
+  unsigned long long marks[4];
+  int kernel;
+  __device__ __forceinline__ explicit TraceScope(int id) : t0(0), kernel(id) {
+    marks[0] = marks[1] = marks[2] = marks[3] = 0;
+    if (threadIdx.x == 0) t0 = trace_now();
+  }
+  __device__ __forceinline__ void mark(int i) {
+    if (threadIdx.x == 0) marks[i] = trace_now();
+  }
+  __device__ __forceinline__ ~TraceScope() {
+    if (threadIdx.x != 0 || g_trace_events == nullptr) return;
+    const unsigned int slot = atomicAdd(&g_trace_cursor, 1u);
+    if (slot >= g_trace_capacity) return;
+    unsigned int sm;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
+    TraceEvent e;
+    e.t0 = t0;
+    e.t1 = trace_now();
+    e.kernel = kernel;
+    e.grid = (int)(gridDim.x * gridDim.y * gridDim.z);
+    e.block = (int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));
+    e.sm = (int)sm;
+    for (int i = 0; i < 4; ++i) e.marks[i] = marks[i];
+    g_trace_events[slot] = e;
+  }
+};
+#define VX_TRACE_SCOPE(id) vx::TraceScope vx_trace_scope_(id)
+#define VX_TRACE_MARK(i) vx_trace_scope_.mark(i)
+#else
+#define VX_TRACE_SCOPE(id)
+#define VX_TRACE_MARK(i)
+#endif
+
 }  // namespace vx
+
+#ifdef VX_TRACE
+// Host side of the trace: point this library's kernels at a device buffer of 64-byte events.
+#define VX_TRACE_API(prefix)                                                                      \
+  VX_API int prefix##_trace_setup(void* events, unsigned int capacity) {                          \
+    vx::TraceEvent* p = (vx::TraceEvent*)events;                                                  \
+    unsigned int zero = 0;                                                                        \
+    cudaError_t e = cudaMemcpyToSymbol(vx::g_trace_events, &p, sizeof(p));                        \
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(vx::g_trace_capacity, &capacity, sizeof(capacity)); \
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(vx::g_trace_cursor, &zero, sizeof(zero));         \
+    return (int)e;                                                                                \
+  }                                                                                               \
+  VX_API int prefix##_trace_count(unsigned int* count) {                                          \
+    return (int)cudaMemcpyFromSymbol(count, vx::g_trace_cursor, sizeof(unsigned int));            \
+  }
+#else
+#define VX_TRACE_API(prefix)
+#endif

@@ -20,6 +20,7 @@ namespace vx {
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                              float* __restrict__ resid, int hidden, int vocab, int* status) {
+  VX_TRACE_SCOPE(1);
   allow_dependents();
   grid_dependency_wait();
   const int t = blockIdx.x;
@@ -49,6 +50,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restric
                                    T* __restrict__ out, const int* __restrict__ rows, int hidden,
                                    int write_resid) {
   __shared__ float scratch[32];
+  VX_TRACE_SCOPE(2);
   allow_dependents();
   grid_dependency_wait();
   const int o = blockIdx.x;
@@ -57,15 +59,17 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restric
   const T* d = delta ? delta + (size_t)r * hidden : nullptr;
   auto value = [&](int i) { return d ? x[i] + to_float(d[i]) : x[i]; };
 
-  // A row of up to 8 elements per thread is read once and kept in registers.
+  // A row of up to 8 elements per thread is read once and kept in registers, and so is the
+  // norm weight: nothing is fetched after the reduction.
   const bool cached = hidden <= NORM_MAX_PER_THREAD * (int)blockDim.x;
-  float vals[NORM_MAX_PER_THREAD];
+  float vals[NORM_MAX_PER_THREAD], wts[NORM_MAX_PER_THREAD];
   float ss = 0.f;
   if (cached) {
 #pragma unroll
     for (int j = 0; j < NORM_MAX_PER_THREAD; ++j) {
       const int i = threadIdx.x + j * blockDim.x;
       vals[j] = i < hidden ? value(i) : 0.f;
+      wts[j] = i < hidden ? weight[i] : 0.f;
     }
 #pragma unroll
     for (int j = 0; j < NORM_MAX_PER_THREAD; ++j) ss += vals[j] * vals[j];
@@ -84,7 +88,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restric
       const int i = threadIdx.x + j * blockDim.x;
       if (i < hidden) {
         if (write_resid) x[i] = vals[j];
-        y[i] = from_float<T>(vals[j] * inv * weight[i]);
+        y[i] = from_float<T>(vals[j] * inv * wts[j]);
       }
     }
   } else {
@@ -112,6 +116,7 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, const int* __restri
                                         T* __restrict__ v_cache, int H, int G, int D, int rot,
                                         int max_pos, long long num_slots, int write_cache,
                                         int* status) {
+  VX_TRACE_SCOPE(3);
   allow_dependents();
   grid_dependency_wait();
   const int t = blockIdx.x;
@@ -252,6 +257,8 @@ __global__ void cast_bf16_to_f32_kernel(const __nv_bfloat16* __restrict__ in,
 // Launchers
 // =============================================================================================
 using namespace vx;
+
+VX_TRACE_API(vx_core)
 
 VX_API int vx_embed(const void* table, int dtype, const int* ids, float* resid, int num_tokens,
                     int hidden, int vocab, int* status, cudaStream_t stream) {

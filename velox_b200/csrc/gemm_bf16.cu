@@ -191,8 +191,10 @@ __device__ __forceinline__ uint32_t cluster_rank() {
 __device__ __forceinline__ float load_peer_shared(uint32_t local_addr, uint32_t rank) {
   uint32_t remote;
   float v;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  // Not volatile: the loads of one reduction are independent and may be in flight together.
+  // They are ordered after the cluster barrier by the barrier's own memory clobber.
+  asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote));
   return v;
 }
 
@@ -230,6 +232,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   __shared__ int epilogue_failed;
   __shared__ float swap_buf[64 * 33];
 
+  VX_TRACE_SCOPE(10 + g.mode);
   allow_dependents();
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -289,6 +292,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     };
     for (int i = 0; i < first_round; ++i) load_w(i);
     grid_dependency_wait();
+    VX_TRACE_MARK(0);
     for (int i = 0; i < first_round; ++i) load_x(i);
     for (int i = first_round; i < num_kb; ++i) {
       const int stage = i % S::STAGES;
@@ -384,9 +388,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   }
   __syncthreads();
+  VX_TRACE_MARK(1);
   if (clustered) {
     // Every CTA of the cluster has parked its partial tile.
     cluster_sync_all();
+    VX_TRACE_MARK(2);
     if (warp >= 2) {
       // This CTA sums the tokens [rank * BN / splits, (rank + 1) * BN / splits) of the tile over
       // all peers, in rank order, and writes them: a thread per output feature.
@@ -399,13 +405,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       for (int j = (int)rank * per_cta; j < ((int)rank + 1) * per_cta; ++j) {
         const int t = t0 + j;
         if (t >= g.T || n >= g.N) continue;
+        // All peers' values first (independent loads), then the sum in rank order.
+        float part[8];
+#pragma unroll
+        for (int peer = 0; peer < 8; ++peer)
+          part[peer] = peer < g.splits ? load_peer_shared(local + (uint32_t)j * 4u, (uint32_t)peer) : 0.f;
         float acc = 0.f;
-        for (int peer = 0; peer < g.splits; ++peer)
-          acc += load_peer_shared(local + (uint32_t)j * 4u, (uint32_t)peer);
+#pragma unroll
+        for (int peer = 0; peer < 8; ++peer) acc += part[peer];
         store_output(g, (size_t)t * g.ldy + n, acc + b);
       }
     }
     // No CTA may leave while a peer still reads its shared memory.
+    VX_TRACE_MARK(3);
     cluster_sync_all();
   }
   if (warp == 1) {
@@ -507,6 +519,8 @@ static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mw2, const CUte
 }  // namespace vx
 
 using namespace vx;
+
+VX_TRACE_API(vx_gemm)
 
 // Token-tile widths the kernel is built for.
 VX_API int vx_gemm_bf16_token_tile(int num_tokens) {

@@ -53,6 +53,8 @@ class DevicePlan:
     merge_items: Optional[torch.Tensor] = None
     num_merges: int = 0
     merge_rows: int = 16  # the most rows a merge item can have (height of the split tiles)
+    # Zeroed counters for the fused merge of the bfloat16 kernels; None: a merge kernel runs.
+    split_counters: Optional[torch.Tensor] = None
     partial_o: Optional[torch.Tensor] = None
     partial_lse: Optional[torch.Tensor] = None
 
@@ -170,6 +172,8 @@ class ModelRunner:
                     )
                 )
         self._signatures = model.attention_signatures()
+        # One counter per (merge item, KV head); the kernels leave them at zero.
+        self._split_counters = torch.zeros(1 << 16, dtype=torch.int32, device=self.device)
 
         self._host: List[Optional[torch.Tensor]] = [None, None]
         self._copied: List[Optional[torch.cuda.Event]] = [None, None]
@@ -371,6 +375,9 @@ class ModelRunner:
                 device_plan.merge_items = dev[offset : offset + shape[0] * 8].view(shape[0], 8)
                 device_plan.num_merges = shape[0]
                 device_plan.merge_rows = max(ap.TILE_ROWS[kind] for kind in entry)
+                needed = shape[0] * key[1][0]
+                if self.dtype != torch.float32 and needed <= self._split_counters.numel():
+                    device_plan.split_counters = self._split_counters
             if plan.partial_rows:
                 head_dim = max(self.model.head_dims())
                 device_plan.partial_o = self._scratch("attention.partial_o", plan.partial_rows * head_dim)

@@ -26,7 +26,8 @@ ITEM_WIDTH = 8
 
 @dataclass
 class AttentionPlan:
-    # kind -> int32 [n, 8] work items {seq, row_begin, row_count, kv_begin, kv_end, partial_base, 0, 0}
+    # kind -> int32 [n, 8] work items
+    # {seq, row_begin, row_count, kv_begin, kv_end, partial_base, merge index, number of splits}
     items: Dict[int, np.ndarray] = field(default_factory=dict)
     # int32 [m, 8] {seq, row_begin, row_count, first_partial_base, num_splits, split_stride, 0, 0}
     merge_items: np.ndarray = field(default_factory=lambda: np.zeros((0, ITEM_WIDTH), np.int32))
@@ -103,12 +104,13 @@ def plan_attention(
         num_key_tiles = -(-hi // KEY_TILE) - first_tile
         tiles_per_split = -(-num_key_tiles // splits)
         stride = opt.num_kv_heads * row_count
+        merge_index = len(merges)
         merges.append([seq, row_begin, row_count, partial_rows, splits, stride, 0, 0])
         for s in range(splits):
             begin = max(lo, (first_tile + s * tiles_per_split) * KEY_TILE)
             end = min(hi, (first_tile + (s + 1) * tiles_per_split) * KEY_TILE)
             end = max(end, begin)
-            out.append([seq, row_begin, row_count, begin, end, partial_rows, 0, 0])
+            out.append([seq, row_begin, row_count, begin, end, partial_rows, merge_index, splits])
             partial_rows += stride
 
     plan = AttentionPlan(partial_rows=partial_rows)

@@ -73,7 +73,7 @@ def attention_lib(head_dim: int):
     if lib is None:
         lib = build.load_attention(head_dim)
         lib.vx_attention.argtypes = [
-            _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _ptr, _ptr,
+            _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _ptr, _ptr, _ptr, _ptr,
             _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_f, _ptr,
         ]
         lib.vx_attention_merge.argtypes = [
@@ -331,8 +331,14 @@ def attention(
     head_dim: int,
     window: Optional[int],
     softmax_scale: float,
+    merge_items: Optional[torch.Tensor] = None,
+    split_counters: Optional[torch.Tensor] = None,
 ) -> None:
-    """Run ``num_items`` work items (see attention.cu for their layout) of one kernel family."""
+    """Run ``num_items`` work items (see attention.cu for their layout) of one kernel family.
+
+    With ``merge_items`` and ``split_counters`` (int32, zero, one per merge item and KV head)
+    the bfloat16 families merge split key ranges themselves: the last split to finish does it.
+    """
     want = torch.float32 if kind == ATTN_F32 else torch.bfloat16
     _need(q, want, "q")
     _need(out, want, "out")
@@ -348,11 +354,15 @@ def attention(
     if partial_o is not None:
         _need(partial_o, torch.float32, "partial_o")
         _need(partial_lse, torch.float32, "partial_lse")
+    if split_counters is not None:
+        _need(split_counters, torch.int32, "split_counters")
+        _need(merge_items, torch.int32, "merge_items")
     lib = attention_lib(head_dim)
     _check(
         lib.vx_attention(kind, _p(q), _p(out), _p(k_cache), _p(v_cache), _p(block_tables),
                          _p(q_start), _p(q_len), _p(kv_len), _p(items), num_items,
-                         _p(partial_o), _p(partial_lse), q.shape[1], out.shape[1],
+                         _p(partial_o), _p(partial_lse), _p(merge_items), _p(split_counters),
+                         q.shape[1], out.shape[1],
                          block_tables.shape[1], num_kv_heads, num_heads // num_kv_heads,
                          k_cache.shape[1], int(window or 0), float(softmax_scale), _stream()),
         "attention",

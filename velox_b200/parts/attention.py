@@ -76,8 +76,9 @@ class Attention(Mixer):
                 kind, qkv, attn, cache.k, cache.v, group.block_tables, ctx.q_start, ctx.q_len,
                 ctx.kv_len, items, count, plan.partial_o, plan.partial_lse, self.num_heads,
                 self.num_kv_heads, self.head_dim, self.window, self.softmax_scale,
+                merge_items=plan.merge_items, split_counters=plan.split_counters,
             )
-        if plan.num_merges:
+        if plan.num_merges and plan.split_counters is None:
             kernels.attention_merge(
                 attn, ctx.q_start, plan.merge_items, plan.num_merges, plan.partial_o,
                 plan.partial_lse, self.num_heads, self.num_kv_heads, self.head_dim,
