@@ -504,12 +504,59 @@ __global__ void attn_merge_kernel(AttnArgs a, const int* __restrict__ merge_item
   merge_row<T>(a, item, blockIdx.y, r, weight_s, &denom_s);
 }
 
+// One warp merges one row: lanes hold the splits' weights, then four dims each.
+__device__ __forceinline__ void merge_row_by_warp(const AttnArgs& a, const int* item, int kvh,
+                                                  int r, int lane) {
+  const int seq = item[0], row_begin = item[1], row_count = item[2], first = item[3],
+            splits = item[4], stride = item[5];
+  const size_t base = (size_t)first + (size_t)kvh * row_count + r;
+  // Up to 64 splits: lane holds splits lane and lane + 32.
+  float lse0 = lane < splits ? __ldcg(&a.partial_lse[base + (size_t)lane * stride]) : -CUDART_INF_F;
+  float lse1 = lane + 32 < splits ? __ldcg(&a.partial_lse[base + (size_t)(lane + 32) * stride])
+                                  : -CUDART_INF_F;
+  const float mt = warp_max(fmaxf(lse0, lse1));
+  const float m_safe = mt == -CUDART_INF_F ? 0.f : mt;
+  const float w0 = lse0 == -CUDART_INF_F ? 0.f : exp2f(lse0 - m_safe);
+  const float w1 = lse1 == -CUDART_INF_F ? 0.f : exp2f(lse1 - m_safe);
+  const float den = warp_sum(w0 + w1);
+  const int row = row_begin + r;
+  const int tok = row / a.group, hg = row - tok * a.group;
+  __nv_bfloat16* dst = (__nv_bfloat16*)a.out + (size_t)(a.q_start[seq] + tok) * a.out_stride +
+                       (size_t)(kvh * a.group + hg) * D;
+  // Every lane runs every iteration (the weights travel by shuffle); lanes past D only idle.
+  for (int d0 = 0; d0 < D; d0 += 128) {
+    const int d = d0 + lane * 4;
+    const bool active = d < D;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s0 = 0; s0 < splits; s0 += 8) {
+      float4 v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        v[i] = (active && s0 + i < splits)
+                   ? __ldcg(reinterpret_cast<const float4*>(&a.partial_o[(base + (size_t)(s0 + i) * stride) * D + d]))
+                   : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int s = s0 + i;
+        const float w = __shfl_sync(0xffffffffu, s < 32 ? w0 : w1, s & 31);
+        acc.x += w * v[i].x;
+        acc.y += w * v[i].y;
+        acc.z += w * v[i].z;
+        acc.w += w * v[i].w;
+      }
+    }
+    const float inv = den > 0.f ? 1.0f / den : 0.f;
+    if (active) {
+      *reinterpret_cast<__nv_bfloat162*>(dst + d) = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+      *reinterpret_cast<__nv_bfloat162*>(dst + d + 2) = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+    }
+  }
+}
+
 // Called by every thread of a CTA after it has written the partial rows of a split item.
-// Returns after the merge if this CTA was the last of its splits to finish.
+// The CTA that completes the splits of its (merge item, KV head) merges them: a warp per row.
 __device__ __forceinline__ void finish_split(const AttnArgs& a, int merge_index, int num_splits,
                                              int kvh) {
-  __shared__ float weight_s[ATTN_MAX_SPLITS];
-  __shared__ float denom_s;
   __shared__ int last_s;
   __threadfence();  // this thread's partial rows are visible before the counter moves
   __syncthreads();
@@ -523,7 +570,8 @@ __device__ __forceinline__ void finish_split(const AttnArgs& a, int merge_index,
   if (!last_s) return;
   __threadfence();
   const int* item = a.merge_items + (size_t)merge_index * 8;
-  for (int r = 0; r < item[2]; ++r) merge_row<__nv_bfloat16>(a, item, kvh, r, weight_s, &denom_s);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int r = warp; r < item[2]; r += (int)(blockDim.x >> 5)) merge_row_by_warp(a, item, kvh, r, lane);
 }
 
 template <int N>

@@ -5,10 +5,10 @@
 // With few tokens (decode) the tensor-core tile is still full, because its 128-row side is made
 // of weight rows; the kernel then streams W once at memory speed.  A projection with few output
 // tiles is split along K over a thread-block cluster (2, 4 or 8 CTAs): every CTA accumulates its
-// share of K in its own tensor memory, parks the partial tile in its shared memory, and after a
-// cluster barrier each CTA sums one slice of the tile over all peers through distributed shared
-// memory, in rank order, and writes it out.  No partial product touches global memory and the
-// order of the sums is fixed.
+// share of K in its own tensor memory and sends every token column of its partial tile to the
+// CTA that owns that column, by stores into the owner's shared memory (distributed shared
+// memory); after one cluster barrier each CTA sums what its peers sent, in rank order, and writes
+// its columns out.  No partial product touches global memory and the order of the sums is fixed.
 //
 //   warp 0, one lane : TMA producer.  cp.async.bulk.tensor 2-D tiles of W [128 x 64] and
 //                      X [BN x 64] into a ring of 128-byte-swizzled shared-memory stages.
@@ -176,8 +176,10 @@ struct GemmArgs {
   int splits;            // CTAs of the cluster that share one output tile (1: no cluster)
 };
 
-__device__ __forceinline__ void cluster_sync_all() {
+__device__ __forceinline__ void cluster_arrive() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
@@ -187,15 +189,11 @@ __device__ __forceinline__ uint32_t cluster_rank() {
   return rank;
 }
 
-// A float of a peer CTA's shared memory, at the same offset as `local_addr` here.
-__device__ __forceinline__ float load_peer_shared(uint32_t local_addr, uint32_t rank) {
+// Stores a float into a peer CTA's shared memory, at the same offset as `local_addr` here.
+__device__ __forceinline__ void store_peer_shared(uint32_t local_addr, uint32_t rank, float v) {
   uint32_t remote;
-  float v;
-  // Not volatile: the loads of one reduction are independent and may be in flight together.
-  // They are ordered after the cluster barrier by the barrier's own memory clobber.
-  asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-  asm("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote));
-  return v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
 }
 
 // One element of the output in the epilogue mode of the launch (modes 0, 1, 2).
@@ -216,7 +214,10 @@ struct GemmShape {
   // an SM, so the next projection's CTAs can move in and prefetch while this one drains.
   static constexpr int STAGES = 4;
   static constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
-  static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024;
+  // Where the peers of a cluster deposit their shares of this CTA's output slice:
+  // [splits][128 rows][BN / splits tokens] floats (token tiles up to 64 only).
+  static constexpr uint32_t RECV_BYTES = BN <= 64 ? GB_BM * BN * 4 : 0;
+  static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + RECV_BYTES + 1024;
 };
 
 template <int BN>
@@ -244,6 +245,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   const int kb_end = min(num_kb_total, kb_begin + g.kb_per_split);
   const int num_kb = max(0, kb_end - kb_begin);
   const bool clustered = g.splits > 1;
+  // First cluster phase: "every CTA of the cluster runs" (nobody may write into a peer before).
+  // Arrive now; the wait comes right before the first remote store and costs nothing by then.
+  if (clustered) cluster_arrive();
 
   if (threadIdx.x == 0) {
     epilogue_failed = 0;
@@ -335,16 +339,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     constexpr int cols = BN >= 32 ? 32 : 16;
     const uint32_t lane_base = tmem_acc + ((uint32_t)(quarter * 32) << 16);
     if (clustered) {
-      // Park the partial tile in shared memory (the stages are free once the MMAs are done):
-      // partial[row][token] at a pitch of BN + 1 floats.
-      float* partial = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw)));
+      // Send column j of this CTA's partial tile to the CTA that owns it (j / per_cta), into
+      // slot [this rank][row][j % per_cta] of the owner's receive area.
+      cluster_wait();
+      const int per_cta = BN / g.splits;
+      const uint32_t rank = cluster_rank();
+      const uint32_t recv = smem_base + S::STAGES * S::STAGE_BYTES;
       for (int c0 = 0; c0 < BN; c0 += 32) {
         float v[32];
         if (ready) {
           if (BN >= 32) tmem_load_32(lane_base + c0, v); else tmem_load_16(lane_base + c0, v);
         }
 #pragma unroll
-        for (int j = 0; j < cols; ++j) partial[row * (BN + 1) + c0 + j] = ready ? v[j] : 0.f;
+        for (int j = 0; j < cols; ++j) {
+          const int col = c0 + j;
+          const uint32_t owner = (uint32_t)(col / per_cta);
+          const uint32_t slot = ((rank * GB_BM + (uint32_t)row) * (uint32_t)per_cta + (uint32_t)(col % per_cta)) * 4u;
+          store_peer_shared(recv + slot, owner, ready ? v[j] : 0.f);
+        }
       }
     } else if (ready) {
       if (g.mode == 3) {
@@ -387,38 +399,37 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   }
+  // Warps 0 and 1 have not waited on the first cluster phase yet (the epilogue warps did).
+  if (clustered && warp < 2) {
+    __syncwarp();  // lane 0 ran a role loop; the barrier instruction wants the whole warp
+    cluster_wait();
+  }
   __syncthreads();
   VX_TRACE_MARK(1);
   if (clustered) {
-    // Every CTA of the cluster has parked its partial tile.
-    cluster_sync_all();
+    // Second phase: every peer's stores into this CTA's receive area are done and visible.
+    cluster_arrive();
+    cluster_wait();
     VX_TRACE_MARK(2);
     if (warp >= 2) {
-      // This CTA sums the tokens [rank * BN / splits, (rank + 1) * BN / splits) of the tile over
-      // all peers, in rank order, and writes them: a thread per output feature.
+      // Sum the shares of this CTA's columns in rank order and write them: a thread per feature.
       const int row = (warp & 3) * 32 + lane;
       const int n = n0 + row;
       const int per_cta = BN / g.splits;
-      const uint32_t rank = cluster_rank();
-      const uint32_t local = smem_base + (uint32_t)(row * (BN + 1)) * 4u;
+      const int rank = (int)cluster_rank();
+      const float* recv = reinterpret_cast<const float*>(
+          smem_raw + (smem_base - smem_u32(smem_raw)) + S::STAGES * S::STAGE_BYTES);
       const float b = (g.bias != nullptr && n < g.N) ? g.bias[n] : 0.f;
-      for (int j = (int)rank * per_cta; j < ((int)rank + 1) * per_cta; ++j) {
-        const int t = t0 + j;
+      for (int jl = 0; jl < per_cta; ++jl) {
+        const int t = t0 + rank * per_cta + jl;
         if (t >= g.T || n >= g.N) continue;
-        // All peers' values first (independent loads), then the sum in rank order.
-        float part[8];
-#pragma unroll
-        for (int peer = 0; peer < 8; ++peer)
-          part[peer] = peer < g.splits ? load_peer_shared(local + (uint32_t)j * 4u, (uint32_t)peer) : 0.f;
         float acc = 0.f;
-#pragma unroll
-        for (int peer = 0; peer < 8; ++peer) acc += part[peer];
+        for (int peer = 0; peer < g.splits; ++peer)
+          acc += recv[((size_t)peer * GB_BM + row) * per_cta + jl];
         store_output(g, (size_t)t * g.ldy + n, acc + b);
       }
     }
-    // No CTA may leave while a peer still reads its shared memory.
     VX_TRACE_MARK(3);
-    cluster_sync_all();
   }
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");

@@ -410,7 +410,9 @@ class ModelRunner:
         at this batch size, the same number for every sequence whatever its length."""
         tiles = -(-opt.group // 16)
         per_split = max(1, num_seqs * opt.num_kv_heads * tiles)
-        return max(1, min(32, -(-opt.target_ctas // per_split)))
+        # Rounded down: all work items should be resident at once (two CTAs per SM), a few
+        # more than that would run as a second wave after the first has finished.
+        return max(1, min(32, opt.target_ctas // per_split))
 
     def _graph_eligible(self, chunks: Sequence[StepChunk]) -> bool:
         if not self.enable_graphs or self._graphs_broken:

@@ -94,7 +94,8 @@ def plan_attention(
         elif base_ctas >= opt.target_ctas:
             splits = 1
         else:
-            wanted = -(-opt.target_ctas // max(base_ctas, 1))
+            # Rounded down: the items should all be resident at once, not spill into a second wave.
+            wanted = opt.target_ctas // max(base_ctas, 1)
             splits = max(1, min(wanted, span // max(opt.min_split_keys, 1), opt.max_splits))
         out = per_kind.setdefault(kind, [])
         if splits <= 1:
