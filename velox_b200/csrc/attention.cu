@@ -53,6 +53,7 @@ struct AttnArgs {
   const int* q_len;         // [S] tokens of the portion
   const int* kv_len;        // [S] keys in the cache once this step's tokens are written
   const int* items;         // [n, 8]
+  int* status;              // device status word (bounded waits report here)
   float* partial_o;         // [rows, D]
   float* partial_lse;       // [rows], log2 units
   // Fused merge (bf16 families): when a split item is done it bumps the counter of its
@@ -205,8 +206,8 @@ __global__ void __launch_bounds__(128) attn_f32_kernel(AttnArgs a) {
 //   WIDE  : 64 rows per item; each of 4 warps owns 16 rows and sees all 64 keys of a tile.
 //   NARROW: 16 rows per item; each of 4 warps owns 16 keys of every 64-key tile and the warps
 //           merge at the end (decode tokens and short portions; this is what gets split).
-// K/V tiles arrive by cp.async into a ring of shared-memory stages, gathered row by row
-// through the block table.
+// K/V tiles arrive by bulk copies (cp.async.bulk, one per key row, completion on an mbarrier)
+// into a ring of shared-memory stages, gathered row by row through the block table.
 // =============================================================================================
 constexpr int B_BN = 64;
 constexpr int B_LD = D + 8;  // row pitch in elements: 16-byte aligned, conflict-free ldmatrix
@@ -272,34 +273,39 @@ __device__ __forceinline__ void load_q_tile(const AttnArgs& a, __nv_bfloat16* q_
 // loads of a tile do not wait for a table lookup first.
 constexpr int TABLE_CAP = 1024;
 
-// Loads keys [n0, n0 + 64) of one KV head into k_s / v_s; rows at or past kv_end are zeroed.
-// Consecutive threads copy consecutive 16-byte chunks of a key row, so a warp's request covers
-// whole rows (a row of one KV head is D * 2 contiguous bytes).
-__device__ __forceinline__ void load_kv_tile(const AttnArgs& a, __nv_bfloat16* k_s,
-                                             __nv_bfloat16* v_s, const int* table,
-                                             const int* table_s, int first_block, int n0,
-                                             int kv_end, int kvh) {
-  constexpr int CH = D / 8;  // 16-byte chunks per row
-  const __nv_bfloat16* kc = (const __nv_bfloat16*)a.k_cache;
-  const __nv_bfloat16* vc = (const __nv_bfloat16*)a.v_cache;
-#pragma unroll 4
-  for (int idx = threadIdx.x; idx < B_BN * CH; idx += 128) {
-    const int j = idx / CH, c = idx - j * CH;
-    const int n = n0 + j;
-    __nv_bfloat16* kd = k_s + j * B_LD + c * 8;
-    __nv_bfloat16* vd = v_s + j * B_LD + c * 8;
-    if (n < kv_end) {
-      const int block = n / a.page_size;
-      const int local = block - first_block;
-      const int page = local < TABLE_CAP ? table_s[local] : table[block];
-      const size_t off =
-          (((size_t)page * a.page_size + (n - block * a.page_size)) * a.num_kv_heads + kvh) * D + c * 8;
-      cp_async16(kd, kc + off);
-      cp_async16(vd, vc + off);
-    } else {
-      *reinterpret_cast<uint4*>(kd) = make_uint4(0u, 0u, 0u, 0u);
-      *reinterpret_cast<uint4*>(vd) = make_uint4(0u, 0u, 0u, 0u);
+// Requests keys [n0, n0 + 64) of one KV head into k_s / v_s: thread j < 64 asks the copy engine
+// for key row j (a row of one KV head is D * 2 contiguous bytes in the cache; one bulk copy for
+// K and one for V) and arrives on the stage's mbarrier with the bytes it expects; a row at or
+// past kv_end is zeroed by the thread itself.  The barrier (64 arrivals) flips when all rows
+// are in.  Called by every thread; threads 64.. do nothing.
+__device__ __forceinline__ void request_kv_tile(const AttnArgs& a, __nv_bfloat16* k_s,
+                                                __nv_bfloat16* v_s, uint32_t bar, const int* table,
+                                                const int* table_s, int first_block, int n0,
+                                                int kv_end, int kvh) {
+  constexpr uint32_t ROW_BYTES = D * 2;
+  const int j = threadIdx.x;
+  if (j >= B_BN) return;
+  const int n = n0 + j;
+  __nv_bfloat16* kd = k_s + j * B_LD;
+  __nv_bfloat16* vd = v_s + j * B_LD;
+  if (n < kv_end) {
+    const int block = n / a.page_size;
+    const int local = block - first_block;
+    const int page = local < TABLE_CAP ? table_s[local] : table[block];
+    const size_t off =
+        (((size_t)page * a.page_size + (n - block * a.page_size)) * a.num_kv_heads + kvh) * D;
+    // The stage was read through ldmatrix before: order those reads before the engine's writes.
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    mbar_expect_tx(bar, 2 * ROW_BYTES);
+    bulk_copy_g2s(smem_u32(kd), (const __nv_bfloat16*)a.k_cache + off, ROW_BYTES, bar);
+    bulk_copy_g2s(smem_u32(vd), (const __nv_bfloat16*)a.v_cache + off, ROW_BYTES, bar);
+  } else {
+#pragma unroll
+    for (int c = 0; c < D / 8; ++c) {
+      *reinterpret_cast<uint4*>(kd + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+      *reinterpret_cast<uint4*>(vd + c * 8) = make_uint4(0u, 0u, 0u, 0u);
     }
+    mbar_arrive(bar);
   }
 }
 
@@ -589,6 +595,7 @@ __global__ void __launch_bounds__(128) attn_bf16_kernel(AttnArgs a) {
   constexpr int TILE = B_BN * B_LD;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ int table_s[TABLE_CAP];
+  __shared__ __align__(8) uint64_t kv_full[STAGES];
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   __nv_bfloat16* kv_s = q_s + ROWS * B_LD;  // stage st: K at kv_s + st * 2 * TILE, V after it
 
@@ -618,6 +625,12 @@ __global__ void __launch_bounds__(128) attn_bf16_kernel(AttnArgs a) {
     const int blocks = min(TABLE_CAP, (tile_end - 1) / a.page_size - first_block + 1);
     for (int i = threadIdx.x; i < blocks; i += blockDim.x) table_s[i] = table[first_block + i];
   }
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int st = 0; st < STAGES; ++st) mbar_init(smem_u32(&kv_full[st]), B_BN);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
   load_q_tile<ROWS>(a, q_s, q_start, row_begin, row_count, kvh);
   __syncthreads();
   VX_TRACE_MARK(1);
@@ -641,26 +654,28 @@ __global__ void __launch_bounds__(128) attn_bf16_kernel(AttnArgs a) {
   for (int st = 0; st < STAGES - 1; ++st) {
     const int n = n_first + st * B_BN;
     if (n < tile_end)
-      load_kv_tile(a, kv_s + st * 2 * TILE, kv_s + st * 2 * TILE + TILE, table, table_s,
-                   first_block, n, kv_end, kvh);
-    cp_async_commit();
+      request_kv_tile(a, kv_s + st * 2 * TILE, kv_s + st * 2 * TILE + TILE,
+                      smem_u32(&kv_full[st]), table, table_s, first_block, n, kv_end, kvh);
   }
   int stage = 0, fill = STAGES - 1;
+  uint32_t parity = 0;  // bit st: the phase of kv_full[st] that the next wait looks for
+  bool alive = true;
   for (int n0 = n_first; n0 < tile_end; n0 += B_BN) {
     const int ahead = n0 + (STAGES - 1) * B_BN;
     if (ahead < tile_end)
-      load_kv_tile(a, kv_s + fill * 2 * TILE, kv_s + fill * 2 * TILE + TILE, table, table_s,
-                   first_block, ahead, kv_end, kvh);
-    cp_async_commit();
-    cp_async_wait_group<STAGES - 1>();  // the tile of this iteration has landed
-    __syncthreads();
+      request_kv_tile(a, kv_s + fill * 2 * TILE, kv_s + fill * 2 * TILE + TILE,
+                      smem_u32(&kv_full[fill]), table, table_s, first_block, ahead, kv_end, kvh);
+    if (alive) alive = mbar_wait(smem_u32(&kv_full[stage]), (parity >> stage) & 1u, a.status);
+    parity ^= 1u << stage;
     if (n0 == n_first) VX_TRACE_MARK(2);
-    const __nv_bfloat16* k_s = kv_s + stage * 2 * TILE;
-    const __nv_bfloat16* v_s = k_s + TILE;
-    float s[NT][4];
-    warp_qk<NT>(s, q_s + row0 * B_LD, k_s, key0, lane);
-    softmax_step<NT>(s, o, m, l, pos, n0 + key0, kv_begin, kv_end, a.window, a.scale_log2, lane);
-    warp_pv<NT>(o, s, v_s, key0, lane);
+    if (alive) {
+      const __nv_bfloat16* k_s = kv_s + stage * 2 * TILE;
+      const __nv_bfloat16* v_s = k_s + TILE;
+      float s[NT][4];
+      warp_qk<NT>(s, q_s + row0 * B_LD, k_s, key0, lane);
+      softmax_step<NT>(s, o, m, l, pos, n0 + key0, kv_begin, kv_end, a.window, a.scale_log2, lane);
+      warp_pv<NT>(o, s, v_s, key0, lane);
+    }
     __syncthreads();  // everyone is done with this stage before it is refilled
     stage = stage + 1 == STAGES ? 0 : stage + 1;
     fill = fill + 1 == STAGES ? 0 : fill + 1;
@@ -674,7 +689,6 @@ __global__ void __launch_bounds__(128) attn_bf16_kernel(AttnArgs a) {
   }
 
   // Merge the four warps (each saw a quarter of every tile) through shared memory.
-  cp_async_wait_group<0>();
   __syncthreads();
   float* mo = reinterpret_cast<float*>(smem_raw);  // [4][16][D]
   float* mm = mo + 4 * 16 * D;                      // [4][16]
@@ -734,7 +748,7 @@ VX_TRACE_API(vx_attn)
 
 static AttnArgs make_args(const void* q, void* out, const void* k_cache, const void* v_cache,
                           const int* block_tables, const int* q_start, const int* q_len,
-                          const int* kv_len, const int* items, float* partial_o,
+                          const int* kv_len, const int* items, int* status, float* partial_o,
                           float* partial_lse, const int* merge_items, int* split_counters,
                           int q_stride, int out_stride, int table_stride,
                           int num_kv_heads, int group, int page_size, int window,
@@ -749,6 +763,7 @@ static AttnArgs make_args(const void* q, void* out, const void* k_cache, const v
   a.q_len = q_len;
   a.kv_len = kv_len;
   a.items = items;
+  a.status = status;
   a.partial_o = partial_o;
   a.partial_lse = partial_lse;
   a.merge_items = merge_items;
@@ -773,7 +788,7 @@ VX_API int vx_attn_tile_rows(int kind) { return kind == 1 ? 64 : 16; }
 VX_API int vx_attention(int kind, const void* q, void* out, const void* k_cache,
                         const void* v_cache, const int* block_tables, const int* q_start,
                         const int* q_len, const int* kv_len, const int* items, int num_items,
-                        float* partial_o, float* partial_lse, const int* merge_items,
+                        int* status, float* partial_o, float* partial_lse, const int* merge_items,
                         int* split_counters, int q_stride, int out_stride, int table_stride,
                         int num_kv_heads, int group, int page_size, int window,
                         float softmax_scale, cudaStream_t stream) {
@@ -781,7 +796,7 @@ VX_API int vx_attention(int kind, const void* q, void* out, const void* k_cache,
   // The float32 family leaves merging to the merge kernel.
   if (kind == 0) split_counters = nullptr;
   const AttnArgs a = make_args(q, out, k_cache, v_cache, block_tables, q_start, q_len, kv_len,
-                               items, partial_o, partial_lse, merge_items, split_counters,
+                               items, status, partial_o, partial_lse, merge_items, split_counters,
                                q_stride, out_stride, table_stride,
                                num_kv_heads, group, page_size, window, softmax_scale);
   const dim3 grid(num_items, num_kv_heads);
@@ -830,7 +845,7 @@ VX_API int vx_attention_merge(int dtype, void* out, const int* q_start, const in
                               int group, cudaStream_t stream) {
   if (num_items <= 0 || max_rows <= 0) return 0;
   AttnArgs a = make_args(nullptr, out, nullptr, nullptr, nullptr, q_start, nullptr, nullptr,
-                         nullptr, const_cast<float*>(partial_o), const_cast<float*>(partial_lse),
+                         nullptr, nullptr, const_cast<float*>(partial_o), const_cast<float*>(partial_lse),
                          merge_items, nullptr, 0, out_stride, 0, num_kv_heads, group, 1, 0, 1.0f);
   const dim3 grid(num_items, num_kv_heads, max_rows);
   const int threads = D >= 128 ? 128 : (D >= 64 ? 64 : 32);

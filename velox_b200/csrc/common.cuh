@@ -74,6 +74,65 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 32 floa
 }
 
 // ---------------------------------------------------------------------------------------------
+// mbarrier helpers (shared::cta).  Every wait is bounded: after about two seconds without a
+// phase flip the waiter records VX_STATUS_WAIT_TIMEOUT and gives up instead of hanging.
+// ---------------------------------------------------------------------------------------------
+constexpr unsigned long long VX_WAIT_CYCLES = 4000000000ull;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait.  Returns false (and records it) if the barrier did not flip in time.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long start = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - start > VX_WAIT_CYCLES) {
+      atomicOr(status, VX_STATUS_WAIT_TIMEOUT);
+      return false;
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// Bulk copy global -> shared (16-byte aligned, size a multiple of 16) that signals `bar`.
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes,
+                                              uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+      : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------
 // Programmatic dependent launch.  Every kernel of a step is launched with the attribute that
 // lets it start while its predecessor in the stream is still running; it may then do work that
 // does not depend on the predecessor (set up barriers, prefetch weights) and must call

@@ -45,47 +45,6 @@ constexpr int GB_BM = 128;
 constexpr int GB_BK = 64;
 constexpr int GB_THREADS = 192;
 constexpr uint32_t GB_A_BYTES = GB_BM * GB_BK * 2;
-constexpr unsigned long long GB_WAIT_CYCLES = 4000000000ull;  // about two seconds
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-               : "memory");
-}
-
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-
-// Bounded wait.  Returns false (and records it) if the barrier did not flip in time.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long start = clock64();
-  while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - start > GB_WAIT_CYCLES) {
-      atomicOr(status, VX_STATUS_WAIT_TIMEOUT);
-      return false;
-    }
-  }
-  return true;
-}
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
                                             uint32_t bar) {

@@ -73,7 +73,7 @@ def attention_lib(head_dim: int):
     if lib is None:
         lib = build.load_attention(head_dim)
         lib.vx_attention.argtypes = [
-            _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _ptr, _ptr, _ptr, _ptr,
+            _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr,
             _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_f, _ptr,
         ]
         lib.vx_attention_merge.argtypes = [
@@ -333,6 +333,7 @@ def attention(
     softmax_scale: float,
     merge_items: Optional[torch.Tensor] = None,
     split_counters: Optional[torch.Tensor] = None,
+    status: Optional[torch.Tensor] = None,
 ) -> None:
     """Run ``num_items`` work items (see attention.cu for their layout) of one kernel family.
 
@@ -361,12 +362,24 @@ def attention(
     _check(
         lib.vx_attention(kind, _p(q), _p(out), _p(k_cache), _p(v_cache), _p(block_tables),
                          _p(q_start), _p(q_len), _p(kv_len), _p(items), num_items,
+                         _p(status if status is not None else _attention_status()),
                          _p(partial_o), _p(partial_lse), _p(merge_items), _p(split_counters),
                          q.shape[1], out.shape[1],
                          block_tables.shape[1], num_kv_heads, num_heads // num_kv_heads,
                          k_cache.shape[1], int(window or 0), float(softmax_scale), _stream()),
         "attention",
     )
+
+
+_default_status = None
+
+
+def _attention_status() -> torch.Tensor:
+    """A status word for callers that pass none (bounded waits need somewhere to report)."""
+    global _default_status
+    if _default_status is None:
+        _default_status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    return _default_status
 
 
 def attention_merge(

@@ -77,6 +77,7 @@ class Attention(Mixer):
                 ctx.kv_len, items, count, plan.partial_o, plan.partial_lse, self.num_heads,
                 self.num_kv_heads, self.head_dim, self.window, self.softmax_scale,
                 merge_items=plan.merge_items, split_counters=plan.split_counters,
+                status=ctx.status,
             )
         if plan.num_merges and plan.split_counters is None:
             kernels.attention_merge(
