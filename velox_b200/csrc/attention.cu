@@ -25,9 +25,16 @@
 //   kv_begin <= n < kv_end, n <= pos, and n > pos - window when window > 0.
 // Key tiles start at multiples of the tile width from position 0, whatever kv_begin is, so the
 // float32 result of an unsplit row does not depend on how the prompt was cut into portions.
+#include <cuda.h>
+
 #include "common.cuh"
 
 #include <math_constants.h>
+#include <string.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
 
 #ifndef VX_HEAD_DIM
 #error "compile with -DVX_HEAD_DIM=<head size>"
@@ -44,6 +51,9 @@ constexpr int D = VX_HEAD_DIM;
 constexpr int ATTN_MAX_SPLITS = 64;
 
 struct AttnArgs {
+  // Tensor maps of the K and V caches viewed as [tokens = pages * page_size, G, D], boxes of
+  // [min(page_size, 64) tokens, one KV head, 64 dims], 128-byte swizzle (TMA_KV kernels only).
+  CUtensorMap map_k, map_v;
   const void* q;            // [tokens, q_stride]; head h at h * D
   void* out;                // [tokens, out_stride]; head h at h * D
   const void* k_cache;      // [pages, page_size, G, D]
@@ -76,7 +86,7 @@ constexpr int F_ROWS = 16, F_RPW = 4, F_BN = 32;
 constexpr int F_DV = (D + 31) / 32;  // output dims per lane
 
 __global__ void __launch_bounds__(128) attn_f32_kernel(AttnArgs a) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
   float(*q_s)[D] = reinterpret_cast<float(*)[D]>(smem_raw);
   float(*k_s)[D + 1] = reinterpret_cast<float(*)[D + 1]>(smem_raw + sizeof(float) * F_ROWS * D);
   float(*v_s)[D + 1] = k_s + F_BN;
@@ -210,7 +220,22 @@ __global__ void __launch_bounds__(128) attn_f32_kernel(AttnArgs a) {
 // into a ring of shared-memory stages, gathered row by row through the block table.
 // =============================================================================================
 constexpr int B_BN = 64;
+constexpr int B_BN_ = 64;
 constexpr int B_LD = D + 8;  // row pitch in elements: 16-byte aligned, conflict-free ldmatrix
+// Head sizes that are multiples of 64 get their K/V tiles by tensor-map TMA: a tile is then D / 64
+// panels of [64 keys x 128 bytes], each 128-byte swizzled (16-byte chunk c of key row r sits at
+// chunk c ^ (r & 7)), which ldmatrix reads without bank conflicts and without padding.
+constexpr bool TMA_KV = (D % 64) == 0;
+constexpr int KV_TILE_ELEMS = TMA_KV ? B_BN_ * D : B_BN_ * (D + 8);
+
+// Address of the 16-byte chunk holding dims [d, d + 8) of key row r in a K or V tile.
+__device__ __forceinline__ const __nv_bfloat16* kv_chunk(const __nv_bfloat16* tile, int r, int d) {
+  if (TMA_KV) {
+    const int panel = d >> 6, chunk = (d & 63) >> 3;
+    return tile + panel * (B_BN_ * 64) + r * 64 + ((chunk ^ (r & 7)) << 3);
+  }
+  return tile + r * (D + 8) + d;
+}
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
   const uint32_t addr = (uint32_t)__cvta_generic_to_shared(p);
@@ -309,6 +334,48 @@ __device__ __forceinline__ void request_kv_tile(const AttnArgs& a, __nv_bfloat16
   }
 }
 
+// The same tile by tensor-map TMA (TMA_KV head sizes): one thread asks for every page of the
+// tile, per panel of 64 dims, for K and for V: boxes of [page rows x 128 bytes].  Rows past the
+// sequence come from whatever page the table names there (the reserved zero page beyond the
+// sequence's own pages); they are masked in the softmax.  The barrier takes one arrival.
+__device__ __forceinline__ void request_kv_tile_tma(const AttnArgs& a, __nv_bfloat16* k_s,
+                                                    __nv_bfloat16* v_s, uint32_t bar,
+                                                    const int* table, const int* table_s,
+                                                    int first_block, int last_block, int n0,
+                                                    int kvh) {
+  if (threadIdx.x != 0) return;
+  const int box_rows = a.page_size < B_BN ? a.page_size : B_BN;
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  mbar_expect_tx(bar, 2u * B_BN * D * 2u);
+  for (int r = 0; r < B_BN; r += box_rows) {
+    const int n = n0 + r;
+    const int block = n / a.page_size;
+    int page = 0;  // past the sequence: the reserved page
+    if (block <= last_block) {
+      const int local = block - first_block;
+      page = local < TABLE_CAP ? table_s[local] : table[block];
+    }
+    const int token = page * a.page_size + (n - block * a.page_size);
+#pragma unroll
+    for (int panel = 0; panel < D / 64; ++panel) {
+      const uint32_t k_dst = smem_u32(k_s + panel * (B_BN * 64) + r * 64);
+      const uint32_t v_dst = smem_u32(v_s + panel * (B_BN * 64) + r * 64);
+      asm volatile(
+          "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
+          "[%0], [%1, {%2, %3, %4}], [%5];"
+          ::"r"(k_dst), "l"(reinterpret_cast<uint64_t>(&a.map_k)), "r"(panel * 64), "r"(kvh),
+            "r"(token), "r"(bar)
+          : "memory");
+      asm volatile(
+          "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
+          "[%0], [%1, {%2, %3, %4}], [%5];"
+          ::"r"(v_dst), "l"(reinterpret_cast<uint64_t>(&a.map_v)), "r"(panel * 64), "r"(kvh),
+            "r"(token), "r"(bar)
+          : "memory");
+    }
+  }
+}
+
 // One warp: S[16 rows x NT*8 keys] = Q[16 x D] * K^T, keys key0.. of the tile in smem.
 template <int NT>
 __device__ __forceinline__ void warp_qk(float (&s)[NT][4], const __nv_bfloat16* q_rows,
@@ -325,8 +392,8 @@ __device__ __forceinline__ void warp_qk(float (&s)[NT][4], const __nv_bfloat16* 
     for (int j = 0; j < NT; j += 2) {
       uint32_t kb[4];
       const int jm = lane >> 3;
-      ldmatrix_x4(kb, k_s + (key0 + j * 8 + (jm >> 1) * 8 + (lane & 7)) * B_LD + kk * 16 +
-                          (jm & 1) * 8);
+      ldmatrix_x4(kb, kv_chunk(k_s, key0 + j * 8 + (jm >> 1) * 8 + (lane & 7),
+                               kk * 16 + (jm & 1) * 8));
       mma_bf16(s[j], qa, kb[0], kb[1]);
       mma_bf16(s[j + 1], qa, kb[2], kb[3]);
     }
@@ -348,8 +415,8 @@ __device__ __forceinline__ void warp_pv(float (&o)[D / 8][4], const float (&p)[N
     for (int jd = 0; jd < D / 8; jd += 2) {
       uint32_t vb[4];
       const int jm = lane >> 3;
-      ldmatrix_x4_trans(vb, v_s + (key0 + ks * 16 + (jm & 1) * 8 + (lane & 7)) * B_LD + jd * 8 +
-                                (jm >> 1) * 8);
+      ldmatrix_x4_trans(vb, kv_chunk(v_s, key0 + ks * 16 + (jm & 1) * 8 + (lane & 7),
+                                     jd * 8 + (jm >> 1) * 8));
       mma_bf16(o[jd], pa, vb[0], vb[1]);
       mma_bf16(o[jd + 1], pa, vb[2], vb[3]);
     }
@@ -589,15 +656,17 @@ __device__ __forceinline__ void cp_async_wait_group() {
 // NARROW = true : 16 rows, every warp owns 16 keys of each tile; the warps merge at the end.
 // STAGES K/V tiles are in shared memory at a time: STAGES - 1 in flight while one is multiplied.
 template <bool NARROW, int STAGES>
-__global__ void __launch_bounds__(128) attn_bf16_kernel(AttnArgs a) {
+__global__ void __launch_bounds__(128) attn_bf16_kernel(const __grid_constant__ AttnArgs a) {
   constexpr int ROWS = NARROW ? 16 : 64;
   constexpr int NT = NARROW ? 2 : 8;
-  constexpr int TILE = B_BN * B_LD;
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int TILE = KV_TILE_ELEMS;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
   __shared__ int table_s[TABLE_CAP];
   __shared__ __align__(8) uint64_t kv_full[STAGES];
-  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-  __nv_bfloat16* kv_s = q_s + ROWS * B_LD;  // stage st: K at kv_s + st * 2 * TILE, V after it
+  // K/V stages first (swizzled panels want 1024-byte alignment), the Q tile after them.
+  unsigned char* smem_al = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  __nv_bfloat16* kv_s = reinterpret_cast<__nv_bfloat16*>(smem_al);  // stage st: K at st*2*TILE, V after
+  __nv_bfloat16* q_s = kv_s + STAGES * 2 * TILE;
 
   VX_TRACE_SCOPE(NARROW ? 21 : 20);
   allow_dependents();
@@ -621,13 +690,14 @@ __global__ void __launch_bounds__(128) attn_bf16_kernel(AttnArgs a) {
   const int tile_end = min(kv_end, last_pos + 1);
   const int n_first = (kv_begin / B_BN) * B_BN;
   const int first_block = n_first / a.page_size;
+  const int last_block = tile_end > 0 ? (tile_end - 1) / a.page_size : 0;
   if (n_first < tile_end) {
     const int blocks = min(TABLE_CAP, (tile_end - 1) / a.page_size - first_block + 1);
     for (int i = threadIdx.x; i < blocks; i += blockDim.x) table_s[i] = table[first_block + i];
   }
   if (threadIdx.x == 0) {
 #pragma unroll
-    for (int st = 0; st < STAGES; ++st) mbar_init(smem_u32(&kv_full[st]), B_BN);
+    for (int st = 0; st < STAGES; ++st) mbar_init(smem_u32(&kv_full[st]), TMA_KV ? 1 : B_BN);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -653,18 +723,28 @@ __global__ void __launch_bounds__(128) attn_bf16_kernel(AttnArgs a) {
 #pragma unroll
   for (int st = 0; st < STAGES - 1; ++st) {
     const int n = n_first + st * B_BN;
-    if (n < tile_end)
-      request_kv_tile(a, kv_s + st * 2 * TILE, kv_s + st * 2 * TILE + TILE,
-                      smem_u32(&kv_full[st]), table, table_s, first_block, n, kv_end, kvh);
+    if (n < tile_end) {
+      if (TMA_KV)
+        request_kv_tile_tma(a, kv_s + st * 2 * TILE, kv_s + st * 2 * TILE + TILE,
+                            smem_u32(&kv_full[st]), table, table_s, first_block, last_block, n, kvh);
+      else
+        request_kv_tile(a, kv_s + st * 2 * TILE, kv_s + st * 2 * TILE + TILE,
+                        smem_u32(&kv_full[st]), table, table_s, first_block, n, kv_end, kvh);
+    }
   }
   int stage = 0, fill = STAGES - 1;
   uint32_t parity = 0;  // bit st: the phase of kv_full[st] that the next wait looks for
   bool alive = true;
   for (int n0 = n_first; n0 < tile_end; n0 += B_BN) {
     const int ahead = n0 + (STAGES - 1) * B_BN;
-    if (ahead < tile_end)
-      request_kv_tile(a, kv_s + fill * 2 * TILE, kv_s + fill * 2 * TILE + TILE,
-                      smem_u32(&kv_full[fill]), table, table_s, first_block, ahead, kv_end, kvh);
+    if (ahead < tile_end) {
+      if (TMA_KV)
+        request_kv_tile_tma(a, kv_s + fill * 2 * TILE, kv_s + fill * 2 * TILE + TILE,
+                            smem_u32(&kv_full[fill]), table, table_s, first_block, last_block, ahead, kvh);
+      else
+        request_kv_tile(a, kv_s + fill * 2 * TILE, kv_s + fill * 2 * TILE + TILE,
+                        smem_u32(&kv_full[fill]), table, table_s, first_block, ahead, kv_end, kvh);
+    }
     if (alive) alive = mbar_wait(smem_u32(&kv_full[stage]), (parity >> stage) & 1u, a.status);
     parity ^= 1u << stage;
     if (n0 == n_first) VX_TRACE_MARK(2);
@@ -690,7 +770,7 @@ __global__ void __launch_bounds__(128) attn_bf16_kernel(AttnArgs a) {
 
   // Merge the four warps (each saw a quarter of every tile) through shared memory.
   __syncthreads();
-  float* mo = reinterpret_cast<float*>(smem_raw);  // [4][16][D]
+  float* mo = reinterpret_cast<float*>(smem_al);  // [4][16][D]
   float* mm = mo + 4 * 16 * D;                      // [4][16]
   float* ml = mm + 4 * 16;                          // [4][16]
 #pragma unroll
@@ -746,6 +826,46 @@ using namespace vx;
 
 VX_TRACE_API(vx_attn)
 
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// Tensor map of a bf16 cache [pages, page_size, G, D] as [tokens, G, D] with boxes of
+// [box_rows tokens, 1 head, 64 dims], 128-byte swizzled.  Cached by (pointer, shape).
+static bool cache_tensor_map(CUtensorMap* map, const void* base, long long tokens, int heads,
+                             int box_rows) {
+  static std::map<std::tuple<const void*, long long, int, int>, CUtensorMap> cache;
+  static std::mutex lock;
+  static EncodeTiledFn encode = nullptr;
+  std::lock_guard<std::mutex> guard(lock);
+  const auto key = std::make_tuple(base, tokens, heads, box_rows);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *map = it->second;
+    return true;
+  }
+  if (encode == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) !=
+            cudaSuccess || result != cudaDriverEntryPointSuccess)
+      return false;
+    encode = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)heads, (cuuint64_t)tokens};
+  const cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)heads * D * 2};
+  const cuuint32_t box[3] = {64, 1, (cuuint32_t)box_rows};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  if (encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides,
+             box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  if (cache.size() > 4096) cache.clear();
+  cache[key] = *map;
+  return true;
+}
+
 static AttnArgs make_args(const void* q, void* out, const void* k_cache, const void* v_cache,
                           const int* block_tables, const int* q_start, const int* q_len,
                           const int* kv_len, const int* items, int* status, float* partial_o,
@@ -754,6 +874,7 @@ static AttnArgs make_args(const void* q, void* out, const void* k_cache, const v
                           int num_kv_heads, int group, int page_size, int window,
                           float softmax_scale) {
   AttnArgs a;
+  memset(&a, 0, sizeof(a));
   a.q = q;
   a.out = out;
   a.k_cache = k_cache;
@@ -790,15 +911,24 @@ VX_API int vx_attention(int kind, const void* q, void* out, const void* k_cache,
                         const int* q_len, const int* kv_len, const int* items, int num_items,
                         int* status, float* partial_o, float* partial_lse, const int* merge_items,
                         int* split_counters, int q_stride, int out_stride, int table_stride,
-                        int num_kv_heads, int group, int page_size, int window,
-                        float softmax_scale, cudaStream_t stream) {
+                        int num_kv_heads, int group, int page_size, long long num_pages,
+                        int window, float softmax_scale, cudaStream_t stream) {
   if (num_items <= 0) return 0;
   // The float32 family leaves merging to the merge kernel.
   if (kind == 0) split_counters = nullptr;
-  const AttnArgs a = make_args(q, out, k_cache, v_cache, block_tables, q_start, q_len, kv_len,
+  AttnArgs a = make_args(q, out, k_cache, v_cache, block_tables, q_start, q_len, kv_len,
                                items, status, partial_o, partial_lse, merge_items, split_counters,
                                q_stride, out_stride, table_stride,
                                num_kv_heads, group, page_size, window, softmax_scale);
+  if (kind != 0 && TMA_KV) {
+    // Page sizes are powers of two: a 64-key tile is whole pages, or lies inside one page.
+    if (page_size <= 0 || (page_size & (page_size - 1)) != 0) return -1;
+    const int box_rows = page_size < B_BN ? page_size : B_BN;
+    const long long tokens = num_pages * page_size;
+    if (!cache_tensor_map(&a.map_k, k_cache, tokens, num_kv_heads, box_rows) ||
+        !cache_tensor_map(&a.map_v, v_cache, tokens, num_kv_heads, box_rows))
+      return -1;
+  }
   const dim3 grid(num_items, num_kv_heads);
   if (kind == 0) {
     const size_t smem = sizeof(float) * (size_t)(F_ROWS * D + 2 * F_BN * (D + 1));
@@ -811,7 +941,7 @@ VX_API int vx_attention(int kind, const void* q, void* out, const void* k_cache,
     }
     launch_pdl(attn_f32_kernel, dim3(grid), dim3(128), smem, stream, a);
   } else if (kind == 1) {
-    const size_t smem = (size_t)(64 + 2 * WIDE_STAGES * B_BN) * B_LD * sizeof(__nv_bfloat16);
+    const size_t smem = ((size_t)64 * B_LD + (size_t)2 * WIDE_STAGES * KV_TILE_ELEMS) * sizeof(__nv_bfloat16) + 1024;
     static bool configured = false;
     if (!configured) {
       cudaError_t e = cudaFuncSetAttribute(attn_bf16_kernel<false, WIDE_STAGES>,
@@ -821,8 +951,8 @@ VX_API int vx_attention(int kind, const void* q, void* out, const void* k_cache,
     }
     launch_pdl(attn_bf16_kernel<false, WIDE_STAGES>, dim3(grid), dim3(128), smem, stream, a);
   } else if (kind == 2) {
-    size_t smem = (size_t)(16 + 2 * NARROW_STAGES * B_BN) * B_LD * sizeof(__nv_bfloat16);
-    const size_t merge = (size_t)(4 * 16 * D + 2 * 4 * 16) * sizeof(float);
+    size_t smem = ((size_t)16 * B_LD + (size_t)2 * NARROW_STAGES * KV_TILE_ELEMS) * sizeof(__nv_bfloat16) + 1024;
+    const size_t merge = (size_t)(4 * 16 * D + 2 * 4 * 16) * sizeof(float) + 1024;
     if (merge > smem) smem = merge;
     static bool configured = false;
     if (!configured) {

@@ -74,7 +74,7 @@ def attention_lib(head_dim: int):
         lib = build.load_attention(head_dim)
         lib.vx_attention.argtypes = [
             _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr,
-            _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_f, _ptr,
+            _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _c_f, _ptr,
         ]
         lib.vx_attention_merge.argtypes = [
             _c_int, _ptr, _ptr, _ptr, _c_int, _c_int, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr,
@@ -366,7 +366,8 @@ def attention(
                          _p(partial_o), _p(partial_lse), _p(merge_items), _p(split_counters),
                          q.shape[1], out.shape[1],
                          block_tables.shape[1], num_kv_heads, num_heads // num_kv_heads,
-                         k_cache.shape[1], int(window or 0), float(softmax_scale), _stream()),
+                         k_cache.shape[1], k_cache.shape[0], int(window or 0), float(softmax_scale),
+                         _stream()),
         "attention",
     )
 
