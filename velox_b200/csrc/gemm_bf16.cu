@@ -5,10 +5,10 @@
 // With few tokens (decode) the tensor-core tile is still full, because its 128-row side is made
 // of weight rows; the kernel then streams W once at memory speed.  A projection with few output
 // tiles is split along K over a thread-block cluster (2, 4 or 8 CTAs): every CTA accumulates its
-// share of K in its own tensor memory and sends every token column of its partial tile to the
-// CTA that owns that column, by stores into the owner's shared memory (distributed shared
+// share of K in its own tensor memory and sends every row (output feature) of its partial tile
+// to the CTA that owns that row, by stores into the owner's shared memory (distributed shared
 // memory); after one cluster barrier each CTA sums what its peers sent, in rank order, and writes
-// its columns out.  No partial product touches global memory and the order of the sums is fixed.
+// its rows out.  No partial product touches global memory and the order of the sums is fixed.
 //
 //   warp 0, one lane : TMA producer.  cp.async.bulk.tensor 2-D tiles of W [128 x 64] and
 //                      X [BN x 64] into a ring of 128-byte-swizzled shared-memory stages.
@@ -148,11 +148,14 @@ __device__ __forceinline__ uint32_t cluster_rank() {
   return rank;
 }
 
-// Stores a float into a peer CTA's shared memory, at the same offset as `local_addr` here.
-__device__ __forceinline__ void store_peer_shared(uint32_t local_addr, uint32_t rank, float v) {
+// Stores four floats into a peer CTA's shared memory, at the same offset as `local_addr` here.
+__device__ __forceinline__ void store_peer_shared4(uint32_t local_addr, uint32_t rank, float a,
+                                                   float b, float c, float d) {
   uint32_t remote;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};"
+               ::"r"(remote), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
 }
 
 // One element of the output in the epilogue mode of the launch (modes 0, 1, 2).
@@ -174,7 +177,7 @@ struct GemmShape {
   static constexpr int STAGES = 4;
   static constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
   // Where the peers of a cluster deposit their shares of this CTA's output slice:
-  // [splits][128 rows][BN / splits tokens] floats (token tiles up to 64 only).
+  // [splits][128 / splits rows][BN tokens] floats (token tiles up to 64 only).
   static constexpr uint32_t RECV_BYTES = BN <= 64 ? GB_BM * BN * 4 : 0;
   static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + RECV_BYTES + 1024;
 };
@@ -298,24 +301,26 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     constexpr int cols = BN >= 32 ? 32 : 16;
     const uint32_t lane_base = tmem_acc + ((uint32_t)(quarter * 32) << 16);
     if (clustered) {
-      // Send column j of this CTA's partial tile to the CTA that owns it (j / per_cta), into
-      // slot [this rank][row][j % per_cta] of the owner's receive area.
+      // Every CTA of the cluster owns 128 / splits rows (output features) of the tile.  Send this
+      // thread's row of the partial tile to its owner, into slot [this rank][row in slice][token]
+      // of the owner's receive area: BN contiguous floats, four per store.
       cluster_wait();
-      const int per_cta = BN / g.splits;
+      const int rows_per_cta = GB_BM / g.splits;
       const uint32_t rank = cluster_rank();
-      const uint32_t recv = smem_base + S::STAGES * S::STAGE_BYTES;
+      const uint32_t owner = (uint32_t)(row / rows_per_cta);
+      const uint32_t recv = smem_base + S::STAGES * S::STAGE_BYTES +
+                            ((rank * (uint32_t)rows_per_cta + (uint32_t)(row % rows_per_cta)) * BN) * 4u;
       for (int c0 = 0; c0 < BN; c0 += 32) {
         float v[32];
         if (ready) {
           if (BN >= 32) tmem_load_32(lane_base + c0, v); else tmem_load_16(lane_base + c0, v);
+        } else {
+#pragma unroll
+          for (int j = 0; j < cols; ++j) v[j] = 0.f;
         }
 #pragma unroll
-        for (int j = 0; j < cols; ++j) {
-          const int col = c0 + j;
-          const uint32_t owner = (uint32_t)(col / per_cta);
-          const uint32_t slot = ((rank * GB_BM + (uint32_t)row) * (uint32_t)per_cta + (uint32_t)(col % per_cta)) * 4u;
-          store_peer_shared(recv + slot, owner, ready ? v[j] : 0.f);
-        }
+        for (int j = 0; j < cols; j += 4)
+          store_peer_shared4(recv + (uint32_t)(c0 + j) * 4u, owner, v[j], v[j + 1], v[j + 2], v[j + 3]);
       }
     } else if (ready) {
       if (g.mode == 3) {
@@ -371,21 +376,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     cluster_wait();
     VX_TRACE_MARK(2);
     if (warp >= 2) {
-      // Sum the shares of this CTA's columns in rank order and write them: a thread per feature.
-      const int row = (warp & 3) * 32 + lane;
-      const int n = n0 + row;
-      const int per_cta = BN / g.splits;
+      // Sum the shares of this CTA's rows in rank order and write them; consecutive threads take
+      // consecutive features of one token.
+      const int rows_per_cta = GB_BM / g.splits;
       const int rank = (int)cluster_rank();
       const float* recv = reinterpret_cast<const float*>(
           smem_raw + (smem_base - smem_u32(smem_raw)) + S::STAGES * S::STAGE_BYTES);
-      const float b = (g.bias != nullptr && n < g.N) ? g.bias[n] : 0.f;
-      for (int jl = 0; jl < per_cta; ++jl) {
-        const int t = t0 + rank * per_cta + jl;
+      for (int e = (warp - 2) * 32 + lane; e < rows_per_cta * BN; e += 128) {
+        const int j = e / rows_per_cta, rl = e - j * rows_per_cta;
+        const int t = t0 + j, n = n0 + rank * rows_per_cta + rl;
         if (t >= g.T || n >= g.N) continue;
         float acc = 0.f;
         for (int peer = 0; peer < g.splits; ++peer)
-          acc += recv[((size_t)peer * GB_BM + row) * per_cta + jl];
-        store_output(g, (size_t)t * g.ldy + n, acc + b);
+          acc += recv[((size_t)peer * rows_per_cta + rl) * BN + j];
+        store_output(g, (size_t)t * g.ldy + n, acc + (g.bias != nullptr ? g.bias[n] : 0.f));
       }
     }
     VX_TRACE_MARK(3);
