@@ -250,3 +250,31 @@ def test_stats():
     scheduler.add_request(request("a", 5, 2))
     stats = scheduler.stats()
     assert stats["num_waiting"] == 1 and stats["num_running"] == 0 and stats["free_blocks"] == 63
+
+
+def test_single_token_layout_matches_the_general_planner():
+    """The array-built layout of a padded decode step equals the looped one."""
+    import numpy as np
+
+    from velox_b200.ops import attention_plan as ap
+
+    rng = np.random.default_rng(0)
+    for trial in range(60):
+        group = int(rng.choice([1, 2, 6, 8, 16]))
+        kv_heads = int(rng.choice([1, 2, 5]))
+        window = None if trial % 3 else int(rng.choice([1, 24, 300]))
+        use_f32 = bool(trial % 2)
+        bucket = int(rng.choice([1, 2, 4, 8]))
+        n = int(rng.integers(0, bucket + 1))
+        splits = int(rng.choice([1, 2, 3, 7, 19]))
+        kv_lens = rng.integers(1, 3000, n)
+        opt = ap.PlanOptions(num_kv_heads=kv_heads, group=group, window=window, use_f32=use_f32)
+        slow = ap.pad_plan(ap.plan_attention([1] * n, kv_lens.tolist(), opt, fixed_splits=splits), bucket, splits, opt)
+        kind, items, merges, partial_rows = ap.plan_single_tokens(kv_lens, bucket, splits, opt)
+        assert list(slow.items) == [kind]
+        assert np.array_equal(slow.items[kind], items), (trial, slow.items[kind][:4], items[:4])
+        if splits > 1:
+            assert np.array_equal(slow.merge_items, merges)
+            assert slow.partial_rows == partial_rows
+        else:
+            assert merges is None and len(slow.merge_items) == 0

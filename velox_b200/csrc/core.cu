@@ -162,8 +162,135 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, const int* __restri
 }
 
 // ---------------------------------------------------------------------------------------------
-// SwiGLU: out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i], float32 inside, one rounding.
+// 16-byte vectors of the storage type: 4 floats or 8 bfloat16.
 // ---------------------------------------------------------------------------------------------
+template <typename T>
+struct Vec16;
+template <>
+struct Vec16<float> {
+  static constexpr int N = 4;
+  float4 raw;
+  __device__ __forceinline__ void unpack(float (&v)[4]) const {
+    v[0] = raw.x; v[1] = raw.y; v[2] = raw.z; v[3] = raw.w;
+  }
+  __device__ __forceinline__ void pack(const float (&v)[4]) { raw = make_float4(v[0], v[1], v[2], v[3]); }
+};
+template <>
+struct Vec16<__nv_bfloat16> {
+  static constexpr int N = 8;
+  uint4 raw;
+  __device__ __forceinline__ void unpack(float (&v)[8]) const {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(h[i]);
+      v[2 * i] = f.x;
+      v[2 * i + 1] = f.y;
+    }
+  }
+  __device__ __forceinline__ void pack(const float (&v)[8]) {
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  }
+};
+
+template <typename T>
+__device__ __forceinline__ Vec16<T> load16(const T* p) {
+  Vec16<T> v;
+  v.raw = *reinterpret_cast<const decltype(v.raw)*>(p);
+  return v;
+}
+template <typename T>
+__device__ __forceinline__ void store16(T* p, const Vec16<T>& v) {
+  *reinterpret_cast<decltype(v.raw)*>(p) = v.raw;
+}
+
+// ---------------------------------------------------------------------------------------------
+// The same rotation and cache write, 16 bytes at a time: one block per token, one thread per
+// 16-byte chunk of the token's q|k|v row.  For head sizes, rotary widths whose half and vector
+// sizes divide evenly (the launcher checks); otherwise the kernel above runs.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_cache_write_vec_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+                                            const float* __restrict__ cos_t,
+                                            const float* __restrict__ sin_t,
+                                            const int* __restrict__ slots, T* __restrict__ k_cache,
+                                            T* __restrict__ v_cache, int H, int G, int D, int rot,
+                                            int max_pos, long long num_slots, int write_cache,
+                                            int* status) {
+  constexpr int N = Vec16<T>::N;
+  VX_TRACE_SCOPE(3);
+  allow_dependents();
+  grid_dependency_wait();
+  const int t = blockIdx.x;
+  const int half = rot >> 1;
+  const int chunks = D / N;  // per head
+  int pos = positions[t];
+  if (rot > 0 && (pos < 0 || pos >= max_pos)) {
+    if (threadIdx.x == 0) atomicOr(status, VX_STATUS_BAD_POSITION);
+    pos = 0;
+  }
+  const int slot = write_cache ? slots[t] : -1;
+  const bool slot_ok = slot >= 0 && (long long)slot < num_slots;
+  if (write_cache && slot >= 0 && !slot_ok && threadIdx.x == 0) atomicOr(status, VX_STATUS_BAD_SLOT);
+  T* row = qkv + (size_t)t * (size_t)(H + 2 * G) * D;
+  const int total = (H + 2 * G) * chunks;
+  for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
+    const int head = idx / chunks, d = (idx - head * chunks) * N;
+    const bool is_q = head < H, is_k = !is_q && head < H + G;
+    T* src = row + (size_t)head * D;
+    T* dst = src;
+    if (!is_q) {
+      if (!slot_ok) continue;
+      const int g = is_k ? head - H : head - H - G;
+      dst = (is_k ? k_cache : v_cache) + ((size_t)slot * G + g) * D;
+    }
+    if ((is_q || is_k) && d < rot) {
+      if (d >= half) continue;  // the high half is written with its low partner
+      float lo[N], hi[N], c[N], s[N], out_lo[N], out_hi[N];
+      load16(src + d).unpack(lo);
+      load16(src + d + half).unpack(hi);
+#pragma unroll
+      for (int k = 0; k < N; ++k) {
+        c[k] = cos_t[(size_t)pos * half + d + k];
+        s[k] = sin_t[(size_t)pos * half + d + k];
+        out_lo[k] = lo[k] * c[k] - hi[k] * s[k];
+        out_hi[k] = lo[k] * s[k] + hi[k] * c[k];
+      }
+      Vec16<T> a, b;
+      a.pack(out_lo);
+      b.pack(out_hi);
+      store16(dst + d, a);
+      store16(dst + d + half, b);
+    } else if (!is_q) {
+      store16(dst + d, load16(src + d));  // dims of k that do not rotate, and all of v
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// SwiGLU: out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i], float32 inside, one rounding.
+// The vector kernel (16 bytes per thread) serves widths that are a multiple of the vector.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void swiglu_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter) {
+  constexpr int N = Vec16<T>::N;
+  allow_dependents();
+  grid_dependency_wait();
+  const size_t t = blockIdx.y;
+  const int i = (blockIdx.x * blockDim.x + threadIdx.x) * N;
+  if (i >= inter) return;
+  float g[N], u[N], r[N];
+  load16(gate_up + t * 2 * inter + i).unpack(g);
+  load16(gate_up + t * 2 * inter + inter + i).unpack(u);
+#pragma unroll
+  for (int k = 0; k < N; ++k) r[k] = g[k] / (1.0f + expf(-g[k])) * u[k];
+  Vec16<T> o;
+  o.pack(r);
+  store16(out + t * inter + i, o);
+}
+
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long total,
                               int inter) {
@@ -296,6 +423,24 @@ VX_API int vx_rope_cache_write(void* qkv, int dtype, const int* positions, const
                                int max_pos, long long num_slots, int write_cache, int* status,
                                cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
+  const int vec = dtype == VX_DTYPE_F32 ? 4 : 8;
+  const bool aligned = (reinterpret_cast<uintptr_t>(qkv) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(k_cache) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(v_cache) & 15) == 0;
+  if (aligned && D % vec == 0 && (rot / 2) % vec == 0) {
+    const int work = (H + 2 * G) * (D / vec);
+    const int block = work >= 256 ? 256 : (work + 31) / 32 * 32;
+    if (dtype == VX_DTYPE_F32)
+      launch_pdl(rope_cache_write_vec_kernel<float>, dim3(num_tokens), dim3(block), 0, stream,
+                 (float*)qkv, positions, cos_t, sin_t, slots, (float*)k_cache, (float*)v_cache, H, G,
+                 D, rot, max_pos, num_slots, write_cache, status);
+    else
+      launch_pdl(rope_cache_write_vec_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(block), 0,
+                 stream, (__nv_bfloat16*)qkv, positions, cos_t, sin_t, slots,
+                 (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, H, G, D, rot, max_pos, num_slots,
+                 write_cache, status);
+    return (int)cudaGetLastError();
+  }
   const int threads = D >= 128 ? 64 : 32;
   const dim3 grid(num_tokens, H + 2 * G);
   if (dtype == VX_DTYPE_F32)
@@ -313,6 +458,19 @@ VX_API int vx_swiglu(const void* gate_up, void* out, int dtype, int num_tokens, 
                      cudaStream_t stream) {
   const long long total = (long long)num_tokens * inter;
   if (total <= 0) return 0;
+  const int vec = dtype == VX_DTYPE_F32 ? 4 : 8;
+  if (inter % vec == 0 && (reinterpret_cast<uintptr_t>(gate_up) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(out) & 15) == 0 && num_tokens <= 65535) {
+    const int threads = 128;
+    const dim3 grid((inter / vec + threads - 1) / threads, num_tokens);
+    if (dtype == VX_DTYPE_F32)
+      launch_pdl(swiglu_vec_kernel<float>, grid, dim3(threads), 0, stream, (const float*)gate_up,
+                 (float*)out, inter);
+    else
+      launch_pdl(swiglu_vec_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream,
+                 (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter);
+    return (int)cudaGetLastError();
+  }
   const int threads = 256;
   long long blocks = (total + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;

@@ -357,6 +357,7 @@ class ModelRunner:
         dev[: packer.size].copy_(host[: packer.size], non_blocking=True)
         self._copied[self._flip ^ 1].record()
         self.last_meta_bytes = packer.size * 4
+        self._last_layout = (where, plan_where, packer.size)
 
         def view(name: str) -> torch.Tensor:
             offset, shape = where[name]
@@ -445,14 +446,81 @@ class ModelRunner:
                 torch.cuda.synchronize(self.device)
                 return None
             self._graphs[bucket] = entry
-        self.prepare(chunks, pad_to=bucket)
+        if not self._fill_padded(entry, bucket, chunks):
+            self.prepare(chunks, pad_to=bucket)
         if entry[2] != (self.workspace.generation, self._meta_generation):
             # A buffer grew while the step was laid out: the graph points at old memory.
             self._graphs.pop(bucket, None)
             return None
-        graph, logits, _ = entry
+        graph, logits = entry[0], entry[1]
         graph.replay()
+        self.kernels_replayed += entry[4]
         return logits[: len(chunks)]
+
+    def _fill_padded(self, entry, bucket: int, chunks: Sequence[StepChunk]) -> bool:
+        """Write a padded single-token step straight into the places the captured step reads
+        (the layout of a bucket never changes), with arrays instead of per-token loops.  What
+        it writes is what ``prepare(chunks, pad_to=bucket)`` writes.  False: use ``prepare``."""
+        where, plan_where, size = entry[3]
+        if any(sig[1] > 16 for _, sig in self._signatures):
+            return False
+        P = self.page_size
+        n = len(chunks)
+        positions = np.fromiter((c.seq.num_computed for c in chunks), np.int64, n)
+        blocks = positions // P
+        for c, block in zip(chunks, blocks):
+            if block >= c.seq.num_logical_blocks:
+                raise ValueError(f"{c.seq.seq_id}: append_slots was not called before the step")
+        host, dev = self._staging(size)
+        host_np = host.numpy()
+
+        def hv(name):
+            offset, shape = where[name]
+            count = int(np.prod(shape)) if shape else 1
+            return host_np[offset : offset + count].reshape(shape)
+
+        ids = hv("ids")
+        ids[:n] = [c.tokens[0] for c in chunks]
+        ids[n:] = 0
+        pos = hv("positions")
+        pos[:n] = positions
+        pos[n:] = 0
+        hv("q_start")[:] = np.arange(bucket, dtype=np.int32)
+        hv("q_len")[:] = 1
+        kv = hv("kv_len")
+        kv[:n] = positions + 1
+        kv[n:] = 1
+        slots = hv("seq_slots")
+        slots[:n] = [self.max_num_seqs if c.seq.slot is None else c.seq.slot for c in chunks]
+        slots[n:] = self.max_num_seqs
+        hv("logit_rows")[:] = np.arange(bucket, dtype=np.int32)
+        for g in range(len(self.cache.groups)):
+            slot_map = hv(f"slots{g}")
+            slot_map[:n] = [c.seq.tables[g][b] * P for c, b in zip(chunks, blocks)] + positions % P
+            slot_map[n:] = -1
+            tables = hv(f"tables{g}")
+            tables[:] = 0
+            for s, c in enumerate(chunks):
+                t = c.seq.tables[g]
+                tables[s, : len(t)] = t
+        kv_lens = positions + 1
+        for key, (entry_where, merge_where) in plan_where.items():
+            num_kv_heads, heads_per_kv, window = key[1]
+            options = dict(num_kv_heads=num_kv_heads, group=heads_per_kv, window=window,
+                           use_f32=self.dtype == torch.float32, target_ctas=2 * self.num_sms)
+            options.update(self.plan_overrides)
+            opt = ap.PlanOptions(**options)
+            splits = self._padded_splits(bucket, opt)
+            kind, items, merges, _ = ap.plan_single_tokens(kv_lens, bucket, splits, opt)
+            offset, shape = entry_where[kind]
+            host_np[offset : offset + items.size] = items.reshape(-1)
+            if merges is not None:
+                offset, shape = merge_where
+                host_np[offset : offset + merges.size] = merges.reshape(-1)
+        dev[:size].copy_(host[:size], non_blocking=True)
+        self._copied[self._flip ^ 1].record()
+        self.last_meta_bytes = size * 4
+        return True
 
     def _capture(self, bucket: int):
         # Twice eagerly on an all-padding batch: buffers get their final size and addresses.
@@ -462,13 +530,17 @@ class ModelRunner:
         torch.cuda.synchronize(self.device)
         generation = (self.workspace.generation, self._meta_generation)
         ctx, ids, rows, count = self.prepare([], pad_to=bucket)
+        layout = self._last_layout
         graph = torch.cuda.CUDAGraph()
+        launches_before = kernels.launch_count
         with torch.cuda.graph(graph):
             logits = self.model.forward(ctx, self.layer_caches, ids, rows, count)
+        launches = kernels.launch_count - launches_before
         torch.cuda.synchronize(self.device)
         if generation != (self.workspace.generation, self._meta_generation):
             raise RuntimeError("buffers moved during capture")
-        return graph, logits, generation
+        # (graph, logits, buffer generation, layout of the step's arrays, kernels per replay)
+        return graph, logits, generation, layout, launches
 
     def _scratch(self, name: str, count: int) -> torch.Tensor:
         ws = self.workspace

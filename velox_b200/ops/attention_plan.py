@@ -153,3 +153,53 @@ def pad_plan(plan: AttentionPlan, num_seqs: int, splits: int, opt: PlanOptions) 
         out.merge_items = np.concatenate([plan.merge_items, merge_padding], axis=0)
         out.partial_rows = want_items * opt.num_kv_heads * height
     return out
+
+
+def plan_single_tokens(kv_lens: np.ndarray, num_seqs: int, splits: int, opt: PlanOptions):
+    """The padded layout of a step of single tokens, computed with arrays instead of loops.
+
+    Equal to ``pad_plan(plan_attention([1] * n, kv_lens, opt, fixed_splits=splits), ...)`` for
+    groups of at most 16 query heads per KV head (one tile per sequence).  Returns
+    (kind, items [num_seqs * splits, 8], merge_items [num_seqs, 8] or None, partial_rows).
+    """
+    if opt.group > 16:
+        raise ValueError("plan_single_tokens handles one 16-row tile per sequence")
+    kind = KIND_F32 if opt.use_f32 else KIND_BF16_NARROW
+    n = len(kv_lens)
+    splits = max(splits, 1)
+    items = np.zeros((num_seqs * splits, ITEM_WIDTH), np.int32)
+    items[:, 0] = -1
+    items[:, 5] = -1
+    kv = np.asarray(kv_lens, dtype=np.int64)
+    lo = np.maximum(0, kv - opt.window) if opt.window else np.zeros_like(kv)
+    if splits == 1:
+        items[:n, 0] = np.arange(n)
+        items[:n, 2] = opt.group
+        items[:n, 3] = lo
+        items[:n, 4] = kv
+        return kind, items, None, 0
+    stride = opt.num_kv_heads * opt.group
+    first_tile = lo // KEY_TILE
+    num_tiles = -(-kv // KEY_TILE) - first_tile
+    per_split = -(-num_tiles // splits)
+    s_idx = np.arange(splits, dtype=np.int64)[None, :]
+    begin = np.maximum(lo[:, None], (first_tile[:, None] + s_idx * per_split[:, None]) * KEY_TILE)
+    end = np.minimum(kv[:, None], (first_tile[:, None] + (s_idx + 1) * per_split[:, None]) * KEY_TILE)
+    end = np.maximum(end, begin)
+    seq = np.repeat(np.arange(n), splits)
+    real = items[: n * splits]
+    real[:, 0] = seq
+    real[:, 2] = opt.group
+    real[:, 3] = begin.reshape(-1)
+    real[:, 4] = end.reshape(-1)
+    real[:, 5] = np.arange(n * splits) * stride
+    real[:, 6] = seq
+    real[:, 7] = splits
+    merges = np.zeros((num_seqs, ITEM_WIDTH), np.int32)
+    merges[:, 0] = -1
+    merges[:n, 0] = np.arange(n)
+    merges[:n, 2] = opt.group
+    merges[:n, 3] = np.arange(n) * splits * stride
+    merges[:n, 4] = splits
+    merges[:n, 5] = stride
+    return kind, items, merges, num_seqs * splits * opt.num_kv_heads * TILE_ROWS[kind]
