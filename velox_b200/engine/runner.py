@@ -181,6 +181,8 @@ class ModelRunner:
         self._flip = 0
         self.num_steps = 0
         self.last_meta_bytes = 0
+        # Launches of this package's kernels made by replaying captured steps.
+        self.kernels_replayed = 0
         # The float32 path stays eager: it is the checking path, and without the fixed key-range
         # splits of a captured step its results do not depend on how the work was cut.
         self.enable_graphs = enable_graphs and self.dtype != torch.float32
