@@ -985,3 +985,161 @@ VX_API int vx_attention_merge(int dtype, void* out, const int* q_start, const in
     launch_pdl(attn_merge_kernel<__nv_bfloat16>, dim3(grid), dim3(threads), 0, stream, a, merge_items);
   return (int)cudaGetLastError();
 }
+
+// =============================================================================================
+// vx_attention_decode_static: the 16-row bfloat16 family with its scratch inside the library.
+// Declared and described in attention_static.h.  Nothing here allocates: no device allocation,
+// no host container; the tensor maps are encoded into the kernel's arguments on every call.
+// =============================================================================================
+#include "attention_static.h"
+
+#include <stdarg.h>
+#include <stdio.h>
+
+namespace {
+constexpr size_t STATIC_O_BYTES = (size_t)VX_ATTENTION_STATIC_MAX_PARTIAL_ROWS * D * sizeof(float);
+constexpr size_t STATIC_LSE_BYTES = (size_t)VX_ATTENTION_STATIC_MAX_PARTIAL_ROWS * sizeof(float);
+constexpr size_t STATIC_COUNTER_BYTES = (size_t)VX_ATTENTION_STATIC_MAX_COUNTERS * sizeof(int);
+constexpr int STATIC_MAX_DEVICES = 64;
+}  // namespace
+
+// [partial_o | partial_lse | counters]; every part starts on a 256-byte boundary.
+static __device__ __align__(256) unsigned char
+    g_static_scratch[STATIC_O_BYTES + STATIC_LSE_BYTES + STATIC_COUNTER_BYTES];
+
+static int static_fail(char* error, int capacity, int code, const char* format, ...) {
+  if (error != nullptr && capacity > 0) {
+    va_list args;
+    va_start(args, format);
+    vsnprintf(error, (size_t)capacity, format, args);
+    va_end(args);
+  }
+  return code;
+}
+
+// Tensor map of a bf16 cache as cache_tensor_map() makes it, written straight into `map`.
+static bool encode_cache_map(EncodeTiledFn encode, CUtensorMap* map, const void* base,
+                             long long tokens, int heads, int box_rows) {
+  const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)heads, (cuuint64_t)tokens};
+  const cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)heads * D * 2};
+  const cuuint32_t box[3] = {64, 1, (cuuint32_t)box_rows};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides,
+                box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) ==
+         CUDA_SUCCESS;
+}
+
+int vx_attention_decode_static(const void* q, void* out, const void* k_cache, const void* v_cache,
+                               const int* block_tables, const int* q_start, const int* q_len,
+                               const int* kv_len, const int* items, int num_items,
+                               const int* merge_items, int num_merges, int partial_rows,
+                               int* status, int q_stride, int out_stride, int table_stride,
+                               int num_kv_heads, int group, int page_size, long long num_pages,
+                               int window, float softmax_scale, cudaStream_t stream, char* error,
+                               int error_capacity) {
+  if (error != nullptr && error_capacity > 0) error[0] = 0;
+  if (num_items < 0 || num_merges < 0 || partial_rows < 0 || num_kv_heads <= 0 || group <= 0)
+    return static_fail(error, error_capacity, VX_ATTENTION_STATIC_BAD_ARGUMENT,
+                       "vx_attention_decode_static: negative count or no heads (items %d, merges "
+                       "%d, partial rows %d, KV heads %d, group %d)",
+                       num_items, num_merges, partial_rows, num_kv_heads, group);
+  if (partial_rows > VX_ATTENTION_STATIC_MAX_PARTIAL_ROWS)
+    return static_fail(error, error_capacity, VX_ATTENTION_STATIC_TOO_LARGE,
+                       "vx_attention_decode_static: the split key ranges need %d partial rows, the "
+                       "library's scratch holds %d (head size %d); use fewer splits or "
+                       "vx_attention with scratch of your own",
+                       partial_rows, VX_ATTENTION_STATIC_MAX_PARTIAL_ROWS, D);
+  const long long counters = (long long)num_merges * num_kv_heads;
+  if (counters > VX_ATTENTION_STATIC_MAX_COUNTERS)
+    return static_fail(error, error_capacity, VX_ATTENTION_STATIC_TOO_LARGE,
+                       "vx_attention_decode_static: %d merge items on %d KV heads need %lld "
+                       "counters, the library's scratch holds %d",
+                       num_merges, num_kv_heads, counters, VX_ATTENTION_STATIC_MAX_COUNTERS);
+  if ((num_merges > 0 && merge_items == nullptr) || (partial_rows > 0 && num_merges == 0))
+    return static_fail(error, error_capacity, VX_ATTENTION_STATIC_BAD_ARGUMENT,
+                       "vx_attention_decode_static: split items need their merge items");
+  if (page_size <= 0 || (page_size & (page_size - 1)) != 0)
+    return static_fail(error, error_capacity, VX_ATTENTION_STATIC_BAD_ARGUMENT,
+                       "vx_attention_decode_static: page size %d is not a power of two", page_size);
+  if (num_items == 0) return 0;
+
+  size_t smem = ((size_t)16 * B_LD + (size_t)2 * NARROW_STAGES * KV_TILE_ELEMS) * sizeof(__nv_bfloat16) + 1024;
+  const size_t merge_smem = (size_t)(4 * 16 * D + 2 * 4 * 16) * sizeof(float) + 1024;
+  if (merge_smem > smem) smem = merge_smem;
+
+  // Set-up, once per device.
+  static std::mutex lock;
+  static unsigned char* scratch_of[STATIC_MAX_DEVICES] = {};
+  static EncodeTiledFn encode = nullptr;
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess)
+    return static_fail(error, error_capacity, (int)e, "vx_attention_decode_static: cudaGetDevice: %s",
+                       cudaGetErrorString(e));
+  if (device < 0 || device >= STATIC_MAX_DEVICES)
+    return static_fail(error, error_capacity, VX_ATTENTION_STATIC_BAD_ARGUMENT,
+                       "vx_attention_decode_static: device %d is beyond the %d this library keeps "
+                       "scratch addresses for", device, STATIC_MAX_DEVICES);
+  unsigned char* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> guard(lock);
+    if (scratch_of[device] == nullptr) {
+      void* address = nullptr;
+      e = cudaGetSymbolAddress(&address, g_static_scratch);
+      if (e != cudaSuccess || address == nullptr)
+        return static_fail(error, error_capacity, e != cudaSuccess ? (int)e : (int)cudaErrorInvalidSymbol,
+                           "vx_attention_decode_static: cudaGetSymbolAddress of the scratch array: %s",
+                           cudaGetErrorString(e));
+      e = cudaFuncSetAttribute(attn_bf16_kernel<true, NARROW_STAGES>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e == cudaSuccess)
+        e = cudaMemset((unsigned char*)address + STATIC_O_BYTES + STATIC_LSE_BYTES, 0,
+                       STATIC_COUNTER_BYTES);
+      if (e != cudaSuccess)
+        return static_fail(error, error_capacity, (int)e, "vx_attention_decode_static: set-up: %s",
+                           cudaGetErrorString(e));
+      if (TMA_KV && encode == nullptr) {
+        void* entry = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &result);
+        if (e != cudaSuccess || result != cudaDriverEntryPointSuccess || entry == nullptr)
+          return static_fail(error, error_capacity, e != cudaSuccess ? (int)e : (int)cudaErrorNotSupported,
+                             "vx_attention_decode_static: the driver has no cuTensorMapEncodeTiled");
+        encode = reinterpret_cast<EncodeTiledFn>(entry);
+      }
+      scratch_of[device] = (unsigned char*)address;
+    }
+    scratch = scratch_of[device];
+  }
+  float* partial_o = reinterpret_cast<float*>(scratch);
+  float* partial_lse = reinterpret_cast<float*>(scratch + STATIC_O_BYTES);
+  int* split_counters = reinterpret_cast<int*>(scratch + STATIC_O_BYTES + STATIC_LSE_BYTES);
+
+  AttnArgs a = make_args(q, out, k_cache, v_cache, block_tables, q_start, q_len, kv_len, items,
+                         status, partial_o, partial_lse, merge_items,
+                         num_merges > 0 ? split_counters : nullptr, q_stride, out_stride,
+                         table_stride, num_kv_heads, group, page_size, window, softmax_scale);
+  if (TMA_KV) {
+    const int box_rows = page_size < B_BN ? page_size : B_BN;
+    const long long tokens = num_pages * page_size;
+    if (!encode_cache_map(encode, &a.map_k, k_cache, tokens, num_kv_heads, box_rows) ||
+        !encode_cache_map(encode, &a.map_v, v_cache, tokens, num_kv_heads, box_rows))
+      return static_fail(error, error_capacity, VX_ATTENTION_STATIC_BAD_ARGUMENT,
+                         "vx_attention_decode_static: the cache (%lld pages of %d, %d KV heads) "
+                         "cannot be described by a tensor map; is it 16-byte aligned?",
+                         num_pages, page_size, num_kv_heads);
+  }
+  if (counters > 0) {
+    e = cudaMemsetAsync(split_counters, 0, (size_t)counters * sizeof(int), stream);
+    if (e != cudaSuccess)
+      return static_fail(error, error_capacity, (int)e, "vx_attention_decode_static: clearing the counters: %s",
+                         cudaGetErrorString(e));
+  }
+  const dim3 grid(num_items, num_kv_heads);
+  e = launch_pdl(attn_bf16_kernel<true, NARROW_STAGES>, dim3(grid), dim3(128), smem, stream, a);
+  if (e != cudaSuccess)
+    return static_fail(error, error_capacity, (int)e, "vx_attention_decode_static: launch: %s",
+                       cudaGetErrorString(e));
+  return 0;
+}

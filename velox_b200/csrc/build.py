@@ -36,7 +36,7 @@ if os.environ.get("VELOX_B200_TRACE") == "1":
 
 CORE_SOURCES = ("core.cu", "sampling.cu", "gemm_bf16.cu")
 ATTENTION_SOURCES = ("attention.cu",)
-HEADERS = ("common.cuh",)
+HEADERS = ("common.cuh", "attention_static.h")
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
