@@ -227,6 +227,16 @@ constexpr int B_LD = D + 8;  // row pitch in elements: 16-byte aligned, conflict
 // chunk c ^ (r & 7)), which ldmatrix reads without bank conflicts and without padding.
 constexpr bool TMA_KV = (D % 64) == 0;
 constexpr int KV_TILE_ELEMS = TMA_KV ? B_BN_ * D : B_BN_ * (D + 8);
+// Row pitch (floats) of the narrow family's cross-warp merge buffer, and its size.
+constexpr int NARROW_MERGE_LD = D + 8;
+constexpr size_t NARROW_MERGE_BYTES = (size_t)(4 * 16 * NARROW_MERGE_LD + 2 * 4 * 16) * sizeof(float);
+// Dynamic shared memory of a bf16 kernel past its 1024-byte alignment: the Q tile and the K/V
+// stages, which the end of the kernel reuses (cross-warp merge, merge of the splits).
+__host__ __device__ constexpr size_t attn_smem_bytes(bool narrow, int stages) {
+  const size_t tiles = ((size_t)(narrow ? 16 : 64) * (D + 8) + (size_t)2 * stages * KV_TILE_ELEMS) *
+                       sizeof(__nv_bfloat16);
+  return narrow && NARROW_MERGE_BYTES > tiles ? NARROW_MERGE_BYTES : tiles;
+}
 
 // Address of the 16-byte chunk holding dims [d, d + 8) of key row r in a K or V tile.
 __device__ __forceinline__ const __nv_bfloat16* kv_chunk(const __nv_bfloat16* tile, int r, int d) {
@@ -577,59 +587,131 @@ __global__ void attn_merge_kernel(AttnArgs a, const int* __restrict__ merge_item
   merge_row<T>(a, item, blockIdx.y, r, weight_s, &denom_s);
 }
 
-// One warp merges one row: lanes hold the splits' weights, then four dims each.
-__device__ __forceinline__ void merge_row_by_warp(const AttnArgs& a, const int* item, int kvh,
-                                                  int r, int lane) {
-  const int seq = item[0], row_begin = item[1], row_count = item[2], first = item[3],
-            splits = item[4], stride = item[5];
-  const size_t base = (size_t)first + (size_t)kvh * row_count + r;
-  // Up to 64 splits: lane holds splits lane and lane + 32.
-  float lse0 = lane < splits ? __ldcg(&a.partial_lse[base + (size_t)lane * stride]) : -CUDART_INF_F;
-  float lse1 = lane + 32 < splits ? __ldcg(&a.partial_lse[base + (size_t)(lane + 32) * stride])
-                                  : -CUDART_INF_F;
-  const float mt = warp_max(fmaxf(lse0, lse1));
-  const float m_safe = mt == -CUDART_INF_F ? 0.f : mt;
-  const float w0 = lse0 == -CUDART_INF_F ? 0.f : exp2f(lse0 - m_safe);
-  const float w1 = lse1 == -CUDART_INF_F ? 0.f : exp2f(lse1 - m_safe);
-  const float den = warp_sum(w0 + w1);
-  const int row = row_begin + r;
-  const int tok = row / a.group, hg = row - tok * a.group;
-  __nv_bfloat16* dst = (__nv_bfloat16*)a.out + (size_t)(a.q_start[seq] + tok) * a.out_stride +
-                       (size_t)(kvh * a.group + hg) * D;
-  // Every lane runs every iteration (the weights travel by shuffle); lanes past D only idle.
-  for (int d0 = 0; d0 < D; d0 += 128) {
-    const int d = d0 + lane * 4;
-    const bool active = d < D;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s0 = 0; s0 < splits; s0 += 8) {
-      float4 v[8];
+// All threads of a CTA (128) merge one (merge item, KV head), sixteen rows at a time.  What
+// bounds the merge is the latency of reading what other SMs have just written (about 2 us a
+// round trip), so everything is asked for at once: the partial rows of as many splits as fit
+// come into shared memory by bulk copies (a split's rows are contiguous), the splits' weights
+// are computed from the log-sum-exps meanwhile (a warp per row), and the sum runs from shared
+// memory.  `scratch`: SMEM_BYTES of shared memory nobody else uses any more; `bar`: an
+// initialised mbarrier (count 1) in phase 0 that only the merge uses.
+struct MergeItem {
+  int row_begin, rows, first, splits, stride, q_start;
+};
+
+template <int SMEM_BYTES>
+__device__ __forceinline__ void merge_item_by_cta(const AttnArgs& a, const MergeItem& item, int kvh,
+                                                  float* scratch, uint64_t* bar) {
+  static_assert(SMEM_BYTES >= 4096 + 16 * D * 4, "no room for one split's rows");
+  constexpr int STAGE_BYTES = SMEM_BYTES - 4096;
+  const int row_begin = item.row_begin, rows = item.rows, first = item.first,
+            splits = item.splits, stride = item.stride;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  constexpr int VEC = D / 4;                  // float4 columns of a row
+  constexpr int E = (16 * VEC + 127) / 128;   // columns a thread owns per pass
+  float* weights = scratch;                   // [16][64]
+  float* stage = scratch + 1024;              // [splits of a round][nrows][D]
+  const int q_start = item.q_start;
+  uint32_t parity = 0;
+  for (int r0 = 0; r0 < rows; r0 += 16) {
+    const int nrows = min(16, rows - r0);
+    const size_t base0 = (size_t)first + (size_t)kvh * rows + r0;
+    const uint32_t split_bytes = (uint32_t)nrows * D * 4;
+    const int per_round = min(splits, STAGE_BYTES / (int)split_bytes);
+    const int total = nrows * VEC;
+    float4 acc[E];
+    int row_of[E], col_of[E];
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
-        v[i] = (active && s0 + i < splits)
-                   ? __ldcg(reinterpret_cast<const float4*>(&a.partial_o[(base + (size_t)(s0 + i) * stride) * D + d]))
-                   : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int e = 0; e < E; ++e) {
+      const int idx = (int)threadIdx.x + 128 * e;
+      acc[e] = make_float4(0.f, 0.f, 0.f, 0.f);
+      row_of[e] = idx < total ? idx / VEC : -1;
+      col_of[e] = idx - (idx / VEC) * VEC;
+    }
+    for (int s0 = 0; s0 < splits; s0 += per_round) {
+      const int ns = min(per_round, splits - s0);
+      __syncthreads();  // nobody reads the staging area (or the weights) of the round before
+      if (warp == 0) {
+        // The rows were written through the generic proxy, here and by other CTAs.
+        asm volatile("fence.proxy.async;" ::: "memory");
+        if (lane == 0) mbar_expect_tx(smem_u32(bar), (uint32_t)ns * split_bytes);
+        __syncwarp();
+        for (int i = lane; i < ns; i += 32)
+          bulk_copy_g2s(smem_u32(stage + (size_t)i * nrows * D),
+                        a.partial_o + (base0 + (size_t)(s0 + i) * stride) * D, split_bytes,
+                        smem_u32(bar));
+      }
+      if (s0 == 0) {
+        float lse0[4], lse1[4];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int s = s0 + i;
-        const float w = __shfl_sync(0xffffffffu, s < 32 ? w0 : w1, s & 31);
-        acc.x += w * v[i].x;
-        acc.y += w * v[i].y;
-        acc.z += w * v[i].z;
-        acc.w += w * v[i].w;
+        for (int j = 0; j < 4; ++j) {
+          const int r = warp + 4 * j;
+          const bool valid = r < nrows;
+          lse0[j] = valid && lane < splits
+                        ? __ldcg(&a.partial_lse[base0 + r + (size_t)lane * stride])
+                        : -CUDART_INF_F;
+          lse1[j] = valid && lane + 32 < splits
+                        ? __ldcg(&a.partial_lse[base0 + r + (size_t)(lane + 32) * stride])
+                        : -CUDART_INF_F;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int r = warp + 4 * j;
+          const float mt = warp_max(fmaxf(lse0[j], lse1[j]));
+          const float m_safe = mt == -CUDART_INF_F ? 0.f : mt;
+          const float w0 = lse0[j] == -CUDART_INF_F ? 0.f : exp2f(lse0[j] - m_safe);
+          const float w1 = lse1[j] == -CUDART_INF_F ? 0.f : exp2f(lse1[j] - m_safe);
+          const float den = warp_sum(w0 + w1);
+          const float inv = den > 0.f ? 1.0f / den : 0.f;
+          if (r < nrows) {
+            weights[r * 64 + lane] = w0 * inv;
+            weights[r * 64 + lane + 32] = w1 * inv;
+          }
+        }
+        __syncthreads();
+      }
+      mbar_wait(smem_u32(bar), parity, a.status);  // on a timeout the status word says so
+      parity ^= 1u;
+      const int split_floats = nrows * D;
+#pragma unroll 2
+      for (int i = 0; i < ns; ++i) {
+        float4 v[E];
+        float w[E];
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          const bool on = row_of[e] >= 0;
+          v[e] = on ? *reinterpret_cast<const float4*>(stage + (size_t)i * split_floats +
+                                                       (size_t)row_of[e] * D + 4 * col_of[e])
+                    : make_float4(0.f, 0.f, 0.f, 0.f);
+          w[e] = on ? weights[row_of[e] * 64 + s0 + i] : 0.f;
+        }
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          acc[e].x += w[e] * v[e].x;
+          acc[e].y += w[e] * v[e].y;
+          acc[e].z += w[e] * v[e].z;
+          acc[e].w += w[e] * v[e].w;
+        }
       }
     }
-    const float inv = den > 0.f ? 1.0f / den : 0.f;
-    if (active) {
-      *reinterpret_cast<__nv_bfloat162*>(dst + d) = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
-      *reinterpret_cast<__nv_bfloat162*>(dst + d + 2) = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      if (row_of[e] < 0) continue;
+      const int row = row_begin + r0 + row_of[e];
+      const int tok = row / a.group, hg = row - tok * a.group;
+      __nv_bfloat16* dst = (__nv_bfloat16*)a.out + (size_t)(q_start + tok) * a.out_stride +
+                           (size_t)(kvh * a.group + hg) * D + 4 * col_of[e];
+      *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(acc[e].x, acc[e].y);
+      *reinterpret_cast<__nv_bfloat162*>(dst + 2) = __floats2bfloat162_rn(acc[e].z, acc[e].w);
     }
   }
 }
 
 // Called by every thread of a CTA after it has written the partial rows of a split item.
-// The CTA that completes the splits of its (merge item, KV head) merges them: a warp per row.
+// The CTA that completes the splits of its (merge item, KV head) merges them.
+template <int SMEM_BYTES>
 __device__ __forceinline__ void finish_split(const AttnArgs& a, int merge_index, int num_splits,
-                                             int kvh) {
+                                             const MergeItem& item, int kvh, float* scratch,
+                                             uint64_t* bar) {
   __shared__ int last_s;
   __threadfence();  // this thread's partial rows are visible before the counter moves
   __syncthreads();
@@ -642,9 +724,7 @@ __device__ __forceinline__ void finish_split(const AttnArgs& a, int merge_index,
   __syncthreads();
   if (!last_s) return;
   __threadfence();
-  const int* item = a.merge_items + (size_t)merge_index * 8;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int r = warp; r < item[2]; r += (int)(blockDim.x >> 5)) merge_row_by_warp(a, item, kvh, r, lane);
+  merge_item_by_cta<SMEM_BYTES>(a, item, kvh, scratch, bar);
 }
 
 template <int N>
@@ -663,6 +743,7 @@ __global__ void __launch_bounds__(128) attn_bf16_kernel(const __grid_constant__ 
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   __shared__ int table_s[TABLE_CAP];
   __shared__ __align__(8) uint64_t kv_full[STAGES];
+  __shared__ __align__(8) uint64_t merge_bar;
   // K/V stages first (swizzled panels want 1024-byte alignment), the Q tile after them.
   unsigned char* smem_al = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   __nv_bfloat16* kv_s = reinterpret_cast<__nv_bfloat16*>(smem_al);  // stage st: K at st*2*TILE, V after
@@ -670,8 +751,9 @@ __global__ void __launch_bounds__(128) attn_bf16_kernel(const __grid_constant__ 
 
   VX_TRACE_SCOPE(NARROW ? 21 : 20);
   allow_dependents();
-  grid_dependency_wait();
-  VX_TRACE_MARK(0);
+  // Before the dependency wait: only what no kernel of this step writes.  The work items, the
+  // lengths and the block tables were copied in before the step's first kernel, and keys below
+  // ctx (the sequence's length before this step) were written by earlier steps.
   const int* item = a.items + (size_t)blockIdx.x * 8;
   const int seq = item[0];
   if (seq < 0) return;
@@ -684,6 +766,14 @@ __global__ void __launch_bounds__(128) attn_bf16_kernel(const __grid_constant__ 
   const int q_start = a.q_start[seq], q_len = a.q_len[seq], kv_len = a.kv_len[seq];
   const int ctx = kv_len - q_len;
   const int* table = a.block_tables + (size_t)seq * a.table_stride;
+  // What the merge of the splits needs is read now: a round trip to memory at the end of the
+  // last CTA's life is time nothing hides.
+  MergeItem merge_item = {row_begin, row_count, 0, num_splits, 0, q_start};
+  if (fused_merge) {
+    const int* mi = a.merge_items + (size_t)merge_index * 8;
+    merge_item.first = mi[3];
+    merge_item.stride = mi[5];
+  }
 
   // Keys past the last row's position are hidden from every row of the item.
   const int last_pos = ctx + (row_begin + row_count - 1) / a.group;
@@ -698,10 +788,37 @@ __global__ void __launch_bounds__(128) attn_bf16_kernel(const __grid_constant__ 
   if (threadIdx.x == 0) {
 #pragma unroll
     for (int st = 0; st < STAGES; ++st) mbar_init(smem_u32(&kv_full[st]), TMA_KV ? 1 : B_BN);
+    mbar_init(smem_u32(&merge_bar), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
+  __syncthreads();
+  auto request = [&](int st, int n) {
+    if (TMA_KV)
+      request_kv_tile_tma(a, kv_s + st * 2 * TILE, kv_s + st * 2 * TILE + TILE,
+                          smem_u32(&kv_full[st]), table, table_s, first_block, last_block, n, kvh);
+    else
+      request_kv_tile(a, kv_s + st * 2 * TILE, kv_s + st * 2 * TILE + TILE,
+                      smem_u32(&kv_full[st]), table, table_s, first_block, n, kv_end, kvh);
+  };
+  // Tiles of old keys only are asked for at once, the others after the wait.
+  int early = 0;
+#pragma unroll
+  for (int st = 0; st < STAGES - 1; ++st) {
+    const int n = n_first + st * B_BN;
+    if (n < tile_end && n + B_BN <= ctx && early == st) {
+      request(st, n);
+      early = st + 1;
+    }
+  }
+  grid_dependency_wait();
+  VX_TRACE_MARK(0);
   load_q_tile<ROWS>(a, q_s, q_start, row_begin, row_count, kvh);
+#pragma unroll
+  for (int st = 0; st < STAGES - 1; ++st) {
+    const int n = n_first + st * B_BN;
+    if (st >= early && n < tile_end) request(st, n);
+  }
   __syncthreads();
   VX_TRACE_MARK(1);
 
@@ -720,31 +837,12 @@ __global__ void __launch_bounds__(128) attn_bf16_kernel(const __grid_constant__ 
     pos[h] = r < row_count ? ctx + (row_begin + r) / a.group : -1;
   }
 
-#pragma unroll
-  for (int st = 0; st < STAGES - 1; ++st) {
-    const int n = n_first + st * B_BN;
-    if (n < tile_end) {
-      if (TMA_KV)
-        request_kv_tile_tma(a, kv_s + st * 2 * TILE, kv_s + st * 2 * TILE + TILE,
-                            smem_u32(&kv_full[st]), table, table_s, first_block, last_block, n, kvh);
-      else
-        request_kv_tile(a, kv_s + st * 2 * TILE, kv_s + st * 2 * TILE + TILE,
-                        smem_u32(&kv_full[st]), table, table_s, first_block, n, kv_end, kvh);
-    }
-  }
   int stage = 0, fill = STAGES - 1;
   uint32_t parity = 0;  // bit st: the phase of kv_full[st] that the next wait looks for
   bool alive = true;
   for (int n0 = n_first; n0 < tile_end; n0 += B_BN) {
     const int ahead = n0 + (STAGES - 1) * B_BN;
-    if (ahead < tile_end) {
-      if (TMA_KV)
-        request_kv_tile_tma(a, kv_s + fill * 2 * TILE, kv_s + fill * 2 * TILE + TILE,
-                            smem_u32(&kv_full[fill]), table, table_s, first_block, last_block, ahead, kvh);
-      else
-        request_kv_tile(a, kv_s + fill * 2 * TILE, kv_s + fill * 2 * TILE + TILE,
-                        smem_u32(&kv_full[fill]), table, table_s, first_block, ahead, kv_end, kvh);
-    }
+    if (ahead < tile_end) request(fill, ahead);
     if (alive) alive = mbar_wait(smem_u32(&kv_full[stage]), (parity >> stage) & 1u, a.status);
     parity ^= 1u << stage;
     if (n0 == n_first) VX_TRACE_MARK(2);
@@ -764,57 +862,88 @@ __global__ void __launch_bounds__(128) attn_bf16_kernel(const __grid_constant__ 
   VX_TRACE_MARK(3);
   if (!NARROW) {
     store_rows(a, o, m, l, row0, row_begin, row_count, q_start, kvh, partial_base, lane);
-    if (fused_merge) finish_split(a, merge_index, num_splits, kvh);
+    if (fused_merge)
+    finish_split<(int)attn_smem_bytes(NARROW, STAGES)>(a, merge_index, num_splits, merge_item, kvh,
+                                                        reinterpret_cast<float*>(smem_al), &merge_bar);
     return;
   }
 
-  // Merge the four warps (each saw a quarter of every tile) through shared memory.
+  // Merge the four warps (each saw a quarter of every tile) through shared memory.  Rows are
+  // NARROW_MERGE_LD floats apart: the fragment stores below then hit every bank once.
   __syncthreads();
-  float* mo = reinterpret_cast<float*>(smem_al);  // [4][16][D]
-  float* mm = mo + 4 * 16 * D;                      // [4][16]
+  constexpr int MD = NARROW_MERGE_LD;
+  float* mo = reinterpret_cast<float*>(smem_al);  // [4][16][MD]
+  float* mm = mo + 4 * 16 * MD;                     // [4][16]
   float* ml = mm + 4 * 16;                          // [4][16]
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = (lane >> 2) + 8 * h;
-    float* dst = mo + ((size_t)warp * 16 + r) * D;
+    float* dst = mo + ((size_t)warp * 16 + r) * MD + 2 * (lane & 3);
 #pragma unroll
-    for (int jd = 0; jd < D / 8; ++jd) {
-      dst[jd * 8 + 2 * (lane & 3)] = o[jd][2 * h];
-      dst[jd * 8 + 2 * (lane & 3) + 1] = o[jd][2 * h + 1];
-    }
+    for (int jd = 0; jd < D / 8; ++jd)
+      *reinterpret_cast<float2*>(dst + jd * 8) = make_float2(o[jd][2 * h], o[jd][2 * h + 1]);
     if ((lane & 3) == 0) {
       mm[warp * 16 + r] = m[h];
       ml[warp * 16 + r] = l[h];
     }
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < 16 * D; idx += blockDim.x) {
-    const int r = idx / D, d = idx - r * D;
-    if (r >= row_count) continue;
-    float mt = -CUDART_INF_F;
+  // Eight threads per row; a thread takes dims 2 * seg + 16 * i, so the eight cover 64
+  // consecutive bytes of the row at a time.
+  {
+    const int r = threadIdx.x >> 3, seg = threadIdx.x & 7;
+    if (r < row_count) {
+      float mt = -CUDART_INF_F;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) mt = fmaxf(mt, mm[w * 16 + r]);
-    const float m_safe = mt == -CUDART_INF_F ? 0.f : mt;
-    float lt = 0.f, acc = 0.f;
+      for (int w = 0; w < 4; ++w) mt = fmaxf(mt, mm[w * 16 + r]);
+      const float m_safe = mt == -CUDART_INF_F ? 0.f : mt;
+      float wgt[4], lt = 0.f;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      const float wgt = exp2f(mm[w * 16 + r] - m_safe);
-      lt += ml[w * 16 + r] * wgt;
-      acc += mo[((size_t)w * 16 + r) * D + d] * wgt;
-    }
-    const float val = lt > 0.f ? acc / lt : 0.f;
-    if (partial_base < 0) {
-      const int row = row_begin + r;
-      const int tok = row / a.group, hg = row - tok * a.group;
-      ((__nv_bfloat16*)a.out)[(size_t)(q_start + tok) * a.out_stride +
-                              (size_t)(kvh * a.group + hg) * D + d] = __float2bfloat16_rn(val);
-    } else {
-      const size_t prow = (size_t)partial_base + (size_t)kvh * row_count + r;
-      a.partial_o[prow * D + d] = val;
-      if (d == 0) a.partial_lse[prow] = lt > 0.f ? mt + log2f(lt) : -CUDART_INF_F;
+      for (int w = 0; w < 4; ++w) {
+        wgt[w] = exp2f(mm[w * 16 + r] - m_safe);
+        lt += ml[w * 16 + r] * wgt[w];
+      }
+      const float inv = lt > 0.f ? 1.0f / lt : 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) wgt[w] *= inv;
+      const float* src = mo + (size_t)r * MD + 2 * seg;
+      if (partial_base < 0) {
+        const int row = row_begin + r;
+        const int tok = row / a.group, hg = row - tok * a.group;
+        __nv_bfloat16* dst = (__nv_bfloat16*)a.out + (size_t)(q_start + tok) * a.out_stride +
+                             (size_t)(kvh * a.group + hg) * D + 2 * seg;
+#pragma unroll
+        for (int i = 0; i < D / 16; ++i) {
+          float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {
+            const float2 v = *reinterpret_cast<const float2*>(src + (size_t)w * 16 * MD + 16 * i);
+            acc.x += v.x * wgt[w];
+            acc.y += v.y * wgt[w];
+          }
+          *reinterpret_cast<__nv_bfloat162*>(dst + 16 * i) = __floats2bfloat162_rn(acc.x, acc.y);
+        }
+      } else {
+        const size_t prow = (size_t)partial_base + (size_t)kvh * row_count + r;
+        float* dst = a.partial_o + prow * D + 2 * seg;
+#pragma unroll
+        for (int i = 0; i < D / 16; ++i) {
+          float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {
+            const float2 v = *reinterpret_cast<const float2*>(src + (size_t)w * 16 * MD + 16 * i);
+            acc.x += v.x * wgt[w];
+            acc.y += v.y * wgt[w];
+          }
+          *reinterpret_cast<float2*>(dst + 16 * i) = acc;
+        }
+        if (seg == 0) a.partial_lse[prow] = lt > 0.f ? mt + log2f(lt) : -CUDART_INF_F;
+      }
     }
   }
-  if (fused_merge) finish_split(a, merge_index, num_splits, kvh);
+  if (fused_merge)
+    finish_split<(int)attn_smem_bytes(NARROW, STAGES)>(a, merge_index, num_splits, merge_item, kvh,
+                                                        reinterpret_cast<float*>(smem_al), &merge_bar);
 }
 
 constexpr int WIDE_STAGES = 2;
@@ -941,7 +1070,7 @@ VX_API int vx_attention(int kind, const void* q, void* out, const void* k_cache,
     }
     launch_pdl(attn_f32_kernel, dim3(grid), dim3(128), smem, stream, a);
   } else if (kind == 1) {
-    const size_t smem = ((size_t)64 * B_LD + (size_t)2 * WIDE_STAGES * KV_TILE_ELEMS) * sizeof(__nv_bfloat16) + 1024;
+    const size_t smem = attn_smem_bytes(false, WIDE_STAGES) + 1024;
     static bool configured = false;
     if (!configured) {
       cudaError_t e = cudaFuncSetAttribute(attn_bf16_kernel<false, WIDE_STAGES>,
@@ -951,9 +1080,7 @@ VX_API int vx_attention(int kind, const void* q, void* out, const void* k_cache,
     }
     launch_pdl(attn_bf16_kernel<false, WIDE_STAGES>, dim3(grid), dim3(128), smem, stream, a);
   } else if (kind == 2) {
-    size_t smem = ((size_t)16 * B_LD + (size_t)2 * NARROW_STAGES * KV_TILE_ELEMS) * sizeof(__nv_bfloat16) + 1024;
-    const size_t merge = (size_t)(4 * 16 * D + 2 * 4 * 16) * sizeof(float) + 1024;
-    if (merge > smem) smem = merge;
+    const size_t smem = attn_smem_bytes(true, NARROW_STAGES) + 1024;
     static bool configured = false;
     if (!configured) {
       cudaError_t e = cudaFuncSetAttribute(attn_bf16_kernel<true, NARROW_STAGES>,
@@ -1064,9 +1191,7 @@ int vx_attention_decode_static(const void* q, void* out, const void* k_cache, co
                        "vx_attention_decode_static: page size %d is not a power of two", page_size);
   if (num_items == 0) return 0;
 
-  size_t smem = ((size_t)16 * B_LD + (size_t)2 * NARROW_STAGES * KV_TILE_ELEMS) * sizeof(__nv_bfloat16) + 1024;
-  const size_t merge_smem = (size_t)(4 * 16 * D + 2 * 4 * 16) * sizeof(float) + 1024;
-  if (merge_smem > smem) smem = merge_smem;
+  const size_t smem = attn_smem_bytes(true, NARROW_STAGES) + 1024;
 
   // Set-up, once per device.
   static std::mutex lock;

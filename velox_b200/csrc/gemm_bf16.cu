@@ -168,13 +168,15 @@ __device__ __forceinline__ void store_output(const GemmArgs& g, size_t index, fl
     ((float*)g.out)[index] += value;
 }
 
-template <int BN>
+template <int BN, int STAGES_>
 struct GemmShape {
   static constexpr uint32_t B_BYTES = BN * GB_BK * 2;
   static constexpr uint32_t STAGE_BYTES = GB_A_BYTES + B_BYTES;
   // Four stages: 64 KB of weight tiles in flight per CTA, and with few tokens two CTAs fit on
   // an SM, so the next projection's CTAs can move in and prefetch while this one drains.
-  static constexpr int STAGES = 4;
+  // Eight stages (narrow token tiles only): 128 KB in flight for a grid that gives every SM one
+  // CTA at most, which is what keeps HBM busy at its loaded latency.
+  static constexpr int STAGES = STAGES_;
   static constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
   // Where the peers of a cluster deposit their shares of this CTA's output slice:
   // [splits][128 / splits rows][BN tokens] floats (token tiles up to 64 only).
@@ -182,11 +184,11 @@ struct GemmShape {
   static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + RECV_BYTES + 1024;
 };
 
-template <int BN>
+template <int BN, int STAGES_>
 __global__ void __launch_bounds__(GB_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
                  const __grid_constant__ CUtensorMap map_x, GemmArgs g) {
-  using S = GemmShape<BN>;
+  using S = GemmShape<BN, STAGES_>;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[S::STAGES];
   __shared__ __align__(8) uint64_t empty_bar[S::STAGES];
@@ -453,13 +455,13 @@ static bool tensor_map_2d(CUtensorMap* map, const void* base, long long rows, lo
   return true;
 }
 
-template <int BN>
+template <int BN, int STAGES_>
 static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx,
                        const GemmArgs& g, dim3 grid, cudaStream_t stream) {
-  using S = GemmShape<BN>;
+  using S = GemmShape<BN, STAGES_>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES_>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)S::SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
@@ -487,7 +489,7 @@ static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mw2, const CUte
   }
   config.attrs = attributes;
   config.numAttrs = count;
-  return (int)cudaLaunchKernelEx(&config, gemm_bf16_kernel<BN>, mw, mw2, mx, g);
+  return (int)cudaLaunchKernelEx(&config, gemm_bf16_kernel<BN, STAGES_>, mw, mw2, mx, g);
 }
 
 }  // namespace vx
@@ -503,6 +505,19 @@ VX_API int vx_gemm_bf16_token_tile(int num_tokens) {
   if (num_tokens <= 64) return 64;
   if (num_tokens <= 128) return 128;
   return 256;
+}
+
+static int sm_count() {
+  static int count = 0;
+  if (count == 0) {
+    int device = 0, value = 0;
+    if (cudaGetDevice(&device) == cudaSuccess &&
+        cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device) == cudaSuccess && value > 0)
+      count = value;
+    else
+      count = 148;
+  }
+  return count;
 }
 
 // Largest power of two <= value, at most 8 (a portable cluster).
@@ -554,11 +569,16 @@ VX_API int vx_gemm_bf16(const void* x, const void* w, const float* bias, void* o
   if (!tensor_map_2d(&mx, x, x_rows, K, bn)) return -1;
   const int n_tile = mode == 3 ? 64 : GB_BM;
   const dim3 grid((N + n_tile - 1) / n_tile, (T + bn - 1) / bn, splits);
+  // A grid that gives an SM one CTA at most keeps more tiles in flight per CTA instead.
+  const bool deep = bn <= 32 && g.kb_per_split > 4 &&
+                    (long long)grid.x * grid.y * grid.z <= (long long)sm_count();
   switch (bn) {
-    case 16: return launch_gemm<16>(mw, mw2, mx, g, grid, stream);
-    case 32: return launch_gemm<32>(mw, mw2, mx, g, grid, stream);
-    case 64: return launch_gemm<64>(mw, mw2, mx, g, grid, stream);
-    case 128: return launch_gemm<128>(mw, mw2, mx, g, grid, stream);
-    default: return launch_gemm<256>(mw, mw2, mx, g, grid, stream);
+    case 16: return deep ? launch_gemm<16, 8>(mw, mw2, mx, g, grid, stream)
+                         : launch_gemm<16, 4>(mw, mw2, mx, g, grid, stream);
+    case 32: return deep ? launch_gemm<32, 8>(mw, mw2, mx, g, grid, stream)
+                         : launch_gemm<32, 4>(mw, mw2, mx, g, grid, stream);
+    case 64: return launch_gemm<64, 4>(mw, mw2, mx, g, grid, stream);
+    case 128: return launch_gemm<128, 4>(mw, mw2, mx, g, grid, stream);
+    default: return launch_gemm<256, 4>(mw, mw2, mx, g, grid, stream);
   }
 }
