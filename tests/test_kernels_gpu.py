@@ -197,7 +197,7 @@ def plain_paged_attention(q, k_all, v_all, ctx, scale, window):
 
 
 def run_attention_case(k, dtype, H, G, D, P, seqs, window=None, seed=0, min_split_keys=256,
-                       target_ctas=296, spike=None, fused_merge=True):
+                       target_ctas=296, spike=None, fused_merge=True, max_cluster=1, max_splits=64):
     """seqs: list of (q_len, ctx_len).  Returns (got, want) as float64 [T, H, D]."""
     from velox_b200.ops import attention_plan as ap
 
@@ -241,7 +241,9 @@ def run_attention_case(k, dtype, H, G, D, P, seqs, window=None, seed=0, min_spli
     plan = ap.plan_attention(
         q_lens, kv_lens,
         ap.PlanOptions(num_kv_heads=G, group=group, window=window, use_f32=dtype == torch.float32,
-                       min_split_keys=min_split_keys, target_ctas=target_ctas),
+                       min_split_keys=min_split_keys, target_ctas=target_ctas,
+                       narrow_max_cluster=max_cluster, max_splits=max_splits,
+                       narrow_global_split_keys=min_split_keys),
     )
     dev = lambda x: torch.as_tensor(x, dtype=torch.int32).cuda()
     out = torch.zeros(T, H * D, dtype=dtype, device="cuda")
@@ -253,7 +255,8 @@ def run_attention_case(k, dtype, H, G, D, P, seqs, window=None, seed=0, min_spli
     merge_dev = dev(plan.merge_items) if fused else None
     for kind, items in plan.items.items():
         k.attention(kind, *args, dev(items), len(items), partial_o, partial_lse, H, G, D, window, 1 / math.sqrt(D),
-                    merge_items=merge_dev, split_counters=counters)
+                    merge_items=merge_dev, split_counters=counters,
+                    cluster=plan.cluster if kind == ap.KIND_BF16_NARROW else 1)
     if fused:
         torch.cuda.synchronize()
         assert int(counters.abs().sum()) == 0  # the last split of every item put its counter back
@@ -313,6 +316,38 @@ def test_attention_split_key_ranges(k, dtype, H, G, D, P, fused_merge):
     assert len(plan.merge_items) > 0 and plan.partial_rows > 0
     err = (got - want).abs().max().item()
     assert err <= _attn_tol(dtype) * want.abs().max().item(), err
+
+
+@pytest.mark.parametrize("H,G,D,P", [(4, 2, 16, 4), (12, 2, 128, 16), (6, 2, 80, 16), (5, 5, 48, 8),
+                                     (3, 3, 256, 32), (32, 1, 64, 16)])
+@pytest.mark.parametrize("max_cluster,max_splits", [(2, 1), (4, 1), (8, 1), (8, 64), (2, 64)])
+def test_attention_cluster_shares_an_item(k, H, G, D, P, max_cluster, max_splits):
+    # The CTAs of a thread-block cluster take runs of an item's key tiles and merge through
+    # distributed shared memory; where more splits are allowed the ranges are split through
+    # memory as well.  Short ranges leave some CTAs of a cluster without keys; a window cuts
+    # others.
+    seqs = [(1, 1500), (1, 700), (2, 1023), (1, 0), (1, 63), (3, 64), (1, 129), (70, 900)]
+    for window in (None, 300):
+        got, want, plan = run_attention_case(k, torch.bfloat16, H, G, D, P, seqs, window=window, seed=7,
+                                             min_split_keys=32, target_ctas=10_000,
+                                             max_cluster=max_cluster, max_splits=max_splits)
+        assert plan.cluster == max_cluster
+        assert (len(plan.merge_items) == 0) == (max_splits == 1)
+        err = (got - want).abs().max().item()
+        assert err <= _attn_tol(torch.bfloat16) * want.abs().max().item(), (window, err)
+
+
+@pytest.mark.parametrize("key_index", [0, 63, 64, 500, 1499])
+def test_attention_cluster_finds_one_far_key(k, key_index):
+    """One key among 1,500 carries the output: whichever CTA of the cluster owns its tile, its
+    share must reach the row's owner with the right weight."""
+    seqs = [(1, 300), (1, 1500), (1, 40)]
+    got, want, plan = run_attention_case(k, torch.bfloat16, 12, 2, 128, 16, seqs, seed=key_index,
+                                         spike=(1, 0, key_index), min_split_keys=64, target_ctas=96,
+                                         max_cluster=8)
+    assert plan.cluster == 8
+    err = (got - want).abs().max().item()
+    assert err <= _attn_tol(torch.bfloat16) * want.abs().max().item(), err
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

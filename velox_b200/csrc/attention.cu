@@ -72,6 +72,8 @@ struct AttnArgs {
   int* split_counters;      // [m * G], zero between steps; null: a separate kernel merges
   int q_stride, out_stride, table_stride;
   int num_kv_heads, group, page_size, window;
+  // Narrow bf16 family: CTAs of a thread-block cluster that share one work item (1, 2, 4, 8).
+  int cluster;
   float scale_log2;  // softmax scale * log2(e)
 };
 
@@ -227,16 +229,35 @@ constexpr int B_LD = D + 8;  // row pitch in elements: 16-byte aligned, conflict
 // chunk c ^ (r & 7)), which ldmatrix reads without bank conflicts and without padding.
 constexpr bool TMA_KV = (D % 64) == 0;
 constexpr int KV_TILE_ELEMS = TMA_KV ? B_BN_ * D : B_BN_ * (D + 8);
-// Row pitch (floats) of the narrow family's cross-warp merge buffer, and its size.
+// Row pitch (floats) of the narrow family's cross-warp merge buffer, and its size (eight
+// consumer warps).
 constexpr int NARROW_MERGE_LD = D + 8;
-constexpr size_t NARROW_MERGE_BYTES = (size_t)(4 * 16 * NARROW_MERGE_LD + 2 * 4 * 16) * sizeof(float);
-// Dynamic shared memory of a bf16 kernel past its 1024-byte alignment: the Q tile and the K/V
-// stages, which the end of the kernel reuses (cross-warp merge, merge of the splits).
-__host__ __device__ constexpr size_t attn_smem_bytes(bool narrow, int stages) {
+constexpr size_t NARROW_MERGE_BYTES = (size_t)(8 * 16 * NARROW_MERGE_LD + 2 * 8 * 16) * sizeof(float);
+// Where the CTAs of a cluster deposit the rows this CTA owns: [16 rows][D] floats and their
+// log-sum-exps, in memory nothing else uses while the kernel runs.
+constexpr size_t NARROW_RECV_BYTES = (size_t)16 * D * sizeof(float) + 64;
+// Dynamic shared memory of a bf16 kernel past its 1024-byte alignment: the K/V stages and the Q
+// tile, which the end of the kernel reuses (cross-warp merge, merge of the splits), and for the
+// narrow family the cluster's receive buffer after them.
+__host__ __device__ constexpr size_t attn_tiles_bytes(bool narrow, int stages) {
   const size_t tiles = ((size_t)(narrow ? 16 : 64) * (D + 8) + (size_t)2 * stages * KV_TILE_ELEMS) *
                        sizeof(__nv_bfloat16);
   return narrow && NARROW_MERGE_BYTES > tiles ? NARROW_MERGE_BYTES : tiles;
 }
+__host__ __device__ constexpr size_t attn_smem_bytes(bool narrow, int stages) {
+  return attn_tiles_bytes(narrow, stages) + (narrow ? NARROW_RECV_BYTES : 0);
+}
+// The wide family keeps two CTAs on an SM (two stages each).  The narrow family streams: one CTA
+// per SM with as many stages as fit (up to 8), so that enough bytes are in flight per SM to keep
+// HBM busy even when the step has only one CTA per SM.
+constexpr int WIDE_STAGES = 2;
+constexpr int narrow_stages() {
+  const size_t stage = (size_t)2 * KV_TILE_ELEMS * sizeof(__nv_bfloat16);
+  const size_t budget = (size_t)216 * 1024 - (size_t)16 * (D + 8) * sizeof(__nv_bfloat16) - NARROW_RECV_BYTES;
+  const size_t n = budget / stage;
+  return n > 8 ? 8 : (n < 2 ? 2 : (int)n);
+}
+constexpr int NARROW_STAGES = narrow_stages();
 
 // Address of the 16-byte chunk holding dims [d, d + 8) of key row r in a K or V tile.
 __device__ __forceinline__ const __nv_bfloat16* kv_chunk(const __nv_bfloat16* tile, int r, int d) {
@@ -286,12 +307,14 @@ __device__ __forceinline__ void cp_async_wait_but_one() {
   asm volatile("cp.async.wait_group 1;\n" ::: "memory");
 }
 
+// Called by `threads` threads numbered tid = 0 .. threads - 1.
 template <int ROWS>
 __device__ __forceinline__ void load_q_tile(const AttnArgs& a, __nv_bfloat16* q_s, int q_start,
-                                            int row_begin, int row_count, int kvh) {
+                                            int row_begin, int row_count, int kvh, int tid,
+                                            int threads) {
   constexpr int CH = D / 8;
   const __nv_bfloat16* qbase = (const __nv_bfloat16*)a.q;
-  for (int idx = threadIdx.x; idx < ROWS * CH; idx += blockDim.x) {
+  for (int idx = tid; idx < ROWS * CH; idx += threads) {
     const int r = idx / CH, c = idx - r * CH;
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
     if (r < row_count) {
@@ -593,7 +616,8 @@ __global__ void attn_merge_kernel(AttnArgs a, const int* __restrict__ merge_item
 // come into shared memory by bulk copies (a split's rows are contiguous), the splits' weights
 // are computed from the log-sum-exps meanwhile (a warp per row), and the sum runs from shared
 // memory.  `scratch`: SMEM_BYTES of shared memory nobody else uses any more; `bar`: an
-// initialised mbarrier (count 1) in phase 0 that only the merge uses.
+// initialised mbarrier (count 1) in phase 0 that only the merge uses.  Called by every thread
+// of the CTA; threads past the first 128 only keep the barriers company.
 struct MergeItem {
   int row_begin, rows, first, splits, stride, q_start;
 };
@@ -624,7 +648,7 @@ __device__ __forceinline__ void merge_item_by_cta(const AttnArgs& a, const Merge
     for (int e = 0; e < E; ++e) {
       const int idx = (int)threadIdx.x + 128 * e;
       acc[e] = make_float4(0.f, 0.f, 0.f, 0.f);
-      row_of[e] = idx < total ? idx / VEC : -1;
+      row_of[e] = idx < total && threadIdx.x < 128 ? idx / VEC : -1;
       col_of[e] = idx - (idx / VEC) * VEC;
     }
     for (int s0 = 0; s0 < splits; s0 += per_round) {
@@ -645,7 +669,7 @@ __device__ __forceinline__ void merge_item_by_cta(const AttnArgs& a, const Merge
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const int r = warp + 4 * j;
-          const bool valid = r < nrows;
+          const bool valid = r < nrows && warp < 4;
           lse0[j] = valid && lane < splits
                         ? __ldcg(&a.partial_lse[base0 + r + (size_t)lane * stride])
                         : -CUDART_INF_F;
@@ -662,7 +686,7 @@ __device__ __forceinline__ void merge_item_by_cta(const AttnArgs& a, const Merge
           const float w1 = lse1[j] == -CUDART_INF_F ? 0.f : exp2f(lse1[j] - m_safe);
           const float den = warp_sum(w0 + w1);
           const float inv = den > 0.f ? 1.0f / den : 0.f;
-          if (r < nrows) {
+          if (r < nrows && warp < 4) {
             weights[r * 64 + lane] = w0 * inv;
             weights[r * 64 + lane + 32] = w1 * inv;
           }
@@ -727,18 +751,42 @@ __device__ __forceinline__ void finish_split(const AttnArgs& a, int merge_index,
   merge_item_by_cta<SMEM_BYTES>(a, item, kvh, scratch, bar);
 }
 
+__device__ __forceinline__ void cluster_arrive() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  return rank;
+}
+// Address, in the shared window of the cluster, of this CTA's `local` in the CTA of `rank`.
+__device__ __forceinline__ uint32_t cluster_map(uint32_t local, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+  return remote;
+}
+__device__ __forceinline__ void st_cluster_f2(uint32_t addr, float2 v) {
+  asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(addr), "f"(v.x), "f"(v.y) : "memory");
+}
+__device__ __forceinline__ void st_cluster_f1(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+
 template <int N>
 __device__ __forceinline__ void cp_async_wait_group() {
   asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
 }
 
-// NARROW = false: 64 rows, every warp owns 16 rows and all 64 keys of a tile.
-// NARROW = true : 16 rows, every warp owns 16 keys of each tile; the warps merge at the end.
-// STAGES K/V tiles are in shared memory at a time: STAGES - 1 in flight while one is multiplied.
-template <bool NARROW, int STAGES>
-__global__ void __launch_bounds__(128) attn_bf16_kernel(const __grid_constant__ AttnArgs a) {
-  constexpr int ROWS = NARROW ? 16 : 64;
-  constexpr int NT = NARROW ? 2 : 8;
+// ---------------------------------------------------------------------------------------------
+// Wide family: 64 rows; every warp owns 16 rows and all 64 keys of a tile.  STAGES K/V tiles are
+// in shared memory at a time: STAGES - 1 in flight while one is multiplied.
+// ---------------------------------------------------------------------------------------------
+template <int STAGES>
+__global__ void __launch_bounds__(128) attn_wide_kernel(const __grid_constant__ AttnArgs a) {
+  constexpr int NT = 8;
   constexpr int TILE = KV_TILE_ELEMS;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   __shared__ int table_s[TABLE_CAP];
@@ -749,7 +797,7 @@ __global__ void __launch_bounds__(128) attn_bf16_kernel(const __grid_constant__ 
   __nv_bfloat16* kv_s = reinterpret_cast<__nv_bfloat16*>(smem_al);  // stage st: K at st*2*TILE, V after
   __nv_bfloat16* q_s = kv_s + STAGES * 2 * TILE;
 
-  VX_TRACE_SCOPE(NARROW ? 21 : 20);
+  VX_TRACE_SCOPE(20);
   allow_dependents();
   // Before the dependency wait: only what no kernel of this step writes.  The work items, the
   // lengths and the block tables were copied in before the step's first kernel, and keys below
@@ -813,7 +861,7 @@ __global__ void __launch_bounds__(128) attn_bf16_kernel(const __grid_constant__ 
   }
   grid_dependency_wait();
   VX_TRACE_MARK(0);
-  load_q_tile<ROWS>(a, q_s, q_start, row_begin, row_count, kvh);
+  load_q_tile<64>(a, q_s, q_start, row_begin, row_count, kvh, (int)threadIdx.x, 128);
 #pragma unroll
   for (int st = 0; st < STAGES - 1; ++st) {
     const int n = n_first + st * B_BN;
@@ -828,8 +876,7 @@ __global__ void __launch_bounds__(128) attn_bf16_kernel(const __grid_constant__ 
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[jd][e] = 0.f;
   float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
-  const int row0 = NARROW ? 0 : warp * 16;   // first row this warp works on
-  const int key0 = NARROW ? warp * 16 : 0;   // first key of a tile this warp works on
+  const int row0 = warp * 16;  // first row this warp works on
   int pos[2];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -850,9 +897,9 @@ __global__ void __launch_bounds__(128) attn_bf16_kernel(const __grid_constant__ 
       const __nv_bfloat16* k_s = kv_s + stage * 2 * TILE;
       const __nv_bfloat16* v_s = k_s + TILE;
       float s[NT][4];
-      warp_qk<NT>(s, q_s + row0 * B_LD, k_s, key0, lane);
-      softmax_step<NT>(s, o, m, l, pos, n0 + key0, kv_begin, kv_end, a.window, a.scale_log2, lane);
-      warp_pv<NT>(o, s, v_s, key0, lane);
+      warp_qk<NT>(s, q_s + row0 * B_LD, k_s, 0, lane);
+      softmax_step<NT>(s, o, m, l, pos, n0, kv_begin, kv_end, a.window, a.scale_log2, lane);
+      warp_pv<NT>(o, s, v_s, 0, lane);
     }
     __syncthreads();  // everyone is done with this stage before it is refilled
     stage = stage + 1 == STAGES ? 0 : stage + 1;
@@ -860,94 +907,361 @@ __global__ void __launch_bounds__(128) attn_bf16_kernel(const __grid_constant__ 
   }
 
   VX_TRACE_MARK(3);
-  if (!NARROW) {
-    store_rows(a, o, m, l, row0, row_begin, row_count, q_start, kvh, partial_base, lane);
-    if (fused_merge)
-    finish_split<(int)attn_smem_bytes(NARROW, STAGES)>(a, merge_index, num_splits, merge_item, kvh,
-                                                        reinterpret_cast<float*>(smem_al), &merge_bar);
-    return;
+  store_rows(a, o, m, l, row0, row_begin, row_count, q_start, kvh, partial_base, lane);
+  if (fused_merge)
+    finish_split<(int)attn_smem_bytes(false, STAGES)>(a, merge_index, num_splits, merge_item, kvh,
+                                                      reinterpret_cast<float*>(smem_al), &merge_bar);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Narrow family: 16 rows (single decoded tokens, short portions); this is what streams the
+// cache in a decode step.  Nine warps: eight consumers in two groups of four and one producer.
+// The producer asks the copy engines for K/V tiles into a ring of STAGES stages and never
+// computes; a group takes every second tile, its four warps 16 keys of the tile each, and hands
+// the stage back through an mbarrier when its warps have read it - there is no block-wide
+// barrier in the loop.  Two groups, because one warp per scheduler cannot hide the latency of
+// its own ldmatrix -> mma -> softmax chain.  At the end the eight warps merge through shared
+// memory.
+// A cluster of 2, 4 or 8 such CTAs may share one work item: CTA `rank` takes a run of the
+// item's key tiles, and the CTAs merge through distributed shared memory by rows.
+// ---------------------------------------------------------------------------------------------
+constexpr int NARROW_GROUPS = 2;
+constexpr int NARROW_CONSUMERS = NARROW_GROUPS * 4 * 32;
+constexpr int NARROW_THREADS = NARROW_CONSUMERS + 32;
+
+// The producer warp's share of a tile: lanes issue the copies side by side.
+__device__ __forceinline__ void produce_kv_tile(const AttnArgs& a, __nv_bfloat16* k_s,
+                                                __nv_bfloat16* v_s, uint32_t bar, const int* table,
+                                                const int* table_s, int first_block,
+                                                int last_block, int n0, int kv_end, int kvh,
+                                                int lane) {
+  // The stage was read through ldmatrix before: order those reads before the engines' writes.
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  if (TMA_KV) {
+    const int box_rows = a.page_size < B_BN ? a.page_size : B_BN;
+    const int pages = B_BN / box_rows;
+    constexpr int PANELS = D / 64 > 0 ? D / 64 : 1;
+    if (lane == 0) mbar_expect_tx(bar, 2u * B_BN * D * 2u);
+    __syncwarp();
+    // One copy per (page, panel, K or V): lanes take them in turn.
+    for (int op = lane; op < pages * PANELS * 2; op += 32) {
+      const int which = op & 1, panel = (op >> 1) % PANELS, pg = (op >> 1) / PANELS;
+      const int r = pg * box_rows;
+      const int n = n0 + r;
+      const int block = n / a.page_size;
+      int page = 0;  // past the sequence: the reserved page
+      if (block <= last_block) {
+        const int local = block - first_block;
+        page = local < TABLE_CAP ? table_s[local] : table[block];
+      }
+      const int token = page * a.page_size + (n - block * a.page_size);
+      const uint32_t dst = smem_u32((which ? v_s : k_s) + panel * (B_BN * 64) + r * 64);
+      const CUtensorMap* map = which ? &a.map_v : &a.map_k;
+      asm volatile(
+          "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
+          "[%0], [%1, {%2, %3, %4}], [%5];"
+          ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(panel * 64), "r"(kvh), "r"(token),
+            "r"(bar)
+          : "memory");
+    }
+  } else {
+    constexpr uint32_t ROW_BYTES = D * 2;
+    // One arrival per key row (the barrier counts 64): a row in the cache comes by two bulk
+    // copies, a row past the range is zeroed here.
+    for (int j = lane; j < B_BN; j += 32) {
+      const int n = n0 + j;
+      __nv_bfloat16* kd = k_s + j * B_LD;
+      __nv_bfloat16* vd = v_s + j * B_LD;
+      if (n < kv_end) {
+        const int block = n / a.page_size;
+        const int local = block - first_block;
+        const int page = local < TABLE_CAP ? table_s[local] : table[block];
+        const size_t off =
+            (((size_t)page * a.page_size + (n - block * a.page_size)) * a.num_kv_heads + kvh) * D;
+        mbar_expect_tx(bar, 2 * ROW_BYTES);
+        bulk_copy_g2s(smem_u32(kd), (const __nv_bfloat16*)a.k_cache + off, ROW_BYTES, bar);
+        bulk_copy_g2s(smem_u32(vd), (const __nv_bfloat16*)a.v_cache + off, ROW_BYTES, bar);
+      } else {
+#pragma unroll
+        for (int c = 0; c < D / 8; ++c) {
+          *reinterpret_cast<uint4*>(kd + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+          *reinterpret_cast<uint4*>(vd + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        mbar_arrive(bar);
+      }
+    }
+  }
+}
+
+template <int STAGES>
+__global__ void __launch_bounds__(NARROW_THREADS) attn_narrow_kernel(const __grid_constant__ AttnArgs a) {
+  constexpr int NT = 2;
+  constexpr int TILE = KV_TILE_ELEMS;
+  constexpr int WARPS = NARROW_GROUPS * 4;  // consumer warps
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  __shared__ int table_s[TABLE_CAP];
+  __shared__ __align__(8) uint64_t kv_full[STAGES];
+  __shared__ __align__(8) uint64_t kv_empty[STAGES];
+  __shared__ __align__(8) uint64_t merge_bar;
+  unsigned char* smem_al = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  __nv_bfloat16* kv_s = reinterpret_cast<__nv_bfloat16*>(smem_al);  // stage st: K at st*2*TILE, V after
+  __nv_bfloat16* q_s = kv_s + STAGES * 2 * TILE;
+
+  VX_TRACE_SCOPE(21);
+  allow_dependents();
+  // Before the dependency wait: only what no kernel of this step writes (see the wide family).
+  const int cluster = a.cluster;
+  const int* item = a.items + (size_t)(cluster > 1 ? blockIdx.x / cluster : blockIdx.x) * 8;
+  const int seq = item[0];
+  if (seq < 0) return;  // padding: every CTA of the cluster leaves here
+  // First cluster phase: "every CTA of the cluster runs" (nobody may write into a peer before).
+  // Arrive now; the wait comes right before the first remote store and costs nothing by then.
+  if (cluster > 1) cluster_arrive();
+  const int row_begin = item[1], row_count = item[2];
+  int kv_begin = item[3], kv_end = item[4];
+  const int partial_base = item[5];
+  const int merge_index = item[6], num_splits = item[7];
+  const bool fused_merge = partial_base >= 0 && a.split_counters != nullptr;
+  const int kvh = blockIdx.y;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int q_start = a.q_start[seq], q_len = a.q_len[seq], kv_len = a.kv_len[seq];
+  const int ctx = kv_len - q_len;
+  const int* table = a.block_tables + (size_t)seq * a.table_stride;
+  MergeItem merge_item = {row_begin, row_count, 0, num_splits, 0, q_start};
+  if (fused_merge) {
+    const int* mi = a.merge_items + (size_t)merge_index * 8;
+    merge_item.first = mi[3];
+    merge_item.stride = mi[5];
   }
 
-  // Merge the four warps (each saw a quarter of every tile) through shared memory.  Rows are
+  // Keys past the last row's position are hidden from every row of the item.
+  const int last_pos = ctx + (row_begin + row_count - 1) / a.group;
+  if (cluster > 1) {
+    // The item's key tiles, dealt out in runs: rank r gets tiles [r * per, (r + 1) * per).
+    const int visible_end = min(kv_end, last_pos + 1);
+    const int tile0 = kv_begin / B_BN;
+    const int tiles = visible_end > kv_begin ? (visible_end + B_BN - 1) / B_BN - tile0 : 0;
+    const int per = (tiles + cluster - 1) / cluster;
+    const int rank = (int)cluster_rank();
+    const int begin = max(kv_begin, (tile0 + rank * per) * B_BN);
+    const int end = min(visible_end, (tile0 + (rank + 1) * per) * B_BN);
+    kv_begin = begin;
+    kv_end = max(end, begin);  // possibly empty: the CTA then contributes nothing to the merge
+  }
+  const int tile_end = min(kv_end, last_pos + 1);
+  const int n_first = (kv_begin / B_BN) * B_BN;
+  const int num_tiles = n_first < tile_end ? (tile_end - n_first + B_BN - 1) / B_BN : 0;
+  const int first_block = n_first / a.page_size;
+  const int last_block = tile_end > 0 ? (tile_end - 1) / a.page_size : 0;
+  if (num_tiles > 0) {
+    const int blocks = min(TABLE_CAP, (tile_end - 1) / a.page_size - first_block + 1);
+    for (int i = threadIdx.x; i < blocks; i += blockDim.x) table_s[i] = table[first_block + i];
+  }
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int st = 0; st < STAGES; ++st) {
+      mbar_init(smem_u32(&kv_full[st]), TMA_KV ? 1 : B_BN);
+      mbar_init(smem_u32(&kv_empty[st]), 4);  // the four warps of the group that read it
+    }
+    mbar_init(smem_u32(&merge_bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+
+  float o[D / 8][4];
+#pragma unroll
+  for (int jd = 0; jd < D / 8; ++jd)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[jd][e] = 0.f;
+  float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
+
+  if (warp == WARPS) {
+    // ------------------------------------------------------------------------------ producer
+    // Tiles of old keys are asked for at once; the first tile that may hold one of this
+    // step's keys waits for the kernel that writes them.
+    bool waited = false, alive = true;
+    int st = 0, round = 0;
+    for (int t = 0; t < num_tiles; ++t) {
+      const int n0 = n_first + t * B_BN;
+      if (!waited && n0 + B_BN > ctx) {
+        grid_dependency_wait();
+        waited = true;
+      }
+      if (round > 0 && alive)
+        alive = mbar_wait(smem_u32(&kv_empty[st]), (uint32_t)(round - 1) & 1u, a.status);
+      produce_kv_tile(a, kv_s + st * 2 * TILE, kv_s + st * 2 * TILE + TILE, smem_u32(&kv_full[st]),
+                      table, table_s, first_block, last_block, n0, kv_end, kvh, lane);
+      if (++st == STAGES) {
+        st = 0;
+        ++round;
+      }
+    }
+  } else {
+    // ----------------------------------------------------------------------------- consumers
+    grid_dependency_wait();
+    VX_TRACE_MARK(0);
+    load_q_tile<16>(a, q_s, q_start, row_begin, row_count, kvh, (int)threadIdx.x, NARROW_CONSUMERS);
+    asm volatile("bar.sync 1, %0;" ::"n"(NARROW_CONSUMERS) : "memory");
+    VX_TRACE_MARK(1);
+    const int group = warp >> 2;
+    const int key0 = (warp & 3) * 16;  // the keys of a tile this warp works on
+    int pos[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = (lane >> 2) + 8 * h;
+      pos[h] = r < row_count ? ctx + (row_begin + r) / a.group : -1;
+    }
+    bool alive = true;
+    for (int t = group; t < num_tiles; t += NARROW_GROUPS) {
+      const int st = t % STAGES, round = t / STAGES;
+      const int n0 = n_first + t * B_BN;
+      if (alive) alive = mbar_wait(smem_u32(&kv_full[st]), (uint32_t)round & 1u, a.status);
+      if (t == group) VX_TRACE_MARK(2);
+      if (alive) {
+        const __nv_bfloat16* k_s = kv_s + st * 2 * TILE;
+        const __nv_bfloat16* v_s = k_s + TILE;
+        float s[NT][4];
+        warp_qk<NT>(s, q_s, k_s, key0, lane);
+        softmax_step<NT>(s, o, m, l, pos, n0 + key0, kv_begin, kv_end, a.window, a.scale_log2, lane);
+        warp_pv<NT>(o, s, v_s, key0, lane);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&kv_empty[st]));  // this warp has read the stage
+    }
+    VX_TRACE_MARK(3);
+  }
+
+  // Merge the eight warps (each saw a quarter of every second tile) through shared memory,
+  // which no copy is writing any more: every tile asked for has been waited for.  Rows are
   // NARROW_MERGE_LD floats apart: the fragment stores below then hit every bank once.
   __syncthreads();
   constexpr int MD = NARROW_MERGE_LD;
-  float* mo = reinterpret_cast<float*>(smem_al);  // [4][16][MD]
-  float* mm = mo + 4 * 16 * MD;                     // [4][16]
-  float* ml = mm + 4 * 16;                          // [4][16]
+  float* mo = reinterpret_cast<float*>(smem_al);  // [WARPS][16][MD]
+  float* mm = mo + WARPS * 16 * MD;                 // [WARPS][16]
+  float* ml = mm + WARPS * 16;                      // [WARPS][16]
+  if (warp < WARPS) {
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const int r = (lane >> 2) + 8 * h;
-    float* dst = mo + ((size_t)warp * 16 + r) * MD + 2 * (lane & 3);
+    for (int h = 0; h < 2; ++h) {
+      const int r = (lane >> 2) + 8 * h;
+      float* dst = mo + ((size_t)warp * 16 + r) * MD + 2 * (lane & 3);
 #pragma unroll
-    for (int jd = 0; jd < D / 8; ++jd)
-      *reinterpret_cast<float2*>(dst + jd * 8) = make_float2(o[jd][2 * h], o[jd][2 * h + 1]);
-    if ((lane & 3) == 0) {
-      mm[warp * 16 + r] = m[h];
-      ml[warp * 16 + r] = l[h];
+      for (int jd = 0; jd < D / 8; ++jd)
+        *reinterpret_cast<float2*>(dst + jd * 8) = make_float2(o[jd][2 * h], o[jd][2 * h + 1]);
+      if ((lane & 3) == 0) {
+        mm[warp * 16 + r] = m[h];
+        ml[warp * 16 + r] = l[h];
+      }
     }
   }
   __syncthreads();
-  // Eight threads per row; a thread takes dims 2 * seg + 16 * i, so the eight cover 64
-  // consecutive bytes of the row at a time.
-  {
-    const int r = threadIdx.x >> 3, seg = threadIdx.x & 7;
-    if (r < row_count) {
+  // Eight threads per row (threads 0..127); a thread takes dims 2 * seg + 16 * i, so the eight
+  // cover 64 consecutive bytes of the row at a time.
+  int r = threadIdx.x >> 3;
+  const int seg = threadIdx.x & 7;
+  bool valid = r < row_count && threadIdx.x < 128;
+  float2 val[D / 16];
+  float lse = -CUDART_INF_F;
+  if (valid) {
+    float mt = -CUDART_INF_F;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) mt = fmaxf(mt, mm[w * 16 + r]);
+    const float m_safe = mt == -CUDART_INF_F ? 0.f : mt;
+    float wgt[WARPS], lt = 0.f;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) {
+      wgt[w] = exp2f(mm[w * 16 + r] - m_safe);
+      lt += ml[w * 16 + r] * wgt[w];
+    }
+    const float inv = lt > 0.f ? 1.0f / lt : 0.f;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) wgt[w] *= inv;
+    const float* src = mo + (size_t)r * MD + 2 * seg;
+#pragma unroll
+    for (int i = 0; i < D / 16; ++i) {
+      float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) {
+        const float2 v = *reinterpret_cast<const float2*>(src + (size_t)w * 16 * MD + 16 * i);
+        acc.x += v.x * wgt[w];
+        acc.y += v.y * wgt[w];
+      }
+      val[i] = acc;
+    }
+    lse = lt > 0.f ? mt + log2f(lt) : -CUDART_INF_F;
+  }
+
+  if (cluster > 1) {
+    // Rows are dealt out to the CTAs of the cluster (row r belongs to rank r % cluster, as its
+    // slot r / cluster).  Every CTA sends each of its rows to the owner; after one cluster
+    // barrier the owner weighs what the ranks sent by their log-sum-exps, in rank order.
+    const int slots = 16 / cluster;
+    const uint32_t rank = cluster_rank();
+    float* recv = reinterpret_cast<float*>(smem_al + attn_tiles_bytes(true, STAGES));  // [cluster][slots][D]
+    float* recv_lse = recv + 16 * D;                                                    // [cluster][slots]
+    cluster_wait();
+    if (valid) {
+      const uint32_t owner = (uint32_t)(r & (cluster - 1));
+      const int slot = r / cluster;
+      const uint32_t base = cluster_map(smem_u32(recv), owner);
+      const uint32_t at = base + (uint32_t)((((int)rank * slots + slot) * D + 2 * seg) * 4);
+#pragma unroll
+      for (int i = 0; i < D / 16; ++i) st_cluster_f2(at + 64u * i, val[i]);
+      if (seg == 0) st_cluster_f1(base + (uint32_t)((16 * D + (int)rank * slots + slot) * 4), lse);
+    }
+    cluster_arrive();
+    cluster_wait();
+    const int slot = threadIdx.x >> 3;
+    r = slot * cluster + (int)rank;
+    valid = slot < slots && r < row_count;
+    if (valid) {
       float mt = -CUDART_INF_F;
-#pragma unroll
-      for (int w = 0; w < 4; ++w) mt = fmaxf(mt, mm[w * 16 + r]);
+      for (int j = 0; j < cluster; ++j) mt = fmaxf(mt, recv_lse[j * slots + slot]);
       const float m_safe = mt == -CUDART_INF_F ? 0.f : mt;
-      float wgt[4], lt = 0.f;
-#pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        wgt[w] = exp2f(mm[w * 16 + r] - m_safe);
-        lt += ml[w * 16 + r] * wgt[w];
+      float den = 0.f;
+      for (int j = 0; j < cluster; ++j) {
+        const float lj = recv_lse[j * slots + slot];
+        den += lj == -CUDART_INF_F ? 0.f : exp2f(lj - m_safe);
       }
-      const float inv = lt > 0.f ? 1.0f / lt : 0.f;
+      const float inv = den > 0.f ? 1.0f / den : 0.f;
 #pragma unroll
-      for (int w = 0; w < 4; ++w) wgt[w] *= inv;
-      const float* src = mo + (size_t)r * MD + 2 * seg;
-      if (partial_base < 0) {
-        const int row = row_begin + r;
-        const int tok = row / a.group, hg = row - tok * a.group;
-        __nv_bfloat16* dst = (__nv_bfloat16*)a.out + (size_t)(q_start + tok) * a.out_stride +
-                             (size_t)(kvh * a.group + hg) * D + 2 * seg;
+      for (int i = 0; i < D / 16; ++i) val[i] = make_float2(0.f, 0.f);
+      for (int j = 0; j < cluster; ++j) {
+        const float lj = recv_lse[j * slots + slot];
+        const float w = lj == -CUDART_INF_F ? 0.f : exp2f(lj - m_safe) * inv;
+        const float* src = recv + (size_t)(j * slots + slot) * D + 2 * seg;
 #pragma unroll
         for (int i = 0; i < D / 16; ++i) {
-          float2 acc = make_float2(0.f, 0.f);
-#pragma unroll
-          for (int w = 0; w < 4; ++w) {
-            const float2 v = *reinterpret_cast<const float2*>(src + (size_t)w * 16 * MD + 16 * i);
-            acc.x += v.x * wgt[w];
-            acc.y += v.y * wgt[w];
-          }
-          *reinterpret_cast<__nv_bfloat162*>(dst + 16 * i) = __floats2bfloat162_rn(acc.x, acc.y);
+          const float2 v = *reinterpret_cast<const float2*>(src + 16 * i);
+          val[i].x += w * v.x;
+          val[i].y += w * v.y;
         }
-      } else {
-        const size_t prow = (size_t)partial_base + (size_t)kvh * row_count + r;
-        float* dst = a.partial_o + prow * D + 2 * seg;
-#pragma unroll
-        for (int i = 0; i < D / 16; ++i) {
-          float2 acc = make_float2(0.f, 0.f);
-#pragma unroll
-          for (int w = 0; w < 4; ++w) {
-            const float2 v = *reinterpret_cast<const float2*>(src + (size_t)w * 16 * MD + 16 * i);
-            acc.x += v.x * wgt[w];
-            acc.y += v.y * wgt[w];
-          }
-          *reinterpret_cast<float2*>(dst + 16 * i) = acc;
-        }
-        if (seg == 0) a.partial_lse[prow] = lt > 0.f ? mt + log2f(lt) : -CUDART_INF_F;
       }
+      lse = den > 0.f ? mt + log2f(den) : -CUDART_INF_F;
+    }
+  }
+
+  if (valid) {
+    if (partial_base < 0) {
+      const int row = row_begin + r;
+      const int tok = row / a.group, hg = row - tok * a.group;
+      __nv_bfloat16* dst = (__nv_bfloat16*)a.out + (size_t)(q_start + tok) * a.out_stride +
+                           (size_t)(kvh * a.group + hg) * D + 2 * seg;
+#pragma unroll
+      for (int i = 0; i < D / 16; ++i)
+        *reinterpret_cast<__nv_bfloat162*>(dst + 16 * i) = __floats2bfloat162_rn(val[i].x, val[i].y);
+    } else {
+      const size_t prow = (size_t)partial_base + (size_t)kvh * row_count + r;
+      float* dst = a.partial_o + prow * D + 2 * seg;
+#pragma unroll
+      for (int i = 0; i < D / 16; ++i) *reinterpret_cast<float2*>(dst + 16 * i) = val[i];
+      if (seg == 0) a.partial_lse[prow] = lse;
     }
   }
   if (fused_merge)
-    finish_split<(int)attn_smem_bytes(NARROW, STAGES)>(a, merge_index, num_splits, merge_item, kvh,
-                                                        reinterpret_cast<float*>(smem_al), &merge_bar);
+    finish_split<(int)attn_smem_bytes(true, STAGES)>(a, merge_index, num_splits * cluster, merge_item,
+                                                     kvh, reinterpret_cast<float*>(smem_al), &merge_bar);
 }
-
-constexpr int WIDE_STAGES = 2;
-constexpr int NARROW_STAGES = 3;
 
 }  // namespace vx
 
@@ -1025,6 +1339,7 @@ static AttnArgs make_args(const void* q, void* out, const void* k_cache, const v
   a.group = group;
   a.page_size = page_size;
   a.window = window;
+  a.cluster = 1;
   a.scale_log2 = softmax_scale * 1.4426950408889634f;
   return a;
 }
@@ -1041,8 +1356,11 @@ VX_API int vx_attention(int kind, const void* q, void* out, const void* k_cache,
                         int* status, float* partial_o, float* partial_lse, const int* merge_items,
                         int* split_counters, int q_stride, int out_stride, int table_stride,
                         int num_kv_heads, int group, int page_size, long long num_pages,
-                        int window, float softmax_scale, cudaStream_t stream) {
+                        int window, float softmax_scale, int cluster, cudaStream_t stream) {
   if (num_items <= 0) return 0;
+  // Only the narrow bf16 family shares an item among the CTAs of a cluster.
+  if (cluster != 1 && (kind != 2 || (cluster != 2 && cluster != 4 && cluster != 8)))
+    return (int)cudaErrorInvalidValue;
   // The float32 family leaves merging to the merge kernel.
   if (kind == 0) split_counters = nullptr;
   AttnArgs a = make_args(q, out, k_cache, v_cache, block_tables, q_start, q_len, kv_len,
@@ -1073,26 +1391,91 @@ VX_API int vx_attention(int kind, const void* q, void* out, const void* k_cache,
     const size_t smem = attn_smem_bytes(false, WIDE_STAGES) + 1024;
     static bool configured = false;
     if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(attn_bf16_kernel<false, WIDE_STAGES>,
+      cudaError_t e = cudaFuncSetAttribute(attn_wide_kernel<WIDE_STAGES>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return (int)e;
       configured = true;
     }
-    launch_pdl(attn_bf16_kernel<false, WIDE_STAGES>, dim3(grid), dim3(128), smem, stream, a);
+    launch_pdl(attn_wide_kernel<WIDE_STAGES>, dim3(grid), dim3(128), smem, stream, a);
   } else if (kind == 2) {
     const size_t smem = attn_smem_bytes(true, NARROW_STAGES) + 1024;
     static bool configured = false;
     if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(attn_bf16_kernel<true, NARROW_STAGES>,
+      cudaError_t e = cudaFuncSetAttribute(attn_narrow_kernel<NARROW_STAGES>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return (int)e;
       configured = true;
     }
-    launch_pdl(attn_bf16_kernel<true, NARROW_STAGES>, dim3(grid), dim3(128), smem, stream, a);
+    if (cluster == 1) {
+      launch_pdl(attn_narrow_kernel<NARROW_STAGES>, dim3(grid), dim3(NARROW_THREADS), smem, stream, a);
+    } else {
+      a.cluster = cluster;
+      cudaLaunchConfig_t config = {};
+      config.gridDim = dim3((unsigned)num_items * (unsigned)cluster, (unsigned)num_kv_heads);
+      config.blockDim = dim3(NARROW_THREADS);
+      config.dynamicSmemBytes = smem;
+      config.stream = stream;
+      cudaLaunchAttribute attributes[2];
+      int count = 0;
+      const char* serialised = getenv("VELOX_B200_NO_PDL");
+      if (serialised == nullptr || serialised[0] != '1') {
+        attributes[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attributes[count].val.programmaticStreamSerializationAllowed = 1;
+        ++count;
+      }
+      attributes[count].id = cudaLaunchAttributeClusterDimension;
+      attributes[count].val.clusterDim.x = (unsigned)cluster;
+      attributes[count].val.clusterDim.y = 1;
+      attributes[count].val.clusterDim.z = 1;
+      ++count;
+      config.attrs = attributes;
+      config.numAttrs = count;
+      cudaError_t e = cudaLaunchKernelEx(&config, attn_narrow_kernel<NARROW_STAGES>, a);
+      if (e != cudaSuccess) return (int)e;
+    }
   } else {
     return (int)cudaErrorInvalidValue;
   }
   return (int)cudaGetLastError();
+}
+
+// What the planner needs to know about the narrow family: how many of its CTAs an SM holds
+// (by shared memory), and the largest cluster that may share a work item.
+VX_API int vx_attn_narrow_ctas_per_sm() {
+  const size_t smem = attn_smem_bytes(true, NARROW_STAGES) + 1024 + 8 * 1024;  // + static, reserved
+  const size_t per_sm = (size_t)228 * 1024;
+  const int n = (int)(per_sm / smem);
+  return n < 1 ? 1 : (n > 8 ? 8 : n);
+}
+VX_API int vx_attn_max_cluster() { return 8; }
+
+// How many clusters of `cluster` CTAs of the narrow family the device holds at a time (a
+// cluster lives inside one GPC, so this is less than the SM count suggests), or a negative
+// cudaError_t.  A launch of more clusters than this runs in waves.
+VX_API int vx_attn_narrow_max_active_clusters(int cluster) {
+  if (cluster != 2 && cluster != 4 && cluster != 8) return -(int)cudaErrorInvalidValue;
+  static int cached[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
+  if (cached[cluster] > 0) return cached[cluster];
+  const size_t smem = attn_smem_bytes(true, NARROW_STAGES) + 1024;
+  cudaError_t e = cudaFuncSetAttribute(attn_narrow_kernel<NARROW_STAGES>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return -(int)e;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3((unsigned)cluster * 64u, 1, 1);
+  config.blockDim = dim3(NARROW_THREADS);
+  config.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeClusterDimension;
+  attribute[0].val.clusterDim.x = (unsigned)cluster;
+  attribute[0].val.clusterDim.y = 1;
+  attribute[0].val.clusterDim.z = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  int clusters = 0;
+  e = cudaOccupancyMaxActiveClusters(&clusters, attn_narrow_kernel<NARROW_STAGES>, &config);
+  if (e != cudaSuccess) return -(int)e;
+  cached[cluster] = clusters;
+  return clusters;
 }
 
 // max_rows: the most rows a merge item has (the height of the tiles that were split).
@@ -1216,7 +1599,7 @@ int vx_attention_decode_static(const void* q, void* out, const void* k_cache, co
         return static_fail(error, error_capacity, e != cudaSuccess ? (int)e : (int)cudaErrorInvalidSymbol,
                            "vx_attention_decode_static: cudaGetSymbolAddress of the scratch array: %s",
                            cudaGetErrorString(e));
-      e = cudaFuncSetAttribute(attn_bf16_kernel<true, NARROW_STAGES>,
+      e = cudaFuncSetAttribute(attn_narrow_kernel<NARROW_STAGES>,
                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e == cudaSuccess)
         e = cudaMemset((unsigned char*)address + STATIC_O_BYTES + STATIC_LSE_BYTES, 0,
@@ -1262,7 +1645,7 @@ int vx_attention_decode_static(const void* q, void* out, const void* k_cache, co
                          cudaGetErrorString(e));
   }
   const dim3 grid(num_items, num_kv_heads);
-  e = launch_pdl(attn_bf16_kernel<true, NARROW_STAGES>, dim3(grid), dim3(128), smem, stream, a);
+  e = launch_pdl(attn_narrow_kernel<NARROW_STAGES>, dim3(grid), dim3(NARROW_THREADS), smem, stream, a);
   if (e != cudaSuccess)
     return static_fail(error, error_capacity, (int)e, "vx_attention_decode_static: launch: %s",
                        cudaGetErrorString(e));

@@ -53,6 +53,7 @@ class DevicePlan:
     merge_items: Optional[torch.Tensor] = None
     num_merges: int = 0
     merge_rows: int = 16  # the most rows a merge item can have (height of the split tiles)
+    cluster: int = 1  # CTAs that share each item of the narrow bf16 kind
     # Zeroed counters for the fused merge of the bfloat16 kernels; None: a merge kernel runs.
     split_counters: Optional[torch.Tensor] = None
     partial_o: Optional[torch.Tensor] = None
@@ -318,16 +319,10 @@ class ModelRunner:
         # Attention work, one layout per distinct (cache group, head grouping, window).
         host_plans = {}
         for group, signature in self._signatures:
-            num_kv_heads, heads_per_kv, window = signature
-            options = dict(
-                num_kv_heads=num_kv_heads, group=heads_per_kv, window=window,
-                use_f32=self.dtype == torch.float32, target_ctas=2 * self.num_sms,
-            )
-            options.update(self.plan_overrides)
-            opt = ap.PlanOptions(**options)
+            opt = self._plan_options(signature)
             if padded:
-                splits = self._padded_splits(num_seqs, opt)
-                plan = ap.plan_attention(q_lens, kv_lens, opt, fixed_splits=splits)
+                splits, cluster = self._padded_splits(num_seqs, opt)
+                plan = ap.plan_attention(q_lens, kv_lens, opt, fixed_splits=splits, fixed_cluster=cluster)
                 plan = ap.pad_plan(plan, num_seqs, splits, opt)
             else:
                 plan = ap.plan_attention(q_lens, kv_lens, opt)
@@ -369,7 +364,7 @@ class ModelRunner:
         plans: Dict[Tuple[Optional[int], Tuple], DevicePlan] = {}
         for key, plan in host_plans.items():
             entry, merge = plan_where[key]
-            device_plan = DevicePlan()
+            device_plan = DevicePlan(cluster=plan.cluster)
             for kind, (offset, shape) in entry.items():
                 count = shape[0]
                 device_plan.launches.append((kind, dev[offset : offset + count * 8].view(count, 8), count))
@@ -408,14 +403,41 @@ class ModelRunner:
         return ctx, view("ids"), view("logit_rows"), num_logit_rows
 
     # ------------------------------------------------------------------ decode steps as CUDA graphs
-    def _padded_splits(self, num_seqs: int, opt: "ap.PlanOptions") -> int:
-        """Key-range splits of a padded single-token step: enough work items to fill the GPU
-        at this batch size, the same number for every sequence whatever its length."""
+    def _plan_options(self, signature) -> "ap.PlanOptions":
+        """How attention work is cut for layers of this (KV heads, heads per KV head, window)."""
+        num_kv_heads, heads_per_kv, window = signature
+        use_f32 = self.dtype == torch.float32
+        options = dict(num_kv_heads=num_kv_heads, group=heads_per_kv, window=window, use_f32=use_f32,
+                       target_ctas=2 * self.num_sms)
+        if not use_f32:
+            head_dim = max(self.model.head_dims())
+            options["narrow_target_ctas"] = kernels.narrow_attention_slots(head_dim) * self.num_sms
+            options["narrow_max_cluster"] = kernels.max_attention_cluster(head_dim)
+            options["narrow_cluster_limits"] = kernels.attention_cluster_limits(head_dim)
+        if "target_ctas" in self.plan_overrides and "narrow_target_ctas" not in self.plan_overrides:
+            options["narrow_target_ctas"] = self.plan_overrides["target_ctas"]
+        options.update(self.plan_overrides)
+        return ap.PlanOptions(**options)
+
+    def _padded_splits(self, num_seqs: int, opt: "ap.PlanOptions") -> Tuple[int, int]:
+        """(splits through memory, cluster size) of a padded single-token step: enough CTAs to
+        fill the GPU at this batch size, the same for every sequence whatever its length."""
         tiles = -(-opt.group // 16)
         per_split = max(1, num_seqs * opt.num_kv_heads * tiles)
-        # Rounded down: all work items should be resident at once (two CTAs per SM), a few
-        # more than that would run as a second wave after the first has finished.
-        return max(1, min(32, opt.target_ctas // per_split))
+        narrow = not opt.use_f32 and opt.group <= opt.narrow_max_rows
+        target = opt.narrow_target_ctas if narrow and opt.narrow_target_ctas is not None else opt.target_ctas
+        # Rounded down: all CTAs should be resident at once; a few more than that would run as
+        # a second wave after the first has finished.
+        wanted = max(1, target // per_split)
+        if not narrow:
+            return max(1, min(32, wanted)), 1
+        cluster = ap.choose_cluster(opt, per_split, wanted)
+        if cluster == 1:
+            return max(1, min(32, wanted)), 1
+        # The layout is the same for every length, so the longest sequence decides whether
+        # splitting through memory as well is worth its slower merge.
+        longest = self.cache.max_model_len
+        return max(1, min(32, wanted // cluster, longest // (cluster * opt.narrow_global_split_keys))), cluster
 
     def _graph_eligible(self, chunks: Sequence[StepChunk]) -> bool:
         if not self.enable_graphs or self._graphs_broken:
@@ -507,12 +529,8 @@ class ModelRunner:
                 tables[s, : len(t)] = t
         kv_lens = positions + 1
         for key, (entry_where, merge_where) in plan_where.items():
-            num_kv_heads, heads_per_kv, window = key[1]
-            options = dict(num_kv_heads=num_kv_heads, group=heads_per_kv, window=window,
-                           use_f32=self.dtype == torch.float32, target_ctas=2 * self.num_sms)
-            options.update(self.plan_overrides)
-            opt = ap.PlanOptions(**options)
-            splits = self._padded_splits(bucket, opt)
+            opt = self._plan_options(key[1])
+            splits, _ = self._padded_splits(bucket, opt)
             kind, items, merges, _ = ap.plan_single_tokens(kv_lens, bucket, splits, opt)
             offset, shape = entry_where[kind]
             host_np[offset : offset + items.size] = items.reshape(-1)

@@ -33,6 +33,10 @@ class AttentionPlan:
     merge_items: np.ndarray = field(default_factory=lambda: np.zeros((0, ITEM_WIDTH), np.int32))
     # Rows of float32 scratch ([rows, D] and [rows]) the splits write.
     partial_rows: int = 0
+    # CTAs of a thread-block cluster that share each item of the narrow bf16 kind: every CTA
+    # takes a run of the item's key tiles and they merge on the chip.  The splits above are
+    # what is left for the scratch in memory; the two multiply.
+    cluster: int = 1
 
 
 @dataclass(frozen=True)
@@ -48,6 +52,30 @@ class PlanOptions:
     max_splits: int = 64
     # Portions with at most this many rows use the narrow (16-row) bf16 family.
     narrow_max_rows: int = 64
+    # The same target for the narrow bf16 family, whose CTAs an SM holds fewer of
+    # (None: target_ctas), and the largest cluster that may share one of its items.
+    narrow_target_ctas: Optional[int] = None
+    narrow_max_cluster: int = 1
+    # ((cluster size, clusters of that size the device holds at a time), ...): a size is used
+    # only if every (tile, KV head) of the step gets its cluster in one wave.  Empty: no limit.
+    narrow_cluster_limits: Tuple[Tuple[int, int], ...] = ()
+    # With a cluster, a key range is split through memory as well only if that leaves every
+    # CTA at least this many keys: the merge through memory is the slow one.
+    narrow_global_split_keys: int = 1024
+
+
+def choose_cluster(opt: PlanOptions, pairs: int, wanted: int) -> int:
+    """Cluster size for the narrow kind when `pairs` (tile, KV head) pairs each want `wanted`
+    CTAs: the largest allowed power of two that is not more than wanted and fits in one wave."""
+    limits = dict(opt.narrow_cluster_limits)
+    size = 1
+    while size * 2 <= opt.narrow_max_cluster:
+        size *= 2
+    while size > 1:
+        if size <= wanted and (size not in limits or pairs <= limits[size]):
+            return size
+        size //= 2
+    return 1
 
 
 def _key_range(q_len: int, kv_len: int, group: int, window: Optional[int], row_begin: int,
@@ -65,9 +93,11 @@ def plan_attention(
     kv_lens: Sequence[int],
     opt: PlanOptions,
     fixed_splits: Optional[int] = None,
+    fixed_cluster: int = 1,
 ) -> AttentionPlan:
     """Lay out one step.  ``fixed_splits`` forces that many splits for every tile (some may be
-    empty), which gives a layout whose shape depends on the batch size only."""
+    empty) and ``fixed_cluster`` the cluster size of the narrow kind, which gives a layout whose
+    shape depends on the batch size only."""
     tiles: List[Tuple[int, int, int, int, int, int]] = []  # kind, seq, row_begin, row_count, lo, hi
     for seq, (q_len, kv_len) in enumerate(zip(q_lens, kv_lens)):
         rows = q_len * opt.group
@@ -84,6 +114,27 @@ def plan_attention(
             tiles.append((kind, seq, row_begin, row_count, lo, hi))
 
     base_ctas = len(tiles) * opt.num_kv_heads
+
+    def wanted_ctas(kind: int, span: int) -> int:
+        """CTAs a tile's key range should be spread over so that the step fills the GPU."""
+        target = opt.target_ctas
+        if kind == KIND_BF16_NARROW and opt.narrow_target_ctas is not None:
+            target = opt.narrow_target_ctas
+        if base_ctas >= target:
+            return 1
+        # Rounded down: the items should all be resident at once, not spill into a second wave.
+        wanted = target // max(base_ctas, 1)
+        return max(1, min(wanted, span // max(opt.min_split_keys, 1)))
+
+    # One cluster size for all items of the narrow kind (it is a property of the launch).
+    cluster = 1
+    if fixed_splits is not None:
+        cluster = max(1, fixed_cluster)
+    elif opt.narrow_max_cluster > 1:
+        narrow = [wanted_ctas(k, hi - lo) for k, _, _, _, lo, hi in tiles if k == KIND_BF16_NARROW]
+        if narrow:
+            cluster = choose_cluster(opt, len(narrow) * opt.num_kv_heads, max(narrow))
+
     per_kind: Dict[int, List[List[int]]] = {}
     merges: List[List[int]] = []
     partial_rows = 0
@@ -91,12 +142,11 @@ def plan_attention(
         span = hi - lo
         if fixed_splits is not None:
             splits = fixed_splits
-        elif base_ctas >= opt.target_ctas:
-            splits = 1
         else:
-            # Rounded down: the items should all be resident at once, not spill into a second wave.
-            wanted = opt.target_ctas // max(base_ctas, 1)
-            splits = max(1, min(wanted, span // max(opt.min_split_keys, 1), opt.max_splits))
+            wanted = wanted_ctas(kind, span)
+            if kind == KIND_BF16_NARROW and cluster > 1:
+                wanted = min(wanted // cluster, span // (cluster * max(opt.narrow_global_split_keys, 1)))
+            splits = max(1, min(wanted, opt.max_splits))
         out = per_kind.setdefault(kind, [])
         if splits <= 1:
             out.append([seq, row_begin, row_count, lo, hi, -1, 0, 0])
@@ -114,7 +164,7 @@ def plan_attention(
             out.append([seq, row_begin, row_count, begin, end, partial_rows, merge_index, splits])
             partial_rows += stride
 
-    plan = AttentionPlan(partial_rows=partial_rows)
+    plan = AttentionPlan(partial_rows=partial_rows, cluster=cluster)
     for kind, rows_ in per_kind.items():
         arr = np.asarray(rows_, dtype=np.int32).reshape(-1, ITEM_WIDTH)
         if fixed_splits is None and len(arr) > 1:
@@ -145,7 +195,7 @@ def pad_plan(plan: AttentionPlan, num_seqs: int, splits: int, opt: PlanOptions) 
     padding = np.zeros((want_items - len(items), ITEM_WIDTH), np.int32)
     padding[:, 0] = -1
     padding[:, 5] = -1
-    out = AttentionPlan(items={kind: np.concatenate([items, padding], axis=0)})
+    out = AttentionPlan(items={kind: np.concatenate([items, padding], axis=0)}, cluster=plan.cluster)
     if splits > 1:
         want_merges = num_seqs * tiles
         merge_padding = np.zeros((want_merges - len(plan.merge_items), ITEM_WIDTH), np.int32)

@@ -74,8 +74,12 @@ def attention_lib(head_dim: int):
         lib = build.load_attention(head_dim)
         lib.vx_attention.argtypes = [
             _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr,
-            _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _c_f, _ptr,
+            _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _c_f, _c_int, _ptr,
         ]
+        lib.vx_attn_narrow_ctas_per_sm.restype = _c_int
+        lib.vx_attn_max_cluster.restype = _c_int
+        lib.vx_attn_narrow_max_active_clusters.restype = _c_int
+        lib.vx_attn_narrow_max_active_clusters.argtypes = [_c_int]
         lib.vx_attention_merge.argtypes = [
             _c_int, _ptr, _ptr, _ptr, _c_int, _c_int, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr,
         ]
@@ -334,11 +338,15 @@ def attention(
     merge_items: Optional[torch.Tensor] = None,
     split_counters: Optional[torch.Tensor] = None,
     status: Optional[torch.Tensor] = None,
+    cluster: int = 1,
 ) -> None:
     """Run ``num_items`` work items (see attention.cu for their layout) of one kernel family.
 
     With ``merge_items`` and ``split_counters`` (int32, zero, one per merge item and KV head)
     the bfloat16 families merge split key ranges themselves: the last split to finish does it.
+    ``cluster`` (1, 2, 4 or 8; narrow bfloat16 family only) CTAs share every item as a
+    thread-block cluster: each takes a run of the item's key tiles and they merge through
+    distributed shared memory.
     """
     want = torch.float32 if kind == ATTN_F32 else torch.bfloat16
     _need(q, want, "q")
@@ -367,9 +375,33 @@ def attention(
                          q.shape[1], out.shape[1],
                          block_tables.shape[1], num_kv_heads, num_heads // num_kv_heads,
                          k_cache.shape[1], k_cache.shape[0], int(window or 0), float(softmax_scale),
-                         _stream()),
+                         int(cluster), _stream()),
         "attention",
     )
+
+
+def narrow_attention_slots(head_dim: int) -> int:
+    """Work items of the narrow bfloat16 family that one SM holds at a time."""
+    return int(attention_lib(head_dim).vx_attn_narrow_ctas_per_sm())
+
+
+def max_attention_cluster(head_dim: int) -> int:
+    return int(attention_lib(head_dim).vx_attn_max_cluster())
+
+
+def attention_cluster_limits(head_dim: int) -> tuple:
+    """((cluster size, clusters of that size the device holds at a time), ...), largest first."""
+    _require_cuda()
+    lib = attention_lib(head_dim)
+    limits = []
+    size = max_attention_cluster(head_dim)
+    while size >= 2:
+        count = int(lib.vx_attn_narrow_max_active_clusters(size))
+        if count < 0:
+            raise KernelError(f"cluster occupancy query for size {size}: CUDA error {-count}")
+        limits.append((size, count))
+        size //= 2
+    return tuple(limits)
 
 
 _default_status = None

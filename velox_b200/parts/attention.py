@@ -78,6 +78,7 @@ class Attention(Mixer):
                 self.num_kv_heads, self.head_dim, self.window, self.softmax_scale,
                 merge_items=plan.merge_items, split_counters=plan.split_counters,
                 status=ctx.status,
+                cluster=plan.cluster if kind == kernels.ATTN_BF16_NARROW else 1,
             )
         if plan.num_merges and plan.split_counters is None:
             kernels.attention_merge(
