@@ -43,7 +43,7 @@ MODEL_1P5B = {
 FULL_LAYERS = 28
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
-BLOCK_SIZE = int(os.environ.get("VELOX_BENCH_BLOCK", "16"))
+BLOCK_SIZE = 64
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 

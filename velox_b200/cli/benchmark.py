@@ -45,7 +45,7 @@ def parse_args(argv: Optional[List[str]] = None) -> argparse.Namespace:
     parser.add_argument("--max-num-seqs", type=int, default=32)
     parser.add_argument("--max-num-batched-tokens", type=int, default=2048)
     parser.add_argument("--max-prefill-chunk-size", type=int, default=512)
-    parser.add_argument("--block-size", type=int, default=16)
+    parser.add_argument("--block-size", type=int, default=64, help="keys per cache page (a power of two)")
     parser.add_argument("--num-gpu-blocks", type=int, default=None)
     parser.add_argument("--gpu-memory-utilization", type=float, default=0.85)
     parser.add_argument("--no-cuda-graphs", action="store_true")

@@ -925,6 +925,159 @@ __global__ void __launch_bounds__(128) attn_wide_kernel(const __grid_constant__ 
 // A cluster of 2, 4 or 8 such CTAs may share one work item: CTA `rank` takes a run of the
 // item's key tiles, and the CTAs merge through distributed shared memory by rows.
 // ---------------------------------------------------------------------------------------------
+// 8x8 transpose of 16-bit elements across a warp: a thread that held (row lane / 4, columns
+// 2 * (lane % 4) + {0, 1}) gets (row' = lane / 4 of the transposed matrix, columns' likewise).
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t v) {
+  uint32_t r;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(v));
+  return r;
+}
+
+// The tile loop of one consumer warp of the narrow family, keys on the M side of the tensor
+// cores: S^T[16 keys x 8 NR rows] = K Q^T and O^T[D x 8 NR rows] += V^T P^T.  Few rows are what
+// a decode step has (the query heads of one KV group), and with them on the N side eight rows
+// cost one n-tile instead of a 16-row m-tile that is half padding: NR = 1 does half the
+// tensor-core work of the rows-on-M form, which is what bounds this kernel on the legacy mma
+// path.  Thread (g = lane / 4, q = lane % 4) holds, of an accumulator tile, keys (or dims)
+// g and g + 8 of rows 8 j + 2 q + {0, 1}.
+// Afterwards the warp's sums, maxima and denominators are in registers; write_rows() puts them
+// into the cross-warp merge buffer.
+template <int NR>
+struct NarrowWarp {
+  float o[D / 16][NR][4];
+  float m[NR][2], l[NR][2];
+  int pos[NR][2];
+  uint32_t qb[D / 16][2 * NR];
+
+  __device__ __forceinline__ void init(const __nv_bfloat16* q_s, int row_begin, int row_count,
+                                       int ctx, int group, int lane) {
+#pragma unroll
+    for (int mt = 0; mt < D / 16; ++mt)
+#pragma unroll
+      for (int j = 0; j < NR; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[mt][j][e] = 0.f;
+#pragma unroll
+    for (int j = 0; j < NR; ++j)
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        m[j][i] = -CUDART_INF_F;
+        l[j][i] = 0.f;
+        const int r = 8 * j + 2 * (lane & 3) + i;
+        pos[j][i] = r < row_count ? ctx + (row_begin + r) / group : -1;
+      }
+    // Q as the B operand, kept for the whole item: matrices (rows 0-7, dims lo), (rows 0-7,
+    // dims hi), (rows 8-15, dims lo), (rows 8-15, dims hi) of every 16-dim step.
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      uint32_t q4[4];
+      ldmatrix_x4(q4, q_s + ((lane & 7) + (lane >> 4) * 8) * B_LD + kk * 16 + ((lane >> 3) & 1) * 8);
+#pragma unroll
+      for (int x = 0; x < 2 * NR; ++x) qb[kk][x] = q4[x];
+    }
+  }
+
+  // Keys [n0 + key0, n0 + key0 + 16) of the tile in k_s / v_s.
+  __device__ __forceinline__ void tile(const __nv_bfloat16* k_s, const __nv_bfloat16* v_s, int key0,
+                                       int nbase, int kv_begin, int kv_end, int window,
+                                       float scale_log2, int lane) {
+    float s[NR][4];
+#pragma unroll
+    for (int j = 0; j < NR; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      uint32_t ka[4];
+      ldmatrix_x4(ka, kv_chunk(k_s, key0 + (lane & 15), kk * 16 + (lane >> 4) * 8));
+#pragma unroll
+      for (int j = 0; j < NR; ++j) mma_bf16(s[j], ka, qb[kk][2 * j], qb[kk][2 * j + 1]);
+    }
+    // Masks and the running softmax of the rows this thread holds (two per n-tile); a row's
+    // keys lie in this thread's two halves and in the eight lanes with the same lane % 4.
+    const int g = lane >> 2;
+    float alpha[NR][2];
+#pragma unroll
+    for (int j = 0; j < NR; ++j) {
+      float mx[2] = {-CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = e & 1;
+        const int n = nbase + g + 8 * (e >> 1);
+        float v = s[j][e] * scale_log2;
+        if (pos[j][i] < 0 || !key_visible(n, pos[j][i], kv_begin, kv_end, window)) v = -CUDART_INF_F;
+        s[j][e] = v;
+        mx[i] = fmaxf(mx[i], v);
+      }
+      float m_safe[2];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 4));
+        mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 8));
+        mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 16));
+        const float m_new = fmaxf(m[j][i], mx[i]);
+        m_safe[i] = m_new == -CUDART_INF_F ? 0.f : m_new;
+        alpha[j][i] = exp2f(m[j][i] - m_safe[i]);
+        m[j][i] = m_new;
+      }
+      float sum[2] = {0.f, 0.f};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float p = exp2f(s[j][e] - m_safe[e & 1]);
+        s[j][e] = p;
+        sum[e & 1] += p;
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 4);
+        sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 8);
+        sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 16);
+        l[j][i] = l[j][i] * alpha[j][i] + sum[i];
+      }
+    }
+    // P^T as the B operand: the accumulator layout, transposed eight by eight.
+    uint32_t pb[NR][2];
+#pragma unroll
+    for (int j = 0; j < NR; ++j) {
+      pb[j][0] = movmatrix_trans(pack_bf16(s[j][0], s[j][1]));
+      pb[j][1] = movmatrix_trans(pack_bf16(s[j][2], s[j][3]));
+    }
+#pragma unroll
+    for (int mt = 0; mt < D / 16; ++mt) {
+      uint32_t va[4];
+      ldmatrix_x4_trans(va, kv_chunk(v_s, key0 + (lane & 7) + (lane >> 4) * 8,
+                                     mt * 16 + ((lane >> 3) & 1) * 8));
+#pragma unroll
+      for (int j = 0; j < NR; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[mt][j][e] *= alpha[j][e & 1];
+        mma_bf16(o[mt][j], va, pb[j][0], pb[j][1]);
+      }
+    }
+  }
+
+  // mo [16 rows][ld] sums, mm / ml [16] maxima and denominators of this warp.
+  __device__ __forceinline__ void write_rows(float* mo, float* mm, float* ml, int ld, int lane) const {
+    const int g = lane >> 2, q = lane & 3;
+#pragma unroll
+    for (int j = 0; j < NR; ++j)
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int r = 8 * j + 2 * q + i;
+        float* dst = mo + (size_t)r * ld + g;
+#pragma unroll
+        for (int mt = 0; mt < D / 16; ++mt) {
+          dst[mt * 16] = o[mt][j][i];
+          dst[mt * 16 + 8] = o[mt][j][i + 2];
+        }
+        if (g == 0) {
+          mm[r] = m[j][i];
+          ml[r] = l[j][i];
+        }
+      }
+  }
+};
+
 constexpr int NARROW_GROUPS = 2;
 constexpr int NARROW_CONSUMERS = NARROW_GROUPS * 4 * 32;
 constexpr int NARROW_THREADS = NARROW_CONSUMERS + 32;
@@ -995,7 +1148,6 @@ __device__ __forceinline__ void produce_kv_tile(const AttnArgs& a, __nv_bfloat16
 
 template <int STAGES>
 __global__ void __launch_bounds__(NARROW_THREADS) attn_narrow_kernel(const __grid_constant__ AttnArgs a) {
-  constexpr int NT = 2;
   constexpr int TILE = KV_TILE_ELEMS;
   constexpr int WARPS = NARROW_GROUPS * 4;  // consumer warps
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -1069,13 +1221,6 @@ __global__ void __launch_bounds__(NARROW_THREADS) attn_narrow_kernel(const __gri
   }
   __syncthreads();
 
-  float o[D / 8][4];
-#pragma unroll
-  for (int jd = 0; jd < D / 8; ++jd)
-#pragma unroll
-    for (int e = 0; e < 4; ++e) o[jd][e] = 0.f;
-  float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
-
   if (warp == WARPS) {
     // ------------------------------------------------------------------------------ producer
     // Tiles of old keys are asked for at once; the first tile that may hold one of this
@@ -1104,57 +1249,45 @@ __global__ void __launch_bounds__(NARROW_THREADS) attn_narrow_kernel(const __gri
     load_q_tile<16>(a, q_s, q_start, row_begin, row_count, kvh, (int)threadIdx.x, NARROW_CONSUMERS);
     asm volatile("bar.sync 1, %0;" ::"n"(NARROW_CONSUMERS) : "memory");
     VX_TRACE_MARK(1);
-    const int group = warp >> 2;
-    const int key0 = (warp & 3) * 16;  // the keys of a tile this warp works on
-    int pos[2];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int r = (lane >> 2) + 8 * h;
-      pos[h] = r < row_count ? ctx + (row_begin + r) / a.group : -1;
-    }
-    bool alive = true;
-    for (int t = group; t < num_tiles; t += NARROW_GROUPS) {
-      const int st = t % STAGES, round = t / STAGES;
-      const int n0 = n_first + t * B_BN;
-      if (alive) alive = mbar_wait(smem_u32(&kv_full[st]), (uint32_t)round & 1u, a.status);
-      if (t == group) VX_TRACE_MARK(2);
-      if (alive) {
-        const __nv_bfloat16* k_s = kv_s + st * 2 * TILE;
-        const __nv_bfloat16* v_s = k_s + TILE;
-        float s[NT][4];
-        warp_qk<NT>(s, q_s, k_s, key0, lane);
-        softmax_step<NT>(s, o, m, l, pos, n0 + key0, kv_begin, kv_end, a.window, a.scale_log2, lane);
-        warp_pv<NT>(o, s, v_s, key0, lane);
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&kv_empty[st]));  // this warp has read the stage
-    }
-    VX_TRACE_MARK(3);
   }
-
-  // Merge the eight warps (each saw a quarter of every second tile) through shared memory,
-  // which no copy is writing any more: every tile asked for has been waited for.  Rows are
-  // NARROW_MERGE_LD floats apart: the fragment stores below then hit every bank once.
-  __syncthreads();
+  // The merge buffer lies over the stages: [WARPS][16][MD] sums, then maxima and denominators.
+  // Rows of up to eight (a decode token's heads of one KV group) take the form with one n-tile.
   constexpr int MD = NARROW_MERGE_LD;
   float* mo = reinterpret_cast<float*>(smem_al);  // [WARPS][16][MD]
   float* mm = mo + WARPS * 16 * MD;                 // [WARPS][16]
   float* ml = mm + WARPS * 16;                      // [WARPS][16]
-  if (warp < WARPS) {
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int r = (lane >> 2) + 8 * h;
-      float* dst = mo + ((size_t)warp * 16 + r) * MD + 2 * (lane & 3);
-#pragma unroll
-      for (int jd = 0; jd < D / 8; ++jd)
-        *reinterpret_cast<float2*>(dst + jd * 8) = make_float2(o[jd][2 * h], o[jd][2 * h + 1]);
-      if ((lane & 3) == 0) {
-        mm[warp * 16 + r] = m[h];
-        ml[warp * 16 + r] = l[h];
+  auto consume = [&](auto& state) {
+    if (warp < WARPS) {
+      state.init(q_s, row_begin, row_count, ctx, a.group, lane);
+      const int group = warp >> 2;
+      const int key0 = (warp & 3) * 16;  // the keys of a tile this warp works on
+      bool alive = true;
+      for (int t = group; t < num_tiles; t += NARROW_GROUPS) {
+        const int st = t % STAGES, round = t / STAGES;
+        const int n0 = n_first + t * B_BN;
+        if (alive) alive = mbar_wait(smem_u32(&kv_full[st]), (uint32_t)round & 1u, a.status);
+        if (t == group) VX_TRACE_MARK(2);
+        if (alive) {
+          const __nv_bfloat16* k_s = kv_s + st * 2 * TILE;
+          state.tile(k_s, k_s + TILE, key0, n0 + key0, kv_begin, kv_end, a.window, a.scale_log2, lane);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&kv_empty[st]));  // this warp has read the stage
       }
+      VX_TRACE_MARK(3);
     }
+    // No copy is writing the stages any more: every tile asked for has been waited for.
+    __syncthreads();
+    if (warp < WARPS) state.write_rows(mo + (size_t)warp * 16 * MD, mm + warp * 16, ml + warp * 16, MD, lane);
+    __syncthreads();
+  };
+  if (row_count <= 8) {
+    NarrowWarp<1> state;
+    consume(state);
+  } else {
+    NarrowWarp<2> state;
+    consume(state);
   }
-  __syncthreads();
   // Eight threads per row (threads 0..127); a thread takes dims 2 * seg + 16 * i, so the eight
   // cover 64 consecutive bytes of the row at a time.
   int r = threadIdx.x >> 3;
