@@ -266,10 +266,14 @@ def run_own(args):
             tok_s, _, _, _ = decode_point(batch, max(8, args.steps // 2), 3)
             points[f"decode_b{batch}"] = round(tok_s, 1)
 
-    # End to end through the entry point: Engine.step with host tokens in and out.
-    prompts = [rng.integers(0, vocab, CONTEXT - args.steps - args.warmup - 8).tolist() for _ in range(args.batch)]
-    requests = [Request(f"e2e{i}", p, SamplingParams(temperature=0.0, max_tokens=args.steps + args.warmup + 4,
-                                                     ignore_eos=True)) for i, p in enumerate(prompts)]
+    # End to end through the entry point: Engine.step with host tokens in and out.  Prompts are
+    # prefilled in turn, so the first request decodes while the others still prefill (two
+    # portions each); max_tokens leaves every request alive until the timed steps are over.
+    head_start = 2 * args.batch
+    budget = args.steps + args.warmup + head_start + 8
+    prompts = [rng.integers(0, vocab, CONTEXT - budget).tolist() for _ in range(args.batch)]
+    requests = [Request(f"e2e{i}", p, SamplingParams(temperature=0.0, max_tokens=budget, ignore_eos=True))
+                for i, p in enumerate(prompts)]
     for request in requests:
         engine.add_request(request)
     while any(not r.is_decoding or r.num_output_tokens < 1 for r in requests):
@@ -278,15 +282,18 @@ def run_own(args):
         engine.step()
     torch.cuda.synchronize()
     produced_before = sum(r.num_output_tokens for r in requests)
+    meta_bytes = 0
     t_start = time.perf_counter()
     for _ in range(args.steps):
         engine.step()
+        meta_bytes = max(meta_bytes, runner.last_meta_bytes)  # the step's arrays, one pinned-memory copy
     torch.cuda.synchronize()
     e2e_seconds = time.perf_counter() - t_start
     produced = sum(r.num_output_tokens for r in requests) - produced_before
+    if produced != args.steps * args.batch:
+        raise RuntimeError(f"e2e: {produced} tokens in {args.steps} steps of {args.batch} requests")
     for request in requests:
         engine.abort_request(request.request_id)
-    meta_bytes = runner.last_meta_bytes  # the step's arrays, one pinned-memory copy
     e2e = {"value": round(produced / e2e_seconds, 1), "unit": "tokens/s",
            "h2d_bytes_per_step": meta_bytes, "d2h_bytes_per_step": 4 * args.batch}
 

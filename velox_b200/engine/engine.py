@@ -17,6 +17,7 @@ from __future__ import annotations
 import json
 import logging
 import os
+import gc
 import time
 from typing import Dict, FrozenSet, Iterable, List, Optional, Sequence
 
@@ -134,6 +135,11 @@ class Engine:
         }
         self.num_steps = 0
         self._timing = True
+        # What exists now (modules, weights, the tables above) lives as long as the engine.
+        # Moved to the permanent generation, it is not walked again by every full collection:
+        # such a walk is a pause of some 10 ms in the middle of decoding.
+        gc.collect()
+        gc.freeze()
 
     # ------------------------------------------------------------------ construction
     @classmethod
