@@ -637,3 +637,58 @@ def test_gemm_bf16_swiglu(k, status, T, I, K):
     want = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
     assert (out.double().cpu() - want.cpu()).abs().max().item() <= 1e-2 * want.abs().max().item()
     assert int(status[0]) == 0
+
+
+@pytest.mark.parametrize("T,N,K,splits", [(8, 2048, 1536, 8), (1, 256, 704, 4), (64, 1536, 1536, 8),
+                                          (17, 136, 480, 1), (33, 331, 240, 2), (16, 384, 200, 1)])
+@pytest.mark.parametrize("mode", ["bf16", "f32"])
+def test_gemm_bf16_makes_its_input_norm(k, status, T, N, K, splits, mode):
+    """The projection of rmsnorm(resid) * w_norm with the norm made inside the kernel: the X
+    tiles come from the float32 rows, 1 / rms is applied to the accumulator, and with split K
+    the sums of squares are added up across the cluster."""
+    gen = torch.Generator().manual_seed(N + K + T)
+    rows = T + 3
+    resid = (torch.randn(rows, K + 4, generator=gen) * 3).cuda()[:, :K]  # a row pitch that is not K
+    resid[:, 5] *= 20  # one dimension dominates the mean square, as in real residual streams
+    w_norm = (torch.rand(K, generator=gen) + 0.5).cuda()
+    eps = 1e-6
+    w = (torch.randn(N, K, generator=gen) / math.sqrt(K)).to(torch.bfloat16).cuda()
+    bias = torch.randn(N, generator=gen).cuda()
+    r64 = resid[:T].double()
+    normed = r64 * torch.rsqrt((r64 * r64).mean(-1, keepdim=True) + eps) * w_norm.double()
+    want = normed @ w.double().T + bias.double()
+    scale = max(want.abs().max().item(), 1.0)
+    if mode == "bf16":
+        out = torch.full((rows, N), 9.0, dtype=torch.bfloat16, device="cuda")
+        k.gemm_bf16_normed(resid, w_norm, eps, w, bias, out, k.GEMM_OUT_BF16, T, status, splits=splits)
+    else:
+        out = torch.full((rows, N), 9.0, dtype=torch.float32, device="cuda")
+        k.gemm_bf16_normed(resid, w_norm, eps, w, bias, out, k.GEMM_OUT_F32, T, status, splits=splits)
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0
+    # The inputs are rounded to bfloat16 once (2^-9 relative each), as the norm kernel's output is.
+    assert (out[:T].double().cpu() - want.cpu()).abs().max().item() <= 1e-2 * scale
+    assert torch.all(out[T:] == 9.0)
+    # It agrees with the two-kernel route to within the rounding of the normalised input.
+    x = torch.zeros(rows, K, dtype=torch.bfloat16, device="cuda")
+    k.add_rmsnorm(resid.contiguous(), None, w_norm, eps, x, T, None, False)
+    two = torch.zeros_like(out)
+    k.gemm_bf16(x, w, bias, two, k.GEMM_OUT_BF16 if mode == "bf16" else k.GEMM_OUT_F32, T, status, splits=splits)
+    assert (out[:T].double() - two[:T].double()).abs().max().item() <= 1e-2 * scale
+
+
+@pytest.mark.parametrize("T,I,K", [(8, 8960, 1536), (40, 704, 256), (3, 200, 240)])
+def test_gemm_bf16_swiglu_makes_its_input_norm(k, status, T, I, K):
+    gen = torch.Generator().manual_seed(I + T)
+    resid = (torch.randn(T, K, generator=gen) * 2).cuda()
+    w_norm = (torch.rand(K, generator=gen) + 0.5).cuda()
+    eps = 1e-5
+    w = (torch.randn(2 * I, K, generator=gen) * 2 / math.sqrt(K)).to(torch.bfloat16).cuda()
+    out = torch.zeros(T, I, dtype=torch.bfloat16, device="cuda")
+    k.gemm_bf16_normed(resid, w_norm, eps, w, None, out, k.GEMM_SWIGLU, T, status)
+    r64 = resid.double()
+    normed = r64 * torch.rsqrt((r64 * r64).mean(-1, keepdim=True) + eps) * w_norm.double()
+    gu = normed @ w.double().T
+    want = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
+    assert (out.double().cpu() - want.cpu()).abs().max().item() <= 1e-2 * want.abs().max().item()
+    assert int(status[0]) == 0

@@ -19,6 +19,16 @@
 //                      feature for 32 tokens, so for a fixed token a warp writes 32 consecutive
 //                      features (one coalesced segment).
 //
+// Fused input norm (GemmArgs::resid): the X operand is made on the spot.  While the weight tiles
+// stream in, the epilogue warps read the float32 residual rows of the CTA's tokens, multiply by
+// the norm weight, round to bf16 and store the [BN x 64] tile of every K block of the CTA into
+// shared memory of their own (after the stages), in the 128-byte-swizzled layout the tensor map
+// would have produced (16-byte chunk c of row r at chunk c ^ (r & 7)); they also sum the
+// squares.  They work in batches of a few K blocks, all loads of a batch in flight at once, and
+// signal every batch on an mbarrier the MMA issuer waits for.  y = rstd[t] * (W (w_norm x)) + b:
+// the row scale is applied in the epilogue; with split K the CTAs of a cluster add up their
+// sums of squares through the same exchange that carries the partial tiles.
+//
 // Epilogue modes:
 //   0  out bf16  [T, ldy] = acc + bias
 //   1  out f32   [T, ldy] = acc + bias          (logits)
@@ -133,6 +143,13 @@ struct GemmArgs {
   int mode;
   int kb_per_split;      // 64-wide K blocks per split
   int splits;            // CTAs of the cluster that share one output tile (1: no cluster)
+  // Fused RMSNorm of the input (token tiles up to 64): x is not read; the epilogue warps make
+  // the X tiles themselves as bf16(resid[t, k] * norm_w[k]) from the float32 residual stream,
+  // and the row's 1 / rms is applied to the accumulator, where it commutes with the product.
+  const float* resid;    // [T, resid_ld] float32, or null: plain input through the tensor map
+  const float* norm_w;   // [K]
+  long long resid_ld;
+  float eps;
 };
 
 __device__ __forceinline__ void cluster_arrive() {
@@ -158,6 +175,12 @@ __device__ __forceinline__ void store_peer_shared4(uint32_t local_addr, uint32_t
                : "memory");
 }
 
+__device__ __forceinline__ void store_peer_shared1(uint32_t local_addr, uint32_t rank, float a) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(a) : "memory");
+}
+
 // One element of the output in the epilogue mode of the launch (modes 0, 1, 2).
 __device__ __forceinline__ void store_output(const GemmArgs& g, size_t index, float value) {
   if (g.mode == 0)
@@ -179,8 +202,12 @@ struct GemmShape {
   static constexpr int STAGES = STAGES_;
   static constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
   // Where the peers of a cluster deposit their shares of this CTA's output slice:
-  // [splits][128 / splits rows][BN tokens] floats (token tiles up to 64 only).
-  static constexpr uint32_t RECV_BYTES = BN <= 64 ? GB_BM * BN * 4 : 0;
+  // [splits][128 / splits rows][BN tokens] floats, then [8][BN] sums of squares of the fused
+  // norm (token tiles up to 64 only).
+  static constexpr uint32_t RECV_BYTES = BN <= 64 ? ((GB_BM * BN * 4 + 8 * BN * 4 + 1023) / 1024) * 1024 : 0;
+  // Fused norm: K blocks whose X tiles one batch of loads makes, and the most batches.
+  static constexpr int NORM_BATCH = BN <= 16 ? 6 : (BN <= 32 ? 4 : 2);
+  static constexpr int NORM_MAX_BATCHES = 32;
   static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + RECV_BYTES + 1024;
 };
 
@@ -196,6 +223,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   __shared__ uint32_t tmem_slot;
   __shared__ int epilogue_failed;
   __shared__ float swap_buf[64 * 33];
+  __shared__ float ssq_s[64];  // fused norm: this CTA's sums of squares, then 1 / rms, per token
+  __shared__ __align__(8) uint64_t x_bar[S::NORM_MAX_BATCHES];  // fused norm: a batch of X tiles is ready
 
   VX_TRACE_SCOPE(10 + g.mode);
   allow_dependents();
@@ -209,6 +238,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   const int kb_end = min(num_kb_total, kb_begin + g.kb_per_split);
   const int num_kb = max(0, kb_end - kb_begin);
   const bool clustered = g.splits > 1;
+  const bool normed = BN <= 64 && g.resid != nullptr;
   // First cluster phase: "every CTA of the cluster runs" (nobody may write into a peer before).
   // Arrive now; the wait comes right before the first remote store and costs nothing by then.
   if (clustered) cluster_arrive();
@@ -219,6 +249,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       mbar_init(smem_u32(&full_bar[s]), 1);
       mbar_init(smem_u32(&empty_bar[s]), 1);
     }
+    if (normed)
+      for (int b = 0; b < S::NORM_MAX_BATCHES; ++b) mbar_init(smem_u32(&x_bar[b]), 1);
     mbar_init(smem_u32(&acc_bar), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -244,7 +276,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       const uint32_t full = smem_u32(&full_bar[stage]);
       const uint32_t a_dst = smem_base + stage * S::STAGE_BYTES;
       const int kx = (kb_begin + i) * GB_BK;
-      mbar_expect_tx(full, S::STAGE_BYTES);
+      mbar_expect_tx(full, normed ? GB_A_BYTES : S::STAGE_BYTES);
       if (g.mode == 3) {
         // 64 gate rows then 64 up rows: two boxes of 64 rows each.
         tma_load_2d(a_dst, &map_w, kx, n0, full);
@@ -261,13 +293,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     for (int i = 0; i < first_round; ++i) load_w(i);
     grid_dependency_wait();
     VX_TRACE_MARK(0);
-    for (int i = 0; i < first_round; ++i) load_x(i);
+    if (!normed)
+      for (int i = 0; i < first_round; ++i) load_x(i);
     for (int i = first_round; i < num_kb; ++i) {
       const int stage = i % S::STAGES;
       const uint32_t phase = (uint32_t)(i / S::STAGES) & 1u;
       if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, g.status)) break;
       load_w(i);
-      load_x(i);
+      if (!normed) load_x(i);
     }
   } else if (warp == 1 && lane == 0) {
     // ---------------------------------------------------------------- MMA issuer
@@ -277,10 +310,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       const int stage = i % S::STAGES;
       const uint32_t phase = (uint32_t)(i / S::STAGES) & 1u;
       ok = mbar_wait(smem_u32(&full_bar[stage]), phase, g.status);
+      if (ok && normed && i % S::NORM_BATCH == 0)
+        ok = mbar_wait(smem_u32(&x_bar[i / S::NORM_BATCH]), 0u, g.status);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t a_addr = smem_base + stage * S::STAGE_BYTES;
-      const uint32_t b_addr = a_addr + GB_A_BYTES;
+      const uint32_t b_addr = normed ? smem_base + S::STAGES * S::STAGE_BYTES + S::RECV_BYTES + i * S::B_BYTES
+                                     : a_addr + GB_A_BYTES;
 #pragma unroll
       for (int k = 0; k < GB_BK / 16; ++k) {
         umma_bf16(tmem_acc, umma_smem_desc(a_addr + k * 32), umma_smem_desc(b_addr + k * 32),
@@ -293,6 +329,77 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   } else if (warp >= 2) {
     // ---------------------------------------------------------------- epilogue
     grid_dependency_wait();
+    if (BN <= 64 && normed) {
+      // The X tiles of the fused norm.  Thread q of the 128 takes 16-byte chunks q, q + 128, ...
+      // of a tile: token q / 8 (+ 16 per further chunk), dims 8 * (q % 8) .. + 7 of the K block.
+      constexpr int CPT = BN <= 64 ? (BN * 8 + 127) / 128 : 1;  // chunks per thread and K block
+      constexpr int NB = S::NORM_BATCH;
+      const int q = (int)threadIdx.x - 64;
+      const int c = q & 7;
+      float ssq[CPT];
+#pragma unroll
+      for (int u = 0; u < CPT; ++u) ssq[u] = 0.f;
+      unsigned char* x_tiles = smem_raw + (smem_base - smem_u32(smem_raw)) + S::STAGES * S::STAGE_BYTES + S::RECV_BYTES;
+      for (int i0 = 0; i0 < num_kb; i0 += NB) {
+        float4 xa[NB][CPT], xb[NB][CPT], wa[NB], wb[NB];
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+          const int k = (kb_begin + i0 + j) * GB_BK + c * 8;
+          const bool in_k = i0 + j < num_kb && k < g.K;  // K is a multiple of 8: a chunk is inside or outside
+          wa[j] = in_k ? __ldg(reinterpret_cast<const float4*>(g.norm_w + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
+          wb[j] = in_k ? __ldg(reinterpret_cast<const float4*>(g.norm_w + k + 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int u = 0; u < CPT; ++u) {
+            const int r = (q >> 3) + 16 * u;
+            const int t = t0 + r;
+            const bool on = in_k && t < g.T && r < BN;
+            const float* src = g.resid + (size_t)t * g.resid_ld + k;
+            xa[j][u] = on ? *reinterpret_cast<const float4*>(src) : make_float4(0.f, 0.f, 0.f, 0.f);
+            xb[j][u] = on ? *reinterpret_cast<const float4*>(src + 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+          if (i0 + j >= num_kb) break;
+          unsigned char* tile = x_tiles + (size_t)(i0 + j) * S::B_BYTES;
+#pragma unroll
+          for (int u = 0; u < CPT; ++u) {
+            const float4 a4 = xa[j][u], b4 = xb[j][u];
+            ssq[u] += a4.x * a4.x + a4.y * a4.y + a4.z * a4.z + a4.w * a4.w +
+                      b4.x * b4.x + b4.y * b4.y + b4.z * b4.z + b4.w * b4.w;
+            __nv_bfloat162 p0 = __floats2bfloat162_rn(a4.x * wa[j].x, a4.y * wa[j].y);
+            __nv_bfloat162 p1 = __floats2bfloat162_rn(a4.z * wa[j].z, a4.w * wa[j].w);
+            __nv_bfloat162 p2 = __floats2bfloat162_rn(b4.x * wb[j].x, b4.y * wb[j].y);
+            __nv_bfloat162 p3 = __floats2bfloat162_rn(b4.z * wb[j].z, b4.w * wb[j].w);
+            const int r = (q >> 3) + 16 * u;
+            if (r < BN)
+              *reinterpret_cast<uint4*>(tile + r * 128 + ((c ^ (r & 7)) << 4)) =
+                  make_uint4(*reinterpret_cast<uint32_t*>(&p0), *reinterpret_cast<uint32_t*>(&p1),
+                             *reinterpret_cast<uint32_t*>(&p2), *reinterpret_cast<uint32_t*>(&p3));
+          }
+        }
+        // The tensor core reads the tiles through the async proxy.
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (q == 0) mbar_arrive(smem_u32(&x_bar[i0 / NB]));
+      }
+      // The eight threads of a token sit in consecutive lanes.
+#pragma unroll
+      for (int u = 0; u < CPT; ++u) {
+        float v = ssq[u];
+        v += __shfl_xor_sync(0xffffffffu, v, 1);
+        v += __shfl_xor_sync(0xffffffffu, v, 2);
+        v += __shfl_xor_sync(0xffffffffu, v, 4);
+        const int r = (q >> 3) + 16 * u;
+        if (c == 0 && r < BN) ssq_s[r] = v;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (!clustered) {
+        // This CTA saw all of K: its sums are the rows' sums.
+        if (q < BN) ssq_s[q] = rsqrtf(ssq_s[q] / (float)g.K + g.eps);
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+    }
     const int quarter = warp & 3;  // TMEM lanes 32 * quarter .. + 31 belong to this warp
     if (!mbar_wait(smem_u32(&acc_bar), 0u, g.status)) epilogue_failed = 1;
     // All four epilogue warps take the same path below (mode 3 has barriers among them).
@@ -312,6 +419,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       const uint32_t owner = (uint32_t)(row / rows_per_cta);
       const uint32_t recv = smem_base + S::STAGES * S::STAGE_BYTES +
                             ((rank * (uint32_t)rows_per_cta + (uint32_t)(row % rows_per_cta)) * BN) * 4u;
+      if (normed && row < BN) {
+        // This CTA's share of the sums of squares goes to every CTA of the cluster.
+        const uint32_t at = smem_base + S::STAGES * S::STAGE_BYTES + (uint32_t)(GB_BM * BN) * 4u +
+                            (rank * (uint32_t)BN + (uint32_t)row) * 4u;
+        for (uint32_t peer = 0; peer < (uint32_t)g.splits; ++peer) store_peer_shared1(at, peer, ssq_s[row]);
+      }
       for (int c0 = 0; c0 < BN; c0 += 32) {
         float v[32];
         if (ready) {
@@ -341,7 +454,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
             for (int j = 0; j < cols; ++j) {
               const int t = t0 + c0 + j;
               if (t < g.T) {
-                const float gate = v[j], up = swap_buf[row * 33 + j];
+                const float scale = normed ? ssq_s[c0 + j] : 1.0f;
+                const float gate = v[j] * scale, up = swap_buf[row * 33 + j] * scale;
                 out[(size_t)t * g.ldy + n] = __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * up);
               }
             }
@@ -357,7 +471,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
           if (n < g.N) {
             for (int j = 0; j < cols; ++j) {
               const int t = t0 + c0 + j;
-              if (t < g.T) store_output(g, (size_t)t * g.ldy + n, v[j] + b);
+              if (t < g.T) store_output(g, (size_t)t * g.ldy + n, v[j] * (normed ? ssq_s[c0 + j] : 1.0f) + b);
             }
           }
         }
@@ -384,6 +498,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       const int rank = (int)cluster_rank();
       const float* recv = reinterpret_cast<const float*>(
           smem_raw + (smem_base - smem_u32(smem_raw)) + S::STAGES * S::STAGE_BYTES);
+      if (normed) {
+        const int j = (int)threadIdx.x - 64;
+        if (j < BN) {
+          float total = 0.f;
+          for (int peer = 0; peer < g.splits; ++peer) total += recv[GB_BM * BN + peer * BN + j];
+          ssq_s[j] = rsqrtf(total / (float)g.K + g.eps);
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
       for (int e = (warp - 2) * 32 + lane; e < rows_per_cta * BN; e += 128) {
         const int j = e / rows_per_cta, rl = e - j * rows_per_cta;
         const int t = t0 + j, n = n0 + rank * rows_per_cta + rl;
@@ -391,6 +514,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         float acc = 0.f;
         for (int peer = 0; peer < g.splits; ++peer)
           acc += recv[((size_t)peer * rows_per_cta + rl) * BN + j];
+        if (normed) acc *= ssq_s[j];
         store_output(g, (size_t)t * g.ldy + n, acc + (g.bias != nullptr ? g.bias[n] : 0.f));
       }
     }
@@ -459,18 +583,30 @@ template <int BN, int STAGES_>
 static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx,
                        const GemmArgs& g, dim3 grid, cudaStream_t stream) {
   using S = GemmShape<BN, STAGES_>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES_>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)S::SMEM_BYTES);
+  // The most dynamic shared memory a CTA may have beside the kernel's static arrays.
+  static int dynamic_limit = 0;
+  if (dynamic_limit == 0) {
+    cudaFuncAttributes attributes_of;
+    cudaError_t e = cudaFuncGetAttributes(&attributes_of, gemm_bf16_kernel<BN, STAGES_>);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    const int limit = 227 * 1024 - (int)attributes_of.sharedSizeBytes;
+    e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES_>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             limit);
+    if (e != cudaSuccess) return (int)e;
+    dynamic_limit = limit;
   }
+  // With the fused norm the X tiles of all the CTA's K blocks follow the stages.
+  size_t smem = S::SMEM_BYTES;
+  if (g.resid != nullptr) {
+    if (BN > 64) return -2;
+    if ((g.kb_per_split + S::NORM_BATCH - 1) / S::NORM_BATCH > S::NORM_MAX_BATCHES) return -2;
+    smem += (size_t)g.kb_per_split * S::B_BYTES;
+  }
+  if (smem > (size_t)dynamic_limit) return -2;
   cudaLaunchConfig_t config = {};
   config.gridDim = grid;
   config.blockDim = dim3(GB_THREADS);
-  config.dynamicSmemBytes = S::SMEM_BYTES;
+  config.dynamicSmemBytes = smem;
   config.stream = stream;
   cudaLaunchAttribute attributes[2];
   int count = 0;
@@ -531,14 +667,23 @@ static int floor_pow2_8(int value) {
 // x_rows is the number of rows the x buffer really has (>= T); rows T.. are read but their
 // results are never written.  `splits` (rounded down to 1, 2, 4 or 8 and to what K and the
 // token tile allow) CTAs share each output tile as a cluster.
-// Returns 0 on launch, a cudaError_t on failure, or -1 if the sizes are refused
-// (K not a multiple of 8, unaligned pointers, no driver entry point).
-VX_API int vx_gemm_bf16(const void* x, const void* w, const float* bias, void* out, int mode,
-                        int T, int x_rows, int N, int K, long long ldy, int splits,
-                        int* status, cudaStream_t stream) {
+// With resid != null the input is rmsnorm(resid) * norm_w instead of x (see the head of the
+// file); x is then not read and T must be at most 64.
+// Returns 0 on launch, a cudaError_t on failure, -1 if the sizes are refused (K not a multiple
+// of 8, unaligned pointers, no driver entry point), or -2 if the fused norm's tiles do not fit
+// in shared memory (the caller then runs the norm by itself).
+static int gemm_bf16(const void* x, int x_rows, const float* resid, long long resid_ld,
+                     const float* norm_w, float eps, const void* w, const float* bias, void* out,
+                     int mode, int T, int N, int K, long long ldy, int splits, int* status,
+                     cudaStream_t stream) {
   if (T <= 0 || N <= 0) return 0;
   if (K <= 0 || (K % 8) != 0) return -1;
-  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return -1;
+  const bool normed = resid != nullptr;
+  if (reinterpret_cast<uintptr_t>(w) & 15) return -1;
+  if (!normed && (reinterpret_cast<uintptr_t>(x) & 15)) return -1;
+  if (normed && (T > 64 || norm_w == nullptr || (resid_ld % 4) != 0 ||
+                 (reinterpret_cast<uintptr_t>(resid) & 15) || (reinterpret_cast<uintptr_t>(norm_w) & 15)))
+    return -1;
   if (mode < 0 || mode > 3) return -1;
   const int bn = vx_gemm_bf16_token_tile(T);
   const int num_kb = (K + GB_BK - 1) / GB_BK;
@@ -556,6 +701,10 @@ VX_API int vx_gemm_bf16(const void* x, const void* w, const float* bias, void* o
   g.mode = mode;
   g.kb_per_split = (num_kb + splits - 1) / splits;
   g.splits = splits;
+  g.resid = resid;
+  g.norm_w = norm_w;
+  g.resid_ld = resid_ld;
+  g.eps = eps;
 
   CUtensorMap mw, mw2, mx;
   if (mode == 3) {
@@ -565,20 +714,45 @@ VX_API int vx_gemm_bf16(const void* x, const void* w, const float* bias, void* o
     if (!tensor_map_2d(&mw, w, N, K, GB_BM)) return -1;
     mw2 = mw;
   }
-  if (x_rows < T) return -1;
-  if (!tensor_map_2d(&mx, x, x_rows, K, bn)) return -1;
+  if (normed) {
+    mx = mw;  // not used
+  } else {
+    if (x_rows < T) return -1;
+    if (!tensor_map_2d(&mx, x, x_rows, K, bn)) return -1;
+  }
   const int n_tile = mode == 3 ? 64 : GB_BM;
   const dim3 grid((N + n_tile - 1) / n_tile, (T + bn - 1) / bn, splits);
   // A grid that gives an SM one CTA at most keeps more tiles in flight per CTA instead.
   const bool deep = bn <= 32 && g.kb_per_split > 4 &&
                     (long long)grid.x * grid.y * grid.z <= (long long)sm_count();
   switch (bn) {
-    case 16: return deep ? launch_gemm<16, 8>(mw, mw2, mx, g, grid, stream)
-                         : launch_gemm<16, 4>(mw, mw2, mx, g, grid, stream);
-    case 32: return deep ? launch_gemm<32, 8>(mw, mw2, mx, g, grid, stream)
-                         : launch_gemm<32, 4>(mw, mw2, mx, g, grid, stream);
+    case 16: {
+      const int code = deep ? launch_gemm<16, 8>(mw, mw2, mx, g, grid, stream) : -2;
+      return code != -2 ? code : launch_gemm<16, 4>(mw, mw2, mx, g, grid, stream);
+    }
+    case 32: {
+      const int code = deep ? launch_gemm<32, 8>(mw, mw2, mx, g, grid, stream) : -2;
+      return code != -2 ? code : launch_gemm<32, 4>(mw, mw2, mx, g, grid, stream);
+    }
     case 64: return launch_gemm<64, 4>(mw, mw2, mx, g, grid, stream);
     case 128: return launch_gemm<128, 4>(mw, mw2, mx, g, grid, stream);
     default: return launch_gemm<256, 4>(mw, mw2, mx, g, grid, stream);
   }
+}
+
+VX_API int vx_gemm_bf16(const void* x, const void* w, const float* bias, void* out, int mode,
+                        int T, int x_rows, int N, int K, long long ldy, int splits,
+                        int* status, cudaStream_t stream) {
+  return gemm_bf16(x, x_rows, nullptr, 0, nullptr, 0.f, w, bias, out, mode, T, N, K, ldy, splits,
+                   status, stream);
+}
+
+// The same product on rmsnorm(resid) * norm_w: resid [T, resid_ld] float32, norm_w [K] float32.
+VX_API int vx_gemm_bf16_normed(const float* resid, long long resid_ld, const float* norm_w,
+                               float eps, const void* w, const float* bias, void* out, int mode,
+                               int T, int N, int K, long long ldy, int splits, int* status,
+                               cudaStream_t stream) {
+  if (resid == nullptr) return -1;
+  return gemm_bf16(nullptr, 0, resid, resid_ld, norm_w, eps, w, bias, out, mode, T, N, K, ldy,
+                   splits, status, stream);
 }

@@ -64,6 +64,9 @@ def core():
         lib.vx_gemm_bf16.argtypes = [
             _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _ptr, _ptr,
         ]
+        lib.vx_gemm_bf16_normed.argtypes = [
+            _ptr, _c_ll, _ptr, _c_f, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _ptr, _ptr,
+        ]
         _core = lib
     return _core
 
@@ -300,6 +303,58 @@ def gemm_bf16(
             "multiple of 8 and both operands 16-byte aligned"
         )
     _check(code, "gemm_bf16")
+
+
+# Steps of at most this many tokens can have their input norm made inside the projection.
+GEMM_NORMED_MAX_TOKENS = 64
+
+
+def gemm_bf16_normed(
+    resid: torch.Tensor,
+    norm_weight: torch.Tensor,
+    eps: float,
+    w: torch.Tensor,
+    bias: Optional[torch.Tensor],
+    out: torch.Tensor,
+    mode: int,
+    num_rows: int,
+    status: torch.Tensor,
+    splits: int = 1,
+) -> bool:
+    """``gemm_bf16`` on ``rmsnorm(resid[:num_rows]) * norm_weight`` without that tensor ever
+    existing: the kernel makes the bf16 tiles from the float32 rows and applies 1 / rms to its
+    accumulator.  At most ``GEMM_NORMED_MAX_TOKENS`` rows.  False (and nothing launched) when
+    the tiles of a row this long do not fit in shared memory."""
+    if resid.dtype != torch.float32 or resid.dim() != 2 or resid.stride(1) != 1:
+        raise TypeError("resid must be float32 rows")
+    _need(norm_weight, torch.float32, "norm_weight")
+    _need(w, torch.bfloat16, "w")
+    n, k = w.shape
+    if mode == GEMM_SWIGLU:
+        if n % 2:
+            raise ValueError("a gate/up matrix needs an even number of rows")
+        n //= 2
+    if resid.dim() != 2 or resid.shape[1] != k or norm_weight.numel() != k:
+        raise ValueError(f"gemm shapes do not agree: resid {tuple(resid.shape)}, w {tuple(w.shape)}")
+    if num_rows > GEMM_NORMED_MAX_TOKENS:
+        raise ValueError(f"gemm_bf16_normed takes at most {GEMM_NORMED_MAX_TOKENS} rows, got {num_rows}")
+    want = torch.bfloat16 if mode in (GEMM_OUT_BF16, GEMM_SWIGLU) else torch.float32
+    _need(out, want, "out")
+    if out.dim() != 2 or out.shape[1] != n:
+        raise ValueError(f"output {tuple(out.shape)} does not match width {n}")
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+    code = core().vx_gemm_bf16_normed(_p(resid), resid.stride(0), _p(norm_weight), float(eps), _p(w), _p(bias),
+                                      _p(out), mode, num_rows, n, k, out.stride(0), splits, _p(status), _stream())
+    if code == -2:
+        return False
+    if code == -1:
+        raise KernelError(
+            f"gemm_bf16_normed refuses resid {tuple(resid.shape)} w {tuple(w.shape)}: the inner size must "
+            "be a multiple of 8, the row pitch of resid a multiple of 4 and the operands 16-byte aligned"
+        )
+    _check(code, "gemm_bf16_normed")
+    return True
 
 
 def cast_bf16_to_f32(src: torch.Tensor, out: torch.Tensor, count: int) -> None:

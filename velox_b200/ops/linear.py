@@ -30,11 +30,29 @@ def _num_sms() -> int:
     return _NUM_SMS
 
 
-def use_tensor_core_kernel(x: torch.Tensor, weight: torch.Tensor, num_rows: int) -> bool:
+def use_tensor_core_kernel(x, weight: torch.Tensor, num_rows: int) -> bool:
+    if _is_pending_norm(x):
+        x = x.out
     return (
         weight.dtype == torch.bfloat16
         and num_rows <= SMALL_STEP_TOKENS
         and kernels.gemm_bf16_supported(x, weight)
+    )
+
+
+def _is_pending_norm(x) -> bool:
+    return not isinstance(x, torch.Tensor) and hasattr(x, "materialize")
+
+
+def _fuses_norm(x, weight: torch.Tensor, num_rows: int, status) -> bool:
+    """``x`` is a norm that has not run and this projection can make it on the fly."""
+    return (
+        _is_pending_norm(x)
+        and status is not None
+        and num_rows <= kernels.GEMM_NORMED_MAX_TOKENS
+        and x.resid.dtype == torch.float32
+        and x.resid.stride(0) % 4 == 0
+        and use_tensor_core_kernel(x, weight, num_rows)
     )
 
 
@@ -60,9 +78,19 @@ def linear(
 
     ``accumulate`` (tensor-core kernel only, float32 ``out``): add to ``out`` instead, which is
     how a projection goes straight into the float32 residual stream.
+
+    ``x`` may be a ``parts.base.PendingNorm``: with few tokens the norm is then made inside the
+    projection, otherwise it runs first.
     """
     if num_rows == 0:
         return out
+    if _is_pending_norm(x):
+        if not accumulate and _fuses_norm(x, weight, num_rows, status):
+            mode = kernels.GEMM_OUT_F32 if out.dtype == torch.float32 else kernels.GEMM_OUT_BF16
+            if kernels.gemm_bf16_normed(x.resid, x.weight, x.eps, weight, bias_f32, out, mode, num_rows, status,
+                                        splits=choose_splits(weight.shape[0], weight.shape[1])):
+                return out
+        x = x.materialize()
     if weight.dtype == torch.float32:
         if accumulate:
             raise ValueError("the float32 GEMM does not accumulate")
@@ -100,5 +128,11 @@ def swiglu_linear(
     status: torch.Tensor,
 ) -> torch.Tensor:
     """out = silu(x @ Wg.T) * (x @ Wu.T) in one kernel (gate and up rows of one matrix)."""
+    if _is_pending_norm(x):
+        if _fuses_norm(x, gate_up_weight, num_rows, status):
+            if kernels.gemm_bf16_normed(x.resid, x.weight, x.eps, gate_up_weight, None, out,
+                                        kernels.GEMM_SWIGLU, num_rows, status):
+                return out
+        x = x.materialize()
     kernels.gemm_bf16(x, gate_up_weight, None, out, kernels.GEMM_SWIGLU, num_rows, status)
     return out

@@ -59,6 +59,9 @@ class Attention(Mixer):
     def attention_signature(self):
         return (self.num_kv_heads, self.num_heads // self.num_kv_heads, self.window)
 
+    # The input is used by the QKV projection only, which can make the norm itself.
+    accepts_pending_norm = True
+
     def forward(self, x, ctx, cache):
         T = ctx.num_tokens
         ws = ctx.workspace

@@ -12,6 +12,10 @@ Interfaces (T = tokens of the step, E = model width, dt = compute dtype):
     normalised rows to ``out`` (dt).  Fusing the add into the norm is why the interface has
     both.
 
+``Norm.pending(resid, out, num_rows)`` may return a ``PendingNorm`` instead of running (a norm
+    that is a row scale times a weight can be made inside the projection that follows); None
+    means it has to run.
+
 A part's product that is waiting to be added to the residual stream ("delta") is a tensor
 dt [T, E], or None when the part has added it into ``ctx.residual`` (the float32 residual
 stream, set by the block around the calls) itself.
@@ -64,6 +68,33 @@ class CacheNeeds:
     state: Optional[StateSpec] = None
 
 
+class PendingNorm:
+    """A norm that has not run yet: the float32 rows it reads (no pending delta), its weight and
+    eps, and the buffer its result belongs in.  A part that declares ``accepts_pending_norm``
+    may get this in place of its normalised input and hand it to ``ops.linear.linear`` or
+    ``swiglu_linear``, which make the norm inside the projection when the step is small;
+    ``materialize()`` runs the norm kernel (once) for anybody who needs the tensor."""
+
+    def __init__(self, norm, resid: torch.Tensor, out: torch.Tensor, num_rows: int) -> None:
+        self.norm = norm
+        self.resid = resid
+        self.out = out
+        self.num_rows = num_rows
+        self.weight = norm.weight
+        self.eps = norm.eps
+        self._done = False
+
+    @property
+    def dtype(self) -> torch.dtype:
+        return self.out.dtype
+
+    def materialize(self) -> torch.Tensor:
+        if not self._done:
+            self.norm.forward(self.resid, None, self.out, self.num_rows)
+            self._done = True
+        return self.out
+
+
 class Part:
     """Base of every part: parameters, weights by local name, compute dtype."""
 
@@ -111,6 +142,11 @@ class FeedForward(Part):
 class Norm(Part):
     def forward(self, resid, delta, out, num_rows, rows=None, write_resid=True) -> torch.Tensor:  # pragma: no cover
         raise NotImplementedError
+
+    def pending(self, resid, out, num_rows) -> Optional["PendingNorm"]:
+        """A description of this norm of ``resid`` (nothing pending to add) for a projection to
+        make on the fly, or None if the norm has to run as a kernel of its own."""
+        return None
 
 
 class PositionEncoding(Part):

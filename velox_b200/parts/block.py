@@ -6,8 +6,13 @@ that follows them, so a block leaves its last product pending in ``hidden.delta`
 """
 from __future__ import annotations
 
+import os
+
 from .base import HiddenState
 from .registry import register_part
+
+# VELOX_B200_NO_NORM_FUSION=1 runs every norm as a kernel of its own (for bisecting).
+_FUSE_NORMS = os.environ.get("VELOX_B200_NO_NORM_FUSION") != "1"
 
 
 @register_part("block", "pre_norm")
@@ -22,10 +27,21 @@ class PreNormBlock:
         T = ctx.num_tokens
         ws = ctx.workspace
         normed = ws.get("block.normed", (ws.max_tokens, hidden.resid.shape[1]), self.mixer.dtype)
-        self.norm_mixer.forward(hidden.resid, hidden.delta, normed, T)
         # A part may add its product into the residual stream itself and return None.
         ctx.residual = hidden.resid
-        mixed = self.mixer.forward(normed, ctx, cache)
-        self.norm_feed_forward.forward(hidden.resid, mixed, normed, T)
-        hidden.delta = self.feed_forward.forward(normed, ctx)
+        mixed = self.mixer.forward(self._normed(self.norm_mixer, self.mixer, hidden.resid, hidden.delta, normed, T),
+                                   ctx, cache)
+        hidden.delta = self.feed_forward.forward(
+            self._normed(self.norm_feed_forward, self.feed_forward, hidden.resid, mixed, normed, T), ctx)
         ctx.residual = None
+
+    @staticmethod
+    def _normed(norm, consumer, resid, delta, out, num_rows):
+        """The consumer's input: the norm's output, or, when nothing is waiting to be added and
+        the consumer can take it, the norm itself for its first projection to make."""
+        if _FUSE_NORMS and delta is None and getattr(consumer, "accepts_pending_norm", False):
+            pending = norm.pending(resid, out, num_rows)
+            if pending is not None:
+                return pending
+        norm.forward(resid, delta, out, num_rows)
+        return out

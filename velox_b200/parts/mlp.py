@@ -19,6 +19,9 @@ class SwiGLU(FeedForward):
         self.w_gate_up = self.expect("gate_up.weight", (2 * self.intermediate_size, self.hidden_size))
         self.w_down = self.expect("down.weight", (self.hidden_size, self.intermediate_size))
 
+    # The input is used by the gate|up projection only, which can make the norm itself.
+    accepts_pending_norm = True
+
     def forward(self, x, ctx):
         T = ctx.num_tokens
         ws = ctx.workspace

@@ -3,7 +3,7 @@ src/decoder_layer.py:49,54)."""
 from __future__ import annotations
 
 from ..ops import kernels
-from .base import Norm
+from .base import Norm, PendingNorm
 from .registry import register_part
 
 
@@ -20,3 +20,6 @@ class RMSNorm(Norm):
     def forward(self, resid, delta, out, num_rows, rows=None, write_resid=True):
         kernels.add_rmsnorm(resid, delta, self.weight, self.eps, out, num_rows, rows, write_resid)
         return out
+
+    def pending(self, resid, out, num_rows):
+        return PendingNorm(self, resid, out, num_rows)
