@@ -232,7 +232,13 @@ constexpr int KV_TILE_ELEMS = TMA_KV ? B_BN_ * D : B_BN_ * (D + 8);
 // Row pitch (floats) of the narrow family's cross-warp merge buffer, and its size (eight
 // consumer warps).
 constexpr int NARROW_MERGE_LD = D + 8;
-constexpr size_t NARROW_MERGE_BYTES = (size_t)(8 * 16 * NARROW_MERGE_LD + 2 * 8 * 16) * sizeof(float);
+#ifndef VX_NARROW_GROUPS
+#define VX_NARROW_GROUPS 1
+#endif
+#ifndef VX_NARROW_SMEM_KB
+#define VX_NARROW_SMEM_KB 110
+#endif
+constexpr size_t NARROW_MERGE_BYTES = (size_t)(VX_NARROW_GROUPS * 4 * 16 * NARROW_MERGE_LD + 2 * VX_NARROW_GROUPS * 4 * 16) * sizeof(float);
 // Where the CTAs of a cluster deposit the rows this CTA owns: [16 rows][D] floats and their
 // log-sum-exps, in memory nothing else uses while the kernel runs.
 constexpr size_t NARROW_RECV_BYTES = (size_t)16 * D * sizeof(float) + 64;
@@ -247,13 +253,16 @@ __host__ __device__ constexpr size_t attn_tiles_bytes(bool narrow, int stages) {
 __host__ __device__ constexpr size_t attn_smem_bytes(bool narrow, int stages) {
   return attn_tiles_bytes(narrow, stages) + (narrow ? NARROW_RECV_BYTES : 0);
 }
-// The wide family keeps two CTAs on an SM (two stages each).  The narrow family streams: one CTA
-// per SM with as many stages as fit (up to 8), so that enough bytes are in flight per SM to keep
-// HBM busy even when the step has only one CTA per SM.
+// Both families keep two CTAs on an SM.  The narrow family has one group of four consumer warps
+// and as many stages as fit in half an SM's shared memory (three at head size 128): a decode
+// step of 8 sequences x 2 KV heads then runs as 16 clusters of 8 CTAs on 128 SMs, where one CTA
+// per SM with two groups and twice the stages fitted only 15 such clusters on the GPU (a
+// cluster lives inside one GPC) and streamed from 64 SMs (measured: 1.73 -> 1.66 ms per step).
+// VX_NARROW_GROUPS / VX_NARROW_SMEM_KB are the two knobs.
 constexpr int WIDE_STAGES = 2;
 constexpr int narrow_stages() {
   const size_t stage = (size_t)2 * KV_TILE_ELEMS * sizeof(__nv_bfloat16);
-  const size_t budget = (size_t)216 * 1024 - (size_t)16 * (D + 8) * sizeof(__nv_bfloat16) - NARROW_RECV_BYTES;
+  const size_t budget = (size_t)VX_NARROW_SMEM_KB * 1024 - (size_t)16 * (D + 8) * sizeof(__nv_bfloat16) - NARROW_RECV_BYTES;
   const size_t n = budget / stage;
   return n > 8 ? 8 : (n < 2 ? 2 : (int)n);
 }
@@ -915,13 +924,11 @@ __global__ void __launch_bounds__(128) attn_wide_kernel(const __grid_constant__ 
 
 // ---------------------------------------------------------------------------------------------
 // Narrow family: 16 rows (single decoded tokens, short portions); this is what streams the
-// cache in a decode step.  Nine warps: eight consumers in two groups of four and one producer.
+// cache in a decode step.  Consumer warps in NARROW_GROUPS groups of four and one producer warp.
 // The producer asks the copy engines for K/V tiles into a ring of STAGES stages and never
-// computes; a group takes every second tile, its four warps 16 keys of the tile each, and hands
-// the stage back through an mbarrier when its warps have read it - there is no block-wide
-// barrier in the loop.  Two groups, because one warp per scheduler cannot hide the latency of
-// its own ldmatrix -> mma -> softmax chain.  At the end the eight warps merge through shared
-// memory.
+// computes; a group takes every NARROW_GROUPS-th tile, its four warps 16 keys of the tile each,
+// and hands the stage back through an mbarrier when its warps have read it - there is no
+// block-wide barrier in the loop.  At the end the consumer warps merge through shared memory.
 // A cluster of 2, 4 or 8 such CTAs may share one work item: CTA `rank` takes a run of the
 // item's key tiles, and the CTAs merge through distributed shared memory by rows.
 // ---------------------------------------------------------------------------------------------
@@ -1078,7 +1085,8 @@ struct NarrowWarp {
   }
 };
 
-constexpr int NARROW_GROUPS = 2;
+constexpr int NARROW_GROUPS = VX_NARROW_GROUPS;
+constexpr int NARROW_TABLE_CAP = 256;  // block-table entries kept in shared memory
 constexpr int NARROW_CONSUMERS = NARROW_GROUPS * 4 * 32;
 constexpr int NARROW_THREADS = NARROW_CONSUMERS + 32;
 
@@ -1105,7 +1113,7 @@ __device__ __forceinline__ void produce_kv_tile(const AttnArgs& a, __nv_bfloat16
       int page = 0;  // past the sequence: the reserved page
       if (block <= last_block) {
         const int local = block - first_block;
-        page = local < TABLE_CAP ? table_s[local] : table[block];
+        page = local < NARROW_TABLE_CAP ? table_s[local] : table[block];
       }
       const int token = page * a.page_size + (n - block * a.page_size);
       const uint32_t dst = smem_u32((which ? v_s : k_s) + panel * (B_BN * 64) + r * 64);
@@ -1128,7 +1136,7 @@ __device__ __forceinline__ void produce_kv_tile(const AttnArgs& a, __nv_bfloat16
       if (n < kv_end) {
         const int block = n / a.page_size;
         const int local = block - first_block;
-        const int page = local < TABLE_CAP ? table_s[local] : table[block];
+        const int page = local < NARROW_TABLE_CAP ? table_s[local] : table[block];
         const size_t off =
             (((size_t)page * a.page_size + (n - block * a.page_size)) * a.num_kv_heads + kvh) * D;
         mbar_expect_tx(bar, 2 * ROW_BYTES);
@@ -1151,7 +1159,7 @@ __global__ void __launch_bounds__(NARROW_THREADS) attn_narrow_kernel(const __gri
   constexpr int TILE = KV_TILE_ELEMS;
   constexpr int WARPS = NARROW_GROUPS * 4;  // consumer warps
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  __shared__ int table_s[TABLE_CAP];
+  __shared__ int table_s[NARROW_TABLE_CAP];
   __shared__ __align__(8) uint64_t kv_full[STAGES];
   __shared__ __align__(8) uint64_t kv_empty[STAGES];
   __shared__ __align__(8) uint64_t merge_bar;
@@ -1206,7 +1214,7 @@ __global__ void __launch_bounds__(NARROW_THREADS) attn_narrow_kernel(const __gri
   const int first_block = n_first / a.page_size;
   const int last_block = tile_end > 0 ? (tile_end - 1) / a.page_size : 0;
   if (num_tiles > 0) {
-    const int blocks = min(TABLE_CAP, (tile_end - 1) / a.page_size - first_block + 1);
+    const int blocks = min(NARROW_TABLE_CAP, (tile_end - 1) / a.page_size - first_block + 1);
     for (int i = threadIdx.x; i < blocks; i += blockDim.x) table_s[i] = table[first_block + i];
   }
   if (threadIdx.x == 0) {
@@ -1575,7 +1583,7 @@ VX_API int vx_attention(int kind, const void* q, void* out, const void* k_cache,
 // What the planner needs to know about the narrow family: how many of its CTAs an SM holds
 // (by shared memory), and the largest cluster that may share a work item.
 VX_API int vx_attn_narrow_ctas_per_sm() {
-  const size_t smem = attn_smem_bytes(true, NARROW_STAGES) + 1024 + 8 * 1024;  // + static, reserved
+  const size_t smem = attn_smem_bytes(true, NARROW_STAGES) + 1024 + 3 * 1024;  // + static, reserved
   const size_t per_sm = (size_t)228 * 1024;
   const int n = (int)(per_sm / smem);
   return n < 1 ? 1 : (n > 8 ? 8 : n);
