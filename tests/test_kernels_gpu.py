@@ -692,3 +692,61 @@ def test_gemm_bf16_swiglu_makes_its_input_norm(k, status, T, I, K):
     want = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
     assert (out.double().cpu() - want.cpu()).abs().max().item() <= 1e-2 * want.abs().max().item()
     assert int(status[0]) == 0
+
+
+@pytest.mark.parametrize("T,H,G,K", [(8, 12, 2, 1536), (1, 2, 1, 256), (37, 3, 3, 704), (64, 4, 2, 512)])
+@pytest.mark.parametrize("normed", [False, True])
+def test_gemm_bf16_qkv_rotates_and_writes_the_cache(k, status, T, H, G, K, normed):
+    """Heads of 128 dims: the QKV projection rotates q and k by the tokens' positions and writes
+    k and v into the paged cache in its epilogue (and makes its input norm, if asked)."""
+    D, P = 128, 16
+    gen = torch.Generator().manual_seed(T + H + K)
+    N = (H + 2 * G) * D
+    w = (torch.randn(N, K, generator=gen) / math.sqrt(K)).to(torch.bfloat16).cuda()
+    bias = torch.randn(N, generator=gen).cuda()
+    max_pos = 300
+    positions = torch.randint(0, max_pos, (T,), generator=gen, dtype=torch.int32)
+    inv_freq = 1.0 / (10000.0 ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
+    angles = torch.outer(torch.arange(max_pos, dtype=torch.float32), inv_freq)
+    cos, sin = angles.cos().cuda(), angles.sin().cuda()
+    pages = 6
+    slots = torch.randperm(pages * P, generator=gen)[:T].to(torch.int32)
+    if T > 2:
+        slots[1] = -1  # a row without a cache slot (padding)
+    k_cache = torch.full((pages, P, G, D), 7.0, dtype=torch.bfloat16, device="cuda")
+    v_cache = torch.full((pages, P, G, D), 7.0, dtype=torch.bfloat16, device="cuda")
+    out = torch.full((T + 2, N), 9.0, dtype=torch.bfloat16, device="cuda")
+    if normed:
+        resid = (torch.randn(T + 2, K, generator=gen) * 2).cuda()
+        w_norm = (torch.rand(K, generator=gen) + 0.5).cuda()
+        r64 = resid[:T].double()
+        x64 = r64 * torch.rsqrt((r64 * r64).mean(-1, keepdim=True) + 1e-6) * w_norm.double()
+        ok = k.gemm_bf16_qkv_rope(None, resid, w_norm, 1e-6, w, bias, out, T, positions.cuda(), cos, sin,
+                                  slots.cuda(), k_cache, v_cache, H, G, status, splits=8)
+    else:
+        x = torch.randn(T + 2, K, generator=gen).to(torch.bfloat16).cuda()
+        x64 = x[:T].double()
+        ok = k.gemm_bf16_qkv_rope(x, None, None, 0.0, w, bias, out, T, positions.cuda(), cos, sin,
+                                  slots.cuda(), k_cache, v_cache, H, G, status, splits=8)
+    assert ok
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0
+    y = (x64 @ w.double().T + bias.double()).cpu().view(T, H + 2 * G, D)
+    c64, s64 = angles.cos().double()[positions.long()], angles.sin().double()[positions.long()]  # [T, 64]
+    lo, hi = y[..., :64], y[..., 64:]
+    rot = torch.cat([lo * c64[:, None] - hi * s64[:, None], lo * s64[:, None] + hi * c64[:, None]], dim=-1)
+    want_q, want_k, want_v = rot[:, :H], rot[:, H:H + G], y[:, H + G:]
+    scale = max(y.abs().max().item(), 1.0)
+    got_q = out[:T, : H * D].double().cpu().view(T, H, D)
+    assert (got_q - want_q).abs().max().item() <= 1e-2 * scale
+    assert torch.all(out[T:] == 9.0)
+    kc, vc = k_cache.double().cpu().view(-1, G, D), v_cache.double().cpu().view(-1, G, D)
+    written = torch.zeros(pages * P, dtype=torch.bool)
+    for t in range(T):
+        slot = int(slots[t])
+        if slot < 0:
+            continue
+        written[slot] = True
+        assert (kc[slot] - want_k[t]).abs().max().item() <= 1e-2 * scale
+        assert (vc[slot] - want_v[t]).abs().max().item() <= 1e-2 * scale
+    assert torch.all(kc[~written] == 7.0) and torch.all(vc[~written] == 7.0)

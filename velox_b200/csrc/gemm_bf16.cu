@@ -36,6 +36,11 @@
 //                                                residual stream; one CTA owns each element)
 //   3  out bf16  [T, ldy] = silu(gate) * up     W rows are [64 gate | 64 up] per CTA (the host
 //                                                passes two tensor maps of the same matrix)
+//   4  QKV of heads of 128 dims, split K only: a CTA's 128 rows are one head; acc + bias is
+//      rotated by the token's position (rotate-half over the whole head, float32 tables) for
+//      query and key heads; query heads go to out bf16 [T, ldy], key and value heads straight
+//      into the paged cache at the token's slot.  The rows of a tile are dealt to the cluster's
+//      CTAs in pairs (d, d + 64), so the owner of a pair rotates it without another exchange.
 //
 // Every wait on an mbarrier is bounded: when the bound is hit the thread sets a status bit,
 // stops issuing work, and the CTA still frees its tensor memory and returns.
@@ -150,6 +155,15 @@ struct GemmArgs {
   const float* norm_w;   // [K]
   long long resid_ld;
   float eps;
+  // Mode 4.
+  const int* positions;  // [T]
+  const float* cos_t;    // [max_pos, 64]
+  const float* sin_t;
+  const int* slots;      // [T] cache slot of the token (page * page_size + offset), < 0: none
+  void* k_cache;         // [slots, kv_heads, 128] bf16, or null: nothing is written to a cache
+  void* v_cache;
+  int heads, kv_heads, max_pos;
+  long long num_slots;
 };
 
 __device__ __forceinline__ void cluster_arrive() {
@@ -416,9 +430,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       cluster_wait();
       const int rows_per_cta = GB_BM / g.splits;
       const uint32_t rank = cluster_rank();
-      const uint32_t owner = (uint32_t)(row / rows_per_cta);
+      // Mode 4 deals rows in pairs (d, d + 64): a CTA owns 64 / splits dims and their partners.
+      const int pairs_per_cta = rows_per_cta / 2;
+      const uint32_t owner = g.mode == 4 ? (uint32_t)((row & 63) / pairs_per_cta) : (uint32_t)(row / rows_per_cta);
+      const uint32_t slot_row = g.mode == 4 ? (uint32_t)((row >> 6) * pairs_per_cta + (row & 63) % pairs_per_cta)
+                                            : (uint32_t)(row % rows_per_cta);
       const uint32_t recv = smem_base + S::STAGES * S::STAGE_BYTES +
-                            ((rank * (uint32_t)rows_per_cta + (uint32_t)(row % rows_per_cta)) * BN) * 4u;
+                            ((rank * (uint32_t)rows_per_cta + slot_row) * BN) * 4u;
       if (normed && row < BN) {
         // This CTA's share of the sums of squares goes to every CTA of the cluster.
         const uint32_t at = smem_base + S::STAGES * S::STAGE_BYTES + (uint32_t)(GB_BM * BN) * 4u +
@@ -507,6 +525,58 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
       }
+      if (g.mode == 4) {
+        // This CTA's pairs (d, d + 64) of one head: sum, scale, bias, rotate, store.
+        const int pairs = rows_per_cta / 2;
+        const int head = blockIdx.x;
+        const bool is_q = head < g.heads, is_k = !is_q && head < g.heads + g.kv_heads;
+        for (int e = (warp - 2) * 32 + lane; e < pairs * BN; e += 128) {
+          const int j = e / pairs, pl = e - j * pairs;
+          const int t = t0 + j;
+          if (t >= g.T) continue;
+          const int d = rank * pairs + pl;
+          float lo = 0.f, hi = 0.f;
+          for (int peer = 0; peer < g.splits; ++peer) {
+            lo += recv[((size_t)peer * rows_per_cta + pl) * BN + j];
+            hi += recv[((size_t)peer * rows_per_cta + pairs + pl) * BN + j];
+          }
+          if (normed) {
+            lo *= ssq_s[j];
+            hi *= ssq_s[j];
+          }
+          if (g.bias != nullptr) {
+            lo += g.bias[n0 + d];
+            hi += g.bias[n0 + d + 64];
+          }
+          if (is_q || is_k) {
+            int pos = g.positions[t];
+            if (pos < 0 || pos >= g.max_pos) {
+              atomicOr(g.status, VX_STATUS_BAD_POSITION);
+              pos = 0;
+            }
+            const float cs = g.cos_t[(size_t)pos * 64 + d], sn = g.sin_t[(size_t)pos * 64 + d];
+            const float r_lo = lo * cs - hi * sn, r_hi = lo * sn + hi * cs;
+            lo = r_lo;
+            hi = r_hi;
+          }
+          __nv_bfloat16* dst;
+          if (is_q) {
+            dst = (__nv_bfloat16*)g.out + (size_t)t * g.ldy + n0 + d;
+          } else {
+            if (g.k_cache == nullptr) continue;
+            const int slot = g.slots[t];
+            if (slot < 0) continue;
+            if ((long long)slot >= g.num_slots) {
+              atomicOr(g.status, VX_STATUS_BAD_SLOT);
+              continue;
+            }
+            const int kvh = is_k ? head - g.heads : head - g.heads - g.kv_heads;
+            dst = (__nv_bfloat16*)(is_k ? g.k_cache : g.v_cache) + ((size_t)slot * g.kv_heads + kvh) * 128 + d;
+          }
+          dst[0] = __float2bfloat16_rn(lo);
+          dst[64] = __float2bfloat16_rn(hi);
+        }
+      } else
       for (int e = (warp - 2) * 32 + lane; e < rows_per_cta * BN; e += 128) {
         const int j = e / rows_per_cta, rl = e - j * rows_per_cta;
         const int t = t0 + j, n = n0 + rank * rows_per_cta + rl;
@@ -672,10 +742,21 @@ static int floor_pow2_8(int value) {
 // Returns 0 on launch, a cudaError_t on failure, -1 if the sizes are refused (K not a multiple
 // of 8, unaligned pointers, no driver entry point), or -2 if the fused norm's tiles do not fit
 // in shared memory (the caller then runs the norm by itself).
+struct RopeArgs {
+  const int* positions;
+  const float* cos_t;
+  const float* sin_t;
+  const int* slots;
+  void* k_cache;
+  void* v_cache;
+  int heads, kv_heads, max_pos;
+  long long num_slots;
+};
+
 static int gemm_bf16(const void* x, int x_rows, const float* resid, long long resid_ld,
                      const float* norm_w, float eps, const void* w, const float* bias, void* out,
                      int mode, int T, int N, int K, long long ldy, int splits, int* status,
-                     cudaStream_t stream) {
+                     cudaStream_t stream, const RopeArgs* rope = nullptr) {
   if (T <= 0 || N <= 0) return 0;
   if (K <= 0 || (K % 8) != 0) return -1;
   const bool normed = resid != nullptr;
@@ -684,12 +765,18 @@ static int gemm_bf16(const void* x, int x_rows, const float* resid, long long re
   if (normed && (T > 64 || norm_w == nullptr || (resid_ld % 4) != 0 ||
                  (reinterpret_cast<uintptr_t>(resid) & 15) || (reinterpret_cast<uintptr_t>(norm_w) & 15)))
     return -1;
-  if (mode < 0 || mode > 3) return -1;
+  if (mode < 0 || mode > 4 || (mode == 4) != (rope != nullptr)) return -1;
   const int bn = vx_gemm_bf16_token_tile(T);
   const int num_kb = (K + GB_BK - 1) / GB_BK;
   if (splits < 1 || mode == 3 || bn > 64) splits = 1;
   splits = floor_pow2_8(splits < num_kb ? splits : num_kb);
   if (splits > bn) splits = bn;
+  if (mode == 4) {
+    // Heads of 128 dims, rotated in the cluster exchange's final sum: split K only.
+    if (splits < 2 || rope->heads <= 0 || rope->kv_heads <= 0 ||
+        N != (rope->heads + 2 * rope->kv_heads) * 128)
+      return -2;
+  }
   GemmArgs g;
   g.bias = bias;
   g.out = out;
@@ -705,6 +792,24 @@ static int gemm_bf16(const void* x, int x_rows, const float* resid, long long re
   g.norm_w = norm_w;
   g.resid_ld = resid_ld;
   g.eps = eps;
+  g.positions = nullptr;
+  g.cos_t = g.sin_t = nullptr;
+  g.slots = nullptr;
+  g.k_cache = g.v_cache = nullptr;
+  g.heads = g.kv_heads = g.max_pos = 0;
+  g.num_slots = 0;
+  if (rope != nullptr) {
+    g.positions = rope->positions;
+    g.cos_t = rope->cos_t;
+    g.sin_t = rope->sin_t;
+    g.slots = rope->slots;
+    g.k_cache = rope->k_cache;
+    g.v_cache = rope->v_cache;
+    g.heads = rope->heads;
+    g.kv_heads = rope->kv_heads;
+    g.max_pos = rope->max_pos;
+    g.num_slots = rope->num_slots;
+  }
 
   CUtensorMap mw, mw2, mx;
   if (mode == 3) {
@@ -755,4 +860,23 @@ VX_API int vx_gemm_bf16_normed(const float* resid, long long resid_ld, const flo
   if (resid == nullptr) return -1;
   return gemm_bf16(nullptr, 0, resid, resid_ld, norm_w, eps, w, bias, out, mode, T, N, K, ldy,
                    splits, status, stream);
+}
+
+// The QKV projection of heads of 128 dims with the rotation and the cache write in its
+// epilogue (mode 4): w [(heads + 2 kv_heads) * 128, K]; query heads go to out bf16 [T, ldy]
+// rotated, key heads rotated and value heads as they are into k_cache / v_cache [num_slots,
+// kv_heads, 128] at slots[t] (null caches: nothing is written).  The input is x, or
+// rmsnorm(resid) * norm_w when resid is given.  -2: this shape is not taken (no split K, other
+// head sizes, too many tokens); the caller runs the projection and the rotation separately.
+VX_API int vx_gemm_bf16_qkv_rope(const void* x, int x_rows, const float* resid, long long resid_ld,
+                                 const float* norm_w, float eps, const void* w, const float* bias,
+                                 void* out, int T, int K, long long ldy, int splits,
+                                 const int* positions, const float* cos_t, const float* sin_t,
+                                 int max_pos, const int* slots, void* k_cache, void* v_cache,
+                                 long long num_slots, int heads, int kv_heads, int* status,
+                                 cudaStream_t stream) {
+  if (T > 64) return -2;
+  RopeArgs rope = {positions, cos_t, sin_t, slots, k_cache, v_cache, heads, kv_heads, max_pos, num_slots};
+  return gemm_bf16(x, x_rows, resid, resid_ld, norm_w, eps, w, bias, out, 4, T,
+                   (heads + 2 * kv_heads) * 128, K, ldy, splits, status, stream, &rope);
 }

@@ -67,6 +67,10 @@ def core():
         lib.vx_gemm_bf16_normed.argtypes = [
             _ptr, _c_ll, _ptr, _c_f, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _ptr, _ptr,
         ]
+        lib.vx_gemm_bf16_qkv_rope.argtypes = [
+            _ptr, _c_int, _ptr, _c_ll, _ptr, _c_f, _ptr, _ptr, _ptr, _c_int, _c_int, _c_ll, _c_int,
+            _ptr, _ptr, _ptr, _c_int, _ptr, _ptr, _ptr, _c_ll, _c_int, _c_int, _ptr, _ptr,
+        ]
         _core = lib
     return _core
 
@@ -354,6 +358,69 @@ def gemm_bf16_normed(
             "be a multiple of 8, the row pitch of resid a multiple of 4 and the operands 16-byte aligned"
         )
     _check(code, "gemm_bf16_normed")
+    return True
+
+
+def gemm_bf16_qkv_rope(
+    x: Optional[torch.Tensor],
+    resid: Optional[torch.Tensor],
+    norm_weight: Optional[torch.Tensor],
+    eps: float,
+    w: torch.Tensor,
+    bias: Optional[torch.Tensor],
+    out: torch.Tensor,
+    num_rows: int,
+    positions: torch.Tensor,
+    cos: torch.Tensor,
+    sin: torch.Tensor,
+    slots: torch.Tensor,
+    k_cache: Optional[torch.Tensor],
+    v_cache: Optional[torch.Tensor],
+    num_heads: int,
+    num_kv_heads: int,
+    status: torch.Tensor,
+    splits: int,
+) -> bool:
+    """The QKV projection of heads of 128 dims with rotate-half RoPE and the cache write in its
+    epilogue: rotated queries go to ``out`` [rows, (heads + 2 kv_heads) * 128] (its key and
+    value columns are left as they are), rotated keys and the values into the paged caches at
+    ``slots`` (None caches: no write).  The input is ``x`` (bfloat16) or, when ``resid`` is
+    given, ``rmsnorm(resid) * norm_weight``.  False, with nothing launched, for shapes the
+    kernel does not take (then project and rotate separately)."""
+    _need(w, torch.bfloat16, "w")
+    _need(out, torch.bfloat16, "out")
+    _need(positions, torch.int32, "positions")
+    _need(slots, torch.int32, "slots")
+    _need(cos, torch.float32, "cos")
+    _need(sin, torch.float32, "sin")
+    n, k = w.shape
+    if n != (num_heads + 2 * num_kv_heads) * 128 or out.shape[1] != n or cos.shape[1] != 64:
+        return False
+    if num_rows > GEMM_NORMED_MAX_TOKENS:
+        return False
+    if resid is not None:
+        if resid.dtype != torch.float32 or resid.stride(1) != 1 or resid.shape[1] != k:
+            raise TypeError("resid must be float32 rows as wide as the weight")
+        _need(norm_weight, torch.float32, "norm_weight")
+    else:
+        _need(x, torch.bfloat16, "x")
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+    write = k_cache is not None
+    if write:
+        _need(k_cache, torch.bfloat16, "k_cache")
+        _need(v_cache, torch.bfloat16, "v_cache")
+        if k_cache.shape[2] != num_kv_heads or k_cache.shape[3] != 128:
+            return False
+    num_slots = k_cache.shape[0] * k_cache.shape[1] if write else 0
+    code = core().vx_gemm_bf16_qkv_rope(
+        _p(x), 0 if x is None else x.shape[0], _p(resid), 0 if resid is None else resid.stride(0),
+        _p(norm_weight), float(eps), _p(w), _p(bias), _p(out), num_rows, k, out.stride(0), splits,
+        _p(positions), _p(cos), _p(sin), cos.shape[0], _p(slots), _p(k_cache), _p(v_cache), num_slots,
+        num_heads, num_kv_heads, _p(status), _stream())
+    if code in (-1, -2):
+        return False
+    _check(code, "gemm_bf16_qkv_rope")
     return True
 
 

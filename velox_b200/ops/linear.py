@@ -136,3 +136,40 @@ def swiglu_linear(
         x = x.materialize()
     kernels.gemm_bf16(x, gate_up_weight, None, out, kernels.GEMM_SWIGLU, num_rows, status)
     return out
+
+
+def qkv_rope_linear(
+    x,
+    weight: torch.Tensor,
+    bias_f32: Optional[torch.Tensor],
+    out: torch.Tensor,
+    num_rows: int,
+    status: Optional[torch.Tensor],
+    positions: torch.Tensor,
+    cos: torch.Tensor,
+    sin: torch.Tensor,
+    slots: torch.Tensor,
+    k_cache: Optional[torch.Tensor],
+    v_cache: Optional[torch.Tensor],
+    num_heads: int,
+    num_kv_heads: int,
+) -> bool:
+    """The QKV projection with the rotation of q and k and the write of k and v into the cache
+    in the same kernel (few tokens, heads of 128 dims, a projection that is split along K).
+    ``x`` is a tensor or a ``PendingNorm``.  False: nothing was done; the caller projects with
+    ``linear`` and rotates with the position part."""
+    if status is None or num_rows == 0 or num_rows > kernels.GEMM_NORMED_MAX_TOKENS:
+        return False
+    if not use_tensor_core_kernel(x, weight, num_rows):
+        return False
+    splits = choose_splits(weight.shape[0], weight.shape[1])
+    if splits < 2:
+        return False
+    if _is_pending_norm(x):
+        if _fuses_norm(x, weight, num_rows, status) and kernels.gemm_bf16_qkv_rope(
+                None, x.resid, x.weight, x.eps, weight, bias_f32, out, num_rows, positions, cos, sin, slots,
+                k_cache, v_cache, num_heads, num_kv_heads, status, splits):
+            return True
+        x = x.materialize()
+    return kernels.gemm_bf16_qkv_rope(x, None, None, 0.0, weight, bias_f32, out, num_rows, positions, cos, sin,
+                                      slots, k_cache, v_cache, num_heads, num_kv_heads, status, splits)

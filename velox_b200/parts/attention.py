@@ -9,14 +9,18 @@ runs which rows.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
 
 from ..ops import kernels
-from ..ops.linear import linear, use_tensor_core_kernel
+from ..ops.linear import linear, qkv_rope_linear, use_tensor_core_kernel
 from .base import CacheNeeds, Mixer, PagedCacheSpec
 from .registry import register_part
+
+# VELOX_B200_NO_ROPE_FUSION=1 always rotates in a kernel of its own (for bisecting).
+_FUSE_ROPE = os.environ.get("VELOX_B200_NO_ROPE_FUSION") != "1"
 
 
 @register_part("mixer", "attention")
@@ -66,11 +70,18 @@ class Attention(Mixer):
         T = ctx.num_tokens
         ws = ctx.workspace
         qkv = ws.get("attention.qkv", (ws.max_tokens, self.qkv_width), self.dtype)
-        linear(x, self.w_qkv, self.b_qkv, qkv, T, self.b_qkv_lowp, status=ctx.status)
         group = ctx.groups[cache.group]
         k_cache, v_cache = (None, None) if cache.read_only else (cache.k, cache.v)
-        self.position.rotate_and_store(qkv, ctx, group.slot_mapping, k_cache, v_cache,
-                                       self.num_heads, self.num_kv_heads)
+        # Few tokens and heads of 128 dims: projection, rotation and cache write in one kernel.
+        tables = None
+        if _FUSE_ROPE and self.head_dim == 128:
+            tables = getattr(self.position, "full_rotation_tables", lambda: None)()
+        if tables is None or not qkv_rope_linear(
+                x, self.w_qkv, self.b_qkv, qkv, T, ctx.status, ctx.positions, tables[0], tables[1],
+                group.slot_mapping, k_cache, v_cache, self.num_heads, self.num_kv_heads):
+            linear(x, self.w_qkv, self.b_qkv, qkv, T, self.b_qkv_lowp, status=ctx.status)
+            self.position.rotate_and_store(qkv, ctx, group.slot_mapping, k_cache, v_cache,
+                                           self.num_heads, self.num_kv_heads)
 
         attn = ws.get("attention.out", (ws.max_tokens, self.q_size), self.dtype)
         plan = ctx.attention_plan(cache.group, self.attention_signature())

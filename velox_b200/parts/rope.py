@@ -43,6 +43,11 @@ class RotaryHalf(PositionEncoding):
             num_heads, num_kv_heads, self.head_dim, self.rotary_dim, ctx.status,
         )
 
+    def full_rotation_tables(self):
+        """(cos, sin) [max_position, head_dim / 2] when every dim of a head rotates, which is
+        what a projection that rotates in its epilogue needs; else None."""
+        return (self.cos, self.sin) if self.rotary_dim == self.head_dim else None
+
 
 @register_part("position", "none")
 class NoPosition(PositionEncoding):
