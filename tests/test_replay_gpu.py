@@ -25,6 +25,7 @@ CASES = {
     "tiny_b": (tiny_configs.TINY_B, 8, (1, 9, 33, 70, 150)),
     "tiny_w": (tiny_configs.TINY_W, 16, (40, 3, 90, 130, 64)),
     "tiny_c": (tiny_configs.TINY_C, 16, (77, 2, 35, 200, 129)),
+    "tiny_d": (tiny_configs.TINY_D, 64, (130, 3, 65, 300, 64)),
 }
 
 
@@ -95,7 +96,8 @@ def changing_cuts(total):
 @pytest.mark.parametrize("case", list(CASES))
 def test_whole_then_decode_then_portions(models, case, dtype):
     folder, cfg, page, prompts, want = models[case]
-    replayer = make_replayer(folder, dtype, max_tokens=256, page=page)
+    longest = max(len(p) for p in prompts)
+    replayer = make_replayer(folder, dtype, max_tokens=max(256, -(-longest // 64) * 64), page=page)
     for index, (tokens, ref) in enumerate(zip(prompts, want)):
         L = len(tokens)
         whole = replay_one(replayer, f"w{index}", tokens, [L])

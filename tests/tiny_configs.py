@@ -85,4 +85,24 @@ TINY_C: Dict[str, Any] = {
     "hidden_act": "silu",
 }
 
-ALL = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_w": TINY_W, "tiny_c": TINY_C}
+# Heads of 128 dims, three query heads per KV head: the shapes that take the decode fast paths
+# (rotation and cache write in the QKV projection's epilogue, norm made inside the projections,
+# tensor-map K/V tiles, a thread-block cluster per sequence and KV head).  Width 768 = 6 x 128.
+TINY_D: Dict[str, Any] = {
+    "architectures": ["Qwen2ForCausalLM"],
+    "model_type": "qwen2",
+    "num_hidden_layers": 2,
+    "hidden_size": 768,
+    "num_attention_heads": 6,
+    "num_key_value_heads": 2,
+    "intermediate_size": 1048,
+    "vocab_size": 777,
+    "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6,
+    "tie_word_embeddings": False,
+    "use_sliding_window": False,
+    "max_position_embeddings": 1536,
+    "hidden_act": "silu",
+}
+
+ALL = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_w": TINY_W, "tiny_c": TINY_C, "tiny_d": TINY_D}
