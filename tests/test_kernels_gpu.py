@@ -197,7 +197,8 @@ def plain_paged_attention(q, k_all, v_all, ctx, scale, window):
 
 
 def run_attention_case(k, dtype, H, G, D, P, seqs, window=None, seed=0, min_split_keys=256,
-                       target_ctas=296, spike=None, fused_merge=True, max_cluster=1, max_splits=64):
+                       target_ctas=296, spike=None, fused_merge=True, max_cluster=1, max_splits=64,
+                       tensor_memory=False, ramp=None):
     """seqs: list of (q_len, ctx_len).  Returns (got, want) as float64 [T, H, D]."""
     from velox_b200.ops import attention_plan as ap
 
@@ -229,6 +230,14 @@ def run_attention_case(k, dtype, H, G, D, P, seqs, window=None, seed=0, min_spli
             q_view = qkv[row + qi, : H * D].view(H, D)
             q_view[:] = (direction * 12).to(dtype)
         slots = [pages[i // P] * P + i % P for i in range(kv_len)]
+        if ramp is not None:
+            # Every query looks along one direction and the keys' share of it grows with the
+            # position, so the running maximum of a row keeps growing along the key tiles.
+            direction = torch.ones(D) / math.sqrt(D)
+            qkv[row : row + q_len, : H * D] = (direction * 8).repeat(H).to(dtype)
+            for i, slot in enumerate(slots):
+                k_cache.view(-1, G, D)[slot] = (direction * ramp * i * math.sqrt(D) / 8
+                                                + 0.1 * torch.randn(G, D, generator=gen)).to(dtype)
         k_all = k_cache.view(-1, G, D)[slots].double()
         v_all = v_cache.view(-1, G, D)[slots].double()
         q = qkv[row : row + q_len, : H * D].view(q_len, H, D).double()
@@ -243,7 +252,7 @@ def run_attention_case(k, dtype, H, G, D, P, seqs, window=None, seed=0, min_spli
         ap.PlanOptions(num_kv_heads=G, group=group, window=window, use_f32=dtype == torch.float32,
                        min_split_keys=min_split_keys, target_ctas=target_ctas,
                        narrow_max_cluster=max_cluster, max_splits=max_splits,
-                       narrow_global_split_keys=min_split_keys),
+                       narrow_global_split_keys=min_split_keys, wide_on_tensor_memory=tensor_memory),
     )
     dev = lambda x: torch.as_tensor(x, dtype=torch.int32).cuda()
     out = torch.zeros(T, H * D, dtype=dtype, device="cuda")
@@ -335,6 +344,41 @@ def test_attention_cluster_shares_an_item(k, H, G, D, P, max_cluster, max_splits
         assert (len(plan.merge_items) == 0) == (max_splits == 1)
         err = (got - want).abs().max().item()
         assert err <= _attn_tol(torch.bfloat16) * want.abs().max().item(), (window, err)
+
+
+@pytest.mark.parametrize("H,G", [(12, 2), (4, 4), (7, 1)])
+@pytest.mark.parametrize("window", [None, 100])
+def test_attention_on_tensor_memory(k, H, G, window):
+    """Prompt portions of head size 128 on tcgen05 tensor cores with S and O in tensor memory:
+    whole prompts, portions with context, a last tile with few rows, page order shuffled."""
+    seqs = [(300, 0), (70, 130), (129, 1000), (200, 57), (1, 40), (64, 64)]
+    got, want, plan = run_attention_case(k, torch.bfloat16, H, G, 128, 16, seqs, window=window, seed=H + G,
+                                         tensor_memory=True)
+    from velox_b200.ops import attention_plan as ap
+
+    assert ap.KIND_BF16_TC in plan.items
+    err = (got - want).abs().max().item()
+    assert err <= _attn_tol(torch.bfloat16) * want.abs().max().item(), err
+
+
+def test_attention_on_tensor_memory_rescales_when_the_maximum_grows(k):
+    """Scores that grow along the keys by far more than 2^8: the reference maximum of the
+    exponentials moves several times and O in tensor memory is rescaled each time."""
+    H, G, D, P = 6, 2, 128, 64
+    seqs = [(128, 400)]
+    got, want, plan = run_attention_case(k, torch.bfloat16, H, G, D, P, seqs, seed=3, tensor_memory=True,
+                                         ramp=0.05)
+    err = (got - want).abs().max().item()
+    assert err <= _attn_tol(torch.bfloat16) * want.abs().max().item(), err
+
+
+def test_attention_on_tensor_memory_split_key_ranges(k):
+    seqs = [(100, 1500), (130, 700)]
+    got, want, plan = run_attention_case(k, torch.bfloat16, 12, 2, 128, 16, seqs, seed=9, min_split_keys=64,
+                                         target_ctas=10_000, tensor_memory=True)
+    assert len(plan.merge_items) > 0
+    err = (got - want).abs().max().item()
+    assert err <= _attn_tol(torch.bfloat16) * want.abs().max().item(), err
 
 
 @pytest.mark.parametrize("key_index", [0, 63, 64, 500, 1499])

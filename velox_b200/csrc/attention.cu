@@ -1404,6 +1404,409 @@ __global__ void __launch_bounds__(NARROW_THREADS) attn_narrow_kernel(const __gri
                                                      kvh, reinterpret_cast<float*>(smem_al), &merge_bar);
 }
 
+
+#if VX_HEAD_DIM == 128
+// ---------------------------------------------------------------------------------------------
+// Tensor-memory family (head size 128): prompt portions on the 5th-generation tensor cores.
+// A CTA owns 128 rows (thread r of the four softmax warps owns row r, which is TMEM lane r) and
+// walks the key tiles of 64:
+//   S[128 x 64]   = Q K^T      tcgen05.mma, A = Q (shared, K-major, 128-byte swizzle), B = the
+//                              K tile as the tensor-map copy left it; accumulator in TMEM
+//   softmax       each thread reads its row of S from TMEM (no shuffles: the row is in one
+//                 thread), masks, keeps the running maximum and sum, writes P as bf16 into
+//                 shared memory - over the K tile, which the first product has finished with
+//   O[128 x 128] += P V        A = P (K-major), B = the V tile taken MN-major (keys x dims as
+//                              stored); accumulator in TMEM for the whole item
+// The maximum that the exponentials refer to only moves when the true maximum has grown by
+// more than 2^8 since; O and the sum are then rescaled (TMEM load, multiply, store).  Between
+// such moves P may reach 2^8, which bf16 holds as well as it holds 1.
+// Warps 0-3 softmax and epilogue, warp 4 lane 0 the K/V producer, warp 5 lane 0 the MMA issuer
+// (warp 5 owns the tensor memory).  Two CTAs fit on an SM (96 KB and 256 TMEM columns each), so
+// one CTA's products run under the other's exponentials.
+// ---------------------------------------------------------------------------------------------
+constexpr int TC_ROWS = 128;
+constexpr int TC_THREADS = 192;
+constexpr int TC_STAGES = 2;
+constexpr uint32_t TC_Q_BYTES = TC_ROWS * D * 2;          // two panels of [128 rows x 128 bytes]
+constexpr uint32_t TC_KV_BYTES = B_BN * D * 2;            // a K or V tile (and a P tile: 128 x 64 bf16)
+constexpr uint32_t TC_STAGE_BYTES = 2 * TC_KV_BYTES;
+constexpr size_t TC_SMEM_BYTES = TC_Q_BYTES + (size_t)TC_STAGES * TC_STAGE_BYTES;
+constexpr uint32_t TC_TMEM_COLS = 256;                    // S in columns 0..63, O in 64..191
+constexpr float TC_RESCALE_AT = 8.0f;                     // log2 units
+
+__device__ __forceinline__ uint64_t tc_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t desc = 0;
+  desc |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  desc |= (uint64_t)((lbo_bytes & 0x3FFFFu) >> 4) << 16;
+  desc |= (uint64_t)((sbo_bytes & 0x3FFFFu) >> 4) << 32;
+  desc |= (uint64_t)1 << 46;  // descriptor version of sm_100
+  desc |= (uint64_t)2 << 61;  // 128-byte swizzle
+  return desc;
+}
+
+// kind::f16 instruction descriptor: D f32, A and B bf16, M = 128, N = n; b_mn: B is MN-major.
+__host__ __device__ constexpr uint32_t tc_idesc(int n, bool b_mn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn ? (1u << 16) : 0u) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(128 >> 4) << 24);
+}
+
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                       uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+
+__device__ __forceinline__ void tc_load32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+        "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+        "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ void tc_store32(uint32_t taddr, const float (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+        "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])),
+        "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])),
+        "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+        "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])),
+        "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])),
+        "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+        "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])),
+        "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])),
+        "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// 2^x by the special-function unit alone: -inf gives 0, and the arguments here never exceed 8.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(TC_THREADS, 2) attn_tc_kernel(const __grid_constant__ AttnArgs a) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  __shared__ int table_s[NARROW_TABLE_CAP];
+  __shared__ __align__(8) uint64_t kv_full[TC_STAGES], kv_empty[TC_STAGES];
+  __shared__ __align__(8) uint64_t q_ready, s_ready, s_free, p_ready, pv_done, merge_bar;
+  __shared__ uint32_t tmem_slot;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t q_addr = smem_base;
+  const uint32_t stage_addr = smem_base + TC_Q_BYTES;  // stage st: K at + st * TC_STAGE_BYTES, V after
+
+  VX_TRACE_SCOPE(23);
+  allow_dependents();
+  const int* item = a.items + (size_t)blockIdx.x * 8;
+  const int seq = item[0];
+  if (seq < 0) return;
+  const int row_begin = item[1], row_count = item[2];
+  const int kv_begin = item[3], kv_end = item[4], partial_base = item[5];
+  const int merge_index = item[6], num_splits = item[7];
+  const bool fused_merge = partial_base >= 0 && a.split_counters != nullptr;
+  const int kvh = blockIdx.y;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int q_start = a.q_start[seq], q_len = a.q_len[seq], kv_len = a.kv_len[seq];
+  const int ctx = kv_len - q_len;
+  const int* table = a.block_tables + (size_t)seq * a.table_stride;
+  MergeItem merge_item = {row_begin, row_count, 0, num_splits, 0, q_start};
+  if (fused_merge) {
+    const int* mi = a.merge_items + (size_t)merge_index * 8;
+    merge_item.first = mi[3];
+    merge_item.stride = mi[5];
+  }
+  const int last_pos = ctx + (row_begin + row_count - 1) / a.group;
+  const int tile_end = min(kv_end, last_pos + 1);
+  const int n_first = (kv_begin / B_BN) * B_BN;
+  const int num_tiles = n_first < tile_end ? (tile_end - n_first + B_BN - 1) / B_BN : 0;
+  const int first_block = n_first / a.page_size;
+  const int last_block = tile_end > 0 ? (tile_end - 1) / a.page_size : 0;
+  if (num_tiles > 0) {
+    const int blocks = min(NARROW_TABLE_CAP, (tile_end - 1) / a.page_size - first_block + 1);
+    for (int i = threadIdx.x; i < blocks; i += blockDim.x) table_s[i] = table[first_block + i];
+  }
+  if (threadIdx.x == 0) {
+    for (int st = 0; st < TC_STAGES; ++st) {
+      mbar_init(smem_u32(&kv_full[st]), 1);
+      mbar_init(smem_u32(&kv_empty[st]), 1);
+    }
+    mbar_init(smem_u32(&q_ready), 4);
+    mbar_init(smem_u32(&s_ready), 1);
+    mbar_init(smem_u32(&s_free), 4);
+    mbar_init(smem_u32(&p_ready), 4);
+    mbar_init(smem_u32(&pv_done), 1);
+    mbar_init(smem_u32(&merge_bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_slot)), "r"(TC_TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_s = tmem_slot;        // S: 64 columns
+  const uint32_t tmem_o = tmem_slot + 64u;  // O: 128 columns
+
+  // Row state of the softmax threads (valid for warps 0-3).
+  const int r = (int)threadIdx.x;  // row of the tile, TMEM lane
+  float m_ref = -CUDART_INF_F, m_true = -CUDART_INF_F, l = 0.f;
+  bool failed = false;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------------- K/V producer
+    bool waited = false, alive = true;
+    for (int t = 0; t < num_tiles; ++t) {
+      const int st = t % TC_STAGES, round = t / TC_STAGES;
+      const int n0 = n_first + t * B_BN;
+      if (!waited && n0 + B_BN > ctx) {
+        grid_dependency_wait();
+        waited = true;
+      }
+      if (round > 0 && alive)
+        alive = mbar_wait(smem_u32(&kv_empty[st]), (uint32_t)(round - 1) & 1u, a.status);
+      __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(smem_al + TC_Q_BYTES + st * TC_STAGE_BYTES);
+      produce_kv_tile(a, k_s, k_s + B_BN * D, smem_u32(&kv_full[st]), table, table_s, first_block, last_block,
+                      n0, kv_end, kvh, lane);
+    }
+  } else if (warp == 5) {
+    // --------------------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      bool ok = mbar_wait(smem_u32(&q_ready), 0u, a.status);
+      constexpr uint32_t idesc_qk = tc_idesc(B_BN, false);
+      constexpr uint32_t idesc_pv = tc_idesc(D, true);
+      // S = Q K^T of tile t: eight steps of 16 dims; a panel holds 64 dims (four steps of 32 bytes).
+      auto first_product = [&](int t) -> bool {
+        const int st = t % TC_STAGES, round = t / TC_STAGES;
+        const uint32_t k_addr = stage_addr + st * TC_STAGE_BYTES;
+        if (!mbar_wait(smem_u32(&kv_full[st]), (uint32_t)round & 1u, a.status)) return false;
+        // The softmax threads have S of the tile before in registers.
+        if (t > 0 && !mbar_wait(smem_u32(&s_free), (uint32_t)(t - 1) & 1u, a.status)) return false;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t qa = q_addr + (kk >> 2) * (TC_ROWS * 128) + (kk & 3) * 32;
+          const uint32_t kb = k_addr + (kk >> 2) * (B_BN * 128) + (kk & 3) * 32;
+          tc_mma(tmem_s, tc_desc(qa, 0, 1024), tc_desc(kb, 0, 1024), idesc_qk, kk > 0 ? 1u : 0u);
+        }
+        tc_commit(smem_u32(&s_ready));
+        return true;
+      };
+      if (ok && num_tiles > 0) ok = first_product(0);
+      for (int t = 0; t < num_tiles && ok; ++t) {
+        const int st = t % TC_STAGES;
+        const uint32_t k_addr = stage_addr + st * TC_STAGE_BYTES, v_addr = k_addr + TC_KV_BYTES;
+        // The next tile's scores are made while this tile's exponentials run.
+        if (t + 1 < num_tiles) ok = first_product(t + 1);
+        if (!ok) break;
+        ok = mbar_wait(smem_u32(&p_ready), (uint32_t)t & 1u, a.status);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        // O += P V: four steps of 16 keys.  P lies over the K tile (one panel of [128 x 128 B]);
+        // V is [64 keys x 128 dims]: MN-major B, 16 keys are two groups of eight rows (2 KB),
+        // the second 64 dims are the next panel (8 KB on).
+#pragma unroll
+        for (int ks = 0; ks < B_BN / 16; ++ks) {
+          const uint32_t pa = k_addr + ks * 32;
+          const uint32_t vb = v_addr + ks * 2048;
+          tc_mma(tmem_o, tc_desc(pa, 0, 1024), tc_desc(vb, B_BN * 128, 1024), idesc_pv,
+                 (t > 0 || ks > 0) ? 1u : 0u);
+        }
+        tc_commit(smem_u32(&kv_empty[st]));
+        tc_commit(smem_u32(&pv_done));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax (warps 0-3)
+    grid_dependency_wait();
+    // Q rows into shared memory, K-major, 128-byte swizzled: chunk c of row r at c ^ (r & 7).
+    {
+      const bool on = r < row_count;
+      const int row = row_begin + r;
+      const int tok = row / a.group, hg = row - tok * a.group;
+      const __nv_bfloat16* src = (const __nv_bfloat16*)a.q + (size_t)(q_start + tok) * a.q_stride +
+                                 (size_t)(kvh * a.group + hg) * D;
+#pragma unroll
+      for (int c = 0; c < D / 8; ++c) {
+        const uint4 v = on ? *reinterpret_cast<const uint4*>(src + c * 8) : make_uint4(0u, 0u, 0u, 0u);
+        unsigned char* dst = smem_al + (c >> 3) * (TC_ROWS * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+        *reinterpret_cast<uint4*>(dst) = v;
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&q_ready));
+    }
+    const int pos = r < row_count ? ctx + (row_begin + r) / a.group : -1;
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    for (int t = 0; t < num_tiles; ++t) {
+      const int st = t % TC_STAGES;
+      const int n0 = n_first + t * B_BN;
+      if (!failed) failed = !mbar_wait(smem_u32(&s_ready), (uint32_t)t & 1u, a.status);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      float s[B_BN];
+      {
+        float half[32];
+        tc_load32(tmem_s + lane_base, half);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) s[i] = half[i];
+        tc_load32(tmem_s + lane_base + 32u, half);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) s[32 + i] = half[i];
+      }
+      // S is in registers: the next tile's first product may overwrite it.
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&s_free));
+      // Most tiles lie wholly inside what every row of the warp may see: no masks then.  The
+      // scores stay unscaled; the scale goes into the exponent's multiply-add.
+      const bool row_sees_all = pos >= 0 && n0 >= kv_begin && n0 + B_BN <= kv_end && n0 + B_BN - 1 <= pos &&
+                                (a.window <= 0 || n0 > pos - a.window);
+      if (!__all_sync(0xffffffffu, row_sees_all)) {
+#pragma unroll
+        for (int i = 0; i < B_BN; ++i)
+          if (pos < 0 || !key_visible(n0 + i, pos, kv_begin, kv_end, a.window)) s[i] = -CUDART_INF_F;
+      }
+      float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+      for (int i = 0; i < B_BN; i += 4) {
+        mx4[0] = fmaxf(mx4[0], s[i]);
+        mx4[1] = fmaxf(mx4[1], s[i + 1]);
+        mx4[2] = fmaxf(mx4[2], s[i + 2]);
+        mx4[3] = fmaxf(mx4[3], s[i + 3]);
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;  // the scale is positive
+      m_true = fmaxf(m_true, mx);
+      // The second product of the tile before is observed once per tile, always before this
+      // thread allows the next one (the barrier's phases are then never two ahead of the
+      // parity asked for): early if O has to be rescaled, else after the exponentials, by when
+      // it has long finished.
+      bool observed = t == 0;
+      const bool move = m_true > m_ref + TC_RESCALE_AT || (m_ref == -CUDART_INF_F && m_true > -CUDART_INF_F);
+      if (__any_sync(0xffffffffu, move)) {
+        const float m_new = move ? m_true : m_ref;
+        const float alpha = (m_ref == -CUDART_INF_F) ? 0.f : exp2f(m_ref - m_new);  // 1 if not moved
+        if (t > 0) {
+          // O is rescaled between two of its products: the one of the tile before is done,
+          // the one of this tile waits for this thread's P.
+          if (!failed) failed = !mbar_wait(smem_u32(&pv_done), (uint32_t)(t - 1) & 1u, a.status);
+          observed = true;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+          for (int c0 = 0; c0 < D; c0 += 32) {
+            float o[32];
+            tc_load32(tmem_o + lane_base + (uint32_t)c0, o);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] *= alpha;
+            tc_store32(tmem_o + lane_base + (uint32_t)c0, o);
+          }
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        }
+        l *= alpha;
+        m_ref = m_new;
+      }
+      const float neg_m = m_ref == -CUDART_INF_F ? 0.f : -m_ref;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      unsigned char* p_row = smem_al + TC_Q_BYTES + st * TC_STAGE_BYTES + r * 128;
+#pragma unroll
+      for (int c = 0; c < B_BN / 8; ++c) {
+        float p[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          p[i] = fast_exp2(fmaf(s[c * 8 + i], a.scale_log2, neg_m));
+          sum4[i & 3] += p[i];
+        }
+        const uint4 packed = make_uint4(pack_bf16(p[0], p[1]), pack_bf16(p[2], p[3]), pack_bf16(p[4], p[5]),
+                                        pack_bf16(p[6], p[7]));
+        *reinterpret_cast<uint4*>(p_row + ((c ^ (r & 7)) << 4)) = packed;
+      }
+      const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      l += sum;
+      if (!observed && !failed) failed = !mbar_wait(smem_u32(&pv_done), (uint32_t)(t - 1) & 1u, a.status);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&p_ready));
+    }
+    // Epilogue: O / l to the output, or to the partial rows of a split.
+    if (num_tiles > 0 && !failed) failed = !mbar_wait(smem_u32(&pv_done), (uint32_t)(num_tiles - 1) & 1u, a.status);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const float inv = l > 0.f ? 1.0f / l : 0.f;
+    const bool on = r < row_count;
+    const int row = row_begin + r;
+    const int tok = row / a.group, hg = row - tok * a.group;
+#pragma unroll
+    for (int c0 = 0; c0 < D; c0 += 32) {
+      float o[32];
+      if (num_tiles > 0) {
+        tc_load32(tmem_o + lane_base + (uint32_t)c0, o);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = 0.f;
+      }
+      if (!on) continue;
+      if (partial_base < 0) {
+        __nv_bfloat16* dst = (__nv_bfloat16*)a.out + (size_t)(q_start + tok) * a.out_stride +
+                             (size_t)(kvh * a.group + hg) * D + c0;
+#pragma unroll
+        for (int i = 0; i < 32; i += 8)
+          *reinterpret_cast<uint4*>(dst + i) =
+              make_uint4(pack_bf16(o[i] * inv, o[i + 1] * inv), pack_bf16(o[i + 2] * inv, o[i + 3] * inv),
+                         pack_bf16(o[i + 4] * inv, o[i + 5] * inv), pack_bf16(o[i + 6] * inv, o[i + 7] * inv));
+      } else {
+        float* dst = a.partial_o + ((size_t)partial_base + (size_t)kvh * row_count + r) * D + c0;
+#pragma unroll
+        for (int i = 0; i < 32; i += 4)
+          *reinterpret_cast<float4*>(dst + i) = make_float4(o[i] * inv, o[i + 1] * inv, o[i + 2] * inv, o[i + 3] * inv);
+      }
+    }
+    if (on && partial_base >= 0)
+      a.partial_lse[(size_t)partial_base + (size_t)kvh * row_count + r] =
+          l > 0.f ? m_ref + log2f(l) : -CUDART_INF_F;
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  }
+  __syncthreads();
+  if (warp == 5) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_slot), "r"(TC_TMEM_COLS)
+                 : "memory");
+  }
+  if (fused_merge)
+    finish_split<(int)TC_SMEM_BYTES>(a, merge_index, num_splits, merge_item, kvh,
+                                     reinterpret_cast<float*>(smem_al), &merge_bar);
+}
+#endif  // VX_HEAD_DIM == 128
+
 }  // namespace vx
 
 using namespace vx;
@@ -1488,7 +1891,16 @@ static AttnArgs make_args(const void* q, void* out, const void* k_cache, const v
 VX_API int vx_attn_head_dim() { return D; }
 
 // Rows per item that each family expects: kind 0 = float32, 1 = bf16 wide, 2 = bf16 narrow.
-VX_API int vx_attn_tile_rows(int kind) { return kind == 1 ? 64 : 16; }
+VX_API int vx_attn_tile_rows(int kind) { return kind == 3 ? 128 : (kind == 1 ? 64 : 16); }
+
+// Whether this head size has the tensor-memory family (kind 3, 128-row tiles).
+VX_API int vx_attn_has_tc() {
+#if VX_HEAD_DIM == 128
+  return 1;
+#else
+  return 0;
+#endif
+}
 
 // kind: 0 = float32, 1 = bf16 wide (64 rows), 2 = bf16 narrow (16 rows).
 VX_API int vx_attention(int kind, const void* q, void* out, const void* k_cache,
@@ -1574,6 +1986,17 @@ VX_API int vx_attention(int kind, const void* q, void* out, const void* k_cache,
       cudaError_t e = cudaLaunchKernelEx(&config, attn_narrow_kernel<NARROW_STAGES>, a);
       if (e != cudaSuccess) return (int)e;
     }
+#if VX_HEAD_DIM == 128
+  } else if (kind == 3) {
+    const size_t smem = TC_SMEM_BYTES + 1024;
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+      configured = true;
+    }
+    launch_pdl(attn_tc_kernel, dim3(grid), dim3(TC_THREADS), smem, stream, a);
+#endif
   } else {
     return (int)cudaErrorInvalidValue;
   }

@@ -22,6 +22,8 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import os
+
 import numpy as np
 import torch
 
@@ -120,6 +122,9 @@ class _Packer:
         self.size += (flat.size + 3) // 4 * 4
         return offset, tuple(array.shape)
 
+
+# VELOX_B200_NO_TC_ATTENTION=1 keeps prompt portions on the mma.sync family (for bisecting).
+_USE_TC_ATTENTION = os.environ.get("VELOX_B200_NO_TC_ATTENTION") != "1"
 
 _STATUS_NAMES = {
     1: "a token id outside the vocabulary",
@@ -414,6 +419,7 @@ class ModelRunner:
             options["narrow_target_ctas"] = kernels.narrow_attention_slots(head_dim) * self.num_sms
             options["narrow_max_cluster"] = kernels.max_attention_cluster(head_dim)
             options["narrow_cluster_limits"] = kernels.attention_cluster_limits(head_dim)
+            options["wide_on_tensor_memory"] = kernels.attention_has_tc(head_dim) and _USE_TC_ATTENTION
         if "target_ctas" in self.plan_overrides and "narrow_target_ctas" not in self.plan_overrides:
             options["narrow_target_ctas"] = self.plan_overrides["target_ctas"]
         options.update(self.plan_overrides)

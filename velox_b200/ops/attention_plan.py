@@ -18,8 +18,8 @@ from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
 
-KIND_F32, KIND_BF16_WIDE, KIND_BF16_NARROW = 0, 1, 2
-TILE_ROWS = {KIND_F32: 16, KIND_BF16_WIDE: 64, KIND_BF16_NARROW: 16}
+KIND_F32, KIND_BF16_WIDE, KIND_BF16_NARROW, KIND_BF16_TC = 0, 1, 2, 3
+TILE_ROWS = {KIND_F32: 16, KIND_BF16_WIDE: 64, KIND_BF16_NARROW: 16, KIND_BF16_TC: 128}
 KEY_TILE = 64
 ITEM_WIDTH = 8
 
@@ -56,6 +56,8 @@ class PlanOptions:
     # (None: target_ctas), and the largest cluster that may share one of its items.
     narrow_target_ctas: Optional[int] = None
     narrow_max_cluster: int = 1
+    # Longer portions go to the tensor-memory family (128-row tiles) instead of the wide one.
+    wide_on_tensor_memory: bool = False
     # ((cluster size, clusters of that size the device holds at a time), ...): a size is used
     # only if every (tile, KV head) of the step gets its cluster in one wave.  Empty: no limit.
     narrow_cluster_limits: Tuple[Tuple[int, int], ...] = ()
@@ -106,7 +108,8 @@ def plan_attention(
         if opt.use_f32:
             kind = KIND_F32
         else:
-            kind = KIND_BF16_NARROW if rows <= opt.narrow_max_rows else KIND_BF16_WIDE
+            kind = KIND_BF16_NARROW if rows <= opt.narrow_max_rows else (
+                KIND_BF16_TC if opt.wide_on_tensor_memory else KIND_BF16_WIDE)
         height = TILE_ROWS[kind]
         for row_begin in range(0, rows, height):
             row_count = min(height, rows - row_begin)
@@ -185,7 +188,8 @@ def pad_plan(plan: AttentionPlan, num_seqs: int, splits: int, opt: PlanOptions) 
     if opt.use_f32:
         kind = KIND_F32
     else:
-        kind = KIND_BF16_NARROW if rows <= opt.narrow_max_rows else KIND_BF16_WIDE
+        kind = KIND_BF16_NARROW if rows <= opt.narrow_max_rows else (
+            KIND_BF16_TC if opt.wide_on_tensor_memory else KIND_BF16_WIDE)
     height = TILE_ROWS[kind]
     tiles = -(-rows // height)
     want_items = num_seqs * tiles * max(splits, 1)

@@ -83,6 +83,7 @@ def attention_lib(head_dim: int):
             _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr,
             _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _c_f, _c_int, _ptr,
         ]
+        lib.vx_attn_has_tc.restype = _c_int
         lib.vx_attn_narrow_ctas_per_sm.restype = _c_int
         lib.vx_attn_max_cluster.restype = _c_int
         lib.vx_attn_narrow_max_active_clusters.restype = _c_int
@@ -431,11 +432,11 @@ def cast_bf16_to_f32(src: torch.Tensor, out: torch.Tensor, count: int) -> None:
 
 
 # ------------------------------------------------------------------------------------------
-ATTN_F32, ATTN_BF16_WIDE, ATTN_BF16_NARROW = 0, 1, 2
+ATTN_F32, ATTN_BF16_WIDE, ATTN_BF16_NARROW, ATTN_BF16_TC = 0, 1, 2, 3
 
 
 def tile_rows(kind: int) -> int:
-    return 64 if kind == ATTN_BF16_WIDE else 16
+    return {ATTN_BF16_WIDE: 64, ATTN_BF16_TC: 128}.get(kind, 16)
 
 
 def attention(
@@ -500,6 +501,11 @@ def attention(
                          int(cluster), _stream()),
         "attention",
     )
+
+
+def attention_has_tc(head_dim: int) -> bool:
+    """Whether prompt portions of this head size run on the tensor-memory (tcgen05) family."""
+    return bool(attention_lib(head_dim).vx_attn_has_tc())
 
 
 def narrow_attention_slots(head_dim: int) -> int:
