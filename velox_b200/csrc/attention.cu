@@ -1426,11 +1426,10 @@ __global__ void __launch_bounds__(NARROW_THREADS) attn_narrow_kernel(const __gri
 // ---------------------------------------------------------------------------------------------
 constexpr int TC_ROWS = 128;
 constexpr int TC_THREADS = 192;
-constexpr int TC_STAGES = 2;
 constexpr uint32_t TC_Q_BYTES = TC_ROWS * D * 2;          // two panels of [128 rows x 128 bytes]
 constexpr uint32_t TC_KV_BYTES = B_BN * D * 2;            // a K or V tile (and a P tile: 128 x 64 bf16)
 constexpr uint32_t TC_STAGE_BYTES = 2 * TC_KV_BYTES;
-constexpr size_t TC_SMEM_BYTES = TC_Q_BYTES + (size_t)TC_STAGES * TC_STAGE_BYTES;
+__host__ __device__ constexpr size_t tc_smem_bytes(int stages) { return TC_Q_BYTES + (size_t)stages * TC_STAGE_BYTES; }
 constexpr uint32_t TC_TMEM_COLS = 256;                    // S in columns 0..63, O in 64..191
 constexpr float TC_RESCALE_AT = 8.0f;                     // log2 units
 
@@ -1512,7 +1511,10 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-__global__ void __launch_bounds__(TC_THREADS, 2) attn_tc_kernel(const __grid_constant__ AttnArgs a) {
+// TC_STAGES = 2: two CTAs per SM, for grids of several waves; 4: one CTA per SM with a deeper
+// K/V ring, for grids where an SM gets one CTA anyway and nothing else hides the copies' latency.
+template <int TC_STAGES>
+__global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_kernel(const __grid_constant__ AttnArgs a) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   __shared__ int table_s[NARROW_TABLE_CAP];
   __shared__ __align__(8) uint64_t kv_full[TC_STAGES], kv_empty[TC_STAGES];
@@ -1802,7 +1804,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) attn_tc_kernel(const __grid_con
                  : "memory");
   }
   if (fused_merge)
-    finish_split<(int)TC_SMEM_BYTES>(a, merge_index, num_splits, merge_item, kvh,
+    finish_split<(int)tc_smem_bytes(TC_STAGES)>(a, merge_index, num_splits, merge_item, kvh,
                                      reinterpret_cast<float*>(smem_al), &merge_bar);
 }
 #endif  // VX_HEAD_DIM == 128
@@ -1988,14 +1990,27 @@ VX_API int vx_attention(int kind, const void* q, void* out, const void* k_cache,
     }
 #if VX_HEAD_DIM == 128
   } else if (kind == 3) {
-    const size_t smem = TC_SMEM_BYTES + 1024;
     static bool configured = false;
     if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)tc_smem_bytes(2) + 1024);
+      if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(attn_tc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)tc_smem_bytes(4) + 1024);
       if (e != cudaSuccess) return (int)e;
       configured = true;
     }
-    launch_pdl(attn_tc_kernel, dim3(grid), dim3(TC_THREADS), smem, stream, a);
+    static int sms = 0;
+    if (sms == 0) {
+      int device = 0;
+      if (cudaGetDevice(&device) != cudaSuccess ||
+          cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0)
+        sms = 148;
+    }
+    if ((long long)num_items * num_kv_heads <= 2LL * sms)
+      launch_pdl(attn_tc_kernel<4>, dim3(grid), dim3(TC_THREADS), tc_smem_bytes(4) + 1024, stream, a);
+    else
+      launch_pdl(attn_tc_kernel<2>, dim3(grid), dim3(TC_THREADS), tc_smem_bytes(2) + 1024, stream, a);
 #endif
   } else {
     return (int)cudaErrorInvalidValue;
