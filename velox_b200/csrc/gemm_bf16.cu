@@ -217,8 +217,9 @@ struct GemmShape {
   static constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
   // Where the peers of a cluster deposit their shares of this CTA's output slice:
   // [splits][128 / splits rows][BN tokens] floats, then [8][BN] sums of squares of the fused
-  // norm (token tiles up to 64 only).
-  static constexpr uint32_t RECV_BYTES = BN <= 64 ? ((GB_BM * BN * 4 + 8 * BN * 4 + 1023) / 1024) * 1024 : 0;
+  // norm (token tiles up to 64 only).  The SwiGLU epilogue, which is never clustered, uses the
+  // same place for the exchange between its gate and up rows (64 x 33 floats).
+  static constexpr uint32_t RECV_BYTES = BN <= 64 ? ((GB_BM * BN * 4 + 8 * BN * 4 + 1023) / 1024) * 1024 : 9216;
   // Fused norm: K blocks whose X tiles one batch of loads makes, and the most batches.
   static constexpr int NORM_BATCH = BN <= 16 ? 6 : (BN <= 32 ? 4 : 2);
   static constexpr int NORM_MAX_BATCHES = 32;
@@ -236,13 +237,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   __shared__ __align__(8) uint64_t acc_bar;
   __shared__ uint32_t tmem_slot;
   __shared__ int epilogue_failed;
-  __shared__ float swap_buf[64 * 33];
   __shared__ float ssq_s[64];  // fused norm: this CTA's sums of squares, then 1 / rms, per token
   __shared__ __align__(8) uint64_t x_bar[S::NORM_MAX_BATCHES];  // fused norm: a batch of X tiles is ready
 
   VX_TRACE_SCOPE(10 + g.mode);
   allow_dependents();
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  float* swap_buf = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw)) + S::STAGES * S::STAGE_BYTES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * (g.mode == 3 ? 64 : GB_BM);
   const int t0 = blockIdx.y * BN;
@@ -839,7 +840,10 @@ static int gemm_bf16(const void* x, int x_rows, const float* resid, long long re
       const int code = deep ? launch_gemm<32, 8>(mw, mw2, mx, g, grid, stream) : -2;
       return code != -2 ? code : launch_gemm<32, 4>(mw, mw2, mx, g, grid, stream);
     }
-    case 64: return launch_gemm<64, 4>(mw, mw2, mx, g, grid, stream);
+    // A short K chunk needs no deep ring, and with two stages two CTAs share an SM: sixteen
+    // clusters of eight then run in one wave (one CTA per SM fits fifteen of them on this GPU).
+    case 64: return g.kb_per_split <= 4 ? launch_gemm<64, 2>(mw, mw2, mx, g, grid, stream)
+                                        : launch_gemm<64, 4>(mw, mw2, mx, g, grid, stream);
     case 128: return launch_gemm<128, 4>(mw, mw2, mx, g, grid, stream);
     default: return launch_gemm<256, 4>(mw, mw2, mx, g, grid, stream);
   }
