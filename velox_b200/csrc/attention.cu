@@ -25,6 +25,17 @@
 //   kv_begin <= n < kv_end, n <= pos, and n > pos - window when window > 0.
 // Key tiles start at multiples of the tile width from position 0, whatever kv_begin is, so the
 // float32 result of an unsplit row does not depend on how the prompt was cut into portions.
+//
+// Kernel families (the `kind` of a launch):
+//   0  attn_f32_kernel      float32, FFMA, 16 rows x 32 keys; its splits are merged by
+//                           attn_merge_kernel
+//   1  attn_wide_kernel     bf16, mma.sync, 64 rows: prompt portions of head sizes without a
+//                           tensor-memory kernel
+//   2  attn_narrow_kernel   bf16, mma.sync with keys on the M side, up to 16 rows: decode tokens
+//                           and short portions; producer warp, mbarrier ring, clusters
+//   3  attn_tc_kernel       bf16, tcgen05.mma with S and O in tensor memory, 128 rows: prompt
+//                           portions at head size 128
+// The bf16 families merge split key ranges themselves (the last CTA of an item to finish).
 #include <cuda.h>
 
 #include "common.cuh"
@@ -300,20 +311,6 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&v);
-}
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
-  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem);
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(addr), "l"(gmem));
-}
-__device__ __forceinline__ void cp_async_wait_all() {
-  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
-}
-__device__ __forceinline__ void cp_async_commit() {
-  asm volatile("cp.async.commit_group;\n" ::: "memory");
-}
-// Wait until at most one committed group (the newest) is still in flight.
-__device__ __forceinline__ void cp_async_wait_but_one() {
-  asm volatile("cp.async.wait_group 1;\n" ::: "memory");
 }
 
 // Called by `threads` threads numbered tid = 0 .. threads - 1.
@@ -782,11 +779,6 @@ __device__ __forceinline__ void st_cluster_f2(uint32_t addr, float2 v) {
 }
 __device__ __forceinline__ void st_cluster_f1(uint32_t addr, float v) {
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
-}
-
-template <int N>
-__device__ __forceinline__ void cp_async_wait_group() {
-  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
 }
 
 // ---------------------------------------------------------------------------------------------
