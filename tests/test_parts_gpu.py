@@ -312,3 +312,210 @@ def test_toy_architecture_with_stateful_mixer(tmp_path, dtype):
     finally:
         unregister_architecture(TOY_ARCH)
         unregister_part("mixer", "toy_running_mean")
+
+
+# ----------------------------------------------------------------------------------------------
+# A second toy architecture: a feed-forward that routes, and a position encoding of its own
+# ----------------------------------------------------------------------------------------------
+ROUTED_ARCH = "ToyRoutedForCausalLM"
+ROUTER_SCALE = 40.0  # router logits far enough apart that no token sits between two experts
+
+
+def register_routed_toy():
+    from velox_b200.config import ModelConfig, register_architecture
+    from velox_b200.parts import register_part
+    from velox_b200.parts.base import FeedForward, PositionEncoding
+    from velox_b200.parts.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, TensorSource, WeightSpec
+
+    @register_part("feed_forward", "toy_top1_experts")
+    class Top1Experts(FeedForward):
+        """out[t] = p * W2[e] relu(W1[e] x[t]) for the expert e with the largest router logit,
+        p its softmax probability (float32 router).  Torch ops: a test double."""
+
+        def __init__(self, params, weights, dtype, device):
+            super().__init__(params, weights, dtype, device)
+            self.E, self.I, self.N = int(params["hidden_size"]), int(params["inner"]), int(params["experts"])
+            self.scale = float(params["router_scale"])
+            self.router = self.expect("router.weight", (self.N, self.E))
+            self.w1 = self.expect("w1", (self.N * self.I, self.E))
+            self.w2 = self.expect("w2", (self.N * self.E, self.I))
+
+        def forward(self, x, ctx):
+            T = ctx.num_tokens
+            out = ctx.workspace.get("toy.routed", (ctx.workspace.max_tokens, self.E), self.dtype)
+            rows = x[:T].float()
+            probs = torch.softmax(self.scale * (rows @ self.router.float().T), dim=-1)
+            weight, expert = probs.max(dim=-1)
+            result = torch.zeros(T, self.E, device=x.device, dtype=torch.float32)
+            for e in range(self.N):
+                mine = (expert == e).nonzero().flatten()
+                if mine.numel() == 0:
+                    continue
+                w1 = self.w1[e * self.I : (e + 1) * self.I].float()
+                w2 = self.w2[e * self.E : (e + 1) * self.E].float()
+                result[mine] = (torch.relu(rows[mine] @ w1.T) @ w2.T) * weight[mine].unsqueeze(1)
+            out[:T] = result.to(self.dtype)
+            return out
+
+    @register_part("position", "toy_rotary_pairs")
+    class RotaryPairs(PositionEncoding):
+        """Rotation of neighbouring pairs (2i, 2i + 1) of every head by position * theta^(-i/(D/2)),
+        and the write of k and v into the paged cache, with torch ops."""
+
+        def __init__(self, params, weights, dtype, device):
+            super().__init__(params, weights, dtype, device)
+            self.D = int(params["head_dim"])
+            self.inv_freq = (float(params["theta"]) ** (-torch.arange(self.D // 2, dtype=torch.float32) / (self.D // 2))).to(device)
+
+        def rotate_and_store(self, qkv, ctx, slots, k_cache, v_cache, num_heads, num_kv_heads):
+            T, D = ctx.num_tokens, self.D
+            ang = ctx.positions[:T].float().unsqueeze(1) * self.inv_freq
+            cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+
+            def rotate(x):  # [T, heads, D]
+                even, odd = x[..., 0::2].float(), x[..., 1::2].float()
+                return torch.stack([even * cos - odd * sin, even * sin + odd * cos], dim=-1).flatten(-2).to(x.dtype)
+
+            q = qkv[:T, : num_heads * D].view(T, num_heads, D)
+            k = qkv[:T, num_heads * D : (num_heads + num_kv_heads) * D].view(T, num_kv_heads, D)
+            v = qkv[:T, (num_heads + num_kv_heads) * D :].view(T, num_kv_heads, D)
+            q.copy_(rotate(q))
+            if k_cache is not None:
+                keep = (slots[:T] >= 0).nonzero().flatten()
+                where = slots[:T][keep].long()
+                k_cache.view(-1, num_kv_heads, D)[where] = rotate(k)[keep]
+                v_cache.view(-1, num_kv_heads, D)[where] = v[keep]
+
+    @dataclass(frozen=True)
+    class RoutedConfig(ModelConfig):
+        num_attention_heads: int = 3
+        num_key_value_heads: int = 1
+        head_dim: int = 32
+        inner: int = 40
+        experts: int = 3
+
+        def to_json_dict(self):
+            return {"architectures": [self.architecture], "vocab_size": self.vocab_size, "hidden_size": self.hidden_size,
+                    "num_hidden_layers": self.num_hidden_layers, "max_position_embeddings": self.max_position_embeddings,
+                    "tie_word_embeddings": self.tie_word_embeddings, "num_attention_heads": self.num_attention_heads,
+                    "num_key_value_heads": self.num_key_value_heads, "head_dim": self.head_dim, "inner": self.inner,
+                    "experts": self.experts}
+
+    def parse(cfg: Mapping[str, Any]) -> RoutedConfig:
+        keys = ("vocab_size", "hidden_size", "num_hidden_layers", "max_position_embeddings", "tie_word_embeddings",
+                "num_attention_heads", "num_key_value_heads", "head_dim", "inner", "experts")
+        return RoutedConfig(architecture=ROUTED_ARCH, **{k: cfg[k] for k in keys})
+
+    def build(c: RoutedConfig) -> ModelSpec:
+        E, H, G, D, V = c.hidden_size, c.num_attention_heads, c.num_key_value_heads, c.head_dim, c.vocab_size
+        mat = lambda *src: WeightSpec(tuple(src), "matrix")
+        vec = lambda *src: WeightSpec(tuple(src), "vector")
+        rms = lambda name: PartSpec("rms", {"size": E, "eps": 1e-5},
+                                    {"weight": vec(TensorSource(name, (E,), "one_plus_normal"))})
+        position = PartSpec("toy_rotary_pairs", {"head_dim": D, "theta": 200.0})
+        layers = []
+        for i in range(c.num_hidden_layers):
+            p = f"l{i}."
+            attn = PartSpec("attention", {"hidden_size": E, "num_heads": H, "num_kv_heads": G, "head_dim": D,
+                                          "qkv_bias": False, "window": None, "softmax_scale": 1 / math.sqrt(D)}, {
+                "qkv.weight": mat(TensorSource(p + "q.weight", (H * D, E)), TensorSource(p + "k.weight", (G * D, E)),
+                                  TensorSource(p + "v.weight", (G * D, E))),
+                "out.weight": mat(TensorSource(p + "o.weight", (E, H * D)))})
+            ffn = PartSpec("toy_top1_experts", {"hidden_size": E, "inner": c.inner, "experts": c.experts,
+                                                "router_scale": ROUTER_SCALE}, {
+                "router.weight": vec(TensorSource(p + "router.weight", (c.experts, E))),
+                "w1": mat(TensorSource(p + "w1", (c.experts * c.inner, E))),
+                "w2": mat(TensorSource(p + "w2", (c.experts * E, c.inner)))})
+            layers.append(LayerSpec("pre_norm", attn, ffn, {"mixer": rms(p + "n1"), "feed_forward": rms(p + "n2")}, position))
+        embed = TensorSource("embed.weight", (V, E))
+        return ModelSpec(
+            architecture=ROUTED_ARCH, hidden_size=E, vocab_size=V, max_position=c.max_position_embeddings,
+            embedding=PartSpec("token_embedding", {"vocab_size": V, "hidden_size": E}, {"weight": mat(embed)}),
+            layers=tuple(layers), schedule=tuple(ScheduleEntry(i) for i in range(c.num_hidden_layers)),
+            final_norm=rms("final.weight"),
+            lm_head=PartSpec("linear_head", {"hidden_size": E, "vocab_size": V}, {"weight": mat(embed)}),
+        )
+
+    register_architecture(ROUTED_ARCH, parse, build)
+
+
+def routed_plain_logits(tensors, cfg, tokens):
+    """Plain float64 forward of the routed toy model, whole sequence; also the smallest gap
+    between the two largest router probabilities (a tie there is a coin toss for any engine)."""
+    t = {k: v.double() for k, v in tensors.items()}
+    E, H, G, D = cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    I, N, T = cfg["inner"], cfg["experts"], len(tokens)
+    h = t["embed.weight"][torch.tensor(tokens)]
+    inv_freq = 200.0 ** (-torch.arange(D // 2, dtype=torch.float64) / (D // 2))
+    ang = torch.arange(T, dtype=torch.float64).unsqueeze(1) * inv_freq
+    cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+
+    def rotate(x):
+        even, odd = x[..., 0::2], x[..., 1::2]
+        return torch.stack([even * cos - odd * sin, even * sin + odd * cos], dim=-1).flatten(-2)
+
+    norm = lambda x, name: plain_model.rms_norm(x, t[name], 1e-5)
+    margin = float("inf")
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"l{i}."
+        x = norm(h, p + "n1")
+        q = rotate((x @ t[p + "q.weight"].T).view(T, H, D))
+        k = rotate((x @ t[p + "k.weight"].T).view(T, G, D)).repeat_interleave(H // G, dim=1)
+        v = (x @ t[p + "v.weight"].T).view(T, G, D).repeat_interleave(H // G, dim=1)
+        o = plain_model.causal_attention(q, k, v, 1 / math.sqrt(D))
+        h = h + o.reshape(T, H * D) @ t[p + "o.weight"].T
+        x = norm(h, p + "n2")
+        probs = torch.softmax(ROUTER_SCALE * (x @ t[p + "router.weight"].T), dim=-1)
+        top2 = probs.topk(2, dim=-1).values
+        margin = min(margin, float((top2[:, 0] - top2[:, 1]).min()))
+        weight, expert = probs.max(dim=-1)
+        out = torch.zeros(T, E, dtype=torch.float64)
+        for e in range(N):
+            mine = (expert == e).nonzero().flatten()
+            w1, w2 = t[p + "w1"][e * I : (e + 1) * I], t[p + "w2"][e * E : (e + 1) * E]
+            out[mine] = (torch.relu(x[mine] @ w1.T) @ w2.T) * weight[mine].unsqueeze(1)
+        h = h + out
+    return norm(h, "final.weight") @ t["embed.weight"].T, margin
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_with_routed_feed_forward_and_its_own_position_encoding(tmp_path, dtype):
+    """A feed-forward that routes tokens to experts and a position encoding that rotates pairs,
+    both defined here, in a model built, loaded and stepped by the framework as it is."""
+    from velox_b200.config import unregister_architecture
+    from velox_b200.engine.replay import TraceReplayer
+    from velox_b200.parts import unregister_part
+    from velox_b200.weights import write_random_model
+
+    register_routed_toy()
+    try:
+        cfg = {"architectures": [ROUTED_ARCH], "vocab_size": 61, "hidden_size": 56, "num_hidden_layers": 2,
+               "max_position_embeddings": 96, "tie_word_embeddings": True, "num_attention_heads": 3,
+               "num_key_value_heads": 1, "head_dim": 32, "inner": 40, "experts": 3}
+        folder = str(tmp_path)
+        write_random_model(folder, cfg, seed=15, dtype="bfloat16", std=0.1)
+        tensors = read_tensors(folder)
+        prompts = random_prompts(61, (40, 17), seed=8)
+        refs = [routed_plain_logits(tensors, cfg, p) for p in prompts]
+        assert min(m for _, m in refs) > 0.05, "pick another seed: two experts nearly tie for a token"
+        replayer = TraceReplayer(folder, dtype, max_tokens=128, block_size=8)
+        a, b = prompts
+        got_a, got_b = np.zeros((40, 61), np.float32), np.zeros((17, 61), np.float32)
+        plan = [[("a", 0, 30)], [("a", 30, 1), ("b", 0, 15)], [("a", 31, 1), ("b", 15, 1)], [("a", 32, 8), ("b", 16, 1)]]
+        for step, entries in enumerate(plan):
+            rec = {"step": step, "end": ["a", "b"] if step == len(plan) - 1 else [],
+                   "entries": [{"id": n, "tokens": (a if n == "a" else b)[s : s + c], "want": list(range(c))} for n, s, c in entries]}
+            out = replayer.run_step(rec)
+            row = 0
+            for n, s, c in entries:
+                (got_a if n == "a" else got_b)[s : s + c] = out[row : row + c]
+                row += c
+        tol = 2e-5 if dtype == "float32" else 3e-2
+        for got, (ref, _), what in ((got_a, refs[0], "a"), (got_b, refs[1], "b")):
+            err = (torch.from_numpy(got).double() - ref).abs().max().item()
+            assert err <= tol * ref.abs().max().item(), (what, err, ref.abs().max().item())
+        assert replayer.cache.num_free_pages() == replayer.cache.num_total_pages
+    finally:
+        unregister_architecture(ROUTED_ARCH)
+        unregister_part("feed_forward", "toy_top1_experts")
+        unregister_part("position", "toy_rotary_pairs")
