@@ -278,3 +278,69 @@ def test_single_token_layout_matches_the_general_planner():
             assert slow.partial_rows == partial_rows
         else:
             assert merges is None and len(slow.merge_items) == 0
+
+
+def test_attention_plan_covers_every_visible_key_exactly_once():
+    """Whatever the step, the options and the splits: for every row tile, the key ranges of its
+    items are disjoint, tile-aligned inside, and their union is what the tile's rows may see."""
+    import numpy as np
+
+    from velox_b200.ops import attention_plan as ap
+
+    rng = np.random.default_rng(1)
+    for trial in range(80):
+        group = int(rng.choice([1, 3, 6, 7, 16, 20]))
+        kv_heads = int(rng.choice([1, 2, 4]))
+        window = None if trial % 4 else int(rng.choice([5, 64, 500]))
+        opt = ap.PlanOptions(
+            num_kv_heads=kv_heads, group=group, window=window, use_f32=bool(trial % 3 == 0),
+            min_split_keys=int(rng.choice([32, 256])), target_ctas=int(rng.choice([16, 296, 5000])),
+            narrow_max_cluster=int(rng.choice([1, 4, 8])), narrow_global_split_keys=int(rng.choice([32, 1024])),
+            narrow_cluster_limits=((8, 15), (4, 37), (2, 74)) if trial % 2 else (),
+            wide_on_tensor_memory=bool(trial % 5 == 0),
+        )
+        n = int(rng.integers(1, 7))
+        q_lens = [int(rng.choice([1, 1, 2, 9, 70, 300])) for _ in range(n)]
+        kv_lens = [q + int(rng.integers(0, 3000)) for q in q_lens]
+        plan = ap.plan_attention(q_lens, kv_lens, opt)
+        assert plan.cluster in (1, 2, 4, 8) and plan.cluster <= opt.narrow_max_cluster
+        covered = {}
+        for kind, items in plan.items.items():
+            height = ap.TILE_ROWS[kind]
+            for seq, row_begin, row_count, lo, hi, partial_base, merge_index, splits in items.tolist():
+                assert 0 < row_count <= height and row_begin % height == 0
+                assert (partial_base >= 0) == (splits > 1)
+                covered.setdefault((seq, row_begin, row_count), []).append((lo, hi))
+        tiles = 0
+        for seq, (q_len, kv_len) in enumerate(zip(q_lens, kv_lens)):
+            rows = q_len * group
+            kinds = [k for k, items in plan.items.items() if (items[:, 0] == seq).any()]
+            assert len(kinds) == 1
+            height = ap.TILE_ROWS[kinds[0]]
+            for row_begin in range(0, rows, height):
+                row_count = min(height, rows - row_begin)
+                ranges = sorted(r for r in covered[(seq, row_begin, row_count)] if r[1] > r[0])
+                ctx = kv_len - q_len
+                hi_want = ctx + (row_begin + row_count - 1) // group + 1
+                lo_want = max(0, ctx + row_begin // group - window + 1) if window else 0
+                assert ranges[0][0] == lo_want and ranges[-1][1] == hi_want, (trial, ranges, lo_want, hi_want)
+                for (a_lo, a_hi), (b_lo, b_hi) in zip(ranges, ranges[1:]):
+                    assert a_hi == b_lo and a_hi % ap.KEY_TILE == 0
+                tiles += 1
+        assert tiles == len(covered)
+
+
+def test_cluster_size_fits_in_one_wave():
+    from velox_b200.ops import attention_plan as ap
+
+    limits = ((8, 15), (4, 37), (2, 74))
+    opt = ap.PlanOptions(num_kv_heads=2, group=6, window=None, use_f32=False, narrow_max_cluster=8,
+                         narrow_cluster_limits=limits)
+    assert ap.choose_cluster(opt, pairs=2, wanted=74) == 8
+    assert ap.choose_cluster(opt, pairs=16, wanted=9) == 4      # sixteen clusters of eight do not fit
+    assert ap.choose_cluster(opt, pairs=16, wanted=3) == 2
+    assert ap.choose_cluster(opt, pairs=64, wanted=2) == 2
+    assert ap.choose_cluster(opt, pairs=128, wanted=2) == 1     # more pairs than clusters of two fit
+    assert ap.choose_cluster(opt, pairs=4, wanted=1) == 1
+    unlimited = ap.PlanOptions(num_kv_heads=2, group=6, window=None, use_f32=False, narrow_max_cluster=8)
+    assert ap.choose_cluster(unlimited, pairs=500, wanted=9) == 8
