@@ -400,10 +400,114 @@ VX_API int vx_embed(const void* table, int dtype, const int* ids, float* resid, 
   return (int)cudaGetLastError();
 }
 
+// The same for rows whose length is a multiple of 4: a thread takes chunks of four consecutive
+// elements (16-byte loads of the residual and the weight, 8- or 16-byte loads of the delta),
+// at most NORM_VEC_CHUNKS of them, kept in registers across the reduction.
+constexpr int NORM_VEC_CHUNKS = 2;
+
+template <typename T>
+__device__ __forceinline__ float4 load4_as_float(const T* p);
+template <>
+__device__ __forceinline__ float4 load4_as_float<float>(const float* p) {
+  return *reinterpret_cast<const float4*>(p);
+}
+template <>
+__device__ __forceinline__ float4 load4_as_float<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+template <typename T>
+__device__ __forceinline__ void store4_from_float(T* p, float4 v);
+template <>
+__device__ __forceinline__ void store4_from_float<float>(float* p, float4 v) {
+  *reinterpret_cast<float4*>(p) = v;
+}
+template <>
+__device__ __forceinline__ void store4_from_float<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<const uint32_t*>(&a);
+  raw.y = *reinterpret_cast<const uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+template <typename T>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+                                       const float* __restrict__ weight, float eps,
+                                       T* __restrict__ out, const int* __restrict__ rows, int hidden,
+                                       int write_resid) {
+  __shared__ float scratch[32];
+  VX_TRACE_SCOPE(2);
+  allow_dependents();
+  const int chunks = hidden >> 2;
+  // The weight does not depend on the kernel before.
+  float4 wts[NORM_VEC_CHUNKS];
+#pragma unroll
+  for (int j = 0; j < NORM_VEC_CHUNKS; ++j) {
+    const int c = threadIdx.x + j * blockDim.x;
+    wts[j] = c < chunks ? *reinterpret_cast<const float4*>(weight + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  grid_dependency_wait();
+  const int o = blockIdx.x;
+  const int r = rows ? rows[o] : o;
+  float* x = resid + (size_t)r * hidden;
+  const T* d = delta ? delta + (size_t)r * hidden : nullptr;
+  float4 vals[NORM_VEC_CHUNKS];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < NORM_VEC_CHUNKS; ++j) {
+    const int c = threadIdx.x + j * blockDim.x;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c < chunks) {
+      v = *reinterpret_cast<const float4*>(x + 4 * c);
+      if (d) {
+        const float4 e = load4_as_float<T>(d + 4 * c);
+        v.x += e.x;
+        v.y += e.y;
+        v.z += e.z;
+        v.w += e.w;
+      }
+    }
+    vals[j] = v;
+    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+  T* y = out + (size_t)o * hidden;
+#pragma unroll
+  for (int j = 0; j < NORM_VEC_CHUNKS; ++j) {
+    const int c = threadIdx.x + j * blockDim.x;
+    if (c < chunks) {
+      const float4 v = vals[j];
+      if (write_resid && d) *reinterpret_cast<float4*>(x + 4 * c) = v;
+      store4_from_float<T>(y + 4 * c, make_float4(v.x * inv * wts[j].x, v.y * inv * wts[j].y,
+                                                   v.z * inv * wts[j].z, v.w * inv * wts[j].w));
+    }
+  }
+}
+
 VX_API int vx_add_rmsnorm(float* resid, const void* delta, const float* weight, float eps,
                           void* out, int dtype, const int* rows, int num_out_rows, int hidden,
                           int write_resid, cudaStream_t stream) {
   if (num_out_rows <= 0) return 0;
+  const bool aligned = (reinterpret_cast<uintptr_t>(resid) & 15) == 0 && (reinterpret_cast<uintptr_t>(weight) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(out) & 15) == 0 && (reinterpret_cast<uintptr_t>(delta) & 15) == 0;
+  if (aligned && hidden % 4 == 0 && hidden / 4 <= 1024 * NORM_VEC_CHUNKS) {
+    // One chunk of four per thread, two for rows of more than 4,096 elements.
+    const int chunks = hidden / 4;
+    int block = chunks <= 1024 ? chunks : (chunks + 1) / 2;
+    block = (block + 31) / 32 * 32;
+    if (block < 64) block = 64;
+    if (dtype == VX_DTYPE_F32)
+      launch_pdl(add_rmsnorm_vec_kernel<float>, dim3(num_out_rows), dim3(block), 0, stream, resid,
+                 (const float*)delta, weight, eps, (float*)out, rows, hidden, write_resid);
+    else
+      launch_pdl(add_rmsnorm_vec_kernel<__nv_bfloat16>, dim3(num_out_rows), dim3(block), 0, stream, resid,
+                 (const __nv_bfloat16*)delta, weight, eps, (__nv_bfloat16*)out, rows, hidden, write_resid);
+    return (int)cudaGetLastError();
+  }
   // About four elements per thread: enough loads in flight per row without starving the sum.
   int threads = ((hidden + 3) / 4 + 31) / 32 * 32;
   threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);

@@ -22,6 +22,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import gc
 import os
 
 import numpy as np
@@ -559,8 +560,16 @@ class ModelRunner:
         layout = self._last_layout
         graph = torch.cuda.CUDAGraph()
         launches_before = kernels.launch_count
-        with torch.cuda.graph(graph):
-            logits = self.model.forward(ctx, self.layer_caches, ids, rows, count)
+        # No cycle collection while the stream is capturing: a collected tensor frees device
+        # memory, and the allocator's bookkeeping for that is not allowed during a capture.
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(ctx, self.layer_caches, ids, rows, count)
+        finally:
+            if collecting:
+                gc.enable()
         launches = kernels.launch_count - launches_before
         torch.cuda.synchronize(self.device)
         if generation != (self.workspace.generation, self._meta_generation):
