@@ -941,6 +941,15 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t v) {
 // g and g + 8 of rows 8 j + 2 q + {0, 1}.
 // Afterwards the warp's sums, maxima and denominators are in registers; write_rows() puts them
 // into the cross-warp merge buffer.
+constexpr float NARROW_RESCALE_AT = 8.0f;  // log2 units
+
+// 2^x by the special-function unit alone: -inf gives 0.
+__device__ __forceinline__ float narrow_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <int NR>
 struct NarrowWarp {
   float o[D / 16][NR][4];
@@ -992,46 +1001,78 @@ struct NarrowWarp {
 #pragma unroll
       for (int j = 0; j < NR; ++j) mma_bf16(s[j], ka, qb[kk][2 * j], qb[kk][2 * j + 1]);
     }
-    // Masks and the running softmax of the rows this thread holds (two per n-tile); a row's
-    // keys lie in this thread's two halves and in the eight lanes with the same lane % 4.
+    // The rows this thread holds (two per n-tile) have their keys in this thread's two halves
+    // and in the eight lanes with the same lane % 4.  Most tiles lie wholly inside what every
+    // row may see and need no masks (rows past the item's last are never read back: they count
+    // as seeing everything).  The scores stay unscaled; the scale goes into the exponent's
+    // multiply-add.  m is the maximum the exponentials refer to: it follows the true maximum
+    // only when that has grown by more than 2^8 since (P then stays below 2^8, which bf16
+    // holds as well as 1), so that most tiles rescale nothing.  l is this thread's share of
+    // the row's sum; the lanes' shares are added up once, in write_rows().
     const int g = lane >> 2;
-    float alpha[NR][2];
+    bool sees_all = true;
+#pragma unroll
+    for (int j = 0; j < NR; ++j)
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int p = pos[j][i];
+        if (p >= 0)
+          sees_all = sees_all && nbase >= kv_begin && nbase + 16 <= kv_end && nbase + 15 <= p &&
+                     (window <= 0 || nbase > p - window);
+      }
+    if (!__all_sync(0xffffffffu, sees_all)) {
+#pragma unroll
+      for (int j = 0; j < NR; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int p = pos[j][e & 1];
+          if (p >= 0 && !key_visible(nbase + g + 8 * (e >> 1), p, kv_begin, kv_end, window))
+            s[j][e] = -CUDART_INF_F;
+        }
+    }
+    float mx[NR][2];
+    bool move = false;
+#pragma unroll
+    for (int j = 0; j < NR; ++j)
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        float v = fmaxf(s[j][i], s[j][i + 2]);
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
+        mx[j][i] = v * scale_log2;  // the scale is positive
+        move = move || mx[j][i] > m[j][i] + NARROW_RESCALE_AT ||
+               (m[j][i] == -CUDART_INF_F && mx[j][i] > -CUDART_INF_F);
+      }
+    if (__any_sync(0xffffffffu, move)) {
+      float alpha[NR][2];
+#pragma unroll
+      for (int j = 0; j < NR; ++j)
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const bool mine = mx[j][i] > m[j][i] + NARROW_RESCALE_AT ||
+                            (m[j][i] == -CUDART_INF_F && mx[j][i] > -CUDART_INF_F);
+          const float m_new = mine ? mx[j][i] : m[j][i];
+          alpha[j][i] = m[j][i] == -CUDART_INF_F ? 0.f : exp2f(m[j][i] - m_new);
+          l[j][i] *= alpha[j][i];
+          m[j][i] = m_new;
+        }
+#pragma unroll
+      for (int mt = 0; mt < D / 16; ++mt)
+#pragma unroll
+        for (int j = 0; j < NR; ++j)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) o[mt][j][e] *= alpha[j][e & 1];
+    }
 #pragma unroll
     for (int j = 0; j < NR; ++j) {
-      float mx[2] = {-CUDART_INF_F, -CUDART_INF_F};
+      const float neg_m[2] = {m[j][0] == -CUDART_INF_F ? 0.f : -m[j][0],
+                              m[j][1] == -CUDART_INF_F ? 0.f : -m[j][1]};
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const int i = e & 1;
-        const int n = nbase + g + 8 * (e >> 1);
-        float v = s[j][e] * scale_log2;
-        if (pos[j][i] < 0 || !key_visible(n, pos[j][i], kv_begin, kv_end, window)) v = -CUDART_INF_F;
-        s[j][e] = v;
-        mx[i] = fmaxf(mx[i], v);
-      }
-      float m_safe[2];
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 4));
-        mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 8));
-        mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 16));
-        const float m_new = fmaxf(m[j][i], mx[i]);
-        m_safe[i] = m_new == -CUDART_INF_F ? 0.f : m_new;
-        alpha[j][i] = exp2f(m[j][i] - m_safe[i]);
-        m[j][i] = m_new;
-      }
-      float sum[2] = {0.f, 0.f};
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float p = exp2f(s[j][e] - m_safe[e & 1]);
+        const float p = narrow_exp2(fmaf(s[j][e], scale_log2, neg_m[e & 1]));
         s[j][e] = p;
-        sum[e & 1] += p;
-      }
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 4);
-        sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 8);
-        sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 16);
-        l[j][i] = l[j][i] * alpha[j][i] + sum[i];
+        l[j][e & 1] += p;
       }
     }
     // P^T as the B operand: the accumulator layout, transposed eight by eight.
@@ -1047,11 +1088,7 @@ struct NarrowWarp {
       ldmatrix_x4_trans(va, kv_chunk(v_s, key0 + (lane & 7) + (lane >> 4) * 8,
                                      mt * 16 + ((lane >> 3) & 1) * 8));
 #pragma unroll
-      for (int j = 0; j < NR; ++j) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) o[mt][j][e] *= alpha[j][e & 1];
-        mma_bf16(o[mt][j], va, pb[j][0], pb[j][1]);
-      }
+      for (int j = 0; j < NR; ++j) mma_bf16(o[mt][j], va, pb[j][0], pb[j][1]);
     }
   }
 
@@ -1069,9 +1106,13 @@ struct NarrowWarp {
           dst[mt * 16] = o[mt][j][i];
           dst[mt * 16 + 8] = o[mt][j][i + 2];
         }
+        float total = l[j][i];
+        total += __shfl_xor_sync(0xffffffffu, total, 4);
+        total += __shfl_xor_sync(0xffffffffu, total, 8);
+        total += __shfl_xor_sync(0xffffffffu, total, 16);
         if (g == 0) {
           mm[r] = m[j][i];
-          ml[r] = l[j][i];
+          ml[r] = total;
         }
       }
   }
