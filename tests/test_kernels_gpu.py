@@ -487,7 +487,26 @@ def test_sample_greedy_first_maximum(k):
     assert out[0] == 30 and out[1] == 999 and out[2] == 0
 
 
-@pytest.mark.parametrize("vocab", [331, 5000])
+@pytest.mark.parametrize("vocab,rows", [(20011, 3), (151936, 8), (40960, 70)])
+def test_sample_greedy_in_segments(k, vocab, rows):
+    """Rows long enough to be cut into segments (20011: rows that do not start on 16 bytes): the
+    first maximum wins across segments too, launch after launch (the arrival counters go back
+    to zero)."""
+    gen = torch.Generator().manual_seed(vocab)
+    logits = torch.randn(rows, vocab, generator=gen).cuda()
+    logits[0, vocab - 1] = 40.0
+    logits[0, 3000] = 40.0
+    logits[1, vocab - 2] = 41.0
+    logits[2] = -1.0  # all equal: index 0
+    out = torch.empty(rows, dtype=torch.int32, device="cuda")
+    for _ in range(3):
+        out.fill_(-1)
+        k.sample(logits, rows, None, None, None, None, out)
+        assert out.tolist() == torch.argmax(logits, dim=-1).tolist()
+    assert out[0] == 3000 and out[1] == vocab - 2 and out[2] == 0
+
+
+@pytest.mark.parametrize("vocab", [331, 5000, 20011, 40960])
 def test_sample_temperature_matches_plain_restatement(k, vocab):
     gen = torch.Generator().manual_seed(vocab)
     R = 6

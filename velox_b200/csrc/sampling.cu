@@ -101,29 +101,57 @@ __device__ __forceinline__ Best block_best(Best v, Best* scratch /* 32 */) {
 // ---------------------------------------------------------------------------------------------
 // One token per row.  temperature[r] == 0: argmax.  Otherwise the exponential race over the
 // entries with logit / T >= threshold[r] (threshold may be null: no filter).
+//
+// A row is cut into gridDim.y segments (multiples of four entries, so that the generator's
+// counter, the index of a group of four, means the same for every cut).  Every block leaves its
+// best entry in `partial`; the block that arrives last at the row's counter takes the best of
+// all of them (`better` is associative and commutative, ties included, so the result does not
+// depend on the cut or on the order of arrival), writes the token and puts the counter back to
+// zero for the next launch.
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(1024)
+constexpr int SAMPLE_THREADS = 256;
+constexpr int SAMPLE_MAX_SEGMENTS = 64;
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, int vocab, long long row_stride,
               const float* __restrict__ temperature, const unsigned long long* __restrict__ seeds,
               const int* __restrict__ draw_index, const float* __restrict__ threshold,
               int* __restrict__ out, int* __restrict__ history, long long history_stride,
-              const int* __restrict__ history_slots, const int* __restrict__ history_lengths) {
+              const int* __restrict__ history_slots, const int* __restrict__ history_lengths,
+              int segment_len, Best* __restrict__ partial, unsigned int* __restrict__ counters) {
   __shared__ Best scratch[32];
+  __shared__ bool is_last;
   allow_dependents();
   grid_dependency_wait();
   const int r = blockIdx.x;
+  const int segments = (int)gridDim.y;
+  const int begin = blockIdx.y * segment_len;
+  const int end = min(vocab, begin + segment_len);
   const float* row = logits + (size_t)r * row_stride;
   const float temp = temperature ? temperature[r] : 0.f;
+  // Groups of four entries by one 16-byte load where the row allows it.
+  const bool vec = (row_stride & 3) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0;
   Best best;
   best.score = 0.f;
   best.index = -1;
 
   if (temp == 0.f) {
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-      Best c;
-      c.score = row[i];
-      c.index = i;
-      if (c.score == c.score) best = better(best, c);
+    for (int base = begin + threadIdx.x * 4; base < end; base += SAMPLE_THREADS * 4) {
+      float v[4];
+      if (vec && base + 4 <= vocab) {
+        const float4 q = *reinterpret_cast<const float4*>(row + base);
+        v[0] = q.x, v[1] = q.y, v[2] = q.z, v[3] = q.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = base + j < vocab ? row[base + j] : CUDART_NAN_F;
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        Best c;
+        c.score = v[j];
+        c.index = base + j;
+        if (c.score == c.score) best = better(best, c);
+      }
     }
   } else {
     const float inv_t = 1.0f / fmaxf(temp, 1e-5f);
@@ -131,24 +159,49 @@ sample_kernel(const float* __restrict__ logits, int vocab, long long row_stride,
     const unsigned long long seed = seeds[r];
     const uint2 key = make_uint2((uint32_t)seed, (uint32_t)(seed >> 32));
     const uint32_t draw = (uint32_t)draw_index[r];
-    for (int base = threadIdx.x * 4; base < vocab; base += blockDim.x * 4) {
+    for (int base = begin + threadIdx.x * 4; base < end; base += SAMPLE_THREADS * 4) {
+      float v[4];
+      if (vec && base + 4 <= vocab) {
+        const float4 q = *reinterpret_cast<const float4*>(row + base);
+        v[0] = q.x, v[1] = q.y, v[2] = q.z, v[3] = q.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = base + j < vocab ? row[base + j] : CUDART_NAN_F;
+      }
       const uint4 bits = philox4x32_10(make_uint4((uint32_t)(base >> 2), draw, 0u, 0u), key);
       const uint32_t b[4] = {bits.x, bits.y, bits.z, bits.w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const int i = base + j;
-        if (i >= vocab) break;
-        const float scaled = row[i] * inv_t;
-        if (!(scaled >= cut)) continue;
+        const float scaled = v[j] * inv_t;
+        if (!(scaled >= cut)) continue;  // also what lies past the row's end (NaN)
         const float noise = fmaxf(-logf(uniform_open(b[j])), 1e-10f);
         Best c;
         c.score = scaled - logf(noise);
-        c.index = i;
+        c.index = base + j;
         best = better(best, c);
       }
     }
   }
   best = block_best(best, scratch);
+  if (segments > 1) {
+    if (threadIdx.x == 0) {
+      partial[(size_t)r * segments + blockIdx.y] = best;
+      __threadfence();
+      is_last = atomicAdd(&counters[r], 1u) == (unsigned int)segments - 1u;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    best.score = 0.f;
+    best.index = -1;
+    if ((int)threadIdx.x < segments) {
+      const volatile Best* p = partial + (size_t)r * segments + threadIdx.x;
+      best.score = p->score;
+      best.index = p->index;
+    }
+    best = block_best(best, scratch);
+    if (threadIdx.x == 0) counters[r] = 0u;
+  }
   if (threadIdx.x == 0) {
     const int token = best.index < 0 ? 0 : best.index;
     out[r] = token;
@@ -276,16 +329,34 @@ __global__ void penalty_apply_kernel(float* __restrict__ logits, long long row_s
 
 using namespace vx;
 
+// How many segments vx_sample cuts a row into, and with that the size of its scratch:
+// `partial` holds num_rows * segments pairs (float, int), `counters` num_rows zeroed uint32
+// (the kernel leaves them zero).  Both may be null when the answer is 1.
+VX_API int vx_sample_segments(int num_rows, int vocab) {
+  if (num_rows <= 0 || vocab < 8192) return 1;
+  // About two blocks per SM, and no segment below 2,048 entries.
+  int segments = (2 * 148 + num_rows - 1) / num_rows;
+  const int most = vocab / 2048;
+  if (segments > most) segments = most;
+  if (segments > SAMPLE_MAX_SEGMENTS) segments = SAMPLE_MAX_SEGMENTS;
+  return segments < 1 ? 1 : segments;
+}
+
 VX_API int vx_sample(const float* logits, int num_rows, int vocab, long long row_stride,
                      const float* temperature, const unsigned long long* seeds,
                      const int* draw_index, const float* threshold, int* out, int* history,
                      long long history_stride, const int* history_slots,
-                     const int* history_lengths, cudaStream_t stream) {
+                     const int* history_lengths, void* partial, unsigned int* counters,
+                     cudaStream_t stream) {
   if (num_rows <= 0) return 0;
-  const int threads = vocab >= 4096 ? 1024 : 256;
-  launch_pdl(sample_kernel, dim3(num_rows), dim3(threads), 0, stream, logits, vocab, row_stride, temperature, seeds,
-                                                  draw_index, threshold, out, history,
-                                                  history_stride, history_slots, history_lengths);
+  int segments = vx_sample_segments(num_rows, vocab);
+  if (partial == nullptr || counters == nullptr) segments = 1;
+  // Segments are multiples of four entries.
+  const int segment_len = (((vocab + segments - 1) / segments) + 3) / 4 * 4;
+  segments = (vocab + segment_len - 1) / segment_len;
+  launch_pdl(sample_kernel, dim3(num_rows, segments), dim3(SAMPLE_THREADS), 0, stream, logits, vocab,
+             row_stride, temperature, seeds, draw_index, threshold, out, history, history_stride,
+             history_slots, history_lengths, segment_len, (Best*)partial, counters);
   return (int)cudaGetLastError();
 }
 

@@ -53,8 +53,9 @@ def core():
         lib.vx_gemm_f32.argtypes = [_ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr]
         lib.vx_cast_bf16_to_f32.argtypes = [_ptr, _ptr, _c_ll, _ptr]
         lib.vx_sample.argtypes = [
-            _ptr, _c_int, _c_int, _c_ll, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_ll, _ptr, _ptr, _ptr,
+            _ptr, _c_int, _c_int, _c_ll, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_ll, _ptr, _ptr, _ptr, _ptr, _ptr,
         ]
+        lib.vx_sample_segments.argtypes = [_c_int, _c_int]
         lib.vx_filter_threshold.argtypes = [
             _ptr, _c_int, _c_int, _c_ll, _ptr, _ptr, _ptr, _ptr, _ptr,
         ]
@@ -567,6 +568,27 @@ def attention_merge(
 
 
 # ------------------------------------------------------------------------------------------
+# Scratch of the sampling kernel per device: the segments' best entries and the rows' arrival
+# counters (zero between launches; the kernel puts them back).
+_sample_scratch: dict = {}
+
+
+def _sample_scratch_for(device: torch.device, num_rows: int, vocab: int):
+    segments = core().vx_sample_segments(num_rows, vocab)
+    if segments <= 1:
+        return None, None
+    key = (device.type, device.index)
+    held = _sample_scratch.get(key)
+    if held is None or held[0].shape[0] < num_rows * segments or held[1].shape[0] < num_rows:
+        rows = max(num_rows, 64)
+        held = (
+            torch.zeros((rows * 64, 2), dtype=torch.int32, device=device),
+            torch.zeros(rows, dtype=torch.int32, device=device),
+        )
+        _sample_scratch[key] = held
+    return held
+
+
 def sample(
     logits: torch.Tensor,
     num_rows: int,
@@ -589,11 +611,12 @@ def sample(
         _need(temperature, torch.float32, "temperature")
         _need(seeds, torch.int64, "seeds")
         _need(draw_index, torch.int32, "draw_index")
+    partial, counters = _sample_scratch_for(logits.device, num_rows, logits.shape[1])
     _check(
         core().vx_sample(_p(logits), num_rows, logits.shape[1], logits.stride(0), _p(temperature),
                          _p(seeds), _p(draw_index), _p(threshold), _p(out), _p(history),
                          0 if history is None else history.stride(0), _p(history_slots),
-                         _p(history_lengths), _stream()),
+                         _p(history_lengths), _p(partial), _p(counters), _stream()),
         "sample",
     )
 
