@@ -628,6 +628,76 @@ struct MergeItem {
   int row_begin, rows, first, splits, stride, q_start;
 };
 
+// The same for taller tiles (up to 128 rows): sixteen rows a round would be eight round trips one
+// after the other, so here every thread reads the splits' rows straight from memory, many
+// 16-byte loads in flight at a time; only the weights go through shared memory.
+// `scratch` holds at least rows * splits floats.
+__device__ __forceinline__ void merge_tall_item_by_cta(const AttnArgs& a, const MergeItem& item, int kvh,
+                                                       float* scratch) {
+  const int row_begin = item.row_begin, rows = item.rows, splits = item.splits, stride = item.stride;
+  const size_t base0 = (size_t)item.first + (size_t)kvh * rows;
+  constexpr int VEC = D / 4;
+  float* weights = scratch;  // [rows][splits]
+  __syncthreads();           // nobody uses the scratch for anything else any more
+  for (int r = threadIdx.x; r < rows; r += blockDim.x) {
+    float mt = -CUDART_INF_F;
+    for (int s = 0; s < splits; ++s) mt = fmaxf(mt, __ldcg(&a.partial_lse[base0 + r + (size_t)s * stride]));
+    const float m_safe = mt == -CUDART_INF_F ? 0.f : mt;
+    float den = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float lse = __ldcg(&a.partial_lse[base0 + r + (size_t)s * stride]);
+      const float w = lse == -CUDART_INF_F ? 0.f : exp2f(lse - m_safe);
+      weights[r * splits + s] = w;
+      den += w;
+    }
+    const float inv = den > 0.f ? 1.0f / den : 0.f;
+    for (int s = 0; s < splits; ++s) weights[r * splits + s] *= inv;
+  }
+  __syncthreads();
+  constexpr int UNROLL = 4;
+  const int total = rows * VEC;
+  for (int idx0 = threadIdx.x; idx0 < total; idx0 += blockDim.x * UNROLL) {
+    float4 acc[UNROLL];
+    int row_of[UNROLL], col_of[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int idx = idx0 + u * blockDim.x;
+      acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      row_of[u] = idx < total ? idx / VEC : -1;
+      col_of[u] = idx - (idx / VEC) * VEC;
+    }
+    for (int s = 0; s < splits; ++s) {
+      float4 v[UNROLL];
+      float w[UNROLL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const bool on = row_of[u] >= 0;
+        v[u] = on ? __ldcg(reinterpret_cast<const float4*>(
+                        a.partial_o + (base0 + row_of[u] + (size_t)s * stride) * D + 4 * col_of[u]))
+                  : make_float4(0.f, 0.f, 0.f, 0.f);
+        w[u] = on ? weights[row_of[u] * splits + s] : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        acc[u].x += w[u] * v[u].x;
+        acc[u].y += w[u] * v[u].y;
+        acc[u].z += w[u] * v[u].z;
+        acc[u].w += w[u] * v[u].w;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      if (row_of[u] < 0) continue;
+      const int row = row_begin + row_of[u];
+      const int tok = row / a.group, hg = row - tok * a.group;
+      __nv_bfloat16* dst = (__nv_bfloat16*)a.out + (size_t)(item.q_start + tok) * a.out_stride +
+                           (size_t)(kvh * a.group + hg) * D + 4 * col_of[u];
+      *reinterpret_cast<uint2*>(dst) =
+          make_uint2(pack_bf16(acc[u].x, acc[u].y), pack_bf16(acc[u].z, acc[u].w));
+    }
+  }
+}
+
 template <int SMEM_BYTES>
 __device__ __forceinline__ void merge_item_by_cta(const AttnArgs& a, const MergeItem& item, int kvh,
                                                   float* scratch, uint64_t* bar) {
@@ -754,7 +824,10 @@ __device__ __forceinline__ void finish_split(const AttnArgs& a, int merge_index,
   __syncthreads();
   if (!last_s) return;
   __threadfence();
-  merge_item_by_cta<SMEM_BYTES>(a, item, kvh, scratch, bar);
+  if (item.rows > 16 && (size_t)item.rows * item.splits * 4 <= (size_t)SMEM_BYTES)
+    merge_tall_item_by_cta(a, item, kvh, scratch);
+  else
+    merge_item_by_cta<SMEM_BYTES>(a, item, kvh, scratch, bar);
 }
 
 __device__ __forceinline__ void cluster_arrive() {
@@ -1703,6 +1776,9 @@ __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_ke
       if (lane == 0) mbar_arrive(smem_u32(&q_ready));
     }
     const int pos = r < row_count ? ctx + (row_begin + r) / a.group : -1;
+    // The keys this row sees are vis_lo <= n < vis_lo + vis_span (none for a row past the end).
+    const int vis_lo = max(kv_begin, a.window > 0 ? pos - a.window + 1 : 0);
+    const unsigned vis_span = pos < 0 ? 0u : (unsigned)max(0, min(kv_end, pos + 1) - vis_lo);
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
     for (int t = 0; t < num_tiles; ++t) {
       const int st = t % TC_STAGES;
@@ -1728,9 +1804,10 @@ __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_ke
       const bool row_sees_all = pos >= 0 && n0 >= kv_begin && n0 + B_BN <= kv_end && n0 + B_BN - 1 <= pos &&
                                 (a.window <= 0 || n0 > pos - a.window);
       if (!__all_sync(0xffffffffu, row_sees_all)) {
+        const int rel = n0 - vis_lo;  // one unsigned compare per key: rel + i in [0, vis_span)
 #pragma unroll
         for (int i = 0; i < B_BN; ++i)
-          if (pos < 0 || !key_visible(n0 + i, pos, kv_begin, kv_end, a.window)) s[i] = -CUDART_INF_F;
+          if ((unsigned)(rel + i) >= vis_span) s[i] = -CUDART_INF_F;
       }
       float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
