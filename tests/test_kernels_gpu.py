@@ -644,7 +644,8 @@ def test_gemm_bf16_plain_and_bias(k, status, T, N, K):
 
 
 @pytest.mark.parametrize("T,N,K,splits", [(8, 1536, 8960, 8), (3, 256, 704, 4), (64, 2048, 1536, 8),
-                                          (17, 136, 480, 100), (1, 1536, 1536, 2), (40, 331, 240, 3)])
+                                          (17, 136, 480, 100), (1, 1536, 1536, 2), (40, 331, 240, 3),
+                                          (8, 1536, 8960, 16), (13, 200, 4104, 5)])
 @pytest.mark.parametrize("mode", ["bf16", "f32", "add"])
 def test_gemm_bf16_split_over_a_cluster(k, status, T, N, K, splits, mode):
     """K split over a thread-block cluster, reduced through distributed shared memory."""
@@ -703,7 +704,8 @@ def test_gemm_bf16_swiglu(k, status, T, I, K):
 
 
 @pytest.mark.parametrize("T,N,K,splits", [(8, 2048, 1536, 8), (1, 256, 704, 4), (64, 1536, 1536, 8),
-                                          (17, 136, 480, 1), (33, 331, 240, 2), (16, 384, 200, 1)])
+                                          (17, 136, 480, 1), (33, 331, 240, 2), (16, 384, 200, 1),
+                                          (5, 256, 4608, 16)])
 @pytest.mark.parametrize("mode", ["bf16", "f32"])
 def test_gemm_bf16_makes_its_input_norm(k, status, T, N, K, splits, mode):
     """The projection of rmsnorm(resid) * w_norm with the norm made inside the kernel: the X

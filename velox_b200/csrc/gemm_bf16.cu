@@ -202,8 +202,12 @@ __device__ __forceinline__ void store_output(const GemmArgs& g, size_t index, fl
   else if (g.mode == 1)
     ((float*)g.out)[index] = value;
   else
-    ((float*)g.out)[index] += value;
+    // Nobody else adds to this element during the launch, so the sum is the same as with a load
+    // and a store; as a reduction at the L2 it needs no round trip and threads do not wait for it.
+    asm volatile("red.global.add.f32 [%0], %1;" ::"l"((float*)g.out + index), "f"(value) : "memory");
 }
+
+constexpr int GB_MAX_SPLITS = 8;  // CTAs of a cluster (a portable one; the device holds too few clusters of sixteen)
 
 template <int BN, int STAGES_>
 struct GemmShape {
@@ -219,7 +223,10 @@ struct GemmShape {
   // [splits][128 / splits rows][BN tokens] floats, then [8][BN] sums of squares of the fused
   // norm (token tiles up to 64 only).  The SwiGLU epilogue, which is never clustered, uses the
   // same place for the exchange between its gate and up rows (64 x 33 floats).
-  static constexpr uint32_t RECV_BYTES = BN <= 64 ? ((GB_BM * BN * 4 + 8 * BN * 4 + 1023) / 1024) * 1024 : 9216;
+  // A row of the receive area is four floats longer than its BN tokens, so that the rows that
+  // the 32 lanes of a warp write or read at a time fall on different banks.
+  static constexpr uint32_t RECV_ROW = BN + 4;
+  static constexpr uint32_t RECV_BYTES = BN <= 64 ? ((GB_BM * RECV_ROW * 4 + GB_MAX_SPLITS * BN * 4 + 1023) / 1024) * 1024 : 9216;
   // Fused norm: K blocks whose X tiles one batch of loads makes, and the most batches.
   static constexpr int NORM_BATCH = BN <= 16 ? 6 : (BN <= 32 ? 4 : 2);
   static constexpr int NORM_MAX_BATCHES = 32;
@@ -437,10 +444,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       const uint32_t slot_row = g.mode == 4 ? (uint32_t)((row >> 6) * pairs_per_cta + (row & 63) % pairs_per_cta)
                                             : (uint32_t)(row % rows_per_cta);
       const uint32_t recv = smem_base + S::STAGES * S::STAGE_BYTES +
-                            ((rank * (uint32_t)rows_per_cta + slot_row) * BN) * 4u;
+                            ((rank * (uint32_t)rows_per_cta + slot_row) * S::RECV_ROW) * 4u;
       if (normed && row < BN) {
         // This CTA's share of the sums of squares goes to every CTA of the cluster.
-        const uint32_t at = smem_base + S::STAGES * S::STAGE_BYTES + (uint32_t)(GB_BM * BN) * 4u +
+        const uint32_t at = smem_base + S::STAGES * S::STAGE_BYTES + (uint32_t)(GB_BM * S::RECV_ROW) * 4u +
                             (rank * (uint32_t)BN + (uint32_t)row) * 4u;
         for (uint32_t peer = 0; peer < (uint32_t)g.splits; ++peer) store_peer_shared1(at, peer, ssq_s[row]);
       }
@@ -521,7 +528,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         const int j = (int)threadIdx.x - 64;
         if (j < BN) {
           float total = 0.f;
-          for (int peer = 0; peer < g.splits; ++peer) total += recv[GB_BM * BN + peer * BN + j];
+          for (int peer = 0; peer < g.splits; ++peer) total += recv[GB_BM * S::RECV_ROW + peer * BN + j];
           ssq_s[j] = rsqrtf(total / (float)g.K + g.eps);
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -538,8 +545,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
           const int d = rank * pairs + pl;
           float lo = 0.f, hi = 0.f;
           for (int peer = 0; peer < g.splits; ++peer) {
-            lo += recv[((size_t)peer * rows_per_cta + pl) * BN + j];
-            hi += recv[((size_t)peer * rows_per_cta + pairs + pl) * BN + j];
+            lo += recv[((size_t)peer * rows_per_cta + pl) * S::RECV_ROW + j];
+            hi += recv[((size_t)peer * rows_per_cta + pairs + pl) * S::RECV_ROW + j];
           }
           if (normed) {
             lo *= ssq_s[j];
@@ -584,7 +591,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         if (t >= g.T || n >= g.N) continue;
         float acc = 0.f;
         for (int peer = 0; peer < g.splits; ++peer)
-          acc += recv[((size_t)peer * rows_per_cta + rl) * BN + j];
+          acc += recv[((size_t)peer * rows_per_cta + rl) * S::RECV_ROW + j];
         if (normed) acc *= ssq_s[j];
         store_output(g, (size_t)t * g.ldy + n, acc + (g.bias != nullptr ? g.bias[n] : 0.f));
       }
@@ -727,10 +734,10 @@ static int sm_count() {
   return count;
 }
 
-// Largest power of two <= value, at most 8 (a portable cluster).
-static int floor_pow2_8(int value) {
+// Largest power of two <= value, at most `most`.
+static int floor_pow2(int value, int most) {
   int p = 1;
-  while (p * 2 <= value && p < 8) p *= 2;
+  while (p * 2 <= value && p * 2 <= most) p *= 2;
   return p;
 }
 
@@ -770,7 +777,7 @@ static int gemm_bf16(const void* x, int x_rows, const float* resid, long long re
   const int bn = vx_gemm_bf16_token_tile(T);
   const int num_kb = (K + GB_BK - 1) / GB_BK;
   if (splits < 1 || mode == 3 || bn > 64) splits = 1;
-  splits = floor_pow2_8(splits < num_kb ? splits : num_kb);
+  splits = floor_pow2(splits < num_kb ? splits : num_kb, GB_MAX_SPLITS);
   if (splits > bn) splits = bn;
   if (mode == 4) {
     // Heads of 128 dims, rotated in the cluster exchange's final sum: split K only.
