@@ -179,20 +179,28 @@ __device__ __forceinline__ uint32_t cluster_rank() {
   return rank;
 }
 
-// Stores four floats into a peer CTA's shared memory, at the same offset as `local_addr` here.
-__device__ __forceinline__ void store_peer_shared4(uint32_t local_addr, uint32_t rank, float a,
-                                                   float b, float c, float d) {
-  uint32_t remote;
+// Stores four floats into a peer CTA's shared memory, at the same offset as `local_addr` here,
+// and counts their 16 bytes on the peer's mbarrier at the offset of `local_bar`: the peer
+// learns from its own barrier that what it waits for has arrived, without a barrier of the
+// whole cluster.
+__device__ __forceinline__ void send_peer_shared4(uint32_t local_addr, uint32_t local_bar, uint32_t rank,
+                                                  float a, float b, float c, float d) {
+  uint32_t remote, remote_bar;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};"
-               ::"r"(remote), "f"(a), "f"(b), "f"(c), "f"(d)
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_bar) : "r"(local_bar), "r"(rank));
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];"
+               ::"r"(remote), "f"(a), "f"(b), "f"(c), "f"(d), "r"(remote_bar)
                : "memory");
 }
 
-__device__ __forceinline__ void store_peer_shared1(uint32_t local_addr, uint32_t rank, float a) {
-  uint32_t remote;
+__device__ __forceinline__ void send_peer_shared1(uint32_t local_addr, uint32_t local_bar, uint32_t rank,
+                                                  float a) {
+  uint32_t remote, remote_bar;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(a) : "memory");
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_bar) : "r"(local_bar), "r"(rank));
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.f32 [%0], %1, [%2];"
+               ::"r"(remote), "f"(a), "r"(remote_bar)
+               : "memory");
 }
 
 // One element of the output in the epilogue mode of the launch (modes 0, 1, 2).
@@ -242,6 +250,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   __shared__ __align__(8) uint64_t full_bar[S::STAGES];
   __shared__ __align__(8) uint64_t empty_bar[S::STAGES];
   __shared__ __align__(8) uint64_t acc_bar;
+  __shared__ __align__(8) uint64_t recv_bar;  // split K: the peers' shares of this CTA's rows have arrived
   __shared__ uint32_t tmem_slot;
   __shared__ int epilogue_failed;
   __shared__ float ssq_s[64];  // fused norm: this CTA's sums of squares, then 1 / rms, per token
@@ -261,9 +270,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   const int num_kb = max(0, kb_end - kb_begin);
   const bool clustered = g.splits > 1;
   const bool normed = BN <= 64 && g.resid != nullptr;
-  // First cluster phase: "every CTA of the cluster runs" (nobody may write into a peer before).
-  // Arrive now; the wait comes right before the first remote store and costs nothing by then.
-  if (clustered) cluster_arrive();
 
   if (threadIdx.x == 0) {
     epilogue_failed = 0;
@@ -274,7 +280,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     if (normed)
       for (int b = 0; b < S::NORM_MAX_BATCHES; ++b) mbar_init(smem_u32(&x_bar[b]), 1);
     mbar_init(smem_u32(&acc_bar), 1);
+    mbar_init(smem_u32(&recv_bar), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // What the cluster will send here: every rank's share of this CTA's 128 / splits rows (its
+    // own included), BN floats a row, and with the fused norm every rank's sums of squares.
+    if (clustered) mbar_expect_tx(smem_u32(&recv_bar), (uint32_t)(GB_BM * BN * 4 + (normed ? g.splits * BN * 4 : 0)));
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
@@ -287,6 +297,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_acc = tmem_slot;
+  // The one barrier of the whole cluster: "every CTA runs and its receive barrier is armed"
+  // (nobody may write into a peer before).  Arrive now; the wait comes right before the first
+  // remote store and costs nothing by then.
+  if (clustered) cluster_arrive();
 
   if (warp == 0 && lane == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -449,7 +463,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         // This CTA's share of the sums of squares goes to every CTA of the cluster.
         const uint32_t at = smem_base + S::STAGES * S::STAGE_BYTES + (uint32_t)(GB_BM * S::RECV_ROW) * 4u +
                             (rank * (uint32_t)BN + (uint32_t)row) * 4u;
-        for (uint32_t peer = 0; peer < (uint32_t)g.splits; ++peer) store_peer_shared1(at, peer, ssq_s[row]);
+        for (uint32_t peer = 0; peer < (uint32_t)g.splits; ++peer)
+          send_peer_shared1(at, smem_u32(&recv_bar), peer, ssq_s[row]);
       }
       for (int c0 = 0; c0 < BN; c0 += 32) {
         float v[32];
@@ -461,7 +476,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         }
 #pragma unroll
         for (int j = 0; j < cols; j += 4)
-          store_peer_shared4(recv + (uint32_t)(c0 + j) * 4u, owner, v[j], v[j + 1], v[j + 2], v[j + 3]);
+          send_peer_shared4(recv + (uint32_t)(c0 + j) * 4u, smem_u32(&recv_bar), owner, v[j], v[j + 1], v[j + 2], v[j + 3]);
       }
     } else if (ready) {
       if (g.mode == 3) {
@@ -513,9 +528,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   __syncthreads();
   VX_TRACE_MARK(1);
   if (clustered) {
-    // Second phase: every peer's stores into this CTA's receive area are done and visible.
-    cluster_arrive();
-    cluster_wait();
+    // Every rank's stores into this CTA's receive area have arrived (and nobody writes here
+    // after that, so this CTA may end while its own stores are still on their way to peers that
+    // wait for them).
+    mbar_wait(smem_u32(&recv_bar), 0u, g.status);
     VX_TRACE_MARK(2);
     if (warp >= 2) {
       // Sum the shares of this CTA's rows in rank order and write them; consecutive threads take
