@@ -847,11 +847,16 @@ __device__ __forceinline__ uint32_t cluster_map(uint32_t local, uint32_t rank) {
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
   return remote;
 }
-__device__ __forceinline__ void st_cluster_f2(uint32_t addr, float2 v) {
-  asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(addr), "f"(v.x), "f"(v.y) : "memory");
+// Stores into a peer's shared memory that count their bytes on the peer's mbarrier `bar`.
+__device__ __forceinline__ void send_cluster_f2(uint32_t addr, float2 v, uint32_t bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v2.f32 [%0], {%1, %2}, [%3];"
+               ::"r"(addr), "f"(v.x), "f"(v.y), "r"(bar)
+               : "memory");
 }
-__device__ __forceinline__ void st_cluster_f1(uint32_t addr, float v) {
-  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+__device__ __forceinline__ void send_cluster_f1(uint32_t addr, float v, uint32_t bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.f32 [%0], %1, [%2];"
+               ::"r"(addr), "f"(v), "r"(bar)
+               : "memory");
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1269,6 +1274,7 @@ __global__ void __launch_bounds__(NARROW_THREADS) attn_narrow_kernel(const __gri
   __shared__ __align__(8) uint64_t kv_full[STAGES];
   __shared__ __align__(8) uint64_t kv_empty[STAGES];
   __shared__ __align__(8) uint64_t merge_bar;
+  __shared__ __align__(8) uint64_t recv_bar;  // cluster: the ranks' shares of this CTA's rows have arrived
   unsigned char* smem_al = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   __nv_bfloat16* kv_s = reinterpret_cast<__nv_bfloat16*>(smem_al);  // stage st: K at st*2*TILE, V after
   __nv_bfloat16* q_s = kv_s + STAGES * 2 * TILE;
@@ -1280,9 +1286,6 @@ __global__ void __launch_bounds__(NARROW_THREADS) attn_narrow_kernel(const __gri
   const int* item = a.items + (size_t)(cluster > 1 ? blockIdx.x / cluster : blockIdx.x) * 8;
   const int seq = item[0];
   if (seq < 0) return;  // padding: every CTA of the cluster leaves here
-  // First cluster phase: "every CTA of the cluster runs" (nobody may write into a peer before).
-  // Arrive now; the wait comes right before the first remote store and costs nothing by then.
-  if (cluster > 1) cluster_arrive();
   const int row_begin = item[1], row_count = item[2];
   int kv_begin = item[3], kv_end = item[4];
   const int partial_base = item[5];
@@ -1330,10 +1333,22 @@ __global__ void __launch_bounds__(NARROW_THREADS) attn_narrow_kernel(const __gri
       mbar_init(smem_u32(&kv_empty[st]), 4);  // the four warps of the group that read it
     }
     mbar_init(smem_u32(&merge_bar), 1);
+    mbar_init(smem_u32(&recv_bar), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    if (cluster > 1) {
+      // Every rank sends each row this CTA owns (rows rank, rank + cluster, ...): D floats and
+      // the log-sum-exp.
+      const int rank = (int)cluster_rank();
+      const int owned = row_count > rank ? (row_count - rank + cluster - 1) / cluster : 0;
+      mbar_expect_tx(smem_u32(&recv_bar), (uint32_t)(cluster * owned * (D * 4 + 4)));
+    }
   }
   __syncthreads();
+  // The one barrier of the whole cluster: "every CTA runs and its receive barrier is armed"
+  // (nobody may write into a peer before).  Arrive now; the wait comes right before the first
+  // remote store and costs nothing by then.
+  if (cluster > 1) cluster_arrive();
 
   if (warp == WARPS) {
     // ------------------------------------------------------------------------------ producer
@@ -1451,13 +1466,16 @@ __global__ void __launch_bounds__(NARROW_THREADS) attn_narrow_kernel(const __gri
       const uint32_t owner = (uint32_t)(r & (cluster - 1));
       const int slot = r / cluster;
       const uint32_t base = cluster_map(smem_u32(recv), owner);
+      const uint32_t bar = cluster_map(smem_u32(&recv_bar), owner);
       const uint32_t at = base + (uint32_t)((((int)rank * slots + slot) * D + 2 * seg) * 4);
 #pragma unroll
-      for (int i = 0; i < D / 16; ++i) st_cluster_f2(at + 64u * i, val[i]);
-      if (seg == 0) st_cluster_f1(base + (uint32_t)((16 * D + (int)rank * slots + slot) * 4), lse);
+      for (int i = 0; i < D / 16; ++i) send_cluster_f2(at + 64u * i, val[i], bar);
+      if (seg == 0) send_cluster_f1(base + (uint32_t)((16 * D + (int)rank * slots + slot) * 4), lse, bar);
     }
-    cluster_arrive();
-    cluster_wait();
+    // The owner learns from its own barrier that every rank's rows have arrived: no second
+    // barrier of the whole cluster, and a CTA may end while its stores are still on their way
+    // to owners that wait for them.
+    mbar_wait(smem_u32(&recv_bar), 0u, a.status);
     const int slot = threadIdx.x >> 3;
     r = slot * cluster + (int)rank;
     valid = slot < slots && r < row_count;
