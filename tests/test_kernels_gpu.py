@@ -742,6 +742,56 @@ def test_gemm_bf16_makes_its_input_norm(k, status, T, N, K, splits, mode):
     assert (out[:T].double() - two[:T].double()).abs().max().item() <= 1e-2 * scale
 
 
+@pytest.mark.parametrize("T,E,I", [(8, 1536, 8960), (16, 256, 704), (1, 128, 64), (5, 640, 1344), (13, 3584, 1024)])
+def test_mlp_fused_is_the_feed_forward(k, status, T, E, I):
+    """The gated feed-forward in one kernel: norm, gate|up, SiLU * up, down and the add into the
+    residual rows, against the formulas in float64 and against the separate projections."""
+    gen = torch.Generator().manual_seed(E + I + T)
+    rows = T + 2
+    resid_in = (torch.randn(rows, E + 4, generator=gen) * 2).cuda()[:, :E]  # a row pitch that is not E
+    resid_in[:, 3] *= 15
+    w_norm = (torch.rand(E, generator=gen) + 0.5).cuda()
+    eps = 1e-6
+    w_gu = (torch.randn(2 * I, E, generator=gen) * 2 / math.sqrt(E)).to(torch.bfloat16).cuda()
+    w_down = (torch.randn(E, I, generator=gen) / math.sqrt(I)).to(torch.bfloat16).cuda()
+    # A far column of W_down that matters: a fault in the tile coordinates of the second part shows.
+    w_down[:, I - 1] *= 8
+    before = torch.randn(rows, E, generator=gen).cuda()
+    resid_out = before.clone()
+    assert k.mlp_fused(resid_in, w_norm, eps, w_gu, w_down, resid_out, T, status)
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0
+    r64 = resid_in[:T].double()
+    normed = (r64 * torch.rsqrt((r64 * r64).mean(-1, keepdim=True) + eps) * w_norm.double()).to(torch.bfloat16).double()
+    gu = normed @ w_gu.double().T
+    act = (torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]).to(torch.bfloat16).double()
+    want = act @ w_down.double().T
+    got = (resid_out[:T] - before[:T]).double()
+    scale = max(want.abs().max().item(), 1.0)
+    assert (got.cpu() - want.cpu()).abs().max().item() <= 1e-2 * scale
+    assert torch.equal(resid_out[T:], before[T:])
+    # The separate kernels of the same step agree to the rounding of the activations.
+    act2 = torch.zeros(rows, I, dtype=torch.bfloat16, device="cuda")
+    assert k.gemm_bf16_normed(resid_in, w_norm, eps, w_gu, None, act2, k.GEMM_SWIGLU, T, status)
+    two = before.clone()
+    k.gemm_bf16(act2, w_down, None, two, k.GEMM_ADD_F32, T, status, splits=4)
+    assert (resid_out[:T].double() - two[:T].double()).abs().max().item() <= 1e-2 * scale
+
+
+def test_mlp_fused_refuses_what_it_cannot_do(k, status):
+    E, I = 256, 128
+    resid = torch.zeros(20, E, device="cuda")
+    out = torch.zeros(20, E, device="cuda")
+    w_norm = torch.ones(E, device="cuda")
+    w_gu = torch.zeros(2 * I, E, dtype=torch.bfloat16, device="cuda")
+    w_down = torch.zeros(E, I, dtype=torch.bfloat16, device="cuda")
+    assert not k.mlp_fused(resid, w_norm, 1e-6, w_gu, w_down, out, 17, status)  # too many rows
+    with pytest.raises(ValueError):
+        k.mlp_fused(resid, w_norm, 1e-6, w_gu, w_down, resid, 4, status)  # in place
+    odd = torch.zeros(2 * 96, E, dtype=torch.bfloat16, device="cuda")
+    assert not k.mlp_fused(resid, w_norm, 1e-6, odd, torch.zeros(E, 96, dtype=torch.bfloat16, device="cuda"), out, 4, status)
+
+
 @pytest.mark.parametrize("T,I,K", [(8, 8960, 1536), (40, 704, 256), (3, 200, 240)])
 def test_gemm_bf16_swiglu_makes_its_input_norm(k, status, T, I, K):
     gen = torch.Generator().manual_seed(I + T)

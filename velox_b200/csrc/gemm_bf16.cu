@@ -164,6 +164,10 @@ struct GemmArgs {
   void* v_cache;
   int heads, kv_heads, max_pos;
   long long num_slots;
+  // Mode 2 with split K only: the sums out + acc are also written to out2 [T, ld2] float32, a
+  // copy of the rows that stays as it is while a later kernel adds to `out` again.
+  float* out2;
+  long long ld2;
 };
 
 __device__ __forceinline__ void cluster_arrive() {
@@ -531,6 +535,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     // Every rank's stores into this CTA's receive area have arrived (and nobody writes here
     // after that, so this CTA may end while its own stores are still on their way to peers that
     // wait for them).
+    // With a second output the old values of this thread's elements are asked for now, so
+    // that they are here when the shares are.
+    constexpr int MIRROR_SLOTS = 8;
+    float old_out[MIRROR_SLOTS];
+    if (g.out2 != nullptr && warp >= 2) {
+      const int rows_per_cta = GB_BM / g.splits;
+      const int rank = (int)cluster_rank();
+#pragma unroll
+      for (int u = 0; u < MIRROR_SLOTS; ++u) {
+        const int e = (warp - 2) * 32 + lane + 128 * u;
+        const int j = e / rows_per_cta, rl = e - j * rows_per_cta;
+        const int t = t0 + j, n = n0 + rank * rows_per_cta + rl;
+        old_out[u] = (e < rows_per_cta * BN && t < g.T && n < g.N) ? __ldcg((const float*)g.out + (size_t)t * g.ldy + n) : 0.f;
+      }
+    }
     mbar_wait(smem_u32(&recv_bar), 0u, g.status);
     VX_TRACE_MARK(2);
     if (warp >= 2) {
@@ -599,6 +618,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
           }
           dst[0] = __float2bfloat16_rn(lo);
           dst[64] = __float2bfloat16_rn(hi);
+        }
+      } else
+      if (g.out2 != nullptr) {
+#pragma unroll
+        for (int u = 0; u < MIRROR_SLOTS; ++u) {
+          const int e = (warp - 2) * 32 + lane + 128 * u;
+          if (e >= rows_per_cta * BN) break;
+          const int j = e / rows_per_cta, rl = e - j * rows_per_cta;
+          const int t = t0 + j, n = n0 + rank * rows_per_cta + rl;
+          if (t >= g.T || n >= g.N) continue;
+          float acc = 0.f;
+          for (int peer = 0; peer < g.splits; ++peer)
+            acc += recv[((size_t)peer * rows_per_cta + rl) * S::RECV_ROW + j];
+          if (normed) acc *= ssq_s[j];
+          const float sum = old_out[u] + (acc + (g.bias != nullptr ? g.bias[n] : 0.f));
+          ((float*)g.out)[(size_t)t * g.ldy + n] = sum;
+          g.out2[(size_t)t * g.ld2 + n] = sum;
         }
       } else
       for (int e = (warp - 2) * 32 + lane; e < rows_per_cta * BN; e += 128) {
@@ -722,6 +758,260 @@ static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mw2, const CUte
   return (int)cudaLaunchKernelEx(&config, gemm_bf16_kernel<BN, STAGES_>, mw, mw2, mx, g);
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// The gated feed-forward of a small step (at most 16 tokens) in one kernel:
+//   resid_out[t, :] += W_down * (silu(W_gate x_t) * (W_up x_t)),  x_t = rmsnorm(resid_in[t, :]) * w_norm.
+// CTA j owns 64 features of the inner width: it streams their 64 gate rows and 64 up rows of
+// [2 I, E] (as the SwiGLU mode above, the input norm made on the spot), turns the accumulator
+// into the [16 tokens x 64 features] bf16 activation tile in shared memory, and goes straight
+// on, with the same ring of stages, to the 64 columns of W_down [E, I] that belong to these
+// features: E / 128 tiles of [128 rows x 64], each one product with the activation tile, each
+// with 16 columns of tensor memory of its own.  What comes out is this CTA's share of the sum
+// over the inner width; the shares meet in the float32 residual stream by reductions at the
+// L2 (red.global.add.f32), so their order, and with it the last bits of the sum, is not fixed.
+// The activations never leave the SM, the W_down tiles are already on their way while the
+// activation is computed, and a layer has one kernel boundary less.
+// resid_in must not be resid_out: other CTAs add to resid_out while this one still reads its
+// input rows.
+// ---------------------------------------------------------------------------------------------
+struct MlpArgs {
+  const float* resid_in;  // [T, resid_in_ld] float32; nobody writes it during the launch
+  const float* norm_w;    // [E]
+  float* resid_out;       // [T, resid_out_ld] float32
+  long long resid_in_ld, resid_out_ld;
+  int* status;
+  float eps;
+  int T, E, I;
+  int tmem_cols;          // 16 + 16 * E / 128, rounded up to a power of two (at least 32)
+};
+
+constexpr int MF_BN = 16;
+constexpr int MF_NORM_BATCH = 6;
+constexpr int MF_MAX_BATCHES = 32;
+constexpr uint32_t MF_X_BYTES = MF_BN * GB_BK * 2;
+
+template <int MF_STAGES>  // 16 KB each: eight, or four where the X tiles of a wide row need the room
+__global__ void __launch_bounds__(GB_THREADS, 1)
+mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_constant__ CUtensorMap map_up,
+                 const __grid_constant__ CUtensorMap map_down, MlpArgs m) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[MF_STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[MF_STAGES];
+  __shared__ __align__(8) uint64_t acc1_bar, acc2_bar, act_bar;
+  __shared__ __align__(8) uint64_t x_bar[MF_MAX_BATCHES];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int epilogue_failed;
+  __shared__ float rstd_s[MF_BN];
+  __shared__ float swap_buf[64 * 17];
+
+  VX_TRACE_SCOPE(15);
+  allow_dependents();
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
+  // stages | activation tile | X tiles of the E / 64 blocks of the first product
+  const uint32_t act_addr = smem_base + MF_STAGES * GB_A_BYTES;
+  const uint32_t x_addr = act_addr + MF_X_BYTES;
+  unsigned char* act_tile = smem_al + MF_STAGES * GB_A_BYTES;
+  unsigned char* x_tiles = act_tile + MF_X_BYTES;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * 64;    // first of this CTA's features of the inner width
+  const int kb1 = m.E / GB_BK;       // blocks of K of the first product
+  const int tiles2 = m.E / GB_BM;    // row tiles of W_down
+  const int total = kb1 + tiles2;
+
+  if (threadIdx.x == 0) {
+    epilogue_failed = 0;
+    for (int s = 0; s < MF_STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int b = 0; b < MF_MAX_BATCHES; ++b) mbar_init(smem_u32(&x_bar[b]), 1);
+    mbar_init(smem_u32(&acc1_bar), 1);
+    mbar_init(smem_u32(&acc2_bar), 1);
+    mbar_init(smem_u32(&act_bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_slot)), "r"(m.tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_acc = tmem_slot;  // columns 0..15: gate|up; 16 + 16 i ..: row tile i of W_down
+
+  if (warp == 0 && lane == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    // Weights only: nothing here depends on the kernel before this one.
+    auto load = [&](int i) {
+      const int stage = i % MF_STAGES;
+      const uint32_t full = smem_u32(&full_bar[stage]);
+      const uint32_t dst = smem_base + stage * GB_A_BYTES;
+      mbar_expect_tx(full, GB_A_BYTES);
+      if (i < kb1) {
+        tma_load_2d(dst, &map_gate, i * GB_BK, n0, full);
+        tma_load_2d(dst + GB_A_BYTES / 2, &map_up, i * GB_BK, n0, full);
+      } else {
+        tma_load_2d(dst, &map_down, n0, (i - kb1) * GB_BM, full);
+      }
+    };
+    const int first_round = min(total, MF_STAGES);
+    for (int i = 0; i < first_round; ++i) load(i);
+    for (int i = first_round; i < total; ++i) {
+      const int stage = i % MF_STAGES;
+      const uint32_t phase = (uint32_t)(i / MF_STAGES) & 1u;
+      if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, m.status)) break;
+      load(i);
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---------------------------------------------------------------- MMA issuer
+    constexpr uint32_t idesc = umma_instr_desc(MF_BN);
+    bool ok = true;
+    for (int i = 0; i < kb1 && ok; ++i) {
+      const int stage = i % MF_STAGES;
+      const uint32_t phase = (uint32_t)(i / MF_STAGES) & 1u;
+      ok = mbar_wait(smem_u32(&full_bar[stage]), phase, m.status);
+      if (ok && i % MF_NORM_BATCH == 0) ok = mbar_wait(smem_u32(&x_bar[i / MF_NORM_BATCH]), 0u, m.status);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t a_addr = smem_base + stage * GB_A_BYTES;
+      const uint32_t b_addr = x_addr + i * MF_X_BYTES;
+#pragma unroll
+      for (int k = 0; k < GB_BK / 16; ++k)
+        umma_bf16(tmem_acc, umma_smem_desc(a_addr + k * 32), umma_smem_desc(b_addr + k * 32), idesc,
+                  (i > 0 || k > 0) ? 1u : 0u);
+      umma_commit(smem_u32(&empty_bar[stage]));
+    }
+    umma_commit(smem_u32(&acc1_bar));
+    // The activation tile is the B operand of every product of the second part.
+    if (ok) ok = mbar_wait(smem_u32(&act_bar), 0u, m.status);
+    for (int t2 = 0; t2 < tiles2 && ok; ++t2) {
+      const int i = kb1 + t2;
+      const int stage = i % MF_STAGES;
+      const uint32_t phase = (uint32_t)(i / MF_STAGES) & 1u;
+      ok = mbar_wait(smem_u32(&full_bar[stage]), phase, m.status);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t a_addr = smem_base + stage * GB_A_BYTES;
+#pragma unroll
+      for (int k = 0; k < GB_BK / 16; ++k)
+        umma_bf16(tmem_acc + 16u + 16u * (uint32_t)t2, umma_smem_desc(a_addr + k * 32),
+                  umma_smem_desc(act_addr + k * 32), idesc, k > 0 ? 1u : 0u);
+      umma_commit(smem_u32(&empty_bar[stage]));
+    }
+    umma_commit(smem_u32(&acc2_bar));
+  } else if (warp >= 2) {
+    // ---------------------------------------------------------------- norm, activation, output
+    grid_dependency_wait();
+    const int q = (int)threadIdx.x - 64;
+    {
+      // X tiles: thread q takes the 16-byte chunk q % 8 of token q / 8 in every K block.
+      constexpr int NB = MF_NORM_BATCH;
+      const int c = q & 7, r = q >> 3;
+      float ssq = 0.f;
+      for (int i0 = 0; i0 < kb1; i0 += NB) {
+        float4 xa[NB], xb[NB], wa[NB], wb[NB];
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+          const int k = (i0 + j) * GB_BK + c * 8;
+          const bool in_k = i0 + j < kb1;
+          wa[j] = in_k ? __ldg(reinterpret_cast<const float4*>(m.norm_w + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
+          wb[j] = in_k ? __ldg(reinterpret_cast<const float4*>(m.norm_w + k + 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+          const bool on = in_k && r < m.T;
+          const float* src = m.resid_in + (size_t)r * m.resid_in_ld + k;
+          xa[j] = on ? *reinterpret_cast<const float4*>(src) : make_float4(0.f, 0.f, 0.f, 0.f);
+          xb[j] = on ? *reinterpret_cast<const float4*>(src + 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+          if (i0 + j >= kb1) break;
+          const float4 a4 = xa[j], b4 = xb[j];
+          ssq += a4.x * a4.x + a4.y * a4.y + a4.z * a4.z + a4.w * a4.w +
+                 b4.x * b4.x + b4.y * b4.y + b4.z * b4.z + b4.w * b4.w;
+          __nv_bfloat162 p0 = __floats2bfloat162_rn(a4.x * wa[j].x, a4.y * wa[j].y);
+          __nv_bfloat162 p1 = __floats2bfloat162_rn(a4.z * wa[j].z, a4.w * wa[j].w);
+          __nv_bfloat162 p2 = __floats2bfloat162_rn(b4.x * wb[j].x, b4.y * wb[j].y);
+          __nv_bfloat162 p3 = __floats2bfloat162_rn(b4.z * wb[j].z, b4.w * wb[j].w);
+          *reinterpret_cast<uint4*>(x_tiles + (size_t)(i0 + j) * MF_X_BYTES + r * 128 + ((c ^ (r & 7)) << 4)) =
+              make_uint4(*reinterpret_cast<uint32_t*>(&p0), *reinterpret_cast<uint32_t*>(&p1),
+                         *reinterpret_cast<uint32_t*>(&p2), *reinterpret_cast<uint32_t*>(&p3));
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (q == 0) mbar_arrive(smem_u32(&x_bar[i0 / NB]));
+      }
+      // The eight threads of a token sit in consecutive lanes.
+      ssq += __shfl_xor_sync(0xffffffffu, ssq, 1);
+      ssq += __shfl_xor_sync(0xffffffffu, ssq, 2);
+      ssq += __shfl_xor_sync(0xffffffffu, ssq, 4);
+      if (c == 0) rstd_s[r] = rsqrtf(ssq / (float)m.E + m.eps);
+    }
+    const int quarter = warp & 3;  // TMEM lanes 32 * quarter .. + 31 belong to this warp
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_base = tmem_acc + ((uint32_t)(quarter * 32) << 16);
+    if (!mbar_wait(smem_u32(&acc1_bar), 0u, m.status)) epilogue_failed = 1;
+    asm volatile("bar.sync 1, 128;" ::: "memory");  // also: rstd_s is written
+    bool ready = epilogue_failed == 0;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    float v[32];
+    if (ready) {
+      tmem_load_16(lane_base, v);
+    } else {
+#pragma unroll
+      for (int j = 0; j < MF_BN; ++j) v[j] = 0.f;
+    }
+    // Rows 0..63 are gate, 64..127 up of the same 64 features: up rows hand their values over.
+    if (row >= 64) {
+#pragma unroll
+      for (int j = 0; j < MF_BN; ++j) swap_buf[(row - 64) * 17 + j] = v[j];
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (row < 64) {
+      // Activation tile [16 tokens x 64 features] bf16, K-major, 128-byte swizzled: feature f
+      // of token t in chunk (f / 8) ^ (t & 7) of row t.
+#pragma unroll
+      for (int j = 0; j < MF_BN; ++j) {
+        const float scale = rstd_s[j];
+        const float gate = v[j] * scale, up = swap_buf[row * 17 + j] * scale;
+        const float a = j < m.T ? gate / (1.0f + __expf(-gate)) * up : 0.f;
+        *reinterpret_cast<__nv_bfloat16*>(act_tile + j * 128 + ((((row >> 3) ^ (j & 7))) << 4) + (row & 7) * 2) =
+            __float2bfloat16_rn(a);
+      }
+    }
+    // The tensor core reads the tile through the async proxy.
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (q == 0) mbar_arrive(smem_u32(&act_bar));
+
+    if (!mbar_wait(smem_u32(&acc2_bar), 0u, m.status)) epilogue_failed = 1;
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    ready = epilogue_failed == 0;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ready) {
+      for (int t2 = 0; t2 < tiles2; ++t2) {
+        tmem_load_16(lane_base + 16u + 16u * (uint32_t)t2, v);
+        float* dst = m.resid_out + (size_t)t2 * GB_BM + row;
+#pragma unroll
+        for (int j = 0; j < MF_BN; ++j)
+          if (j < m.T)
+            asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst + (size_t)j * m.resid_out_ld), "f"(v[j]) : "memory");
+      }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  }
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(m.tmem_cols)
+                 : "memory");
+  }
+}
+
 }  // namespace vx
 
 using namespace vx;
@@ -780,7 +1070,8 @@ struct RopeArgs {
 static int gemm_bf16(const void* x, int x_rows, const float* resid, long long resid_ld,
                      const float* norm_w, float eps, const void* w, const float* bias, void* out,
                      int mode, int T, int N, int K, long long ldy, int splits, int* status,
-                     cudaStream_t stream, const RopeArgs* rope = nullptr) {
+                     cudaStream_t stream, const RopeArgs* rope = nullptr, float* out2 = nullptr,
+                     long long ld2 = 0) {
   if (T <= 0 || N <= 0) return 0;
   if (K <= 0 || (K % 8) != 0) return -1;
   const bool normed = resid != nullptr;
@@ -822,6 +1113,10 @@ static int gemm_bf16(const void* x, int x_rows, const float* resid, long long re
   g.k_cache = g.v_cache = nullptr;
   g.heads = g.kv_heads = g.max_pos = 0;
   g.num_slots = 0;
+  g.out2 = out2;
+  g.ld2 = ld2;
+  // The second output: mode 2, split K, at most eight elements per thread of the final sum.
+  if (out2 != nullptr && (mode != 2 || splits < 2 || (GB_BM / splits) * bn > 8 * 128)) return -4;
   if (rope != nullptr) {
     g.positions = rope->positions;
     g.cos_t = rope->cos_t;
@@ -879,6 +1174,17 @@ VX_API int vx_gemm_bf16(const void* x, const void* w, const float* bias, void* o
                    status, stream);
 }
 
+// Mode 2 (out += x w^T, float32) that also writes the sums to out2 [T, ld2]: a copy of the rows
+// for a later kernel that reads them while others already add to `out` again.  -4 (nothing
+// launched) where the launch would not split K or a thread would own more than eight sums.
+VX_API int vx_gemm_bf16_add_mirrored(const void* x, const void* w, float* out, float* out2, int T,
+                                     int x_rows, int N, int K, long long ldy, long long ld2, int splits,
+                                     int* status, cudaStream_t stream) {
+  if (out2 == nullptr) return -1;
+  return gemm_bf16(x, x_rows, nullptr, 0, nullptr, 0.f, w, nullptr, out, 2, T, N, K, ldy, splits, status,
+                   stream, nullptr, out2, ld2);
+}
+
 // The same product on rmsnorm(resid) * norm_w: resid [T, resid_ld] float32, norm_w [K] float32.
 VX_API int vx_gemm_bf16_normed(const float* resid, long long resid_ld, const float* norm_w,
                                float eps, const void* w, const float* bias, void* out, int mode,
@@ -906,4 +1212,89 @@ VX_API int vx_gemm_bf16_qkv_rope(const void* x, int x_rows, const float* resid, 
   RopeArgs rope = {positions, cos_t, sin_t, slots, k_cache, v_cache, heads, kv_heads, max_pos, num_slots};
   return gemm_bf16(x, x_rows, resid, resid_ld, norm_w, eps, w, bias, out, 4, T,
                    (heads + 2 * kv_heads) * 128, K, ldy, splits, status, stream, &rope);
+}
+
+// The most dynamic shared memory a CTA of the fused feed-forward may have (set once), or
+// minus a cudaError_t.
+template <int STAGES>
+static int mlp_fused_limit() {
+  static int limit = 0;
+  if (limit == 0) {
+    cudaFuncAttributes attributes_of;
+    cudaError_t e = cudaFuncGetAttributes(&attributes_of, mlp_fused_kernel<STAGES>);
+    if (e != cudaSuccess) return -(int)e;
+    const int value = 227 * 1024 - (int)attributes_of.sharedSizeBytes;
+    e = cudaFuncSetAttribute(mlp_fused_kernel<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, value);
+    if (e != cudaSuccess) return -(int)e;
+    limit = value;
+  }
+  return limit;
+}
+
+// The gated feed-forward of at most 16 tokens in one kernel (see mlp_fused_kernel):
+// resid_out += W_down (silu(W_gate x) * (W_up x)), x = rmsnorm(resid_in) * norm_w, with
+// w_gate_up [2 I, E] (gate rows, then up rows) and w_down [E, I] bf16.  Returns 0 on launch, a
+// cudaError_t on failure, -1 if the arguments are refused (more than 16 tokens, E no multiple
+// of 128, I no multiple of 64, unaligned pointers, resid_in == resid_out), -2 if a row this wide
+// does not fit in shared or tensor memory (the caller then uses the separate projections).
+VX_API int vx_mlp_fused(const float* resid_in, long long resid_in_ld, const float* norm_w, float eps,
+                        const void* w_gate_up, const void* w_down, float* resid_out,
+                        long long resid_out_ld, int T, int E, int I, int* status, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (T > MF_BN || E <= 0 || I <= 0 || (E % GB_BM) != 0 || (I % 64) != 0) return -1;
+  if (resid_in == nullptr || resid_out == nullptr || norm_w == nullptr || (const float*)resid_out == resid_in) return -1;
+  if ((reinterpret_cast<uintptr_t>(resid_in) & 15) || (reinterpret_cast<uintptr_t>(norm_w) & 15) ||
+      (reinterpret_cast<uintptr_t>(w_gate_up) & 15) || (reinterpret_cast<uintptr_t>(w_down) & 15) ||
+      (resid_in_ld % 4) != 0)
+    return -1;
+  const int kb1 = E / GB_BK, tiles2 = E / GB_BM;
+  if ((kb1 + MF_NORM_BATCH - 1) / MF_NORM_BATCH > MF_MAX_BATCHES) return -2;
+  int cols = 32;
+  while (cols < 16 + 16 * tiles2) cols *= 2;
+  if (cols > 512) return -2;
+  const size_t tiles_bytes = MF_X_BYTES + (size_t)kb1 * MF_X_BYTES + 1024;
+  int stages = 0;
+  for (int want : {8, 4}) {
+    const int limit = want == 8 ? mlp_fused_limit<8>() : mlp_fused_limit<4>();
+    if (limit < 0) return -limit;
+    if ((size_t)want * GB_A_BYTES + tiles_bytes <= (size_t)limit) {
+      stages = want;
+      break;
+    }
+  }
+  if (stages == 0) return -2;
+  const size_t smem = (size_t)stages * GB_A_BYTES + tiles_bytes;
+  CUtensorMap mg, mu, md;
+  if (!tensor_map_2d(&mg, w_gate_up, I, E, 64)) return -1;
+  if (!tensor_map_2d(&mu, (const __nv_bfloat16*)w_gate_up + (size_t)I * E, I, E, 64)) return -1;
+  if (!tensor_map_2d(&md, w_down, E, I, GB_BM)) return -1;
+  MlpArgs m;
+  m.resid_in = resid_in;
+  m.norm_w = norm_w;
+  m.resid_out = resid_out;
+  m.resid_in_ld = resid_in_ld;
+  m.resid_out_ld = resid_out_ld;
+  m.status = status;
+  m.eps = eps;
+  m.T = T;
+  m.E = E;
+  m.I = I;
+  m.tmem_cols = cols;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(I / 64);
+  config.blockDim = dim3(GB_THREADS);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attributes[1];
+  int count = 0;
+  const char* serialised = getenv("VELOX_B200_NO_PDL");
+  if (serialised == nullptr || serialised[0] != '1') {
+    attributes[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[count].val.programmaticStreamSerializationAllowed = 1;
+    ++count;
+  }
+  config.attrs = attributes;
+  config.numAttrs = count;
+  if (stages == 8) return (int)cudaLaunchKernelEx(&config, mlp_fused_kernel<8>, mg, mu, md, m);
+  return (int)cudaLaunchKernelEx(&config, mlp_fused_kernel<4>, mg, mu, md, m);
 }

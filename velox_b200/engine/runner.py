@@ -101,6 +101,11 @@ class StepContext:
     plans: Dict[Tuple[Optional[int], Tuple], DevicePlan]
     # The float32 residual stream while a block runs its parts (they may add into it), else None.
     residual: Optional[torch.Tensor] = None
+    # A float32 buffer the block offers the mixer for a copy of the residual rows as they are
+    # after the mixer's product (a feed-forward that adds into the stream from many CTAs reads its
+    # input there), and whether the mixer has written it.
+    residual_mirror: Optional[torch.Tensor] = None
+    residual_mirror_written: bool = False
     # Host copies, for parts that lay out work of their own.
     q_lens_host: List[int] = field(default_factory=list)
     kv_lens_host: List[int] = field(default_factory=list)

@@ -56,6 +56,12 @@ def core():
             _ptr, _c_int, _c_int, _c_ll, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_ll, _ptr, _ptr, _ptr, _ptr, _ptr,
         ]
         lib.vx_sample_segments.argtypes = [_c_int, _c_int]
+        lib.vx_gemm_bf16_add_mirrored.argtypes = [
+            _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_int, _ptr, _ptr,
+        ]
+        lib.vx_mlp_fused.argtypes = [
+            _ptr, _c_ll, _ptr, _c_f, _ptr, _ptr, _ptr, _c_ll, _c_int, _c_int, _c_int, _ptr, _ptr,
+        ]
         lib.vx_filter_threshold.argtypes = [
             _ptr, _c_int, _c_int, _c_ll, _ptr, _ptr, _ptr, _ptr, _ptr,
         ]
@@ -367,6 +373,82 @@ def gemm_bf16_normed(
             "be a multiple of 8, the row pitch of resid a multiple of 4 and the operands 16-byte aligned"
         )
     _check(code, "gemm_bf16_normed")
+    return True
+
+
+def gemm_bf16_add_mirrored(
+    x: torch.Tensor,
+    w: torch.Tensor,
+    out: torch.Tensor,
+    mirror: torch.Tensor,
+    num_rows: int,
+    status: torch.Tensor,
+    splits: int,
+) -> bool:
+    """out[:num_rows] += x[:num_rows] @ w.T (float32) with the sums also written to ``mirror``:
+    a copy of the rows that stays as it is while a later kernel adds to ``out`` again.  False
+    (nothing launched) where the launch would not be split along K."""
+    _need(x, torch.bfloat16, "x")
+    _need(w, torch.bfloat16, "w")
+    _need(out, torch.float32, "out")
+    if mirror.dtype != torch.float32 or mirror.dim() != 2 or mirror.stride(1) != 1 or mirror.shape[1] != out.shape[1]:
+        raise TypeError("mirror must be float32 rows of the width of out")
+    n, k = w.shape
+    if x.shape[1] != k or out.shape[1] != n:
+        raise ValueError(f"gemm shapes do not agree: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    code = core().vx_gemm_bf16_add_mirrored(_p(x), _p(w), _p(out), _p(mirror), num_rows, x.shape[0], n, k,
+                                            out.stride(0), mirror.stride(0), splits, _p(status), _stream())
+    if code in (-1, -4):
+        return False
+    _check(code, "gemm_bf16_add_mirrored")
+    return True
+
+
+# Steps of at most this many tokens can run the gated feed-forward as one kernel.
+MLP_FUSED_MAX_TOKENS = 16
+
+
+def mlp_fused(
+    resid_in: torch.Tensor,
+    norm_weight: torch.Tensor,
+    eps: float,
+    w_gate_up: torch.Tensor,
+    w_down: torch.Tensor,
+    resid_out: torch.Tensor,
+    num_rows: int,
+    status: torch.Tensor,
+) -> bool:
+    """resid_out[:num_rows] += w_down @ (silu(gate) * up) of rmsnorm(resid_in[:num_rows]) *
+    norm_weight, in one kernel (see ``mlp_fused_kernel`` in gemm_bf16.cu): the norm is made on
+    the spot, the activations stay on the SM, and the CTAs' shares of the sum over the inner
+    width meet in ``resid_out`` by float32 reductions at the L2, whose order is not fixed.
+    ``resid_in`` and ``resid_out`` are float32 rows and must not overlap (other CTAs add to
+    the output while a CTA still reads its input).  False (nothing launched) when the sizes
+    do not fit: more than ``MLP_FUSED_MAX_TOKENS`` rows, a width that is no multiple of 128 or
+    too long for shared or tensor memory, an inner width that is no multiple of 64."""
+    for name, t in (("resid_in", resid_in), ("resid_out", resid_out)):
+        if t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1 or not t.is_cuda:
+            raise TypeError(f"{name} must be float32 rows on the device")
+    _need(norm_weight, torch.float32, "norm_weight")
+    _need(w_gate_up, torch.bfloat16, "w_gate_up")
+    _need(w_down, torch.bfloat16, "w_down")
+    width = resid_in.shape[1]
+    inner = w_down.shape[1]
+    if w_gate_up.shape != (2 * inner, width) or w_down.shape[0] != width or resid_out.shape[1] != width:
+        raise ValueError(
+            f"mlp_fused shapes do not agree: rows of {width}, gate|up {tuple(w_gate_up.shape)}, down {tuple(w_down.shape)}")
+    if norm_weight.numel() != width:
+        raise ValueError("mlp_fused: the norm weight has another width than the rows")
+    if num_rows > MLP_FUSED_MAX_TOKENS or width % 128 or inner % 64 or resid_in.stride(0) % 4:
+        return False
+    if resid_in.data_ptr() == resid_out.data_ptr():
+        raise ValueError("mlp_fused: resid_in and resid_out must be different buffers")
+    code = core().vx_mlp_fused(_p(resid_in), resid_in.stride(0), _p(norm_weight), float(eps), _p(w_gate_up),
+                               _p(w_down), _p(resid_out), resid_out.stride(0), num_rows, width, inner,
+                               _p(status), _stream())
+    if code in (-1, -2):
+        return False
+    _check(code, "mlp_fused")
     return True
 
 

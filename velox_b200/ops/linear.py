@@ -73,11 +73,13 @@ def linear(
     bias_lowp: Optional[torch.Tensor] = None,
     status: Optional[torch.Tensor] = None,
     accumulate: bool = False,
+    mirror: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """out[:num_rows] = x[:num_rows] @ weight.T (+ bias), in the dtype of ``out``.
 
     ``accumulate`` (tensor-core kernel only, float32 ``out``): add to ``out`` instead, which is
-    how a projection goes straight into the float32 residual stream.
+    how a projection goes straight into the float32 residual stream.  With ``mirror`` (float32
+    rows) the sums are written there as well, by the same kernel where it can.
 
     ``x`` may be a ``parts.base.PendingNorm``: with few tokens the norm is then made inside the
     projection, otherwise it runs first.
@@ -99,6 +101,12 @@ def linear(
     if weight.dtype != torch.bfloat16:
         raise TypeError(f"linear: weights must be float32 or bfloat16, got {weight.dtype}")
     if status is not None and use_tensor_core_kernel(x, weight, num_rows):
+        if accumulate and mirror is not None and bias_f32 is None:
+            splits = choose_splits(weight.shape[0], weight.shape[1])
+            if not kernels.gemm_bf16_add_mirrored(x, weight, out, mirror, num_rows, status, splits):
+                kernels.gemm_bf16(x, weight, None, out, kernels.GEMM_ADD_F32, num_rows, status, splits=splits)
+                mirror[:num_rows].copy_(out[:num_rows])
+            return out
         if accumulate:
             mode = kernels.GEMM_ADD_F32
         else:

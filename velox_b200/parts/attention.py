@@ -103,7 +103,10 @@ class Attention(Mixer):
 
         if ctx.residual is not None and use_tensor_core_kernel(attn, self.w_out, T):
             # Few tokens: the projection is added straight into the float32 residual stream.
-            linear(attn, self.w_out, None, ctx.residual, T, status=ctx.status, accumulate=True)
+            mirror = getattr(ctx, "residual_mirror", None)
+            linear(attn, self.w_out, None, ctx.residual, T, status=ctx.status, accumulate=True, mirror=mirror)
+            if mirror is not None:
+                ctx.residual_mirror_written = True
             return None
         out = ws.get("mixer.out", (ws.max_tokens, self.hidden_size), self.dtype)
         linear(attn, self.w_out, None, out, T, status=ctx.status)

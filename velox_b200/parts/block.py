@@ -8,6 +8,8 @@ from __future__ import annotations
 
 import os
 
+import torch
+
 from .base import HiddenState
 from .registry import register_part
 
@@ -29,11 +31,22 @@ class PreNormBlock:
         normed = ws.get("block.normed", (ws.max_tokens, hidden.resid.shape[1]), self.mixer.dtype)
         # A part may add its product into the residual stream itself and return None.
         ctx.residual = hidden.resid
+        # A feed-forward that adds into the stream while it still reads its input asks for a
+        # copy of the rows; a mixer that adds its product itself can write it on the way.
+        ctx.residual_mirror = None
+        ctx.residual_mirror_written = False
+        wants = getattr(self.feed_forward, "wants_residual_mirror", None)
+        if wants is not None and wants(T, ctx):
+            ctx.residual_mirror = ws.get("block.residual_mirror", (ws.max_tokens, hidden.resid.shape[1]), torch.float32)
         mixed = self.mixer.forward(self._normed(self.norm_mixer, self.mixer, hidden.resid, hidden.delta, normed, T),
                                    ctx, cache)
+        source = hidden.resid
+        if mixed is None and ctx.residual_mirror is not None and ctx.residual_mirror_written:
+            source = ctx.residual_mirror
         hidden.delta = self.feed_forward.forward(
-            self._normed(self.norm_feed_forward, self.feed_forward, hidden.resid, mixed, normed, T), ctx)
+            self._normed(self.norm_feed_forward, self.feed_forward, source, mixed, normed, T), ctx)
         ctx.residual = None
+        ctx.residual_mirror = None
 
     @staticmethod
     def _normed(norm, consumer, resid, delta, out, num_rows):

@@ -4,10 +4,19 @@ with gate and up fused into one matrix whose first half is gate, and no biases
 rounds to the model dtype between the two)."""
 from __future__ import annotations
 
+import os
+
+import torch
+
 from ..ops import kernels
 from ..ops.linear import linear, swiglu_linear, use_tensor_core_kernel
 from .base import FeedForward
 from .registry import register_part
+
+
+# VELOX_B200_NO_MLP_FUSION=1 keeps the two projections of a small step as kernels of their own
+# (for bisecting; the fused kernel's sum over the inner width has no fixed order).
+_FUSE_MLP = os.environ.get("VELOX_B200_NO_MLP_FUSION") != "1"
 
 
 @register_part("feed_forward", "swiglu")
@@ -22,9 +31,22 @@ class SwiGLU(FeedForward):
     # The input is used by the gate|up projection only, which can make the norm itself.
     accepts_pending_norm = True
 
+    def _fusable(self, T, ctx) -> bool:
+        return (_FUSE_MLP and 0 < T <= kernels.MLP_FUSED_MAX_TOKENS and self.dtype == torch.bfloat16
+                and ctx.status is not None and self.hidden_size % 128 == 0 and self.intermediate_size % 64 == 0)
+
+    def wants_residual_mirror(self, T, ctx) -> bool:
+        """With few tokens the whole feed-forward is one kernel whose CTAs add their shares into
+        the residual stream while others still read their input rows: it reads a copy."""
+        return self._fusable(T, ctx)
+
     def forward(self, x, ctx):
         T = ctx.num_tokens
         ws = ctx.workspace
+        if (self._fusable(T, ctx) and ctx.residual is not None and getattr(x, "resid", None) is not None
+                and x.resid.data_ptr() != ctx.residual.data_ptr() and x.resid.dtype == torch.float32):
+            if kernels.mlp_fused(x.resid, x.weight, x.eps, self.w_gate_up, self.w_down, ctx.residual, T, ctx.status):
+                return None
         act = ws.get("swiglu.act", (ws.max_tokens, self.intermediate_size), self.dtype)
         if use_tensor_core_kernel(x, self.w_gate_up, T) and use_tensor_core_kernel(act, self.w_down, T):
             # Few tokens: SiLU(gate) * up in the projection's epilogue, then the down projection
