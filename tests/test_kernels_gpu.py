@@ -778,6 +778,30 @@ def test_mlp_fused_is_the_feed_forward(k, status, T, E, I):
     assert (resid_out[:T].double() - two[:T].double()).abs().max().item() <= 1e-2 * scale
 
 
+@pytest.mark.parametrize("T,N,K,splits", [(8, 1536, 1536, 8), (16, 256, 704, 4), (3, 136, 480, 2), (40, 384, 512, 8)])
+def test_gemm_bf16_add_mirrored(k, status, T, N, K, splits):
+    """out += x w^T with the sums written to a second buffer as well."""
+    gen = torch.Generator().manual_seed(N + K)
+    rows = T + 1
+    x = torch.randn(rows, K, generator=gen).to(torch.bfloat16).cuda()
+    w = (torch.randn(N, K, generator=gen) / math.sqrt(K)).to(torch.bfloat16).cuda()
+    before = torch.randn(rows, N, generator=gen).cuda()
+    out = before.clone()
+    mirror = torch.full((rows, N + 4), 7.0, device="cuda")[:, :N]  # a row pitch of its own
+    assert k.gemm_bf16_add_mirrored(x, w, out, mirror, T, status, splits)
+    want = before[:T].double() + x[:T].double() @ w.double().T
+    assert (out[:T].double() - want).abs().max().item() <= 2e-5 * max(want.abs().max().item(), 1.0)
+    assert torch.equal(mirror[:T], out[:T])
+    assert torch.equal(out[T:], before[T:]) and torch.all(mirror[T:] == 7.0)
+    # the plain accumulate gives the same sums
+    plain = before.clone()
+    k.gemm_bf16(x, w, None, plain, k.GEMM_ADD_F32, T, status, splits=splits)
+    assert torch.equal(plain[:T], out[:T])
+    assert int(status[0]) == 0
+    # no split along K: refused, nothing written
+    assert not k.gemm_bf16_add_mirrored(x, w, out, mirror, T, status, 1)
+
+
 def test_mlp_fused_refuses_what_it_cannot_do(k, status):
     E, I = 256, 128
     resid = torch.zeros(20, E, device="cuda")
