@@ -789,16 +789,18 @@ struct MlpArgs {
 constexpr int MF_BN = 16;
 constexpr int MF_NORM_BATCH = 6;
 constexpr int MF_MAX_BATCHES = 32;
+constexpr int MF_MAX_TILES = 31;  // row tiles of W_down: 16 columns of tensor memory each, after the first 16
 constexpr uint32_t MF_X_BYTES = MF_BN * GB_BK * 2;
 
-template <int MF_STAGES>  // 16 KB each: eight, or four where the X tiles of a wide row need the room
+template <int MF_STAGES>  // 16 KB each: as many of ten, eight and four as fit beside the X tiles of the row
 __global__ void __launch_bounds__(GB_THREADS, 1)
 mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_constant__ CUtensorMap map_up,
                  const __grid_constant__ CUtensorMap map_down, MlpArgs m) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[MF_STAGES];
   __shared__ __align__(8) uint64_t empty_bar[MF_STAGES];
-  __shared__ __align__(8) uint64_t acc1_bar, acc2_bar, act_bar;
+  __shared__ __align__(8) uint64_t acc1_bar, act_bar;
+  __shared__ __align__(8) uint64_t tile_bar[MF_MAX_TILES];  // row tile i of the second part is in tensor memory
   __shared__ __align__(8) uint64_t x_bar[MF_MAX_BATCHES];
   __shared__ uint32_t tmem_slot;
   __shared__ int epilogue_failed;
@@ -828,7 +830,7 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
     }
     for (int b = 0; b < MF_MAX_BATCHES; ++b) mbar_init(smem_u32(&x_bar[b]), 1);
     mbar_init(smem_u32(&acc1_bar), 1);
-    mbar_init(smem_u32(&acc2_bar), 1);
+    for (int i = 0; i < MF_MAX_TILES; ++i) mbar_init(smem_u32(&tile_bar[i]), 1);
     mbar_init(smem_u32(&act_bar), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -902,8 +904,8 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
         umma_bf16(tmem_acc + 16u + 16u * (uint32_t)t2, umma_smem_desc(a_addr + k * 32),
                   umma_smem_desc(act_addr + k * 32), idesc, k > 0 ? 1u : 0u);
       umma_commit(smem_u32(&empty_bar[stage]));
+      umma_commit(smem_u32(&tile_bar[t2]));
     }
-    umma_commit(smem_u32(&acc2_bar));
   } else if (warp >= 2) {
     // ---------------------------------------------------------------- norm, activation, output
     grid_dependency_wait();
@@ -988,12 +990,11 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
     asm volatile("bar.sync 1, 128;" ::: "memory");
     if (q == 0) mbar_arrive(smem_u32(&act_bar));
 
-    if (!mbar_wait(smem_u32(&acc2_bar), 0u, m.status)) epilogue_failed = 1;
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    ready = epilogue_failed == 0;
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    // Row tiles are written out as they finish, the last ones while their weights still arrive.
     if (ready) {
       for (int t2 = 0; t2 < tiles2; ++t2) {
+        if (!mbar_wait(smem_u32(&tile_bar[t2]), 0u, m.status)) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         tmem_load_16(lane_base + 16u + 16u * (uint32_t)t2, v);
         float* dst = m.resid_out + (size_t)t2 * GB_BM + row;
 #pragma unroll
@@ -1254,8 +1255,8 @@ VX_API int vx_mlp_fused(const float* resid_in, long long resid_in_ld, const floa
   if (cols > 512) return -2;
   const size_t tiles_bytes = MF_X_BYTES + (size_t)kb1 * MF_X_BYTES + 1024;
   int stages = 0;
-  for (int want : {8, 4}) {
-    const int limit = want == 8 ? mlp_fused_limit<8>() : mlp_fused_limit<4>();
+  for (int want : {10, 8, 4}) {
+    const int limit = want == 10 ? mlp_fused_limit<10>() : (want == 8 ? mlp_fused_limit<8>() : mlp_fused_limit<4>());
     if (limit < 0) return -limit;
     if ((size_t)want * GB_A_BYTES + tiles_bytes <= (size_t)limit) {
       stages = want;
@@ -1295,6 +1296,7 @@ VX_API int vx_mlp_fused(const float* resid_in, long long resid_in_ld, const floa
   }
   config.attrs = attributes;
   config.numAttrs = count;
+  if (stages == 10) return (int)cudaLaunchKernelEx(&config, mlp_fused_kernel<10>, mg, mu, md, m);
   if (stages == 8) return (int)cudaLaunchKernelEx(&config, mlp_fused_kernel<8>, mg, mu, md, m);
   return (int)cudaLaunchKernelEx(&config, mlp_fused_kernel<4>, mg, mu, md, m);
 }
