@@ -1480,29 +1480,70 @@ __global__ void __launch_bounds__(NARROW_THREADS) attn_narrow_kernel(const __gri
     r = slot * cluster + (int)rank;
     valid = slot < slots && r < row_count;
     if (valid) {
-      float mt = -CUDART_INF_F;
-      for (int j = 0; j < cluster; ++j) mt = fmaxf(mt, recv_lse[j * slots + slot]);
-      const float m_safe = mt == -CUDART_INF_F ? 0.f : mt;
-      float den = 0.f;
-      for (int j = 0; j < cluster; ++j) {
-        const float lj = recv_lse[j * slots + slot];
-        den += lj == -CUDART_INF_F ? 0.f : exp2f(lj - m_safe);
-      }
-      const float inv = den > 0.f ? 1.0f / den : 0.f;
+      if constexpr (D <= 128) {
+        // All loads are asked for at once (a loop over the ranks with its loads and exponentials
+        // one after the other took 1.2 us here): eight slots, those past the cluster's size empty.
+        constexpr int MAX_CLUSTER = 8;
+        float lj[MAX_CLUSTER], w[MAX_CLUSTER];
 #pragma unroll
-      for (int i = 0; i < D / 16; ++i) val[i] = make_float2(0.f, 0.f);
-      for (int j = 0; j < cluster; ++j) {
-        const float lj = recv_lse[j * slots + slot];
-        const float w = lj == -CUDART_INF_F ? 0.f : exp2f(lj - m_safe) * inv;
-        const float* src = recv + (size_t)(j * slots + slot) * D + 2 * seg;
+        for (int j = 0; j < MAX_CLUSTER; ++j) lj[j] = j < cluster ? recv_lse[j * slots + slot] : -CUDART_INF_F;
+        float2 part[MAX_CLUSTER][D / 16];
 #pragma unroll
-        for (int i = 0; i < D / 16; ++i) {
-          const float2 v = *reinterpret_cast<const float2*>(src + 16 * i);
-          val[i].x += w * v.x;
-          val[i].y += w * v.y;
+        for (int j = 0; j < MAX_CLUSTER; ++j) {
+          const float* src = recv + (size_t)(j * slots + slot) * D + 2 * seg;
+#pragma unroll
+          for (int i = 0; i < D / 16; ++i)
+            part[j][i] = j < cluster ? *reinterpret_cast<const float2*>(src + 16 * i) : make_float2(0.f, 0.f);
         }
+        float mt = -CUDART_INF_F;
+#pragma unroll
+        for (int j = 0; j < MAX_CLUSTER; ++j) mt = fmaxf(mt, lj[j]);
+        const float m_safe = mt == -CUDART_INF_F ? 0.f : mt;
+        float den = 0.f;
+#pragma unroll
+        for (int j = 0; j < MAX_CLUSTER; ++j) {
+          w[j] = lj[j] == -CUDART_INF_F ? 0.f : exp2f(lj[j] - m_safe);
+          den += w[j];
+        }
+        const float inv = den > 0.f ? 1.0f / den : 0.f;
+#pragma unroll
+        for (int i = 0; i < D / 16; ++i) val[i] = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < MAX_CLUSTER; ++j) {
+          const float wj = w[j] * inv;
+#pragma unroll
+          for (int i = 0; i < D / 16; ++i) {
+            val[i].x += wj * part[j][i].x;
+            val[i].y += wj * part[j][i].y;
+          }
+        }
+        lse = den > 0.f ? mt + log2f(den) : -CUDART_INF_F;
+      } else {
+        // Heads too wide to hold every rank's share in registers: rank after rank.
+        float mt = -CUDART_INF_F;
+        for (int j = 0; j < cluster; ++j) mt = fmaxf(mt, recv_lse[j * slots + slot]);
+        const float m_safe = mt == -CUDART_INF_F ? 0.f : mt;
+        float den = 0.f;
+        for (int j = 0; j < cluster; ++j) {
+          const float lj = recv_lse[j * slots + slot];
+          den += lj == -CUDART_INF_F ? 0.f : exp2f(lj - m_safe);
+        }
+        const float inv = den > 0.f ? 1.0f / den : 0.f;
+#pragma unroll
+        for (int i = 0; i < D / 16; ++i) val[i] = make_float2(0.f, 0.f);
+        for (int j = 0; j < cluster; ++j) {
+          const float lj = recv_lse[j * slots + slot];
+          const float w = lj == -CUDART_INF_F ? 0.f : exp2f(lj - m_safe) * inv;
+          const float* src = recv + (size_t)(j * slots + slot) * D + 2 * seg;
+#pragma unroll
+          for (int i = 0; i < D / 16; ++i) {
+            const float2 v = *reinterpret_cast<const float2*>(src + 16 * i);
+            val[i].x += w * v.x;
+            val[i].y += w * v.y;
+          }
+        }
+        lse = den > 0.f ? mt + log2f(den) : -CUDART_INF_F;
       }
-      lse = den > 0.f ? mt + log2f(den) : -CUDART_INF_F;
     }
   }
 
