@@ -742,7 +742,8 @@ def test_gemm_bf16_makes_its_input_norm(k, status, T, N, K, splits, mode):
     assert (out[:T].double() - two[:T].double()).abs().max().item() <= 1e-2 * scale
 
 
-@pytest.mark.parametrize("T,E,I", [(8, 1536, 8960), (16, 256, 704), (1, 128, 64), (5, 640, 1344), (13, 3584, 1024)])
+@pytest.mark.parametrize("T,E,I", [(8, 1536, 8960), (16, 256, 704), (1, 128, 64), (5, 640, 1344), (13, 3584, 1024),
+                                   (32, 1536, 8960), (17, 256, 704), (25, 1792, 320)])
 def test_mlp_fused_is_the_feed_forward(k, status, T, E, I):
     """The gated feed-forward in one kernel: norm, gate|up, SiLU * up, down and the add into the
     residual rows, against the formulas in float64 and against the separate projections."""
@@ -804,12 +805,12 @@ def test_gemm_bf16_add_mirrored(k, status, T, N, K, splits):
 
 def test_mlp_fused_refuses_what_it_cannot_do(k, status):
     E, I = 256, 128
-    resid = torch.zeros(20, E, device="cuda")
-    out = torch.zeros(20, E, device="cuda")
+    resid = torch.zeros(40, E, device="cuda")
+    out = torch.zeros(40, E, device="cuda")
     w_norm = torch.ones(E, device="cuda")
     w_gu = torch.zeros(2 * I, E, dtype=torch.bfloat16, device="cuda")
     w_down = torch.zeros(E, I, dtype=torch.bfloat16, device="cuda")
-    assert not k.mlp_fused(resid, w_norm, 1e-6, w_gu, w_down, out, 17, status)  # too many rows
+    assert not k.mlp_fused(resid, w_norm, 1e-6, w_gu, w_down, out, 33, status)  # too many rows
     with pytest.raises(ValueError):
         k.mlp_fused(resid, w_norm, 1e-6, w_gu, w_down, resid, 4, status)  # in place
     odd = torch.zeros(2 * 96, E, dtype=torch.bfloat16, device="cuda")

@@ -760,14 +760,14 @@ static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mw2, const CUte
 
 
 // ---------------------------------------------------------------------------------------------
-// The gated feed-forward of a small step (at most 16 tokens) in one kernel:
+// The gated feed-forward of a small step (at most 32 tokens: a tile of 16 or of 32) in one kernel:
 //   resid_out[t, :] += W_down * (silu(W_gate x_t) * (W_up x_t)),  x_t = rmsnorm(resid_in[t, :]) * w_norm.
 // CTA j owns 64 features of the inner width: it streams their 64 gate rows and 64 up rows of
 // [2 I, E] (as the SwiGLU mode above, the input norm made on the spot), turns the accumulator
-// into the [16 tokens x 64 features] bf16 activation tile in shared memory, and goes straight
+// into the [tokens x 64 features] bf16 activation tile in shared memory, and goes straight
 // on, with the same ring of stages, to the 64 columns of W_down [E, I] that belong to these
 // features: E / 128 tiles of [128 rows x 64], each one product with the activation tile, each
-// with 16 columns of tensor memory of its own.  What comes out is this CTA's share of the sum
+// with one tile width of tensor-memory columns of its own.  What comes out is this CTA's share of the sum
 // over the inner width; the shares meet in the float32 residual stream by reductions at the
 // L2 (red.global.add.f32), so their order, and with it the last bits of the sum, is not fixed.
 // The activations never leave the SM, the W_down tiles are already on their way while the
@@ -783,16 +783,15 @@ struct MlpArgs {
   int* status;
   float eps;
   int T, E, I;
-  int tmem_cols;          // 16 + 16 * E / 128, rounded up to a power of two (at least 32)
+  int tmem_cols;          // tile width x (1 + E / 128), rounded up to a power of two (at least 32)
 };
 
-constexpr int MF_BN = 16;
-constexpr int MF_NORM_BATCH = 6;
+constexpr int MF_MAX_BN = 32;
 constexpr int MF_MAX_BATCHES = 32;
-constexpr int MF_MAX_TILES = 31;  // row tiles of W_down: 16 columns of tensor memory each, after the first 16
-constexpr uint32_t MF_X_BYTES = MF_BN * GB_BK * 2;
+constexpr int MF_MAX_TILES = 31;  // row tiles of W_down: MF_BN columns of tensor memory each, after the first MF_BN
 
-template <int MF_STAGES>  // 16 KB each: as many of ten, eight and four as fit beside the X tiles of the row
+// MF_BN: tokens of the tile (16 or 32).  MF_STAGES: stages of 16 KB, as many as fit beside the X tiles.
+template <int MF_BN, int MF_STAGES>
 __global__ void __launch_bounds__(GB_THREADS, 1)
 mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_constant__ CUtensorMap map_up,
                  const __grid_constant__ CUtensorMap map_down, MlpArgs m) {
@@ -805,7 +804,9 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
   __shared__ uint32_t tmem_slot;
   __shared__ int epilogue_failed;
   __shared__ float rstd_s[MF_BN];
-  __shared__ float swap_buf[64 * 17];
+  __shared__ float swap_buf[64 * (MF_BN + 1)];
+  constexpr uint32_t MF_X_BYTES = MF_BN * GB_BK * 2;
+  constexpr int MF_NORM_BATCH = MF_BN == 16 ? 6 : 3;
 
   VX_TRACE_SCOPE(15);
   allow_dependents();
@@ -844,7 +845,7 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem_acc = tmem_slot;  // columns 0..15: gate|up; 16 + 16 i ..: row tile i of W_down
+  const uint32_t tmem_acc = tmem_slot;  // columns 0..MF_BN-1: gate|up; MF_BN (1 + i) ..: row tile i of W_down
 
   if (warp == 0 && lane == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -901,7 +902,7 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
       const uint32_t a_addr = smem_base + stage * GB_A_BYTES;
 #pragma unroll
       for (int k = 0; k < GB_BK / 16; ++k)
-        umma_bf16(tmem_acc + 16u + 16u * (uint32_t)t2, umma_smem_desc(a_addr + k * 32),
+        umma_bf16(tmem_acc + (uint32_t)MF_BN * (1u + (uint32_t)t2), umma_smem_desc(a_addr + k * 32),
                   umma_smem_desc(act_addr + k * 32), idesc, k > 0 ? 1u : 0u);
       umma_commit(smem_u32(&empty_bar[stage]));
       umma_commit(smem_u32(&tile_bar[t2]));
@@ -911,46 +912,61 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
     grid_dependency_wait();
     const int q = (int)threadIdx.x - 64;
     {
-      // X tiles: thread q takes the 16-byte chunk q % 8 of token q / 8 in every K block.
+      // X tiles: thread q takes the 16-byte chunk q % 8 of tokens q / 8 (+ 16) in every K block.
       constexpr int NB = MF_NORM_BATCH;
-      const int c = q & 7, r = q >> 3;
-      float ssq = 0.f;
+      constexpr int CPT = MF_BN / 16;  // chunks (tokens) per thread and K block
+      const int c = q & 7;
+      float ssq[CPT];
+#pragma unroll
+      for (int u = 0; u < CPT; ++u) ssq[u] = 0.f;
       for (int i0 = 0; i0 < kb1; i0 += NB) {
-        float4 xa[NB], xb[NB], wa[NB], wb[NB];
+        float4 xa[NB][CPT], xb[NB][CPT], wa[NB], wb[NB];
 #pragma unroll
         for (int j = 0; j < NB; ++j) {
           const int k = (i0 + j) * GB_BK + c * 8;
           const bool in_k = i0 + j < kb1;
           wa[j] = in_k ? __ldg(reinterpret_cast<const float4*>(m.norm_w + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
           wb[j] = in_k ? __ldg(reinterpret_cast<const float4*>(m.norm_w + k + 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
-          const bool on = in_k && r < m.T;
-          const float* src = m.resid_in + (size_t)r * m.resid_in_ld + k;
-          xa[j] = on ? *reinterpret_cast<const float4*>(src) : make_float4(0.f, 0.f, 0.f, 0.f);
-          xb[j] = on ? *reinterpret_cast<const float4*>(src + 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int u = 0; u < CPT; ++u) {
+            const int r = (q >> 3) + 16 * u;
+            const bool on = in_k && r < m.T;
+            const float* src = m.resid_in + (size_t)r * m.resid_in_ld + k;
+            xa[j][u] = on ? *reinterpret_cast<const float4*>(src) : make_float4(0.f, 0.f, 0.f, 0.f);
+            xb[j][u] = on ? *reinterpret_cast<const float4*>(src + 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
         }
 #pragma unroll
         for (int j = 0; j < NB; ++j) {
           if (i0 + j >= kb1) break;
-          const float4 a4 = xa[j], b4 = xb[j];
-          ssq += a4.x * a4.x + a4.y * a4.y + a4.z * a4.z + a4.w * a4.w +
-                 b4.x * b4.x + b4.y * b4.y + b4.z * b4.z + b4.w * b4.w;
-          __nv_bfloat162 p0 = __floats2bfloat162_rn(a4.x * wa[j].x, a4.y * wa[j].y);
-          __nv_bfloat162 p1 = __floats2bfloat162_rn(a4.z * wa[j].z, a4.w * wa[j].w);
-          __nv_bfloat162 p2 = __floats2bfloat162_rn(b4.x * wb[j].x, b4.y * wb[j].y);
-          __nv_bfloat162 p3 = __floats2bfloat162_rn(b4.z * wb[j].z, b4.w * wb[j].w);
-          *reinterpret_cast<uint4*>(x_tiles + (size_t)(i0 + j) * MF_X_BYTES + r * 128 + ((c ^ (r & 7)) << 4)) =
-              make_uint4(*reinterpret_cast<uint32_t*>(&p0), *reinterpret_cast<uint32_t*>(&p1),
-                         *reinterpret_cast<uint32_t*>(&p2), *reinterpret_cast<uint32_t*>(&p3));
+#pragma unroll
+          for (int u = 0; u < CPT; ++u) {
+            const int r = (q >> 3) + 16 * u;
+            const float4 a4 = xa[j][u], b4 = xb[j][u];
+            ssq[u] += a4.x * a4.x + a4.y * a4.y + a4.z * a4.z + a4.w * a4.w +
+                      b4.x * b4.x + b4.y * b4.y + b4.z * b4.z + b4.w * b4.w;
+            __nv_bfloat162 p0 = __floats2bfloat162_rn(a4.x * wa[j].x, a4.y * wa[j].y);
+            __nv_bfloat162 p1 = __floats2bfloat162_rn(a4.z * wa[j].z, a4.w * wa[j].w);
+            __nv_bfloat162 p2 = __floats2bfloat162_rn(b4.x * wb[j].x, b4.y * wb[j].y);
+            __nv_bfloat162 p3 = __floats2bfloat162_rn(b4.z * wb[j].z, b4.w * wb[j].w);
+            *reinterpret_cast<uint4*>(x_tiles + (size_t)(i0 + j) * MF_X_BYTES + r * 128 + ((c ^ (r & 7)) << 4)) =
+                make_uint4(*reinterpret_cast<uint32_t*>(&p0), *reinterpret_cast<uint32_t*>(&p1),
+                           *reinterpret_cast<uint32_t*>(&p2), *reinterpret_cast<uint32_t*>(&p3));
+          }
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (q == 0) mbar_arrive(smem_u32(&x_bar[i0 / NB]));
       }
       // The eight threads of a token sit in consecutive lanes.
-      ssq += __shfl_xor_sync(0xffffffffu, ssq, 1);
-      ssq += __shfl_xor_sync(0xffffffffu, ssq, 2);
-      ssq += __shfl_xor_sync(0xffffffffu, ssq, 4);
-      if (c == 0) rstd_s[r] = rsqrtf(ssq / (float)m.E + m.eps);
+#pragma unroll
+      for (int u = 0; u < CPT; ++u) {
+        float v = ssq[u];
+        v += __shfl_xor_sync(0xffffffffu, v, 1);
+        v += __shfl_xor_sync(0xffffffffu, v, 2);
+        v += __shfl_xor_sync(0xffffffffu, v, 4);
+        if (c == 0) rstd_s[(q >> 3) + 16 * u] = rsqrtf(v / (float)m.E + m.eps);
+      }
     }
     const int quarter = warp & 3;  // TMEM lanes 32 * quarter .. + 31 belong to this warp
     const int row = quarter * 32 + lane;
@@ -961,7 +977,7 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     float v[32];
     if (ready) {
-      tmem_load_16(lane_base, v);
+      if (MF_BN == 32) tmem_load_32(lane_base, v); else tmem_load_16(lane_base, v);
     } else {
 #pragma unroll
       for (int j = 0; j < MF_BN; ++j) v[j] = 0.f;
@@ -969,16 +985,16 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
     // Rows 0..63 are gate, 64..127 up of the same 64 features: up rows hand their values over.
     if (row >= 64) {
 #pragma unroll
-      for (int j = 0; j < MF_BN; ++j) swap_buf[(row - 64) * 17 + j] = v[j];
+      for (int j = 0; j < MF_BN; ++j) swap_buf[(row - 64) * (MF_BN + 1) + j] = v[j];
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");
     if (row < 64) {
-      // Activation tile [16 tokens x 64 features] bf16, K-major, 128-byte swizzled: feature f
+      // Activation tile [MF_BN tokens x 64 features] bf16, K-major, 128-byte swizzled: feature f
       // of token t in chunk (f / 8) ^ (t & 7) of row t.
 #pragma unroll
       for (int j = 0; j < MF_BN; ++j) {
         const float scale = rstd_s[j];
-        const float gate = v[j] * scale, up = swap_buf[row * 17 + j] * scale;
+        const float gate = v[j] * scale, up = swap_buf[row * (MF_BN + 1) + j] * scale;
         const float a = j < m.T ? gate / (1.0f + __expf(-gate)) * up : 0.f;
         *reinterpret_cast<__nv_bfloat16*>(act_tile + j * 128 + ((((row >> 3) ^ (j & 7))) << 4) + (row & 7) * 2) =
             __float2bfloat16_rn(a);
@@ -995,7 +1011,8 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
       for (int t2 = 0; t2 < tiles2; ++t2) {
         if (!mbar_wait(smem_u32(&tile_bar[t2]), 0u, m.status)) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        tmem_load_16(lane_base + 16u + 16u * (uint32_t)t2, v);
+        const uint32_t at = lane_base + (uint32_t)MF_BN * (1u + (uint32_t)t2);
+        if (MF_BN == 32) tmem_load_32(at, v); else tmem_load_16(at, v);
         float* dst = m.resid_out + (size_t)t2 * GB_BM + row;
 #pragma unroll
         for (int j = 0; j < MF_BN; ++j)
@@ -1215,56 +1232,60 @@ VX_API int vx_gemm_bf16_qkv_rope(const void* x, int x_rows, const float* resid, 
                    (heads + 2 * kv_heads) * 128, K, ldy, splits, status, stream, &rope);
 }
 
-// The most dynamic shared memory a CTA of the fused feed-forward may have (set once), or
-// minus a cudaError_t.
-template <int STAGES>
-static int mlp_fused_limit() {
-  static int limit = 0;
-  if (limit == 0) {
-    cudaFuncAttributes attributes_of;
-    cudaError_t e = cudaFuncGetAttributes(&attributes_of, mlp_fused_kernel<STAGES>);
-    if (e != cudaSuccess) return -(int)e;
-    const int value = 227 * 1024 - (int)attributes_of.sharedSizeBytes;
-    e = cudaFuncSetAttribute(mlp_fused_kernel<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, value);
-    if (e != cudaSuccess) return -(int)e;
-    limit = value;
+// One instantiation of the fused feed-forward: the most dynamic shared memory a CTA of it may
+// have (set once; minus a cudaError_t on failure) and its launch.
+template <int BN, int STAGES>
+struct MlpFusedVariant {
+  static int limit() {
+    static int value = 0;
+    if (value == 0) {
+      cudaFuncAttributes attributes_of;
+      cudaError_t e = cudaFuncGetAttributes(&attributes_of, mlp_fused_kernel<BN, STAGES>);
+      if (e != cudaSuccess) return -(int)e;
+      const int most = 227 * 1024 - (int)attributes_of.sharedSizeBytes;
+      e = cudaFuncSetAttribute(mlp_fused_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+      if (e != cudaSuccess) return -(int)e;
+      value = most;
+    }
+    return value;
   }
-  return limit;
-}
+  // 0 launched, a cudaError_t, or -2 if `tiles_bytes` beside the stages do not fit.
+  static int launch(cudaLaunchConfig_t& config, size_t tiles_bytes, const CUtensorMap& mg, const CUtensorMap& mu,
+                    const CUtensorMap& md, const MlpArgs& m) {
+    const int most = limit();
+    if (most < 0) return -most;
+    const size_t smem = (size_t)STAGES * GB_A_BYTES + tiles_bytes;
+    if (smem > (size_t)most) return -2;
+    config.dynamicSmemBytes = smem;
+    return (int)cudaLaunchKernelEx(&config, mlp_fused_kernel<BN, STAGES>, mg, mu, md, m);
+  }
+};
 
-// The gated feed-forward of at most 16 tokens in one kernel (see mlp_fused_kernel):
+// The gated feed-forward of at most 32 tokens in one kernel (see mlp_fused_kernel):
 // resid_out += W_down (silu(W_gate x) * (W_up x)), x = rmsnorm(resid_in) * norm_w, with
 // w_gate_up [2 I, E] (gate rows, then up rows) and w_down [E, I] bf16.  Returns 0 on launch, a
-// cudaError_t on failure, -1 if the arguments are refused (more than 16 tokens, E no multiple
+// cudaError_t on failure, -1 if the arguments are refused (more than 32 tokens, E no multiple
 // of 128, I no multiple of 64, unaligned pointers, resid_in == resid_out), -2 if a row this wide
 // does not fit in shared or tensor memory (the caller then uses the separate projections).
 VX_API int vx_mlp_fused(const float* resid_in, long long resid_in_ld, const float* norm_w, float eps,
                         const void* w_gate_up, const void* w_down, float* resid_out,
                         long long resid_out_ld, int T, int E, int I, int* status, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (T > MF_BN || E <= 0 || I <= 0 || (E % GB_BM) != 0 || (I % 64) != 0) return -1;
+  if (T > MF_MAX_BN || E <= 0 || I <= 0 || (E % GB_BM) != 0 || (I % 64) != 0) return -1;
   if (resid_in == nullptr || resid_out == nullptr || norm_w == nullptr || (const float*)resid_out == resid_in) return -1;
   if ((reinterpret_cast<uintptr_t>(resid_in) & 15) || (reinterpret_cast<uintptr_t>(norm_w) & 15) ||
       (reinterpret_cast<uintptr_t>(w_gate_up) & 15) || (reinterpret_cast<uintptr_t>(w_down) & 15) ||
       (resid_in_ld % 4) != 0)
     return -1;
+  const int bn = T <= 16 ? 16 : 32;
+  const int norm_batch = bn == 16 ? 6 : 3;
   const int kb1 = E / GB_BK, tiles2 = E / GB_BM;
-  if ((kb1 + MF_NORM_BATCH - 1) / MF_NORM_BATCH > MF_MAX_BATCHES) return -2;
+  if ((kb1 + norm_batch - 1) / norm_batch > MF_MAX_BATCHES || tiles2 > MF_MAX_TILES) return -2;
   int cols = 32;
-  while (cols < 16 + 16 * tiles2) cols *= 2;
+  while (cols < bn * (1 + tiles2)) cols *= 2;
   if (cols > 512) return -2;
-  const size_t tiles_bytes = MF_X_BYTES + (size_t)kb1 * MF_X_BYTES + 1024;
-  int stages = 0;
-  for (int want : {10, 8, 4}) {
-    const int limit = want == 10 ? mlp_fused_limit<10>() : (want == 8 ? mlp_fused_limit<8>() : mlp_fused_limit<4>());
-    if (limit < 0) return -limit;
-    if ((size_t)want * GB_A_BYTES + tiles_bytes <= (size_t)limit) {
-      stages = want;
-      break;
-    }
-  }
-  if (stages == 0) return -2;
-  const size_t smem = (size_t)stages * GB_A_BYTES + tiles_bytes;
+  // The activation tile and the X tiles of the first product's K blocks, and the alignment.
+  const size_t tiles_bytes = (size_t)(1 + kb1) * bn * GB_BK * 2 + 1024;
   CUtensorMap mg, mu, md;
   if (!tensor_map_2d(&mg, w_gate_up, I, E, 64)) return -1;
   if (!tensor_map_2d(&mu, (const __nv_bfloat16*)w_gate_up + (size_t)I * E, I, E, 64)) return -1;
@@ -1284,7 +1305,6 @@ VX_API int vx_mlp_fused(const float* resid_in, long long resid_in_ld, const floa
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(I / 64);
   config.blockDim = dim3(GB_THREADS);
-  config.dynamicSmemBytes = smem;
   config.stream = stream;
   cudaLaunchAttribute attributes[1];
   int count = 0;
@@ -1296,7 +1316,15 @@ VX_API int vx_mlp_fused(const float* resid_in, long long resid_in_ld, const floa
   }
   config.attrs = attributes;
   config.numAttrs = count;
-  if (stages == 10) return (int)cudaLaunchKernelEx(&config, mlp_fused_kernel<10>, mg, mu, md, m);
-  if (stages == 8) return (int)cudaLaunchKernelEx(&config, mlp_fused_kernel<8>, mg, mu, md, m);
-  return (int)cudaLaunchKernelEx(&config, mlp_fused_kernel<4>, mg, mu, md, m);
+  // As many stages as fit beside the tiles.
+  int code;
+  if (bn == 16) {
+    code = MlpFusedVariant<16, 10>::launch(config, tiles_bytes, mg, mu, md, m);
+    if (code == -2) code = MlpFusedVariant<16, 8>::launch(config, tiles_bytes, mg, mu, md, m);
+    if (code == -2) code = MlpFusedVariant<16, 4>::launch(config, tiles_bytes, mg, mu, md, m);
+  } else {
+    code = MlpFusedVariant<32, 7>::launch(config, tiles_bytes, mg, mu, md, m);
+    if (code == -2) code = MlpFusedVariant<32, 4>::launch(config, tiles_bytes, mg, mu, md, m);
+  }
+  return code;
 }

@@ -405,7 +405,7 @@ def gemm_bf16_add_mirrored(
 
 
 # Steps of at most this many tokens can run the gated feed-forward as one kernel.
-MLP_FUSED_MAX_TOKENS = 16
+MLP_FUSED_MAX_TOKENS = 32
 
 
 def mlp_fused(
