@@ -1455,8 +1455,9 @@ __global__ void __launch_bounds__(NARROW_THREADS) attn_narrow_kernel(const __gri
 
   if (cluster > 1) {
     // Rows are dealt out to the CTAs of the cluster (row r belongs to rank r % cluster, as its
-    // slot r / cluster).  Every CTA sends each of its rows to the owner; after one cluster
-    // barrier the owner weighs what the ranks sent by their log-sum-exps, in rank order.
+    // slot r / cluster).  Every CTA sends each of its rows to the owner; when the owner's own
+    // barrier has counted all their bytes it weighs what the ranks sent by their log-sum-exps,
+    // in rank order.
     const int slots = 16 / cluster;
     const uint32_t rank = cluster_rank();
     float* recv = reinterpret_cast<float*>(smem_al + attn_tiles_bytes(true, STAGES));  // [cluster][slots][D]

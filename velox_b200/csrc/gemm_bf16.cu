@@ -6,9 +6,11 @@
 // of weight rows; the kernel then streams W once at memory speed.  A projection with few output
 // tiles is split along K over a thread-block cluster (2, 4 or 8 CTAs): every CTA accumulates its
 // share of K in its own tensor memory and sends every row (output feature) of its partial tile
-// to the CTA that owns that row, by stores into the owner's shared memory (distributed shared
-// memory); after one cluster barrier each CTA sums what its peers sent, in rank order, and writes
-// its rows out.  No partial product touches global memory and the order of the sums is fixed.
+// to the CTA that owns that row, by st.async stores into the owner's shared memory (distributed
+// shared memory) that count their bytes on the owner's own mbarrier; when all its bytes are in,
+// each CTA sums what the ranks sent, in rank order, and writes its rows out.  The one barrier
+// of the whole cluster is at the start ("everybody runs").  No partial product touches global
+// memory and the order of the sums is fixed.
 //
 //   warp 0, one lane : TMA producer.  cp.async.bulk.tensor 2-D tiles of W [128 x 64] and
 //                      X [BN x 64] into a ring of 128-byte-swizzled shared-memory stages.
@@ -33,7 +35,8 @@
 //   0  out bf16  [T, ldy] = acc + bias
 //   1  out f32   [T, ldy] = acc + bias          (logits)
 //   2  out f32   [T, ldy] += acc                (projection added straight into the float32
-//                                                residual stream; one CTA owns each element)
+//                                                residual stream; one CTA owns each element;
+//                                                optionally the sums go to a second buffer too)
 //   3  out bf16  [T, ldy] = silu(gate) * up     W rows are [64 gate | 64 up] per CTA (the host
 //                                                passes two tensor maps of the same matrix)
 //   4  QKV of heads of 128 dims, split K only: a CTA's 128 rows are one head; acc + bias is
