@@ -63,6 +63,39 @@ def test_registry_picks_the_model_by_architecture(tmp_path):
         architecture_of({})
 
 
+def test_named_model_sizes_are_configurations_of_the_architecture():
+    """Every --model-size name parses as this architecture; 1.5b has the sizes the benchmark names."""
+    from velox_b200.config import Qwen2Config, architecture_of
+    from velox_b200.config.presets import MODEL_SIZES, model_size
+
+    for name in MODEL_SIZES:
+        cfg = model_size(name)
+        assert architecture_of(cfg).name == "Qwen2ForCausalLM"
+        c = Qwen2Config.from_dict(cfg)
+        assert c.num_attention_heads % c.num_key_value_heads == 0
+    c = Qwen2Config.from_dict(model_size("1.5b"))
+    assert (c.num_hidden_layers, c.hidden_size, c.num_attention_heads, c.num_key_value_heads, c.head_dim,
+            c.intermediate_size, c.vocab_size, c.tie_word_embeddings) == (28, 1536, 12, 2, 128, 8960, 151936, True)
+    cfg = model_size("7b")
+    cfg["hidden_size"] = 1  # a copy: the table is not touched
+    assert model_size("7b")["hidden_size"] == 3584
+    with pytest.raises(KeyError, match="known"):
+        model_size("70b")
+
+
+def test_benchmark_command_line_options():
+    from velox_b200.cli.benchmark import build_prompts, parse_args
+
+    args = parse_args(["--model-size", "tiny-a", "--prompt-len", "9", "--decode-len", "5", "--batch", "1,4"])
+    assert args.max_tokens == 5 and args.prompt_len == 9 and args.batch == "1,4" and args.model is None
+    prompts = build_prompts("mixed", 3, 50, 100, seed=0, fixed_len=args.prompt_len)
+    assert [len(p) for p in prompts] == [9, 9, 9] and all(0 <= t < 50 for p in prompts for t in p)
+    with pytest.raises(SystemExit):
+        parse_args(["--model", "x", "--model-size", "tiny-a"])
+    with pytest.raises(SystemExit):
+        parse_args([])
+
+
 def test_spec_names_every_checkpoint_tensor():
     from velox_b200.config import get_architecture
 

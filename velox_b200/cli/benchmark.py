@@ -11,7 +11,10 @@ project): ``--model``, ``--workload {short,long,mixed}``, ``--num-requests``, ``
 tokenizer; there is no tokenizer here, so prompts are seeded uniform-random token ids whose
 lengths follow the workload (short: 16-64, long: 512-1536, mixed: both).  Added: ``--dtype``,
 ``--random-weights CONFIG_JSON`` with ``--weights-seed`` (writes the model folder first), and
-``--top-k``.  It prints what the reference prints: wall time, steps, prompt and generated
+``--top-k``, ``--model-size NAME`` (random weights with a named configuration's layer sizes,
+``--layers N`` of them), ``--prompt-len`` / ``--decode-len`` (fixed lengths), ``--batch 1,8,64``
+(that many requests and sequences per run) and a roofline line (bytes the steps had to read
+over GPU-busy time).  It prints what the reference prints: wall time, steps, prompt and generated
 tokens, decode tokens/s (generated / wall), time to first token and inter-token latency
 percentiles, the per-stage time of a step, and the sweep table.
 """
@@ -33,7 +36,17 @@ def parse_args(argv: Optional[List[str]] = None) -> argparse.Namespace:
     parser.add_argument("--model", default=None, help="model folder (config.json + model.safetensors)")
     parser.add_argument("--random-weights", default=None, metavar="CONFIG_JSON",
                         help="write a random-weights model folder from this config.json first")
+    parser.add_argument("--model-size", default=None, metavar="NAME",
+                        help="random weights with the layer sizes of a named configuration "
+                             "(tiny-a, tiny-b, 0.5b, 1.5b, 3b, 7b, 14b)")
+    parser.add_argument("--layers", type=int, default=None,
+                        help="with --model-size / --random-weights: build only this many layers")
     parser.add_argument("--weights-seed", type=int, default=0)
+    parser.add_argument("--prompt-len", type=int, default=None,
+                        help="every prompt has this many tokens (instead of the workload's lengths)")
+    parser.add_argument("--decode-len", type=int, default=None, help="the same as --max-tokens")
+    parser.add_argument("--batch", default=None,
+                        help="comma-separated batch sizes: for each, that many requests and max_num_seqs")
     parser.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     parser.add_argument("--workload", default="mixed", choices=sorted(WORKLOADS))
     parser.add_argument("--num-requests", type=int, default=16)
@@ -54,16 +67,21 @@ def parse_args(argv: Optional[List[str]] = None) -> argparse.Namespace:
     parser.add_argument("--output-json", default=None)
     parser.add_argument("--seed", type=int, default=0)
     args = parser.parse_args(argv)
-    if (args.model is None) == (args.random_weights is None):
-        parser.error("give exactly one of --model and --random-weights")
+    if sum(v is not None for v in (args.model, args.random_weights, args.model_size)) != 1:
+        parser.error("give exactly one of --model, --random-weights and --model-size")
+    if args.decode_len is not None:
+        args.max_tokens = args.decode_len
+    if args.batch is not None and args.sweep_batch_size is not None:
+        parser.error("--batch and --sweep-batch-size exclude each other")
     return args
 
 
-def build_prompts(workload: str, count: int, vocab: int, limit: int, seed: int) -> List[List[int]]:
+def build_prompts(workload: str, count: int, vocab: int, limit: int, seed: int,
+                  fixed_len: Optional[int] = None) -> List[List[int]]:
     import numpy as np
 
     rng = np.random.default_rng(seed)
-    ranges = WORKLOADS[workload]
+    ranges = WORKLOADS[workload] if fixed_len is None else [(fixed_len, fixed_len)]
     prompts = []
     for index in range(count):
         low, high = ranges[index % len(ranges)]
@@ -99,7 +117,9 @@ def run_workload(engine, prompts, args) -> Dict[str, object]:
         request.arrival_time = time.time()
         engine.add_request(request)
     steps = 0
+    live_tokens = 0  # keys the steps' attention reads, summed over the steps
     while engine.has_work():
+        live_tokens += sum(r.num_tokens for r in engine.scheduler.running)
         engine.step()
         steps += 1
     wall = time.perf_counter() - start
@@ -120,8 +140,50 @@ def run_workload(engine, prompts, args) -> Dict[str, object]:
         "preemptions": engine.scheduler.num_preemptions,
         "stages_ms": {name: (statistics.mean(v) if v else 0.0) for name, v in engine.stats.items()},
         "blocks_used_peak": None,
+        "live_tokens": live_tokens,
         "requests": requests,
     }
+
+
+def streamed_bytes(model) -> int:
+    """Bytes of the matrices a step reads once: every block's and the head's (an embedding that
+    is also the head counts once; one that is only looked up does not count)."""
+    seen = {}
+    parts = [model.lm_head]
+    for block in model.blocks:
+        parts.extend(getattr(block, name) for name in ("mixer", "feed_forward") if hasattr(block, name))
+    for part in parts:
+        for tensor in getattr(part, "weights", {}).values():
+            if tensor is not None and tensor.dim() == 2:
+                seen[tensor.data_ptr()] = tensor.numel() * tensor.element_size()
+    return sum(seen.values())
+
+
+def hbm_peak_gbs() -> float:
+    """The measured copy bandwidth of this pool's GPUs if the driver left it beside the
+    repository, else the recipe's fallback."""
+    import os
+
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))),
+                        "MEASURED_PEAKS.json")
+    try:
+        with open(path, "r", encoding="utf-8") as handle:
+            return float(json.load(handle)["hbm_gbs"])
+    except (OSError, KeyError, ValueError):
+        return 6650.0
+
+
+def roofline(engine, result: Dict[str, object]) -> Dict[str, float]:
+    """Bytes the run's steps had to read (every matrix once a step, the cache of the live
+    requests) over the time the GPU was busy, against the copy bandwidth."""
+    gpu_ms = engine.stats.get("gpu_ms", [])
+    busy = sum(gpu_ms) / 1000.0
+    total_pages = max(1, engine.cache.num_pages)
+    per_token = engine.runner.kv_cache_bytes() / (total_pages * engine.cache.page_size)
+    needed = streamed_bytes(engine.model) * result["steps"] + per_token * result["live_tokens"]
+    achieved = needed / busy / 1e9 if busy > 0 else 0.0
+    peak = hbm_peak_gbs()
+    return {"hbm_gbs": achieved, "hbm_peak_gbs": peak, "hbm_frac": achieved / peak}
 
 
 def report(result: Dict[str, object], label: str) -> None:
@@ -136,6 +198,9 @@ def report(result: Dict[str, object], label: str) -> None:
     print("per-step stage (mean ms): " + "  ".join(f"{k}={v:.3f}" for k, v in stages.items()))
     if stages.get("step_ms"):
         print(f"GPU-busy fraction  {stages.get('gpu_ms', 0.0) / stages['step_ms']:.2f}")
+    if "hbm_gbs" in result:
+        print(f"HBM roofline       {result['hbm_gbs']:.0f} of {result['hbm_peak_gbs']:.0f} GB/s = {result['hbm_frac']:.2f} "
+              "(weights once a step + cache of the live requests, over GPU-busy time)")
 
 
 def main(argv: Optional[List[str]] = None) -> int:
@@ -145,18 +210,28 @@ def main(argv: Optional[List[str]] = None) -> int:
 
     model_dir = args.model
     holder = None
-    if args.random_weights is not None:
+    if args.random_weights is not None or args.model_size is not None:
         from ..weights import write_random_model
 
-        with open(args.random_weights, "r", encoding="utf-8") as handle:
-            config_json = json.load(handle)
+        if args.model_size is not None:
+            from ..config.presets import model_size
+
+            config_json = model_size(args.model_size)
+        else:
+            with open(args.random_weights, "r", encoding="utf-8") as handle:
+                config_json = json.load(handle)
+        if args.layers is not None:
+            config_json["num_hidden_layers"] = args.layers
         holder = tempfile.TemporaryDirectory(prefix="velox_model_")
         model_dir = holder.name
         write_random_model(model_dir, config_json, seed=args.weights_seed, dtype="bfloat16")
 
     sweep = [int(v) for v in args.sweep_batch_size.split(",")] if args.sweep_batch_size else [args.max_num_seqs]
+    if args.batch is not None:
+        sweep = [int(v) for v in args.batch.split(",")]
     table = []
     for max_num_seqs in sweep:
+        num_requests = max_num_seqs if args.batch is not None else args.num_requests
         engine = Engine.from_pretrained(EngineConfig(
             model=model_dir, dtype=args.dtype, max_model_len=args.max_model_len, max_num_seqs=max_num_seqs,
             max_num_batched_tokens=max(args.max_num_batched_tokens, max_num_seqs),
@@ -165,8 +240,10 @@ def main(argv: Optional[List[str]] = None) -> int:
             enable_cuda_graphs=not args.no_cuda_graphs, seed=args.seed,
         ))
         limit = engine.max_model_len - args.max_tokens - 1
-        prompts = build_prompts(args.workload, args.num_requests, engine.model.vocab_size, limit, args.seed)
+        prompts = build_prompts(args.workload, num_requests, engine.model.vocab_size, limit, args.seed,
+                                fixed_len=args.prompt_len)
         result = run_workload(engine, prompts, args)
+        result.update(roofline(engine, result))
         report(result, f"max_num_seqs={max_num_seqs} workload={args.workload} dtype={args.dtype}")
         if args.show_outputs:
             for request in result["requests"]:
@@ -177,9 +254,10 @@ def main(argv: Optional[List[str]] = None) -> int:
         del engine
     if len(table) > 1:
         print("== sweep")
-        print("max_num_seqs  decode tok/s  TTFT p50 s  preemptions")
+        print("max_num_seqs  decode tok/s  TTFT p50 s  preemptions  HBM roofline")
         for row in table:
-            print(f"{row['max_num_seqs']:>12}  {row['decode_tok_s']:>12.1f}  {row['ttft_p50_s']:>10.4f}  {row['preemptions']:>11}")
+            print(f"{row['max_num_seqs']:>12}  {row['decode_tok_s']:>12.1f}  {row['ttft_p50_s']:>10.4f}  "
+                  f"{row['preemptions']:>11}  {row['hbm_frac']:>12.2f}")
     if args.output_json:
         with open(args.output_json, "w", encoding="utf-8") as handle:
             json.dump(table, handle, indent=1)

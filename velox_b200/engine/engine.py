@@ -169,13 +169,17 @@ class Engine:
         return engine
 
     def warmup(self) -> None:
-        """One short request through the whole loop, so that library handles and kernel images
-        exist before the first real step (engine/engine.py:174-211 does the same)."""
+        """One request through the whole loop before the first real step, so that library
+        handles, kernel images and the work buffers at their final sizes exist (the reference
+        warms up and captures its decode graphs at construction too, engine/engine.py:174-211):
+        a prompt as long as a prefill portion, which takes the route of long steps, two decoded
+        tokens, and then the graph of every decode bucket."""
         limit = self.max_model_len - 2
         if limit < 1:
             return
+        portion = min(self.config.max_prefill_chunk_size, self.config.max_num_batched_tokens, limit)
         request = Request(
-            "__warmup__", [0] * min(8, limit), SamplingParams(temperature=0.0, max_tokens=2, ignore_eos=True)
+            "__warmup__", [0] * max(1, portion), SamplingParams(temperature=0.0, max_tokens=2, ignore_eos=True)
         )
         self.add_request(request)
         guard = 0
@@ -183,6 +187,9 @@ class Engine:
             self.step()
             guard += 1
         self.scheduler.abort_request(request.request_id)
+        self.scheduler.schedule()  # the aborted request's pages and slot go back now
+        torch.cuda.synchronize(self.device)
+        self.runner.capture_decode_graphs()
         torch.cuda.synchronize(self.device)
         for values in self.stats.values():
             values.clear()

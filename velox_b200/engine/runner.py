@@ -493,6 +493,33 @@ class ModelRunner:
         self.kernels_replayed += entry[4]
         return logits[: len(chunks)]
 
+    def capture_decode_graphs(self) -> int:
+        """Capture the graph of every decode bucket that has none yet (1, 2, 4, ... up to the most
+        requests), smallest first; returns how many it captured.  Nothing happens where steps
+        are not replayed as graphs.  A later step that makes a work buffer grow still recaptures
+        its bucket; after a warm-up that has run a full prefill portion none does."""
+        if not self.enable_graphs or self._graphs_broken:
+            return 0
+        captured = 0
+        bucket = 1
+        while True:
+            bucket = min(bucket, self.max_num_seqs)
+            entry = self._graphs.get(bucket)
+            if entry is None or entry[2] != (self.workspace.generation, self._meta_generation):
+                try:
+                    self._graphs[bucket] = self._capture(bucket)
+                except Exception as exc:  # the same fallback as at the first use of a bucket
+                    import logging
+
+                    logging.getLogger(__name__).warning("CUDA graph capture failed (%s); running eagerly", exc)
+                    self._graphs_broken = True
+                    torch.cuda.synchronize(self.device)
+                    return captured
+                captured += 1
+            if bucket >= self.max_num_seqs:
+                return captured
+            bucket *= 2
+
     def _fill_padded(self, entry, bucket: int, chunks: Sequence[StepChunk]) -> bool:
         """Write a padded single-token step straight into the places the captured step reads
         (the layout of a bucket never changes), with arrays instead of per-token loops.  What
