@@ -61,6 +61,8 @@ class DevicePlan:
     split_counters: Optional[torch.Tensor] = None
     partial_o: Optional[torch.Tensor] = None
     partial_lse: Optional[torch.Tensor] = None
+    # Set by the first layer that has run this layout: its tensors need no second look.
+    checked: bool = False
 
 
 class Workspace:

@@ -552,8 +552,12 @@ def attention(
     split_counters: Optional[torch.Tensor] = None,
     status: Optional[torch.Tensor] = None,
     cluster: int = 1,
+    layout_checked: bool = False,
 ) -> None:
     """Run ``num_items`` work items (see attention.cu for their layout) of one kernel family.
+
+    ``layout_checked``: the caller has passed these same index and scratch tensors before (the
+    step's layout is shared by all layers); only q, out and the caches are checked again.
 
     With ``merge_items`` and ``split_counters`` (int32, zero, one per merge item and KV head)
     the bfloat16 families merge split key ranges themselves: the last split to finish does it.
@@ -566,19 +570,20 @@ def attention(
     _need(out, want, "out")
     _need(k_cache, want, "k_cache")
     _need(v_cache, want, "v_cache")
-    for name, t in (("block_tables", block_tables), ("q_start", q_start), ("q_len", q_len),
-                    ("kv_len", kv_len), ("items", items)):
-        _need(t, torch.int32, name)
     if k_cache.shape[2] != num_kv_heads or k_cache.shape[3] != head_dim:
         raise ValueError(f"cache shape {tuple(k_cache.shape)} does not match {num_kv_heads} x {head_dim}")
-    if num_heads % num_kv_heads != 0:
-        raise ValueError("num_heads must be a multiple of num_kv_heads")
-    if partial_o is not None:
-        _need(partial_o, torch.float32, "partial_o")
-        _need(partial_lse, torch.float32, "partial_lse")
-    if split_counters is not None:
-        _need(split_counters, torch.int32, "split_counters")
-        _need(merge_items, torch.int32, "merge_items")
+    if not layout_checked:
+        for name, t in (("block_tables", block_tables), ("q_start", q_start), ("q_len", q_len),
+                        ("kv_len", kv_len), ("items", items)):
+            _need(t, torch.int32, name)
+        if num_heads % num_kv_heads != 0:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        if partial_o is not None:
+            _need(partial_o, torch.float32, "partial_o")
+            _need(partial_lse, torch.float32, "partial_lse")
+        if split_counters is not None:
+            _need(split_counters, torch.int32, "split_counters")
+            _need(merge_items, torch.int32, "merge_items")
     lib = attention_lib(head_dim)
     _check(
         lib.vx_attention(kind, _p(q), _p(out), _p(k_cache), _p(v_cache), _p(block_tables),

@@ -122,10 +122,19 @@ def linear(
     if bias_f32 is not None:
         if bias_lowp is None:
             raise ValueError("the bfloat16 library GEMM needs the bias in bfloat16 too")
-        torch.addmm(bias_lowp, xs, weight.t(), out=os_)
+        torch.addmm(bias_lowp, xs, _transposed(weight), out=os_)
     else:
-        torch.mm(xs, weight.t(), out=os_)
+        torch.mm(xs, _transposed(weight), out=os_)
     return out
+
+
+def _transposed(weight: torch.Tensor) -> torch.Tensor:
+    """The transposed view of a weight, made once and kept on the weight itself."""
+    view = getattr(weight, "_vx_transposed", None)
+    if view is None:
+        view = weight.t()
+        weight._vx_transposed = view
+    return view
 
 
 def swiglu_linear(

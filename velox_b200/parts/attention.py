@@ -93,7 +93,10 @@ class Attention(Mixer):
                 merge_items=plan.merge_items, split_counters=plan.split_counters,
                 status=ctx.status,
                 cluster=plan.cluster if kind == kernels.ATTN_BF16_NARROW else 1,
+                layout_checked=getattr(plan, "checked", False),
             )
+        if hasattr(plan, "checked"):
+            plan.checked = True
         if plan.num_merges and plan.split_counters is None:
             kernels.attention_merge(
                 attn, ctx.q_start, plan.merge_items, plan.num_merges, plan.partial_o,
