@@ -132,6 +132,8 @@ def _p(t: Optional[torch.Tensor]) -> Optional[int]:
 
 
 def _need(t: torch.Tensor, dtype: torch.dtype, name: str) -> None:
+    if t.dtype is dtype and t.is_cuda and t.is_contiguous():
+        return
     if t.dtype != dtype:
         raise TypeError(f"{name} must be {dtype}, got {t.dtype}")
     if not t.is_cuda:
