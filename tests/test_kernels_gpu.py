@@ -566,10 +566,11 @@ def plain_candidates(scaled, top_k, top_p):
     return set(order[keep].tolist())
 
 
-@pytest.mark.parametrize("top_k,top_p", [(5, 1.0), (0, 0.6), (40, 0.9), (1, 1.0), (0, 0.05)])
-def test_filter_threshold(k, top_k, top_p):
+@pytest.mark.parametrize("vocab", [3001, 50021])
+@pytest.mark.parametrize("top_k,top_p", [(5, 1.0), (0, 0.6), (40, 0.9), (1, 1.0), (0, 0.05), (700, 0.999)])
+def test_filter_threshold(k, top_k, top_p, vocab):
     gen = torch.Generator().manual_seed(top_k + int(top_p * 100))
-    R, vocab = 4, 3001
+    R = 4
     logits = (torch.randn(R, vocab, generator=gen) * 3).cuda()
     temps = torch.tensor([0.7, 1.0, 1.3, 0.0]).cuda()
     thr = torch.empty(R, device="cuda")
