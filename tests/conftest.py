@@ -1,12 +1,14 @@
-import os
+"""Test set-up: the repository and the tests' own helpers on the import path, the ``gpu`` marker,
+and a skip for GPU tests on a machine without a CUDA device."""
+import pathlib
 import sys
 
 import pytest
 
-REPO_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-for path in (REPO_ROOT, os.path.dirname(os.path.abspath(__file__))):
-    if path not in sys.path:
-        sys.path.insert(0, path)
+_HERE = pathlib.Path(__file__).resolve().parent
+for _folder in (_HERE.parent, _HERE):
+    if str(_folder) not in sys.path:
+        sys.path.insert(0, str(_folder))
 
 
 def pytest_configure(config):
@@ -14,11 +16,12 @@ def pytest_configure(config):
 
 
 def pytest_collection_modifyitems(config, items):
+    gpu_tests = [item for item in items if item.get_closest_marker("gpu") is not None]
+    if not gpu_tests:
+        return
     import torch
 
-    if torch.cuda.is_available():
-        return
-    skip = pytest.mark.skip(reason="no CUDA device available")
-    for item in items:
-        if "gpu" in item.keywords:
-            item.add_marker(skip)
+    if not torch.cuda.is_available():
+        reason = pytest.mark.skip(reason="this test needs a CUDA device and there is none")
+        for item in gpu_tests:
+            item.add_marker(reason)

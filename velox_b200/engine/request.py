@@ -1,18 +1,25 @@
-"""A generation request and its life cycle.
+"""A generation request: its tokens, where it stands, and who wants to hear about it.
 
-Field names and meanings follow engine/request.py:14-179 of the reference: ``all_token_ids``
-is prompt plus generated tokens, ``num_computed_tokens`` counts the tokens whose keys and values
-are in the cache, a request *is decoding* when at most one token is not yet computed, and
-prefill and decode are the same operation at different chunk sizes.
+The public names are the ones a user of the reference engine knows (engine/request.py of that
+project: ``request_id``, ``prompt_token_ids``, ``output_token_ids``, ``all_token_ids``,
+``num_computed_tokens``, ``finish_reason`` ...), because requests are part of the Python entry
+point.  How they are kept is this engine's own: one token list with the prompt's length as a
+mark, the cache bookkeeping in the request's ``SequenceCache`` (``cache``), and a table that
+says which status follows from which facts.
 """
 from __future__ import annotations
 
+import logging
 import time
 from enum import Enum
-from typing import Callable, FrozenSet, List, Optional
+from typing import Callable, FrozenSet, List, Optional, Sequence
 
 from ..cache.manager import SequenceCache
 from ..sampling.params import SamplingParams
+
+_log = logging.getLogger(__name__)
+
+Listener = Callable[["Request", str, Optional[int]], None]
 
 
 class RequestStatus(Enum):
@@ -25,142 +32,166 @@ class RequestStatus(Enum):
 
 
 class FinishReason(str, Enum):
-    STOP = "stop"
-    LENGTH = "length"
-    ABORT = "abort"
+    STOP = "stop"      # an end-of-sequence or stop token was sampled
+    LENGTH = "length"  # max_tokens reached
+    ABORT = "abort"    # taken out by the caller
+
+
+# What a finished request's status is, by the reason it ended for.
+_STATUS_AFTER = {
+    FinishReason.STOP: RequestStatus.FINISHED,
+    FinishReason.LENGTH: RequestStatus.FINISHED,
+    FinishReason.ABORT: RequestStatus.ABORTED,
+}
 
 
 class Request:
+    """One prompt and what has been generated for it so far.
+
+    A request is *decoding* when at most one of its tokens is not in the cache yet: prefill and
+    decode are the same operation on portions of different length, and a preempted request
+    simply has all of its tokens (prompt and generated) uncomputed again.
+    """
+
     def __init__(
         self,
         request_id: str,
-        prompt_token_ids: List[int],
+        prompt_token_ids: Sequence[int],
         sampling_params: Optional[SamplingParams] = None,
         arrival_time: Optional[float] = None,
     ) -> None:
-        if not prompt_token_ids:
-            raise ValueError("prompt_token_ids must contain at least one token")
+        tokens = [int(t) for t in prompt_token_ids]
+        if len(tokens) == 0:
+            raise ValueError(f"request {request_id!r}: an empty prompt cannot be continued")
         self.request_id = request_id
-        self.prompt_token_ids = list(prompt_token_ids)
-        self.num_prompt_tokens = len(self.prompt_token_ids)
-        self.sampling_params = sampling_params or SamplingParams()
-        self.arrival_time = time.time() if arrival_time is None else arrival_time
-
-        self.status = RequestStatus.WAITING
-        self.output_token_ids: List[int] = []
-        self.all_token_ids: List[int] = list(self.prompt_token_ids)
-
-        # Set by the scheduler when the request is first queued.
+        self.sampling_params = SamplingParams() if sampling_params is None else sampling_params
+        self.arrival_time = arrival_time if arrival_time is not None else time.time()
+        # prompt first, generated tokens after it
+        self._tokens: List[int] = tokens
+        self._prompt_len = len(tokens)
+        # Given by the scheduler at the first queueing; holds the block tables, the state slot
+        # and the count of computed tokens.
         self.cache: Optional[SequenceCache] = None
+        # Tokens the scheduler gave this request in the step that is being run.
         self.current_chunk_size = 0
-
-        self.finished = False
+        self.status = RequestStatus.WAITING
         self.finish_reason: Optional[FinishReason] = None
         self.num_preemptions = 0
         self.first_token_time: Optional[float] = None
         self.finish_time: Optional[float] = None
-        self._listeners: List[Callable[["Request", str, Optional[int]], None]] = []
+        self._listeners: List[Listener] = []
 
-    # ------------------------------------------------------------------ views of the cache state
+    # ------------------------------------------------------------------ tokens
     @property
-    def num_computed_tokens(self) -> int:
-        return 0 if self.cache is None else self.cache.num_computed
-
-    @property
-    def block_table(self) -> List[int]:
-        """Block table of the first cache group."""
-        return [] if self.cache is None or not self.cache.tables else self.cache.tables[0]
+    def all_token_ids(self) -> List[int]:
+        """Prompt and generated tokens, the list itself (what a recompute prefills)."""
+        return self._tokens
 
     @property
-    def seq_index(self) -> Optional[int]:
-        return None if self.cache is None else self.cache.slot
+    def prompt_token_ids(self) -> List[int]:
+        return self._tokens[: self._prompt_len]
 
-    # ------------------------------------------------------------------ counts
     @property
-    def num_tokens(self) -> int:
-        return len(self.all_token_ids)
+    def output_token_ids(self) -> List[int]:
+        return self._tokens[self._prompt_len :]
+
+    @property
+    def num_prompt_tokens(self) -> int:
+        return self._prompt_len
 
     @property
     def num_output_tokens(self) -> int:
-        return len(self.output_token_ids)
+        return len(self._tokens) - self._prompt_len
+
+    @property
+    def num_tokens(self) -> int:
+        return len(self._tokens)
+
+    @property
+    def max_tokens(self) -> int:
+        return self.sampling_params.max_tokens
+
+    # ------------------------------------------------------------------ what the cache holds
+    @property
+    def num_computed_tokens(self) -> int:
+        return self.cache.num_computed if self.cache is not None else 0
 
     @property
     def num_uncomputed_tokens(self) -> int:
-        return max(0, len(self.all_token_ids) - self.num_computed_tokens)
+        return max(len(self._tokens) - self.num_computed_tokens, 0)
 
     @property
     def is_decoding(self) -> bool:
         return self.num_uncomputed_tokens <= 1
 
     @property
-    def max_tokens(self) -> int:
-        return self.sampling_params.max_tokens
+    def block_table(self) -> List[int]:
+        """Pages of the first cache group (all groups have tables of the same length)."""
+        if self.cache is None or not self.cache.tables:
+            return []
+        return self.cache.tables[0]
+
+    @property
+    def seq_index(self) -> Optional[int]:
+        """The state slot, while the request runs."""
+        return self.cache.slot if self.cache is not None else None
 
     def tokens_for_chunk(self, chunk_size: int) -> List[int]:
-        start = self.num_computed_tokens
-        return self.all_token_ids[start : start + chunk_size]
+        """The next ``chunk_size`` tokens that are not in the cache yet."""
+        first = self.num_computed_tokens
+        return self._tokens[first : first + chunk_size]
 
-    # ------------------------------------------------------------------ transitions
-    def append_token(self, token_id: int) -> None:
-        self.output_token_ids.append(token_id)
-        self.all_token_ids.append(token_id)
-        if self.first_token_time is None:
-            self.first_token_time = time.time()
-        self._emit("token", token_id)
+    # ------------------------------------------------------------------ life cycle
+    @property
+    def finished(self) -> bool:
+        return self.finish_reason is not None
 
     def refresh_status(self) -> None:
-        if self.finished:
-            return
-        self.status = (
-            RequestStatus.RUNNING_DECODE if self.is_decoding else RequestStatus.RUNNING_PREFILL
-        )
+        """A running request is in prefill or in decode by how much of it is uncomputed."""
+        if not self.finished:
+            self.status = RequestStatus.RUNNING_DECODE if self.is_decoding else RequestStatus.RUNNING_PREFILL
+
+    def append_token(self, token_id: int) -> None:
+        self._tokens.append(int(token_id))
+        if self.first_token_time is None:
+            self.first_token_time = time.time()
+        self._tell("token", token_id)
 
     def should_stop(self, token_id: int, eos_token_ids: FrozenSet[int]) -> Optional[FinishReason]:
+        """Whether the token just appended ends the request, and why."""
         params = self.sampling_params
-        if not params.ignore_eos and (
-            token_id in eos_token_ids or token_id in params.stop_token_ids
-        ):
+        ends_text = token_id in eos_token_ids or token_id in params.stop_token_ids
+        if ends_text and not params.ignore_eos:
             return FinishReason.STOP
-        if len(self.output_token_ids) >= params.max_tokens:
-            return FinishReason.LENGTH
-        return None
+        return FinishReason.LENGTH if self.num_output_tokens >= params.max_tokens else None
 
     def finish(self, reason: FinishReason) -> None:
+        """Ends the request once; a second call changes nothing."""
         if self.finished:
             return
-        self.finished = True
         self.finish_reason = reason
+        self.status = _STATUS_AFTER[reason]
         self.finish_time = time.time()
-        self.status = (
-            RequestStatus.ABORTED if reason is FinishReason.ABORT else RequestStatus.FINISHED
-        )
-        self._emit("finish", None)
-
-    # ------------------------------------------------------------------ listeners
-    def add_listener(self, listener: Callable[["Request", str, Optional[int]], None]) -> None:
-        """``listener(request, kind, token_id)`` with kind "token" or "finish"."""
-        self._listeners.append(listener)
-
-    def _emit(self, kind: str, token_id: Optional[int]) -> None:
-        for listener in self._listeners:
-            try:
-                listener(self, kind, token_id)
-            except Exception:  # a listener must not break the engine loop
-                import logging
-
-                logging.getLogger(__name__).exception(
-                    "request %s: listener raised", self.request_id
-                )
+        self._tell("finish", None)
 
     @property
     def time_to_first_token(self) -> Optional[float]:
-        if self.first_token_time is None:
-            return None
-        return self.first_token_time - self.arrival_time
+        return None if self.first_token_time is None else self.first_token_time - self.arrival_time
+
+    # ------------------------------------------------------------------ listeners
+    def add_listener(self, listener: Listener) -> None:
+        """``listener(request, "token", token_id)`` after every generated token and
+        ``listener(request, "finish", None)`` at the end.  A listener that raises is logged and
+        does not stop the engine."""
+        self._listeners.append(listener)
+
+    def _tell(self, kind: str, token_id: Optional[int]) -> None:
+        for listener in self._listeners:
+            try:
+                listener(self, kind, token_id)
+            except Exception:
+                _log.exception("request %s: a listener raised on %r", self.request_id, kind)
 
     def __repr__(self) -> str:
-        return (
-            f"Request(id={self.request_id}, status={self.status.name}, "
-            f"prompt={self.num_prompt_tokens}, computed={self.num_computed_tokens}, "
-            f"output={len(self.output_token_ids)})"
-        )
+        return (f"<Request {self.request_id} {self.status.value}: {self._prompt_len} prompt + "
+                f"{self.num_output_tokens} generated tokens, {self.num_computed_tokens} in the cache>")
