@@ -344,3 +344,41 @@ def test_cluster_size_fits_in_one_wave():
     assert ap.choose_cluster(opt, pairs=4, wanted=1) == 1
     unlimited = ap.PlanOptions(num_kv_heads=2, group=6, window=None, use_f32=False, narrow_max_cluster=8)
     assert ap.choose_cluster(unlimited, pairs=500, wanted=9) == 8
+
+
+def test_request_keeps_its_tokens_and_tells_its_listeners():
+    r = Request("q", (4, 5, 6), SamplingParams(temperature=0.0, max_tokens=2, stop_token_ids=[9]))
+    heard = []
+    r.add_listener(lambda req, kind, token: heard.append((kind, token)))
+    r.add_listener(lambda req, kind, token: 1 / 0)  # a listener that raises does not stop anything
+    assert r.prompt_token_ids == [4, 5, 6] and r.output_token_ids == [] and r.num_tokens == 3
+    assert r.num_computed_tokens == 0 and r.num_uncomputed_tokens == 3 and not r.is_decoding
+    assert r.block_table == [] and r.seq_index is None and not r.finished
+    r.append_token(7)
+    assert r.all_token_ids == [4, 5, 6, 7] and r.output_token_ids == [7] and r.num_output_tokens == 1
+    assert r.should_stop(7, frozenset()) is None
+    assert r.should_stop(9, frozenset()) is FinishReason.STOP and r.should_stop(3, frozenset({3})) is FinishReason.STOP
+    r.append_token(8)
+    assert r.should_stop(8, frozenset()) is FinishReason.LENGTH
+    r.finish(FinishReason.LENGTH)
+    r.finish(FinishReason.ABORT)  # the first reason stands
+    assert r.finished and r.finish_reason is FinishReason.LENGTH and r.status is RequestStatus.FINISHED
+    assert heard == [("token", 7), ("token", 8), ("finish", None)]
+    assert r.time_to_first_token is not None and r.time_to_first_token >= 0.0
+    quiet = Request("e", [1], SamplingParams(max_tokens=5, ignore_eos=True, stop_token_ids=[2]))
+    quiet.append_token(2)
+    assert quiet.should_stop(2, frozenset({2})) is None  # ignore_eos: only the length ends it
+    aborted = Request("a", [1])
+    aborted.finish(FinishReason.ABORT)
+    assert aborted.status is RequestStatus.ABORTED
+
+
+@pytest.mark.parametrize("bad", [dict(n=2), dict(temperature=-0.1), dict(top_p=0.0), dict(top_p=1.01), dict(top_k=-1),
+                                 dict(repetition_penalty=0.0), dict(max_tokens=0)])
+def test_sampling_params_ranges(bad):
+    with pytest.raises(ValueError, match=next(iter(bad))):
+        SamplingParams(**bad)
+    p = SamplingParams(temperature=0.0, top_k=3, presence_penalty=0.1)
+    assert p.is_greedy and p.filters_candidates and p.has_penalties
+    q = SamplingParams()
+    assert not q.is_greedy and not q.filters_candidates and not q.has_penalties
