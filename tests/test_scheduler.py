@@ -382,3 +382,32 @@ def test_sampling_params_ranges(bad):
     assert p.is_greedy and p.filters_candidates and p.has_penalties
     q = SamplingParams()
     assert not q.is_greedy and not q.filters_candidates and not q.has_penalties
+
+
+def test_planner_with_arrays_equals_the_plain_one():
+    """Long steps are laid out with arrays: the same items, merges and cluster as tile by tile."""
+    import random
+
+    import numpy as np
+
+    from velox_b200.ops import attention_plan as ap
+
+    rng = random.Random(5)
+    for _ in range(300):
+        opt = ap.PlanOptions(
+            num_kv_heads=rng.choice([1, 2, 4]), group=rng.choice([1, 2, 6, 8, 20]), window=rng.choice([None, 8, 100]),
+            use_f32=rng.random() < 0.2, target_ctas=rng.choice([8, 64, 296]), min_split_keys=rng.choice([64, 256]),
+            max_splits=rng.choice([1, 4, 64]), narrow_max_rows=rng.choice([16, 64]),
+            narrow_target_ctas=rng.choice([None, 148]), narrow_max_cluster=rng.choice([1, 2, 8]),
+            narrow_cluster_limits=rng.choice([(), ((8, 16), (4, 37), (2, 74))]),
+            narrow_global_split_keys=rng.choice([256, 1024]), wide_on_tensor_memory=rng.random() < 0.5)
+        q = [rng.choice([0, 1, 1, 2, 5, 17, 64, 300, 700]) for _ in range(rng.randint(0, 9))]
+        kv = [n + rng.choice([0, 3, 100, 2000, 9000]) for n in q]
+        plain, fast = ap.plan_attention_plain(q, kv, opt), ap._plan_with_arrays(q, kv, opt)
+        assert (plain.partial_rows, plain.cluster, list(plain.items)) == (fast.partial_rows, fast.cluster, list(fast.items))
+        for kind in plain.items:
+            assert np.array_equal(plain.items[kind], fast.items[kind]) and fast.items[kind].dtype == np.int32
+        assert np.array_equal(plain.merge_items, fast.merge_items) and plain.merge_items.shape == fast.merge_items.shape
+        # and the public entry picks one of the two
+        both = ap.plan_attention(q, kv, opt)
+        assert all(np.array_equal(plain.items[kind], both.items[kind]) for kind in plain.items)

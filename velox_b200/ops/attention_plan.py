@@ -99,6 +99,138 @@ def plan_attention(
 ) -> AttentionPlan:
     """Lay out one step.  ``fixed_splits`` forces that many splits for every tile (some may be
     empty) and ``fixed_cluster`` the cluster size of the narrow kind, which gives a layout whose
+    shape depends on the batch size only.
+
+    Without forced splits the layout of a long step is computed with arrays
+    (``_plan_with_arrays``); the loops of ``plan_attention_plain`` say the same thing tile by
+    tile, serve the short steps, and are what the tests compare the arrays with."""
+    if fixed_splits is None:
+        # The arrays cost about as much as forty tiles of the loops, whatever the step.
+        rows = sum(q_lens) * opt.group
+        if rows > _ARRAYS_FROM_TILES * TILE_ROWS[KIND_BF16_TC if opt.wide_on_tensor_memory and not opt.use_f32
+                                                 else KIND_F32]:
+            return _plan_with_arrays(q_lens, kv_lens, opt)
+    return plan_attention_plain(q_lens, kv_lens, opt, fixed_splits, fixed_cluster)
+
+
+_ARRAYS_FROM_TILES = 40
+
+
+def _plan_with_arrays(q_lens: Sequence[int], kv_lens: Sequence[int], opt: PlanOptions) -> AttentionPlan:
+    """``plan_attention_plain`` without forced splits, a sequence's tiles at a time."""
+    group = opt.group
+    q_len = np.asarray(q_lens, dtype=np.int64)
+    kv_len = np.asarray(kv_lens, dtype=np.int64)[: len(q_len)]
+    q_len = q_len[: len(kv_len)]
+    rows = q_len * group
+    if opt.use_f32:
+        kind_of_seq = np.full(len(rows), KIND_F32, np.int64)
+    else:
+        long_kind = KIND_BF16_TC if opt.wide_on_tensor_memory else KIND_BF16_WIDE
+        kind_of_seq = np.where(rows <= opt.narrow_max_rows, KIND_BF16_NARROW, long_kind)
+    height_of_kind = np.zeros(max(TILE_ROWS) + 1, np.int64)
+    for k, h in TILE_ROWS.items():
+        height_of_kind[k] = h
+    height_of_seq = height_of_kind[kind_of_seq]
+    tiles_of_seq = np.where(rows > 0, -(-rows // height_of_seq), 0)
+    total = int(tiles_of_seq.sum())
+    if total == 0:
+        return AttentionPlan()
+    seq_of = np.repeat(np.arange(len(rows), dtype=np.int64), tiles_of_seq)
+    first_tile_of_seq = np.cumsum(tiles_of_seq) - tiles_of_seq
+    kind_of = kind_of_seq[seq_of]
+    row_begin = (np.arange(total, dtype=np.int64) - first_tile_of_seq[seq_of]) * height_of_seq[seq_of]
+    row_count = np.minimum(height_of_seq[seq_of], rows[seq_of] - row_begin)
+    ctx = (kv_len - q_len)[seq_of]
+    hi = ctx + (row_begin + row_count - 1) // group + 1
+    if opt.window:
+        lo = np.maximum(0, ctx + row_begin // group - opt.window + 1)
+    else:
+        lo = np.zeros(total, np.int64)
+    span = hi - lo
+    num_tiles = len(kind_of)
+    base_ctas = num_tiles * opt.num_kv_heads
+    narrow = kind_of == KIND_BF16_NARROW
+
+    # CTAs a tile's key range should be spread over so that the step fills the GPU.
+    target = np.full(num_tiles, opt.target_ctas, np.int64)
+    if opt.narrow_target_ctas is not None:
+        target[narrow] = opt.narrow_target_ctas
+    per_tile = np.minimum(target // max(base_ctas, 1), span // max(opt.min_split_keys, 1))
+    wanted = np.where(base_ctas >= target, 1, np.maximum(1, per_tile))
+
+    cluster = 1
+    if opt.narrow_max_cluster > 1 and narrow.any():
+        cluster = choose_cluster(opt, int(narrow.sum()) * opt.num_kv_heads, int(wanted[narrow].max()))
+    if cluster > 1:
+        through_memory = np.minimum(wanted // cluster, span // (cluster * max(opt.narrow_global_split_keys, 1)))
+        wanted = np.where(narrow, through_memory, wanted)
+    splits = np.maximum(1, np.minimum(wanted, opt.max_splits))
+
+    # Items: one row per unsplit tile; the split tiles (few) are cut one by one, in tile order,
+    # because the places of their partial rows follow that order.
+    items = np.zeros((num_tiles, ITEM_WIDTH), np.int64)
+    items[:, 0] = seq_of
+    items[:, 1] = row_begin
+    items[:, 2] = row_count
+    items[:, 3] = lo
+    items[:, 4] = hi
+    items[:, 5] = -1
+    order_key = np.arange(num_tiles, dtype=np.int64) * (opt.max_splits + 1)
+    extra_rows, extra_keys, extra_kinds = [], [], []
+    merges: List[List[int]] = []
+    partial_rows = 0
+    split_tiles = np.nonzero(splits > 1)[0]
+    for t in split_tiles:
+        n = int(splits[t])
+        t_lo, t_hi, rows_t = int(lo[t]), int(hi[t]), int(row_count[t])
+        first_tile = t_lo // KEY_TILE
+        tiles_per_split = -(-(-(-t_hi // KEY_TILE) - first_tile) // n)
+        stride = opt.num_kv_heads * rows_t
+        merge_index = len(merges)
+        merges.append([int(seq_of[t]), int(row_begin[t]), rows_t, partial_rows, n, stride, 0, 0])
+        for s in range(n):
+            begin = max(t_lo, (first_tile + s * tiles_per_split) * KEY_TILE)
+            end = max(min(t_hi, (first_tile + (s + 1) * tiles_per_split) * KEY_TILE), begin)
+            extra_rows.append([int(seq_of[t]), int(row_begin[t]), rows_t, begin, end, partial_rows, merge_index, n])
+            extra_keys.append(int(order_key[t]) + s)
+            extra_kinds.append(int(kind_of[t]))
+            partial_rows += stride
+    keep = splits <= 1
+    all_items = items[keep]
+    all_keys = order_key[keep]
+    all_kinds = kind_of[keep]
+    if extra_rows:
+        all_items = np.concatenate([all_items, np.asarray(extra_rows, np.int64).reshape(-1, ITEM_WIDTH)])
+        all_keys = np.concatenate([all_keys, np.asarray(extra_keys, np.int64)])
+        all_kinds = np.concatenate([all_kinds, np.asarray(extra_kinds, np.int64)])
+
+    plan = AttentionPlan(partial_rows=partial_rows, cluster=cluster)
+    # Kinds appear in the order of their first tile, as the loops would meet them.
+    first_seen = {}
+    for k in kind_of.tolist():
+        first_seen.setdefault(k, len(first_seen))
+    for kind in sorted(first_seen, key=first_seen.get):
+        mine = all_kinds == kind
+        arr = all_items[mine][np.argsort(all_keys[mine], kind="stable")]
+        if len(arr) > 1:
+            # Longest key ranges first: the tail of the grid is then made of short items.
+            arr = arr[np.argsort(-(arr[:, 4] - arr[:, 3]), kind="stable")]
+        plan.items[int(kind)] = arr.astype(np.int32)
+    if merges:
+        plan.merge_items = np.asarray(merges, dtype=np.int32).reshape(-1, ITEM_WIDTH)
+    return plan
+
+
+def plan_attention_plain(
+    q_lens: Sequence[int],
+    kv_lens: Sequence[int],
+    opt: PlanOptions,
+    fixed_splits: Optional[int] = None,
+    fixed_cluster: int = 1,
+) -> AttentionPlan:
+    """Lay out one step, tile by tile.  ``fixed_splits`` forces that many splits for every tile (some may be
+    empty) and ``fixed_cluster`` the cluster size of the narrow kind, which gives a layout whose
     shape depends on the batch size only."""
     tiles: List[Tuple[int, int, int, int, int, int]] = []  # kind, seq, row_begin, row_count, lo, hi
     for seq, (q_len, kv_len) in enumerate(zip(q_lens, kv_lens)):
