@@ -316,7 +316,7 @@ def run_own(args):
             "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
             "head_dim": cfg["hidden_size"] // cfg["num_attention_heads"], "intermediate": cfg["intermediate_size"],
             "vocab": cfg["vocab_size"], "global_batch": args.batch, "seq_len": CONTEXT, "prefill_tokens": PREFILL_TOKENS,
-            "kv_block_size": BLOCK_SIZE, "tied_embeddings": True, "parallelism": "single GPU",
+            "kv_block_size": BLOCK_SIZE, "kv_block_size_reference_default": 16, "tied_embeddings": True, "parallelism": "single GPU",
             "l2": "inputs larger than L2 (weights streamed every step)", "gemm": "decode: own tcgen05 kernels; prefill: cuBLAS (library)",
         },
         "clocks": clock_summary,
