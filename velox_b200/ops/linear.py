@@ -101,10 +101,13 @@ def linear(
     if weight.dtype != torch.bfloat16:
         raise TypeError(f"linear: weights must be float32 or bfloat16, got {weight.dtype}")
     if status is not None and use_tensor_core_kernel(x, weight, num_rows):
-        if accumulate and mirror is not None and bias_f32 is None:
+        if accumulate and mirror is not None:
+            # The kernel writes both where it can (no bias, K split over a cluster); else the
+            # sums are copied, so that a caller who passes a mirror always finds it written.
             splits = choose_splits(weight.shape[0], weight.shape[1])
-            if not kernels.gemm_bf16_add_mirrored(x, weight, out, mirror, num_rows, status, splits):
-                kernels.gemm_bf16(x, weight, None, out, kernels.GEMM_ADD_F32, num_rows, status, splits=splits)
+            if bias_f32 is not None or not kernels.gemm_bf16_add_mirrored(x, weight, out, mirror, num_rows, status,
+                                                                         splits):
+                kernels.gemm_bf16(x, weight, bias_f32, out, kernels.GEMM_ADD_F32, num_rows, status, splits=splits)
                 mirror[:num_rows].copy_(out[:num_rows])
             return out
         if accumulate:
