@@ -411,3 +411,50 @@ def test_planner_with_arrays_equals_the_plain_one():
         # and the public entry picks one of the two
         both = ap.plan_attention(q, kv, opt)
         assert all(np.array_equal(plain.items[kind], both.items[kind]) for kind in plain.items)
+
+
+def test_engine_loop_with_a_fake_model():
+    """``Engine.step`` and ``generate`` around a runner and a sampler that are stand-ins: portions
+    reach the runner in order, the last token of a prompt asks for logits, sampled tokens come
+    back to their requests, stop tokens and lengths end them, and every page returns."""
+    from velox_b200.engine.engine import Engine
+
+    scheduler, cache = make(num_pages=40, page_size=4, max_num_seqs=3, budget=16, chunk=8, max_model_len=64)
+    seen = []
+
+    class FakeRunner:
+        def step(self, chunks):
+            seen.append([(c.seq.seq_id, list(c.tokens), tuple(c.want)) for c in chunks])
+            return [c.seq.seq_id for c in chunks if c.want]
+
+    class FakeTokens:
+        def __init__(self, values):
+            self.values = values
+
+        def tolist(self):
+            return self.values
+
+    class FakeSampler:
+        def sample(self, logits, params, names, draw_indices, slots=None, history_lengths=None):
+            assert logits == names and all(s is not None for s in slots)
+            # request "s" draws its stop token as its second token; the others count upwards
+            return FakeTokens([99 if name == "s" and index == 1 else 10 + index for name, index in zip(names, draw_indices)])
+
+    engine = Engine.__new__(Engine)
+    engine.scheduler, engine.cache, engine.runner, engine.sampler = scheduler, cache, FakeRunner(), FakeSampler()
+    engine.eos_token_ids = frozenset()
+    engine.stats = {name: [] for name in ("scheduler_ms", "prepare_ms", "gpu_ms", "cpu_sync_wait_ms", "sampling_ms", "step_ms")}
+    engine.num_steps, engine._timing = 0, False
+    a = Request("a", list(range(1, 12)), SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True))
+    s = Request("s", [5, 6], SamplingParams(temperature=0.0, max_tokens=9, stop_token_ids=[99]))
+    engine.generate([a, s])
+    assert a.output_token_ids == [10, 11, 12] and a.finish_reason is FinishReason.LENGTH
+    assert s.output_token_ids == [10, 99] and s.finish_reason is FinishReason.STOP
+    # first step: 8 tokens of a (a portion, no logits wanted), the whole of s (logits at its last token)
+    assert seen[0] == [("a", list(range(1, 9)), ()), ("s", [5, 6], (1,))]
+    # second step: prompt portions first, decoded tokens after them
+    assert seen[1] == [("a", [9, 10, 11], (2,)), ("s", [10], (0,))]
+    assert all(len(tokens) == 1 for step in seen[2:] for _, tokens, _ in step)
+    scheduler.schedule()  # the last finished request is reaped at the next schedule()
+    assert cache.num_free_pages() == cache.num_total_pages and cache.num_free_slots == 3
+    assert engine.num_steps == len(seen) and not scheduler.has_work()
