@@ -331,12 +331,167 @@ def run_own(args):
 
 
 def run_reference(args):
-    print(json.dumps({
-        "impl": "reference",
-        "unavailable": "the reference has neither setup.py nor pyproject.toml: pip install of its tree fails "
-                       "('Directory is not installable'), so there is no baseline/_ref to run",
-    }))
+    """The unmodified reference engine from ``baseline/_ref`` (a plain copy of its source tree:
+    it has no packaging, and imports as ``engine`` / ``src`` from its root) on the same random
+    model folder, batch and context, through its own ``Engine.from_pretrained`` and ``step``
+    (engine/engine.py:106-172,276-369 of that project) with its defaults: 16-key pages, CUDA
+    graphs, prefix caching.  Nothing of this package runs on that path except the writer of the
+    random-weights folder."""
+    ref_root = os.environ.get("VELOX_REFERENCE_TREE") or os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isfile(os.path.join(ref_root, "engine", "engine.py")):
+        print(json.dumps({"impl": "reference",
+                          "unavailable": f"no copy of the reference's source tree at {os.path.relpath(ref_root, ROOT)}"}))
+        return 0
+    log_dir = os.path.join(ROOT, "gpurun_out")
+    try:
+        line = _reference_numbers(args, ref_root)
+    except Exception as exc:  # the reference's own code failed here: say why, keep the traceback
+        import traceback
+
+        text = traceback.format_exc()
+        try:
+            os.makedirs(log_dir, exist_ok=True)
+            with open(os.path.join(log_dir, "reference_arm_failure.log"), "w") as handle:
+                handle.write(text)
+        except OSError:
+            pass
+        print(text, file=sys.stderr)
+        reason = f"{type(exc).__name__}: {exc}".replace("\n", " ")[:300]
+        print(json.dumps({"impl": "reference", "unavailable": "the reference's engine failed on this box: " + reason}))
+        return 0
+    print(json.dumps(line))
     return 0
+
+
+def _reference_numbers(args, ref_root):
+    import numpy as np
+    import torch
+
+    from velox_b200.weights import write_random_model
+
+    os.environ.setdefault("HF_HUB_OFFLINE", "1")
+    os.environ.setdefault("TRANSFORMERS_OFFLINE", "1")
+    cfg = dict(MODEL_1P5B, num_hidden_layers=args.layers)
+    folder = tempfile.mkdtemp(prefix="velox_bench_ref_")
+    write_random_model(folder, cfg, seed=0, dtype="bfloat16")
+
+    sys.path.insert(0, ref_root)
+    from engine.config import EngineConfig as RefEngineConfig  # the reference's
+    from engine.engine import Engine as RefEngine
+    from engine.request import Request as RefRequest
+    from engine.utils import SamplingParams as RefSamplingParams
+
+    ref_block = RefEngineConfig().block_size
+    rng = np.random.default_rng(0)
+    vocab = cfg["vocab_size"]
+
+    def build(max_batch):
+        return RefEngine.from_pretrained(RefEngineConfig(
+            model=folder, dtype="bfloat16", device="cuda", max_model_len=CONTEXT + 16, max_num_seqs=max_batch,
+            max_num_batched_tokens=max(PREFILL_TOKENS, max_batch), max_prefill_chunk_size=PREFILL_TOKENS,
+            num_gpu_blocks=max_batch * (CONTEXT // ref_block + 2) + 8, seed=0,
+        ))
+
+    def decode_point(engine, batch, steps, warmup):
+        """``batch`` requests brought to the benchmark's context through the engine's own loop,
+        then ``steps`` decode steps timed on the device (events around ``step``) and ``steps``
+        more by the wall clock."""
+        head_start = 2 * batch
+        budget = 2 * steps + warmup + head_start + 8
+        requests = [RefRequest(request_id=f"ref{batch}_{i}", prompt_token_ids=rng.integers(0, vocab, CONTEXT - budget).tolist(),
+                               sampling_params=RefSamplingParams(temperature=0.0, max_tokens=budget, ignore_eos=True))
+                    for i in range(batch)]
+        for request in requests:
+            engine.add_request(request)
+        guard = 0
+        while any(r.num_output_tokens < 1 or r.num_computed_tokens < r.num_tokens - 1 for r in requests):
+            engine.step()
+            guard += 1
+            if guard > 100 * batch:
+                raise RuntimeError("the reference's engine did not reach pure decoding")
+        for _ in range(warmup):
+            engine.step()
+        times = []
+        for _ in range(steps):
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            before = sum(r.num_output_tokens for r in requests)
+            start.record()
+            engine.step()
+            end.record()
+            torch.cuda.synchronize()
+            if sum(r.num_output_tokens for r in requests) - before != batch:
+                raise RuntimeError("a timed step of the reference was not a pure decode step of the whole batch")
+            times.append(start.elapsed_time(end))
+        torch.cuda.synchronize()
+        before = sum(r.num_output_tokens for r in requests)
+        t_start = time.perf_counter()
+        for _ in range(steps):
+            engine.step()
+        torch.cuda.synchronize()
+        seconds = time.perf_counter() - t_start
+        produced = sum(r.num_output_tokens for r in requests) - before
+        for request in requests:
+            engine.abort_request(request.request_id)
+        engine.step()  # lets the scheduler reap them
+        ms = sum(times) / len(times)
+        return batch * 1000.0 / ms, ms, produced / seconds
+
+    max_batch = max(args.batch, 64 if args.points else args.batch)
+    engine = build(max_batch)
+    import shutil
+
+    shutil.rmtree(folder, ignore_errors=True)
+    clocks = ClockSampler()
+    clocks.start()
+    value, ms_per_step, e2e_value = decode_point(engine, args.batch, args.steps, args.warmup)
+    clock_summary = clocks.stop()
+
+    # Prefill: a 2,048-token prompt in one step, to its first token.
+    prefill_times = []
+    for i in range(3 + 3):
+        request = RefRequest(request_id=f"refprefill{i}", prompt_token_ids=rng.integers(0, vocab, PREFILL_TOKENS).tolist(),
+                             sampling_params=RefSamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True))
+        engine.add_request(request)
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        engine.step()
+        end.record()
+        torch.cuda.synchronize()
+        if request.num_output_tokens != 1:
+            raise RuntimeError("the reference did not prefill the prompt in one step")
+        engine.step()
+        if i >= 3:
+            prefill_times.append(start.elapsed_time(end))
+    prefill_ms = sum(prefill_times) / len(prefill_times)
+
+    points = {}
+    if args.points:
+        for batch in (1, 64):
+            tok_s, _, _ = decode_point(engine, batch, max(8, args.steps // 2), 3)
+            points[f"decode_b{batch}"] = round(tok_s, 1)
+
+    return {
+        "impl": "reference",
+        "metric": "decode tok/s at batch 1/8/64; prefill tok/s at 2,048 tokens (Qwen2.5-1.5B)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": round(value / 226.0, 2), "dtype": "bf16",
+        "data": "synthetic: seeded random weights, uniform-random token ids",
+        "config": {
+            "model": "Qwen2.5-1.5B layer sizes", "layers": args.layers, "layers_full_model": FULL_LAYERS,
+            "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+            "head_dim": cfg["hidden_size"] // cfg["num_attention_heads"], "intermediate": cfg["intermediate_size"],
+            "vocab": cfg["vocab_size"], "global_batch": args.batch, "seq_len": CONTEXT, "prefill_tokens": PREFILL_TOKENS,
+            "kv_block_size": ref_block, "tied_embeddings": True, "parallelism": "single GPU",
+            "timing": "CUDA events around each Engine.step of the reference (its host work included)",
+        },
+        "clocks": clock_summary,
+        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s"},
+        "prefill": {"value": round(PREFILL_TOKENS * 1000.0 / prefill_ms, 1), "tokens": PREFILL_TOKENS, "ms": round(prefill_ms, 3)},
+        "points": points,
+    }
 
 
 def main():

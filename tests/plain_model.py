@@ -66,8 +66,8 @@ def causal_attention(
     k = k.repeat_interleave(group, dim=1)
     v = v.repeat_interleave(group, dim=1)
     scores = torch.einsum("thd,shd->hts", q, k) * scale
-    query_pos = torch.arange(T).unsqueeze(1)
-    key_pos = torch.arange(T).unsqueeze(0)
+    query_pos = torch.arange(T, device=q.device).unsqueeze(1)
+    key_pos = torch.arange(T, device=q.device).unsqueeze(0)
     hidden = key_pos > query_pos
     if window is not None:
         hidden = hidden | (key_pos <= query_pos - window)
@@ -150,7 +150,8 @@ def forward_hidden(
 ) -> torch.Tensor:
     """Embedding, every layer in order, final norm (src/transformer.py:43-52)."""
     weights: Dict[str, torch.Tensor] = {name: t.to(dtype) for name, t in tensors.items()}
-    ids = torch.as_tensor(list(token_ids), dtype=torch.long)
+    device = next(iter(weights.values())).device
+    ids = torch.as_tensor(list(token_ids), dtype=torch.long, device=device)
     heads = int(cfg["num_attention_heads"])
     head_dim = int(cfg.get("head_dim") or int(cfg["hidden_size"]) // heads)
     scaling = cfg.get("rope_scaling") or {}
@@ -158,7 +159,7 @@ def forward_hidden(
     if (scaling.get("type") or scaling.get("rope_type")) == "linear":
         factor = float(scaling.get("factor", 1.0))
     angles = rope_angles(head_dim, float(cfg.get("rope_theta", 10000.0)), factor, torch.arange(len(ids)))
-    cos, sin = angles.cos().to(dtype), angles.sin().to(dtype)
+    cos, sin = angles.cos().to(dtype).to(device), angles.sin().to(dtype).to(device)
 
     h = weights["model.embed_tokens.weight"][ids]
     for layer in range(int(cfg["num_hidden_layers"])):
@@ -171,10 +172,13 @@ def forward_logits(
     cfg: Mapping[str, object],
     token_ids: Sequence[int],
     dtype: torch.dtype = torch.float32,
+    rows: Optional[Sequence[int]] = None,
 ) -> torch.Tensor:
-    """Logits at every position: ``hidden @ lm_head.T``; the head is the embedding when
-    ``tie_word_embeddings`` is set (src/transformer.py:60-68)."""
+    """Logits at every position (or at ``rows`` only): ``hidden @ lm_head.T``; the head is the
+    embedding when ``tie_word_embeddings`` is set (src/transformer.py:60-68)."""
     hidden = forward_hidden(tensors, cfg, token_ids, dtype)
+    if rows is not None:
+        hidden = hidden[torch.as_tensor(list(rows), dtype=torch.long, device=hidden.device)]
     if cfg.get("tie_word_embeddings", False):
         head = tensors["model.embed_tokens.weight"]
     else:

@@ -59,7 +59,7 @@ def test_tables_grow_by_pages_and_slots_address_tokens():
 
 def test_max_model_len_is_clamped_to_the_pool():
     manager = CacheManager([CacheGroup("all")], num_pages=24, page_size=8, max_model_len=4096)
-    assert manager.max_model_len == 192 and manager.max_blocks_per_seq == 24
+    assert manager.max_model_len == 184 and manager.max_blocks_per_seq == 23
 
 
 def test_append_is_all_groups_or_none():

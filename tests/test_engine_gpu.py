@@ -14,7 +14,8 @@ pytestmark = pytest.mark.gpu
 @pytest.fixture(scope="module")
 def folders(tmp_path_factory):
     out = {}
-    for name, cfg in (("tiny_a", tiny_configs.TINY_A), ("tiny_b", tiny_configs.TINY_B), ("tiny_w", tiny_configs.TINY_W)):
+    for name, cfg in (("tiny_a", tiny_configs.TINY_A), ("tiny_b", tiny_configs.TINY_B), ("tiny_w", tiny_configs.TINY_W),
+                      ("tiny_d", tiny_configs.TINY_D)):
         folder = str(tmp_path_factory.mktemp(name))
         write_model(folder, cfg, seed=31, dtype="bfloat16")
         out[name] = (folder, cfg, read_tensors(folder))
@@ -75,6 +76,104 @@ def test_greedy_generation_bfloat16_tracks_plain(folders):
         for row, token in zip(rows, request.output_token_ids):
             # the chosen token is the plain argmax, or within bfloat16 noise of it
             assert row[token] >= row.max() - 3e-2 * row.abs().max()
+
+
+def within_bfloat16_noise_of_plain_argmax(tensors, cfg, request):
+    """Every generated token, given the tokens before it, is the plain argmax or within
+    bfloat16 noise of it."""
+    full = request.all_token_ids
+    logits = plain_model.forward_logits(tensors, cfg, full[:-1], dtype=torch.float64)
+    rows = logits[request.num_prompt_tokens - 1 :]
+    assert len(rows) == len(request.output_token_ids)
+    for index, (row, token) in enumerate(zip(rows, request.output_token_ids)):
+        assert row[token] >= row.max() - 3e-2 * row.abs().max(), (request.request_id, index)
+
+
+@pytest.mark.parametrize("case,page,pages,lengths,tokens", [
+    # Heads of 128 dims: the fused projection / rotation / cache write, the norm inside the
+    # projections, the one-kernel feed-forward, clusters in captured graphs.  64-key pages;
+    # every request ends with about 230 tokens = 4 pages, and 11 usable pages cannot hold four.
+    ("tiny_d", 64, 12, (150, 130, 171, 140), 70),
+    ("tiny_b", 8, 41, (60, 56, 52, 66), 80),
+])
+def test_bfloat16_preemption_with_graphs(folders, case, page, pages, lengths, tokens):
+    folder, cfg, tensors = folders[case]
+    prompts = random_prompts(cfg["vocab_size"], lengths, seed=12)
+    longest = max(lengths) + tokens
+    engine = build_engine(folder, "bfloat16", block_size=page, num_gpu_blocks=pages, max_model_len=-(-longest // page) * page,
+                          max_num_batched_tokens=128, max_prefill_chunk_size=64, enable_cuda_graphs=True)
+    assert engine.runner.enable_graphs
+    requests = make_requests(prompts, temperature=0.0, max_tokens=tokens)
+    engine.generate(requests)
+    assert engine.scheduler.num_preemptions > 0
+    assert engine.runner._graphs and not engine.runner._graphs_broken and engine.runner.kernels_replayed > 0
+    for request in requests:
+        assert len(request.output_token_ids) == tokens and request.finish_reason.value == "length"
+        within_bfloat16_noise_of_plain_argmax(tensors, cfg, request)
+    engine.scheduler.schedule()
+    engine.cache.assert_consistent()
+    assert engine.cache.num_free_pages() == engine.cache.num_total_pages
+    assert engine.cache.num_free_slots == engine.config.max_num_seqs
+    engine.runner.check_status()
+
+
+def test_bfloat16_seeded_temperature_workload(folders):
+    """Prompts of 1, 9, 33 and 70 tokens, portions of 16 mixed with decoding, 12 tokens at
+    temperature 0.8 under fixed seeds: the same tokens on a second run, and for each request
+    alone as in the batch (its draws depend on its seed and token index only; its logits on
+    the batch only within bfloat16 rounding)."""
+    folder, cfg, _ = folders["tiny_b"]
+    prompts = random_prompts(cfg["vocab_size"], (1, 9, 33, 70), seed=5)
+    from velox_b200.engine.request import Request
+    from velox_b200.sampling.params import SamplingParams
+
+    def run(engine, subset):
+        requests = [
+            Request(f"s{i}", prompts[i], SamplingParams(temperature=0.8, seed=7 + i, max_tokens=12, ignore_eos=True))
+            for i in subset
+        ]
+        engine.generate(requests)
+        return {i: r.output_token_ids for i, r in zip(subset, requests)}
+
+    engine = build_engine(folder, "bfloat16", block_size=8, max_model_len=192, max_prefill_chunk_size=16)
+    together = run(engine, [0, 1, 2, 3])
+    assert all(len(v) == 12 for v in together.values())
+    # Three of four, not four: the one-kernel feed-forward of small steps adds its shares in no
+    # fixed order, so the last bit of a bfloat16 logit can differ between runs, and a draw
+    # whose two best scores sit within that bit may then fall the other way.
+    again = run(engine, [0, 1, 2, 3])
+    assert sum(again[i] == together[i] for i in range(4)) >= 3, "a second run drew different tokens"
+    agree = sum(run(engine, [i])[i] == together[i] for i in range(4))
+    assert agree >= 3, "alone and in the batch, seeded requests drew different tokens"
+
+
+def test_bfloat16_generation_at_head_size_128(folders):
+    folder, cfg, tensors = folders["tiny_d"]
+    engine = build_engine(folder, "bfloat16", block_size=64, num_gpu_blocks=40, max_model_len=512,
+                          max_num_batched_tokens=256, max_prefill_chunk_size=128)
+    prompts = random_prompts(cfg["vocab_size"], (3, 70, 129, 300), seed=13)
+    requests = make_requests(prompts, temperature=0.0, max_tokens=24)
+    engine.generate(requests)
+    for request in requests:
+        within_bfloat16_noise_of_plain_argmax(tensors, cfg, request)
+    assert engine.runner.kernels_replayed > 0
+
+
+def test_status_word_reaches_generation(folders):
+    """A kernel that refuses an access only sets a bit; generation reads the word with the
+    sampled tokens and stops instead of going on with tokens that mean nothing."""
+    folder, cfg, _ = folders["tiny_a"]
+    engine = build_engine(folder, "float32")
+    request = make_requests([[3, 4, 5]], temperature=0.0, max_tokens=4)[0]
+    engine.add_request(request)
+    engine.step()
+    assert len(request.output_token_ids) == 1
+    engine.runner.status[0] = 4  # as a kernel would have left it
+    with pytest.raises(RuntimeError, match="a cache slot outside the pool"):
+        engine.step()
+    assert int(engine.runner.status[0].item()) == 0
+    engine.step()
+    assert len(request.output_token_ids) == 2
 
 
 def test_batched_equals_one_at_a_time(folders):

@@ -891,3 +891,28 @@ def test_gemm_bf16_qkv_rotates_and_writes_the_cache(k, status, T, H, G, K, norme
         assert (kc[slot] - want_k[t]).abs().max().item() <= 1e-2 * scale
         assert (vc[slot] - want_v[t]).abs().max().item() <= 1e-2 * scale
     assert torch.all(kc[~written] == 7.0) and torch.all(vc[~written] == 7.0)
+
+
+def test_bounded_wait_runs_out_and_reports(k, tmp_path):
+    """A wait on a barrier that nobody arrives at: the kernel returns by itself after its limit
+    (a few milliseconds here, about two seconds in the engine's kernels), the status word gets
+    its bit, and the runner turns the word into an error that names the wait."""
+    import time
+
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    start = time.perf_counter()
+    assert k.selftest_bounded_wait(status, 5_000_000) == 1  # about 3 ms of SM clock
+    assert time.perf_counter() - start < 1.0
+    assert int(status[0].item()) == 16
+    # the context is still good: another kernel runs and gives the right answer
+    x = torch.arange(8, dtype=torch.float32, device="cuda")
+    assert float((x * 2).sum()) == 56.0
+
+    from velox_b200.engine.runner import ModelRunner
+
+    runner = ModelRunner.__new__(ModelRunner)
+    runner.status = status
+    with pytest.raises(RuntimeError, match="a bounded wait ran out"):
+        runner.check_status()
+    assert int(status[0].item()) == 0

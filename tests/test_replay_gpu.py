@@ -13,7 +13,7 @@ import torch
 
 import plain_model
 import tiny_configs
-from helpers import random_prompts, read_tensors, write_model
+from helpers import check_logits, random_prompts, read_tensors, write_model
 
 pytestmark = pytest.mark.gpu
 
@@ -27,13 +27,6 @@ CASES = {
     "tiny_c": (tiny_configs.TINY_C, 16, (77, 2, 35, 200, 129)),
     "tiny_d": (tiny_configs.TINY_D, 64, (130, 3, 65, 300, 64)),
 }
-
-
-def tolerance(dtype: str, scale: float) -> float:
-    """float32: both sides round differently in sums of a few hundred terms.  bfloat16:
-    activations are rounded to 8 bits of mantissa about six times per layer; over a few layers
-    that is about 1e-2 of the activations' scale (3 sigma: 3e-2)."""
-    return (2e-5 if dtype == "float32" else 3e-2) * max(scale, 1e-3)
 
 
 @pytest.fixture(scope="module")
@@ -57,14 +50,7 @@ def make_replayer(folder, dtype, max_tokens, page, **kw):
 
 
 def check(got_rows, want_rows, dtype, what):
-    got = torch.from_numpy(np.asarray(got_rows)).double()
-    want = want_rows.double()
-    assert got.shape == want.shape, (what, got.shape, want.shape)
-    scale = want.abs().max().item()
-    err = (got - want).abs().max().item()
-    assert err <= tolerance(dtype, scale), f"{what}: max abs error {err:.3e}, logit scale {scale:.3e}"
-    if dtype == "float32":
-        assert torch.equal(got.argmax(-1), want.argmax(-1)), what
+    check_logits(got_rows, want_rows, dtype, what)
 
 
 def replay_one(replayer, name, tokens, cuts):

@@ -24,6 +24,11 @@ def request(name, prompt_len, max_tokens=8):
 def fake_step(scheduler, cache, output, token=7):
     """What the engine does after a forward, without a model."""
     for r in output.scheduled:
+        # Whoever runs in a step holds a slot and pages for all of its tokens, and is not queued
+        # (a request preempted and admitted again in the same step is running again).
+        assert r.cache.slot is not None and r not in scheduler.waiting
+        assert r.current_chunk_size > 0
+        assert r.cache.num_logical_blocks * cache.page_size >= r.num_computed_tokens + r.current_chunk_size
         completes = r.num_computed_tokens + r.current_chunk_size >= len(r.all_token_ids)
         cache.advance(r.cache, r.current_chunk_size)
         r.refresh_status()
@@ -212,6 +217,45 @@ def test_oldest_running_prefill_may_preempt_younger_ones():
         cache.assert_consistent()
     assert a.finished and b.finished
     assert preemptions and set(preemptions) == {"b"}
+
+
+def test_a_prefill_that_takes_pages_from_a_request_already_in_the_step():
+    # a: an old long prompt; b: a younger request that is decoding.  When a's next portion needs
+    # pages, b (the newest) is preempted although this step had already given it its token.
+    scheduler, cache = make(num_pages=9, page_size=4, budget=16, chunk=8, max_model_len=32)
+    a, b = request("a", 28, 2), request("b", 3, 20)
+    scheduler.add_request(a)
+    scheduler.add_request(b)
+    both = []
+    for _ in range(200):
+        if not scheduler.has_work():
+            break
+        out = scheduler.schedule()
+        both.extend(r.request_id for r in out.scheduled if r in scheduler.waiting or not r.cache.tables[0])
+        assert out.num_batched_tokens == sum(r.current_chunk_size for r in out.scheduled)
+        for r in scheduler.waiting:
+            assert r.num_computed_tokens == 0 and r.cache.slot is None and r.current_chunk_size == 0
+            assert r.status in (RequestStatus.WAITING, RequestStatus.PREEMPTED)
+        fake_step(scheduler, cache, out)
+        cache.assert_consistent()
+    assert not both
+    assert a.finished and b.finished and b.num_preemptions >= 1
+    assert len(a.output_token_ids) == 2 and len(b.output_token_ids) == 20
+    scheduler.schedule()
+    assert cache.num_free_pages() == cache.num_total_pages and cache.num_free_slots == 4
+
+
+def test_capacity_does_not_count_the_reserved_page():
+    # 5 pages of 4: four can be handed out, so 16 tokens is the most one request can ever hold.
+    scheduler, cache = make(num_pages=5, page_size=4, budget=64, chunk=64, max_model_len=64)
+    assert cache.max_model_len == 16 and scheduler.config.max_model_len == 16
+    with pytest.raises(ValueError, match="exceeds"):
+        scheduler.add_request(request("never", 15, 2))
+    fits = request("fits", 14, 2)
+    scheduler.add_request(fits)
+    history = run_all(scheduler, cache, limit=50)
+    assert fits.finished and len(fits.output_token_ids) == 2 and len(history) < 50
+    assert fits.num_preemptions == 0
 
 
 def test_limits_and_abort():
@@ -435,8 +479,8 @@ def test_engine_loop_with_a_fake_model():
             return self.values
 
     class FakeSampler:
-        def sample(self, logits, params, names, draw_indices, slots=None, history_lengths=None):
-            assert logits == names and all(s is not None for s in slots)
+        def sample(self, logits, params, names, draw_indices, slots=None, history_lengths=None, status=None):
+            assert status is None and logits == names and all(s is not None for s in slots)
             # request "s" draws its stop token as its second token; the others count upwards
             return FakeTokens([99 if name == "s" and index == 1 else 10 + index for name, index in zip(names, draw_indices)])
 
@@ -458,3 +502,52 @@ def test_engine_loop_with_a_fake_model():
     scheduler.schedule()  # the last finished request is reaped at the next schedule()
     assert cache.num_free_pages() == cache.num_total_pages and cache.num_free_slots == 3
     assert engine.num_steps == len(seen) and not scheduler.has_work()
+
+
+def test_engine_step_raises_when_the_status_word_comes_back_set():
+    """The device status word rides behind the sampled tokens; a non-zero word stops the step
+    before any token reaches a request, and the word is cleared."""
+    from velox_b200.engine.engine import Engine
+
+    scheduler, cache = make(num_pages=40, page_size=4, max_num_seqs=3, budget=16, chunk=8, max_model_len=64)
+
+    class FakeTokens:
+        def __init__(self, values):
+            self.values = values
+
+        def tolist(self):
+            return list(self.values)
+
+    class FakeRunner:
+        status = "the-device-word"
+        word = 0
+        cleared = 0
+
+        def step(self, chunks):
+            return [c.seq.seq_id for c in chunks if c.want]
+
+        def raise_for_status(self, word):
+            FakeRunner.cleared += 1
+            FakeRunner.word = 0
+            raise RuntimeError(f"a kernel of the step refused an access: word {word}")
+
+    class FakeSampler:
+        def sample(self, logits, params, names, draw_indices, slots=None, history_lengths=None, status=None):
+            assert status == "the-device-word"
+            return FakeTokens([11] * len(names) + [FakeRunner.word])
+
+    engine = Engine.__new__(Engine)
+    engine.scheduler, engine.cache, engine.runner, engine.sampler = scheduler, cache, FakeRunner(), FakeSampler()
+    engine.eos_token_ids = frozenset()
+    engine.stats = {name: [] for name in ("scheduler_ms", "prepare_ms", "gpu_ms", "cpu_sync_wait_ms", "sampling_ms", "step_ms")}
+    engine.num_steps, engine._timing = 0, False
+    a = Request("a", [1, 2, 3], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+    engine.add_request(a)
+    engine.step()
+    assert a.output_token_ids == [11]
+    FakeRunner.word = 4 | 16
+    with pytest.raises(RuntimeError, match="word 20"):
+        engine.step()
+    assert a.output_token_ids == [11] and FakeRunner.cleared == 1
+    engine.step()
+    assert a.output_token_ids == [11, 11]

@@ -31,7 +31,24 @@ def _static_entry(head_dim):
     return kernels, fn
 
 
-def _decode_case(H, G, D, P, contexts, seed):
+def _plain(case, qkv):
+    """The same attention in float64, sequence by sequence, from the cache's pages."""
+    from test_kernels_gpu import plain_paged_attention
+
+    H, G, D, P = case["H"], case["G"], case["D"], case["P"]
+    k_flat = case["k_cache"].cpu().view(-1, G, D)
+    v_flat = case["v_cache"].cpu().view(-1, G, D)
+    tables = case["tables"].cpu()
+    rows = []
+    for s, kv_len in enumerate(case["kv_len"].cpu().tolist()):
+        slots = [int(tables[s, i // P]) * P + i % P for i in range(kv_len)]
+        q = qkv[s : s + 1, : H * D].cpu().view(1, H, D).double()
+        rows.append(plain_paged_attention(q, k_flat[slots].double(), v_flat[slots].double(), kv_len - 1,
+                                          1 / math.sqrt(D), None))
+    return torch.cat(rows).view(len(rows), H * D)
+
+
+def _decode_case(H, G, D, P, contexts, seed, split=True):
     """Single decoded tokens over contexts of the given lengths, pages in shuffled order."""
     from velox_b200.ops import attention_plan as ap
 
@@ -46,15 +63,16 @@ def _decode_case(H, G, D, P, contexts, seed):
     plan = ap.plan_attention(
         [1] * len(contexts), kv_lens,
         ap.PlanOptions(num_kv_heads=G, group=H // G, window=None, use_f32=False,
-                       min_split_keys=64, target_ctas=10_000),
+                       min_split_keys=64, target_ctas=10_000 if split else 1),
     )
-    assert set(plan.items) == {ap.KIND_BF16_NARROW} and len(plan.merge_items) > 0
+    assert set(plan.items) == {ap.KIND_BF16_NARROW} and (len(plan.merge_items) > 0) == split
     dev = lambda x: torch.as_tensor(x, dtype=torch.int32).cuda()
     return dict(
         k_cache=torch.randn(total_pages, P, G, D, generator=gen).bfloat16().cuda(),
         v_cache=torch.randn(total_pages, P, G, D, generator=gen).bfloat16().cuda(),
         tables=tables.cuda(), q_start=dev(list(range(len(contexts)))), q_len=dev([1] * len(contexts)),
-        kv_len=dev(kv_lens), items=dev(plan.items[ap.KIND_BF16_NARROW]), merges=dev(plan.merge_items),
+        kv_len=dev(kv_lens), items=dev(plan.items[ap.KIND_BF16_NARROW]),
+        merges=dev(plan.merge_items) if split else torch.zeros(1, 8, dtype=torch.int32, device="cuda"),
         plan=plan, gen=gen, H=H, G=G, D=D, P=P, T=len(contexts),
     )
 
@@ -85,7 +103,7 @@ def _static(fn, case, qkv, status, partial_rows=None):
     free_before = torch.cuda.mem_get_info()[0]
     code = fn(ptr(qkv), ptr(out), ptr(case["k_cache"]), ptr(case["v_cache"]), ptr(case["tables"]),
               ptr(case["q_start"]), ptr(case["q_len"]), ptr(case["kv_len"]), ptr(case["items"]),
-              len(case["items"]), ptr(case["merges"]), len(case["merges"]),
+              len(case["items"]), ptr(case["merges"]), len(case["plan"].merge_items),
               case["plan"].partial_rows if partial_rows is None else partial_rows, ptr(status),
               qkv.shape[1], out.shape[1], case["tables"].shape[1], G, H // G, case["P"],
               case["k_cache"].shape[0], 0, 1 / math.sqrt(D),
@@ -112,7 +130,43 @@ def test_static_scratch_entry_matches_the_ordinary_launcher(H, G, D, P):
         err = (got.double() - want).abs().max().item()
         assert err <= tol * want.abs().max().item(), (call, err)
         assert want.abs().max().item() > 0.1
+        # and against the plain statement of the operation, not only another path of the engine
+        plain = _plain(case, qkv)
+        err = (got.double().cpu() - plain).abs().max().item()
+        assert err <= tol * plain.abs().max().item(), (call, err)
     assert int(status.item()) == 0
+
+
+def test_static_scratch_entry_without_split_key_ranges():
+    """Contexts so short that no key range is split: no merge items, no partial rows."""
+    kernels, fn = _static_entry(128)
+    case = _decode_case(12, 2, 128, 16, contexts=[40, 7, 100, 63], seed=9, split=False)
+    assert case["plan"].partial_rows == 0
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    qkv = torch.randn(case["T"], 16 * 128, generator=case["gen"]).bfloat16().cuda()
+    code, message, got, _ = _static(fn, case, qkv, status)
+    assert code == 0, message
+    plain = _plain(case, qkv)
+    err = (got.double().cpu() - plain).abs().max().item()
+    assert err <= 2.5e-2 * plain.abs().max().item()
+    assert int(status.item()) == 0
+
+
+def test_static_scratch_entry_flags_rows_beyond_its_scratch():
+    """A caller that under-reports its partial rows: the kernel writes nothing beyond the
+    array and says so in the status word."""
+    kernels, fn = _static_entry(128)
+    case = _decode_case(12, 2, 128, 16, contexts=[600, 300], seed=5)
+    items = case["items"].clone()
+    split = items[:, 5] >= 0
+    assert bool(split.any())
+    items[:, 5] = torch.where(split, items[:, 5] + MAX_PARTIAL_ROWS, items[:, 5])  # every partial row lies beyond
+    case = dict(case, items=items)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    qkv = torch.randn(case["T"], 16 * 128, generator=case["gen"]).bfloat16().cuda()
+    code, message, _, _ = _static(fn, case, qkv, status)
+    assert code == 0, message
+    assert int(status.item()) & 32
 
 
 def test_static_scratch_entry_refuses_what_does_not_fit():

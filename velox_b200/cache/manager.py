@@ -69,9 +69,11 @@ class CacheManager:
         self.num_pages = num_pages
         self.allocators: List[PageAllocator] = [PageAllocator(num_pages) for _ in self.groups]
 
-        # A pool of N pages can hold at most N * page_size tokens of one request, the reserved
-        # page included, as the reference counts it (src/block_manager.py:22-24).
-        capacity = num_pages * page_size
+        # A pool of N pages hands out N - 1 of them (page 0 is reserved), so one request can
+        # never hold more than (N - 1) * page_size tokens.  The reference counts the reserved
+        # page in (src/block_manager.py:22-24) and with that admits a request that can never
+        # fit and preempts itself for ever.
+        capacity = max(num_pages - 1, 0) * page_size
         self.max_model_len = min(max_model_len, capacity) if max_model_len else capacity
         self.max_blocks_per_seq = -(-self.max_model_len // page_size)
 

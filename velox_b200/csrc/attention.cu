@@ -77,6 +77,9 @@ struct AttnArgs {
   int* status;              // device status word (bounded waits report here)
   float* partial_o;         // [rows, D]
   float* partial_lse;       // [rows], log2 units
+  // Rows that partial_o / partial_lse hold when the launcher knows it (the scratch inside the
+  // library); a split item whose rows would lie beyond is skipped and flagged.  0: not checked.
+  int partial_capacity;
   // Fused merge (bf16 families): when a split item is done it bumps the counter of its
   // (merge item, KV head); the CTA that brings it to the number of splits merges them all.
   const int* merge_items;   // [m, 8] or null
@@ -1559,10 +1562,15 @@ __global__ void __launch_bounds__(NARROW_THREADS) attn_narrow_kernel(const __gri
         *reinterpret_cast<__nv_bfloat162*>(dst + 16 * i) = __floats2bfloat162_rn(val[i].x, val[i].y);
     } else {
       const size_t prow = (size_t)partial_base + (size_t)kvh * row_count + r;
-      float* dst = a.partial_o + prow * D + 2 * seg;
+      if (a.partial_capacity > 0 && prow >= (size_t)a.partial_capacity) {
+        // The caller's count of partial rows was too small for its items: write nothing there.
+        if (seg == 0) atomicOr(a.status, VX_STATUS_BAD_PARTIAL_ROW);
+      } else {
+        float* dst = a.partial_o + prow * D + 2 * seg;
 #pragma unroll
-      for (int i = 0; i < D / 16; ++i) *reinterpret_cast<float2*>(dst + 16 * i) = val[i];
-      if (seg == 0) a.partial_lse[prow] = lse;
+        for (int i = 0; i < D / 16; ++i) *reinterpret_cast<float2*>(dst + 16 * i) = val[i];
+        if (seg == 0) a.partial_lse[prow] = lse;
+      }
     }
   }
   if (fused_merge)
@@ -2046,6 +2054,7 @@ static AttnArgs make_args(const void* q, void* out, const void* k_cache, const v
   a.status = status;
   a.partial_o = partial_o;
   a.partial_lse = partial_lse;
+  a.partial_capacity = 0;
   a.merge_items = merge_items;
   a.split_counters = split_counters;
   a.q_stride = q_stride;
@@ -2377,6 +2386,9 @@ int vx_attention_decode_static(const void* q, void* out, const void* k_cache, co
                          status, partial_o, partial_lse, merge_items,
                          num_merges > 0 ? split_counters : nullptr, q_stride, out_stride,
                          table_stride, num_kv_heads, group, page_size, window, softmax_scale);
+  // The items live on the device and are not read here, so partial_rows is the caller's word;
+  // the kernel holds every partial row against the array's real size.
+  a.partial_capacity = VX_ATTENTION_STATIC_MAX_PARTIAL_ROWS;
   if (TMA_KV) {
     const int box_rows = page_size < B_BN ? page_size : B_BN;
     const long long tokens = num_pages * page_size;

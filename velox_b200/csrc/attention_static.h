@@ -54,7 +54,12 @@ extern "C" {
  * num_kv_heads, head size] bfloat16; block_tables [sequences, table_stride]; q_start, q_len,
  * kv_len one int per sequence; items [num_items, 8]; merge_items [num_merges, 8] (may be null
  * when num_merges is 0); partial_rows: the rows the items' partial_base fields span (0 if no
- * item is split); status: one int on the device that collects the kernels' error bits.
+ * item is split).  The items stay on the device and are not read by this function, so
+ * partial_rows is taken on the caller's word for the size check; should an item all the same
+ * name a row beyond VX_ATTENTION_STATIC_MAX_PARTIAL_ROWS, the kernel writes nothing for it and
+ * sets bit 32 of *status.  The items must come from a plan made for the same num_kv_heads and
+ * group (row = partial_base + kv_head * row_count + r).  status: one int on the device that
+ * collects the kernels' error bits.
  * error (may be null) receives a zero-terminated message of at most error_capacity bytes
  * when the return value is not 0. */
 __attribute__((visibility("default"))) int vx_attention_decode_static(

@@ -22,6 +22,7 @@
 #define VX_STATUS_BAD_SLOT 4
 #define VX_STATUS_BAD_PAGE 8
 #define VX_STATUS_WAIT_TIMEOUT 16
+#define VX_STATUS_BAD_PARTIAL_ROW 32
 
 #define VX_API extern "C" __attribute__((visibility("default")))
 
@@ -106,17 +107,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait.  Returns false (and records it) if the barrier did not flip in time.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status) {
+// Bounded wait.  Returns false (and records it) if the barrier did not flip within `limit`
+// cycles of the SM's clock.
+__device__ __forceinline__ bool mbar_wait_limited(uint32_t bar, uint32_t parity, int* status,
+                                                  unsigned long long limit) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long start = clock64();
   while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - start > VX_WAIT_CYCLES) {
+    if (clock64() - start > limit) {
       atomicOr(status, VX_STATUS_WAIT_TIMEOUT);
       return false;
     }
   }
   return true;
+}
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status) {
+  return mbar_wait_limited(bar, parity, status, VX_WAIT_CYCLES);
 }
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {

@@ -378,6 +378,23 @@ __global__ void cast_bf16_to_f32_kernel(const __nv_bfloat16* __restrict__ in,
     out[idx] = __bfloat162float(in[idx]);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Self-test of the bounded wait: one CTA arms a barrier that nobody will ever arrive at and
+// waits for it through the helper every kernel of this package waits with, with a short limit.
+// The wait has to run out, set VX_STATUS_WAIT_TIMEOUT and let the kernel return normally.
+// ---------------------------------------------------------------------------------------------
+__global__ void bounded_wait_selftest_kernel(int* status, unsigned long long limit_cycles, int* returned) {
+  __shared__ __align__(8) uint64_t never;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&never), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  const bool flipped = mbar_wait_limited(smem_u32(&never), 0u, status, limit_cycles);
+  __syncthreads();
+  if (threadIdx.x == 0) *returned = flipped ? 2 : 1;
+}
+
 }  // namespace vx
 
 // =============================================================================================
@@ -600,5 +617,16 @@ VX_API int vx_cast_bf16_to_f32(const void* in, float* out, long long total, cuda
   long long blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   launch_pdl(cast_bf16_to_f32_kernel, dim3((int)blocks), dim3(256), 0, stream, (const __nv_bfloat16*)in, out, total);
+  return (int)cudaGetLastError();
+}
+
+// Test entry: see bounded_wait_selftest_kernel.  `returned` (one int on the device) becomes 1
+// when the wait gave up as it must, 2 if the barrier flipped.  limit_cycles is capped at the
+// limit of the ordinary waits.
+VX_API int vx_selftest_bounded_wait(int* status, long long limit_cycles, int* returned, cudaStream_t stream) {
+  if (status == nullptr || returned == nullptr || limit_cycles <= 0) return (int)cudaErrorInvalidValue;
+  unsigned long long limit = (unsigned long long)limit_cycles;
+  if (limit > VX_WAIT_CYCLES) limit = VX_WAIT_CYCLES;
+  bounded_wait_selftest_kernel<<<1, 64, 0, stream>>>(status, limit, returned);
   return (int)cudaGetLastError();
 }

@@ -118,7 +118,8 @@ sample_kernel(const float* __restrict__ logits, int vocab, long long row_stride,
               const int* __restrict__ draw_index, const float* __restrict__ threshold,
               int* __restrict__ out, int* __restrict__ history, long long history_stride,
               const int* __restrict__ history_slots, const int* __restrict__ history_lengths,
-              int segment_len, Best* __restrict__ partial, unsigned int* __restrict__ counters) {
+              int segment_len, Best* __restrict__ partial, unsigned int* __restrict__ counters,
+              const int* __restrict__ status_word) {
   __shared__ Best scratch[32];
   __shared__ bool is_last;
   allow_dependents();
@@ -205,6 +206,9 @@ sample_kernel(const float* __restrict__ logits, int vocab, long long row_stride,
   if (threadIdx.x == 0) {
     const int token = best.index < 0 ? 0 : best.index;
     out[r] = token;
+    // The device status word rides behind the tokens, so the host's one read-back of the step
+    // also tells it whether a kernel of the step refused an access or gave up a wait.
+    if (status_word != nullptr && r == 0) out[gridDim.x] = *reinterpret_cast<const volatile int*>(status_word);
     // Append to the request's token history (kept for the penalties) when there is one.
     if (history != nullptr) {
       const int n = history_lengths[r];
@@ -454,7 +458,7 @@ VX_API int vx_sample(const float* logits, int num_rows, int vocab, long long row
                      const int* draw_index, const float* threshold, int* out, int* history,
                      long long history_stride, const int* history_slots,
                      const int* history_lengths, void* partial, unsigned int* counters,
-                     cudaStream_t stream) {
+                     const int* status_word, cudaStream_t stream) {
   if (num_rows <= 0) return 0;
   int segments = vx_sample_segments(num_rows, vocab);
   if (partial == nullptr || counters == nullptr) segments = 1;
@@ -463,7 +467,7 @@ VX_API int vx_sample(const float* logits, int num_rows, int vocab, long long row
   segments = (vocab + segment_len - 1) / segment_len;
   launch_pdl(sample_kernel, dim3(num_rows, segments), dim3(SAMPLE_THREADS), 0, stream, logits, vocab,
              row_stride, temperature, seeds, draw_index, threshold, out, history, history_stride,
-             history_slots, history_lengths, segment_len, (Best*)partial, counters);
+             history_slots, history_lengths, segment_len, (Best*)partial, counters, status_word);
   return (int)cudaGetLastError();
 }
 

@@ -39,10 +39,6 @@ from .scheduler import Scheduler
 
 logger = logging.getLogger(__name__)
 
-# What the reference falls back to when a model folder names no end-of-sequence ids
-# (engine/engine.py:23).
-DEFAULT_EOS_TOKEN_IDS = frozenset({151643, 151645})
-
 
 def load_model(model_dir: str, dtype: torch.dtype, device: torch.device, max_position: Optional[int] = None):
     """Model folder -> (typed config, spec, model).  The class is chosen by config.json."""
@@ -67,9 +63,9 @@ def _eos_token_ids(model_dir: str, spec_ids: Sequence[int]) -> FrozenSet[int]:
                 return frozenset(int(t) for t in eos)
         except (OSError, ValueError):
             pass
-    if spec_ids:
-        return frozenset(spec_ids)
-    return DEFAULT_EOS_TOKEN_IDS
+    # The architecture's own ids (its config.json's, or what its spec builder falls back to); a
+    # model whose folder and spec name none ends on length and stop tokens only.
+    return frozenset(spec_ids)
 
 
 class Engine:
@@ -84,9 +80,7 @@ class Engine:
         self.config = config
         self.model = model
         self.device = model.device
-        self.eos_token_ids: FrozenSet[int] = frozenset(
-            DEFAULT_EOS_TOKEN_IDS if eos_token_ids is None else eos_token_ids
-        )
+        self.eos_token_ids: FrozenSet[int] = frozenset(() if eos_token_ids is None else eos_token_ids)
         self.cache = CacheManager(
             model.cache_groups,
             num_pages=num_pages,
@@ -220,6 +214,8 @@ class Engine:
         sampled: List[Request] = []
         for request in scheduled.scheduled:
             n = request.current_chunk_size
+            if request.cache.slot is None or n < 1:
+                raise RuntimeError(f"{request.request_id} was scheduled without a state slot or without tokens")
             completes = request.num_computed_tokens + n >= len(request.all_token_ids)
             chunks.append(
                 StepChunk(request.cache, request.tokens_for_chunk(n), want=(n - 1,) if completes else ())
@@ -244,12 +240,20 @@ class Engine:
                 [r.num_output_tokens for r in sampled],
                 slots=[r.seq_index for r in sampled],
                 history_lengths=[r.num_tokens for r in sampled],
+                status=getattr(self.runner, "status", None),
             )
             if self._timing:
                 end_event.record()
             sync_start = time.perf_counter()
             # The one place per step where the host waits for the device.
             tokens = tokens_gpu.tolist()
+            if len(tokens) > len(sampled):
+                # The device status word came back behind the tokens: kernels that refuse an
+                # access or give up a wait only set a bit there, and tokens drawn after that
+                # mean nothing.
+                word = tokens.pop()
+                if word:
+                    self.runner.raise_for_status(word)
             now = time.perf_counter()
             self.stats["cpu_sync_wait_ms"].append((now - sync_start) * 1000)
             self.stats["sampling_ms"].append((now - t_prepare) * 1000)

@@ -100,7 +100,7 @@ class CausalLM:
 
     # ------------------------------------------------------------------ what the step lays out
     def attention_signatures(self):
-        """Distinct (cache group, (kv_heads, group, window)) pairs among the schedule's mixers."""
+        """Distinct (cache group, (kv_heads, group, window, head_dim)) pairs among the schedule's mixers."""
         seen = []
         for index, entry in enumerate(self.spec.schedule):
             signature = self.blocks[entry.layer].mixer.attention_signature()

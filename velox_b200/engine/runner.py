@@ -140,6 +140,7 @@ _STATUS_NAMES = {
     4: "a cache slot outside the pool",
     8: "a page id outside the pool",
     16: "a bounded wait ran out",
+    32: "a partial attention row outside the scratch",
 }
 
 
@@ -390,7 +391,7 @@ class ModelRunner:
                 if self.dtype != torch.float32 and needed <= self._split_counters.numel():
                     device_plan.split_counters = self._split_counters
             if plan.partial_rows:
-                head_dim = max(self.model.head_dims())
+                head_dim = key[1][3]
                 device_plan.partial_o = self._scratch("attention.partial_o", plan.partial_rows * head_dim)
                 device_plan.partial_lse = self._scratch("attention.partial_lse", plan.partial_rows)
             plans[key] = device_plan
@@ -417,13 +418,13 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ decode steps as CUDA graphs
     def _plan_options(self, signature) -> "ap.PlanOptions":
-        """How attention work is cut for layers of this (KV heads, heads per KV head, window)."""
-        num_kv_heads, heads_per_kv, window = signature
+        """How attention work is cut for layers of this (KV heads, heads per KV head, window,
+        head size): what an SM holds of the kernels depends on the head size."""
+        num_kv_heads, heads_per_kv, window, head_dim = signature
         use_f32 = self.dtype == torch.float32
         options = dict(num_kv_heads=num_kv_heads, group=heads_per_kv, window=window, use_f32=use_f32,
                        target_ctas=2 * self.num_sms)
         if not use_f32:
-            head_dim = max(self.model.head_dims())
             options["narrow_target_ctas"] = kernels.narrow_attention_slots(head_dim) * self.num_sms
             options["narrow_max_cluster"] = kernels.max_attention_cluster(head_dim)
             options["narrow_cluster_limits"] = kernels.attention_cluster_limits(head_dim)
@@ -622,7 +623,11 @@ class ModelRunner:
     # ------------------------------------------------------------------ checks
     def check_status(self) -> None:
         """Read the device status word (this synchronises) and raise if a kernel flagged a fault."""
-        word = int(self.status[0].item())
+        self.raise_for_status(int(self.status[0].item()))
+
+    def raise_for_status(self, word: int) -> None:
+        """Raise for a status word that was read back (by ``check_status`` or, in generation,
+        behind the sampled tokens), after clearing the word on the device."""
         if word:
             self.status.zero_()
             what = [text for bit, text in _STATUS_NAMES.items() if word & bit]

@@ -13,7 +13,9 @@ its decisions are what a user of that engine observes:
 Pages run out in three ways, with three answers.  A decode that cannot grow takes pages from
 the request that started running last, then the one before, until it fits; if it reaches
 itself it gives up and is the one preempted.  The prompt portion of the request that has been
-running longest may do the same; younger ones sit the step out.  A newcomer never takes
+running longest may do the same; younger ones sit the step out.  A victim that had already been
+given its token in this step loses it again (the reference leaves such a request in the step's
+batch with empty tables, engine/scheduler.py:241-244 there).  A newcomer never takes
 anything.  Preempting is recomputing: the victim's pages go back, nothing of it counts as
 computed, it keeps what it has generated and goes to the front of the queue, and when it is
 admitted again prompt and generated tokens are prefilled as one prompt.
@@ -68,6 +70,16 @@ class _StepPlan:
         (self.out.decode_batch if decoding else self.out.prefill_batch).append(request)
         self.out.num_batched_tokens += tokens
         self.budget -= tokens
+
+    def take_back(self, request: Request) -> None:
+        """Undo ``give``: a request that was given work earlier in this step and has now lost
+        its pages runs nothing, and its tokens return to the budget."""
+        for batch in (self.out.decode_batch, self.out.prefill_batch):
+            if request in batch:
+                batch.remove(request)
+                self.out.num_batched_tokens -= request.current_chunk_size
+                self.budget += request.current_chunk_size
+        request.current_chunk_size = 0
 
 
 class Scheduler:
@@ -218,6 +230,7 @@ class Scheduler:
 
     def _preempt(self, victim: Request, plan: _StepPlan) -> None:
         """Recompute later: pages and slot go back, the request goes to the front of the queue."""
+        plan.take_back(victim)
         self.cache.reset_for_recompute(victim.cache)
         self.cache.release_slot(victim.cache)
         if victim in self.running:

@@ -32,6 +32,10 @@ from ..parts.spec import (
 
 ARCHITECTURE = "Qwen2ForCausalLM"
 
+# End-of-sequence ids of the Qwen2.5 vocabulary, for a folder whose config.json and
+# generation_config.json name none: what the reference falls back to (engine/engine.py:23).
+DEFAULT_EOS_TOKEN_IDS = (151643, 151645)
+
 
 def _matrix(*sources: TensorSource) -> WeightSpec:
     return WeightSpec(sources=tuple(sources), role="matrix")
@@ -148,7 +152,7 @@ def build_qwen2_spec(config: ModelConfig) -> ModelSpec:
             params={"hidden_size": E, "vocab_size": V},
             weights={"weight": _matrix(head_source)},
         ),
-        eos_token_ids=c.eos_token_ids,
+        eos_token_ids=tuple(c.eos_token_ids) or DEFAULT_EOS_TOKEN_IDS,
         # A tied checkpoint may still store a copy of the head; it is not read.
         ignored_tensors=("lm_head.weight",) if c.tie_word_embeddings else (),
     )

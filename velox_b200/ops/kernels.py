@@ -54,8 +54,10 @@ def core():
         lib.vx_cast_bf16_to_f32.argtypes = [_ptr, _ptr, _c_ll, _ptr]
         lib.vx_sample.argtypes = [
             _ptr, _c_int, _c_int, _c_ll, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_ll, _ptr, _ptr, _ptr, _ptr, _ptr,
+            _ptr,
         ]
         lib.vx_sample_segments.argtypes = [_c_int, _c_int]
+        lib.vx_selftest_bounded_wait.argtypes = [_ptr, _c_ll, _ptr, _ptr]
         lib.vx_gemm_bf16_add_mirrored.argtypes = [
             _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_int, _ptr, _ptr,
         ]
@@ -150,6 +152,17 @@ def _code(dtype: torch.dtype) -> int:
 
 
 # ------------------------------------------------------------------------------------------
+def selftest_bounded_wait(status: torch.Tensor, limit_cycles: int) -> int:
+    """Run one CTA that waits, with a limit of ``limit_cycles`` SM cycles, on a barrier nobody
+    arrives at.  Returns 1 when the wait gave up (and set its bit in ``status``), 2 if the
+    barrier flipped, 0 if the kernel never reported.  Synchronises."""
+    _need(status, torch.int32, "status")
+    returned = torch.zeros(1, dtype=torch.int32, device=status.device)
+    _check(core().vx_selftest_bounded_wait(_p(status), int(limit_cycles), _p(returned), _stream()),
+           "selftest_bounded_wait")
+    return int(returned.item())
+
+
 def embed(table: torch.Tensor, ids: torch.Tensor, resid: torch.Tensor, status: torch.Tensor) -> None:
     """resid[t, :] = float32(table[ids[t], :]); ids outside the table set a status bit."""
     _need(ids, torch.int32, "ids")
@@ -696,13 +709,17 @@ def sample(
     history: Optional[torch.Tensor] = None,
     history_slots: Optional[torch.Tensor] = None,
     history_lengths: Optional[torch.Tensor] = None,
+    status: Optional[torch.Tensor] = None,
 ) -> None:
     """One token per row: argmax where temperature is 0 (or None), else the exponential race.
 
     With ``history`` (int32 [slots, width]) the token of row r is also stored at
-    ``history[history_slots[r], history_lengths[r]]``."""
+    ``history[history_slots[r], history_lengths[r]]``.  With ``status`` (the device status
+    word) its first entry is copied to ``out[num_rows]``, so ``out`` needs one entry more."""
     _need(logits, torch.float32, "logits")
     _need(out, torch.int32, "out")
+    if out.numel() < num_rows + (0 if status is None else 1):
+        raise ValueError("out is too short for the rows (and the status word)")
     if temperature is not None:
         _need(temperature, torch.float32, "temperature")
         _need(seeds, torch.int64, "seeds")
@@ -712,7 +729,7 @@ def sample(
         core().vx_sample(_p(logits), num_rows, logits.shape[1], logits.stride(0), _p(temperature),
                          _p(seeds), _p(draw_index), _p(threshold), _p(out), _p(history),
                          0 if history is None else history.stride(0), _p(history_slots),
-                         _p(history_lengths), _p(partial), _p(counters), _stream()),
+                         _p(history_lengths), _p(partial), _p(counters), _p(status), _stream()),
         "sample",
     )
 

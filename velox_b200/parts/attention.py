@@ -61,7 +61,7 @@ class Attention(Mixer):
         return CacheNeeds(paged=PagedCacheSpec(self.num_kv_heads, self.head_dim, self.window))
 
     def attention_signature(self):
-        return (self.num_kv_heads, self.num_heads // self.num_kv_heads, self.window)
+        return (self.num_kv_heads, self.num_heads // self.num_kv_heads, self.window, self.head_dim)
 
     # The input is used by the QKV projection only, which can make the norm itself.
     accepts_pending_norm = True
@@ -72,9 +72,10 @@ class Attention(Mixer):
         qkv = ws.get("attention.qkv", (ws.max_tokens, self.qkv_width), self.dtype)
         group = ctx.groups[cache.group]
         k_cache, v_cache = (None, None) if cache.read_only else (cache.k, cache.v)
-        # Few tokens and heads of 128 dims: projection, rotation and cache write in one kernel.
+        # Projection, rotation and cache write in one kernel, where the position encoding
+        # offers its tables and the kernel takes the shape (it says no otherwise).
         tables = None
-        if _FUSE_ROPE and self.head_dim == 128:
+        if _FUSE_ROPE:
             tables = getattr(self.position, "full_rotation_tables", lambda: None)()
         if tables is None or not qkv_rope_linear(
                 x, self.w_qkv, self.b_qkv, qkv, T, ctx.status, ctx.positions, tables[0], tables[1],

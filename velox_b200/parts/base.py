@@ -127,7 +127,8 @@ class Mixer(Part):
         return CacheNeeds()
 
     def attention_signature(self):
-        """(num_kv_heads, group, window) if the step should lay out attention work for it."""
+        """(num_kv_heads, heads per KV head, window, head_dim) if the step should lay out
+        attention work for it; layers with equal signatures in one cache group share a layout."""
         return None
 
     def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:  # pragma: no cover

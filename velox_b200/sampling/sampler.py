@@ -50,7 +50,8 @@ class Sampler:
         self._used = [False, False]
         self._flip = 0
         self._dev = torch.zeros((_COLUMNS + 1, rows), dtype=torch.int32, device=device)
-        self.tokens = torch.zeros(rows, dtype=torch.int32, device=device)
+        # One entry more than rows: the device status word can ride behind the tokens.
+        self.tokens = torch.zeros(rows + 1, dtype=torch.int32, device=device)
         self._threshold = torch.zeros(rows, dtype=torch.float32, device=device)
         # Made on first use: most workloads never ask for penalties.
         self._history: Optional[torch.Tensor] = None
@@ -82,21 +83,25 @@ class Sampler:
         draw_indices: Sequence[int],
         slots: Optional[Sequence[int]] = None,
         history_lengths: Optional[Sequence[int]] = None,
+        status: Optional[torch.Tensor] = None,
     ) -> torch.Tensor:
         """Returns int32 device tokens [R]; the caller decides when to read them back.
 
         ``draw_indices[r]`` is the index of the output token being drawn for row r.  ``slots``
         and ``history_lengths`` (tokens of the request so far) are needed for the penalties.
+        With ``status`` (the runner's device status word) the result has R + 1 entries, the
+        last one being that word as it stood when the tokens were drawn: one read-back brings
+        both.
         """
         rows = logits.shape[0]
         if len(params) != rows:
             raise ValueError(f"got {len(params)} sampling params for {rows} rows of logits")
         if rows > self.max_num_seqs:
             raise ValueError(f"{rows} rows exceed the sampler's {self.max_num_seqs}")
-        out = self.tokens[:rows]
+        out = self.tokens[: rows + (0 if status is None else 1)]
         any_penalty = any(p.has_penalties for p in params)
         if all(p.is_greedy for p in params) and not any_penalty:
-            kernels.sample(logits, rows, None, None, None, None, out)
+            kernels.sample(logits, rows, None, None, None, None, out, status=status)
             return out
 
         index = self._flip
@@ -152,5 +157,6 @@ class Sampler:
             logits, rows, temperature, seeds, draw, threshold, out,
             history, dev[9, :rows] if history is not None else None,
             dev[10, :rows] if history is not None else None,
+            status=status,
         )
         return out
