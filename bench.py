@@ -385,11 +385,13 @@ def _reference_numbers(args, ref_root):
     rng = np.random.default_rng(0)
     vocab = cfg["vocab_size"]
 
-    def build(max_batch):
+    def build(max_batch, total_requests):
+        # Its prefix cache (on by default) keeps the pages of requests that have ended and counts
+        # only the leaves of its tree as free again, so the pool holds every request of the run.
         return RefEngine.from_pretrained(RefEngineConfig(
             model=folder, dtype="bfloat16", device="cuda", max_model_len=CONTEXT + 16, max_num_seqs=max_batch,
             max_num_batched_tokens=max(PREFILL_TOKENS, max_batch), max_prefill_chunk_size=PREFILL_TOKENS,
-            num_gpu_blocks=max_batch * (CONTEXT // ref_block + 2) + 8, seed=0,
+            num_gpu_blocks=total_requests * (CONTEXT // ref_block + 2) + 64, seed=0,
         ))
 
     def decode_point(engine, batch, steps, warmup):
@@ -438,7 +440,7 @@ def _reference_numbers(args, ref_root):
         return batch * 1000.0 / ms, ms, produced / seconds
 
     max_batch = max(args.batch, 64 if args.points else args.batch)
-    engine = build(max_batch)
+    engine = build(max_batch, args.batch + 6 + (1 + 64 if args.points else 0))
     import shutil
 
     shutil.rmtree(folder, ignore_errors=True)

@@ -103,7 +103,7 @@ def test_long_prompt_every_way_of_cutting(sized, dtype, monkeypatch):
 
     def spying_mlp_fused(*args, **kwargs):
         answer = real_mlp_fused(*args, **kwargs)
-        fused_answers.append(answer)
+        fused_answers.append((args[6], answer))  # (rows of the step, taken or refused)
         return answer
 
     monkeypatch.setattr(kernels, "mlp_fused", spying_mlp_fused)
@@ -136,11 +136,14 @@ def test_long_prompt_every_way_of_cutting(sized, dtype, monkeypatch):
         # The single-token steps ran as captured graphs with the fused kernels of small steps.
         assert replayer.runner._graphs and not replayer.runner._graphs_broken
         assert fused_answers, "no small step reached the one-kernel feed-forward"
-        if cfg["hidden_size"] == 5120:
-            # 40 output tiles and the activation tile need more tensor-memory columns than an SM has.
-            assert not any(fused_answers), "the one-kernel feed-forward took a width it cannot hold"
-        else:
-            assert all(fused_answers)
+        # A step's tile of 16 or 32 tokens needs (1 + width / 128) x tile columns of tensor
+        # memory out of 512: all small steps at 1,536, steps of up to 16 tokens at 3,584, none at
+        # 5,120, where the step must take the two-kernel route (and still match, above).
+        width = cfg["hidden_size"]
+        for rows_of_step, taken in fused_answers:
+            tile = 16 if rows_of_step <= 16 else 32
+            assert taken == ((1 + width // 128) * tile <= 512), (width, rows_of_step, taken)
+        assert any(taken for _, taken in fused_answers) == (width < 5120)
     replayer.cache.assert_consistent()
     assert replayer.cache.num_free_pages() == replayer.cache.num_total_pages
 
