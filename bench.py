@@ -162,13 +162,12 @@ def run_own(args):
     ))
     import shutil
 
-    shutil.rmtree(folder, ignore_errors=True)
     runner, cache, sampler = engine.runner, engine.cache, engine.sampler
     vocab = cfg["vocab_size"]
     rng = np.random.default_rng(0)
     weight_bytes, kv_bytes_per_token = model_bytes(cfg, layers)
 
-    def fill(batch, context):
+    def fill(batch, context, runner=runner, cache=cache):
         """``batch`` sequences with ``context`` tokens in the cache, through the step function."""
         seqs = []
         for b in range(batch):
@@ -185,12 +184,12 @@ def run_own(args):
         torch.cuda.synchronize()
         return seqs
 
-    def release(seqs):
+    def release(seqs, cache=cache):
         for seq in seqs:
             cache.free(seq)
             cache.release_slot(seq)
 
-    def decode_steps(seqs, steps, warmup):
+    def decode_steps(seqs, steps, warmup, runner=runner, cache=cache, sampler=sampler):
         """Device time (ms) of each of ``steps`` decode steps after ``warmup`` untimed ones."""
         batch = len(seqs)
         tokens = rng.integers(0, vocab, batch).tolist()
@@ -219,13 +218,82 @@ def run_own(args):
                 times.append(start.elapsed_time(end))
         return times, kernels.launch_count + runner.kernels_replayed - launches_before
 
-    def decode_point(batch, steps, warmup):
+    def decode_point(batch, steps, warmup, engine=engine):
         context = CONTEXT - steps - warmup - 1
-        seqs = fill(batch, context)
-        times, launches = decode_steps(seqs, steps, warmup)
-        release(seqs)
+        seqs = fill(batch, context, engine.runner, engine.cache)
+        times, launches = decode_steps(seqs, steps, warmup, engine.runner, engine.cache, engine.sampler)
+        release(seqs, engine.cache)
         ms = sum(times) / len(times)
         return batch * 1000.0 / ms, ms, launches, context + warmup + steps // 2
+
+    E, H, G, I, V = (cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"],
+                     cfg["intermediate_size"], cfg["vocab_size"])
+    D = E // H
+    # Bytes every launch of a kind has to read: its matrix once (the cache for attention).
+    kind_bytes = {"qkv": (H + 2 * G) * D * E * 2, "o": E * H * D * 2, "feed_forward": 3 * I * E * 2, "lm_head": V * E * 2}
+    kind_of = {"gemm_bf16_qkv_rope": "qkv", "rope_cache_write": "qkv", "attention": "attention", "attention_merge": "attention",
+               "gemm_bf16_add_mirrored": "o", "mlp_fused": "feed_forward", "swiglu": "feed_forward"}
+
+    def kernel_breakdown(batch, repeats=5):
+        """Device time of each kind of kernel in one decode step of ``batch`` requests at the
+        benchmark's context: the step is laid out as the captured step is, but launched kernel
+        by kernel behind a queued delay with an event after every launch."""
+        context = CONTEXT - 8
+        seqs = fill(batch, context)
+        chunks = []
+        for seq in seqs:
+            assert cache.append_slots(seq, 1)
+            chunks.append(StepChunk(seq, [int(rng.integers(0, vocab))], (0,)))
+        bucket = runner._bucket(batch)
+        totals = []
+        for _ in range(repeats):
+            ctx, ids, rows, count = runner.prepare(chunks, pad_to=bucket)
+            torch.cuda.synchronize()
+            torch.cuda._sleep(40_000_000)  # about 20 ms: the host queues the whole step meanwhile
+            first = torch.cuda.Event(enable_timing=True)
+            first.record()
+            kernels.launch_events = []
+            try:
+                runner.model.forward(ctx, runner.layer_caches, ids, rows, count)
+            finally:
+                events, kernels.launch_events = kernels.launch_events, None
+            torch.cuda.synchronize()
+            per_kind, previous, last_gemm = {}, first, None
+            for index, (name, event) in enumerate(events):
+                took = previous.elapsed_time(event) * 1000.0
+                previous = event
+                kind = kind_of.get(name)
+                if name.startswith("gemm_bf16") and kind is None:
+                    last_gemm = index
+                    kind = "o" if name == "gemm_bf16" else "feed_forward"  # settled below for the last one
+                per_kind.setdefault(kind or "other", []).append((index, took))
+            flat = {}
+            for kind, entries in per_kind.items():
+                for index, took in entries:
+                    real = "lm_head" if index == last_gemm else kind
+                    flat[real] = flat.get(real, 0.0) + took
+            totals.append(flat)
+        release(seqs)
+        out = {}
+        for kind in sorted({k for t in totals for k in t}):
+            values = sorted(t.get(kind, 0.0) for t in totals)
+            out[kind] = values[len(values) // 2]
+        return out, context + 1
+
+    def kernel_report(times_us, batch, keys):
+        report = {}
+        for kind, us in times_us.items():
+            per_step = kind_bytes.get(kind)
+            if kind == "attention":
+                per_step = batch * keys * kv_bytes_per_token
+            elif per_step is not None and kind != "lm_head":
+                per_step *= layers
+            entry = {"us": round(us, 1)}
+            if per_step:
+                gbs = per_step / (us * 1e-6) / 1e9
+                entry.update({"gbs": round(gbs, 1), "frac": round(gbs / peaks["hbm_gbs"], 3)})
+            report[kind] = entry
+        return report
 
     clocks = ClockSampler()
     clocks.start()
@@ -260,11 +328,50 @@ def run_own(args):
                "ms": round(prefill_ms, 3),
                "frac": round(prefill_flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
 
+    # The same prompt as four portions of 512, one step each.
+    split_times = []
+    for i in range(2 + 3):
+        seq = cache.new_sequence(f"prefill4_{i}")
+        assert cache.acquire_slot(seq)
+        ids = rng.integers(0, vocab, PREFILL_TOKENS).tolist()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for part in range(4):
+            assert cache.append_slots(seq, 512)
+            runner.step([StepChunk(seq, ids[512 * part : 512 * (part + 1)], (511,) if part == 3 else ())])
+            cache.advance(seq, 512)
+        end.record()
+        torch.cuda.synchronize()
+        release([seq])
+        if i >= 2:
+            split_times.append(start.elapsed_time(end))
+    split_ms = sum(split_times) / len(split_times)
+    prefill_4x512 = {"value": round(PREFILL_TOKENS * 1000.0 / split_ms, 1), "ms": round(split_ms, 3),
+                     "frac": round(prefill_flops / (split_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
+
     points = {}
+    kernel_times = {}
     if args.points:
         for batch in (1, 64):
             tok_s, _, _, _ = decode_point(batch, max(8, args.steps // 2), 3)
             points[f"decode_b{batch}"] = round(tok_s, 1)
+        times8, keys8 = kernel_breakdown(args.batch)
+        kernel_times = kernel_report(times8, args.batch, keys8)
+        times64, keys64 = kernel_breakdown(64)
+        kernel_times["attention_b64"] = kernel_report({"attention": times64["attention"]}, 64, keys64)["attention"]
+        kernel_times["method"] = ("one decode step launched kernel by kernel behind a queued delay, a CUDA event after every "
+                                  "launch; us summed over the layers, bytes = the matrices (the cache) each kind must read")
+        # The reference's page size (16 keys): a second engine on the same weights.
+        small_pages = Engine.from_pretrained(EngineConfig(
+            model=folder, dtype="bfloat16", max_model_len=CONTEXT + 16, max_num_seqs=args.batch,
+            max_num_batched_tokens=max(PREFILL_TOKENS, args.batch), max_prefill_chunk_size=PREFILL_TOKENS,
+            block_size=16, num_gpu_blocks=args.batch * (CONTEXT // 16 + 2) + 8, seed=0,
+        ))
+        tok_s, _, _, _ = decode_point(args.batch, max(8, args.steps // 2), 3, engine=small_pages)
+        points[f"decode_b{args.batch}_block16"] = round(tok_s, 1)
+        del small_pages
+    shutil.rmtree(folder, ignore_errors=True)
 
     # End to end through the entry point: Engine.step with host tokens in and out.  Prompts are
     # prefilled in turn, so the first request decodes while the others still prefill (two
@@ -323,8 +430,10 @@ def run_own(args):
         "e2e": e2e,
         "gpu_launches": launches,
         "prefill": prefill,
+        "prefill_4x512": prefill_4x512,
         "roofline": roofline,
         "points": points,
+        "kernels": kernel_times,
     }
     print(json.dumps(line))
     return 0

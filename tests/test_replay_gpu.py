@@ -288,3 +288,62 @@ def test_decode_as_cuda_graph_matches_eager(models):
         head = {"a": 100, "b": 40, "c": 20}[n]
         check(outs[True][n], want[ref_index][head:], "bfloat16", f"graph decode {n}")
         check(outs[False][n], want[ref_index][head:], "bfloat16", f"eager decode {n}")
+
+
+@pytest.mark.parametrize("case", ["tiny_w", "tiny_d"])
+def test_padded_step_staging_equals_prepare(models, case):
+    """The captured decode step reads its arrays from fixed places; the fast path that fills
+    them (it rewrites only what has changed since the same host copy was last used) must leave
+    on the device exactly what the general ``prepare`` writes, step after step, while requests
+    join, leave, sit steps out, grow new pages and (with a window) give pages back."""
+    from velox_b200.engine.runner import StepChunk
+
+    folder, cfg, page, prompts, _ = models[case]
+    replayer = make_replayer(folder, "bfloat16", max_tokens=1024, page=page, max_live=4)
+    runner, cache = replayer.runner, replayer.cache
+    rng = np.random.default_rng(3)
+    vocab = cfg["vocab_size"]
+    heads = {"a": 70, "b": 3, "c": 33, "d": 120}
+    replayer.run_step({"step": 0, "end": [], "entries": [
+        {"id": name, "tokens": rng.integers(0, vocab, n).tolist(), "want": []} for name, n in heads.items()]})
+    live = dict(replayer.live)
+    compared = 0
+    for step in range(150):
+        if step == 60:  # one leaves, another of the same name comes with other pages
+            seq = live.pop("b")
+            cache.free(seq)
+            cache.release_slot(seq)
+            replayer.live.pop("b")
+            replayer.run_step({"step": 1000, "end": [], "entries": [{"id": "b", "tokens": rng.integers(0, vocab, 40).tolist(), "want": []}]})
+            live["b"] = replayer.live["b"]
+        names = [name for name in sorted(live) if rng.random() < 0.75] or ["a"]
+        chunks = []
+        for name in names:
+            assert cache.append_slots(live[name], 1)
+            chunks.append(StepChunk(live[name], [int(rng.integers(0, vocab))], (0,)))
+        bucket = runner._bucket(len(chunks))
+        entry = runner._graphs.get(bucket)
+        if entry is None or entry[2] != (runner.workspace.generation, runner._meta_generation):
+            entry = runner._graphs[bucket] = runner._capture(bucket)
+        where, plan_where, size = entry[3]
+        # The arrays of the step; between them lie a few ints of alignment that nobody writes.
+        used = torch.zeros(size, dtype=torch.bool, device="cuda")
+        pieces = list(where.values())
+        for entry_where, merge_where in plan_where.values():
+            pieces.extend(entry_where.values())
+            if merge_where is not None:
+                pieces.append(merge_where)
+        for offset, shape in pieces:
+            used[offset : offset + int(np.prod(shape))] = True
+        assert runner._fill_padded(entry, bucket, chunks)
+        torch.cuda.synchronize()
+        fast = runner._device_meta[:size][used]
+        runner.prepare(chunks, pad_to=bucket)
+        torch.cuda.synchronize()
+        assert runner._last_layout[2] == size
+        plain = runner._device_meta[:size][used]
+        assert torch.equal(fast, plain), (step, names, torch.nonzero(fast != plain).flatten().tolist()[:10])
+        compared += 1
+        for name in names:
+            cache.advance(live[name], 1)
+    assert compared == 150

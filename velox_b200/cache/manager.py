@@ -20,6 +20,7 @@ this ``seq_index`` (engine/scheduler.py:58,113-129).
 """
 from __future__ import annotations
 
+import itertools
 from collections import deque
 from dataclasses import dataclass, field
 from typing import Callable, Deque, Dict, List, Optional, Sequence
@@ -45,6 +46,11 @@ class SequenceCache:
     # Per group, the first logical block that has not been given back yet.
     first_live: List[int] = field(default_factory=list)
     slot: Optional[int] = None
+    # A number no other sequence of the process has, and a count of the changes to the tables
+    # (pages appended, given back, dropped): who keeps a copy of the tables knows by the pair
+    # whether the copy still holds.
+    serial: int = field(default_factory=itertools.count().__next__)
+    tables_version: int = 0
 
     @property
     def num_logical_blocks(self) -> int:
@@ -126,6 +132,7 @@ class CacheManager:
             return False
         for table, alloc in zip(seq.tables, self.allocators):
             table.extend(alloc.take(extra))
+        seq.tables_version += 1
         self._live[seq.seq_id] = seq
         return True
 
@@ -149,6 +156,7 @@ class CacheManager:
             for block in range(seq.first_live[index], dead_blocks):
                 self.allocators[index].give_back(table[block])
                 table[block] = NULL_PAGE
+                seq.tables_version += 1
             seq.first_live[index] = max(seq.first_live[index], dead_blocks)
 
     def free(self, seq: SequenceCache) -> None:
@@ -159,6 +167,7 @@ class CacheManager:
                 alloc.give_back(table[block])
             seq.tables[index] = []
             seq.first_live[index] = 0
+        seq.tables_version += 1
         self._live.pop(seq.seq_id, None)
 
     def reset_for_recompute(self, seq: SequenceCache) -> None:

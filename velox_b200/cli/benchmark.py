@@ -12,7 +12,10 @@ tokenizer; there is no tokenizer here, so prompts are seeded uniform-random toke
 lengths follow the workload (short: 16-64, long: 512-1536, mixed: both).  Added: ``--dtype``,
 ``--random-weights CONFIG_JSON`` with ``--weights-seed`` (writes the model folder first), and
 ``--top-k``, ``--model-size NAME`` (random weights with a named configuration's layer sizes,
-``--layers N`` of them), ``--prompt-len`` / ``--decode-len`` (fixed lengths), ``--batch 1,8,64``
+``--layers N`` of them), ``--prompt-len`` / ``--decode-len`` (fixed lengths), ``--prompt-range
+LOW,HIGH`` (lengths uniform in that range), ``--rounds N`` (the reference's option: the same
+requests N times on one engine; here it also says whether every round gave the same tokens),
+``--batch 1,8,64``
 (that many requests and sequences per run) and a roofline line (bytes the steps had to read
 over GPU-busy time).  It prints what the reference prints: wall time, steps, prompt and generated
 tokens, decode tokens/s (generated / wall), time to first token and inter-token latency
@@ -44,6 +47,9 @@ def parse_args(argv: Optional[List[str]] = None) -> argparse.Namespace:
     parser.add_argument("--weights-seed", type=int, default=0)
     parser.add_argument("--prompt-len", type=int, default=None,
                         help="every prompt has this many tokens (instead of the workload's lengths)")
+    parser.add_argument("--prompt-range", default=None, metavar="LOW,HIGH",
+                        help="prompt lengths uniform in [LOW, HIGH] (instead of the workload's lengths)")
+    parser.add_argument("--rounds", type=int, default=1, help="run the same requests this many times on one engine")
     parser.add_argument("--decode-len", type=int, default=None, help="the same as --max-tokens")
     parser.add_argument("--batch", default=None,
                         help="comma-separated batch sizes: for each, that many requests and max_num_seqs")
@@ -77,11 +83,14 @@ def parse_args(argv: Optional[List[str]] = None) -> argparse.Namespace:
 
 
 def build_prompts(workload: str, count: int, vocab: int, limit: int, seed: int,
-                  fixed_len: Optional[int] = None) -> List[List[int]]:
+                  fixed_len: Optional[int] = None, length_range: Optional[str] = None) -> List[List[int]]:
     import numpy as np
 
     rng = np.random.default_rng(seed)
     ranges = WORKLOADS[workload] if fixed_len is None else [(fixed_len, fixed_len)]
+    if length_range is not None:
+        low, high = (int(v) for v in length_range.split(","))
+        ranges = [(low, high)]
     prompts = []
     for index in range(count):
         low, high = ranges[index % len(ranges)]
@@ -97,7 +106,7 @@ def percentile(values: List[float], q: float) -> float:
     return ordered[min(len(ordered) - 1, int(q * len(ordered)))]
 
 
-def run_workload(engine, prompts, args) -> Dict[str, object]:
+def run_workload(engine, prompts, args, round_index: int = 0) -> Dict[str, object]:
     from ..engine.request import Request
     from ..sampling.params import SamplingParams
 
@@ -106,7 +115,7 @@ def run_workload(engine, prompts, args) -> Dict[str, object]:
     for index, prompt in enumerate(prompts):
         params = SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k,
                                 max_tokens=args.max_tokens, ignore_eos=True, seed=args.seed + index)
-        request = Request(f"bench-{index}", prompt, params)
+        request = Request(f"bench-{round_index}-{index}", prompt, params)
         token_times[request.request_id] = []
         request.add_listener(
             lambda r, kind, token: token_times[r.request_id].append(time.perf_counter()) if kind == "token" else None
@@ -241,10 +250,22 @@ def main(argv: Optional[List[str]] = None) -> int:
         ))
         limit = engine.max_model_len - args.max_tokens - 1
         prompts = build_prompts(args.workload, num_requests, engine.model.vocab_size, limit, args.seed,
-                                fixed_len=args.prompt_len)
-        result = run_workload(engine, prompts, args)
-        result.update(roofline(engine, result))
-        report(result, f"max_num_seqs={max_num_seqs} workload={args.workload} dtype={args.dtype}")
+                                fixed_len=args.prompt_len, length_range=args.prompt_range)
+        outputs = []
+        for round_index in range(max(1, args.rounds)):
+            for values in engine.stats.values():
+                values.clear()
+            preemptions_before = engine.scheduler.num_preemptions
+            result = run_workload(engine, prompts, args, round_index)
+            result["preemptions"] -= preemptions_before
+            result.update(roofline(engine, result))
+            suffix = f" round={round_index + 1}" if args.rounds > 1 else ""
+            report(result, f"max_num_seqs={max_num_seqs} workload={args.workload} dtype={args.dtype}{suffix}")
+            outputs.append([r.output_token_ids for r in result["requests"]])
+        if args.rounds > 1:
+            same = sum(outputs[0][i] == later[i] for later in outputs[1:] for i in range(len(prompts)))
+            print(f"rounds             {same} of {(len(outputs) - 1) * len(prompts)} requests repeated their first round's tokens")
+            result["rounds_same_tokens"] = same
         if args.show_outputs:
             for request in result["requests"]:
                 print(request.request_id, request.output_token_ids)

@@ -131,6 +131,68 @@ class _Packer:
         return offset, tuple(array.shape)
 
 
+class _PaddedStage:
+    """Host side of one decode bucket: two pinned copies of the captured step's arrays (used in
+    turn, so that one can be written while the other's copy to the device may still run), views
+    into them by name, and a record of what each copy holds."""
+
+    def __init__(self, layout, bucket: int, num_groups: int, no_slot: int) -> None:
+        where, plan_where, size = layout
+        self.layout = layout
+        self.bucket = bucket
+        self.no_slot = no_slot
+        self.num_groups = num_groups
+        self.buffers = [torch.zeros(size, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self.events: List[Optional[torch.cuda.Event]] = [None, None]
+        self.flip = 0
+        self.plan_options: Dict[Tuple, Tuple] = {}
+        self.views: List[Dict] = []
+        self.held: List[Dict] = []
+        for buffer in self.buffers:
+            array = buffer.numpy()
+            views: Dict = {}
+            for name, (offset, shape) in where.items():
+                count = int(np.prod(shape)) if shape else 1
+                views[name] = array[offset : offset + count].reshape(shape)
+            for key, (entry_where, merge_where) in plan_where.items():
+                (offset, shape), = entry_where.values()
+                views[("items", key)] = array[offset : offset + shape[0] * 8].reshape(shape[0], 8)
+                if merge_where is not None:
+                    offset, shape = merge_where
+                    views[("merges", key)] = array[offset : offset + shape[0] * 8].reshape(shape[0], 8)
+            self.views.append(views)
+            self.held.append({"count": -1, "rows": [[None] * bucket for _ in range(num_groups)]})
+
+    def take(self):
+        """The copy to write now: (its index, its views, what it holds)."""
+        index = self.flip
+        self.flip ^= 1
+        if self.events[index] is not None:
+            self.events[index].synchronize()
+        return index, self.views[index], self.held[index]
+
+    def copied(self, index: int) -> None:
+        if self.events[index] is None:
+            self.events[index] = torch.cuda.Event()
+        self.events[index].record()
+
+    def write_padding(self, index: int, n: int) -> None:
+        """Everything that depends only on how many real sequences the step has."""
+        bucket = self.bucket
+        views, held = self.views[index], self.held[index]
+        views["ids"][n:] = 0
+        views["positions"][n:] = 0
+        views["q_start"][:] = np.arange(bucket, dtype=np.int32)
+        views["q_len"][:] = 1
+        views["kv_len"][n:] = 1
+        views["seq_slots"][n:] = self.no_slot
+        views["logit_rows"][:] = np.arange(bucket, dtype=np.int32)
+        for g in range(self.num_groups):
+            views[f"slots{g}"][n:] = -1
+            views[f"tables{g}"][n:] = 0
+            held["rows"][g][n:] = [None] * (bucket - n)
+
+
 # VELOX_B200_NO_TC_ATTENTION=1 keeps prompt portions on the mma.sync family (for bisecting).
 _USE_TC_ATTENTION = os.environ.get("VELOX_B200_NO_TC_ATTENTION") != "1"
 
@@ -202,6 +264,7 @@ class ModelRunner:
         # splits of a captured step its results do not depend on how the work was cut.
         self.enable_graphs = enable_graphs and self.dtype != torch.float32
         self._graphs: Dict[int, tuple] = {}
+        self._padded_stages: Dict[int, "_PaddedStage"] = {}
         self._graphs_broken = False
         self._meta_generation = 0
 
@@ -526,63 +589,77 @@ class ModelRunner:
     def _fill_padded(self, entry, bucket: int, chunks: Sequence[StepChunk]) -> bool:
         """Write a padded single-token step straight into the places the captured step reads
         (the layout of a bucket never changes), with arrays instead of per-token loops.  What
-        it writes is what ``prepare(chunks, pad_to=bucket)`` writes.  False: use ``prepare``."""
+        reaches the device is what ``prepare(chunks, pad_to=bucket)`` writes.  Every bucket has
+        two pinned host copies of its arrays, used in turn, and remembers what each holds: a
+        block-table row is written again only when its sequence's tables have changed, the
+        padding only when the number of real sequences has.  False: use ``prepare``."""
         where, plan_where, size = entry[3]
         if any(sig[1] > 16 for _, sig in self._signatures):
             return False
+        stage = self._padded_stages.get(bucket)
+        if stage is None or stage.layout is not entry[3]:
+            stage = _PaddedStage(entry[3], bucket, len(self.cache.groups), self.max_num_seqs)
+            self._padded_stages[bucket] = stage
         P = self.page_size
         n = len(chunks)
         positions = np.fromiter((c.seq.num_computed for c in chunks), np.int64, n)
-        blocks = positions // P
+        blocks = (positions // P).tolist()
         for c, block in zip(chunks, blocks):
             if block >= c.seq.num_logical_blocks:
                 raise ValueError(f"{c.seq.seq_id}: append_slots was not called before the step")
-        host, dev = self._staging(size)
-        host_np = host.numpy()
-
-        def hv(name):
-            offset, shape = where[name]
-            count = int(np.prod(shape)) if shape else 1
-            return host_np[offset : offset + count].reshape(shape)
-
-        ids = hv("ids")
-        ids[:n] = [c.tokens[0] for c in chunks]
-        ids[n:] = 0
-        pos = hv("positions")
-        pos[:n] = positions
-        pos[n:] = 0
-        hv("q_start")[:] = np.arange(bucket, dtype=np.int32)
-        hv("q_len")[:] = 1
-        kv = hv("kv_len")
-        kv[:n] = positions + 1
-        kv[n:] = 1
-        slots = hv("seq_slots")
-        slots[:n] = [self.max_num_seqs if c.seq.slot is None else c.seq.slot for c in chunks]
-        slots[n:] = self.max_num_seqs
-        hv("logit_rows")[:] = np.arange(bucket, dtype=np.int32)
-        for g in range(len(self.cache.groups)):
-            slot_map = hv(f"slots{g}")
-            slot_map[:n] = [c.seq.tables[g][b] * P for c, b in zip(chunks, blocks)] + positions % P
-            slot_map[n:] = -1
-            tables = hv(f"tables{g}")
-            tables[:] = 0
-            for s, c in enumerate(chunks):
-                t = c.seq.tables[g]
-                tables[s, : len(t)] = t
+        index, views, held = stage.take()
+        fresh = held["count"] != n
+        if fresh:
+            stage.write_padding(index, n)
+            held["count"] = n
+        views["ids"][:n] = [c.tokens[0] for c in chunks]
+        views["positions"][:n] = positions
         kv_lens = positions + 1
+        views["kv_len"][:n] = kv_lens
+        views["seq_slots"][:n] = [self.max_num_seqs if c.seq.slot is None else c.seq.slot for c in chunks]
+        offsets = positions % P
+        rows = held["rows"]
+        for g in range(len(self.cache.groups)):
+            views[f"slots{g}"][:n] = np.fromiter(
+                (c.seq.tables[g][b] for c, b in zip(chunks, blocks)), np.int64, n) * P + offsets
+            tables = views[f"tables{g}"]
+            row_keys = rows[g]
+            for s, c in enumerate(chunks):
+                key = (c.seq.serial, c.seq.tables_version)
+                if row_keys[s] != key:
+                    t = c.seq.tables[g]
+                    tables[s, : len(t)] = t
+                    tables[s, len(t):] = 0
+                    row_keys[s] = key
         for key, (entry_where, merge_where) in plan_where.items():
-            opt = self._plan_options(key[1])
-            splits, _ = self._padded_splits(bucket, opt)
-            kind, items, merges, _ = ap.plan_single_tokens(kv_lens, bucket, splits, opt)
-            offset, shape = entry_where[kind]
-            host_np[offset : offset + items.size] = items.reshape(-1)
-            if merges is not None:
-                offset, shape = merge_where
-                host_np[offset : offset + merges.size] = merges.reshape(-1)
-        dev[:size].copy_(host[:size], non_blocking=True)
-        self._copied[self._flip ^ 1].record()
+            opt, splits = stage.plan_options.get(key, (None, None))
+            if opt is None:
+                opt = self._plan_options(key[1])
+                splits, _ = self._padded_splits(bucket, opt)
+                stage.plan_options[key] = (opt, splits)
+            items_view, merges_view = views[("items", key)], views.get(("merges", key))
+            if splits <= 1 and not fresh:
+                # Only the key ranges move from step to step.
+                lo = np.maximum(0, kv_lens - opt.window) if opt.window else 0
+                items_view[:n, 3] = lo
+                items_view[:n, 4] = kv_lens
+                continue
+            _, items, merges, _ = ap.plan_single_tokens(kv_lens, bucket, splits, opt)
+            items_view[:] = items
+            if merges is not None and merges_view is not None:
+                merges_view[:] = merges
+        host, dev = stage.buffers[index], self._device_for(size)
+        dev[:size].copy_(host, non_blocking=True)
+        stage.copied(index)
         self.last_meta_bytes = size * 4
         return True
+
+    def _device_for(self, size: int) -> torch.Tensor:
+        if self._device_meta is None or self._device_meta.numel() < size:
+            capacity = 1 << (max(size, 1 << 14) - 1).bit_length()
+            self._device_meta = torch.empty(capacity, dtype=torch.int32, device=self.device)
+            self._meta_generation += 1
+        return self._device_meta
 
     def _capture(self, bucket: int):
         # Twice eagerly on an all-padding batch: buffers get their final size and addresses.

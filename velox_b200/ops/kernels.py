@@ -58,6 +58,7 @@ def core():
         ]
         lib.vx_sample_segments.argtypes = [_c_int, _c_int]
         lib.vx_selftest_bounded_wait.argtypes = [_ptr, _c_ll, _ptr, _ptr]
+        lib.vx_l2_prefetch.argtypes = [_ptr, _c_ll, _ptr]
         lib.vx_gemm_bf16_add_mirrored.argtypes = [
             _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_int, _ptr, _ptr,
         ]
@@ -121,12 +122,23 @@ def _stream() -> int:
 # Launcher calls made so far (each is at least one kernel of this package).
 launch_count = 0
 
+# While this is a list, every launcher call appends (launcher name, a CUDA event recorded right
+# after its launch).  With the host running ahead of the device (the caller queues a delay
+# first), the time between consecutive events is the device time of each launch, without a
+# profiler.  An event between two kernels also keeps the second from starting early, so the
+# times are those of kernels that run one after the other.
+launch_events: Optional[list] = None
+
 
 def _check(code: int, what: str) -> None:
     global launch_count
     launch_count += 1
     if code != 0:
         raise KernelError(f"{what}: CUDA error {code} at launch")
+    if launch_events is not None:
+        event = torch.cuda.Event(enable_timing=True)
+        event.record()
+        launch_events.append((what, event))
 
 
 def _p(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -161,6 +173,13 @@ def selftest_bounded_wait(status: torch.Tensor, limit_cycles: int) -> int:
     _check(core().vx_selftest_bounded_wait(_p(status), int(limit_cycles), _p(returned), _stream()),
            "selftest_bounded_wait")
     return int(returned.item())
+
+
+def l2_prefetch(tensor: torch.Tensor) -> None:
+    """Ask the L2 for a contiguous tensor's bytes; returns at once."""
+    if not tensor.is_contiguous():
+        raise ValueError("l2_prefetch wants a contiguous tensor")
+    _check(core().vx_l2_prefetch(_p(tensor), tensor.numel() * tensor.element_size(), _stream()), "l2_prefetch")
 
 
 def embed(table: torch.Tensor, ids: torch.Tensor, resid: torch.Tensor, status: torch.Tensor) -> None:
