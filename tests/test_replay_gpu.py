@@ -347,3 +347,37 @@ def test_padded_step_staging_equals_prepare(models, case):
         for name in names:
             cache.advance(live[name], 1)
     assert compared == 150
+
+
+@pytest.mark.parametrize("case", ["tiny_d", "tiny_w"])
+def test_mixed_steps_replayed_as_graphs(models, case):
+    """Steps of any shape are laid out with rounded extents and, from the second time a shape
+    comes, captured and replayed.  The same mixed trace three times over: the third pass runs
+    on replayed graphs and must give the logits of the plain implementation, like the first."""
+    folder, cfg, page, prompts, want = models[case]
+    seqs = [prompts[i] for i in (0, 2, 3, 4)]
+    refs = [want[i] for i in (0, 2, 3, 4)]
+    need = sum(-(-len(p) // 64) * 64 for p in seqs)
+    replayer = make_replayer(folder, "bfloat16", max_tokens=need, page=page)
+    runner = replayer.runner
+    assert runner._mixed_graphs_on
+    steps = mixed_trace(seqs, np.random.default_rng(9))
+    passes = []
+    for round_index in range(3):
+        replayed_before = runner.kernels_replayed
+        got = [np.zeros((len(p), cfg["vocab_size"]), np.float32) for p in seqs]
+        for step, entries, ends in steps:
+            rec = {"step": step, "end": [f"r{r}" for r in ends],
+                   "entries": [{"id": f"r{r}", "tokens": seqs[r][s : s + n], "want": list(range(n))} for r, s, n in entries]}
+            out = replayer.run_step(rec)
+            row = 0
+            for r, s, n in entries:
+                got[r][s : s + n] = out[row : row + n]
+                row += n
+        for r, ref in enumerate(refs):
+            check(got[r], ref, "bfloat16", f"{case} pass {round_index} request {r}")
+        passes.append(runner.kernels_replayed - replayed_before)
+        assert replayer.cache.num_free_pages() == replayer.cache.num_total_pages
+    assert len(runner._mixed_graphs) > 0
+    # every step of the third pass was a replay: as many kernels as steps x launches, none eager
+    assert passes[2] > passes[1] > passes[0] >= 0

@@ -457,6 +457,28 @@ def test_planner_with_arrays_equals_the_plain_one():
         assert all(np.array_equal(plain.items[kind], both.items[kind]) for kind in plain.items)
 
 
+def test_rounded_plans_only_add_padding():
+    import numpy as np
+
+    from velox_b200.engine.runner import ModelRunner
+    from velox_b200.ops import attention_plan as ap
+
+    assert [ModelRunner._round_tokens(n) for n in (1, 16, 17, 128, 129, 520, 1024, 1025, 2048)] == \
+        [16, 16, 32, 128, 160, 544, 1024, 1088, 2048]
+    assert [ModelRunner._round_count(n) for n in (0, 1, 3, 8, 9, 24, 25)] == [0, 1, 4, 8, 16, 24, 32]
+    opt = ap.PlanOptions(num_kv_heads=2, group=6, window=None, use_f32=False, target_ctas=64, narrow_max_cluster=1)
+    plan = ap.plan_attention([300, 1, 1, 5], [900, 700, 64, 5], opt)
+    rounded = ap.round_plan(plan, ModelRunner._round_count)
+    assert rounded.partial_rows == plan.partial_rows and rounded.cluster == plan.cluster
+    for kind, items in plan.items.items():
+        padded = rounded.items[kind]
+        assert len(padded) == ModelRunner._round_count(len(items)) and padded.dtype == np.int32
+        assert np.array_equal(padded[: len(items)], items)
+        assert (padded[len(items):, 0] == -1).all() and (padded[len(items):, 5] == -1).all()
+    assert np.array_equal(rounded.merge_items[: len(plan.merge_items)], plan.merge_items)
+    assert (rounded.merge_items[len(plan.merge_items):, 0] == -1).all()
+
+
 def test_engine_loop_with_a_fake_model():
     """``Engine.step`` and ``generate`` around a runner and a sampler that are stand-ins: portions
     reach the runner in order, the last token of a prompt asks for logits, sampled tokens come

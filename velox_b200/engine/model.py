@@ -111,6 +111,13 @@ class CausalLM:
                 seen.append(key)
         return seen
 
+    def parts_take_padded_steps(self) -> bool:
+        """Whether every mixer and feed-forward has said that it takes steps whose arrays are
+        padded with tokens of no sequence (``takes_padded_steps``): only then are steps of any
+        shape captured and replayed."""
+        return all(getattr(part, "takes_padded_steps", False)
+                   for block in self.blocks for part in (block.mixer, block.feed_forward))
+
     def head_dims(self) -> List[int]:
         dims = []
         for needs in self.entry_needs:

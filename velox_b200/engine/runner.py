@@ -19,6 +19,7 @@ progress after it (``CacheManager.advance``).
 """
 from __future__ import annotations
 
+from collections import OrderedDict
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -264,6 +265,13 @@ class ModelRunner:
         # splits of a captured step its results do not depend on how the work was cut.
         self.enable_graphs = enable_graphs and self.dtype != torch.float32
         self._graphs: Dict[int, tuple] = {}
+        # Captured steps of other shapes, by rounded shape; the shapes used last are kept.
+        self._mixed_graphs: "OrderedDict[tuple, tuple]" = OrderedDict()
+        self._mixed_graphs_kept = 64
+        self._mixed_seen: Dict[tuple, int] = {}
+        self._mixed_graphs_on = (self.enable_graphs and os.environ.get("VELOX_B200_NO_MIXED_GRAPHS") != "1"
+                                 and model.parts_take_padded_steps())
+        self._last_shape: Tuple[tuple, int] = ((), 0)
         self._padded_stages: Dict[int, "_PaddedStage"] = {}
         self._graphs_broken = False
         self._meta_generation = 0
@@ -312,12 +320,79 @@ class ModelRunner:
             if logits is not None:
                 self.num_steps += 1
                 return logits
+        if self._mixed_graphs_on:
+            logits = self._mixed_step(chunks)
+            self.num_steps += 1
+            return logits
         ctx, ids, logit_rows, num_logit_rows = self.prepare(chunks)
         logits = self.model.forward(ctx, self.layer_caches, ids, logit_rows, num_logit_rows)
         self.num_steps += 1
         return logits
 
-    def prepare(self, chunks: Sequence[StepChunk], pad_to: Optional[int] = None):
+    # ------------------------------------------------------------------ mixed steps as CUDA graphs
+    def _mixed_step(self, chunks: Sequence[StepChunk]) -> Optional[torch.Tensor]:
+        """A step of any shape, laid out with its arrays padded to round sizes (``prepare`` with
+        ``round_shape``) so that steps of the same rounded shape run the same launches on the
+        same buffers.  The first step of a shape runs launch by launch; from the second on the
+        shape has a captured graph and a step costs the host its layout, one copy and one
+        launch, where the launches of a 512-token step cost it about twice what they cost the
+        device.  Graphs are kept for the shapes used last."""
+        ctx, ids, logit_rows, num_logit_rows = self.prepare(chunks, round_shape=True)
+        key, wanted = self._last_shape
+        entry = self._mixed_graphs.get(key)
+        generation = (self.workspace.generation, self._meta_generation)
+        if entry is not None and entry[2] == generation:
+            self._mixed_graphs.move_to_end(key)
+            entry[0].replay()
+            self.kernels_replayed += entry[3]
+            return None if wanted == 0 else entry[1][:wanted]
+        logits = self.model.forward(ctx, self.layer_caches, ids, logit_rows, num_logit_rows)
+        seen = self._mixed_seen.get(key, 0) + 1
+        self._mixed_seen[key] = seen
+        if len(self._mixed_seen) > 4096:
+            self._mixed_seen.clear()
+        if seen >= 2 and not self._graphs_broken:
+            # The shape has come back: capture what has just run (the capture itself runs nothing).
+            try:
+                graph = torch.cuda.CUDAGraph()
+                launches_before = kernels.launch_count
+                collecting = gc.isenabled()
+                gc.disable()
+                try:
+                    with torch.cuda.graph(graph):
+                        captured = self.model.forward(ctx, self.layer_caches, ids, logit_rows, num_logit_rows)
+                finally:
+                    if collecting:
+                        gc.enable()
+                if generation == (self.workspace.generation, self._meta_generation):
+                    self._mixed_graphs[key] = (graph, captured, generation, kernels.launch_count - launches_before)
+                    while len(self._mixed_graphs) > self._mixed_graphs_kept:
+                        self._mixed_graphs.popitem(last=False)
+            except Exception as exc:  # a part that cannot be captured: run launch by launch from now on
+                import logging
+
+                logging.getLogger(__name__).warning("CUDA graph capture of a mixed step failed (%s); running eagerly", exc)
+                self._mixed_graphs_on = False
+                torch.cuda.synchronize(self.device)
+        return None if logits is None else logits[:wanted]
+
+    @staticmethod
+    def _round_tokens(count: int) -> int:
+        """Token counts that share a captured step: multiples of 16 up to 128, of 32 up to 1,024,
+        of 64 beyond (the padding rows cost what real rows cost)."""
+        step = 16 if count <= 128 else 32 if count <= 1024 else 64
+        return -(-count // step) * step
+
+    @staticmethod
+    def _round_count(count: int, granule: int = 8) -> int:
+        """Powers of two up to the granule, multiples of it beyond."""
+        if count <= 0:
+            return 0
+        if count <= granule:
+            return 1 << (count - 1).bit_length()
+        return -(-count // granule) * granule
+
+    def prepare(self, chunks: Sequence[StepChunk], pad_to: Optional[int] = None, round_shape: bool = False):
         """Build the step's device-side description: (context, token ids, logit rows, their count).
 
         ``pad_to`` (single-token steps only) pads the batch to that many sequences with rows
@@ -325,6 +400,13 @@ class ModelRunner:
         logits are never looked at.  A padded step has the same shape whatever the real batch
         is, every array lands at the same place of the device buffer, and the logits of all
         ``pad_to`` rows are computed.
+
+        ``round_shape`` (any step) rounds every extent up: tokens, sequences, wanted rows, the
+        work items of each kernel family and the merge items, and gives the block tables their
+        full width.  Padding tokens belong to no sequence, write to no cache slot and are
+        covered by no work item; padding items have sequence -1 and do nothing.  Steps with
+        equal rounded extents get equal layouts; ``self._last_shape`` is (the extents as a
+        key, the number of rows really wanted).
         """
         P = self.page_size
         real_seqs = len(chunks)
@@ -383,6 +465,22 @@ class ModelRunner:
         if padded:
             width = self.cache.max_blocks_per_seq
             logit_rows = list(range(num_seqs))
+        wanted_rows = len(logit_rows)
+        if round_shape and not padded:
+            real_tokens = num_tokens
+            num_tokens = min(self.max_tokens, self._round_tokens(real_tokens))
+            num_seqs = min(self.max_num_seqs, 1 << (real_seqs - 1).bit_length())
+            extra = num_tokens - real_tokens
+            ids = np.concatenate([ids, np.zeros(extra, np.int32)])
+            positions = np.concatenate([positions, np.zeros(extra, np.int32)])
+            slot_maps = [np.concatenate([m, np.full(extra, -1, np.int32)]) for m in slot_maps]
+            more = num_seqs - real_seqs
+            q_start = np.concatenate([q_start, np.full(more, real_tokens, np.int32)])
+            q_len_arr = np.concatenate([q_len_arr[:real_seqs], np.zeros(more, np.int32)])
+            kv_len_arr = np.concatenate([kv_len_arr[:real_seqs], np.zeros(more, np.int32)])
+            seq_slots = np.concatenate([seq_slots[:real_seqs], np.full(more, self.max_num_seqs, np.int32)])
+            width = self.cache.max_blocks_per_seq
+            logit_rows = logit_rows + [0] * (self._round_count(wanted_rows) - wanted_rows)
         width = (width + 7) // 8 * 8
         tables = [np.zeros((num_seqs, width), np.int32) for _ in range(num_groups)]
         for s, chunk in enumerate(chunks):
@@ -403,7 +501,17 @@ class ModelRunner:
                 plan = ap.pad_plan(plan, num_seqs, splits, opt)
             else:
                 plan = ap.plan_attention(q_lens, kv_lens, opt)
+                if round_shape:
+                    plan = ap.round_plan(plan, self._round_count)
             host_plans[(group, signature)] = plan
+        if round_shape and not padded:
+            self._last_shape = (
+                (num_tokens, num_seqs, len(logit_rows), width, tuple(
+                    (key, plan.cluster, tuple((kind, len(items)) for kind, items in sorted(plan.items.items())),
+                     len(plan.merge_items), plan.partial_rows > 0)
+                    for key, plan in host_plans.items())),
+                wanted_rows,
+            )
 
         packer = _Packer()
         where = {

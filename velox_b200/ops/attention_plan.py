@@ -312,6 +312,25 @@ def plan_attention_plain(
     return plan
 
 
+def round_plan(plan: AttentionPlan, round_count) -> AttentionPlan:
+    """The same work with every array padded to ``round_count(length)`` entries: padding work
+    items and merge items have sequence -1 and do nothing.  Plans of steps that differ a little
+    then have equal array sizes."""
+    out = AttentionPlan(partial_rows=plan.partial_rows, cluster=plan.cluster)
+    for kind, items in plan.items.items():
+        padding = np.zeros((round_count(len(items)) - len(items), ITEM_WIDTH), np.int32)
+        padding[:, 0] = -1
+        padding[:, 5] = -1
+        out.items[kind] = np.concatenate([items.astype(np.int32, copy=False), padding], axis=0)
+    merges = plan.merge_items
+    if len(merges):
+        padding = np.zeros((round_count(len(merges)) - len(merges), ITEM_WIDTH), np.int32)
+        padding[:, 0] = -1
+        merges = np.concatenate([merges, padding], axis=0)
+    out.merge_items = merges
+    return out
+
+
 def pad_plan(plan: AttentionPlan, num_seqs: int, splits: int, opt: PlanOptions) -> AttentionPlan:
     """Give a plan of single-token sequences (made with ``fixed_splits=splits``) the shape it
     would have with ``num_seqs`` sequences: missing work items are padding (seq = -1).  The

@@ -65,6 +65,9 @@ class Attention(Mixer):
 
     # The input is used by the QKV projection only, which can make the norm itself.
     accepts_pending_norm = True
+    # Rows of tokens that belong to no sequence (padding of a rounded step) pass through like any
+    # other row and are looked at by nobody.
+    takes_padded_steps = True
 
     def forward(self, x, ctx, cache):
         T = ctx.num_tokens

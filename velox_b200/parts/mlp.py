@@ -30,6 +30,9 @@ class SwiGLU(FeedForward):
 
     # The input is used by the gate|up projection only, which can make the norm itself.
     accepts_pending_norm = True
+    # Rows of tokens that belong to no sequence (padding of a rounded step) pass through like any
+    # other row and are looked at by nobody.
+    takes_padded_steps = True
 
     def _fusable(self, T, ctx) -> bool:
         return (_FUSE_MLP and 0 < T <= kernels.MLP_FUSED_MAX_TOKENS and self.dtype == torch.bfloat16
