@@ -519,3 +519,113 @@ def test_toy_architecture_with_routed_feed_forward_and_its_own_position_encoding
         unregister_architecture(ROUTED_ARCH)
         unregister_part("feed_forward", "toy_top1_experts")
         unregister_part("position", "toy_rotary_pairs")
+
+
+# ----------------------------------------------------------------------------------------------
+# A third toy architecture: attention layers of different head sizes in one model
+# ----------------------------------------------------------------------------------------------
+TWO_SIZES_ARCH = "ToyTwoHeadSizesForCausalLM"
+TWO_SIZES_LAYERS = ((4, 2, 16), (2, 1, 32), (4, 4, 16))  # (heads, KV heads, head size) per layer
+
+
+def register_two_head_sizes():
+    from velox_b200.config import ModelConfig, register_architecture
+    from velox_b200.parts.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, TensorSource, WeightSpec
+
+    @dataclass(frozen=True)
+    class Config(ModelConfig):
+        intermediate_size: int = 64
+
+        def to_json_dict(self):
+            return {"architectures": [self.architecture], "vocab_size": self.vocab_size, "hidden_size": self.hidden_size,
+                    "num_hidden_layers": self.num_hidden_layers, "max_position_embeddings": self.max_position_embeddings,
+                    "tie_word_embeddings": self.tie_word_embeddings, "intermediate_size": self.intermediate_size}
+
+    def parse(cfg: Mapping[str, Any]) -> Config:
+        return Config(architecture=TWO_SIZES_ARCH, vocab_size=cfg["vocab_size"], hidden_size=cfg["hidden_size"],
+                      num_hidden_layers=cfg["num_hidden_layers"], max_position_embeddings=cfg["max_position_embeddings"],
+                      tie_word_embeddings=cfg["tie_word_embeddings"], intermediate_size=cfg["intermediate_size"])
+
+    def build(c: Config) -> ModelSpec:
+        E, I, V = c.hidden_size, c.intermediate_size, c.vocab_size
+        mat = lambda *src: WeightSpec(tuple(src), "matrix")
+        vec = lambda *src: WeightSpec(tuple(src), "vector")
+        rms = lambda name: PartSpec("rms", {"size": E, "eps": 1e-6}, {"weight": vec(TensorSource(name, (E,), "one_plus_normal"))})
+        layers = []
+        for index, (H, G, D) in enumerate(TWO_SIZES_LAYERS):
+            p = f"l{index}."
+            position = PartSpec("rotary_half", {"head_dim": D, "rotary_dim": D, "theta": 10000.0, "scaling_factor": 1.0,
+                                                "max_position": c.max_position_embeddings})
+            mixer = PartSpec("attention", {"hidden_size": E, "num_heads": H, "num_kv_heads": G, "head_dim": D, "qkv_bias": False,
+                                           "window": None, "softmax_scale": 1 / math.sqrt(D)}, {
+                "qkv.weight": mat(TensorSource(p + "q.weight", (H * D, E)), TensorSource(p + "k.weight", (G * D, E)),
+                                  TensorSource(p + "v.weight", (G * D, E))),
+                "out.weight": mat(TensorSource(p + "o.weight", (E, H * D)))})
+            ffn = PartSpec("swiglu", {"hidden_size": E, "intermediate_size": I}, {
+                "gate_up.weight": mat(TensorSource(p + "gate.weight", (I, E)), TensorSource(p + "up.weight", (I, E))),
+                "down.weight": mat(TensorSource(p + "down.weight", (E, I)))})
+            layers.append(LayerSpec("pre_norm", mixer, ffn, {"mixer": rms(p + "n1"), "feed_forward": rms(p + "n2")}, position))
+        embed = TensorSource("embed.weight", (V, E))
+        return ModelSpec(
+            architecture=TWO_SIZES_ARCH, hidden_size=E, vocab_size=V, max_position=c.max_position_embeddings,
+            embedding=PartSpec("token_embedding", {"vocab_size": V, "hidden_size": E}, {"weight": mat(embed)}),
+            layers=tuple(layers), schedule=tuple(ScheduleEntry(i) for i in range(len(layers))),
+            final_norm=rms("final.weight"),
+            lm_head=PartSpec("linear_head", {"hidden_size": E, "vocab_size": V}, {"weight": mat(embed)}))
+
+    register_architecture(TWO_SIZES_ARCH, parse, build)
+
+
+def two_sizes_plain_logits(tensors, tokens):
+    t = {k: v.double() for k, v in tensors.items()}
+    T = len(tokens)
+    h = t["embed.weight"][torch.tensor(tokens)]
+    for index, (H, G, D) in enumerate(TWO_SIZES_LAYERS):
+        p = f"l{index}."
+        ang = plain_model.rope_angles(D, 10000.0, 1.0, torch.arange(T)).double()
+        x = plain_model.rms_norm(h, t[p + "n1"], 1e-6)
+        q = plain_model.rotate_half((x @ t[p + "q.weight"].T).view(T, H, D), ang.cos(), ang.sin())
+        k = plain_model.rotate_half((x @ t[p + "k.weight"].T).view(T, G, D), ang.cos(), ang.sin())
+        v = (x @ t[p + "v.weight"].T).view(T, G, D)
+        o = plain_model.causal_attention(q, k, v, 1 / math.sqrt(D))
+        h = h + o.reshape(T, H * D) @ t[p + "o.weight"].T
+        x = plain_model.rms_norm(h, t[p + "n2"], 1e-6)
+        h = h + plain_model.swiglu_mlp(x, t[p + "gate.weight"], t[p + "up.weight"], t[p + "down.weight"])
+    return plain_model.rms_norm(h, t["final.weight"], 1e-6) @ t["embed.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_with_two_head_sizes(tmp_path, dtype):
+    """Layers whose attention differs in head size (and in head counts) in one model: every
+    signature gets a work layout and scratch of its own head size, and long single-token steps
+    with split key ranges (forced here) stay right in both."""
+    from velox_b200.config import unregister_architecture
+    from velox_b200.engine.replay import TraceReplayer
+    from velox_b200.weights import write_random_model
+
+    register_two_head_sizes()
+    try:
+        cfg = {"architectures": [TWO_SIZES_ARCH], "vocab_size": 211, "hidden_size": 64, "num_hidden_layers": 3,
+               "max_position_embeddings": 512, "tie_word_embeddings": True, "intermediate_size": 96}
+        folder = str(tmp_path)
+        write_random_model(folder, cfg, seed=8, dtype="bfloat16", std=0.08)
+        tensors = read_tensors(folder)
+        tokens = random_prompts(211, (300,), seed=6)[0]
+        want = two_sizes_plain_logits(tensors, tokens)
+        replayer = TraceReplayer(folder, dtype, max_tokens=320, block_size=16,
+                                 plan_overrides={"min_split_keys": 64, "target_ctas": 4096})
+        signatures = replayer.runner._signatures
+        assert sorted({sig[3] for _, sig in signatures}) == [16, 32] and len(signatures) == 3
+        rows, start = [], 0
+        for step, n in enumerate([150, 2, 100] + [1] * 48):
+            out = replayer.run_step({"step": step, "end": ["r"] if start + n == 300 else [],
+                                     "entries": [{"id": "r", "tokens": tokens[start : start + n], "want": list(range(n))}]})
+            rows.append(out)
+            start += n
+        got = torch.from_numpy(np.concatenate(rows)).double()
+        tol = 2e-5 if dtype == "float32" else 3e-2
+        err = (got - want).abs().max().item()
+        assert err <= tol * want.abs().max().item(), (err, want.abs().max().item())
+        assert replayer.cache.num_free_pages() == replayer.cache.num_total_pages
+    finally:
+        unregister_architecture(TWO_SIZES_ARCH)

@@ -270,6 +270,8 @@ def main(argv: Optional[List[str]] = None) -> int:
             for request in result["requests"]:
                 print(request.request_id, request.output_token_ids)
         stats = engine.snapshot()
+        print("steps with prompt portions: " + ", ".join(
+            f"{int(stats.get('mixed_steps_' + how, 0))} {how}" for how in ("replayed", "eager", "captured")))
         table.append({"max_num_seqs": max_num_seqs, **{k: v for k, v in result.items() if k != "requests"},
                       "total_blocks": stats["total_blocks"]})
         del engine

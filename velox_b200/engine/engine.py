@@ -289,6 +289,8 @@ class Engine:
         stats = self.scheduler.stats()
         stats["num_steps"] = float(self.num_steps)
         stats["kv_cache_bytes"] = float(self.runner.kv_cache_bytes())
+        for how, count in getattr(self.runner, "mixed_step_counts", {}).items():
+            stats[f"mixed_steps_{how}"] = float(count)
         return stats
 
 

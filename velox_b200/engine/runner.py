@@ -269,6 +269,8 @@ class ModelRunner:
         self._mixed_graphs: "OrderedDict[tuple, tuple]" = OrderedDict()
         self._mixed_graphs_kept = 64
         self._mixed_seen: Dict[tuple, int] = {}
+        # How the steps that are not single-token steps ran: replayed, launch by launch, captured.
+        self.mixed_step_counts = {"replayed": 0, "eager": 0, "captured": 0}
         self._mixed_graphs_on = (self.enable_graphs and os.environ.get("VELOX_B200_NO_MIXED_GRAPHS") != "1"
                                  and model.parts_take_padded_steps())
         self._last_shape: Tuple[tuple, int] = ((), 0)
@@ -345,8 +347,10 @@ class ModelRunner:
             self._mixed_graphs.move_to_end(key)
             entry[0].replay()
             self.kernels_replayed += entry[3]
+            self.mixed_step_counts["replayed"] += 1
             return None if wanted == 0 else entry[1][:wanted]
         logits = self.model.forward(ctx, self.layer_caches, ids, logit_rows, num_logit_rows)
+        self.mixed_step_counts["eager"] += 1
         seen = self._mixed_seen.get(key, 0) + 1
         self._mixed_seen[key] = seen
         if len(self._mixed_seen) > 4096:
@@ -366,6 +370,7 @@ class ModelRunner:
                         gc.enable()
                 if generation == (self.workspace.generation, self._meta_generation):
                     self._mixed_graphs[key] = (graph, captured, generation, kernels.launch_count - launches_before)
+                    self.mixed_step_counts["captured"] += 1
                     while len(self._mixed_graphs) > self._mixed_graphs_kept:
                         self._mixed_graphs.popitem(last=False)
             except Exception as exc:  # a part that cannot be captured: run launch by launch from now on
