@@ -712,9 +712,11 @@ static bool tensor_map_2d(CUtensorMap* map, const void* base, long long rows, lo
   return true;
 }
 
+// `one_wave`: launch only if all the grid's clusters are resident at once with this variant's
+// shared memory (-2 otherwise: the caller takes the variant of which an SM holds two CTAs).
 template <int BN, int STAGES_>
 static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx,
-                       const GemmArgs& g, dim3 grid, cudaStream_t stream) {
+                       const GemmArgs& g, dim3 grid, cudaStream_t stream, bool one_wave = false) {
   using S = GemmShape<BN, STAGES_>;
   // The most dynamic shared memory a CTA may have beside the kernel's static arrays.
   static int dynamic_limit = 0;
@@ -758,6 +760,28 @@ static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mw2, const CUte
   }
   config.attrs = attributes;
   config.numAttrs = count;
+  if (one_wave && g.splits > 1) {
+    // Clusters of this size and shared memory that the device holds at a time (asked once).
+    static std::map<std::pair<size_t, int>, int> held;
+    static std::mutex held_lock;
+    int active = 0;
+    {
+      std::lock_guard<std::mutex> guard(held_lock);
+      const auto key = std::make_pair(smem, g.splits);
+      auto it = held.find(key);
+      if (it == held.end()) {
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, gemm_bf16_kernel<BN, STAGES_>, &config) != cudaSuccess) {
+          (void)cudaGetLastError();
+          clusters = 0;
+        }
+        it = held.emplace(key, clusters).first;
+      }
+      active = it->second;
+    }
+    const long long clusters_wanted = (long long)grid.x * grid.y;
+    if (active > 0 && clusters_wanted > active) return -2;
+  }
   return (int)cudaLaunchKernelEx(&config, gemm_bf16_kernel<BN, STAGES_>, mw, mw2, mx, g);
 }
 
@@ -1172,11 +1196,11 @@ static int gemm_bf16(const void* x, int x_rows, const float* resid, long long re
                     (long long)grid.x * grid.y * grid.z <= (long long)sm_count();
   switch (bn) {
     case 16: {
-      const int code = deep ? launch_gemm<16, 8>(mw, mw2, mx, g, grid, stream) : -2;
+      const int code = deep ? launch_gemm<16, 8>(mw, mw2, mx, g, grid, stream, true) : -2;
       return code != -2 ? code : launch_gemm<16, 4>(mw, mw2, mx, g, grid, stream);
     }
     case 32: {
-      const int code = deep ? launch_gemm<32, 8>(mw, mw2, mx, g, grid, stream) : -2;
+      const int code = deep ? launch_gemm<32, 8>(mw, mw2, mx, g, grid, stream, true) : -2;
       return code != -2 ? code : launch_gemm<32, 4>(mw, mw2, mx, g, grid, stream);
     }
     // A short K chunk needs no deep ring, and with two stages two CTAs share an SM: sixteen
