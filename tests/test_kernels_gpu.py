@@ -916,3 +916,22 @@ def test_bounded_wait_runs_out_and_reports(k, tmp_path):
     with pytest.raises(RuntimeError, match="a bounded wait ran out"):
         runner.check_status()
     assert int(status[0].item()) == 0
+
+
+@pytest.mark.parametrize("T,N,K,chunks", [(8, 1536, 8960, 24), (64, 5120, 1600, 3), (3, 331, 240, 2), (130, 136, 1352, 5),
+                                          (200, 640, 4096, 9), (17, 384, 200, 50), (1, 128, 64, 4)])
+def test_gemm_bf16_add_chunked(k, status, T, N, K, chunks):
+    """out += x w^T with the inner dimension in chunks of independent CTAs that meet in the
+    output by reductions at the L2: any number of chunks (more than there are K blocks is cut
+    down), widths and rows that are no multiple of a tile, what was in the output kept."""
+    gen = torch.Generator().manual_seed(N + K + T)
+    x = torch.randn(T + 3, K, generator=gen).to(torch.bfloat16).cuda()
+    w = (torch.randn(N, K, generator=gen) / math.sqrt(K)).to(torch.bfloat16).cuda()
+    start = torch.randn(T + 2, N, generator=gen).cuda()
+    out = start.clone()
+    k.gemm_bf16_add_chunked(x, w, out, T, status, chunks)
+    want = start[:T].double() + x[:T].double() @ w.double().T
+    torch.cuda.synchronize()
+    assert (out[:T].double() - want).abs().max().item() <= 2e-5 * want.abs().max().item()
+    assert torch.equal(out[T:], start[T:])  # rows past the step are not touched
+    assert int(status[0]) == 0

@@ -379,24 +379,6 @@ __global__ void cast_bf16_to_f32_kernel(const __nv_bfloat16* __restrict__ in,
 }
 
 // ---------------------------------------------------------------------------------------------
-// Ask the L2 for a range of global memory (a matrix the next kernels will stream, pages of the
-// cache): one bulk prefetch per 32 KB piece, nothing waits for them.
-// ---------------------------------------------------------------------------------------------
-constexpr unsigned int L2_PREFETCH_PIECE = 32768;
-
-__global__ void l2_prefetch_kernel(const unsigned char* base, unsigned long long bytes) {
-  allow_dependents();
-  const unsigned long long pieces = (bytes + L2_PREFETCH_PIECE - 1) / L2_PREFETCH_PIECE;
-  for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < pieces;
-       i += (unsigned long long)gridDim.x * blockDim.x) {
-    const unsigned long long off = i * L2_PREFETCH_PIECE;
-    const unsigned long long left = bytes - off;
-    const unsigned int n = (unsigned int)(left < L2_PREFETCH_PIECE ? left : L2_PREFETCH_PIECE) & ~15u;
-    if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + off), "r"(n) : "memory");
-  }
-}
-
-// ---------------------------------------------------------------------------------------------
 // Self-test of the bounded wait: one CTA arms a barrier that nobody will ever arrive at and
 // waits for it through the helper every kernel of this package waits with, with a short limit.
 // The wait has to run out, set VX_STATUS_WAIT_TIMEOUT and let the kernel return normally.
@@ -646,19 +628,5 @@ VX_API int vx_selftest_bounded_wait(int* status, long long limit_cycles, int* re
   unsigned long long limit = (unsigned long long)limit_cycles;
   if (limit > VX_WAIT_CYCLES) limit = VX_WAIT_CYCLES;
   bounded_wait_selftest_kernel<<<1, 64, 0, stream>>>(status, limit, returned);
-  return (int)cudaGetLastError();
-}
-
-// Prefetch [base, base + bytes) into the L2 (base 16-byte aligned).  Returns at once; the
-// copies run behind whatever the stream does next.
-VX_API int vx_l2_prefetch(const void* base, long long bytes, cudaStream_t stream) {
-  if (base == nullptr || bytes <= 0) return 0;
-  if (reinterpret_cast<uintptr_t>(base) & 15) return (int)cudaErrorInvalidValue;
-  const long long pieces = (bytes + L2_PREFETCH_PIECE - 1) / L2_PREFETCH_PIECE;
-  const int threads = 128;
-  long long blocks = (pieces + threads - 1) / threads;
-  if (blocks > 148) blocks = 148;
-  launch_pdl(l2_prefetch_kernel, dim3((int)blocks), dim3(threads), 0, stream, (const unsigned char*)base,
-             (unsigned long long)bytes);
   return (int)cudaGetLastError();
 }

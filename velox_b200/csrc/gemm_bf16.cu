@@ -1116,7 +1116,7 @@ static int gemm_bf16(const void* x, int x_rows, const float* resid, long long re
                      const float* norm_w, float eps, const void* w, const float* bias, void* out,
                      int mode, int T, int N, int K, long long ldy, int splits, int* status,
                      cudaStream_t stream, const RopeArgs* rope = nullptr, float* out2 = nullptr,
-                     long long ld2 = 0) {
+                     long long ld2 = 0, int chunks = 1) {
   if (T <= 0 || N <= 0) return 0;
   if (K <= 0 || (K % 8) != 0) return -1;
   const bool normed = resid != nullptr;
@@ -1148,6 +1148,18 @@ static int gemm_bf16(const void* x, int x_rows, const float* resid, long long re
   g.mode = mode;
   g.kb_per_split = (num_kb + splits - 1) / splits;
   g.splits = splits;
+  // K in chunks of independent CTAs (mode 2 only): every CTA adds its partial tile to the output
+  // by reductions at the L2, so no cluster and any number of chunks; the order of the additions
+  // is then not fixed.
+  if (chunks > 1) {
+    if (mode != 2 || normed || bias != nullptr || out2 != nullptr || rope != nullptr) return -1;
+    if (chunks > num_kb) chunks = num_kb;
+    g.splits = 1;
+    g.kb_per_split = (num_kb + chunks - 1) / chunks;
+    chunks = (num_kb + g.kb_per_split - 1) / g.kb_per_split;  // no empty chunk
+  } else {
+    chunks = 1;
+  }
   g.resid = resid;
   g.norm_w = norm_w;
   g.resid_ld = resid_ld;
@@ -1190,7 +1202,7 @@ static int gemm_bf16(const void* x, int x_rows, const float* resid, long long re
     if (!tensor_map_2d(&mx, x, x_rows, K, bn)) return -1;
   }
   const int n_tile = mode == 3 ? 64 : GB_BM;
-  const dim3 grid((N + n_tile - 1) / n_tile, (T + bn - 1) / bn, splits);
+  const dim3 grid((N + n_tile - 1) / n_tile, (T + bn - 1) / bn, chunks > 1 ? chunks : splits);
   // A grid that gives an SM one CTA at most keeps more tiles in flight per CTA instead.
   const bool deep = bn <= 32 && g.kb_per_split > 4 &&
                     (long long)grid.x * grid.y * grid.z <= (long long)sm_count();
@@ -1228,6 +1240,16 @@ VX_API int vx_gemm_bf16_add_mirrored(const void* x, const void* w, float* out, f
   if (out2 == nullptr) return -1;
   return gemm_bf16(x, x_rows, nullptr, 0, nullptr, 0.f, w, nullptr, out, 2, T, N, K, ldy, splits, status,
                    stream, nullptr, out2, ld2);
+}
+
+// Mode 2 (out += x w^T, float32) with K cut into `chunks` ranges that independent CTAs take:
+// each adds its partial tile to `out` by float32 reductions at the L2.  Fills the GPU whatever
+// the number of output tiles (a cluster holds eight CTAs at most and wants a power of two);
+// the order of the additions, and with it the last bits of the sums, is not fixed.
+VX_API int vx_gemm_bf16_add_chunked(const void* x, const void* w, float* out, int T, int x_rows, int N, int K,
+                                    long long ldy, int chunks, int* status, cudaStream_t stream) {
+  return gemm_bf16(x, x_rows, nullptr, 0, nullptr, 0.f, w, nullptr, out, 2, T, N, K, ldy, 1, status, stream,
+                   nullptr, nullptr, 0, chunks < 1 ? 1 : chunks);
 }
 
 // The same product on rmsnorm(resid) * norm_w: resid [T, resid_ld] float32, norm_w [K] float32.

@@ -58,7 +58,6 @@ def core():
         ]
         lib.vx_sample_segments.argtypes = [_c_int, _c_int]
         lib.vx_selftest_bounded_wait.argtypes = [_ptr, _c_ll, _ptr, _ptr]
-        lib.vx_l2_prefetch.argtypes = [_ptr, _c_ll, _ptr]
         lib.vx_gemm_bf16_add_mirrored.argtypes = [
             _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_int, _ptr, _ptr,
         ]
@@ -73,6 +72,9 @@ def core():
         ]
         lib.vx_gemm_bf16.argtypes = [
             _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _ptr, _ptr,
+        ]
+        lib.vx_gemm_bf16_add_chunked.argtypes = [
+            _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _ptr, _ptr,
         ]
         lib.vx_gemm_bf16_normed.argtypes = [
             _ptr, _c_ll, _ptr, _c_f, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _ptr, _ptr,
@@ -173,13 +175,6 @@ def selftest_bounded_wait(status: torch.Tensor, limit_cycles: int) -> int:
     _check(core().vx_selftest_bounded_wait(_p(status), int(limit_cycles), _p(returned), _stream()),
            "selftest_bounded_wait")
     return int(returned.item())
-
-
-def l2_prefetch(tensor: torch.Tensor) -> None:
-    """Ask the L2 for a contiguous tensor's bytes; returns at once."""
-    if not tensor.is_contiguous():
-        raise ValueError("l2_prefetch wants a contiguous tensor")
-    _check(core().vx_l2_prefetch(_p(tensor), tensor.numel() * tensor.element_size(), _stream()), "l2_prefetch")
 
 
 def embed(table: torch.Tensor, ids: torch.Tensor, resid: torch.Tensor, status: torch.Tensor) -> None:
@@ -356,6 +351,25 @@ def gemm_bf16(
             "multiple of 8 and both operands 16-byte aligned"
         )
     _check(code, "gemm_bf16")
+
+
+def gemm_bf16_add_chunked(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, num_rows: int,
+                          status: torch.Tensor, chunks: int) -> None:
+    """out[:num_rows] += x[:num_rows] @ w.T (float32 ``out``) with the inner dimension cut into
+    ``chunks`` ranges taken by independent CTAs, which add their partial tiles to ``out`` by
+    reductions at the L2: any number of CTAs per output tile, no cluster, and an order of
+    additions that is not fixed."""
+    _need(x, torch.bfloat16, "x")
+    _need(w, torch.bfloat16, "w")
+    _need(out, torch.float32, "out")
+    n, k = w.shape
+    if x.shape[1] != k or out.dim() != 2 or out.shape[1] != n:
+        raise ValueError(f"gemm shapes do not agree: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    code = core().vx_gemm_bf16_add_chunked(_p(x), _p(w), _p(out), num_rows, x.shape[0], n, k, out.stride(0),
+                                           int(chunks), _p(status), _stream())
+    if code == -1:
+        raise KernelError(f"gemm_bf16_add_chunked refuses x {tuple(x.shape)} w {tuple(w.shape)}")
+    _check(code, "gemm_bf16_add_chunked")
 
 
 # Steps of at most this many tokens can have their input norm made inside the projection.

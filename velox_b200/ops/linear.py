@@ -12,6 +12,7 @@ src/self_attention.py:32-33, src/mlp.py:9-10, src/transformer.py:60 of that proj
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -56,12 +57,36 @@ def _fuses_norm(x, weight: torch.Tensor, num_rows: int, status) -> bool:
     )
 
 
-def choose_splits(out_features: int, in_features: int, tile: int = 128) -> int:
-    """CTAs per output tile so that tiles x splits is about the number of SMs, with at least two
-    64-wide blocks of the inner dimension each (the launcher rounds down to 1, 2, 4 or 8)."""
-    tiles = -(-out_features // tile)
+def choose_splits(out_features: int, in_features: int, num_rows: int = 1, tile: int = 128) -> int:
+    """CTAs per output tile (a power of two up to 8) so that tiles x splits fills the GPU, with
+    at least two 64-wide blocks of the inner dimension each.  With at most 32 tokens an SM holds
+    two CTAs of the kernel, and a grid of up to 1.6 CTAs per SM streams faster than one that
+    leaves SMs idle (measured at the 7B and 14B sizes: 40 tiles x 4 = 160 CTAs take 43 us for the
+    14B down projection, 40 x 2 = 80 take 49); wider token tiles are one CTA per SM."""
+    tiles = max(1, -(-out_features // tile))
     blocks = -(-in_features // 64)
-    return max(1, min(_num_sms() // max(tiles, 1), blocks // 2, 8))
+    room = _num_sms() * (8 if num_rows <= 32 else 5) // 5
+    splits = 1
+    while splits * 2 <= min(8, blocks // 2) and tiles * splits * 2 <= room:
+        splits *= 2
+    return splits
+
+
+# VELOX_B200_NO_CHUNKED_SPLITK=1 keeps the sums into the residual stream in a fixed order (the
+# cluster form of split K), for bisecting and for runs that must repeat bit by bit.
+_CHUNKED_SPLITK = os.environ.get("VELOX_B200_NO_CHUNKED_SPLITK") != "1"
+
+
+def choose_chunks(out_features: int, in_features: int, num_rows: int, tile: int = 128) -> int:
+    """Ranges of the inner dimension for ``kernels.gemm_bf16_add_chunked``: enough CTAs for two
+    per SM with at most 32 tokens and one per SM with more (measured: the down projection of the
+    14B sizes at 64 tokens takes 49 us as 40 x 3 CTAs, 67 us as 40 clusters of two), each with
+    at least four 64-wide blocks."""
+    token_tile = 16 if num_rows <= 16 else 32 if num_rows <= 32 else 64 if num_rows <= 64 else 128 if num_rows <= 128 else 256
+    tiles = max(1, -(-out_features // tile)) * max(1, -(-num_rows // token_tile))
+    room = _num_sms() * (2 if num_rows <= 32 else 1)
+    blocks = -(-in_features // 64)
+    return max(1, min(room // tiles, blocks // 4))
 
 
 def linear(
@@ -90,7 +115,7 @@ def linear(
         if not accumulate and _fuses_norm(x, weight, num_rows, status):
             mode = kernels.GEMM_OUT_F32 if out.dtype == torch.float32 else kernels.GEMM_OUT_BF16
             if kernels.gemm_bf16_normed(x.resid, x.weight, x.eps, weight, bias_f32, out, mode, num_rows, status,
-                                        splits=choose_splits(weight.shape[0], weight.shape[1])):
+                                        splits=choose_splits(weight.shape[0], weight.shape[1], num_rows)):
                 return out
         x = x.materialize()
     if weight.dtype == torch.float32:
@@ -104,18 +129,22 @@ def linear(
         if accumulate and mirror is not None:
             # The kernel writes both where it can (no bias, K split over a cluster); else the
             # sums are copied, so that a caller who passes a mirror always finds it written.
-            splits = choose_splits(weight.shape[0], weight.shape[1])
+            splits = choose_splits(weight.shape[0], weight.shape[1], num_rows)
             if bias_f32 is not None or not kernels.gemm_bf16_add_mirrored(x, weight, out, mirror, num_rows, status,
                                                                          splits):
                 kernels.gemm_bf16(x, weight, bias_f32, out, kernels.GEMM_ADD_F32, num_rows, status, splits=splits)
                 mirror[:num_rows].copy_(out[:num_rows])
             return out
         if accumulate:
+            chunks = choose_chunks(weight.shape[0], weight.shape[1], num_rows) if _CHUNKED_SPLITK else 1
+            if chunks > 1 and bias_f32 is None:
+                kernels.gemm_bf16_add_chunked(x, weight, out, num_rows, status, chunks)
+                return out
             mode = kernels.GEMM_ADD_F32
         else:
             mode = kernels.GEMM_OUT_F32 if out.dtype == torch.float32 else kernels.GEMM_OUT_BF16
         kernels.gemm_bf16(x, weight, bias_f32, out, mode, num_rows, status,
-                          splits=choose_splits(weight.shape[0], weight.shape[1]))
+                          splits=choose_splits(weight.shape[0], weight.shape[1], num_rows))
         return out
     if accumulate:
         raise ValueError("only the tensor-core kernel accumulates into its output")
@@ -182,7 +211,7 @@ def qkv_rope_linear(
         return False
     if not use_tensor_core_kernel(x, weight, num_rows):
         return False
-    splits = choose_splits(weight.shape[0], weight.shape[1])
+    splits = choose_splits(weight.shape[0], weight.shape[1], num_rows)
     if splits < 2:
         return False
     if _is_pending_norm(x):
