@@ -935,3 +935,36 @@ def test_gemm_bf16_add_chunked(k, status, T, N, K, chunks):
     assert (out[:T].double() - want).abs().max().item() <= 2e-5 * want.abs().max().item()
     assert torch.equal(out[T:], start[T:])  # rows past the step are not touched
     assert int(status[0]) == 0
+
+
+@pytest.mark.parametrize("T,N,K,mode", [(16, 1792, 5120, "swiglu"), (8, 1024, 5120, "swiglu"), (3, 640, 8960, "swiglu"),
+                                        (11, 384, 7168, "f32"), (16, 256, 14336, "bf16")])
+def test_gemm_bf16_norm_with_a_ring_of_x_tiles(k, status, T, N, K, mode):
+    """The norm made inside the projection when the X tiles of all K blocks do not fit in shared
+    memory at once: their places are a ring, written again when the products that read them
+    have finished."""
+    gen = torch.Generator().manual_seed(N + K + T)
+    resid = (torch.randn(T + 1, K, generator=gen) * 1.5).cuda()
+    w_norm = (torch.rand(K, generator=gen) + 0.5).cuda()
+    r64 = resid[:T].double()
+    x64 = r64 * torch.rsqrt((r64 * r64).mean(-1, keepdim=True) + 1e-5) * w_norm.double()
+    rows = 2 * N if mode == "swiglu" else N
+    w = (torch.randn(rows, K, generator=gen) * 2 / math.sqrt(K)).to(torch.bfloat16).cuda()
+    if mode == "swiglu":
+        out = torch.zeros(T, N, dtype=torch.bfloat16, device="cuda")
+        assert k.gemm_bf16_normed(resid, w_norm, 1e-5, w, None, out, k.GEMM_SWIGLU, T, status)
+        # wider token tiles are refused (the norm then runs as a kernel of its own)
+        if K >= 5120:
+            wide = torch.zeros(64, N, dtype=torch.bfloat16, device="cuda")
+            rows64 = torch.randn(64, K, device="cuda")
+            assert not k.gemm_bf16_normed(rows64, w_norm, 1e-5, w, None, wide, k.GEMM_SWIGLU, 64, status)
+        gu = x64 @ w.double().T
+        want = torch.nn.functional.silu(gu[:, :N]) * gu[:, N:]
+    else:
+        out = torch.zeros(T, N, dtype=torch.float32 if mode == "f32" else torch.bfloat16, device="cuda")
+        assert k.gemm_bf16_normed(resid, w_norm, 1e-5, w, None, out, k.GEMM_OUT_F32 if mode == "f32" else k.GEMM_OUT_BF16,
+                                  T, status, splits=1)
+        want = x64 @ w.double().T
+    torch.cuda.synchronize()
+    assert (out.double() - want).abs().max().item() <= 1.2e-2 * want.abs().max().item()
+    assert int(status[0]) == 0

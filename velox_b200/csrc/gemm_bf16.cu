@@ -158,6 +158,11 @@ struct GemmArgs {
   const float* norm_w;   // [K]
   long long resid_ld;
   float eps;
+  // X tiles of the fused norm that shared memory holds at a time (a multiple of the batch in
+  // which they are made).  At least the CTA's K blocks: every tile has a place of its own.
+  // Fewer: the places are a ring, and a batch is written when the products that read the
+  // batch before it in its place have finished.
+  int x_slots;
   // Mode 4.
   const int* positions;  // [T]
   const float* cos_t;    // [max_pos, 64]
@@ -261,7 +266,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   __shared__ uint32_t tmem_slot;
   __shared__ int epilogue_failed;
   __shared__ float ssq_s[64];  // fused norm: this CTA's sums of squares, then 1 / rms, per token
-  __shared__ __align__(8) uint64_t x_bar[S::NORM_MAX_BATCHES];  // fused norm: a batch of X tiles is ready
+  __shared__ __align__(8) uint64_t x_bar[S::NORM_MAX_BATCHES];   // fused norm: a batch of X tiles is ready
+  __shared__ __align__(8) uint64_t x_free[S::NORM_MAX_BATCHES];  // ... and its place may be written again
 
   VX_TRACE_SCOPE(10 + g.mode);
   allow_dependents();
@@ -285,7 +291,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       mbar_init(smem_u32(&empty_bar[s]), 1);
     }
     if (normed)
-      for (int b = 0; b < S::NORM_MAX_BATCHES; ++b) mbar_init(smem_u32(&x_bar[b]), 1);
+      for (int b = 0; b < S::NORM_MAX_BATCHES; ++b) {
+        mbar_init(smem_u32(&x_bar[b]), 1);
+        mbar_init(smem_u32(&x_free[b]), 1);
+      }
     mbar_init(smem_u32(&acc_bar), 1);
     mbar_init(smem_u32(&recv_bar), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -353,12 +362,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       const int stage = i % S::STAGES;
       const uint32_t phase = (uint32_t)(i / S::STAGES) & 1u;
       ok = mbar_wait(smem_u32(&full_bar[stage]), phase, g.status);
+      // Batch b of X tiles lies in place b % ring_batches; its barrier has been used b / ring_batches times.
+      const int batch = i / S::NORM_BATCH, ring_batches = normed ? g.x_slots / S::NORM_BATCH : 1;
       if (ok && normed && i % S::NORM_BATCH == 0)
-        ok = mbar_wait(smem_u32(&x_bar[i / S::NORM_BATCH]), 0u, g.status);
+        ok = mbar_wait(smem_u32(&x_bar[batch % ring_batches]), (uint32_t)(batch / ring_batches) & 1u, g.status);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t a_addr = smem_base + stage * S::STAGE_BYTES;
-      const uint32_t b_addr = normed ? smem_base + S::STAGES * S::STAGE_BYTES + S::RECV_BYTES + i * S::B_BYTES
+      const uint32_t b_addr = normed ? smem_base + S::STAGES * S::STAGE_BYTES + S::RECV_BYTES +
+                                           (uint32_t)(i % g.x_slots) * S::B_BYTES
                                      : a_addr + GB_A_BYTES;
 #pragma unroll
       for (int k = 0; k < GB_BK / 16; ++k) {
@@ -366,6 +378,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                   idesc, (i > 0 || k > 0) ? 1u : 0u);
       }
       umma_commit(smem_u32(&empty_bar[stage]));
+      // The last product of a batch: when it has finished, the batch's place is free again.
+      if (normed && (i % S::NORM_BATCH == S::NORM_BATCH - 1 || i == num_kb - 1))
+        umma_commit(smem_u32(&x_free[batch % ring_batches]));
     }
     // Arrives when every MMA above has finished (or at once if there were none).
     umma_commit(smem_u32(&acc_bar));
@@ -383,6 +398,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
 #pragma unroll
       for (int u = 0; u < CPT; ++u) ssq[u] = 0.f;
       unsigned char* x_tiles = smem_raw + (smem_base - smem_u32(smem_raw)) + S::STAGES * S::STAGE_BYTES + S::RECV_BYTES;
+      const int ring_batches = g.x_slots / NB;
+      bool x_alive = true;
       for (int i0 = 0; i0 < num_kb; i0 += NB) {
         float4 xa[NB][CPT], xb[NB][CPT], wa[NB], wb[NB];
 #pragma unroll
@@ -401,10 +418,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
             xb[j][u] = on ? *reinterpret_cast<const float4*>(src + 4) : make_float4(0.f, 0.f, 0.f, 0.f);
           }
         }
+        // The place of this batch: free from the start the first time round, afterwards when
+        // the products of the batch that lay there have finished (the loads above are under way
+        // meanwhile).
+        const int batch = i0 / NB;
+        if (batch >= ring_batches && x_alive)
+          x_alive = mbar_wait(smem_u32(&x_free[batch % ring_batches]), (uint32_t)(batch / ring_batches - 1) & 1u, g.status);
 #pragma unroll
         for (int j = 0; j < NB; ++j) {
           if (i0 + j >= num_kb) break;
-          unsigned char* tile = x_tiles + (size_t)(i0 + j) * S::B_BYTES;
+          unsigned char* tile = x_tiles + (size_t)((i0 + j) % g.x_slots) * S::B_BYTES;
 #pragma unroll
           for (int u = 0; u < CPT; ++u) {
             const float4 a4 = xa[j][u], b4 = xb[j][u];
@@ -424,7 +447,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         // The tensor core reads the tiles through the async proxy.
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (q == 0) mbar_arrive(smem_u32(&x_bar[i0 / NB]));
+        if (q == 0) mbar_arrive(smem_u32(&x_bar[batch % ring_batches]));
       }
       // The eight threads of a token sit in consecutive lanes.
 #pragma unroll
@@ -712,6 +735,23 @@ static bool tensor_map_2d(CUtensorMap* map, const void* base, long long rows, lo
   return true;
 }
 
+// Dynamic shared memory of a CTA that leaves room for a second one on its SM.
+constexpr int TWO_PER_SM_BYTES = 113 * 1024;
+
+// SMs of the current device (asked once).
+static int device_sm_count() {
+  static int count = 0;
+  if (count == 0) {
+    int device = 0, value = 0;
+    if (cudaGetDevice(&device) == cudaSuccess &&
+        cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device) == cudaSuccess && value > 0)
+      count = value;
+    else
+      count = 148;
+  }
+  return count;
+}
+
 // `one_wave`: launch only if all the grid's clusters are resident at once with this variant's
 // shared memory (-2 otherwise: the caller takes the variant of which an SM holds two CTAs).
 template <int BN, int STAGES_>
@@ -730,12 +770,43 @@ static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mw2, const CUte
     if (e != cudaSuccess) return (int)e;
     dynamic_limit = limit;
   }
-  // With the fused norm the X tiles of all the CTA's K blocks follow the stages.
+  // With the fused norm the X tiles follow the stages: all of the CTA's K blocks if they fit
+  // (beside a second CTA on the SM when the grid has more CTAs than the device has SMs), else a
+  // ring of at least two batches.
   size_t smem = S::SMEM_BYTES;
+  GemmArgs launched = g;
   if (g.resid != nullptr) {
     if (BN > 64) return -2;
-    if ((g.kb_per_split + S::NORM_BATCH - 1) / S::NORM_BATCH > S::NORM_MAX_BATCHES) return -2;
-    smem += (size_t)g.kb_per_split * S::B_BYTES;
+    const int batches = (g.kb_per_split + S::NORM_BATCH - 1) / S::NORM_BATCH;
+    const size_t batch_bytes = (size_t)S::NORM_BATCH * S::B_BYTES;
+    const bool shares_sm = (long long)grid.x * grid.y * grid.z > (long long)device_sm_count();
+    // A grid of more CTAs than SMs runs in one wave only with two CTAs on an SM: the X tiles
+    // then have to fit beside that (measured at the 7B sizes, 32 tokens: the gate|up projection
+    // with a ring that filled the SM took 84 us, norm and projection as two kernels 61).
+    const size_t budget = shares_sm ? (size_t)TWO_PER_SM_BYTES : (size_t)dynamic_limit;
+    const size_t all_resident = S::SMEM_BYTES + (size_t)g.kb_per_split * S::B_BYTES;
+    int ring;
+    if (all_resident <= budget) {
+      ring = batches;  // every tile in a place of its own
+    } else if (BN <= 16 && S::SMEM_BYTES + 2 * batch_bytes <= budget) {
+      // A ring, for the narrowest token tile only: every CTA reads the rows again, and at 64
+      // tokens those are as many bytes as its weights.  Then the step is faster with the norm
+      // as a kernel of its own (measured: 1.5B sizes, 64 tokens, 3.03 ms a step against 3.56;
+      // 14B sizes, 32 tokens, QKV 41 us against 7 + 31).
+      ring = (int)((budget - S::SMEM_BYTES) / batch_bytes);
+      if (ring > S::NORM_MAX_BATCHES) ring = S::NORM_MAX_BATCHES;
+      if (ring >= batches) ring = batches;
+    } else if (all_resident <= (size_t)dynamic_limit && batches <= S::NORM_MAX_BATCHES) {
+      ring = batches;  // fits, at the price of the SM to itself
+    } else {
+      return -2;
+    }
+    launched.x_slots = ring * S::NORM_BATCH;
+    // All resident: exactly the CTA's K blocks (the last batch may be a short one); every
+    // kilobyte counts where two CTAs are to share an SM.
+    smem += ring == batches ? (size_t)g.kb_per_split * S::B_BYTES : (size_t)ring * batch_bytes;
+  } else {
+    launched.x_slots = S::NORM_BATCH;
   }
   if (smem > (size_t)dynamic_limit) return -2;
   cudaLaunchConfig_t config = {};
@@ -782,7 +853,7 @@ static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mw2, const CUte
     const long long clusters_wanted = (long long)grid.x * grid.y;
     if (active > 0 && clusters_wanted > active) return -2;
   }
-  return (int)cudaLaunchKernelEx(&config, gemm_bf16_kernel<BN, STAGES_>, mw, mw2, mx, g);
+  return (int)cudaLaunchKernelEx(&config, gemm_bf16_kernel<BN, STAGES_>, mw, mw2, mx, launched);
 }
 
 
@@ -1131,6 +1202,22 @@ static int gemm_bf16(const void* x, int x_rows, const float* resid, long long re
   if (splits < 1 || mode == 3 || bn > 64) splits = 1;
   splits = floor_pow2(splits < num_kb ? splits : num_kb, GB_MAX_SPLITS);
   if (splits > bn) splits = bn;
+  if (normed && bn <= 64) {
+    // With the norm made in the kernel the X tiles lie in shared memory beside the stages.  A
+    // grid of more CTAs than SMs needs two CTAs on an SM to run in one wave; where the tiles
+    // (or a ring of two batches of them, narrowest token tile only) do not leave room for
+    // that, fewer and longer splits do better.
+    const long long tiles = (long long)((N + (mode == 3 ? 64 : GB_BM) - 1) / (mode == 3 ? 64 : GB_BM)) * ((T + bn - 1) / bn);
+    const size_t b_bytes = (size_t)bn * GB_BK * 2;
+    const size_t recv = ((size_t)GB_BM * (bn + 4) * 4 + GB_MAX_SPLITS * bn * 4 + 1023) / 1024 * 1024;
+    const size_t base = 4 * (GB_A_BYTES + b_bytes) + recv + 1024;
+    const size_t batch = (size_t)(bn <= 16 ? 6 : (bn <= 32 ? 4 : 2)) * b_bytes;
+    while (splits > (mode == 4 ? 2 : 1) && tiles * splits > (long long)sm_count()) {
+      const size_t kb = (size_t)(num_kb + splits - 1) / splits;
+      if (base + kb * b_bytes <= (size_t)TWO_PER_SM_BYTES || (bn <= 16 && base + 2 * batch <= (size_t)TWO_PER_SM_BYTES)) break;
+      splits /= 2;
+    }
+  }
   if (mode == 4) {
     // Heads of 128 dims, rotated in the cluster exchange's final sum: split K only.
     if (splits < 2 || rope->heads <= 0 || rope->kv_heads <= 0 ||
