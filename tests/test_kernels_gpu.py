@@ -176,6 +176,32 @@ def test_gemm_f32_rows_do_not_depend_on_batch(k):
         assert torch.equal(one[0], full[row])
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden,T", [(1536, 700), (3584, 300), (240, 513), (4100, 260)])
+def test_add_rmsnorm_many_rows(k, dtype, hidden, T):
+    """Steps of many rows (a warp per row in bfloat16), with and without rows to add, selected
+    rows, and a tail that does not fill the last block."""
+    gen = torch.Generator().manual_seed(hidden + T)
+    resid = (torch.randn(T + 2, hidden, generator=gen) * 3).cuda()
+    delta = torch.randn(T + 2, hidden, generator=gen).to(dtype).cuda()
+    weight = (1 + 0.1 * torch.randn(hidden, generator=gen)).cuda()
+    before = resid.clone()
+    out = torch.full((T + 2, hidden), 5.0, dtype=dtype, device="cuda")
+    k.add_rmsnorm(resid, delta, weight, 1e-6, out, T)
+    v = before[:T].double() + delta[:T].double()
+    want = plain_model.rms_norm(v, weight.double(), 1e-6)
+    _close(out[:T], want, dtype)
+    assert torch.allclose(resid[:T].double(), v, atol=1e-6)
+    assert torch.equal(resid[T:], before[T:]) and bool((out[T:] == 5.0).all())  # rows past the step untouched
+    picked = min(300, T)  # as many rows as the index array names, never more
+    rows = torch.randperm(T, generator=gen)[:picked].to(torch.int32).cuda()
+    out2 = torch.empty(picked, hidden, dtype=dtype, device="cuda")
+    resid2 = before.clone()
+    k.add_rmsnorm(resid2, None, weight, 1e-6, out2, picked, rows=rows, write_resid=False)
+    _close(out2, plain_model.rms_norm(before.double()[rows.long()], weight.double(), 1e-6), dtype)
+    assert torch.equal(resid2, before)
+
+
 # ----------------------------------------------------------------------------------------------
 # Attention
 # ----------------------------------------------------------------------------------------------

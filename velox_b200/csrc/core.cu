@@ -270,25 +270,117 @@ __global__ void rope_cache_write_vec_kernel(T* __restrict__ qkv, const int* __re
 }
 
 // ---------------------------------------------------------------------------------------------
+// The rotation over the whole head (rot == D), 16 bytes at a time, with no idle threads: a
+// thread takes a chunk of the low half and its partner in the high half of one head (for v: the
+// two chunks as they are), the angles as vectors.  Same arithmetic as the kernels above.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_cache_write_pair_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+                                             const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                             const int* __restrict__ slots, T* __restrict__ k_cache,
+                                             T* __restrict__ v_cache, int H, int G, int D, int max_pos,
+                                             long long num_slots, int write_cache, int num_tokens, int* status) {
+  constexpr int N = Vec16<T>::N;
+  VX_TRACE_SCOPE(3);
+  allow_dependents();
+  grid_dependency_wait();
+  const int half = D >> 1;
+  const int pairs = half / N;              // per head
+  const int per_token = (H + 2 * G) * pairs;
+  const long long total = (long long)num_tokens * per_token;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(idx / per_token);
+    const int within = (int)(idx - (long long)t * per_token);
+    const int head = within / pairs, d = (within - head * pairs) * N;
+    const bool is_q = head < H, is_k = !is_q && head < H + G;
+    T* src = qkv + (size_t)t * (size_t)(H + 2 * G) * D + (size_t)head * D;
+    T* dst = src;
+    if (!is_q) {
+      if (!write_cache) continue;
+      const int slot = slots[t];
+      if (slot < 0) continue;
+      if ((long long)slot >= num_slots) {
+        if (d == 0) atomicOr(status, VX_STATUS_BAD_SLOT);
+        continue;
+      }
+      const int g = is_k ? head - H : head - H - G;
+      dst = (is_k ? k_cache : v_cache) + ((size_t)slot * G + g) * D;
+    }
+    const Vec16<T> a = load16(src + d), b = load16(src + d + half);
+    if (is_q || is_k) {
+      int pos = positions[t];
+      if (pos < 0 || pos >= max_pos) {
+        if (within == 0) atomicOr(status, VX_STATUS_BAD_POSITION);
+        pos = 0;
+      }
+      float lo[N], hi[N], c[N], s[N], out_lo[N], out_hi[N];
+      a.unpack(lo);
+      b.unpack(hi);
+      const float4* cp = reinterpret_cast<const float4*>(cos_t + (size_t)pos * half + d);
+      const float4* sp = reinterpret_cast<const float4*>(sin_t + (size_t)pos * half + d);
+#pragma unroll
+      for (int v4 = 0; v4 < N / 4; ++v4) {
+        const float4 cv = __ldg(cp + v4), sv = __ldg(sp + v4);
+        c[4 * v4] = cv.x, c[4 * v4 + 1] = cv.y, c[4 * v4 + 2] = cv.z, c[4 * v4 + 3] = cv.w;
+        s[4 * v4] = sv.x, s[4 * v4 + 1] = sv.y, s[4 * v4 + 2] = sv.z, s[4 * v4 + 3] = sv.w;
+      }
+#pragma unroll
+      for (int k = 0; k < N; ++k) {
+        out_lo[k] = lo[k] * c[k] - hi[k] * s[k];
+        out_hi[k] = lo[k] * s[k] + hi[k] * c[k];
+      }
+      Vec16<T> ra, rb;
+      ra.pack(out_lo);
+      rb.pack(out_hi);
+      store16(dst + d, ra);
+      store16(dst + d + half, rb);
+    } else {
+      store16(dst + d, a);
+      store16(dst + d + half, b);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // SwiGLU: out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i], float32 inside, one rounding.
 // The vector kernel (16 bytes per thread) serves widths that are a multiple of the vector.
 // ---------------------------------------------------------------------------------------------
+// A thread takes SWIGLU_PER_THREAD chunks of 16 bytes, a block's width apart, and asks for all
+// of its gate and up values before it computes: eight loads under way per thread.
+constexpr int SWIGLU_PER_THREAD = 4;
+
 template <typename T>
 __global__ void swiglu_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter) {
   constexpr int N = Vec16<T>::N;
   allow_dependents();
   grid_dependency_wait();
   const size_t t = blockIdx.y;
-  const int i = (blockIdx.x * blockDim.x + threadIdx.x) * N;
-  if (i >= inter) return;
-  float g[N], u[N], r[N];
-  load16(gate_up + t * 2 * inter + i).unpack(g);
-  load16(gate_up + t * 2 * inter + inter + i).unpack(u);
+  const T* gate = gate_up + t * 2 * inter;
+  const T* up = gate + inter;
+  const int first = (blockIdx.x * SWIGLU_PER_THREAD * blockDim.x + threadIdx.x) * N;
+  Vec16<T> gv[SWIGLU_PER_THREAD], uv[SWIGLU_PER_THREAD];
 #pragma unroll
-  for (int k = 0; k < N; ++k) r[k] = g[k] / (1.0f + expf(-g[k])) * u[k];
-  Vec16<T> o;
-  o.pack(r);
-  store16(out + t * inter + i, o);
+  for (int j = 0; j < SWIGLU_PER_THREAD; ++j) {
+    const int i = first + j * (int)blockDim.x * N;
+    if (i < inter) {
+      gv[j] = load16(gate + i);
+      uv[j] = load16(up + i);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < SWIGLU_PER_THREAD; ++j) {
+    const int i = first + j * (int)blockDim.x * N;
+    if (i >= inter) continue;
+    float g[N], u[N], r[N];
+    gv[j].unpack(g);
+    uv[j].unpack(u);
+#pragma unroll
+    for (int k = 0; k < N; ++k) r[k] = g[k] / (1.0f + expf(-g[k])) * u[k];
+    Vec16<T> o;
+    o.pack(r);
+    store16(out + t * inter + i, o);
+  }
 }
 
 template <typename T>
@@ -505,12 +597,86 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __res
   }
 }
 
+// The same with a warp per row, for steps of many rows: a lane keeps its share of the row
+// (chunks lane, lane + 32, ... of four elements) in registers and has all its loads under way
+// at once, the sum of squares goes through shuffles, and no thread waits at a block barrier
+// between its loads and its stores.  (One block per row reached about half of the memory
+// bandwidth at 2,048 rows: three waves of blocks that each load, meet, and store.)
+template <typename T, int MAX_CHUNKS>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_warp_kernel(float* __restrict__ resid, const T* __restrict__ delta, const float* __restrict__ weight,
+                        float eps, T* __restrict__ out, const int* __restrict__ rows, int hidden, int write_resid,
+                        int num_rows) {
+  VX_TRACE_SCOPE(2);
+  allow_dependents();
+  grid_dependency_wait();
+  const int lane = threadIdx.x & 31;
+  const int o = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (o >= num_rows) return;
+  const int r = rows ? rows[o] : o;
+  const int chunks = hidden >> 2;
+  float* x = resid + (size_t)r * hidden;
+  const T* d = delta ? delta + (size_t)r * hidden : nullptr;
+  float4 vals[MAX_CHUNKS];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < MAX_CHUNKS; ++j) {
+    const int c = lane + 32 * j;
+    vals[j] = c < chunks ? *reinterpret_cast<const float4*>(x + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  if (d) {
+#pragma unroll
+    for (int j = 0; j < MAX_CHUNKS; ++j) {
+      const int c = lane + 32 * j;
+      if (c < chunks) {
+        const float4 e = load4_as_float<T>(d + 4 * c);
+        vals[j].x += e.x;
+        vals[j].y += e.y;
+        vals[j].z += e.z;
+        vals[j].w += e.w;
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < MAX_CHUNKS; ++j)
+    ss += vals[j].x * vals[j].x + vals[j].y * vals[j].y + vals[j].z * vals[j].z + vals[j].w * vals[j].w;
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+  T* y = out + (size_t)o * hidden;
+#pragma unroll
+  for (int j = 0; j < MAX_CHUNKS; ++j) {
+    const int c = lane + 32 * j;
+    if (c < chunks) {
+      const float4 v = vals[j];
+      const float4 w = __ldg(reinterpret_cast<const float4*>(weight + 4 * c));
+      if (write_resid && d) *reinterpret_cast<float4*>(x + 4 * c) = v;
+      store4_from_float<T>(y + 4 * c, make_float4(v.x * inv * w.x, v.y * inv * w.y, v.z * inv * w.z, v.w * inv * w.w));
+    }
+  }
+}
+
+template <typename T, int MAX_CHUNKS>
+static void launch_rmsnorm_warp(float* resid, const void* delta, const float* weight, float eps, void* out,
+                                const int* rows, int num_rows, int hidden, int write_resid, cudaStream_t stream) {
+  const int warps = 8;
+  launch_pdl(add_rmsnorm_warp_kernel<T, MAX_CHUNKS>, dim3((num_rows + warps - 1) / warps), dim3(warps * 32), 0, stream,
+             resid, (const T*)delta, weight, eps, (T*)out, rows, hidden, write_resid, num_rows);
+}
+
 VX_API int vx_add_rmsnorm(float* resid, const void* delta, const float* weight, float eps,
                           void* out, int dtype, const int* rows, int num_out_rows, int hidden,
                           int write_resid, cudaStream_t stream) {
   if (num_out_rows <= 0) return 0;
   const bool aligned = (reinterpret_cast<uintptr_t>(resid) & 15) == 0 && (reinterpret_cast<uintptr_t>(weight) & 15) == 0 &&
                        (reinterpret_cast<uintptr_t>(out) & 15) == 0 && (reinterpret_cast<uintptr_t>(delta) & 15) == 0;
+  // Many rows: a warp per row (rows of up to 4,096 elements, whole chunks of four).  Not in
+  // the float32 path: there a row's sum of squares is added up in the same order whatever the
+  // step, so that results do not depend on how the work was cut.
+  if (aligned && dtype == VX_DTYPE_BF16 && num_out_rows >= 256 && hidden % 4 == 0 && hidden <= 4096) {
+    if (hidden <= 2048) launch_rmsnorm_warp<__nv_bfloat16, 16>(resid, delta, weight, eps, out, rows, num_out_rows, hidden, write_resid, stream);
+    else launch_rmsnorm_warp<__nv_bfloat16, 32>(resid, delta, weight, eps, out, rows, num_out_rows, hidden, write_resid, stream);
+    return (int)cudaGetLastError();
+  }
   if (aligned && hidden % 4 == 0 && hidden / 4 <= 1024 * NORM_VEC_CHUNKS) {
     // One chunk of four per thread, two for rows of more than 4,096 elements.
     const int chunks = hidden / 4;
@@ -548,6 +714,23 @@ VX_API int vx_rope_cache_write(void* qkv, int dtype, const int* positions, const
   const bool aligned = (reinterpret_cast<uintptr_t>(qkv) & 15) == 0 &&
                        (reinterpret_cast<uintptr_t>(k_cache) & 15) == 0 &&
                        (reinterpret_cast<uintptr_t>(v_cache) & 15) == 0;
+  // The whole head rotates and a half is whole vectors (of angles too): pairs of chunks.
+  if (aligned && rot == D && (D / 2) % vec == 0 && (D / 2) % 4 == 0 &&
+      (reinterpret_cast<uintptr_t>(cos_t) & 15) == 0 && (reinterpret_cast<uintptr_t>(sin_t) & 15) == 0) {
+    const long long total = (long long)num_tokens * (H + 2 * G) * (D / 2 / vec);
+    const int block = 256;
+    long long blocks = (total + block - 1) / block;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (dtype == VX_DTYPE_F32)
+      launch_pdl(rope_cache_write_pair_kernel<float>, dim3((int)blocks), dim3(block), 0, stream, (float*)qkv, positions,
+                 cos_t, sin_t, slots, (float*)k_cache, (float*)v_cache, H, G, D, max_pos, num_slots, write_cache,
+                 num_tokens, status);
+    else
+      launch_pdl(rope_cache_write_pair_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(block), 0, stream,
+                 (__nv_bfloat16*)qkv, positions, cos_t, sin_t, slots, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
+                 H, G, D, max_pos, num_slots, write_cache, num_tokens, status);
+    return (int)cudaGetLastError();
+  }
   if (aligned && D % vec == 0 && (rot / 2) % vec == 0) {
     const int work = (H + 2 * G) * (D / vec);
     const int block = work >= 256 ? 256 : (work + 31) / 32 * 32;
@@ -583,7 +766,7 @@ VX_API int vx_swiglu(const void* gate_up, void* out, int dtype, int num_tokens, 
   if (inter % vec == 0 && (reinterpret_cast<uintptr_t>(gate_up) & 15) == 0 &&
       (reinterpret_cast<uintptr_t>(out) & 15) == 0 && num_tokens <= 65535) {
     const int threads = 128;
-    const dim3 grid((inter / vec + threads - 1) / threads, num_tokens);
+    const dim3 grid((inter / vec + threads * SWIGLU_PER_THREAD - 1) / (threads * SWIGLU_PER_THREAD), num_tokens);
     if (dtype == VX_DTYPE_F32)
       launch_pdl(swiglu_vec_kernel<float>, grid, dim3(threads), 0, stream, (const float*)gate_up,
                  (float*)out, inter);

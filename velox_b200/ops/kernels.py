@@ -143,6 +143,16 @@ def _check(code: int, what: str) -> None:
         launch_events.append((what, event))
 
 
+def note_library_launch(what: str) -> None:
+    """Called after a library kernel (a cuBLAS product through torch) has been queued, so that a
+    timeline of ``launch_events`` has an entry for it too.  It does not count as a launch of
+    this package's kernels."""
+    if launch_events is not None:
+        event = torch.cuda.Event(enable_timing=True)
+        event.record()
+        launch_events.append((what, event))
+
+
 def _p(t: Optional[torch.Tensor]) -> Optional[int]:
     return None if t is None else t.data_ptr()
 
@@ -220,6 +230,12 @@ def add_rmsnorm(
             raise ValueError("delta width does not match the residual width")
     if rows is not None:
         _need(rows, torch.int32, "rows")
+        if rows.numel() < num_rows:
+            raise ValueError(f"{num_rows} rows asked for, the index array names {rows.numel()}")
+    elif resid.shape[0] < num_rows or (delta is not None and delta.shape[0] < num_rows):
+        raise ValueError(f"{num_rows} rows asked for, the input has {resid.shape[0]}")
+    if out.shape[0] < num_rows:
+        raise ValueError(f"{num_rows} rows asked for, the output holds {out.shape[0]}")
     _check(
         core().vx_add_rmsnorm(_p(resid), _p(delta), _p(weight), float(eps), _p(out),
                               _code(out.dtype), _p(rows), num_rows, hidden,

@@ -157,6 +157,7 @@ def linear(
         torch.addmm(bias_lowp, xs, _transposed(weight), out=os_)
     else:
         torch.mm(xs, _transposed(weight), out=os_)
+    kernels.note_library_launch("library_gemm")
     return out
 
 
