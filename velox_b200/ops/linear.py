@@ -73,8 +73,12 @@ def choose_splits(out_features: int, in_features: int, num_rows: int = 1, tile: 
 
 
 # VELOX_B200_NO_CHUNKED_SPLITK=1 keeps the sums into the residual stream in a fixed order (the
-# cluster form of split K), for bisecting and for runs that must repeat bit by bit.
-_CHUNKED_SPLITK = os.environ.get("VELOX_B200_NO_CHUNKED_SPLITK") != "1"
+# cluster form of split K), for bisecting.  VELOX_B200_DETERMINISTIC=1 does that and keeps the
+# feed-forward of small steps as two kernels: every sum of the bfloat16 path then has a fixed
+# order and a run repeats bit by bit (seeded sampling gives the same tokens again), at the
+# price of the two fastest forms of small steps.
+DETERMINISTIC = os.environ.get("VELOX_B200_DETERMINISTIC") == "1"
+_CHUNKED_SPLITK = os.environ.get("VELOX_B200_NO_CHUNKED_SPLITK") != "1" and not DETERMINISTIC
 
 
 def choose_chunks(out_features: int, in_features: int, num_rows: int, tile: int = 128) -> int:

@@ -9,14 +9,14 @@ import os
 import torch
 
 from ..ops import kernels
-from ..ops.linear import linear, swiglu_linear, use_tensor_core_kernel
+from ..ops.linear import DETERMINISTIC, linear, swiglu_linear, use_tensor_core_kernel
 from .base import FeedForward
 from .registry import register_part
 
 
 # VELOX_B200_NO_MLP_FUSION=1 keeps the two projections of a small step as kernels of their own
 # (for bisecting; the fused kernel's sum over the inner width has no fixed order).
-_FUSE_MLP = os.environ.get("VELOX_B200_NO_MLP_FUSION") != "1"
+_FUSE_MLP = os.environ.get("VELOX_B200_NO_MLP_FUSION") != "1" and not DETERMINISTIC
 
 
 @register_part("feed_forward", "swiglu")
