@@ -274,6 +274,9 @@ class ModelRunner:
         self._mixed_graphs_on = (self.enable_graphs and os.environ.get("VELOX_B200_NO_MIXED_GRAPHS") != "1"
                                  and model.parts_take_padded_steps())
         self._last_shape: Tuple[tuple, int] = ((), 0)
+        # One memory pool for whatever a capture allocates (a library's workspace): the graphs
+        # run one at a time on one stream, so they can share it instead of each keeping its own.
+        self._graph_pool = torch.cuda.graph_pool_handle() if self.enable_graphs else None
         self._padded_stages: Dict[int, "_PaddedStage"] = {}
         self._graphs_broken = False
         self._meta_generation = 0
@@ -363,7 +366,7 @@ class ModelRunner:
                 collecting = gc.isenabled()
                 gc.disable()
                 try:
-                    with torch.cuda.graph(graph):
+                    with torch.cuda.graph(graph, pool=self._graph_pool):
                         captured = self.model.forward(ctx, self.layer_caches, ids, logit_rows, num_logit_rows)
                 finally:
                     if collecting:
@@ -790,7 +793,7 @@ class ModelRunner:
         collecting = gc.isenabled()
         gc.disable()
         try:
-            with torch.cuda.graph(graph):
+            with torch.cuda.graph(graph, pool=self._graph_pool):
                 logits = self.model.forward(ctx, self.layer_caches, ids, rows, count)
         finally:
             if collecting:
