@@ -573,3 +573,46 @@ def test_engine_step_raises_when_the_status_word_comes_back_set():
     assert a.output_token_ids == [11] and FakeRunner.cleared == 1
     engine.step()
     assert a.output_token_ids == [11, 11]
+
+
+def test_split_and_chunk_choices_fill_the_gpu_without_overfilling():
+    """How many CTAs share an output tile (cluster split K) or a K range (chunks): pure
+    arithmetic on the sizes, checked at the three model sizes the benchmarks use."""
+    from velox_b200.ops import linear
+
+    linear._NUM_SMS = 148
+    try:
+        # (out, in): 1.5B QKV / O / down, 7B, 14B
+        few = {(2048, 1536): 8, (1536, 1536): 8, (1536, 8960): 8, (4608, 3584): 4, (3584, 3584): 8, (3584, 18944): 8,
+               (7168, 5120): 4, (5120, 5120): 4, (5120, 13824): 4, (151936, 1536): 1}
+        for (n, k), want in few.items():
+            assert linear.choose_splits(n, k, 8) == want, (n, k)
+            tiles = -(-n // 128)
+            assert tiles * linear.choose_splits(n, k, 8) <= 148 * 8 // 5 or want == 1
+            # wider token tiles: one CTA per SM
+            assert tiles * linear.choose_splits(n, k, 64) <= 148 or linear.choose_splits(n, k, 64) == 1
+        for (n, k) in few:
+            for rows, per_sm in ((8, 2), (32, 2), (64, 1), (200, 1)):
+                chunks = linear.choose_chunks(n, k, rows)
+                token_tiles = 1 if rows <= 64 else -(-rows // (128 if rows <= 128 else 256))
+                tiles = -(-n // 128) * token_tiles
+                assert chunks >= 1 and (chunks == 1 or tiles * chunks <= 148 * per_sm)
+                assert chunks == 1 or -(-k // 64) // chunks >= 4  # at least four K blocks a chunk
+    finally:
+        linear._NUM_SMS = None
+
+
+def test_benchmark_command_line_options():
+    from velox_b200.cli.benchmark import build_prompts, parse_args
+
+    args = parse_args(["--model-size", "7b", "--prompt-range", "128,2048", "--rounds", "2", "--max-tokens", "256",
+                       "--num-requests", "64", "--max-prefill-chunk-size", "512"])
+    assert args.prompt_range == "128,2048" and args.rounds == 2 and args.model_size == "7b"
+    prompts = build_prompts("mixed", 40, 1000, 4096, 3, length_range=args.prompt_range)
+    lengths = [len(p) for p in prompts]
+    assert len(prompts) == 40 and min(lengths) >= 128 and max(lengths) <= 2048 and len(set(lengths)) > 20
+    assert all(0 <= t < 1000 for p in prompts for t in p)
+    assert build_prompts("mixed", 40, 1000, 4096, 3, length_range=args.prompt_range) == prompts  # seeded
+    assert [len(p) for p in build_prompts("short", 5, 50, 30, 1, fixed_len=77)] == [30] * 5  # cut to the limit
+    with pytest.raises(SystemExit):
+        parse_args(["--model-size", "7b", "--model", "x"])
