@@ -229,12 +229,18 @@ sample_kernel(const float* __restrict__ logits, int vocab, long long row_stride,
 // the entries that share the digits found so far (how many, and their mass); the digit is the
 // smallest one above which count and mass still pass.  Five sweeps over the row in all (maximum,
 // normaliser, three digits) where a bisection over the patterns took up to 34 (measured at 64
-// rows of 151,936: 0.42 ms instead of 1.2 ms).  Masses are summed as 2^-40 fixed-point
+// rows of 151,936: 0.17 ms instead of 1.2 ms).  Masses are summed as 2^-40 fixed-point
 // integers, so the histogram, and with it the threshold, does not depend on the order in which
 // threads add.
 // ---------------------------------------------------------------------------------------------
 constexpr int FILTER_THREADS = 1024;
 constexpr int FILTER_BINS = 2048;
+// Copies of the histogram for the first digit.  That digit is sign, exponent and two bits of
+// the mantissa, so a row's entries share a few dozen of its values and their atomics queue up
+// on those bins; with a copy per four warps the queues are an eighth as long.  The copies are
+// added up before the digit is chosen (integer sums: the result does not depend on the copies).
+constexpr int FILTER_COPIES = 8;
+constexpr size_t FILTER_SMEM_BYTES = (size_t)FILTER_COPIES * FILTER_BINS * (sizeof(unsigned int) + sizeof(unsigned long long));
 constexpr float FILTER_MASS_SCALE = 1099511627776.0f;  // 2^40
 
 __device__ __forceinline__ unsigned long long fixed_mass(float e) {
@@ -312,8 +318,9 @@ filter_threshold_kernel(const float* __restrict__ logits, int vocab, long long r
   __shared__ float scratch[32];
   __shared__ unsigned int sc[32];
   __shared__ unsigned long long sm[32];
-  __shared__ unsigned int hist_count[FILTER_BINS];
-  __shared__ unsigned long long hist_mass[FILTER_BINS];
+  extern __shared__ __align__(16) unsigned char filter_smem[];
+  unsigned long long* hist_mass = reinterpret_cast<unsigned long long*>(filter_smem);          // [COPIES][BINS]
+  unsigned int* hist_count = reinterpret_cast<unsigned int*>(hist_mass + FILTER_COPIES * FILTER_BINS);  // [COPIES][BINS]
   __shared__ unsigned int chosen_digit, chosen_count;
   __shared__ unsigned long long chosen_mass, total_mass;
   allow_dependents();
@@ -371,11 +378,14 @@ filter_threshold_kernel(const float* __restrict__ logits, int vocab, long long r
   for (int level = 0; level < 3; ++level) {
     const int shift = shifts[level];
     const uint32_t digit_mask = (1u << bits[level]) - 1u;
-    for (int b = threadIdx.x; b < FILTER_BINS; b += blockDim.x) {
+    const int copies = level == 0 ? FILTER_COPIES : 1;
+    for (int b = threadIdx.x; b < copies * FILTER_BINS; b += blockDim.x) {
       hist_count[b] = 0u;
       hist_mass[b] = 0ull;
     }
     __syncthreads();
+    unsigned int* my_count = hist_count + (level == 0 ? ((threadIdx.x >> 7) % FILTER_COPIES) * FILTER_BINS : 0);
+    unsigned long long* my_mass = hist_mass + (level == 0 ? ((threadIdx.x >> 7) % FILTER_COPIES) * FILTER_BINS : 0);
     const float top = m;
     const uint32_t above = prefix;
     const int level_bits = bits[level];
@@ -385,10 +395,25 @@ filter_threshold_kernel(const float* __restrict__ logits, int vocab, long long r
       const uint32_t key = float_key(s);
       if (level > 0 && (key >> (shift + level_bits)) != above) return;
       const uint32_t digit = (key >> shift) & digit_mask;
-      atomicAdd(&hist_count[digit], 1u);
-      atomicAdd(&hist_mass[digit], fixed_mass(expf(s - top)));
+      // What the filter in force does not look at is not counted.
+      if (use_k) atomicAdd(&my_count[digit], 1u);
+      if (use_p) atomicAdd(&my_mass[digit], fixed_mass(expf(s - top)));
     });
     __syncthreads();
+    if (level == 0) {
+      for (int b = threadIdx.x; b < FILTER_BINS; b += blockDim.x) {
+        unsigned int c = hist_count[b];
+        unsigned long long w = hist_mass[b];
+#pragma unroll
+        for (int copy = 1; copy < FILTER_COPIES; ++copy) {
+          c += hist_count[copy * FILTER_BINS + b];
+          w += hist_mass[copy * FILTER_BINS + b];
+        }
+        hist_count[b] = c;
+        hist_mass[b] = w;
+      }
+      __syncthreads();
+    }
     // Thread t owns digits 2t and 2t + 1.  A digit d passes if what lies above it (the larger
     // digits, and everything above the prefix) is fewer than k entries and less than top_p.
     const unsigned int c0 = hist_count[2 * threadIdx.x], c1 = hist_count[2 * threadIdx.x + 1];
@@ -511,7 +536,14 @@ VX_API int vx_filter_threshold(const float* logits, int num_rows, int vocab, lon
                                const float* temperature, const int* top_k, const float* top_p,
                                float* threshold, cudaStream_t stream) {
   if (num_rows <= 0) return 0;
-  launch_pdl(filter_threshold_kernel, dim3(num_rows), dim3(FILTER_THREADS), 0, stream, logits, vocab, row_stride,
+  static bool configured = false;
+  if (!configured) {
+    const cudaError_t e = cudaFuncSetAttribute(filter_threshold_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)FILTER_SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  launch_pdl(filter_threshold_kernel, dim3(num_rows), dim3(FILTER_THREADS), FILTER_SMEM_BYTES, stream, logits, vocab, row_stride,
                                                             temperature, top_k, top_p, threshold);
   return (int)cudaGetLastError();
 }
