@@ -43,7 +43,10 @@ MODEL_1P5B = {
 FULL_LAYERS = 28
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
-BLOCK_SIZE = 64
+# Keys per cache page: the benchmark configuration's (and the reference's default).  The engine's own
+# default is 64; a point with 64-key pages is reported beside the main numbers.
+BLOCK_SIZE = 16
+ENGINE_DEFAULT_BLOCK_SIZE = 64
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -154,11 +157,12 @@ def run_own(args):
     print(f"[bench] wrote random {layers}-layer model in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
 
     max_batch = max(args.batch, 64 if args.points else args.batch)
-    pages_per_seq = CONTEXT // BLOCK_SIZE + 1
+    block_size = args.block_size
+    pages_per_seq = CONTEXT // block_size + 1
     engine = Engine.from_pretrained(EngineConfig(
         model=folder, dtype="bfloat16", max_model_len=CONTEXT + 16, max_num_seqs=max_batch,
         max_num_batched_tokens=max(PREFILL_TOKENS, max_batch), max_prefill_chunk_size=PREFILL_TOKENS,
-        block_size=BLOCK_SIZE, num_gpu_blocks=max_batch * pages_per_seq + 8, seed=0,
+        block_size=block_size, num_gpu_blocks=max_batch * pages_per_seq + 8, seed=0,
     ))
     import shutil
 
@@ -362,15 +366,17 @@ def run_own(args):
         kernel_times["attention_b64"] = kernel_report({"attention": times64["attention"]}, 64, keys64)["attention"]
         kernel_times["method"] = ("one decode step launched kernel by kernel behind a queued delay, a CUDA event after every "
                                   "launch; us summed over the layers, bytes = the matrices (the cache) each kind must read")
-        # The reference's page size (16 keys): a second engine on the same weights.
-        small_pages = Engine.from_pretrained(EngineConfig(
+        # The other page size (the engine's default of 64 keys, or 16 if the run itself uses
+        # 64): a second engine on the same weights.
+        other = ENGINE_DEFAULT_BLOCK_SIZE if block_size != ENGINE_DEFAULT_BLOCK_SIZE else 16
+        other_pages = Engine.from_pretrained(EngineConfig(
             model=folder, dtype="bfloat16", max_model_len=CONTEXT + 16, max_num_seqs=args.batch,
             max_num_batched_tokens=max(PREFILL_TOKENS, args.batch), max_prefill_chunk_size=PREFILL_TOKENS,
-            block_size=16, num_gpu_blocks=args.batch * (CONTEXT // 16 + 2) + 8, seed=0,
+            block_size=other, num_gpu_blocks=args.batch * (CONTEXT // other + 2) + 8, seed=0,
         ))
-        tok_s, _, _, _ = decode_point(args.batch, max(8, args.steps // 2), 3, engine=small_pages)
-        points[f"decode_b{args.batch}_block16"] = round(tok_s, 1)
-        del small_pages
+        tok_s, _, _, _ = decode_point(args.batch, max(8, args.steps // 2), 3, engine=other_pages)
+        points[f"decode_b{args.batch}_block{other}"] = round(tok_s, 1)
+        del other_pages
     shutil.rmtree(folder, ignore_errors=True)
 
     # End to end through the entry point: Engine.step with host tokens in and out.  Prompts are
@@ -423,7 +429,7 @@ def run_own(args):
             "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
             "head_dim": cfg["hidden_size"] // cfg["num_attention_heads"], "intermediate": cfg["intermediate_size"],
             "vocab": cfg["vocab_size"], "global_batch": args.batch, "seq_len": CONTEXT, "prefill_tokens": PREFILL_TOKENS,
-            "kv_block_size": BLOCK_SIZE, "kv_block_size_reference_default": 16, "tied_embeddings": True, "parallelism": "single GPU",
+            "kv_block_size": block_size, "kv_block_size_engine_default": ENGINE_DEFAULT_BLOCK_SIZE, "tied_embeddings": True, "parallelism": "single GPU",
             "l2": "inputs larger than L2 (weights streamed every step)", "gemm": "decode: own tcgen05 kernels; prefill: cuBLAS (library)",
         },
         "clocks": clock_summary,
@@ -612,6 +618,7 @@ def main():
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers of the same sizes (reported)")
+    parser.add_argument("--block-size", type=int, default=BLOCK_SIZE, help="keys per cache page of the main engine (reported)")
     parser.add_argument("--impl", default="own", choices=["own", "reference"])
     parser.add_argument("--no-points", dest="points", action="store_false", help="skip the batch 1 / 64 points")
     args = parser.parse_args()
