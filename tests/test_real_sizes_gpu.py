@@ -59,6 +59,10 @@ def sized(request, tmp_path_factory):
     torch.cuda.empty_cache()
     yield name, folder, cfg, SIZES[name], prompts, want
     torch.cuda.empty_cache()
+    # Gigabytes of weights: not left for pytest's own clean-up, which keeps the last runs.
+    import shutil
+
+    shutil.rmtree(folder, ignore_errors=True)
 
 
 def replay(replayer, name, tokens, cuts, rows):
