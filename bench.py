@@ -457,7 +457,7 @@ def run_reference(args):
         print(json.dumps({"impl": "reference",
                           "unavailable": f"no copy of the reference's source tree at {os.path.relpath(ref_root, ROOT)}"}))
         return 0
-    log_dir = os.path.join(ROOT, "gpurun_out")
+    log_dir = os.environ.get("VELOX_BENCH_LOG_DIR") or tempfile.gettempdir()
     try:
         line = _reference_numbers(args, ref_root)
     except Exception as exc:  # the reference's own code failed here: say why, keep the traceback
