@@ -592,16 +592,17 @@ def plain_candidates(scaled, top_k, top_p):
     return set(order[keep].tolist())
 
 
+@pytest.mark.parametrize("kind", [1, 2], ids=["one_cta", "cluster"])
 @pytest.mark.parametrize("vocab", [3001, 50021])
 @pytest.mark.parametrize("top_k,top_p", [(5, 1.0), (0, 0.6), (40, 0.9), (1, 1.0), (0, 0.05), (700, 0.999)])
-def test_filter_threshold(k, top_k, top_p, vocab):
+def test_filter_threshold(k, top_k, top_p, vocab, kind):
     gen = torch.Generator().manual_seed(top_k + int(top_p * 100))
     R = 4
     logits = (torch.randn(R, vocab, generator=gen) * 3).cuda()
     temps = torch.tensor([0.7, 1.0, 1.3, 0.0]).cuda()
     thr = torch.empty(R, device="cuda")
     k.filter_threshold(logits, R, temps, torch.full((R,), top_k, dtype=torch.int32).cuda(),
-                       torch.full((R,), top_p).cuda(), thr)
+                       torch.full((R,), top_p).cuda(), thr, kind=kind)
     for r in range(3):
         scaled = logits[r].double().cpu() / float(temps[r])
         want = plain_candidates(scaled, top_k, top_p)
@@ -610,6 +611,52 @@ def test_filter_threshold(k, top_k, top_p, vocab):
         assert len(got ^ want) <= 1, (len(got), len(want))
         assert max(scaled.argmax().item(), 0) in got
     assert thr[3].item() == float("-inf")
+
+
+@pytest.mark.parametrize("vocab", [7, 1000, 8191, 151936, 196608])
+def test_filter_threshold_kernels_agree(k, vocab):
+    """One CTA a row and the cluster of eight add up the same integers: equal thresholds, bit
+    for bit, with rows off a 16-byte boundary, mixed options per row, NaN and -inf entries
+    and a row whose mass sits in one entry."""
+    gen = torch.Generator().manual_seed(vocab)
+    R = 9
+    # With an odd row length most rows start off a 16-byte boundary.
+    store = torch.randn(R, vocab, generator=gen) * torch.tensor([0.1, 0.5, 1, 2, 4, 8, 1, 1, 1]).unsqueeze(1)
+    store[6, : vocab // 2] = float("-inf")
+    store[7, ::5] = float("nan")
+    store[8, vocab // 3] = 60.0
+    logits = store.cuda()
+    temps = torch.tensor([0.7, 1.0, 1.3, 0.0, 0.3, 2.0, 1.0, 1.0, 1.0]).cuda()
+    top_k = torch.tensor([0, 50, 3, 5, 0, vocab + 5, 0, 20, 0], dtype=torch.int32).cuda()
+    top_p = torch.tensor([0.9, 1.0, 0.5, 0.9, 0.999, 0.95, 0.8, 0.7, 0.9]).cuda()
+    one, cluster, auto = (torch.full((R,), 7.0, device="cuda") for _ in range(3))
+    k.filter_threshold(logits, R, temps, top_k, top_p, one, kind=1)
+    k.filter_threshold(logits, R, temps, top_k, top_p, cluster, kind=2)
+    k.filter_threshold(logits, R, temps, top_k, top_p, auto, kind=0)
+    assert torch.equal(one.view(torch.int32), cluster.view(torch.int32)), (one.tolist(), cluster.tolist())
+    assert torch.equal(one.view(torch.int32), auto.view(torch.int32))
+    assert one[3].item() == float("-inf")
+    # The entry that holds the row's mass is the only candidate of the last row.
+    assert int((logits[8] >= one[8]).sum()) == 1
+
+
+def test_filter_threshold_beyond_the_cluster_kernel(k):
+    """A row longer than the cluster's registers hold takes the one-CTA kernel; asking for the
+    cluster kernel by name is refused."""
+    vocab, R = 196608 + 40, 2
+    gen = torch.Generator().manual_seed(3)
+    logits = (torch.randn(R, vocab, generator=gen) * 2).cuda()
+    temps = torch.ones(R).cuda()
+    top_k = torch.tensor([10, 0], dtype=torch.int32).cuda()
+    top_p = torch.tensor([1.0, 0.5]).cuda()
+    thr = torch.empty(R, device="cuda")
+    k.filter_threshold(logits, R, temps, top_k, top_p, thr)
+    assert int((logits[0] >= thr[0]).sum()) == 10
+    want = plain_candidates(logits[1].double().cpu(), 0, 0.5)
+    got = set(torch.nonzero(logits[1] >= thr[1]).flatten().tolist())
+    assert len(got ^ want) <= 1
+    with pytest.raises(RuntimeError):
+        k.filter_threshold(logits, R, temps, top_k, top_p, thr, kind=2)
 
 
 def test_penalties(k):

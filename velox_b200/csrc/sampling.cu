@@ -227,9 +227,9 @@ sample_kernel(const float* __restrict__ logits, int vocab, long long row_stride,
 // The threshold is found digit by digit over the ordered bit patterns of float (11 + 11 + 10
 // bits): a sweep over the row builds, in shared memory, the histogram of the next digit among
 // the entries that share the digits found so far (how many, and their mass); the digit is the
-// smallest one above which count and mass still pass.  Five sweeps over the row in all (maximum,
-// normaliser, three digits) where a bisection over the patterns took up to 34 (measured at 64
-// rows of 151,936: 0.17 ms instead of 1.2 ms).  Masses are summed as 2^-40 fixed-point
+// smallest one above which count and mass still pass.  Four sweeps over the row in all (maximum,
+// three digits; the first digit's histogram also gives the normaliser) where a bisection over
+// the patterns took up to 34.  Masses are summed as 2^-40 fixed-point
 // integers, so the histogram, and with it the threshold, does not depend on the order in which
 // threads add.
 // ---------------------------------------------------------------------------------------------
@@ -281,6 +281,66 @@ __device__ __forceinline__ void suffix_sums(unsigned int c, unsigned long long m
   __syncthreads();
 }
 
+// What the digit search carries from one digit to the next: how many entries, and how much
+// mass, lie above the digits found so far, and the mass that top_p allows.
+struct DigitSearch {
+  unsigned int above_count;
+  unsigned long long above_mass, mass_limit;
+};
+
+struct DigitChoice {
+  unsigned int digit, count;
+  unsigned long long mass, total;
+};
+
+// The next digit from the row's histogram of it, by a block of 1,024 threads: thread t brings
+// the bins of digits 2t and 2t + 1.  A digit d passes if what lies above it (the larger digits,
+// and everything above the digits found before) is fewer than k entries and less than top_p of
+// the mass; passing is monotone in the digit, and the digit chosen is the smallest that passes.
+// The first digit's histogram holds every entry of the row, so its masses add up to the
+// normaliser: the sums that are compared are sums of the same integers.
+__device__ __forceinline__ unsigned int choose_digit(unsigned int c0, unsigned int c1, unsigned long long m0,
+                                                     unsigned long long m1, bool first, bool use_k, int k, bool use_p,
+                                                     float p, DigitSearch& search, unsigned int* sc,
+                                                     unsigned long long* sm, DigitChoice* choice) {
+  unsigned int c_above;
+  unsigned long long m_above;
+  suffix_sums(c0 + c1, m0 + m1, sc, sm, c_above, m_above);
+  if (first) {
+    if (threadIdx.x == 0) choice->total = m_above + m0 + m1;
+    __syncthreads();
+    search.mass_limit = (unsigned long long)((double)p * (double)choice->total);
+  }
+  const unsigned int c_hi = search.above_count + c_above, c_lo = c_hi + c1;  // above digit 2t + 1, above 2t
+  const unsigned long long m_hi = search.above_mass + m_above, m_lo = m_hi + m1;
+  const bool pass_hi = (!use_k || c_hi < (unsigned int)k) && (!use_p || m_hi < search.mass_limit);
+  const bool pass_lo = (!use_k || c_lo < (unsigned int)k) && (!use_p || m_lo < search.mass_limit);
+  // The smallest passing digit is the one whose lower neighbour fails (or digit 0).
+  if (pass_hi && !pass_lo) {
+    choice->digit = 2u * threadIdx.x + 1u;
+    choice->count = c_hi;
+    choice->mass = m_hi;
+  }
+  if (pass_lo) {
+    // The digit below 2t is 2t - 1 (thread t - 1's); what lies above it is also digit 2t.
+    bool below_fails = threadIdx.x == 0;
+    if (!below_fails) {
+      const unsigned int cb = c_lo + c0;
+      const unsigned long long mb = m_lo + m0;
+      below_fails = !((!use_k || cb < (unsigned int)k) && (!use_p || mb < search.mass_limit));
+    }
+    if (below_fails) {
+      choice->digit = 2u * threadIdx.x;
+      choice->count = c_lo;
+      choice->mass = m_lo;
+    }
+  }
+  __syncthreads();
+  search.above_count = choice->count;
+  search.above_mass = choice->mass;
+  return choice->digit;
+}
+
 // Calls f(value) for every entry of a row, the block's threads side by side.  With a row that
 // starts on a 16-byte boundary a thread asks for four vectors of four entries before it looks
 // at the first: sixteen loads' worth under way per thread instead of one (a sweep with one was
@@ -321,8 +381,7 @@ filter_threshold_kernel(const float* __restrict__ logits, int vocab, long long r
   extern __shared__ __align__(16) unsigned char filter_smem[];
   unsigned long long* hist_mass = reinterpret_cast<unsigned long long*>(filter_smem);          // [COPIES][BINS]
   unsigned int* hist_count = reinterpret_cast<unsigned int*>(hist_mass + FILTER_COPIES * FILTER_BINS);  // [COPIES][BINS]
-  __shared__ unsigned int chosen_digit, chosen_count;
-  __shared__ unsigned long long chosen_mass, total_mass;
+  __shared__ DigitChoice choice;
   allow_dependents();
   grid_dependency_wait();
   const int r = blockIdx.x;
@@ -341,7 +400,7 @@ filter_threshold_kernel(const float* __restrict__ logits, int vocab, long long r
   const bool vectors = (reinterpret_cast<uintptr_t>(row) & 15) == 0;
 
   float m = -CUDART_INF_F;
-  sweep_row(row, vocab, vectors, [&](float x) { m = fmaxf(m, x * inv_t); });
+  sweep_row(row, vocab, vectors, [&](float x) { m = fmaxf(m, __fmul_rn(x, inv_t)); });
   m = warp_max(m);
   if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = m;
   __syncthreads();
@@ -354,25 +413,9 @@ filter_threshold_kernel(const float* __restrict__ logits, int vocab, long long r
   m = scratch[0];
   __syncthreads();
 
-  // The normaliser, in the same fixed point as the histogram's masses.
-  if (threadIdx.x == 0) total_mass = 0ull;
-  __syncthreads();
-  {
-    unsigned long long z = 0ull;
-    const float top = m;
-    sweep_row(row, vocab, vectors, [&](float x) { z += fixed_mass(expf(x * inv_t - top)); });
-#pragma unroll
-    for (int offset = 16; offset > 0; offset >>= 1) z += __shfl_xor_sync(0xffffffffu, z, offset);
-    if ((threadIdx.x & 31) == 0) atomicAdd(&total_mass, z);
-  }
-  __syncthreads();
-  const unsigned long long mass_limit = (unsigned long long)((double)p * (double)total_mass);
-
-  // Digits of the threshold's pattern, most significant first; above_* count what lies above
-  // the digits found so far.
+  // Digits of the threshold's pattern, most significant first.
   uint32_t prefix = 0u;
-  unsigned int above_count = 0u;
-  unsigned long long above_mass = 0ull;
+  DigitSearch search = {0u, 0ull, 0ull};
   const int shifts[3] = {21, 10, 0};
   const int bits[3] = {11, 11, 10};
   for (int level = 0; level < 3; ++level) {
@@ -390,7 +433,9 @@ filter_threshold_kernel(const float* __restrict__ logits, int vocab, long long r
     const uint32_t above = prefix;
     const int level_bits = bits[level];
     sweep_row(row, vocab, vectors, [&](float x) {
-      const float s = x * inv_t;
+      // The rounded product, never folded into the subtraction below: the scaled value is the
+      // same number wherever it is looked at (here, in the cluster kernel, in the sampler).
+      const float s = __fmul_rn(x, inv_t);
       if (!(s == s)) return;  // NaN is never a candidate
       const uint32_t key = float_key(s);
       if (level > 0 && (key >> (shift + level_bits)) != above) return;
@@ -400,59 +445,195 @@ filter_threshold_kernel(const float* __restrict__ logits, int vocab, long long r
       if (use_p) atomicAdd(&my_mass[digit], fixed_mass(expf(s - top)));
     });
     __syncthreads();
-    if (level == 0) {
-      for (int b = threadIdx.x; b < FILTER_BINS; b += blockDim.x) {
-        unsigned int c = hist_count[b];
-        unsigned long long w = hist_mass[b];
+    unsigned int c[2] = {0u, 0u};
+    unsigned long long w[2] = {0ull, 0ull};
+    for (int copy = 0; copy < copies; ++copy)
 #pragma unroll
-        for (int copy = 1; copy < FILTER_COPIES; ++copy) {
-          c += hist_count[copy * FILTER_BINS + b];
-          w += hist_mass[copy * FILTER_BINS + b];
-        }
-        hist_count[b] = c;
-        hist_mass[b] = w;
+      for (int i = 0; i < 2; ++i) {
+        c[i] += hist_count[copy * FILTER_BINS + 2 * threadIdx.x + i];
+        w[i] += hist_mass[copy * FILTER_BINS + 2 * threadIdx.x + i];
       }
-      __syncthreads();
-    }
-    // Thread t owns digits 2t and 2t + 1.  A digit d passes if what lies above it (the larger
-    // digits, and everything above the prefix) is fewer than k entries and less than top_p.
-    const unsigned int c0 = hist_count[2 * threadIdx.x], c1 = hist_count[2 * threadIdx.x + 1];
-    const unsigned long long m0 = hist_mass[2 * threadIdx.x], m1 = hist_mass[2 * threadIdx.x + 1];
-    unsigned int c_above;
-    unsigned long long m_above;
-    suffix_sums(c0 + c1, m0 + m1, sc, sm, c_above, m_above);
-    const unsigned int c_hi = above_count + c_above, c_lo = c_hi + c1;  // above digit 2t + 1, above 2t
-    const unsigned long long m_hi = above_mass + m_above, m_lo = m_hi + m1;
-    const bool pass_hi = (!use_k || c_hi < (unsigned int)k) && (!use_p || m_hi < mass_limit);
-    const bool pass_lo = (!use_k || c_lo < (unsigned int)k) && (!use_p || m_lo < mass_limit);
-    // Passing is monotone in the digit: the smallest passing digit is the one whose lower
-    // neighbour fails (or digit 0).
-    if (pass_hi && !pass_lo) {
-      chosen_digit = 2u * threadIdx.x + 1u;
-      chosen_count = c_hi;
-      chosen_mass = m_hi;
-    }
-    if (pass_lo) {
-      // The digit below 2t is 2t - 1 (thread t - 1's); what lies above it is also digit 2t.
-      bool below_fails = threadIdx.x == 0;
-      if (!below_fails) {
-        const unsigned int cb = c_lo + c0;
-        const unsigned long long mb = m_lo + m0;
-        below_fails = !((!use_k || cb < (unsigned int)k) && (!use_p || mb < mass_limit));
-      }
-      if (below_fails) {
-        chosen_digit = 2u * threadIdx.x;
-        chosen_count = c_lo;
-        chosen_mass = m_lo;
-      }
-    }
-    __syncthreads();
-    prefix = (prefix << bits[level]) | chosen_digit;
-    above_count = chosen_count;
-    above_mass = chosen_mass;
+    const unsigned int digit = choose_digit(c[0], c[1], w[0], w[1], level == 0, use_k, k, use_p, p, search, sc, sm, &choice);
+    prefix = (prefix << bits[level]) | digit;
     __syncthreads();
   }
   if (threadIdx.x == 0) threshold[r] = key_float(prefix);
+}
+
+// ---------------------------------------------------------------------------------------------
+// The same threshold by a cluster of eight CTAs per row, for rows of up to 196,608 entries.  Each
+// CTA reads an eighth of the row once and keeps it in registers (24 entries a thread); what the
+// kernel above does in five sweeps over memory happens here over registers.  Every CTA builds
+// the histogram of its share in its own shared memory and adds the bins that are not empty into
+// the row's histogram, which lies in the shared memory of the cluster's first CTA; that CTA
+// chooses the digit (with the same code as above) and writes it into its peers' shared memory.
+// The normaliser is the sum of the first histogram's masses: all sums are of the same integers
+// as above, so both kernels give the same threshold bit for bit.
+//
+// A 64-bit sum in shared memory is a compare-and-swap loop; the masses (41 bits at most) are
+// therefore added as two 32-bit words, the low word's carry found from the value it held before.
+// ---------------------------------------------------------------------------------------------
+constexpr int FC_CLUSTER = 8;
+constexpr int FC_PER_THREAD = 24;
+constexpr int FC_COPIES = 4;
+constexpr int FC_MAX_VOCAB = FC_CLUSTER * FILTER_THREADS * FC_PER_THREAD;
+constexpr size_t FC_SMEM_BYTES = (size_t)FILTER_BINS * (sizeof(unsigned long long) + sizeof(unsigned int)) +
+                                 (size_t)FC_COPIES * FILTER_BINS * 3 * sizeof(unsigned int);
+
+__device__ __forceinline__ void add_mass_words(unsigned int* lo, unsigned int* hi, uint32_t bin, unsigned long long w) {
+  const unsigned int wl = (unsigned int)w;
+  unsigned int wh = (unsigned int)(w >> 32);
+  if (wl != 0u) {
+    const unsigned int before = atomicAdd(&lo[bin], wl);
+    if (before + wl < before) ++wh;  // the low word wrapped
+  }
+  if (wh != 0u) atomicAdd(&hi[bin], wh);
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// The address, in this CTA's window onto the cluster's shared memory, of `local` in CTA `rank`.
+template <typename T>
+__device__ __forceinline__ T* cluster_peer(T* local, unsigned int rank) {
+  uint64_t out;
+  asm volatile("mapa.u64 %0, %1, %2;" : "=l"(out) : "l"(reinterpret_cast<uint64_t>(local)), "r"(rank));
+  return reinterpret_cast<T*>(out);
+}
+
+__global__ void __launch_bounds__(FILTER_THREADS, 1)
+filter_threshold_cluster_kernel(const float* __restrict__ logits, int vocab, long long row_stride,
+                                const float* __restrict__ temperature, const int* __restrict__ top_k,
+                                const float* __restrict__ top_p, float* __restrict__ threshold) {
+  __shared__ float scratch[32];
+  __shared__ unsigned int sc[32];
+  __shared__ unsigned long long sm[32];
+  __shared__ float peer_max[FC_CLUSTER];
+  __shared__ unsigned int chosen_digit;
+  __shared__ DigitChoice choice;
+  extern __shared__ __align__(16) unsigned char filter_smem[];
+  unsigned long long* row_mass = reinterpret_cast<unsigned long long*>(filter_smem);   // [BINS], used in CTA 0
+  unsigned int* row_count = reinterpret_cast<unsigned int*>(row_mass + FILTER_BINS);    // [BINS], used in CTA 0
+  unsigned int* own_count = row_count + FILTER_BINS;                                    // [COPIES][BINS]
+  unsigned int* own_lo = own_count + FC_COPIES * FILTER_BINS;
+  unsigned int* own_hi = own_lo + FC_COPIES * FILTER_BINS;
+  allow_dependents();
+  grid_dependency_wait();
+  unsigned int rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  const int r = blockIdx.x / FC_CLUSTER;
+  const int tid = (int)threadIdx.x;
+  const float temp = temperature[r];
+  const int k = top_k[r];
+  const float p = top_p[r];
+  const bool use_k = k > 0 && k < vocab;
+  const bool use_p = p < 1.0f;
+  // The same for every CTA of the cluster: none is left waiting at a barrier.
+  if (temp == 0.f || (!use_k && !use_p)) {
+    if (rank == 0u && tid == 0) threshold[r] = -CUDART_INF_F;
+    return;
+  }
+  const float* row = logits + (size_t)r * row_stride;
+  const float inv_t = 1.0f / fmaxf(temp, 1e-5f);
+  const bool vectors = (reinterpret_cast<uintptr_t>(row) & 15) == 0;
+
+  // This CTA's share in groups of four entries, the threads side by side; what lies past the
+  // share or the row is NaN, which no step below counts.
+  const int groups = (vocab + 3) >> 2;
+  const int share = (groups + FC_CLUSTER - 1) / FC_CLUSTER;
+  const int group_begin = (int)rank * share, group_end = min(groups, group_begin + share);
+  float s[FC_PER_THREAD];
+#pragma unroll
+  for (int j = 0; j < FC_PER_THREAD / 4; ++j) {
+    const int g = group_begin + j * FILTER_THREADS + tid;
+    const int base = g << 2;
+    if (g < group_end && vectors && base + 4 <= vocab) {
+      const float4 q = reinterpret_cast<const float4*>(row)[g];
+      s[4 * j] = __fmul_rn(q.x, inv_t), s[4 * j + 1] = __fmul_rn(q.y, inv_t), s[4 * j + 2] = __fmul_rn(q.z, inv_t),
+      s[4 * j + 3] = __fmul_rn(q.w, inv_t);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) s[4 * j + i] = (g < group_end && base + i < vocab) ? __fmul_rn(row[base + i], inv_t) : CUDART_NAN_F;
+    }
+  }
+  for (int b = tid; b < FILTER_BINS; b += FILTER_THREADS) {
+    row_mass[b] = 0ull;
+    row_count[b] = 0u;
+  }
+  for (int b = tid; b < FC_COPIES * FILTER_BINS; b += FILTER_THREADS) {
+    own_count[b] = 0u;
+    own_lo[b] = 0u;
+    own_hi[b] = 0u;
+  }
+  float m = -CUDART_INF_F;
+#pragma unroll
+  for (int j = 0; j < FC_PER_THREAD; ++j) m = fmaxf(m, s[j]);  // fmaxf passes over NaN
+  m = warp_max(m);
+  if ((tid & 31) == 0) scratch[tid >> 5] = m;
+  __syncthreads();
+  if (tid < 32) {
+    float w = scratch[tid];
+    w = warp_max(w);
+    if (tid < FC_CLUSTER) *cluster_peer(&peer_max[rank], (unsigned int)tid) = w;
+  }
+  // Every CTA's maximum is in every CTA, and CTA 0's row histogram is zero, before anyone adds.
+  cluster_sync_all();
+  m = peer_max[0];
+#pragma unroll
+  for (int c = 1; c < FC_CLUSTER; ++c) m = fmaxf(m, peer_max[c]);
+  const float top = m;
+
+  unsigned int* count0 = cluster_peer(row_count, 0u);
+  unsigned long long* mass0 = cluster_peer(row_mass, 0u);
+  uint32_t prefix = 0u;
+  DigitSearch search = {0u, 0ull, 0ull};
+  const int shifts[3] = {21, 10, 0};
+  const int bits[3] = {11, 11, 10};
+#pragma unroll
+  for (int level = 0; level < 3; ++level) {
+    const int shift = shifts[level], level_bits = bits[level];
+    const uint32_t digit_mask = (1u << level_bits) - 1u;
+    const int copies = level == 0 ? FC_COPIES : 1;
+    const int copy = level == 0 ? ((tid >> 6) % FC_COPIES) * FILTER_BINS : 0;
+#pragma unroll
+    for (int j = 0; j < FC_PER_THREAD; ++j) {
+      const float x = s[j];
+      if (!(x == x)) continue;
+      const uint32_t key = float_key(x);
+      if (level > 0 && (key >> (shift + level_bits)) != prefix) continue;
+      const uint32_t digit = (key >> shift) & digit_mask;
+      if (use_k) atomicAdd(&own_count[copy + digit], 1u);
+      if (use_p) add_mass_words(own_lo + copy, own_hi + copy, digit, fixed_mass(expf(x - top)));
+    }
+    __syncthreads();
+    // This CTA's bins into the row's histogram; its own go back to zero for the next digit.
+    for (int b = tid; b < FILTER_BINS; b += FILTER_THREADS) {
+      unsigned int c = 0u;
+      unsigned long long w = 0ull;
+      for (int i = 0; i < copies; ++i) {
+        const int at = i * FILTER_BINS + b;
+        c += own_count[at];
+        w += ((unsigned long long)own_hi[at] << 32) + own_lo[at];
+        own_count[at] = 0u, own_lo[at] = 0u, own_hi[at] = 0u;
+      }
+      if (c != 0u) atomicAdd(&count0[b], c);
+      if (w != 0ull) atomicAdd(&mass0[b], w);
+    }
+    cluster_sync_all();
+    if (rank == 0u) {
+      const unsigned int c0 = row_count[2 * tid], c1 = row_count[2 * tid + 1];
+      const unsigned long long m0 = row_mass[2 * tid], m1 = row_mass[2 * tid + 1];
+      row_count[2 * tid] = 0u, row_count[2 * tid + 1] = 0u;
+      row_mass[2 * tid] = 0ull, row_mass[2 * tid + 1] = 0ull;
+      const unsigned int digit = choose_digit(c0, c1, m0, m1, level == 0, use_k, k, use_p, p, search, sc, sm, &choice);
+      if (tid < FC_CLUSTER) *cluster_peer(&chosen_digit, (unsigned int)tid) = digit;
+    }
+    cluster_sync_all();
+    prefix = (prefix << level_bits) | chosen_digit;
+  }
+  if (rank == 0u && tid == 0) threshold[r] = key_float(prefix);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -532,16 +713,46 @@ VX_API int vx_sample(const float* logits, int num_rows, int vocab, long long row
   return (int)cudaGetLastError();
 }
 
+// kind 0: the cluster kernel where the row fits its registers, else one CTA a row; 1: one CTA a
+// row; 2: the cluster kernel or an error.
 VX_API int vx_filter_threshold(const float* logits, int num_rows, int vocab, long long row_stride,
                                const float* temperature, const int* top_k, const float* top_p,
-                               float* threshold, cudaStream_t stream) {
+                               float* threshold, int kind, cudaStream_t stream) {
   if (num_rows <= 0) return 0;
   static bool configured = false;
   if (!configured) {
-    const cudaError_t e = cudaFuncSetAttribute(filter_threshold_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               (int)FILTER_SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(filter_threshold_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)FILTER_SMEM_BYTES);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(filter_threshold_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)FC_SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
     configured = true;
+  }
+  if (kind == 2 && vocab > FC_MAX_VOCAB) return (int)cudaErrorInvalidValue;
+  if (kind != 1 && vocab <= FC_MAX_VOCAB) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3((unsigned)num_rows * FC_CLUSTER);
+    config.blockDim = dim3(FILTER_THREADS);
+    config.dynamicSmemBytes = FC_SMEM_BYTES;
+    config.stream = stream;
+    cudaLaunchAttribute attributes[2];
+    int count = 0;
+    attributes[count].id = cudaLaunchAttributeClusterDimension;
+    attributes[count].val.clusterDim.x = FC_CLUSTER;
+    attributes[count].val.clusterDim.y = 1;
+    attributes[count].val.clusterDim.z = 1;
+    ++count;
+    const char* serialised = getenv("VELOX_B200_NO_PDL");
+    if (serialised == nullptr || serialised[0] != '1') {
+      attributes[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attributes[count].val.programmaticStreamSerializationAllowed = 1;
+      ++count;
+    }
+    config.attrs = attributes;
+    config.numAttrs = count;
+    return (int)cudaLaunchKernelEx(&config, filter_threshold_cluster_kernel, logits, vocab, row_stride, temperature,
+                                   top_k, top_p, threshold);
   }
   launch_pdl(filter_threshold_kernel, dim3(num_rows), dim3(FILTER_THREADS), FILTER_SMEM_BYTES, stream, logits, vocab, row_stride,
                                                             temperature, top_k, top_p, threshold);

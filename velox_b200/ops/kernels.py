@@ -65,7 +65,7 @@ def core():
             _ptr, _c_ll, _ptr, _c_f, _ptr, _ptr, _ptr, _c_ll, _c_int, _c_int, _c_int, _ptr, _ptr,
         ]
         lib.vx_filter_threshold.argtypes = [
-            _ptr, _c_int, _c_int, _c_ll, _ptr, _ptr, _ptr, _ptr, _ptr,
+            _ptr, _c_int, _c_int, _c_ll, _ptr, _ptr, _ptr, _ptr, _c_int, _ptr,
         ]
         lib.vx_apply_penalties.argtypes = [
             _ptr, _c_int, _c_int, _c_ll, _ptr, _c_ll, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
@@ -790,7 +790,13 @@ def filter_threshold(
     top_k: torch.Tensor,
     top_p: torch.Tensor,
     threshold: torch.Tensor,
+    kind: int = 0,
 ) -> None:
+    """threshold[r]: the smallest scaled logit that is a top-k / top-p candidate of row r.
+
+    ``kind`` picks the kernel: 0 a cluster of eight CTAs per row where the row fits their
+    registers (196,608 entries) and one CTA per row otherwise, 1 always one CTA per row, 2 the
+    cluster kernel or an error.  Both give the same threshold bit for bit."""
     _need(logits, torch.float32, "logits")
     _need(temperature, torch.float32, "temperature")
     _need(top_k, torch.int32, "top_k")
@@ -798,7 +804,7 @@ def filter_threshold(
     _need(threshold, torch.float32, "threshold")
     _check(
         core().vx_filter_threshold(_p(logits), num_rows, logits.shape[1], logits.stride(0),
-                                   _p(temperature), _p(top_k), _p(top_p), _p(threshold), _stream()),
+                                   _p(temperature), _p(top_k), _p(top_p), _p(threshold), kind, _stream()),
         "filter_threshold",
     )
 
