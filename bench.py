@@ -4,9 +4,10 @@ tokens/s at 2,048 tokens, at Qwen2.5-1.5B layer sizes with random weights, on on
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference]
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second of the step function (device time
-of K decode steps, CUDA events); ``e2e`` is the same through the Python entry point
-(``Engine.step``: host token ids in through pinned memory, sampled tokens read back, every
-step).  ``prefill`` is one 2,048-token prompt in one step; ``roofline`` is the decode step's
+of K decode steps queued back to back, CUDA events; each step is fed the tokens the step
+before it sampled, on the device); ``e2e`` is the same through the Python entry point (the
+loop of ``Engine.generate``: every step's arrays go up through pinned memory and its sampled
+tokens are read back, one step behind).  ``prefill`` is one 2,048-token prompt in one step; ``roofline`` is the decode step's
 bytes (every weight once, the live requests' cache) over its time against the measured copy
 bandwidth.  With --gpus N > 1 it says that the engine is single-GPU and exits with 2.
 """
@@ -194,33 +195,42 @@ def run_own(args):
             cache.release_slot(seq)
 
     def decode_steps(seqs, steps, warmup, runner=runner, cache=cache, sampler=sampler):
-        """Device time (ms) of each of ``steps`` decode steps after ``warmup`` untimed ones."""
+        """Device time (ms) of ``steps`` decode steps after ``warmup`` untimed ones, and the
+        launches they made.  The timed steps are queued back to back, as ``Engine.generate``
+        queues them: each step's token ids are stand-ins that the embedding resolves from the
+        tokens the step before it sampled on the device, so the host prepares a step while the
+        device runs the one before; one pair of events brackets all of them."""
         batch = len(seqs)
         tokens = rng.integers(0, vocab, batch).tolist()
         params = [SamplingParams(temperature=0.0, max_tokens=1)] * batch
         names = [s.seq_id for s in seqs]
-        times = []
-        launches_before = None
-        for step in range(warmup + steps):
-            if step == warmup:
-                launches_before = kernels.launch_count + runner.kernels_replayed
+        runner.fed_tokens = sampler.tokens
+
+        def one_step(ids):
             chunks = []
-            for seq, token in zip(seqs, tokens):
+            for seq, token in zip(seqs, ids):
                 assert cache.append_slots(seq, 1)
                 chunks.append(StepChunk(seq, [token], (0,)))
-            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            torch.cuda.synchronize()
-            start.record()
             logits = runner.step(chunks)
             out = sampler.sample(logits, params, names, [0] * batch)
-            end.record()
-            torch.cuda.synchronize()
-            tokens = out.tolist()
             for seq in seqs:
                 cache.advance(seq, 1)
-            if step >= warmup:
-                times.append(start.elapsed_time(end))
-        return times, kernels.launch_count + runner.kernels_replayed - launches_before
+            return out
+
+        for _ in range(warmup):
+            tokens = one_step(tokens).tolist()
+        fed = [-1 - row for row in range(batch)]
+        launches_before = kernels.launch_count + runner.kernels_replayed
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(steps):
+            out = one_step(fed)
+        end.record()
+        torch.cuda.synchronize()
+        assert all(0 <= t < vocab for t in out.tolist())
+        runner.check_status()
+        return [start.elapsed_time(end) / steps] * steps, kernels.launch_count + runner.kernels_replayed - launches_before
 
     def decode_point(batch, steps, warmup, engine=engine):
         context = CONTEXT - steps - warmup - 1
@@ -379,7 +389,7 @@ def run_own(args):
         del other_pages
     shutil.rmtree(folder, ignore_errors=True)
 
-    # End to end through the entry point: Engine.step with host tokens in and out.  Prompts are
+    # End to end through the entry point, host tokens in and out.  Prompts are
     # prefilled in turn, so the first request decodes while the others still prefill (two
     # portions each); max_tokens leaves every request alive until the timed steps are over.
     head_start = 2 * args.batch
@@ -392,14 +402,19 @@ def run_own(args):
     while any(not r.is_decoding or r.num_output_tokens < 1 for r in requests):
         engine.step()
     for _ in range(args.warmup):
-        engine.step()
+        engine.step_pipelined()
+    engine.drain()
     torch.cuda.synchronize()
     produced_before = sum(r.num_output_tokens for r in requests)
     meta_bytes = 0
     t_start = time.perf_counter()
+    # The loop of Engine.generate: every call queues a step (its arrays go up in one copy from
+    # pinned memory) and reads the tokens of the step before from pinned memory; drain() reads
+    # the last step's.
     for _ in range(args.steps):
-        engine.step()
-        meta_bytes = max(meta_bytes, runner.last_meta_bytes)  # the step's arrays, one pinned-memory copy
+        engine.step_pipelined()
+        meta_bytes = max(meta_bytes, runner.last_meta_bytes)
+    engine.drain()
     torch.cuda.synchronize()
     e2e_seconds = time.perf_counter() - t_start
     produced = sum(r.num_output_tokens for r in requests) - produced_before
@@ -430,7 +445,8 @@ def run_own(args):
             "head_dim": cfg["hidden_size"] // cfg["num_attention_heads"], "intermediate": cfg["intermediate_size"],
             "vocab": cfg["vocab_size"], "global_batch": args.batch, "seq_len": CONTEXT, "prefill_tokens": PREFILL_TOKENS,
             "kv_block_size": block_size, "kv_block_size_engine_default": ENGINE_DEFAULT_BLOCK_SIZE, "tied_embeddings": True, "parallelism": "single GPU",
-            "l2": "inputs larger than L2 (weights streamed every step)", "gemm": "decode: own tcgen05 kernels; prefill: cuBLAS (library)",
+            "l2": "inputs larger than L2 (weights streamed every step)",
+            "decode_steps": "queued back to back; each is fed the tokens the step before sampled, on the device", "gemm": "decode: own tcgen05 kernels; prefill: cuBLAS (library)",
         },
         "clocks": clock_summary,
         "e2e": e2e,

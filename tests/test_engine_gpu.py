@@ -275,6 +275,60 @@ def test_stop_tokens_max_tokens_and_limits(folders):
         engine.add_request(Request("long2", [1] * 100, SamplingParams(max_tokens=40)))
 
 
+@pytest.mark.parametrize("dtype,case", [("float32", "tiny_a"), ("float32", "tiny_w"), ("bfloat16", "tiny_d")])
+def test_pipelined_generation_equals_step_by_step(folders, dtype, case):
+    """``generate`` queues a step before it has read the tokens of the one before and feeds
+    them on the device; the tokens, the reasons for ending and what the listeners hear are
+    those of one step at a time: greedy and seeded requests, a stop token in the middle of
+    decoding, penalties, prompts cut into portions, and a pool so small that requests are
+    preempted while a token is on its way."""
+    from velox_b200.engine.request import Request
+    from velox_b200.sampling.params import SamplingParams
+
+    folder, cfg, _ = folders[case]
+    prompts = random_prompts(cfg["vocab_size"], (30, 3, 41, 17, 26, 9), seed=12)
+
+    def run(pipeline, stop_on=None):
+        engine = build_engine(folder, dtype, num_gpu_blocks=45, pipeline_decode=pipeline)
+        heard = []
+        requests = [
+            Request("greedy", prompts[0], SamplingParams(temperature=0.0, max_tokens=30, ignore_eos=True)),
+            Request("stops", prompts[1], SamplingParams(temperature=0.0, max_tokens=30,
+                                                        stop_token_ids=[] if stop_on is None else [stop_on])),
+            Request("seeded", prompts[2], SamplingParams(temperature=0.9, seed=5, max_tokens=25, ignore_eos=True)),
+            Request("filtered", prompts[3], SamplingParams(temperature=1.1, seed=6, top_k=12, top_p=0.8, max_tokens=33,
+                                                           ignore_eos=True)),
+            Request("penalised", prompts[4], SamplingParams(temperature=0.7, seed=7, repetition_penalty=1.3,
+                                                            frequency_penalty=0.2, max_tokens=20, ignore_eos=True)),
+            Request("short", prompts[5], SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True)),
+        ]
+        for request in requests:
+            request.add_listener(lambda r, kind, token: heard.append((r.request_id, kind, token)))
+        engine.generate(requests)
+        assert not engine.has_work()
+        engine.scheduler.schedule()
+        engine.cache.assert_consistent()
+        assert engine.cache.num_free_pages() == engine.cache.num_total_pages
+        assert all(t >= 0 for r in requests for t in r.all_token_ids)
+        per_request = {r.request_id: [h[1:] for h in heard if h[0] == r.request_id] for r in requests}
+        return requests, per_request, engine.scheduler.num_preemptions
+
+    free, _, _ = run(False)
+    stop_on = free[1].output_token_ids[11]
+    want, want_heard, want_preemptions = run(False, stop_on)
+    got, got_heard, got_preemptions = run(True, stop_on)
+    assert want_preemptions > 0 and got_preemptions > 0
+    for a, b in zip(got, want):
+        assert a.output_token_ids == b.output_token_ids, a.request_id
+        assert a.finish_reason is b.finish_reason
+        assert got_heard[a.request_id] == want_heard[b.request_id]
+        assert got_heard[a.request_id][-1] == ("finish", None)
+        assert [t for kind, t in got_heard[a.request_id] if kind == "token"] == a.output_token_ids
+    first = free[1].output_token_ids.index(stop_on)
+    assert got[1].finish_reason.value == "stop" and got[1].output_token_ids == free[1].output_token_ids[: first + 1]
+    assert got[5].finish_reason.value == "length" and len(got[5].output_token_ids) == 1
+
+
 def test_llm_entry_point(folders):
     folder, cfg, tensors = folders["tiny_a"]
     from velox_b200.engine.engine import LLM

@@ -479,26 +479,55 @@ def test_rounded_plans_only_add_padding():
     assert (rounded.merge_items[len(plan.merge_items):, 0] == -1).all()
 
 
-def test_engine_loop_with_a_fake_model():
-    """``Engine.step`` and ``generate`` around a runner and a sampler that are stand-ins: portions
-    reach the runner in order, the last token of a prompt asks for logits, sampled tokens come
-    back to their requests, stop tokens and lengths end them, and every page returns."""
+class FakeReadback:
+    """Stands in for the pinned-memory read-back: the fake sampler's values, handed over later."""
+
+    def begin(self, tokens):
+        return tokens.tolist()
+
+    def end(self, ticket):
+        return list(ticket)
+
+
+class FakeTokens:
+    def __init__(self, values):
+        self.values = values
+
+    def tolist(self):
+        return list(self.values)
+
+
+def fake_engine(scheduler, cache, runner, sampler, pipeline=True, eos=()):
+    """An ``Engine`` around stand-ins for everything that needs a device."""
+    from types import SimpleNamespace
+
     from velox_b200.engine.engine import Engine
 
+    engine = Engine.__new__(Engine)
+    engine.scheduler, engine.cache, engine.runner, engine.sampler = scheduler, cache, runner, sampler
+    engine.readback, engine._flight = FakeReadback(), None
+    engine.config = SimpleNamespace(pipeline_decode=pipeline)
+    engine.eos_token_ids = frozenset(eos)
+    engine.stats = {name: [] for name in ("scheduler_ms", "prepare_ms", "gpu_ms", "cpu_sync_wait_ms", "sampling_ms", "step_ms")}
+    engine.num_steps, engine._timing = 0, False
+    return engine
+
+
+@pytest.mark.parametrize("pipeline", [False, True])
+def test_engine_loop_with_a_fake_model(pipeline):
+    """``Engine.generate`` around a runner and a sampler that are stand-ins, one step at a time
+    and pipelined: portions reach the runner in order, the last token of a prompt asks for
+    logits, sampled tokens come back to their requests, stop tokens and lengths end them, and
+    every page returns.  Pipelined, a decoded token is fed as the stand-in that names its row in
+    the step before, and a stop token costs one extra step whose token is thrown away."""
     scheduler, cache = make(num_pages=40, page_size=4, max_num_seqs=3, budget=16, chunk=8, max_model_len=64)
     seen = []
+    heard = []
 
     class FakeRunner:
         def step(self, chunks):
             seen.append([(c.seq.seq_id, list(c.tokens), tuple(c.want)) for c in chunks])
             return [c.seq.seq_id for c in chunks if c.want]
-
-    class FakeTokens:
-        def __init__(self, values):
-            self.values = values
-
-        def tolist(self):
-            return self.values
 
     class FakeSampler:
         def sample(self, logits, params, names, draw_indices, slots=None, history_lengths=None, status=None):
@@ -506,24 +535,131 @@ def test_engine_loop_with_a_fake_model():
             # request "s" draws its stop token as its second token; the others count upwards
             return FakeTokens([99 if name == "s" and index == 1 else 10 + index for name, index in zip(names, draw_indices)])
 
-    engine = Engine.__new__(Engine)
-    engine.scheduler, engine.cache, engine.runner, engine.sampler = scheduler, cache, FakeRunner(), FakeSampler()
-    engine.eos_token_ids = frozenset()
-    engine.stats = {name: [] for name in ("scheduler_ms", "prepare_ms", "gpu_ms", "cpu_sync_wait_ms", "sampling_ms", "step_ms")}
-    engine.num_steps, engine._timing = 0, False
+    engine = fake_engine(scheduler, cache, FakeRunner(), FakeSampler(), pipeline=pipeline)
     a = Request("a", list(range(1, 12)), SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True))
     s = Request("s", [5, 6], SamplingParams(temperature=0.0, max_tokens=9, stop_token_ids=[99]))
+    for request in (a, s):
+        request.add_listener(lambda r, kind, token: heard.append((r.request_id, kind, token)))
     engine.generate([a, s])
     assert a.output_token_ids == [10, 11, 12] and a.finish_reason is FinishReason.LENGTH
     assert s.output_token_ids == [10, 99] and s.finish_reason is FinishReason.STOP
+    assert a.all_token_ids == list(range(1, 12)) + [10, 11, 12] and s.all_token_ids == [5, 6, 10, 99]
+    # every token is announced once and in order, the end after the last token
+    assert [h for h in heard if h[0] == "a"] == [("a", "token", 10), ("a", "token", 11), ("a", "token", 12), ("a", "finish", None)]
+    assert [h for h in heard if h[0] == "s"] == [("s", "token", 10), ("s", "token", 99), ("s", "finish", None)]
     # first step: 8 tokens of a (a portion, no logits wanted), the whole of s (logits at its last token)
     assert seen[0] == [("a", list(range(1, 9)), ()), ("s", [5, 6], (1,))]
-    # second step: prompt portions first, decoded tokens after them
-    assert seen[1] == [("a", [9, 10, 11], (2,)), ("s", [10], (0,))]
+    # second step: prompt portions first, decoded tokens after them; s's first token was row 0
+    # of the first step's sampled rows
+    assert seen[1] == [("a", [9, 10, 11], (2,)), ("s", [-1 if pipeline else 10], (0,))]
     assert all(len(tokens) == 1 for step in seen[2:] for _, tokens, _ in step)
+    if pipeline:
+        # third step: both decode; their tokens are rows 0 (a) and 1 (s) of the second step
+        assert seen[2] == [("a", [-1], (0,)), ("s", [-2], (0,))]
+        # s's stop token became known after the third step had been queued with s in it; the
+        # fourth step was scheduled without it
+        assert [name for name, _, _ in seen[3]] == ["a"]
+    else:
+        assert seen[2] == [("a", [10], (0,))]
     scheduler.schedule()  # the last finished request is reaped at the next schedule()
     assert cache.num_free_pages() == cache.num_total_pages and cache.num_free_slots == 3
-    assert engine.num_steps == len(seen) and not scheduler.has_work()
+    assert engine.num_steps == len(seen) and not engine.has_work()
+
+
+def test_pipelined_steps_deliver_one_call_later_and_drain():
+    """``step_pipelined`` hands out a step's tokens during the next call; ``drain`` (and a plain
+    ``step``) first finish what is on its way.  Aborting a request between two calls drops the
+    token that is on its way to it."""
+    scheduler, cache = make(num_pages=40, page_size=4, max_num_seqs=3, budget=16, chunk=8, max_model_len=64)
+
+    class FakeRunner:
+        def step(self, chunks):
+            return [c.seq.seq_id for c in chunks if c.want]
+
+    class FakeSampler:
+        def sample(self, logits, params, names, draw_indices, slots=None, history_lengths=None, status=None):
+            return FakeTokens([100 * (1 + "abcd".index(name)) + index for name, index in zip(names, draw_indices)])
+
+    engine = fake_engine(scheduler, cache, FakeRunner(), FakeSampler())
+    a, b, c = (Request(name, [1, 2, 3], SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True)) for name in "abc")
+    for request in (a, b, c):
+        engine.add_request(request)
+    d = Request("d", [1, 2, 3], SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True))
+    # when a hears its second token, it takes c out: c's token of the same step is on its way
+    a.add_listener(lambda r, kind, token: engine.abort_request("c") if token == 101 else None)
+    engine.step_pipelined()
+    assert a.output_token_ids == [] and a.num_output_tokens == 0 and engine.has_work()
+    engine.step_pipelined()
+    # the first step's tokens are here; the second step is queued and nothing of it is booked yet
+    assert a.output_token_ids == [100] and a.num_output_tokens == 1 and a.num_computed_tokens == 3
+    assert engine.abort_request("b")
+    engine.step_pipelined()
+    # the second step is booked and handed out; b's token of it is thrown away, c's too
+    assert b.output_token_ids == [200] and b.finish_reason is FinishReason.ABORT and b.all_token_ids == [1, 2, 3, 200]
+    assert c.output_token_ids == [300] and c.finish_reason is FinishReason.ABORT and c.all_token_ids == [1, 2, 3, 300]
+    assert a.output_token_ids == [100, 101] and a.num_output_tokens == 2
+    engine.drain()
+    assert a.output_token_ids == [100, 101, 102] and a.num_output_tokens == 3 and engine._flight is None
+    engine.add_request(d)
+    engine.step()  # a plain step after pipelined ones: start to end
+    assert a.output_token_ids == [100, 101, 102, 103] and d.output_token_ids == [400]
+    engine.generate([])
+    assert a.output_token_ids == [100, 101, 102, 103, 104] and a.finish_reason is FinishReason.LENGTH
+    scheduler.schedule()
+    assert cache.num_free_pages() == cache.num_total_pages and not engine.has_work()
+    cache.assert_consistent()
+
+
+def test_pipelined_requests_with_penalties_get_their_tokens_first():
+    """A request whose sampler history is rebuilt from the host's token list never has a
+    stand-in in that list when a step is scheduled."""
+    scheduler, cache = make(num_pages=40, page_size=4, max_num_seqs=3, budget=16, chunk=8, max_model_len=64)
+    fed = []
+
+    class FakeRunner:
+        def step(self, chunks):
+            fed.extend(t for c in chunks for t in c.tokens)
+            return [c.seq.seq_id for c in chunks if c.want]
+
+    class FakeSampler:
+        def sample(self, logits, params, names, draw_indices, slots=None, history_lengths=None, status=None):
+            return FakeTokens([7 + index for index in draw_indices])
+
+    engine = fake_engine(scheduler, cache, FakeRunner(), FakeSampler())
+    a = Request("a", [1, 2, 3], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True, repetition_penalty=1.2))
+    engine.generate([a])
+    assert a.output_token_ids == [7, 8, 9, 10] and all(t >= 0 for t in fed)
+
+
+def test_pipelined_preemption_refeeds_the_stand_in():
+    """Pages run out while a token is on its way: the victim is recomputed, and if it is taken
+    up again in the very same step its portion ends with the stand-in for that token."""
+    scheduler, cache = make(num_pages=7, page_size=4, max_num_seqs=2, budget=32, chunk=32, max_model_len=24)
+    seen = []
+
+    class FakeRunner:
+        def step(self, chunks):
+            seen.append([(c.seq.seq_id, list(c.tokens)) for c in chunks])
+            return [c.seq.seq_id for c in chunks if c.want]
+
+    class FakeSampler:
+        def sample(self, logits, params, names, draw_indices, slots=None, history_lengths=None, status=None):
+            return FakeTokens([50 + index for index in draw_indices])
+
+    for pipeline in (False, True):
+        seen.clear()
+        engine = fake_engine(scheduler, cache, FakeRunner(), FakeSampler(), pipeline=pipeline)
+        a = Request("a" + str(pipeline), list(range(1, 10)), SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+        b = Request("b" + str(pipeline), list(range(1, 10)), SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+        engine.generate([a, b])
+        assert a.output_token_ids == list(range(50, 58)) and b.output_token_ids == list(range(50, 58))
+        assert scheduler.num_preemptions > 0
+        # whatever was fed for a position, resolved: the prompt and then the tokens drawn
+        for request in (a, b):
+            assert request.all_token_ids == list(range(1, 10)) + list(range(50, 58))
+        scheduler.schedule()
+        assert cache.num_free_pages() == cache.num_total_pages
+        cache.assert_consistent()
 
 
 def test_engine_step_raises_when_the_status_word_comes_back_set():
@@ -558,11 +694,7 @@ def test_engine_step_raises_when_the_status_word_comes_back_set():
             assert status == "the-device-word"
             return FakeTokens([11] * len(names) + [FakeRunner.word])
 
-    engine = Engine.__new__(Engine)
-    engine.scheduler, engine.cache, engine.runner, engine.sampler = scheduler, cache, FakeRunner(), FakeSampler()
-    engine.eos_token_ids = frozenset()
-    engine.stats = {name: [] for name in ("scheduler_ms", "prepare_ms", "gpu_ms", "cpu_sync_wait_ms", "sampling_ms", "step_ms")}
-    engine.num_steps, engine._timing = 0, False
+    engine = fake_engine(scheduler, cache, FakeRunner(), FakeSampler())
     a = Request("a", [1, 2, 3], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
     engine.add_request(a)
     engine.step()
@@ -573,6 +705,53 @@ def test_engine_step_raises_when_the_status_word_comes_back_set():
     assert a.output_token_ids == [11] and FakeRunner.cleared == 1
     engine.step()
     assert a.output_token_ids == [11, 11]
+
+
+def test_pipelined_status_error_gives_up_the_steps_on_their_way():
+    """Pipelined, a status word that comes back set belongs to a step that is already booked,
+    with another queued behind it: the requests of both are taken out, whoever was not part of
+    them goes on, and every page comes back."""
+    scheduler, cache = make(num_pages=40, page_size=4, max_num_seqs=3, budget=16, chunk=8, max_model_len=64)
+    heard = []
+
+    class FakeRunner:
+        status = "the-device-word"
+        word = 0
+
+        def step(self, chunks):
+            return [c.seq.seq_id for c in chunks if c.want]
+
+        def raise_for_status(self, word):
+            FakeRunner.word = 0
+            raise RuntimeError(f"a kernel of the step refused an access: word {word}")
+
+    class FakeSampler:
+        def sample(self, logits, params, names, draw_indices, slots=None, history_lengths=None, status=None):
+            return FakeTokens([11] * len(names) + [FakeRunner.word])
+
+    engine = fake_engine(scheduler, cache, FakeRunner(), FakeSampler())
+    a = Request("a", [1, 2, 3], SamplingParams(temperature=0.0, max_tokens=2, ignore_eos=True))
+    b = Request("b", [1, 2, 3], SamplingParams(temperature=0.0, max_tokens=9, ignore_eos=True))
+    for request in (a, b):
+        request.add_listener(lambda r, kind, token: heard.append((r.request_id, kind, token)))
+        engine.add_request(request)
+    engine.step_pipelined()
+    FakeRunner.word = 16
+    engine.step_pipelined()  # the second step carries the word; the first is handed out
+    assert a.output_token_ids == [11] and b.output_token_ids == [11]
+    late = Request("late", [4, 5], SamplingParams(temperature=0.0, max_tokens=2, ignore_eos=True))
+    with pytest.raises(RuntimeError, match="word 16"):
+        engine.step_pipelined()
+    # a had reached its length with the token that never came; b was in both steps
+    assert a.finish_reason is FinishReason.ABORT and b.finish_reason is FinishReason.ABORT
+    assert a.output_token_ids == [11] and a.all_token_ids == [1, 2, 3, 11] and b.all_token_ids == [1, 2, 3, 11]
+    assert heard.count(("a", "finish", None)) == 1 and heard.count(("b", "finish", None)) == 1
+    assert engine._flight is None
+    engine.generate([late])
+    assert late.output_token_ids == [11, 11] and late.finish_reason is FinishReason.LENGTH
+    scheduler.schedule()
+    assert cache.num_free_pages() == cache.num_total_pages and not engine.has_work()
+    cache.assert_consistent()
 
 
 def test_split_and_chunk_choices_fill_the_gpu_without_overfilling():

@@ -68,6 +68,8 @@ def parse_args(argv: Optional[List[str]] = None) -> argparse.Namespace:
     parser.add_argument("--num-gpu-blocks", type=int, default=None)
     parser.add_argument("--gpu-memory-utilization", type=float, default=0.85)
     parser.add_argument("--no-cuda-graphs", action="store_true")
+    parser.add_argument("--no-pipeline", action="store_true",
+                        help="one step at a time: read a step's tokens before the next step is queued")
     parser.add_argument("--sweep-batch-size", default=None, help="comma-separated max_num_seqs values to sweep")
     parser.add_argument("--show-outputs", action="store_true")
     parser.add_argument("--output-json", default=None)
@@ -127,10 +129,12 @@ def run_workload(engine, prompts, args, round_index: int = 0) -> Dict[str, objec
         engine.add_request(request)
     steps = 0
     live_tokens = 0  # keys the steps' attention reads, summed over the steps
+    one_step = engine.step_pipelined if engine.config.pipeline_decode else engine.step
     while engine.has_work():
         live_tokens += sum(r.num_tokens for r in engine.scheduler.running)
-        engine.step()
+        one_step()
         steps += 1
+    engine.drain()
     wall = time.perf_counter() - start
     generated = sum(r.num_output_tokens for r in requests)
     ttft = [times[0] - start for times in token_times.values() if times]
@@ -246,7 +250,7 @@ def main(argv: Optional[List[str]] = None) -> int:
             max_num_batched_tokens=max(args.max_num_batched_tokens, max_num_seqs),
             max_prefill_chunk_size=args.max_prefill_chunk_size, block_size=args.block_size,
             num_gpu_blocks=args.num_gpu_blocks, gpu_memory_utilization=args.gpu_memory_utilization,
-            enable_cuda_graphs=not args.no_cuda_graphs, seed=args.seed,
+            enable_cuda_graphs=not args.no_cuda_graphs, pipeline_decode=not args.no_pipeline, seed=args.seed,
         ))
         limit = engine.max_model_len - args.max_tokens - 1
         prompts = build_prompts(args.workload, num_requests, engine.model.vocab_size, limit, args.seed,

@@ -56,6 +56,10 @@ class EngineConfig:
     max_num_batched_tokens: int = _option(2048, lambda v: v >= 1, "be at least 1")
     max_prefill_chunk_size: int = _option(512, lambda v: v >= 1, "be at least 1")
     enable_cuda_graphs: bool = True
+    # ``Engine.generate`` queues a step on the device before it has read the tokens of the step
+    # before (which the new step takes from the sampler's device buffer); False: one step at a
+    # time, as ``Engine.step`` always does.
+    pipeline_decode: bool = True
 
     # the cache.  A page of 64 keys is one key tile of the attention kernels and arrives by one
     # tensor-map copy per 64 dims; with smaller pages the copy engines' rate of small copies,

@@ -16,15 +16,20 @@ namespace vx {
 
 // ---------------------------------------------------------------------------------------------
 // Embedding: resid[t, :] = float(table[ids[t], :])
+// With `fed` given, an id of -1 - r stands for "the token the sampler drew for row r of the step
+// before": it is read from fed[r] here, so a step can be queued before the host has seen the
+// tokens of the step before it.
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                             float* __restrict__ resid, int hidden, int vocab, int* status) {
+                             float* __restrict__ resid, int hidden, int vocab, int* status,
+                             const int* __restrict__ fed, int fed_rows) {
   VX_TRACE_SCOPE(1);
   allow_dependents();
   grid_dependency_wait();
   const int t = blockIdx.x;
   int id = ids[t];
+  if (id < 0 && fed != nullptr && -1 - id < fed_rows) id = fed[-1 - id];
   const bool bad = id < 0 || id >= vocab;
   if (bad) {
     if (threadIdx.x == 0) atomicOr(status, VX_STATUS_BAD_TOKEN_ID);
@@ -497,15 +502,15 @@ using namespace vx;
 VX_TRACE_API(vx_core)
 
 VX_API int vx_embed(const void* table, int dtype, const int* ids, float* resid, int num_tokens,
-                    int hidden, int vocab, int* status, cudaStream_t stream) {
+                    int hidden, int vocab, int* status, const int* fed, int fed_rows, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   const int threads = hidden >= 1024 ? 256 : 128;
   if (dtype == VX_DTYPE_F32)
     launch_pdl(embed_kernel<float>, dim3(num_tokens), dim3(threads), 0, stream, (const float*)table, ids, resid,
-                                                            hidden, vocab, status);
+               hidden, vocab, status, fed, fed_rows);
   else
-    launch_pdl(embed_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(threads), 0, stream, 
-        (const __nv_bfloat16*)table, ids, resid, hidden, vocab, status);
+    launch_pdl(embed_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(threads), 0, stream,
+               (const __nv_bfloat16*)table, ids, resid, hidden, vocab, status, fed, fed_rows);
   return (int)cudaGetLastError();
 }
 

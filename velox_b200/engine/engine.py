@@ -11,6 +11,14 @@ plus ``add_request`` / ``step`` / ``has_work`` / ``abort_request`` / ``snapshot`
 that drive the loop themselves, and ``LLM`` as a thin wrapper that takes and returns token id
 lists.  One step is: schedule -> one mixed forward -> sample the rows that completed -> one
 read-back of the sampled tokens (the only host wait of the step) -> bookkeeping.
+
+``step`` does these one after the other.  ``step_pipelined`` (what ``generate`` uses unless
+``EngineConfig.pipeline_decode`` is off) queues step k + 1 before it reads the tokens of step
+k: everything the scheduler needs of step k is known without them (which requests got a token,
+which reached their length), and the ids step k + 1 feeds for those tokens are stand-ins that
+the embedding kernel resolves from the sampler's device buffer.  The host's work for a step
+then runs beside the device's work for the step before.  A token that turns out to be a stop
+token ends its request one step late: the extra step's token for it is thrown away.
 """
 from __future__ import annotations
 
@@ -19,7 +27,8 @@ import logging
 import os
 import gc
 import time
-from typing import Dict, FrozenSet, Iterable, List, Optional, Sequence
+from dataclasses import dataclass, field
+from typing import Dict, FrozenSet, Iterable, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -30,7 +39,7 @@ from ..config.registry import architecture_of, load_model_config
 from ..config.model_config import read_config_json
 from ..ops import kernels
 from ..sampling.params import SamplingParams
-from ..sampling.sampler import Sampler
+from ..sampling.sampler import Sampler, TokenReadback
 from ..weights.loader import Checkpoint, WeightStore
 from .model import CausalLM
 from .request import FinishReason, Request
@@ -66,6 +75,20 @@ def _eos_token_ids(model_dir: str, spec_ids: Sequence[int]) -> FrozenSet[int]:
     # The architecture's own ids (its config.json's, or what its spec builder falls back to); a
     # model whose folder and spec name none ends on length and stop tokens only.
     return frozenset(spec_ids)
+
+
+@dataclass
+class _Flight:
+    """A step that is queued (or running) on the device and whose tokens the host has not read."""
+
+    scheduled: List[Tuple[Request, int]]   # (request, tokens it was given)
+    sampled: List[Request]                 # row r of the sampler's tokens is sampled[r]'s
+    ticket: object = None                  # of the read-back of the tokens (and the status word)
+    events: Optional[Tuple[torch.cuda.Event, torch.cuda.Event]] = None
+    launched_at: float = 0.0
+    committed: bool = False
+    tokens: Optional[List[int]] = None     # the sampled tokens, once they have been read
+    places: List[int] = field(default_factory=list)  # where each row's token goes; -1: nowhere
 
 
 class Engine:
@@ -118,6 +141,11 @@ class Engine:
                 self.sampler.start_sequence(seq.slot, request.all_token_ids, request.sampling_params)
 
         self.cache.on_slot_acquired = on_slot
+        # A step's ids may name a token of the step before by its row in the sampler's buffer.
+        self.runner.fed_tokens = self.sampler.tokens
+        # How sampled tokens (and the status word behind them) reach the host.
+        self.readback = TokenReadback(config.max_num_seqs + 1)
+        self._flight: Optional[_Flight] = None
 
         self.stats: Dict[str, List[float]] = {
             "scheduler_ms": [],
@@ -198,20 +226,22 @@ class Engine:
         return self.scheduler.abort_request(request_id)
 
     def has_work(self) -> bool:
-        return self.scheduler.has_work()
+        return self.scheduler.has_work() or self._flight is not None
 
-    # ------------------------------------------------------------------ one step
-    @torch.no_grad()
-    def step(self) -> None:
+    # ------------------------------------------------------------------ one step, in three parts
+    def _launch(self) -> Optional[_Flight]:
+        """Schedule a step and queue it on the device: forward, sampling, and the copy of the
+        sampled tokens to pinned memory.  Nothing here waits for the device."""
         step_start = time.perf_counter()
         scheduled = self.scheduler.schedule()
         t_sched = time.perf_counter()
         self.stats["scheduler_ms"].append((t_sched - step_start) * 1000)
         if scheduled.is_empty():
-            return
+            return None
 
         chunks: List[StepChunk] = []
         sampled: List[Request] = []
+        given: List[Tuple[Request, int]] = []
         for request in scheduled.scheduled:
             n = request.current_chunk_size
             if request.cache.slot is None or n < 1:
@@ -220,18 +250,17 @@ class Engine:
             chunks.append(
                 StepChunk(request.cache, request.tokens_for_chunk(n), want=(n - 1,) if completes else ())
             )
+            given.append((request, n))
             if completes:
                 sampled.append(request)
 
+        flight = _Flight(scheduled=given, sampled=sampled)
         if self._timing:
-            start_event = torch.cuda.Event(enable_timing=True)
-            end_event = torch.cuda.Event(enable_timing=True)
-            start_event.record()
+            flight.events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            flight.events[0].record()
         logits = self.runner.step(chunks)
         t_prepare = time.perf_counter()
         self.stats["prepare_ms"].append((t_prepare - t_sched) * 1000)
-
-        tokens: List[int] = []
         if sampled:
             tokens_gpu = self.sampler.sample(
                 logits,
@@ -242,47 +271,149 @@ class Engine:
                 history_lengths=[r.num_tokens for r in sampled],
                 status=getattr(self.runner, "status", None),
             )
-            if self._timing:
-                end_event.record()
-            sync_start = time.perf_counter()
-            # The one place per step where the host waits for the device.
-            tokens = tokens_gpu.tolist()
-            if len(tokens) > len(sampled):
-                # The device status word came back behind the tokens: kernels that refuse an
-                # access or give up a wait only set a bit there, and tokens drawn after that
-                # mean nothing.
-                word = tokens.pop()
-                if word:
-                    self.runner.raise_for_status(word)
-            now = time.perf_counter()
-            self.stats["cpu_sync_wait_ms"].append((now - sync_start) * 1000)
-            self.stats["sampling_ms"].append((now - t_prepare) * 1000)
-            if self._timing:
-                self.stats["gpu_ms"].append(start_event.elapsed_time(end_event))
+            flight.ticket = self.readback.begin(tokens_gpu)
+        if flight.events is not None:
+            flight.events[1].record()
+        flight.launched_at = time.perf_counter()
+        return flight
 
-        for request in scheduled.scheduled:
-            self.cache.advance(request.cache, request.current_chunk_size)
+    def _commit(self, flight: _Flight) -> None:
+        """What follows from a queued step without its tokens: the caches hold what it was
+        given, every sampled request is one token longer (a stand-in that names the sampler's
+        row takes the token's place), and a request that has reached its length is over."""
+        flight.committed = True
+        for request, n in flight.scheduled:
+            if request.finished:  # aborted, or ended by the tokens of the step before
+                continue
+            self.cache.advance(request.cache, n)
             request.refresh_status()
-        for request, token in zip(sampled, tokens):
-            request.append_token(int(token))
+        for row, request in enumerate(flight.sampled):
+            if request.finished:
+                flight.places.append(-1)
+                continue
+            flight.places.append(request.append_pending(-1 - row))
             request.refresh_status()
+            if request.num_output_tokens >= request.max_tokens:
+                request.finish(FinishReason.LENGTH, announce=False)
+
+    def _await(self, flight: _Flight) -> None:
+        """Wait for the step's tokens (the one place per step where the host waits for the
+        device) and look at the status word that came with them."""
+        if not flight.sampled or flight.tokens is not None:
+            return
+        sync_start = time.perf_counter()
+        tokens = self.readback.end(flight.ticket)
+        word = tokens.pop() if len(tokens) > len(flight.sampled) else 0
+        now = time.perf_counter()
+        self.stats["cpu_sync_wait_ms"].append((now - sync_start) * 1000)
+        self.stats["sampling_ms"].append((now - flight.launched_at) * 1000)
+        if flight.events is not None:
+            self.stats["gpu_ms"].append(flight.events[0].elapsed_time(flight.events[1]))
+        if word:
+            # Kernels that refuse an access or give up a wait only set a bit in the device
+            # status word, which rides behind the tokens; tokens drawn after that mean nothing.
+            self.runner.raise_for_status(word)
+        flight.tokens = tokens
+
+    def _deliver(self, flight: _Flight) -> None:
+        """Hand the tokens of a booked step to their requests."""
+        for request, token, place in zip(flight.sampled, flight.tokens or (), flight.places):
+            if place < 0:
+                continue
+            if request.finish_reason is FinishReason.ABORT:
+                request.drop_pending(place)
+                continue
+            request.resolve_pending(place, int(token))
             reason = request.should_stop(int(token), self.eos_token_ids)
-            if reason is not None:
+            if request.finished:
+                request.announce_finish(reason)
+            elif reason is not None:
+                # A stop token.  If the request is part of a step that is already queued, that
+                # step's token for it is dropped when it comes (the request is over by then).
                 request.finish(reason)
 
+    def _abandon(self, *flights: Optional[_Flight]) -> None:
+        """Steps whose tokens cannot be trusted: their requests are taken out (stand-ins for
+        tokens that will not come are dropped), so that the engine can go on with the rest."""
+        for flight in flights:
+            if flight is None:
+                continue
+            for request, place in zip(flight.sampled, flight.places):
+                if place >= 0:
+                    request.drop_pending(place)
+            for request, _ in flight.scheduled:
+                if request.finished and not request.finish_announced:
+                    request.announce_finish(FinishReason.ABORT)
+                self.scheduler.abort_request(request.request_id)
+
+    def drain(self) -> None:
+        """Finish the step that is on its way, if any: afterwards every token that has been
+        drawn is in its request and no work is queued."""
+        flight, self._flight = self._flight, None
+        if flight is not None:
+            self._finish_flight(flight)
+
+    def _finish_flight(self, flight: _Flight, queued_behind: Optional[_Flight] = None) -> None:
+        """Tokens of ``flight`` to their requests.  A step that has not been booked yet is only
+        booked once its status word has come back clean (a refused step can then be run again);
+        if it has been booked, and maybe another step queued behind it, the requests of both are
+        given up before the error goes to the caller."""
+        try:
+            self._await(flight)
+        except Exception:
+            if flight.committed:
+                self._abandon(flight, queued_behind)
+            raise
+        if not flight.committed:
+            self._commit(flight)
+        self._deliver(flight)
+
+    @torch.no_grad()
+    def step(self) -> None:
+        """One step, start to end: when it returns, its tokens are in their requests."""
+        step_start = time.perf_counter()
+        self.drain()
+        flight = self._launch()
+        if flight is None:
+            return
+        self._finish_flight(flight)
         self.num_steps += 1
         self.stats["step_ms"].append((time.perf_counter() - step_start) * 1000)
+
+    @torch.no_grad()
+    def step_pipelined(self) -> None:
+        """Queue the next step, then hand out the tokens of the one before it.  ``has_work``
+        stays true while a step is on its way; ``drain`` ends the pipeline."""
+        step_start = time.perf_counter()
+        previous, self._flight = self._flight, None
+        if previous is not None:
+            self._commit(previous)
+            # A request with penalties keeps its tokens in the sampler's history, which is
+            # written from the host's list when the request (re)takes a slot: such requests
+            # get their tokens before anything is scheduled.
+            if any(r.sampling_params.has_penalties for r in previous.sampled):
+                self._finish_flight(previous)
+                previous = None
+        flight = self._launch()
+        if previous is not None:
+            self._finish_flight(previous, queued_behind=flight)
+        self._flight = flight
+        if flight is not None:
+            self.num_steps += 1
+            self.stats["step_ms"].append((time.perf_counter() - step_start) * 1000)
 
     @torch.no_grad()
     def generate(self, requests: Sequence[Request], max_steps: Optional[int] = None) -> List[Request]:
         for request in requests:
             self.add_request(request)
+        one_step = self.step_pipelined if self.config.pipeline_decode else self.step
         steps = 0
         while self.has_work():
-            self.step()
+            one_step()
             steps += 1
             if max_steps is not None and steps >= max_steps:
                 break
+        self.drain()
         return list(requests)
 
     def snapshot(self) -> Dict[str, float]:

@@ -80,6 +80,10 @@ class Request:
         self.first_token_time: Optional[float] = None
         self.finish_time: Optional[float] = None
         self._listeners: List[Listener] = []
+        # Generated tokens at the end of the list that are only known on the device so far (the
+        # list holds a stand-in for each), and whether the end has been told to the listeners.
+        self._pending = 0
+        self._finish_told = False
 
     # ------------------------------------------------------------------ tokens
     @property
@@ -93,7 +97,9 @@ class Request:
 
     @property
     def output_token_ids(self) -> List[int]:
-        return self._tokens[self._prompt_len :]
+        """The generated tokens the host knows (a token still on its way from the device is
+        counted by ``num_output_tokens`` but not shown here)."""
+        return self._tokens[self._prompt_len : len(self._tokens) - self._pending]
 
     @property
     def num_prompt_tokens(self) -> int:
@@ -157,6 +163,28 @@ class Request:
             self.first_token_time = time.time()
         self._tell("token", token_id)
 
+    def append_pending(self, stand_in: int) -> int:
+        """A token has been drawn on the device and is not known here yet: ``stand_in`` (a
+        negative id that the embedding resolves on the device) takes its place.  Returns the
+        place, for ``resolve_pending``.  Nobody is told."""
+        self._tokens.append(int(stand_in))
+        self._pending += 1
+        return len(self._tokens) - 1
+
+    def resolve_pending(self, place: int, token_id: int) -> None:
+        """The token at ``place`` has arrived: it replaces its stand-in and is announced."""
+        self._tokens[place] = int(token_id)
+        self._pending -= 1
+        if self.first_token_time is None:
+            self.first_token_time = time.time()
+        self._tell("token", token_id)
+
+    def drop_pending(self, place: int) -> None:
+        """The token at ``place`` is not wanted any more (the request ended before it came)."""
+        if place == len(self._tokens) - 1 and self._pending > 0:
+            self._tokens.pop()
+            self._pending -= 1
+
     def should_stop(self, token_id: int, eos_token_ids: FrozenSet[int]) -> Optional[FinishReason]:
         """Whether the token just appended ends the request, and why."""
         params = self.sampling_params
@@ -165,14 +193,31 @@ class Request:
             return FinishReason.STOP
         return FinishReason.LENGTH if self.num_output_tokens >= params.max_tokens else None
 
-    def finish(self, reason: FinishReason) -> None:
-        """Ends the request once; a second call changes nothing."""
+    def finish(self, reason: FinishReason, announce: bool = True) -> None:
+        """Ends the request once; a second call changes nothing.  With ``announce=False`` the
+        listeners hear of it only at ``announce_finish`` (the engine ends a request that has
+        reached its length before the last token has come back from the device)."""
         if self.finished:
             return
         self.finish_reason = reason
         self.status = _STATUS_AFTER[reason]
         self.finish_time = time.time()
-        self._tell("finish", None)
+        if announce:
+            self.announce_finish()
+
+    @property
+    def finish_announced(self) -> bool:
+        return self._finish_told
+
+    def announce_finish(self, reason: Optional[FinishReason] = None) -> None:
+        """Tells the listeners of the end, once.  ``reason`` replaces the recorded one (a last
+        token that is a stop token ends the request by STOP, not by LENGTH)."""
+        if reason is not None and self.finish_reason is not FinishReason.ABORT:
+            self.finish_reason = reason
+            self.status = _STATUS_AFTER[reason]
+        if not self._finish_told:
+            self._finish_told = True
+            self._tell("finish", None)
 
     @property
     def time_to_first_token(self) -> Optional[float]:

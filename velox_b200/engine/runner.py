@@ -109,6 +109,9 @@ class StepContext:
     # input there), and whether the mixer has written it.
     residual_mirror: Optional[torch.Tensor] = None
     residual_mirror_written: bool = False
+    # int32 on the device, or None: the tokens the sampler drew in the step before, one per row.
+    # A token id of -1 - r in this step's ids stands for row r of it (looked up by the embedding).
+    fed_tokens: Optional[torch.Tensor] = None
     # Host copies, for parts that lay out work of their own.
     q_lens_host: List[int] = field(default_factory=list)
     kv_lens_host: List[int] = field(default_factory=list)
@@ -232,6 +235,9 @@ class ModelRunner:
 
         self.workspace = Workspace(self.max_tokens, max_logit_rows or max_num_seqs, self.device)
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+        # Set by whoever owns the sampler, before any graph is captured: its device tokens, which
+        # a step's ids may name instead of a token (StepContext.fed_tokens).
+        self.fed_tokens: Optional[torch.Tensor] = None
         self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
 
         # One cache per schedule entry that owns one; entries that read another's share it.
@@ -590,6 +596,7 @@ class ModelRunner:
             status=self.status,
             workspace=self.workspace,
             plans=plans,
+            fed_tokens=self.fed_tokens,
             q_lens_host=[int(n) for n in q_len_arr],
             kv_lens_host=[int(n) for n in kv_len_arr],
         )

@@ -41,7 +41,7 @@ def core():
     global _core
     if _core is None:
         lib = build.load_core()
-        lib.vx_embed.argtypes = [_ptr, _c_int, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr, _ptr]
+        lib.vx_embed.argtypes = [_ptr, _c_int, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr, _ptr, _c_int, _ptr]
         lib.vx_add_rmsnorm.argtypes = [
             _ptr, _ptr, _ptr, _c_f, _ptr, _c_int, _ptr, _c_int, _c_int, _c_int, _ptr,
         ]
@@ -187,9 +187,15 @@ def selftest_bounded_wait(status: torch.Tensor, limit_cycles: int) -> int:
     return int(returned.item())
 
 
-def embed(table: torch.Tensor, ids: torch.Tensor, resid: torch.Tensor, status: torch.Tensor) -> None:
-    """resid[t, :] = float32(table[ids[t], :]); ids outside the table set a status bit."""
+def embed(table: torch.Tensor, ids: torch.Tensor, resid: torch.Tensor, status: torch.Tensor,
+          fed: Optional[torch.Tensor] = None) -> None:
+    """resid[t, :] = float32(table[ids[t], :]); ids outside the table set a status bit.
+
+    With ``fed`` (int32 on the device: the tokens the sampler drew in the step before, one per
+    row) an id of ``-1 - r`` stands for ``fed[r]`` and is looked up on the device."""
     _need(ids, torch.int32, "ids")
+    if fed is not None:
+        _need(fed, torch.int32, "fed")
     _need(resid, torch.float32, "resid")
     _need(table, table.dtype, "table")
     vocab, hidden = table.shape
@@ -198,7 +204,7 @@ def embed(table: torch.Tensor, ids: torch.Tensor, resid: torch.Tensor, status: t
         raise ValueError(f"resid {tuple(resid.shape)} cannot hold {n} rows of width {hidden}")
     _check(
         core().vx_embed(_p(table), _code(table.dtype), _p(ids), _p(resid), n, hidden, vocab,
-                        _p(status), _stream()),
+                        _p(status), _p(fed), 0 if fed is None else fed.numel(), _stream()),
         "embed",
     )
 

@@ -21,7 +21,8 @@ class TokenEmbedding(Part):
         self.table = self.expect("weight", (self.vocab_size, self.hidden_size))
 
     def forward(self, ids, resid, ctx) -> None:
-        kernels.embed(self.table, ids[: ctx.num_tokens], resid, ctx.status)
+        # ctx.fed_tokens: the sampler's tokens of the step before, for ids that name one of them.
+        kernels.embed(self.table, ids[: ctx.num_tokens], resid, ctx.status, getattr(ctx, "fed_tokens", None))
 
 
 @register_part("lm_head", "linear_head")

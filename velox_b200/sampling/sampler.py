@@ -30,6 +30,31 @@ def _derive_seed(base: int, request_id: str) -> int:
     return int.from_bytes(digest[:8], "little")
 
 
+class TokenReadback:
+    """Sampled tokens from the device to the host without stopping the host: ``begin`` queues
+    the copy into pinned memory behind the sampling kernel and returns a ticket, ``end`` waits
+    for that copy alone and returns the values.  Two buffers, used in turn: two steps' tokens
+    can be on their way at a time."""
+
+    def __init__(self, capacity: int) -> None:
+        self._host = [torch.zeros(capacity, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._events = [torch.cuda.Event(), torch.cuda.Event()]
+        self._flip = 0
+
+    def begin(self, tokens: torch.Tensor):
+        index = self._flip
+        self._flip ^= 1
+        count = int(tokens.numel())
+        self._host[index][:count].copy_(tokens, non_blocking=True)
+        self._events[index].record()
+        return index, count
+
+    def end(self, ticket) -> List[int]:
+        index, count = ticket
+        self._events[index].synchronize()
+        return self._host[index][:count].tolist()
+
+
 class Sampler:
     def __init__(
         self,
