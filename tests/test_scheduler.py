@@ -525,7 +525,7 @@ def test_engine_loop_with_a_fake_model(pipeline):
     heard = []
 
     class FakeRunner:
-        def step(self, chunks):
+        def step(self, chunks, capture=True):
             seen.append([(c.seq.seq_id, list(c.tokens), tuple(c.want)) for c in chunks])
             return [c.seq.seq_id for c in chunks if c.want]
 
@@ -573,7 +573,7 @@ def test_pipelined_steps_deliver_one_call_later_and_drain():
     scheduler, cache = make(num_pages=40, page_size=4, max_num_seqs=3, budget=16, chunk=8, max_model_len=64)
 
     class FakeRunner:
-        def step(self, chunks):
+        def step(self, chunks, capture=True):
             return [c.seq.seq_id for c in chunks if c.want]
 
     class FakeSampler:
@@ -617,7 +617,7 @@ def test_pipelined_requests_with_penalties_get_their_tokens_first():
     fed = []
 
     class FakeRunner:
-        def step(self, chunks):
+        def step(self, chunks, capture=True):
             fed.extend(t for c in chunks for t in c.tokens)
             return [c.seq.seq_id for c in chunks if c.want]
 
@@ -638,7 +638,7 @@ def test_pipelined_preemption_refeeds_the_stand_in():
     seen = []
 
     class FakeRunner:
-        def step(self, chunks):
+        def step(self, chunks, capture=True):
             seen.append([(c.seq.seq_id, list(c.tokens)) for c in chunks])
             return [c.seq.seq_id for c in chunks if c.want]
 
@@ -681,7 +681,7 @@ def test_engine_step_raises_when_the_status_word_comes_back_set():
         word = 0
         cleared = 0
 
-        def step(self, chunks):
+        def step(self, chunks, capture=True):
             return [c.seq.seq_id for c in chunks if c.want]
 
         def raise_for_status(self, word):
@@ -718,7 +718,7 @@ def test_pipelined_status_error_gives_up_the_steps_on_their_way():
         status = "the-device-word"
         word = 0
 
-        def step(self, chunks):
+        def step(self, chunks, capture=True):
             return [c.seq.seq_id for c in chunks if c.want]
 
         def raise_for_status(self, word):

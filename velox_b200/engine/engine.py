@@ -229,9 +229,10 @@ class Engine:
         return self.scheduler.has_work() or self._flight is not None
 
     # ------------------------------------------------------------------ one step, in three parts
-    def _launch(self) -> Optional[_Flight]:
+    def _launch(self, ahead: bool = False) -> Optional[_Flight]:
         """Schedule a step and queue it on the device: forward, sampling, and the copy of the
-        sampled tokens to pinned memory.  Nothing here waits for the device."""
+        sampled tokens to pinned memory.  Nothing here waits for the device.  ``ahead``: the
+        step is queued behind one that is still running."""
         step_start = time.perf_counter()
         scheduled = self.scheduler.schedule()
         t_sched = time.perf_counter()
@@ -258,7 +259,7 @@ class Engine:
         if self._timing:
             flight.events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
             flight.events[0].record()
-        logits = self.runner.step(chunks)
+        logits = self.runner.step(chunks, capture=False) if ahead else self.runner.step(chunks)
         t_prepare = time.perf_counter()
         self.stats["prepare_ms"].append((t_prepare - t_sched) * 1000)
         if sampled:
@@ -394,7 +395,7 @@ class Engine:
             if any(r.sampling_params.has_penalties for r in previous.sampled):
                 self._finish_flight(previous)
                 previous = None
-        flight = self._launch()
+        flight = self._launch(ahead=True)
         if previous is not None:
             self._finish_flight(previous, queued_behind=flight)
         self._flight = flight

@@ -321,9 +321,14 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ the step
     @torch.no_grad()
-    def step(self, chunks: Sequence[StepChunk]) -> Optional[torch.Tensor]:
+    def step(self, chunks: Sequence[StepChunk], capture: bool = True) -> Optional[torch.Tensor]:
         """Run one batch.  Returns float32 logits [number of wanted places, vocab] in the order
-        of the chunks and of their ``want`` lists, or None if nothing is wanted."""
+        of the chunks and of their ``want`` lists, or None if nothing is wanted.
+
+        ``capture=False`` keeps steps with prompt portions out of the captured-graph route (the
+        graphs of single-token steps exist since warm-up and are used either way): a caller that
+        queues steps ahead of the device has its launches hidden already, and a capture would
+        only make the device wait for the host."""
         if not chunks:
             return None
         if self._graph_eligible(chunks):
@@ -331,7 +336,7 @@ class ModelRunner:
             if logits is not None:
                 self.num_steps += 1
                 return logits
-        if self._mixed_graphs_on:
+        if self._mixed_graphs_on and capture:
             logits = self._mixed_step(chunks)
             self.num_steps += 1
             return logits
