@@ -807,6 +807,10 @@ static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mw2, const CUte
     smem += ring == batches ? (size_t)g.kb_per_split * S::B_BYTES : (size_t)ring * batch_bytes;
   } else {
     launched.x_slots = S::NORM_BATCH;
+    // Nothing is exchanged through shared memory without a cluster, a SwiGLU epilogue or the
+    // norm: the launch leaves the receive area out, and with token tiles of 64 two CTAs then
+    // fit on an SM, one loading while the other stores (the LM head at 64 rows: 1,187 CTAs).
+    if (g.splits <= 1 && g.mode != 3) smem -= S::RECV_BYTES;
   }
   if (smem > (size_t)dynamic_limit) return -2;
   cudaLaunchConfig_t config = {};
