@@ -1,5 +1,5 @@
-"""The layer sizes that are benchmarked and served, composed: Qwen2.5-1.5B, 7B and 14B widths,
-head counts, inner widths and vocabularies with two layers and random weights, replayed through
+"""The layer sizes that are benchmarked and served, composed: Qwen2.5-0.5B, 1.5B, 3B, 7B and 14B
+widths, head counts, inner widths and vocabularies with two layers and random weights, replayed through
 the engine with the work laid out as the runner itself chooses (no planner overrides) and
 compared with the plain implementation in float64 on the same device.
 
@@ -27,7 +27,9 @@ TAIL = 32
 F32_TOLERANCE = 1e-4
 
 # name -> page size of the cache (the reference's default and this engine's)
-SIZES = {"1.5b": 64, "7b": 16, "14b": 64}
+SIZES = {"0.5b": 16, "1.5b": 64, "3b": 64, "7b": 16, "14b": 64}
+# 0.5B has heads of 64 dims, seven to a KV head (kernels of another head size, a group that does
+# not fill a tile of eight); 3B has eight to a KV head and a width of 2,048.
 MIXED_LENGTHS = (2300, 700, 150, 333)
 
 
@@ -141,8 +143,9 @@ def test_long_prompt_every_way_of_cutting(sized, dtype, monkeypatch):
         assert replayer.runner._graphs and not replayer.runner._graphs_broken
         assert fused_answers, "no small step reached the one-kernel feed-forward"
         # A step's tile of 16 or 32 tokens needs (1 + width / 128) x tile columns of tensor
-        # memory out of 512: all small steps at 1,536, steps of up to 16 tokens at 3,584, none at
-        # 5,120, where the step must take the two-kernel route (and still match, above).
+        # memory out of 512: all small steps at 896 and 1,536, steps of up to 16 tokens at 2,048
+        # and 3,584, none at 5,120, where the step must take the two-kernel route (and still
+        # match, above).
         width = cfg["hidden_size"]
         for rows_of_step, taken in fused_answers:
             tile = 16 if rows_of_step <= 16 else 32
