@@ -795,3 +795,18 @@ def test_benchmark_command_line_options():
     assert [len(p) for p in build_prompts("short", 5, 50, 30, 1, fixed_len=77)] == [30] * 5  # cut to the limit
     with pytest.raises(SystemExit):
         parse_args(["--model-size", "7b", "--model", "x"])
+
+
+def test_roofline_command_counts_a_layers_bytes():
+    """The bytes a decode step must read of one layer: its five matrices once in bfloat16, and
+    keys and values of every live request."""
+    from velox_b200.cli import roofline
+    from velox_b200.config.presets import model_size
+
+    weights, cached = roofline.layer_bytes(model_size("1.5b"), batch=8, context=4096)
+    assert weights == 2 * (1536 * 2048 + 1536 * 1536 + 3 * 1536 * 8960)
+    assert cached == 8 * 4096 * 2 * 128 * 2 * 2
+    weights, cached = roofline.layer_bytes(model_size("0.5b"), batch=1, context=10)
+    assert weights == 2 * (896 * (14 + 4) * 64 + 896 * 896 + 3 * 896 * 4864) and cached == 10 * 2 * 64 * 4
+    args = roofline.parse_args(["--model-size", "7b", "--batch", "1,8", "--context", "512"])
+    assert (args.model_size, args.batch, args.context, args.layers, args.block_size) == ("7b", "1,8", "512", "2,6", 16)
