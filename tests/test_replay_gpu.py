@@ -322,9 +322,10 @@ def test_padded_step_staging_equals_prepare(models, case):
             assert cache.append_slots(live[name], 1)
             chunks.append(StepChunk(live[name], [int(rng.integers(0, vocab))], (0,)))
         bucket = runner._bucket(len(chunks))
-        entry = runner._graphs.get(bucket)
+        reach = runner._reaches[-1]
+        entry = runner._graphs.get((bucket, reach))
         if entry is None or entry[2] != (runner.workspace.generation, runner._meta_generation):
-            entry = runner._graphs[bucket] = runner._capture(bucket)
+            entry = runner._graphs[(bucket, reach)] = runner._capture(bucket, reach)
         where, plan_where, size = entry[3]
         # The arrays of the step; between them lie a few ints of alignment that nobody writes.
         used = torch.zeros(size, dtype=torch.bool, device="cuda")
@@ -347,6 +348,54 @@ def test_padded_step_staging_equals_prepare(models, case):
         for name in names:
             cache.advance(live[name], 1)
     assert compared == 150
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_layouts_by_reach(models, dtype):
+    """Captured single-token steps come in two layouts: one without splits through memory for
+    steps whose sequences are all short, one cut for the longest sequence the engine allows.
+    With the thresholds moved down to tiny sizes both are captured and used, alone and together,
+    and the logits are the plain ones either way."""
+    folder, cfg, page, prompts, want = models["tiny_d"]
+    overrides = dict(short_reach=128, narrow_global_split_keys=32, narrow_global_fine_keys=16)
+    replayer = make_replayer(folder, dtype, max_tokens=1024, page=page, plan_overrides=overrides)
+    runner = replayer.runner
+    assert runner._reaches == [128, 1024]
+    long_index, short_index, tail = 3, 2, 12          # 300 and 65 tokens
+    got = {long_index: [], short_index: []}
+    step = 0
+
+    def feed(entries, end=()):
+        nonlocal step
+        record = {"step": step, "end": list(end), "entries": [
+            {"id": f"r{i}", "tokens": prompts[i][a:b], "want": list(range(b - a)) if b - a == 1 else []}
+            for i, a, b in entries]}
+        out = replayer.run_step(record)
+        step += 1
+        row = 0
+        for i, a, b in entries:
+            if b - a == 1:
+                got[i].append((a, out[row]))
+                row += 1
+
+    L, S = len(prompts[long_index]), len(prompts[short_index])
+    feed([(long_index, 0, L - tail), (short_index, 0, S - tail)])
+    for k in range(tail // 2):                        # both: the long layout, two sequences
+        feed([(long_index, L - tail + k, L - tail + k + 1), (short_index, S - tail + k, S - tail + k + 1)])
+    for k in range(tail // 2, tail):                  # each alone: long and short layout, one sequence
+        feed([(long_index, L - tail + k, L - tail + k + 1)])
+        feed([(short_index, S - tail + k, S - tail + k + 1)])
+    for index in (long_index, short_index):
+        places = [a for a, _ in got[index]]
+        assert places == list(range(len(prompts[index]) - tail, len(prompts[index])))
+        check(np.stack([row for _, row in got[index]]), want[index][places], dtype, f"tiny_d {dtype} request {index}")
+    assert not runner._graphs_broken
+    if dtype == "bfloat16":  # float32 steps are not captured
+        assert {key for key in runner._graphs} >= {(1, 128), (1, 1024), (2, 1024)}
+        # the long layout splits through memory, the short one does not
+        opt = runner._plan_options(runner._signatures[0][1])
+        assert runner._padded_splits(1, opt, 1024)[0] > 1 and runner._padded_splits(1, opt, 128)[0] == 1
+    runner.check_status()
 
 
 @pytest.mark.parametrize("case", ["tiny_d", "tiny_w"])

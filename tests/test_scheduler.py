@@ -810,3 +810,19 @@ def test_roofline_command_counts_a_layers_bytes():
     assert weights == 2 * (896 * (14 + 4) * 64 + 896 * 896 + 3 * 896 * 4864) and cached == 10 * 2 * 64 * 4
     args = roofline.parse_args(["--model-size", "7b", "--batch", "1,8", "--context", "512"])
     assert (args.model_size, args.batch, args.context, args.layers, args.block_size) == ("7b", "1,8", "512", "2,6", 16)
+
+
+def test_splits_through_memory_start_coarse_and_go_fine():
+    import numpy as np
+
+    from velox_b200.ops import attention_plan as ap
+
+    opt = ap.PlanOptions(num_kv_heads=2, group=6, window=None, use_f32=False)
+    assert (opt.narrow_global_split_keys, opt.narrow_global_fine_keys) == (1024, 512)
+    # a cluster of eight: no split below 16,384 keys, then one per 4,096
+    assert [ap.splits_through_memory(n, 8, opt) for n in (100, 8192, 16383, 16384, 32768)] == [1, 1, 1, 4, 8]
+    assert ap.splits_through_memory(np.array([100, 16384, 40000]), 8, opt).tolist() == [1, 4, 9]
+    assert ap.splits_through_memory(4096, 2, opt) == 4 and ap.splits_through_memory(4095, 2, opt) == 1
+    # a finer start than the fine size: the start decides both
+    tight = ap.PlanOptions(num_kv_heads=2, group=6, window=None, use_f32=False, narrow_global_split_keys=256)
+    assert ap.splits_through_memory(4096, 8, tight) == 2 and ap.splits_through_memory(4095, 8, tight) == 1

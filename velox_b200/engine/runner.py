@@ -230,6 +230,9 @@ class ModelRunner:
         self.max_num_seqs = max_num_seqs
         self.max_tokens = max(max_num_batched_tokens, max_num_seqs)
         self.plan_overrides = dict(plan_overrides or {})
+        # Not a planner option: up to how many keys the layout without splits through memory is
+        # used for padded single-token steps (tests move it down to their sizes).
+        self.short_reach = int(self.plan_overrides.pop("short_reach", self.SHORT_REACH))
         if [g.window for g in cache.groups] != [g.window for g in model.cache_groups]:
             raise ValueError("the cache manager's groups are not the model's cache groups")
 
@@ -270,7 +273,10 @@ class ModelRunner:
         # The float32 path stays eager: it is the checking path, and without the fixed key-range
         # splits of a captured step its results do not depend on how the work was cut.
         self.enable_graphs = enable_graphs and self.dtype != torch.float32
-        self._graphs: Dict[int, tuple] = {}
+        # Captured single-token steps by (bucket of sequences, reach in keys).
+        self._graphs: Dict[Tuple[int, int], tuple] = {}
+        longest = cache.max_model_len
+        self._reaches: List[int] = [longest] if longest <= self.short_reach else [self.short_reach, longest]
         # Captured steps of other shapes, by rounded shape; the shapes used last are kept.
         self._mixed_graphs: "OrderedDict[tuple, tuple]" = OrderedDict()
         self._mixed_graphs_kept = 64
@@ -283,7 +289,7 @@ class ModelRunner:
         # One memory pool for whatever a capture allocates (a library's workspace): the graphs
         # run one at a time on one stream, so they can share it instead of each keeping its own.
         self._graph_pool = torch.cuda.graph_pool_handle() if self.enable_graphs else None
-        self._padded_stages: Dict[int, "_PaddedStage"] = {}
+        self._padded_stages: Dict[Tuple[int, int], "_PaddedStage"] = {}
         self._graphs_broken = False
         self._meta_generation = 0
 
@@ -411,7 +417,8 @@ class ModelRunner:
             return 1 << (count - 1).bit_length()
         return -(-count // granule) * granule
 
-    def prepare(self, chunks: Sequence[StepChunk], pad_to: Optional[int] = None, round_shape: bool = False):
+    def prepare(self, chunks: Sequence[StepChunk], pad_to: Optional[int] = None, round_shape: bool = False,
+                reach: Optional[int] = None):
         """Build the step's device-side description: (context, token ids, logit rows, their count).
 
         ``pad_to`` (single-token steps only) pads the batch to that many sequences with rows
@@ -515,7 +522,7 @@ class ModelRunner:
         for group, signature in self._signatures:
             opt = self._plan_options(signature)
             if padded:
-                splits, cluster = self._padded_splits(num_seqs, opt)
+                splits, cluster = self._padded_splits(num_seqs, opt, reach)
                 plan = ap.plan_attention(q_lens, kv_lens, opt, fixed_splits=splits, fixed_cluster=cluster)
                 plan = ap.pad_plan(plan, num_seqs, splits, opt)
             else:
@@ -625,9 +632,22 @@ class ModelRunner:
         options.update(self.plan_overrides)
         return ap.PlanOptions(**options)
 
-    def _padded_splits(self, num_seqs: int, opt: "ap.PlanOptions") -> Tuple[int, int]:
+    # A padded single-token step is laid out for sequences of up to so many keys (its "reach"):
+    # the shortest class has no splits through memory, whose merge costs a layer of a small model
+    # about six microseconds, the other is cut for ``max_model_len``.
+    SHORT_REACH = 8192
+
+    def _reach_of(self, longest: int) -> int:
+        """The smallest reach that holds a sequence of ``longest`` keys."""
+        for reach in self._reaches:
+            if longest <= reach:
+                return reach
+        return self._reaches[-1]
+
+    def _padded_splits(self, num_seqs: int, opt: "ap.PlanOptions", reach: Optional[int] = None) -> Tuple[int, int]:
         """(splits through memory, cluster size) of a padded single-token step: enough CTAs to
-        fill the GPU at this batch size, the same for every sequence whatever its length."""
+        fill the GPU at this batch size, the same for every sequence of up to ``reach`` keys
+        (``max_model_len`` if not given) whatever its length."""
         tiles = -(-opt.group // 16)
         per_split = max(1, num_seqs * opt.num_kv_heads * tiles)
         narrow = not opt.use_f32 and opt.group <= opt.narrow_max_rows
@@ -640,10 +660,10 @@ class ModelRunner:
         cluster = ap.choose_cluster(opt, per_split, wanted)
         if cluster == 1:
             return max(1, min(32, wanted)), 1
-        # The layout is the same for every length, so the longest sequence decides whether
-        # splitting through memory as well is worth its slower merge.
-        longest = self.cache.max_model_len
-        return max(1, min(32, wanted // cluster, longest // (cluster * opt.narrow_global_split_keys))), cluster
+        # The layout is the same for every length, so the longest sequence it is made for decides
+        # whether splitting through memory as well is worth its slower merge.
+        longest = self.cache.max_model_len if reach is None else min(reach, self.cache.max_model_len)
+        return max(1, min(32, wanted // cluster, ap.splits_through_memory(longest, cluster, opt))), cluster
 
     def _graph_eligible(self, chunks: Sequence[StepChunk]) -> bool:
         if not self.enable_graphs or self._graphs_broken:
@@ -662,12 +682,13 @@ class ModelRunner:
         """A step of single tokens, padded to a bucket size and replayed as one CUDA graph
         (the reference captures its decode forward per bucket too, engine/model_runner.py:330-393)."""
         bucket = self._bucket(len(chunks))
-        entry = self._graphs.get(bucket)
+        reach = self._reach_of(max(c.seq.num_computed for c in chunks) + 1)
+        entry = self._graphs.get((bucket, reach))
         if entry is not None and entry[2] != (self.workspace.generation, self._meta_generation):
             entry = None
         if entry is None:
             try:
-                entry = self._capture(bucket)
+                entry = self._capture(bucket, reach)
             except Exception as exc:  # a part that cannot be captured: run eagerly from now on
                 import logging
 
@@ -675,12 +696,12 @@ class ModelRunner:
                 self._graphs_broken = True
                 torch.cuda.synchronize(self.device)
                 return None
-            self._graphs[bucket] = entry
-        if not self._fill_padded(entry, bucket, chunks):
-            self.prepare(chunks, pad_to=bucket)
+            self._graphs[(bucket, reach)] = entry
+        if not self._fill_padded(entry, bucket, chunks, reach):
+            self.prepare(chunks, pad_to=bucket, reach=reach)
         if entry[2] != (self.workspace.generation, self._meta_generation):
             # A buffer grew while the step was laid out: the graph points at old memory.
-            self._graphs.pop(bucket, None)
+            self._graphs.pop((bucket, reach), None)
             return None
         graph, logits = entry[0], entry[1]
         graph.replay()
@@ -689,7 +710,7 @@ class ModelRunner:
 
     def capture_decode_graphs(self) -> int:
         """Capture the graph of every decode bucket that has none yet (1, 2, 4, ... up to the most
-        requests), smallest first; returns how many it captured.  Nothing happens where steps
+        requests, each for every reach), smallest first; returns how many it captured.  Nothing happens where steps
         are not replayed as graphs.  A later step that makes a work buffer grow still recaptures
         its bucket; after a warm-up that has run a full prefill portion none does."""
         if not self.enable_graphs or self._graphs_broken:
@@ -698,10 +719,12 @@ class ModelRunner:
         bucket = 1
         while True:
             bucket = min(bucket, self.max_num_seqs)
-            entry = self._graphs.get(bucket)
-            if entry is None or entry[2] != (self.workspace.generation, self._meta_generation):
+            for reach in self._reaches:
+                entry = self._graphs.get((bucket, reach))
+                if entry is not None and entry[2] == (self.workspace.generation, self._meta_generation):
+                    continue
                 try:
-                    self._graphs[bucket] = self._capture(bucket)
+                    self._graphs[(bucket, reach)] = self._capture(bucket, reach)
                 except Exception as exc:  # the same fallback as at the first use of a bucket
                     import logging
 
@@ -714,7 +737,7 @@ class ModelRunner:
                 return captured
             bucket *= 2
 
-    def _fill_padded(self, entry, bucket: int, chunks: Sequence[StepChunk]) -> bool:
+    def _fill_padded(self, entry, bucket: int, chunks: Sequence[StepChunk], reach: Optional[int] = None) -> bool:
         """Write a padded single-token step straight into the places the captured step reads
         (the layout of a bucket never changes), with arrays instead of per-token loops.  What
         reaches the device is what ``prepare(chunks, pad_to=bucket)`` writes.  Every bucket has
@@ -724,10 +747,11 @@ class ModelRunner:
         where, plan_where, size = entry[3]
         if any(sig[1] > 16 for _, sig in self._signatures):
             return False
-        stage = self._padded_stages.get(bucket)
+        reach = self._reaches[-1] if reach is None else reach
+        stage = self._padded_stages.get((bucket, reach))
         if stage is None or stage.layout is not entry[3]:
             stage = _PaddedStage(entry[3], bucket, len(self.cache.groups), self.max_num_seqs)
-            self._padded_stages[bucket] = stage
+            self._padded_stages[(bucket, reach)] = stage
         P = self.page_size
         n = len(chunks)
         positions = np.fromiter((c.seq.num_computed for c in chunks), np.int64, n)
@@ -763,7 +787,7 @@ class ModelRunner:
             opt, splits = stage.plan_options.get(key, (None, None))
             if opt is None:
                 opt = self._plan_options(key[1])
-                splits, _ = self._padded_splits(bucket, opt)
+                splits, _ = self._padded_splits(bucket, opt, reach)
                 stage.plan_options[key] = (opt, splits)
             items_view, merges_view = views[("items", key)], views.get(("merges", key))
             if splits <= 1 and not fresh:
@@ -789,14 +813,15 @@ class ModelRunner:
             self._meta_generation += 1
         return self._device_meta
 
-    def _capture(self, bucket: int):
+    def _capture(self, bucket: int, reach: Optional[int] = None):
+        reach = self._reaches[-1] if reach is None else reach
         # Twice eagerly on an all-padding batch: buffers get their final size and addresses.
         for _ in range(2):
-            ctx, ids, rows, count = self.prepare([], pad_to=bucket)
+            ctx, ids, rows, count = self.prepare([], pad_to=bucket, reach=reach)
             self.model.forward(ctx, self.layer_caches, ids, rows, count)
         torch.cuda.synchronize(self.device)
         generation = (self.workspace.generation, self._meta_generation)
-        ctx, ids, rows, count = self.prepare([], pad_to=bucket)
+        ctx, ids, rows, count = self.prepare([], pad_to=bucket, reach=reach)
         layout = self._last_layout
         graph = torch.cuda.CUDAGraph()
         launches_before = kernels.launch_count

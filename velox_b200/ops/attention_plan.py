@@ -61,9 +61,23 @@ class PlanOptions:
     # ((cluster size, clusters of that size the device holds at a time), ...): a size is used
     # only if every (tile, KV head) of the step gets its cluster in one wave.  Empty: no limit.
     narrow_cluster_limits: Tuple[Tuple[int, int], ...] = ()
-    # With a cluster, a key range is split through memory as well only if that leaves every
-    # CTA at least this many keys: the merge through memory is the slow one.
+    # With a cluster, a key range is split through memory as well only if two such splits leave
+    # every CTA at least this many keys (the merge through memory is the slow one, about as long
+    # as sixteen key tiles of a CTA); once it is split, the merge is paid and every CTA may get
+    # as few as ``narrow_global_fine_keys``.
     narrow_global_split_keys: int = 1024
+    narrow_global_fine_keys: int = 512
+
+
+def splits_through_memory(span, cluster: int, opt: PlanOptions):
+    """How many clusters a key range of ``span`` keys (a number or an array) may be spread over
+    when each cluster has ``cluster`` CTAs: one, unless two splits leave a CTA
+    ``narrow_global_split_keys`` keys; then as many as leave it ``narrow_global_fine_keys``."""
+    coarse = span // (cluster * max(opt.narrow_global_split_keys, 1))
+    fine = span // (cluster * max(min(opt.narrow_global_fine_keys, opt.narrow_global_split_keys), 1))
+    if isinstance(span, np.ndarray):
+        return np.where(coarse >= 2, fine, 1)
+    return fine if coarse >= 2 else 1
 
 
 def choose_cluster(opt: PlanOptions, pairs: int, wanted: int) -> int:
@@ -163,7 +177,7 @@ def _plan_with_arrays(q_lens: Sequence[int], kv_lens: Sequence[int], opt: PlanOp
     if opt.narrow_max_cluster > 1 and narrow.any():
         cluster = choose_cluster(opt, int(narrow.sum()) * opt.num_kv_heads, int(wanted[narrow].max()))
     if cluster > 1:
-        through_memory = np.minimum(wanted // cluster, span // (cluster * max(opt.narrow_global_split_keys, 1)))
+        through_memory = np.minimum(wanted // cluster, splits_through_memory(span, cluster, opt))
         wanted = np.where(narrow, through_memory, wanted)
     splits = np.maximum(1, np.minimum(wanted, opt.max_splits))
 
@@ -280,7 +294,7 @@ def plan_attention_plain(
         else:
             wanted = wanted_ctas(kind, span)
             if kind == KIND_BF16_NARROW and cluster > 1:
-                wanted = min(wanted // cluster, span // (cluster * max(opt.narrow_global_split_keys, 1)))
+                wanted = min(wanted // cluster, splits_through_memory(span, cluster, opt))
             splits = max(1, min(wanted, opt.max_splits))
         out = per_kind.setdefault(kind, [])
         if splits <= 1:
