@@ -191,25 +191,31 @@ class Engine:
         return engine
 
     def warmup(self) -> None:
-        """One request through the whole loop before the first real step, so that library
-        handles, kernel images and the work buffers at their final sizes exist (the reference
-        warms up and captures its decode graphs at construction too, engine/engine.py:174-211):
-        a prompt as long as a prefill portion, which takes the route of long steps, two decoded
-        tokens, and then the graph of every decode bucket."""
+        """Requests through the whole loop before the first real step, so that library handles,
+        kernel images and the work buffers at their final sizes exist (the reference warms up
+        and captures its decode graphs at construction too, engine/engine.py:174-211): prompts
+        as long as a prefill portion, as many as fill a step (the route of long steps), two
+        decoded tokens each, and then the graph of every decode bucket."""
         limit = self.max_model_len - 2
         if limit < 1:
             return
         portion = min(self.config.max_prefill_chunk_size, self.config.max_num_batched_tokens, limit)
-        request = Request(
-            "__warmup__", [0] * max(1, portion), SamplingParams(temperature=0.0, max_tokens=2, ignore_eos=True)
-        )
-        self.add_request(request)
+        # As many requests as fill a step's token budget: where one request cannot be that long
+        # (a short max_model_len), the step with the most tokens is still one that has been run.
+        count = max(1, min(self.config.max_num_seqs, self.config.max_num_batched_tokens // max(1, portion)))
+        requests = [
+            Request(f"__warmup_{i}__", [0] * max(1, portion), SamplingParams(temperature=0.0, max_tokens=2, ignore_eos=True))
+            for i in range(count)
+        ]
+        for request in requests:
+            self.add_request(request)
         guard = 0
-        while self.has_work() and guard < 16:
+        while self.has_work() and guard < 16 + 2 * count:
             self.step()
             guard += 1
-        self.scheduler.abort_request(request.request_id)
-        self.scheduler.schedule()  # the aborted request's pages and slot go back now
+        for request in requests:
+            self.scheduler.abort_request(request.request_id)
+        self.scheduler.schedule()  # aborted requests' pages and slots go back now
         torch.cuda.synchronize(self.device)
         self.runner.capture_decode_graphs()
         torch.cuda.synchronize(self.device)
@@ -217,6 +223,9 @@ class Engine:
             values.clear()
         self.num_steps = 0
         self.scheduler.num_finished = 0
+        self.scheduler.num_preemptions = 0
+        for how in getattr(self.runner, "mixed_step_counts", {}):
+            self.runner.mixed_step_counts[how] = 0
 
     # ------------------------------------------------------------------ requests
     def add_request(self, request: Request) -> None:
