@@ -1635,6 +1635,19 @@ __device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t a_desc, uint64_
       : "memory");
 }
 
+// The same product with A read from tensor memory: row r of A in lane r, two bf16 to a column.
+__device__ __forceinline__ void tc_mma_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t b_desc, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+      "}\n"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                : "memory");
@@ -1678,6 +1691,50 @@ __device__ __forceinline__ void tc_store32(uint32_t taddr, const float (&v)[32])
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+// Sixteen 32-bit words of this thread's lane into sixteen columns (no wait: see tc_store_wait).
+__device__ __forceinline__ void tc_store16_words(uint32_t taddr, const uint32_t (&w)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]),
+        "r"(w[8]), "r"(w[9]), "r"(w[10]), "r"(w[11]), "r"(w[12]), "r"(w[13]), "r"(w[14]), "r"(w[15])
+      : "memory");
+}
+__device__ __forceinline__ void tc_store_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// The K tile or the V tile (`which` 0 or 1) of keys n0 .. n0 + 63 into `dst`, by tensor-map
+// copies that complete on `bar`: one per (page, panel of 64 dims), the lanes taking them in turn.
+__device__ __forceinline__ void produce_tc_half(const AttnArgs& a, __nv_bfloat16* dst_s, uint32_t bar, int which,
+                                                const int* table, const int* table_s, int first_block,
+                                                int last_block, int n0, int kvh, int lane) {
+  const int box_rows = a.page_size < B_BN ? a.page_size : B_BN;
+  const int pages = B_BN / box_rows;
+  constexpr int PANELS = D / 64 > 0 ? D / 64 : 1;
+  if (lane == 0) mbar_expect_tx(bar, (uint32_t)B_BN * D * 2u);
+  __syncwarp();
+  const CUtensorMap* map = which ? &a.map_v : &a.map_k;
+  for (int op = lane; op < pages * PANELS; op += 32) {
+    const int panel = op % PANELS, pg = op / PANELS;
+    const int r = pg * box_rows;
+    const int n = n0 + r;
+    const int block = n / a.page_size;
+    int page = 0;  // past the sequence: the reserved page
+    if (block <= last_block) {
+      const int local = block - first_block;
+      page = local < NARROW_TABLE_CAP ? table_s[local] : table[block];
+    }
+    const int token = page * a.page_size + (n - block * a.page_size);
+    const uint32_t dst = smem_u32(dst_s + panel * (B_BN * 64) + r * 64);
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(panel * 64), "r"(kvh), "r"(token), "r"(bar)
+        : "memory");
+  }
+}
+
 // 2^x by the special-function unit alone: -inf gives 0, and the arguments here never exceed 8.
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -1687,11 +1744,17 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 // TC_STAGES = 2: two CTAs per SM, for grids of several waves; 4: one CTA per SM with a deeper
 // K/V ring, for grids where an SM gets one CTA anyway and nothing else hides the copies' latency.
-template <int TC_STAGES>
+// P_TMEM: the probabilities go back to tensor memory (two buffers of 32 columns, two bf16 to a
+// column) and the second product reads them there; the K tile of a stage is then free as soon as
+// its scores are made and the V tile as soon as its product is, each with a barrier of its own,
+// so that with two stages both are asked for a tile earlier.  Without it P lies over the K tile
+// in shared memory and a stage is one unit.
+template <int TC_STAGES, bool P_TMEM>
 __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_kernel(const __grid_constant__ AttnArgs a) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   __shared__ int table_s[NARROW_TABLE_CAP];
-  __shared__ __align__(8) uint64_t kv_full[TC_STAGES], kv_empty[TC_STAGES];
+  // kv_*: the K tile's barriers with P_TMEM, the stage's without; v_*: the V tile's (P_TMEM only).
+  __shared__ __align__(8) uint64_t kv_full[TC_STAGES], kv_empty[TC_STAGES], v_full[TC_STAGES], v_empty[TC_STAGES];
   __shared__ __align__(8) uint64_t q_ready, s_ready, s_free, p_ready, pv_done, merge_bar;
   __shared__ uint32_t tmem_slot;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -1733,6 +1796,8 @@ __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_ke
     for (int st = 0; st < TC_STAGES; ++st) {
       mbar_init(smem_u32(&kv_full[st]), 1);
       mbar_init(smem_u32(&kv_empty[st]), 1);
+      mbar_init(smem_u32(&v_full[st]), 1);
+      mbar_init(smem_u32(&v_empty[st]), 1);
     }
     mbar_init(smem_u32(&q_ready), 4);
     mbar_init(smem_u32(&s_ready), 1);
@@ -1752,8 +1817,9 @@ __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_ke
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem_s = tmem_slot;        // S: 64 columns
-  const uint32_t tmem_o = tmem_slot + 64u;  // O: 128 columns
+  const uint32_t tmem_s = tmem_slot;         // S: 64 columns
+  const uint32_t tmem_o = tmem_slot + 64u;   // O: 128 columns
+  const uint32_t tmem_p = tmem_slot + 192u;  // P (P_TMEM): two buffers of 32 columns
 
   // Row state of the softmax threads (valid for warps 0-3).
   const int r = (int)threadIdx.x;  // row of the tile, TMEM lane
@@ -1773,8 +1839,16 @@ __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_ke
       if (round > 0 && alive)
         alive = mbar_wait(smem_u32(&kv_empty[st]), (uint32_t)(round - 1) & 1u, a.status);
       __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(smem_al + TC_Q_BYTES + st * TC_STAGE_BYTES);
-      produce_kv_tile(a, k_s, k_s + B_BN * D, smem_u32(&kv_full[st]), table, table_s, first_block, last_block,
-                      n0, kv_end, kvh, lane);
+      if (P_TMEM) {
+        produce_tc_half(a, k_s, smem_u32(&kv_full[st]), 0, table, table_s, first_block, last_block, n0, kvh, lane);
+        if (round > 0 && alive)
+          alive = mbar_wait(smem_u32(&v_empty[st]), (uint32_t)(round - 1) & 1u, a.status);
+        produce_tc_half(a, k_s + B_BN * D, smem_u32(&v_full[st]), 1, table, table_s, first_block, last_block, n0,
+                        kvh, lane);
+      } else {
+        produce_kv_tile(a, k_s, k_s + B_BN * D, smem_u32(&kv_full[st]), table, table_s, first_block, last_block,
+                        n0, kv_end, kvh, lane);
+      }
     }
   } else if (warp == 5) {
     // --------------------------------------------------------------------------- MMA issuer
@@ -1797,6 +1871,7 @@ __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_ke
           tc_mma(tmem_s, tc_desc(qa, 0, 1024), tc_desc(kb, 0, 1024), idesc_qk, kk > 0 ? 1u : 0u);
         }
         tc_commit(smem_u32(&s_ready));
+        if (P_TMEM) tc_commit(smem_u32(&kv_empty[st]));  // nothing else reads the K tile
         return true;
       };
       if (ok && num_tiles > 0) ok = first_product(0);
@@ -1808,18 +1883,26 @@ __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_ke
         if (!ok) break;
         ok = mbar_wait(smem_u32(&p_ready), (uint32_t)t & 1u, a.status);
         if (!ok) break;
+        if (P_TMEM) {
+          ok = mbar_wait(smem_u32(&v_full[st]), (uint32_t)(t / TC_STAGES) & 1u, a.status);
+          if (!ok) break;
+        }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        // O += P V: four steps of 16 keys.  P lies over the K tile (one panel of [128 x 128 B]);
-        // V is [64 keys x 128 dims]: MN-major B, 16 keys are two groups of eight rows (2 KB),
-        // the second 64 dims are the next panel (8 KB on).
+        // O += P V: four steps of 16 keys.  P lies over the K tile (one panel of [128 x 128 B])
+        // or in tensor memory (eight columns a step); V is [64 keys x 128 dims]: MN-major B, 16
+        // keys are two groups of eight rows (2 KB), the second 64 dims are the next panel (8 KB on).
 #pragma unroll
         for (int ks = 0; ks < B_BN / 16; ++ks) {
           const uint32_t pa = k_addr + ks * 32;
           const uint32_t vb = v_addr + ks * 2048;
-          tc_mma(tmem_o, tc_desc(pa, 0, 1024), tc_desc(vb, B_BN * 128, 1024), idesc_pv,
-                 (t > 0 || ks > 0) ? 1u : 0u);
+          if (P_TMEM)
+            tc_mma_a_tmem(tmem_o, tmem_p + (uint32_t)(t & 1) * 32u + (uint32_t)ks * 8u,
+                          tc_desc(vb, B_BN * 128, 1024), idesc_pv, (t > 0 || ks > 0) ? 1u : 0u);
+          else
+            tc_mma(tmem_o, tc_desc(pa, 0, 1024), tc_desc(vb, B_BN * 128, 1024), idesc_pv,
+                   (t > 0 || ks > 0) ? 1u : 0u);
         }
-        tc_commit(smem_u32(&kv_empty[st]));
+        tc_commit(smem_u32(P_TMEM ? &v_empty[st] : &kv_empty[st]));
         tc_commit(smem_u32(&pv_done));
       }
     }
@@ -1917,23 +2000,43 @@ __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_ke
       }
       const float neg_m = m_ref == -CUDART_INF_F ? 0.f : -m_ref;
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-      unsigned char* p_row = smem_al + TC_Q_BYTES + st * TC_STAGE_BYTES + r * 128;
+      if (P_TMEM) {
+        // This tile's buffer was last read by the product of two tiles ago, which was observed
+        // (through pv_done) before this thread let the tile before go on.
+        const uint32_t p_at = tmem_p + (uint32_t)(t & 1) * 32u + lane_base;
 #pragma unroll
-      for (int c = 0; c < B_BN / 8; ++c) {
-        float p[8];
+        for (int half = 0; half < 2; ++half) {
+          uint32_t words[16];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          p[i] = fast_exp2(fmaf(s[c * 8 + i], a.scale_log2, neg_m));
-          sum4[i & 3] += p[i];
+          for (int i = 0; i < 16; ++i) {
+            const float p0 = fast_exp2(fmaf(s[half * 32 + 2 * i], a.scale_log2, neg_m));
+            const float p1 = fast_exp2(fmaf(s[half * 32 + 2 * i + 1], a.scale_log2, neg_m));
+            sum4[i & 1] += p0;
+            sum4[2 + (i & 1)] += p1;
+            words[i] = pack_bf16(p0, p1);
+          }
+          tc_store16_words(p_at + (uint32_t)half * 16u, words);
         }
-        const uint4 packed = make_uint4(pack_bf16(p[0], p[1]), pack_bf16(p[2], p[3]), pack_bf16(p[4], p[5]),
-                                        pack_bf16(p[6], p[7]));
-        *reinterpret_cast<uint4*>(p_row + ((c ^ (r & 7)) << 4)) = packed;
+        tc_store_wait();
+      } else {
+        unsigned char* p_row = smem_al + TC_Q_BYTES + st * TC_STAGE_BYTES + r * 128;
+#pragma unroll
+        for (int c = 0; c < B_BN / 8; ++c) {
+          float p[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            p[i] = fast_exp2(fmaf(s[c * 8 + i], a.scale_log2, neg_m));
+            sum4[i & 3] += p[i];
+          }
+          const uint4 packed = make_uint4(pack_bf16(p[0], p[1]), pack_bf16(p[2], p[3]), pack_bf16(p[4], p[5]),
+                                          pack_bf16(p[6], p[7]));
+          *reinterpret_cast<uint4*>(p_row + ((c ^ (r & 7)) << 4)) = packed;
+        }
       }
       const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       l += sum;
       if (!observed && !failed) failed = !mbar_wait(smem_u32(&pv_done), (uint32_t)(t - 1) & 1u, a.status);
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      if (!P_TMEM) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&p_ready));
@@ -2092,8 +2195,10 @@ VX_API int vx_attention(int kind, const void* q, void* out, const void* k_cache,
                         int num_kv_heads, int group, int page_size, long long num_pages,
                         int window, float softmax_scale, int cluster, cudaStream_t stream) {
   if (num_items <= 0) return 0;
-  // Only the narrow bf16 family shares an item among the CTAs of a cluster.
-  if (cluster != 1 && (kind != 2 || (cluster != 2 && cluster != 4 && cluster != 8)))
+  // Only the narrow bf16 family shares an item among the CTAs of a cluster; for the
+  // tensor-memory family 2 means "two CTAs on an SM" (see its launch below).
+  if (cluster != 1 && !(kind == 3 && cluster == 2) &&
+      (kind != 2 || (cluster != 2 && cluster != 4 && cluster != 8)))
     return (int)cudaErrorInvalidValue;
   // The float32 family leaves merging to the merge kernel.
   if (kind == 0) split_counters = nullptr;
@@ -2171,14 +2276,21 @@ VX_API int vx_attention(int kind, const void* q, void* out, const void* k_cache,
   } else if (kind == 3) {
     static bool configured = false;
     if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           (int)tc_smem_bytes(2) + 1024);
-      if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(attn_tc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)tc_smem_bytes(4) + 1024);
+      cudaError_t e = cudaSuccess;
+      const void* kernels_of[3] = {(const void*)attn_tc_kernel<2, true>, (const void*)attn_tc_kernel<2, false>,
+                                   (const void*)attn_tc_kernel<4, false>};
+      for (int i = 0; i < 3 && e == cudaSuccess; ++i)
+        e = cudaFuncSetAttribute(kernels_of[i], cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)tc_smem_bytes(i < 2 ? 2 : 4) + 1024);
       if (e != cudaSuccess) return (int)e;
       configured = true;
     }
+    // VELOX_B200_TC_P_IN_SMEM=1 keeps the probabilities in shared memory with two CTAs per SM
+    // too, VELOX_B200_TC_CTAS_PER_SM=1|2 forces the number of CTAs per SM (for A/B runs).
+    static const bool p_tmem = [] {
+      const char* value = getenv("VELOX_B200_TC_P_IN_SMEM");
+      return !(value != nullptr && value[0] == '1');
+    }();
     static int sms = 0;
     if (sms == 0) {
       int device = 0;
@@ -2186,10 +2298,22 @@ VX_API int vx_attention(int kind, const void* q, void* out, const void* k_cache,
           cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0)
         sms = 148;
     }
-    if ((long long)num_items * num_kv_heads <= 2LL * sms)
-      launch_pdl(attn_tc_kernel<4>, dim3(grid), dim3(TC_THREADS), tc_smem_bytes(4) + 1024, stream, a);
+    static const int forced = [] {
+      const char* value = getenv("VELOX_B200_TC_CTAS_PER_SM");
+      return value != nullptr ? atoi(value) : 0;
+    }();
+    // Two CTAs per SM (probabilities in tensor memory, K and V asked for a tile earlier) where
+    // the grid is more than two CTAs per SM anyway, or where the caller says that the items'
+    // key ranges are long (`cluster` = 2): a CTA alone on its SM walks a tile in 0.84 us, two
+    // side by side in 1.46 us each, so two pay where the SM's work, not one CTA's chain, decides.
+    const bool one_per_sm = forced == 1 || (forced != 2 && cluster < 2 &&
+                                            (long long)num_items * num_kv_heads <= 2LL * sms);
+    if (one_per_sm)
+      launch_pdl(attn_tc_kernel<4, false>, dim3(grid), dim3(TC_THREADS), tc_smem_bytes(4) + 1024, stream, a);
+    else if (p_tmem)
+      launch_pdl(attn_tc_kernel<2, true>, dim3(grid), dim3(TC_THREADS), tc_smem_bytes(2) + 1024, stream, a);
     else
-      launch_pdl(attn_tc_kernel<2>, dim3(grid), dim3(TC_THREADS), tc_smem_bytes(2) + 1024, stream, a);
+      launch_pdl(attn_tc_kernel<2, false>, dim3(grid), dim3(TC_THREADS), tc_smem_bytes(2) + 1024, stream, a);
 #endif
   } else {
     return (int)cudaErrorInvalidValue;

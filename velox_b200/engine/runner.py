@@ -58,6 +58,9 @@ class DevicePlan:
     num_merges: int = 0
     merge_rows: int = 16  # the most rows a merge item can have (height of the split tiles)
     cluster: int = 1  # CTAs that share each item of the narrow bf16 kind
+    # 2: the tensor-memory kind's items have long key ranges and outnumber the SMs (its launcher
+    # then puts two CTAs on an SM); 1: the launcher decides by the grid alone.
+    tc_ctas_per_sm: int = 1
     # Zeroed counters for the fused merge of the bfloat16 kernels; None: a merge kernel runs.
     split_counters: Optional[torch.Tensor] = None
     partial_o: Optional[torch.Tensor] = None
@@ -576,6 +579,13 @@ class ModelRunner:
         for key, plan in host_plans.items():
             entry, merge = plan_where[key]
             device_plan = DevicePlan(cluster=plan.cluster)
+            long_items = plan.items.get(ap.KIND_BF16_TC)
+            if long_items is not None and len(long_items):
+                real = long_items[long_items[:, 0] >= 0]
+                if len(real) * key[1][0] > self.num_sms and len(real):
+                    tiles = -(-(real[:, 4] - real[:, 3]).astype(np.int64) // ap.KEY_TILE)
+                    if float(tiles.mean()) >= self.TC_LONG_TILES:
+                        device_plan.tc_ctas_per_sm = 2
             for kind, (offset, shape) in entry.items():
                 count = shape[0]
                 device_plan.launches.append((kind, dev[offset : offset + count * 8].view(count, 8), count))
@@ -631,6 +641,11 @@ class ModelRunner:
             options["narrow_target_ctas"] = self.plan_overrides["target_ctas"]
         options.update(self.plan_overrides)
         return ap.PlanOptions(**options)
+
+    # Key tiles per work item from which the tensor-memory attention runs two CTAs on an SM when
+    # it has more items than SMs (measured: 192 items of 500 tiles 616 us against 774 with one
+    # CTA per SM, 192 items of 48 tiles 84 against 78).
+    TC_LONG_TILES = 96
 
     # A padded single-token step is laid out for sequences of up to so many keys (its "reach"):
     # the shortest class has no splits through memory, whose merge costs a layer of a small model

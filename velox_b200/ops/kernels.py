@@ -631,9 +631,10 @@ def attention(
 
     With ``merge_items`` and ``split_counters`` (int32, zero, one per merge item and KV head)
     the bfloat16 families merge split key ranges themselves: the last split to finish does it.
-    ``cluster`` (1, 2, 4 or 8; narrow bfloat16 family only) CTAs share every item as a
-    thread-block cluster: each takes a run of the item's key tiles and they merge through
-    distributed shared memory.
+    ``cluster`` (1, 2, 4 or 8; narrow bfloat16 family) CTAs share every item as a thread-block
+    cluster: each takes a run of the item's key tiles and they merge through distributed shared
+    memory.  For the tensor-memory family 2 asks for two CTAs on an SM whatever the grid's size
+    (the caller knows that the items' key ranges are long).
     """
     want = torch.float32 if kind == ATTN_F32 else torch.bfloat16
     _need(q, want, "q")

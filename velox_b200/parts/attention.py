@@ -96,7 +96,8 @@ class Attention(Mixer):
                 self.num_kv_heads, self.head_dim, self.window, self.softmax_scale,
                 merge_items=plan.merge_items, split_counters=plan.split_counters,
                 status=ctx.status,
-                cluster=plan.cluster if kind == kernels.ATTN_BF16_NARROW else 1,
+                cluster=(plan.cluster if kind == kernels.ATTN_BF16_NARROW else
+                         getattr(plan, "tc_ctas_per_sm", 1) if kind == kernels.ATTN_BF16_TC else 1),
                 layout_checked=getattr(plan, "checked", False),
             )
         if hasattr(plan, "checked"):
