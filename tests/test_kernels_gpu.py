@@ -224,7 +224,7 @@ def plain_paged_attention(q, k_all, v_all, ctx, scale, window):
 
 def run_attention_case(k, dtype, H, G, D, P, seqs, window=None, seed=0, min_split_keys=256,
                        target_ctas=296, spike=None, fused_merge=True, max_cluster=1, max_splits=64,
-                       tensor_memory=False, ramp=None):
+                       tensor_memory=False, ramp=None, tc_ctas_per_sm=1):
     """seqs: list of (q_len, ctx_len).  Returns (got, want) as float64 [T, H, D]."""
     from velox_b200.ops import attention_plan as ap
 
@@ -291,7 +291,8 @@ def run_attention_case(k, dtype, H, G, D, P, seqs, window=None, seed=0, min_spli
     for kind, items in plan.items.items():
         k.attention(kind, *args, dev(items), len(items), partial_o, partial_lse, H, G, D, window, 1 / math.sqrt(D),
                     merge_items=merge_dev, split_counters=counters,
-                    cluster=plan.cluster if kind == ap.KIND_BF16_NARROW else 1)
+                    cluster=(plan.cluster if kind == ap.KIND_BF16_NARROW else
+                             tc_ctas_per_sm if kind == ap.KIND_BF16_TC else 1))
     if fused:
         torch.cuda.synchronize()
         assert int(counters.abs().sum()) == 0  # the last split of every item put its counter back
@@ -372,14 +373,19 @@ def test_attention_cluster_shares_an_item(k, H, G, D, P, max_cluster, max_splits
         assert err <= _attn_tol(torch.bfloat16) * want.abs().max().item(), (window, err)
 
 
+# One CTA per SM with P in shared memory over the K tile, or two with P in tensor memory.
+TC_FORMS = pytest.mark.parametrize("per_sm", [1, 2], ids=["p_in_shared_memory", "p_in_tensor_memory"])
+
+
+@TC_FORMS
 @pytest.mark.parametrize("H,G", [(12, 2), (4, 4), (7, 1)])
 @pytest.mark.parametrize("window", [None, 100])
-def test_attention_on_tensor_memory(k, H, G, window):
+def test_attention_on_tensor_memory(k, H, G, window, per_sm):
     """Prompt portions of head size 128 on tcgen05 tensor cores with S and O in tensor memory:
     whole prompts, portions with context, a last tile with few rows, page order shuffled."""
     seqs = [(300, 0), (70, 130), (129, 1000), (200, 57), (1, 40), (64, 64)]
     got, want, plan = run_attention_case(k, torch.bfloat16, H, G, 128, 16, seqs, window=window, seed=H + G,
-                                         tensor_memory=True)
+                                         tensor_memory=True, tc_ctas_per_sm=per_sm)
     from velox_b200.ops import attention_plan as ap
 
     assert ap.KIND_BF16_TC in plan.items
@@ -387,22 +393,40 @@ def test_attention_on_tensor_memory(k, H, G, window):
     assert err <= _attn_tol(torch.bfloat16) * want.abs().max().item(), err
 
 
-def test_attention_on_tensor_memory_rescales_when_the_maximum_grows(k):
+@TC_FORMS
+def test_attention_on_tensor_memory_rescales_when_the_maximum_grows(k, per_sm):
     """Scores that grow along the keys by far more than 2^8: the reference maximum of the
     exponentials moves several times and O in tensor memory is rescaled each time."""
     H, G, D, P = 6, 2, 128, 64
     seqs = [(128, 400)]
     got, want, plan = run_attention_case(k, torch.bfloat16, H, G, D, P, seqs, seed=3, tensor_memory=True,
-                                         ramp=0.05)
+                                         ramp=0.05, tc_ctas_per_sm=per_sm)
     err = (got - want).abs().max().item()
     assert err <= _attn_tol(torch.bfloat16) * want.abs().max().item(), err
 
 
-def test_attention_on_tensor_memory_split_key_ranges(k):
+@TC_FORMS
+def test_attention_on_tensor_memory_split_key_ranges(k, per_sm):
     seqs = [(100, 1500), (130, 700)]
     got, want, plan = run_attention_case(k, torch.bfloat16, 12, 2, 128, 16, seqs, seed=9, min_split_keys=64,
-                                         target_ctas=10_000, tensor_memory=True)
+                                         target_ctas=10_000, tensor_memory=True, tc_ctas_per_sm=per_sm)
     assert len(plan.merge_items) > 0
+    err = (got - want).abs().max().item()
+    assert err <= _attn_tol(torch.bfloat16) * want.abs().max().item(), err
+
+
+@TC_FORMS
+@pytest.mark.parametrize("key_index", [0, 63, 64, 1000, 1940])
+def test_attention_on_tensor_memory_finds_one_far_key(k, key_index, per_sm):
+    """One key among 1,950 carries the output of a row of a 200-token portion: its tile's
+    probabilities must reach the second product with the right weight, whichever buffer and
+    stage they pass through."""
+    seqs = [(64, 300), (200, 1800), (130, 40)]
+    got, want, plan = run_attention_case(k, torch.bfloat16, 12, 2, 128, 16, seqs, seed=key_index,
+                                         spike=(1, 150, key_index), tensor_memory=True, tc_ctas_per_sm=per_sm)
+    from velox_b200.ops import attention_plan as ap
+
+    assert ap.KIND_BF16_TC in plan.items
     err = (got - want).abs().max().item()
     assert err <= _attn_tol(torch.bfloat16) * want.abs().max().item(), err
 
