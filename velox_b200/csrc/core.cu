@@ -380,8 +380,11 @@ __global__ void swiglu_vec_kernel(const T* __restrict__ gate_up, T* __restrict__
     float g[N], u[N], r[N];
     gv[j].unpack(g);
     uv[j].unpack(u);
+    // The result is rounded to bfloat16 right away: the fast exponential and division (a few
+    // units in the last place of float32) are far below that; float32 rows take the exact ones.
 #pragma unroll
-    for (int k = 0; k < N; ++k) r[k] = g[k] / (1.0f + expf(-g[k])) * u[k];
+    for (int k = 0; k < N; ++k)
+      r[k] = sizeof(T) == 2 ? __fdividef(g[k], 1.0f + __expf(-g[k])) * u[k] : g[k] / (1.0f + expf(-g[k])) * u[k];
     Vec16<T> o;
     o.pack(r);
     store16(out + t * inter + i, o);
