@@ -826,3 +826,68 @@ def test_splits_through_memory_start_coarse_and_go_fine():
     # a finer start than the fine size: the start decides both
     tight = ap.PlanOptions(num_kv_heads=2, group=6, window=None, use_f32=False, narrow_global_split_keys=256)
     assert ap.splits_through_memory(4096, 8, tight) == 2 and ap.splits_through_memory(4095, 8, tight) == 1
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_pipelined_equals_step_by_step_under_random_traffic(seed):
+    """Requests of random lengths arriving while others run, stop tokens, lengths, a pool that
+    forces preemptions: the pipelined loop hands every request the tokens that one step at a
+    time hands it, tells its listeners the same things in the same order, and gives every page
+    back.  (The stand-in sampler draws a token from the request's name and the token's index, as
+    a seeded request does.)"""
+    import random
+
+    def token_for(name, index):
+        return (hash((name, index, seed)) % 50) + 1  # 1..50; 7 is everybody's stop token
+
+    class FakeRunner:
+        def __init__(self):
+            self.fed = 0
+
+        def step(self, chunks, capture=True):
+            self.fed += sum(len(c.tokens) for c in chunks)
+            return [c.seq.seq_id for c in chunks if c.want]
+
+    class FakeSampler:
+        def sample(self, logits, params, names, draw_indices, slots=None, history_lengths=None, status=None):
+            return FakeTokens([token_for(name, index) for name, index in zip(names, draw_indices)])
+
+    def run(pipeline):
+        rng = random.Random(seed)
+        scheduler, cache = make(num_pages=24, page_size=4, max_num_seqs=4, budget=24, chunk=8, max_model_len=80)
+        engine = fake_engine(scheduler, cache, FakeRunner(), FakeSampler(), pipeline=pipeline)
+        heard = {}
+        arrivals = []
+        for i in range(14):
+            prompt = [rng.randrange(1, 50) for _ in range(rng.randrange(1, 30))]
+            params = SamplingParams(temperature=0.0, max_tokens=rng.randrange(1, 25), stop_token_ids=[7],
+                                    ignore_eos=rng.random() < 0.3)
+            arrivals.append((rng.randrange(0, 40), Request(f"q{i}", prompt, params)))
+        arrivals.sort(key=lambda pair: pair[0])
+        requests = [r for _, r in arrivals]
+        for r in requests:
+            heard[r.request_id] = []
+            r.add_listener(lambda req, kind, token: heard[req.request_id].append((kind, token)))
+        step = engine.step_pipelined if pipeline else engine.step
+        tick, waiting = 0, list(arrivals)
+        while waiting or engine.has_work():
+            while waiting and waiting[0][0] <= tick:
+                engine.add_request(waiting.pop(0)[1])
+            step()
+            tick += 1
+            assert tick < 5000
+        engine.drain()
+        scheduler.schedule()
+        cache.assert_consistent()
+        assert cache.num_free_pages() == cache.num_total_pages and cache.num_free_slots == 4
+        return requests, heard, scheduler.num_preemptions
+
+    want, want_heard, _ = run(False)
+    got, got_heard, preemptions = run(True)
+    for a, b in zip(got, want):
+        assert a.request_id == b.request_id
+        assert a.output_token_ids == b.output_token_ids and a.all_token_ids == b.all_token_ids, a.request_id
+        assert a.finish_reason is b.finish_reason
+        assert got_heard[a.request_id] == want_heard[b.request_id]
+        assert all(t > 0 for t in a.all_token_ids)
+        assert got_heard[a.request_id][-1] == ("finish", None)
