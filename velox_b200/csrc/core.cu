@@ -605,37 +605,44 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __res
   }
 }
 
-// The same with a warp per row, for steps of many rows: a lane keeps its share of the row
-// (chunks lane, lane + 32, ... of four elements) in registers and has all its loads under way
-// at once, the sum of squares goes through shuffles, and no thread waits at a block barrier
-// between its loads and its stores.  (One block per row reached about half of the memory
-// bandwidth at 2,048 rows: three waves of blocks that each load, meet, and store.)
-template <typename T, int MAX_CHUNKS>
+// The same with a few warps per row, for steps of many rows: a lane keeps its share of the row
+// (chunks idx, idx + lanes, ... of four elements) in registers and has all its loads under way
+// at once, the sum of squares goes through shuffles and one exchange between the row's warps,
+// and a block (two rows) meets once between its loads and its stores.  (One block per row reached
+// about half of the memory bandwidth at 2,048 rows: three waves of blocks that each load, meet,
+// and store.)
+template <typename T, int MAX_CHUNKS, int WPR>
 __global__ void __launch_bounds__(256)
 add_rmsnorm_warp_kernel(float* __restrict__ resid, const T* __restrict__ delta, const float* __restrict__ weight,
                         float eps, T* __restrict__ out, const int* __restrict__ rows, int hidden, int write_resid,
                         int num_rows) {
+  // WPR warps share a row (their 32 * WPR lanes take chunks idx, idx + 32 * WPR, ...):
+  // fewer instructions per warp, whose chain is what a launch of one wave takes, and the weights
+  // are asked for together with the row, not after the sum.
+  constexpr int LANES = 32 * WPR;
+  __shared__ float warp_sums[8];
   VX_TRACE_SCOPE(2);
   allow_dependents();
   grid_dependency_wait();
-  const int lane = threadIdx.x & 31;
-  const int o = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (o >= num_rows) return;
-  const int r = rows ? rows[o] : o;
-  const int chunks = hidden >> 2;
+  const int warp = threadIdx.x >> 5;
+  const int idx = threadIdx.x % LANES;
+  const int o = blockIdx.x * (blockDim.x / LANES) + (threadIdx.x / LANES);
+  const bool live = o < num_rows;
+  const int r = live ? (rows ? rows[o] : o) : 0;
+  const int chunks = live ? hidden >> 2 : 0;
   float* x = resid + (size_t)r * hidden;
   const T* d = delta ? delta + (size_t)r * hidden : nullptr;
-  float4 vals[MAX_CHUNKS];
+  float4 vals[MAX_CHUNKS], w[MAX_CHUNKS];
   float ss = 0.f;
 #pragma unroll
   for (int j = 0; j < MAX_CHUNKS; ++j) {
-    const int c = lane + 32 * j;
+    const int c = idx + LANES * j;
     vals[j] = c < chunks ? *reinterpret_cast<const float4*>(x + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
   if (d) {
 #pragma unroll
     for (int j = 0; j < MAX_CHUNKS; ++j) {
-      const int c = lane + 32 * j;
+      const int c = idx + LANES * j;
       if (c < chunks) {
         const float4 e = load4_as_float<T>(d + 4 * c);
         vals[j].x += e.x;
@@ -646,29 +653,42 @@ add_rmsnorm_warp_kernel(float* __restrict__ resid, const T* __restrict__ delta, 
     }
   }
 #pragma unroll
+  for (int j = 0; j < MAX_CHUNKS; ++j) {
+    const int c = idx + LANES * j;
+    w[j] = c < chunks ? __ldg(reinterpret_cast<const float4*>(weight + 4 * c)) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+#pragma unroll
   for (int j = 0; j < MAX_CHUNKS; ++j)
     ss += vals[j].x * vals[j].x + vals[j].y * vals[j].y + vals[j].z * vals[j].z + vals[j].w * vals[j].w;
   ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) warp_sums[warp] = ss;
+  __syncthreads();
+  if (!live) return;
+  // The same terms in the same order in every warp of the row.
+  ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < WPR; ++i) ss += warp_sums[(warp / WPR) * WPR + i];
   const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
   T* y = out + (size_t)o * hidden;
 #pragma unroll
   for (int j = 0; j < MAX_CHUNKS; ++j) {
-    const int c = lane + 32 * j;
+    const int c = idx + LANES * j;
     if (c < chunks) {
       const float4 v = vals[j];
-      const float4 w = __ldg(reinterpret_cast<const float4*>(weight + 4 * c));
       if (write_resid && d) *reinterpret_cast<float4*>(x + 4 * c) = v;
-      store4_from_float<T>(y + 4 * c, make_float4(v.x * inv * w.x, v.y * inv * w.y, v.z * inv * w.z, v.w * inv * w.w));
+      store4_from_float<T>(y + 4 * c, make_float4(v.x * inv * w[j].x, v.y * inv * w[j].y, v.z * inv * w[j].z,
+                                                   v.w * inv * w[j].w));
     }
   }
 }
 
-template <typename T, int MAX_CHUNKS>
+template <typename T, int MAX_CHUNKS, int WPR>
 static void launch_rmsnorm_warp(float* resid, const void* delta, const float* weight, float eps, void* out,
                                 const int* rows, int num_rows, int hidden, int write_resid, cudaStream_t stream) {
-  const int warps = 8;
-  launch_pdl(add_rmsnorm_warp_kernel<T, MAX_CHUNKS>, dim3((num_rows + warps - 1) / warps), dim3(warps * 32), 0, stream,
-             resid, (const T*)delta, weight, eps, (T*)out, rows, hidden, write_resid, num_rows);
+  const int rows_per_block = 8 / WPR;  // eight warps
+  launch_pdl(add_rmsnorm_warp_kernel<T, MAX_CHUNKS, WPR>, dim3((num_rows + rows_per_block - 1) / rows_per_block),
+             dim3(256), 0, stream, resid, (const T*)delta, weight, eps, (T*)out, rows, hidden, write_resid,
+             num_rows);
 }
 
 VX_API int vx_add_rmsnorm(float* resid, const void* delta, const float* weight, float eps,
@@ -677,12 +697,14 @@ VX_API int vx_add_rmsnorm(float* resid, const void* delta, const float* weight, 
   if (num_out_rows <= 0) return 0;
   const bool aligned = (reinterpret_cast<uintptr_t>(resid) & 15) == 0 && (reinterpret_cast<uintptr_t>(weight) & 15) == 0 &&
                        (reinterpret_cast<uintptr_t>(out) & 15) == 0 && (reinterpret_cast<uintptr_t>(delta) & 15) == 0;
-  // Many rows: a warp per row (rows of up to 4,096 elements, whole chunks of four).  Not in
+  // Many rows: a few warps per row (rows of up to 4,096 elements, whole chunks of four).  Not in
   // the float32 path: there a row's sum of squares is added up in the same order whatever the
   // step, so that results do not depend on how the work was cut.
   if (aligned && dtype == VX_DTYPE_BF16 && num_out_rows >= 256 && hidden % 4 == 0 && hidden <= 4096) {
-    if (hidden <= 2048) launch_rmsnorm_warp<__nv_bfloat16, 16>(resid, delta, weight, eps, out, rows, num_out_rows, hidden, write_resid, stream);
-    else launch_rmsnorm_warp<__nv_bfloat16, 32>(resid, delta, weight, eps, out, rows, num_out_rows, hidden, write_resid, stream);
+    // Four warps a row (measured in a prefill of the 1.5B sizes: 9.1 us a launch at 2,048 rows
+    // with one warp a row, 7.9 with two, 6.8 with four, 7.3 with eight; 8.5 -> 3.1 us at 512 rows).
+    if (hidden <= 2048) launch_rmsnorm_warp<__nv_bfloat16, 4, 4>(resid, delta, weight, eps, out, rows, num_out_rows, hidden, write_resid, stream);
+    else launch_rmsnorm_warp<__nv_bfloat16, 8, 4>(resid, delta, weight, eps, out, rows, num_out_rows, hidden, write_resid, stream);
     return (int)cudaGetLastError();
   }
   if (aligned && hidden % 4 == 0 && hidden / 4 <= 1024 * NORM_VEC_CHUNKS) {
