@@ -276,7 +276,7 @@ def run_attention_case(k, dtype, H, G, D, P, seqs, window=None, seed=0, min_spli
     plan = ap.plan_attention(
         q_lens, kv_lens,
         ap.PlanOptions(num_kv_heads=G, group=group, window=window, use_f32=dtype == torch.float32,
-                       min_split_keys=min_split_keys, target_ctas=target_ctas,
+                       min_split_keys=min_split_keys, tc_min_split_keys=min_split_keys, target_ctas=target_ctas,
                        narrow_max_cluster=max_cluster, max_splits=max_splits,
                        narrow_global_split_keys=min_split_keys, wide_on_tensor_memory=tensor_memory),
     )

@@ -441,7 +441,7 @@ def test_planner_with_arrays_equals_the_plain_one():
         opt = ap.PlanOptions(
             num_kv_heads=rng.choice([1, 2, 4]), group=rng.choice([1, 2, 6, 8, 20]), window=rng.choice([None, 8, 100]),
             use_f32=rng.random() < 0.2, target_ctas=rng.choice([8, 64, 296]), min_split_keys=rng.choice([64, 256]),
-            max_splits=rng.choice([1, 4, 64]), narrow_max_rows=rng.choice([16, 64]),
+            max_splits=rng.choice([1, 4, 64]), narrow_max_rows=rng.choice([16, 64]), tc_min_split_keys=rng.choice([64, 1024]),
             narrow_target_ctas=rng.choice([None, 148]), narrow_max_cluster=rng.choice([1, 2, 8]),
             narrow_cluster_limits=rng.choice([(), ((8, 16), (4, 37), (2, 74))]),
             narrow_global_split_keys=rng.choice([256, 1024]), wide_on_tensor_memory=rng.random() < 0.5)
@@ -891,3 +891,24 @@ def test_pipelined_equals_step_by_step_under_random_traffic(seed):
         assert got_heard[a.request_id] == want_heard[b.request_id]
         assert all(t > 0 for t in a.all_token_ids)
         assert got_heard[a.request_id][-1] == ("finish", None)
+
+
+def test_planner_splits_tensor_memory_tiles_only_into_long_ranges():
+    """The 128-row family walks 64 keys in less than a microsecond and merges a split through
+    memory in about ten: a 512-token portion alone in the cache is not split at all, one behind
+    7,680 keys is split into ranges of at least 1,024 keys."""
+    from velox_b200.ops import attention_plan as ap
+
+    opt = ap.PlanOptions(num_kv_heads=2, group=6, window=None, use_f32=False, wide_on_tensor_memory=True,
+                         narrow_max_cluster=8, target_ctas=296)
+    alone = ap.plan_attention([512], [512], opt)
+    assert list(alone.items) == [ap.KIND_BF16_TC] and len(alone.merge_items) == 0 and len(alone.items[ap.KIND_BF16_TC]) == 24
+    behind = ap.plan_attention([512], [8192], opt)
+    items = behind.items[ap.KIND_BF16_TC]
+    assert len(behind.merge_items) == 24 and len(items) > 24
+    spans = items[:, 4] - items[:, 3]
+    assert spans.min() >= 1024 - 64 and len(items) * 2 <= 296 + 48
+    # the 16-row family keeps its own, finer rule
+    narrow = ap.plan_attention([1], [2048], ap.PlanOptions(num_kv_heads=2, group=6, window=None, use_f32=False,
+                                                           target_ctas=296, narrow_max_cluster=1))
+    assert len(narrow.merge_items) == 1 and len(narrow.items[ap.KIND_BF16_NARROW]) == 8

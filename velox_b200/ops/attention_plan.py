@@ -49,6 +49,11 @@ class PlanOptions:
     target_ctas: int = 148 * 2
     # A split never gets fewer keys than this.
     min_split_keys: int = 256
+    # The same for the tensor-memory family, whose CTAs walk 64 keys in 0.84 us while the merge
+    # of a split through memory takes about ten: shorter splits cost more than they save
+    # (a 512-token portion alone in the cache: 22.7 us a layer with splits of 256 keys, 13.5
+    # without any).
+    tc_min_split_keys: int = 1024
     max_splits: int = 64
     # Portions with at most this many rows use the narrow (16-row) bf16 family.
     narrow_max_rows: int = 64
@@ -170,7 +175,8 @@ def _plan_with_arrays(q_lens: Sequence[int], kv_lens: Sequence[int], opt: PlanOp
     target = np.full(num_tiles, opt.target_ctas, np.int64)
     if opt.narrow_target_ctas is not None:
         target[narrow] = opt.narrow_target_ctas
-    per_tile = np.minimum(target // max(base_ctas, 1), span // max(opt.min_split_keys, 1))
+    least = np.where(kind_of == KIND_BF16_TC, max(opt.tc_min_split_keys, opt.min_split_keys, 1), max(opt.min_split_keys, 1))
+    per_tile = np.minimum(target // max(base_ctas, 1), span // least)
     wanted = np.where(base_ctas >= target, 1, np.maximum(1, per_tile))
 
     cluster = 1
@@ -273,7 +279,8 @@ def plan_attention_plain(
             return 1
         # Rounded down: the items should all be resident at once, not spill into a second wave.
         wanted = target // max(base_ctas, 1)
-        return max(1, min(wanted, span // max(opt.min_split_keys, 1)))
+        least = max(opt.tc_min_split_keys, opt.min_split_keys) if kind == KIND_BF16_TC else opt.min_split_keys
+        return max(1, min(wanted, span // max(least, 1)))
 
     # One cluster size for all items of the narrow kind (it is a property of the launch).
     cluster = 1
