@@ -378,13 +378,14 @@ TC_FORMS = pytest.mark.parametrize("per_sm", [1, 2], ids=["p_in_shared_memory", 
 
 
 @TC_FORMS
+@pytest.mark.parametrize("D", [128, 64])
 @pytest.mark.parametrize("H,G", [(12, 2), (4, 4), (7, 1)])
 @pytest.mark.parametrize("window", [None, 100])
-def test_attention_on_tensor_memory(k, H, G, window, per_sm):
-    """Prompt portions of head size 128 on tcgen05 tensor cores with S and O in tensor memory:
-    whole prompts, portions with context, a last tile with few rows, page order shuffled."""
+def test_attention_on_tensor_memory(k, H, G, window, per_sm, D):
+    """Prompt portions of head sizes 128 and 64 on tcgen05 tensor cores with S and O in tensor
+    memory: whole prompts, portions with context, a last tile with few rows, page order shuffled."""
     seqs = [(300, 0), (70, 130), (129, 1000), (200, 57), (1, 40), (64, 64)]
-    got, want, plan = run_attention_case(k, torch.bfloat16, H, G, 128, 16, seqs, window=window, seed=H + G,
+    got, want, plan = run_attention_case(k, torch.bfloat16, H, G, D, 16, seqs, window=window, seed=H + G,
                                          tensor_memory=True, tc_ctas_per_sm=per_sm)
     from velox_b200.ops import attention_plan as ap
 
@@ -394,10 +395,11 @@ def test_attention_on_tensor_memory(k, H, G, window, per_sm):
 
 
 @TC_FORMS
-def test_attention_on_tensor_memory_rescales_when_the_maximum_grows(k, per_sm):
+@pytest.mark.parametrize("D", [128, 64])
+def test_attention_on_tensor_memory_rescales_when_the_maximum_grows(k, per_sm, D):
     """Scores that grow along the keys by far more than 2^8: the reference maximum of the
     exponentials moves several times and O in tensor memory is rescaled each time."""
-    H, G, D, P = 6, 2, 128, 64
+    H, G, P = 6, 2, 64
     seqs = [(128, 400)]
     got, want, plan = run_attention_case(k, torch.bfloat16, H, G, D, P, seqs, seed=3, tensor_memory=True,
                                          ramp=0.05, tc_ctas_per_sm=per_sm)
@@ -406,9 +408,10 @@ def test_attention_on_tensor_memory_rescales_when_the_maximum_grows(k, per_sm):
 
 
 @TC_FORMS
-def test_attention_on_tensor_memory_split_key_ranges(k, per_sm):
+@pytest.mark.parametrize("D", [128, 64])
+def test_attention_on_tensor_memory_split_key_ranges(k, per_sm, D):
     seqs = [(100, 1500), (130, 700)]
-    got, want, plan = run_attention_case(k, torch.bfloat16, 12, 2, 128, 16, seqs, seed=9, min_split_keys=64,
+    got, want, plan = run_attention_case(k, torch.bfloat16, 12, 2, D, 16, seqs, seed=9, min_split_keys=64,
                                          target_ctas=10_000, tensor_memory=True, tc_ctas_per_sm=per_sm)
     assert len(plan.merge_items) > 0
     err = (got - want).abs().max().item()
@@ -416,13 +419,14 @@ def test_attention_on_tensor_memory_split_key_ranges(k, per_sm):
 
 
 @TC_FORMS
+@pytest.mark.parametrize("D", [128, 64])
 @pytest.mark.parametrize("key_index", [0, 63, 64, 1000, 1940])
-def test_attention_on_tensor_memory_finds_one_far_key(k, key_index, per_sm):
+def test_attention_on_tensor_memory_finds_one_far_key(k, key_index, per_sm, D):
     """One key among 1,950 carries the output of a row of a 200-token portion: its tile's
     probabilities must reach the second product with the right weight, whichever buffer and
     stage they pass through."""
     seqs = [(64, 300), (200, 1800), (130, 40)]
-    got, want, plan = run_attention_case(k, torch.bfloat16, 12, 2, 128, 16, seqs, seed=key_index,
+    got, want, plan = run_attention_case(k, torch.bfloat16, 12, 2, D, 16, seqs, seed=key_index,
                                          spike=(1, 150, key_index), tensor_memory=True, tc_ctas_per_sm=per_sm)
     from velox_b200.ops import attention_plan as ap
 

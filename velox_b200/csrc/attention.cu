@@ -1579,9 +1579,10 @@ __global__ void __launch_bounds__(NARROW_THREADS) attn_narrow_kernel(const __gri
 }
 
 
-#if VX_HEAD_DIM == 128
+#if VX_HEAD_DIM == 128 || VX_HEAD_DIM == 64
+#define VX_HAS_TC_ATTENTION 1
 // ---------------------------------------------------------------------------------------------
-// Tensor-memory family (head size 128): prompt portions on the 5th-generation tensor cores.
+// Tensor-memory family (head sizes 128 and 64): prompt portions on the 5th-generation tensor cores.
 // A CTA owns 128 rows (thread r of the four softmax warps owns row r, which is TMEM lane r) and
 // walks the key tiles of 64:
 //   S[128 x 64]   = Q K^T      tcgen05.mma, A = Q (shared, K-major, 128-byte swizzle), B = the
@@ -1589,22 +1590,25 @@ __global__ void __launch_bounds__(NARROW_THREADS) attn_narrow_kernel(const __gri
 //   softmax       each thread reads its row of S from TMEM (no shuffles: the row is in one
 //                 thread), masks, keeps the running maximum and sum, writes P as bf16 into
 //                 shared memory - over the K tile, which the first product has finished with
-//   O[128 x 128] += P V        A = P (K-major), B = the V tile taken MN-major (keys x dims as
+//   O[128 x D] += P V          A = P (K-major), B = the V tile taken MN-major (keys x dims as
 //                              stored); accumulator in TMEM for the whole item
 // The maximum that the exponentials refer to only moves when the true maximum has grown by
 // more than 2^8 since; O and the sum are then rescaled (TMEM load, multiply, store).  Between
 // such moves P may reach 2^8, which bf16 holds as well as it holds 1.
 // Warps 0-3 softmax and epilogue, warp 4 lane 0 the K/V producer, warp 5 lane 0 the MMA issuer
-// (warp 5 owns the tensor memory).  Two CTAs fit on an SM (96 KB and 256 TMEM columns each), so
+// (warp 5 owns the tensor memory).  Two CTAs fit on an SM (96 KB at head size 128 and 256 TMEM columns each), so
 // one CTA's products run under the other's exponentials.
 // ---------------------------------------------------------------------------------------------
 constexpr int TC_ROWS = 128;
 constexpr int TC_THREADS = 192;
 constexpr uint32_t TC_Q_BYTES = TC_ROWS * D * 2;          // two panels of [128 rows x 128 bytes]
-constexpr uint32_t TC_KV_BYTES = B_BN * D * 2;            // a K or V tile (and a P tile: 128 x 64 bf16)
-constexpr uint32_t TC_STAGE_BYTES = 2 * TC_KV_BYTES;
+constexpr uint32_t TC_KV_BYTES = B_BN * D * 2;            // a K or V tile
+constexpr uint32_t TC_P_BYTES = TC_ROWS * B_BN * 2;       // a P tile where it lies over the K tile
+// The K tile's place in a stage also holds P (the form with P in shared memory): the larger of the two.
+constexpr uint32_t TC_KP_BYTES = TC_KV_BYTES > TC_P_BYTES ? TC_KV_BYTES : TC_P_BYTES;
+constexpr uint32_t TC_STAGE_BYTES = TC_KP_BYTES + TC_KV_BYTES;
 __host__ __device__ constexpr size_t tc_smem_bytes(int stages) { return TC_Q_BYTES + (size_t)stages * TC_STAGE_BYTES; }
-constexpr uint32_t TC_TMEM_COLS = 256;                    // S in columns 0..63, O in 64..191
+constexpr uint32_t TC_TMEM_COLS = 256;                    // S in columns 0..63, O behind it (D columns), then P
 constexpr float TC_RESCALE_AT = 8.0f;                     // log2 units
 
 __device__ __forceinline__ uint64_t tc_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
@@ -1818,8 +1822,9 @@ __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_ke
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_s = tmem_slot;         // S: 64 columns
-  const uint32_t tmem_o = tmem_slot + 64u;   // O: 128 columns
-  const uint32_t tmem_p = tmem_slot + 192u;  // P (P_TMEM): two buffers of 32 columns
+  const uint32_t tmem_o = tmem_slot + 64u;   // O: D columns
+  const uint32_t tmem_p = tmem_slot + 64u + (uint32_t)D;  // P (P_TMEM): two buffers of 32 columns
+  static_assert(64 + D + 64 <= (int)TC_TMEM_COLS, "S, O and two P buffers do not fit the allocation");
 
   // Row state of the softmax threads (valid for warps 0-3).
   const int r = (int)threadIdx.x;  // row of the tile, TMEM lane
@@ -1843,10 +1848,10 @@ __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_ke
         produce_tc_half(a, k_s, smem_u32(&kv_full[st]), 0, table, table_s, first_block, last_block, n0, kvh, lane);
         if (round > 0 && alive)
           alive = mbar_wait(smem_u32(&v_empty[st]), (uint32_t)(round - 1) & 1u, a.status);
-        produce_tc_half(a, k_s + B_BN * D, smem_u32(&v_full[st]), 1, table, table_s, first_block, last_block, n0,
+        produce_tc_half(a, k_s + TC_KP_BYTES / 2, smem_u32(&v_full[st]), 1, table, table_s, first_block, last_block, n0,
                         kvh, lane);
       } else {
-        produce_kv_tile(a, k_s, k_s + B_BN * D, smem_u32(&kv_full[st]), table, table_s, first_block, last_block,
+        produce_kv_tile(a, k_s, k_s + TC_KP_BYTES / 2, smem_u32(&kv_full[st]), table, table_s, first_block, last_block,
                         n0, kv_end, kvh, lane);
       }
     }
@@ -1877,7 +1882,7 @@ __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_ke
       if (ok && num_tiles > 0) ok = first_product(0);
       for (int t = 0; t < num_tiles && ok; ++t) {
         const int st = t % TC_STAGES;
-        const uint32_t k_addr = stage_addr + st * TC_STAGE_BYTES, v_addr = k_addr + TC_KV_BYTES;
+        const uint32_t k_addr = stage_addr + st * TC_STAGE_BYTES, v_addr = k_addr + TC_KP_BYTES;
         // The next tile's scores are made while this tile's exponentials run.
         if (t + 1 < num_tiles) ok = first_product(t + 1);
         if (!ok) break;
@@ -2088,7 +2093,7 @@ __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_ke
     finish_split<(int)tc_smem_bytes(TC_STAGES)>(a, merge_index, num_splits, merge_item, kvh,
                                      reinterpret_cast<float*>(smem_al), &merge_bar);
 }
-#endif  // VX_HEAD_DIM == 128
+#endif  // VX_HEAD_DIM == 128 || VX_HEAD_DIM == 64
 
 }  // namespace vx
 
@@ -2179,7 +2184,7 @@ VX_API int vx_attn_tile_rows(int kind) { return kind == 3 ? 128 : (kind == 1 ? 6
 
 // Whether this head size has the tensor-memory family (kind 3, 128-row tiles).
 VX_API int vx_attn_has_tc() {
-#if VX_HEAD_DIM == 128
+#ifdef VX_HAS_TC_ATTENTION
   return 1;
 #else
   return 0;
@@ -2272,7 +2277,7 @@ VX_API int vx_attention(int kind, const void* q, void* out, const void* k_cache,
       cudaError_t e = cudaLaunchKernelEx(&config, attn_narrow_kernel<NARROW_STAGES>, a);
       if (e != cudaSuccess) return (int)e;
     }
-#if VX_HEAD_DIM == 128
+#ifdef VX_HAS_TC_ATTENTION
   } else if (kind == 3) {
     static bool configured = false;
     if (!configured) {
