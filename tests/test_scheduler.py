@@ -912,3 +912,37 @@ def test_planner_splits_tensor_memory_tiles_only_into_long_ranges():
     narrow = ap.plan_attention([1], [2048], ap.PlanOptions(num_kv_heads=2, group=6, window=None, use_f32=False,
                                                            target_ctas=296, narrow_max_cluster=1))
     assert len(narrow.merge_items) == 1 and len(narrow.items[ap.KIND_BF16_NARROW]) == 8
+
+
+def test_pipelined_step_that_cannot_be_queued_keeps_the_step_before():
+    """The runner refuses a step (here: once, by raising): the error goes to the caller, the step
+    that was on its way is still handed out by ``drain``, and the loop can go on."""
+    scheduler, cache = make(num_pages=40, page_size=4, max_num_seqs=3, budget=16, chunk=8, max_model_len=64)
+
+    class FakeRunner:
+        fail_at = 2
+        calls = 0
+
+        def step(self, chunks, capture=True):
+            FakeRunner.calls += 1
+            if FakeRunner.calls == FakeRunner.fail_at:
+                raise ValueError("no room for this step")
+            return [c.seq.seq_id for c in chunks if c.want]
+
+    class FakeSampler:
+        def sample(self, logits, params, names, draw_indices, slots=None, history_lengths=None, status=None):
+            return FakeTokens([30 + index for index in draw_indices])
+
+    engine = fake_engine(scheduler, cache, FakeRunner(), FakeSampler())
+    a = Request("a", [1, 2, 3], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+    engine.add_request(a)
+    engine.step_pipelined()
+    with pytest.raises(ValueError, match="no room"):
+        engine.step_pipelined()
+    assert engine._flight is not None and a.output_token_ids == []
+    engine.drain()
+    assert a.output_token_ids == [30]
+    engine.generate([])
+    assert a.output_token_ids == [30, 31, 32, 33] and a.finish_reason is FinishReason.LENGTH
+    scheduler.schedule()
+    assert cache.num_free_pages() == cache.num_total_pages

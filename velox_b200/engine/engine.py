@@ -404,7 +404,12 @@ class Engine:
             if any(r.sampling_params.has_penalties for r in previous.sampled):
                 self._finish_flight(previous)
                 previous = None
-        flight = self._launch(ahead=True)
+        try:
+            flight = self._launch(ahead=True)
+        except BaseException:
+            # The step before is still on its way and booked: drain() hands its tokens out.
+            self._flight = previous
+            raise
         if previous is not None:
             self._finish_flight(previous, queued_behind=flight)
         self._flight = flight
