@@ -44,6 +44,10 @@ MODEL_1P5B = {
 FULL_LAYERS = 28
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
+# Untimed decode steps in front of every timed decode region, beyond --warmup, in both arms: the
+# first few dozen steps after a pause of the device run some 5 % slower than the ones that follow
+# (measured: 1.45, 1.38, then 1.355 ms a step over three windows of 20 steps in a row).
+SETTLE_STEPS = 40
 # Keys per cache page: the benchmark configuration's (and the reference's default).  The engine's own
 # default is 64; a point with 64-key pages is reported beside the main numbers.
 BLOCK_SIZE = 16
@@ -220,6 +224,8 @@ def run_own(args):
         for _ in range(warmup):
             tokens = one_step(tokens).tolist()
         fed = [-1 - row for row in range(batch)]
+        for _ in range(SETTLE_STEPS):
+            one_step(fed)
         launches_before = kernels.launch_count + runner.kernels_replayed
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
@@ -233,12 +239,12 @@ def run_own(args):
         return [start.elapsed_time(end) / steps] * steps, kernels.launch_count + runner.kernels_replayed - launches_before
 
     def decode_point(batch, steps, warmup, engine=engine):
-        context = CONTEXT - steps - warmup - 1
+        context = CONTEXT - steps - warmup - SETTLE_STEPS - 1
         seqs = fill(batch, context, engine.runner, engine.cache)
         times, launches = decode_steps(seqs, steps, warmup, engine.runner, engine.cache, engine.sampler)
         release(seqs, engine.cache)
         ms = sum(times) / len(times)
-        return batch * 1000.0 / ms, ms, launches, context + warmup + steps // 2
+        return batch * 1000.0 / ms, ms, launches, context + warmup + SETTLE_STEPS + steps // 2
 
     E, H, G, I, V = (cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"],
                      cfg["intermediate_size"], cfg["vocab_size"])
@@ -384,7 +390,7 @@ def run_own(args):
             max_num_batched_tokens=max(PREFILL_TOKENS, args.batch), max_prefill_chunk_size=PREFILL_TOKENS,
             block_size=other, num_gpu_blocks=args.batch * (CONTEXT // other + 2) + 8, seed=0,
         ))
-        tok_s, _, _, _ = decode_point(args.batch, max(8, args.steps // 2), 3, engine=other_pages)
+        tok_s, _, _, _ = decode_point(args.batch, args.steps, args.warmup, engine=other_pages)
         points[f"decode_b{args.batch}_block{other}"] = round(tok_s, 1)
         del other_pages
     shutil.rmtree(folder, ignore_errors=True)
@@ -393,7 +399,7 @@ def run_own(args):
     # prefilled in turn, so the first request decodes while the others still prefill (two
     # portions each); max_tokens leaves every request alive until the timed steps are over.
     head_start = 2 * args.batch
-    budget = args.steps + args.warmup + head_start + 8
+    budget = args.steps + args.warmup + SETTLE_STEPS + head_start + 8
     prompts = [rng.integers(0, vocab, CONTEXT - budget).tolist() for _ in range(args.batch)]
     requests = [Request(f"e2e{i}", p, SamplingParams(temperature=0.0, max_tokens=budget, ignore_eos=True))
                 for i, p in enumerate(prompts)]
@@ -401,7 +407,7 @@ def run_own(args):
         engine.add_request(request)
     while any(not r.is_decoding or r.num_output_tokens < 1 for r in requests):
         engine.step()
-    for _ in range(args.warmup):
+    for _ in range(args.warmup + SETTLE_STEPS):
         engine.step_pipelined()
     engine.drain()
     torch.cuda.synchronize()
@@ -446,7 +452,7 @@ def run_own(args):
             "vocab": cfg["vocab_size"], "global_batch": args.batch, "seq_len": CONTEXT, "prefill_tokens": PREFILL_TOKENS,
             "kv_block_size": block_size, "kv_block_size_engine_default": ENGINE_DEFAULT_BLOCK_SIZE, "tied_embeddings": True, "parallelism": "single GPU",
             "l2": "inputs larger than L2 (weights streamed every step)",
-            "decode_steps": "queued back to back; each is fed the tokens the step before sampled, on the device", "gemm": "decode: own tcgen05 kernels; prefill: cuBLAS (library)",
+            "decode_steps": "queued back to back; each is fed the tokens the step before sampled, on the device; 40 more untimed steps before the timed ones", "gemm": "decode: own tcgen05 kernels; prefill: cuBLAS (library)",
         },
         "clocks": clock_summary,
         "e2e": e2e,
@@ -530,7 +536,7 @@ def _reference_numbers(args, ref_root):
         then ``steps`` decode steps timed on the device (events around ``step``) and ``steps``
         more by the wall clock."""
         head_start = 2 * batch
-        budget = 2 * steps + warmup + head_start + 8
+        budget = 2 * steps + warmup + SETTLE_STEPS + head_start + 8
         requests = [RefRequest(request_id=f"ref{batch}_{i}", prompt_token_ids=rng.integers(0, vocab, CONTEXT - budget).tolist(),
                                sampling_params=RefSamplingParams(temperature=0.0, max_tokens=budget, ignore_eos=True))
                     for i in range(batch)]
@@ -542,7 +548,7 @@ def _reference_numbers(args, ref_root):
             guard += 1
             if guard > 100 * batch:
                 raise RuntimeError("the reference's engine did not reach pure decoding")
-        for _ in range(warmup):
+        for _ in range(warmup + SETTLE_STEPS):
             engine.step()
         times = []
         for _ in range(steps):
@@ -618,7 +624,7 @@ def _reference_numbers(args, ref_root):
             "head_dim": cfg["hidden_size"] // cfg["num_attention_heads"], "intermediate": cfg["intermediate_size"],
             "vocab": cfg["vocab_size"], "global_batch": args.batch, "seq_len": CONTEXT, "prefill_tokens": PREFILL_TOKENS,
             "kv_block_size": ref_block, "tied_embeddings": True, "parallelism": "single GPU",
-            "timing": "CUDA events around each Engine.step of the reference (its host work included)",
+            "timing": "CUDA events around each Engine.step of the reference (its host work included); 40 more untimed steps before the timed ones",
         },
         "clocks": clock_summary,
         "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s"},
