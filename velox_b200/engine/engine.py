@@ -85,7 +85,7 @@ class _Flight:
     sampled: List[Request]                 # row r of the sampler's tokens is sampled[r]'s
     ticket: object = None                  # of the read-back of the tokens (and the status word)
     events: Optional[Tuple[torch.cuda.Event, torch.cuda.Event]] = None
-    launched_at: float = 0.0
+    sampling_host_ms: float = 0.0          # the host's time to queue sampling and read-back
     committed: bool = False
     tokens: Optional[List[int]] = None     # the sampled tokens, once they have been read
     places: List[int] = field(default_factory=list)  # where each row's token goes; -1: nowhere
@@ -284,7 +284,7 @@ class Engine:
             flight.ticket = self.readback.begin(tokens_gpu)
         if flight.events is not None:
             flight.events[1].record()
-        flight.launched_at = time.perf_counter()
+        flight.sampling_host_ms = (time.perf_counter() - t_prepare) * 1000
         return flight
 
     def _commit(self, flight: _Flight) -> None:
@@ -316,7 +316,9 @@ class Engine:
         word = tokens.pop() if len(tokens) > len(flight.sampled) else 0
         now = time.perf_counter()
         self.stats["cpu_sync_wait_ms"].append((now - sync_start) * 1000)
-        self.stats["sampling_ms"].append((now - flight.launched_at) * 1000)
+        # queueing the sampler plus the wait for its tokens (one after the other when a step is run
+        # start to end; with steps queued ahead the wait is what is left of the step before)
+        self.stats["sampling_ms"].append(flight.sampling_host_ms + (now - sync_start) * 1000)
         if flight.events is not None:
             self.stats["gpu_ms"].append(flight.events[0].elapsed_time(flight.events[1]))
         if word:
