@@ -376,3 +376,29 @@ def test_bfloat16_soak_many_requests_tight_pool(folders, pipeline):
     assert engine.cache.num_free_pages() == engine.cache.num_total_pages
     assert engine.cache.num_free_slots == engine.config.max_num_seqs
     engine.runner.check_status()
+
+
+def test_command_lines_run_on_tiny_sizes(tmp_path, capsys):
+    """The benchmark and the roofline command lines, start to end, on the tiny named sizes:
+    pipelined and one step at a time, greedy and with candidate filters, and the JSON they write."""
+    import json
+
+    from velox_b200.cli import benchmark, roofline
+
+    out = tmp_path / "bench.json"
+    common = ["--model-size", "tiny-b", "--num-requests", "6", "--max-tokens", "12", "--max-model-len", "128",
+              "--max-num-seqs", "4", "--max-num-batched-tokens", "64", "--max-prefill-chunk-size", "16",
+              "--block-size", "8", "--workload", "short", "--seed", "3"]
+    assert benchmark.main(common + ["--temperature", "0", "--output-json", str(out)]) == 0
+    first = capsys.readouterr().out
+    assert "decode throughput" in first and "GPU-busy fraction" in first
+    record = json.loads(out.read_text())
+    assert record
+    assert benchmark.main(common + ["--temperature", "0.8", "--top-p", "0.9", "--top-k", "20", "--no-pipeline"]) == 0
+    assert "decode throughput" in capsys.readouterr().out
+    table = tmp_path / "roofline.json"
+    assert roofline.main(["--model-size", "tiny-b", "--batch", "1,3", "--context", "20,60", "--layers", "1,3",
+                          "--steps", "4", "--warmup", "1", "--block-size", "8", "--output-json", str(table)]) == 0
+    rows = json.loads(table.read_text())
+    assert [(r["batch"], r["context"]) for r in rows] == [(1, 20), (1, 60), (3, 20), (3, 60)]
+    assert all(r["us_by_bytes"] > 0 and r["size"] == "tiny-b" for r in rows)
