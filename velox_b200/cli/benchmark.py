@@ -172,18 +172,28 @@ def streamed_bytes(model) -> int:
     return sum(seen.values())
 
 
-def hbm_peak_gbs() -> float:
-    """The measured copy bandwidth (``hbm_gbs`` of a ``MEASURED_PEAKS.json`` at the repository's
-    root) if that file exists, else 6,650 GB/s, an earlier measurement on a B200."""
+def _measured_peak(key: str, fallback: float) -> float:
     import os
 
     path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))),
                         "MEASURED_PEAKS.json")
     try:
         with open(path, "r", encoding="utf-8") as handle:
-            return float(json.load(handle)["hbm_gbs"])
+            return float(json.load(handle)[key])
     except (OSError, KeyError, ValueError):
-        return 6650.0
+        return fallback
+
+
+def hbm_peak_gbs() -> float:
+    """The measured copy bandwidth (``hbm_gbs`` of a ``MEASURED_PEAKS.json`` at the repository's
+    root) if that file exists, else 6,650 GB/s, an earlier measurement on a B200."""
+    return _measured_peak("hbm_gbs", 6650.0)
+
+
+def bf16_peak_tflops() -> float:
+    """The measured library bf16 matrix-product rate (``bf16_tflops`` of the same file), else
+    1,590 TFLOP/s, an earlier measurement on a B200."""
+    return _measured_peak("bf16_tflops", 1590.0)
 
 
 def roofline(engine, result: Dict[str, object]) -> Dict[str, float]:

@@ -85,6 +85,35 @@ def splits_through_memory(span, cluster: int, opt: PlanOptions):
     return fine if coarse >= 2 else 1
 
 
+def tc_uniform_splits(num_tiles: int, mean_span: float, opt: PlanOptions) -> int:
+    """How many key ranges every long tile of the tensor-memory family is cut into, by what the
+    launch is then expected to take.  Its CTAs run two to an SM (``target_ctas`` places) and walk a
+    64-key tile in about 1.46 us that way, 0.9 us alone on an SM; a launch takes as many rounds as
+    its CTAs need places, each as long as one CTA's run of tiles, and splitting costs about 30 us
+    (partial rows written in float32, read again and merged by the last CTA of every tile, at the
+    end of the launch).  Filling the places only by whole multiples ("as many splits as fit at
+    once") leaves 160 tiles x heads of a 512-token portion on 296 places unsplit at 0.54 of the
+    device; three splits run in two rounds of a third of the length.  A larger count is taken
+    only where it is expected to save a tenth (measured: a 2,048-token portion behind 2,048 keys
+    is 5 % slower in three splits than in none, behind 30,000 keys 38 % faster)."""
+    ctas = num_tiles * opt.num_kv_heads
+    tiles = max(mean_span, 1.0) / KEY_TILE
+    places = max(opt.target_ctas, 1)
+    alone = max(places // 2, 1)
+    least = max(opt.tc_min_split_keys, opt.min_split_keys, 1)
+    most = int(min(opt.max_splits, 16, max(mean_span // least, 1)))
+    best, best_cost = 1, None
+    for count in range(1, most + 1):
+        total = ctas * count
+        per_cta = tiles / count
+        cost = per_cta * 0.9 if total <= alone else -(-total // places) * per_cta * 1.46
+        if count > 1:
+            cost += 30.0
+        if best_cost is None or cost < 0.9 * best_cost:
+            best, best_cost = count, cost
+    return best
+
+
 def choose_cluster(opt: PlanOptions, pairs: int, wanted: int) -> int:
     """Cluster size for the narrow kind when `pairs` (tile, KV head) pairs each want `wanted`
     CTAs: the largest allowed power of two that is not more than wanted and fits in one wave."""
@@ -178,6 +207,12 @@ def _plan_with_arrays(q_lens: Sequence[int], kv_lens: Sequence[int], opt: PlanOp
     least = np.where(kind_of == KIND_BF16_TC, max(opt.tc_min_split_keys, opt.min_split_keys, 1), max(opt.min_split_keys, 1))
     per_tile = np.minimum(target // max(base_ctas, 1), span // least)
     wanted = np.where(base_ctas >= target, 1, np.maximum(1, per_tile))
+    on_tc = kind_of == KIND_BF16_TC
+    if on_tc.any():
+        # The tensor-memory family's launch is its own: one count for all its tiles, by the
+        # expected time of the launch; a tile gets it as far as its own key range allows.
+        uniform = tc_uniform_splits(int(on_tc.sum()), float(span[on_tc].mean()), opt)
+        wanted = np.where(on_tc, np.maximum(1, np.minimum(uniform, span // least)), wanted)
 
     cluster = 1
     if opt.narrow_max_cluster > 1 and narrow.any():
@@ -269,9 +304,14 @@ def plan_attention_plain(
             tiles.append((kind, seq, row_begin, row_count, lo, hi))
 
     base_ctas = len(tiles) * opt.num_kv_heads
+    tc_spans = [hi - lo for kind, _, _, _, lo, hi in tiles if kind == KIND_BF16_TC]
+    tc_uniform = tc_uniform_splits(len(tc_spans), sum(tc_spans) / len(tc_spans), opt) if tc_spans else 1
 
     def wanted_ctas(kind: int, span: int) -> int:
         """CTAs a tile's key range should be spread over so that the step fills the GPU."""
+        if kind == KIND_BF16_TC:
+            least = max(opt.tc_min_split_keys, opt.min_split_keys, 1)
+            return max(1, min(tc_uniform, span // least))
         target = opt.target_ctas
         if kind == KIND_BF16_NARROW and opt.narrow_target_ctas is not None:
             target = opt.narrow_target_ctas
