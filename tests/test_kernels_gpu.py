@@ -224,7 +224,7 @@ def plain_paged_attention(q, k_all, v_all, ctx, scale, window):
 
 def run_attention_case(k, dtype, H, G, D, P, seqs, window=None, seed=0, min_split_keys=256,
                        target_ctas=296, spike=None, fused_merge=True, max_cluster=1, max_splits=64,
-                       tensor_memory=False, ramp=None, tc_ctas_per_sm=1):
+                       tensor_memory=False, ramp=None, tc_ctas_per_sm=1, tc_merge_us=30.0):
     """seqs: list of (q_len, ctx_len).  Returns (got, want) as float64 [T, H, D]."""
     from velox_b200.ops import attention_plan as ap
 
@@ -276,7 +276,8 @@ def run_attention_case(k, dtype, H, G, D, P, seqs, window=None, seed=0, min_spli
     plan = ap.plan_attention(
         q_lens, kv_lens,
         ap.PlanOptions(num_kv_heads=G, group=group, window=window, use_f32=dtype == torch.float32,
-                       min_split_keys=min_split_keys, tc_min_split_keys=min_split_keys, target_ctas=target_ctas,
+                       min_split_keys=min_split_keys, tc_min_split_keys=min_split_keys, tc_merge_us=tc_merge_us,
+                       target_ctas=target_ctas,
                        narrow_max_cluster=max_cluster, max_splits=max_splits,
                        narrow_global_split_keys=min_split_keys, wide_on_tensor_memory=tensor_memory),
     )
@@ -412,7 +413,8 @@ def test_attention_on_tensor_memory_rescales_when_the_maximum_grows(k, per_sm, D
 def test_attention_on_tensor_memory_split_key_ranges(k, per_sm, D):
     seqs = [(100, 1500), (130, 700)]
     got, want, plan = run_attention_case(k, torch.bfloat16, 12, 2, D, 16, seqs, seed=9, min_split_keys=64,
-                                         target_ctas=10_000, tensor_memory=True, tc_ctas_per_sm=per_sm)
+                                         target_ctas=10_000, tensor_memory=True, tc_ctas_per_sm=per_sm,
+                                         tc_merge_us=0.0)
     assert len(plan.merge_items) > 0
     err = (got - want).abs().max().item()
     assert err <= _attn_tol(torch.bfloat16) * want.abs().max().item(), err

@@ -1765,6 +1765,18 @@ __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_ke
   unsigned char* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t q_addr = smem_base;
   const uint32_t stage_addr = smem_base + TC_Q_BYTES;  // stage st: K at + st * TC_STAGE_BYTES, V after
+#ifdef VX_TRACE
+  // Cycles of the MMA issuer: 0 waiting on barriers, 1 issuing first products, 2 second products, 3 commits.
+  __shared__ long long mma_cycles[4];
+  long long mma_tick = 0;
+#define TC_MMA_WAIT(call) [&] { const long long from = clock64(); const bool got = (call); mma_cycles[0] += clock64() - from; return got; }()
+#define TC_MMA_TICK() { mma_tick = clock64(); }
+#define TC_MMA_TOCK(i) { const long long now = clock64(); mma_cycles[i] += now - mma_tick; mma_tick = now; }
+#else
+#define TC_MMA_WAIT(call) (call)
+#define TC_MMA_TICK()
+#define TC_MMA_TOCK(i)
+#endif
 
   VX_TRACE_SCOPE(23);
   allow_dependents();
@@ -1811,6 +1823,9 @@ __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_ke
     mbar_init(smem_u32(&merge_bar), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+#ifdef VX_TRACE
+    for (int i = 0; i < 4; ++i) mma_cycles[i] = 0;
+#endif
   }
   if (warp == 5) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -1865,18 +1880,21 @@ __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_ke
       auto first_product = [&](int t) -> bool {
         const int st = t % TC_STAGES, round = t / TC_STAGES;
         const uint32_t k_addr = stage_addr + st * TC_STAGE_BYTES;
-        if (!mbar_wait(smem_u32(&kv_full[st]), (uint32_t)round & 1u, a.status)) return false;
+        if (!TC_MMA_WAIT(mbar_wait(smem_u32(&kv_full[st]), (uint32_t)round & 1u, a.status))) return false;
         // The softmax threads have S of the tile before in registers.
-        if (t > 0 && !mbar_wait(smem_u32(&s_free), (uint32_t)(t - 1) & 1u, a.status)) return false;
+        if (t > 0 && !TC_MMA_WAIT(mbar_wait(smem_u32(&s_free), (uint32_t)(t - 1) & 1u, a.status))) return false;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        TC_MMA_TICK();
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t qa = q_addr + (kk >> 2) * (TC_ROWS * 128) + (kk & 3) * 32;
           const uint32_t kb = k_addr + (kk >> 2) * (B_BN * 128) + (kk & 3) * 32;
           tc_mma(tmem_s, tc_desc(qa, 0, 1024), tc_desc(kb, 0, 1024), idesc_qk, kk > 0 ? 1u : 0u);
         }
+        TC_MMA_TOCK(1);
         tc_commit(smem_u32(&s_ready));
         if (P_TMEM) tc_commit(smem_u32(&kv_empty[st]));  // nothing else reads the K tile
+        TC_MMA_TOCK(3);
         return true;
       };
       if (ok && num_tiles > 0) ok = first_product(0);
@@ -1886,13 +1904,14 @@ __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_ke
         // The next tile's scores are made while this tile's exponentials run.
         if (t + 1 < num_tiles) ok = first_product(t + 1);
         if (!ok) break;
-        ok = mbar_wait(smem_u32(&p_ready), (uint32_t)t & 1u, a.status);
+        ok = TC_MMA_WAIT(mbar_wait(smem_u32(&p_ready), (uint32_t)t & 1u, a.status));
         if (!ok) break;
         if (P_TMEM) {
-          ok = mbar_wait(smem_u32(&v_full[st]), (uint32_t)(t / TC_STAGES) & 1u, a.status);
+          ok = TC_MMA_WAIT(mbar_wait(smem_u32(&v_full[st]), (uint32_t)(t / TC_STAGES) & 1u, a.status));
           if (!ok) break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        TC_MMA_TICK();
         // O += P V: four steps of 16 keys.  P lies over the K tile (one panel of [128 x 128 B])
         // or in tensor memory (eight columns a step); V is [64 keys x 128 dims]: MN-major B, 16
         // keys are two groups of eight rows (2 KB), the second 64 dims are the next panel (8 KB on).
@@ -1907,8 +1926,10 @@ __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_ke
             tc_mma(tmem_o, tc_desc(pa, 0, 1024), tc_desc(vb, B_BN * 128, 1024), idesc_pv,
                    (t > 0 || ks > 0) ? 1u : 0u);
         }
+        TC_MMA_TOCK(2);
         tc_commit(smem_u32(P_TMEM ? &v_empty[st] : &kv_empty[st]));
         tc_commit(smem_u32(&pv_done));
+        TC_MMA_TOCK(3);
       }
     }
   } else {
@@ -1936,11 +1957,21 @@ __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_ke
     const int vis_lo = max(kv_begin, a.window > 0 ? pos - a.window + 1 : 0);
     const unsigned vis_span = pos < 0 ? 0u : (unsigned)max(0, min(kv_end, pos + 1) - vis_lo);
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+#ifdef VX_TRACE
+    // Cycles of the softmax threads' four phases, summed over the tiles (thread 0 reports them
+    // in the low words of the event's marks; the high words are the MMA issuer's).
+    long long phase_cycles[4] = {0, 0, 0, 0};
+    long long tick = clock64();
+#define TC_PHASE(i) { const long long now = clock64(); phase_cycles[i] += now - tick; tick = now; }
+#else
+#define TC_PHASE(i)
+#endif
     for (int t = 0; t < num_tiles; ++t) {
       const int st = t % TC_STAGES;
       const int n0 = n_first + t * B_BN;
       if (!failed) failed = !mbar_wait(smem_u32(&s_ready), (uint32_t)t & 1u, a.status);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      TC_PHASE(0);  // waiting for the scores
       float s[B_BN];
       {
         float half[32];
@@ -1955,6 +1986,7 @@ __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_ke
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&s_free));
+      TC_PHASE(1);  // the scores into registers
       // Most tiles lie wholly inside what every row of the warp may see: no masks then.  The
       // scores stay unscaled; the scale goes into the exponent's multiply-add.
       const bool row_sees_all = pos >= 0 && n0 >= kv_begin && n0 + B_BN <= kv_end && n0 + B_BN - 1 <= pos &&
@@ -2004,6 +2036,7 @@ __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_ke
         m_ref = m_new;
       }
       const float neg_m = m_ref == -CUDART_INF_F ? 0.f : -m_ref;
+      TC_PHASE(2);  // masks, maximum, rescaling
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
       if (P_TMEM) {
         // This tile's buffer was last read by the product of two tiles ago, which was observed
@@ -2045,7 +2078,11 @@ __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_ke
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&p_ready));
+      TC_PHASE(3);  // exponentials, P stored and announced
     }
+#ifdef VX_TRACE
+    for (int i = 0; i < 4; ++i) VX_TRACE_SET(i, (unsigned long long)phase_cycles[i] & 0xffffffffull);
+#endif
     // Epilogue: O / l to the output, or to the partial rows of a split.
     if (num_tiles > 0 && !failed) failed = !mbar_wait(smem_u32(&pv_done), (uint32_t)(num_tiles - 1) & 1u, a.status);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -2084,6 +2121,11 @@ __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_ke
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   }
   __syncthreads();
+#ifdef VX_TRACE
+  if (threadIdx.x == 0)
+    for (int i = 0; i < 4; ++i)
+      VX_TRACE_SET(i, vx_trace_scope_.marks[i] | ((unsigned long long)mma_cycles[i] << 32));
+#endif
   if (warp == 5) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_slot), "r"(TC_TMEM_COLS)

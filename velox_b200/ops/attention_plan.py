@@ -54,6 +54,9 @@ class PlanOptions:
     # (a 512-token portion alone in the cache: 22.7 us a layer with splits of 256 keys, 13.5
     # without any).
     tc_min_split_keys: int = 1024
+    # What cutting that family's key ranges is expected to cost a launch, in microseconds (the
+    # partial rows written and read again, the merge by the last CTA of every tile).
+    tc_merge_us: float = 30.0
     max_splits: int = 64
     # Portions with at most this many rows use the narrow (16-row) bf16 family.
     narrow_max_rows: int = 64
@@ -89,7 +92,7 @@ def tc_uniform_splits(num_tiles: int, mean_span: float, opt: PlanOptions) -> int
     """How many key ranges every long tile of the tensor-memory family is cut into, by what the
     launch is then expected to take.  Its CTAs run two to an SM (``target_ctas`` places) and walk a
     64-key tile in about 1.46 us that way, 0.9 us alone on an SM; a launch takes as many rounds as
-    its CTAs need places, each as long as one CTA's run of tiles, and splitting costs about 30 us
+    its CTAs need places, each as long as one CTA's run of tiles, and splitting costs ``tc_merge_us``
     (partial rows written in float32, read again and merged by the last CTA of every tile, at the
     end of the launch).  Filling the places only by whole multiples ("as many splits as fit at
     once") leaves 160 tiles x heads of a 512-token portion on 296 places unsplit at 0.54 of the
@@ -108,7 +111,7 @@ def tc_uniform_splits(num_tiles: int, mean_span: float, opt: PlanOptions) -> int
         per_cta = tiles / count
         cost = per_cta * 0.9 if total <= alone else -(-total // places) * per_cta * 1.46
         if count > 1:
-            cost += 30.0
+            cost += opt.tc_merge_us
         if best_cost is None or cost < 0.9 * best_cost:
             best, best_cost = count, cost
     return best
