@@ -1,6 +1,8 @@
 """Generation through the Python entry point: greedy tokens against the plain implementation,
 batched against one at a time, preemption under page pressure, seeded sampling, limits."""
 import numpy as np
+import os
+
 import pytest
 import torch
 
@@ -402,3 +404,24 @@ def test_command_lines_run_on_tiny_sizes(tmp_path, capsys):
     rows = json.loads(table.read_text())
     assert [(r["batch"], r["context"]) for r in rows] == [(1, 20), (1, 60), (3, 20), (3, 60)]
     assert all(r["us_by_bytes"] > 0 and r["size"] == "tiny-b" for r in rows)
+    assert roofline.main(["--model-size", "tiny-b", "--prefill", "24,70", "--context", "0,50", "--layers", "1,3",
+                          "--warmup", "1", "--block-size", "8", "--output-json", str(table)]) == 0
+    rows = json.loads(table.read_text())
+    assert [(r["tokens"], r["context"]) for r in rows] == [(24, 0), (24, 50), (70, 0), (70, 50)]
+    assert all(r["tflops"] >= 0 for r in rows)
+
+
+def test_timeline_command_line_runs_on_a_tiny_size():
+    """The timeline build (kernels compiled with their CTA trace) through its command line, in a
+    process of its own because the build flag is read when the libraries are loaded: a decode
+    step and a prompt portion, every launch listed with its CTAs."""
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for mode in (["--batch", "3", "--context", "40"], ["--prefill", "70", "--context", "30"]):
+        done = subprocess.run([sys.executable, "-m", "velox_b200.cli.timeline", "--model-size", "tiny-b", "--layers", "2",
+                               "--block-size", "8"] + mode, cwd=root, capture_output=True, text=True, timeout=600)
+        assert done.returncode == 0, done.stdout[-2000:] + done.stderr[-2000:]
+        assert "launches" in done.stdout and "by kernel and grid" in done.stdout
+        assert "attn" in done.stdout and "gemm" in done.stdout
