@@ -1746,6 +1746,32 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// Two multiply-adds, or two additions, in one instruction (the packed float32 forms of sm_100):
+// the softmax threads are bound by the instructions they issue, not by a pipe.
+__device__ __forceinline__ void fma_pair(float& x0, float& x1, float a0, float a1, float b, float c) {
+  asm("{\n"
+      ".reg .b64 ra, rb, rc, rd;\n"
+      "mov.b64 ra, {%2, %3};\n"
+      "mov.b64 rb, {%4, %4};\n"
+      "mov.b64 rc, {%5, %5};\n"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n"
+      "mov.b64 {%0, %1}, rd;\n"
+      "}"
+      : "=f"(x0), "=f"(x1)
+      : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
+__device__ __forceinline__ void add_pair(float& s0, float& s1, float a0, float a1) {
+  asm("{\n"
+      ".reg .b64 ra, rs;\n"
+      "mov.b64 ra, {%2, %3};\n"
+      "mov.b64 rs, {%0, %1};\n"
+      "add.rn.f32x2 rs, rs, ra;\n"
+      "mov.b64 {%0, %1}, rs;\n"
+      "}"
+      : "+f"(s0), "+f"(s1)
+      : "f"(a0), "f"(a1));
+}
+
 // TC_STAGES = 2: two CTAs per SM, for grids of several waves; 4: one CTA per SM with a deeper
 // K/V ring, for grids where an SM gets one CTA anyway and nothing else hides the copies' latency.
 // P_TMEM: the probabilities go back to tensor memory (two buffers of 32 columns, two bf16 to a
@@ -2047,10 +2073,10 @@ __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_ke
           uint32_t words[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            const float p0 = fast_exp2(fmaf(s[half * 32 + 2 * i], a.scale_log2, neg_m));
-            const float p1 = fast_exp2(fmaf(s[half * 32 + 2 * i + 1], a.scale_log2, neg_m));
-            sum4[i & 1] += p0;
-            sum4[2 + (i & 1)] += p1;
+            float x0, x1;
+            fma_pair(x0, x1, s[half * 32 + 2 * i], s[half * 32 + 2 * i + 1], a.scale_log2, neg_m);
+            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+            add_pair(sum4[2 * (i & 1)], sum4[2 * (i & 1) + 1], p0, p1);
             words[i] = pack_bf16(p0, p1);
           }
           tc_store16_words(p_at + (uint32_t)half * 16u, words);
@@ -2062,9 +2088,12 @@ __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_ke
         for (int c = 0; c < B_BN / 8; ++c) {
           float p[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            p[i] = fast_exp2(fmaf(s[c * 8 + i], a.scale_log2, neg_m));
-            sum4[i & 3] += p[i];
+          for (int i = 0; i < 8; i += 2) {
+            float x0, x1;
+            fma_pair(x0, x1, s[c * 8 + i], s[c * 8 + i + 1], a.scale_log2, neg_m);
+            p[i] = fast_exp2(x0);
+            p[i + 1] = fast_exp2(x1);
+            add_pair(sum4[i & 2], sum4[(i & 2) + 1], p[i], p[i + 1]);
           }
           const uint4 packed = make_uint4(pack_bf16(p[0], p[1]), pack_bf16(p[2], p[3]), pack_bf16(p[4], p[5]),
                                           pack_bf16(p[6], p[7]));
