@@ -776,7 +776,7 @@ def test_split_and_chunk_choices_fill_the_gpu_without_overfilling():
                 token_tiles = 1 if rows <= 64 else -(-rows // (128 if rows <= 128 else 256))
                 tiles = -(-n // 128) * token_tiles
                 assert chunks >= 1 and (chunks == 1 or tiles * chunks <= 148 * per_sm)
-                assert chunks == 1 or -(-k // 64) // chunks >= 4  # at least four K blocks a chunk
+                assert chunks == 1 or -(-k // 64) // chunks >= 2  # at least two K blocks a chunk
     finally:
         linear._NUM_SMS = None
 

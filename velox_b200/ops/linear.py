@@ -85,12 +85,13 @@ def choose_chunks(out_features: int, in_features: int, num_rows: int, tile: int 
     """Ranges of the inner dimension for ``kernels.gemm_bf16_add_chunked``: enough CTAs for two
     per SM with at most 32 tokens and one per SM with more (measured: the down projection of the
     14B sizes at 64 tokens takes 49 us as 40 x 3 CTAs, 67 us as 40 clusters of two), each with
-    at least four 64-wide blocks."""
+    at least two 64-wide blocks (the output projection of the 1.5B sizes at 64 tokens, alone with
+    a cold L2: 9.9 us as 12 x 6 CTAs of four blocks, 8.7 us as 12 x 12 of two)."""
     token_tile = 16 if num_rows <= 16 else 32 if num_rows <= 32 else 64 if num_rows <= 64 else 128 if num_rows <= 128 else 256
     tiles = max(1, -(-out_features // tile)) * max(1, -(-num_rows // token_tile))
     room = _num_sms() * (2 if num_rows <= 32 else 1)
     blocks = -(-in_features // 64)
-    return max(1, min(room // tiles, blocks // 4))
+    return max(1, min(room // tiles, blocks // 2))
 
 
 def linear(
