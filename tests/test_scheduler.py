@@ -912,6 +912,19 @@ def test_planner_splits_tensor_memory_tiles_only_into_long_ranges():
     narrow = ap.plan_attention([1], [2048], ap.PlanOptions(num_kv_heads=2, group=6, window=None, use_f32=False,
                                                            target_ctas=296, narrow_max_cluster=1))
     assert len(narrow.merge_items) == 1 and len(narrow.items[ap.KIND_BF16_NARROW]) == 8
+    # The count follows the expected time of the launch, not what fits at once: 192 CTAs with
+    # 31,000 keys each run 38 % faster as three thirds in two rounds; behind 2,048 keys the merge
+    # costs more than the rounds save; the 160 CTAs of a 512-token portion with 8 KV heads, which
+    # would leave 136 places idle, are cut in seven (four rounds of a seventh of the length).
+    assert ap.tc_uniform_splits(96, 31024.0, opt) == 3
+    assert ap.tc_uniform_splits(96, 3072.0, opt) == 1
+    wide = ap.PlanOptions(num_kv_heads=8, group=5, window=None, use_f32=False, wide_on_tensor_memory=True,
+                          target_ctas=296)
+    assert ap.tc_uniform_splits(20, 30256.0, wide) == 7
+    # a merge that costs nothing: as many ranges as the least length allows
+    free = ap.PlanOptions(num_kv_heads=2, group=6, window=None, use_f32=False, wide_on_tensor_memory=True,
+                          target_ctas=10_000, tc_min_split_keys=64, min_split_keys=64, tc_merge_us=0.0)
+    assert ap.tc_uniform_splits(12, 1200.0, free) > 4
 
 
 def test_pipelined_step_that_cannot_be_queued_keeps_the_step_before():

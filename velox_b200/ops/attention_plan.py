@@ -96,9 +96,11 @@ def tc_uniform_splits(num_tiles: int, mean_span: float, opt: PlanOptions) -> int
     (partial rows written in float32, read again and merged by the last CTA of every tile, at the
     end of the launch).  Filling the places only by whole multiples ("as many splits as fit at
     once") leaves 160 tiles x heads of a 512-token portion on 296 places unsplit at 0.54 of the
-    device; three splits run in two rounds of a third of the length.  A larger count is taken
-    only where it is expected to save a tenth (measured: a 2,048-token portion behind 2,048 keys
-    is 5 % slower in three splits than in none, behind 30,000 keys 38 % faster)."""
+    device; three splits run in two rounds of a third of the length, seven in four rounds of a
+    seventh (measured at those sizes behind 30,000 keys: 586 us unsplit, 413 in three, 408 in
+    seven).  A larger count is taken only where it is expected to save a tenth (measured: a
+    2,048-token portion behind 2,048 keys is 5 % slower in three splits than in none, behind
+    30,000 keys 38 % faster)."""
     ctas = num_tiles * opt.num_kv_heads
     tiles = max(mean_span, 1.0) / KEY_TILE
     places = max(opt.target_ctas, 1)
