@@ -959,3 +959,49 @@ def test_pipelined_step_that_cannot_be_queued_keeps_the_step_before():
     assert a.output_token_ids == [30, 31, 32, 33] and a.finish_reason is FinishReason.LENGTH
     scheduler.schedule()
     assert cache.num_free_pages() == cache.num_total_pages
+
+
+def test_roofline_command_counts_a_portions_operations():
+    """Two operations per weight and token, four per query, key and head dimension under the
+    causal mask (a token sees the context and, on average, half of its own portion)."""
+    from velox_b200.cli import roofline
+
+    cfg = {"hidden_size": 64, "num_attention_heads": 4, "num_key_value_heads": 2, "intermediate_size": 160, "head_dim": 32}
+    weights = 64 * (4 + 2 * 2) * 32 + 4 * 32 * 64 + 3 * 64 * 160
+    assert roofline.layer_flops(cfg, 10, 0) == 2.0 * 10 * weights + 4.0 * 10 * 5.5 * 4 * 32
+    assert roofline.layer_flops(cfg, 10, 100) - roofline.layer_flops(cfg, 10, 0) == 4.0 * 10 * 100 * 4 * 32
+
+
+def test_timeline_command_groups_ctas_into_launches():
+    """The trace is one event a CTA; a launch is as many events of one (kernel, grid) as the
+    grid has CTAs, in the order the CTAs started, whatever other kernels' CTAs lie between."""
+    import numpy as np
+
+    from velox_b200.cli import timeline
+
+    layout = np.dtype([("t0", "<u8"), ("t1", "<u8"), ("kernel", "<i4"), ("grid", "<i4"), ("block", "<i4"),
+                       ("sm", "<i4"), ("m0", "<u8"), ("m1", "<u8"), ("m2", "<u8"), ("m3", "<u8")])
+    assert layout.itemsize == timeline.EVENT_BYTES
+    rows = [(10, 20, 12, 2, 0, 0), (11, 30, 21, 3, 0, 1), (12, 22, 12, 2, 1, 2), (13, 31, 21, 3, 1, 3),
+            (14, 33, 21, 3, 2, 4), (40, 50, 12, 2, 0, 0), (41, 52, 12, 2, 1, 1), (60, 61, 21, 3, 0, 0)]
+    events = np.zeros(len(rows), dtype=layout)
+    for event, (t0, t1, kernel, grid, block, sm) in zip(events, rows):
+        event["t0"], event["t1"], event["kernel"], event["grid"], event["block"], event["sm"] = t0, t1, kernel, grid, block, sm
+    launches = timeline.group_launches(events)
+    # two whole launches of kernel 12, one of kernel 21; the lone CTA of an unfinished launch is left out
+    assert [(key, len(group)) for key, group in launches] == [((12, 2), 2), ((21, 3), 3), ((12, 2), 2)]
+    assert [int(e["t0"]) for e in launches[1][1]] == [11, 13, 14]
+    assert set(timeline.KERNEL_NAMES) >= {1, 2, 3, 10, 11, 12, 13, 14, 15, 20, 21, 22, 23}
+
+
+def test_bench_refuses_more_than_one_gpu():
+    """The engine is for one GPU: for N > 1 the benchmark prints one line that says so and exits with 2."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    done = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--gpus", "2", "--steps", "1", "--warmup", "1"],
+                          capture_output=True, text=True, timeout=300)
+    assert done.returncode == 2
+    assert len((done.stdout + done.stderr).strip().splitlines()) == 1 and "one GPU" in done.stdout + done.stderr
